@@ -1,0 +1,401 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operands
+// staged by TMA into 128-byte-swizzled shared memory).  Replaces the cuBLAS calls behind every
+// nn.Linear of the reference (its models are HF/Megatron modules: siirl/engine/fsdp_workers.py:631-744).
+//
+//   C[M,N] (+)= sum_k A[m,k] * B[n,k]
+//
+// Operand storage ("major"):
+//   A K-major : global [M, K] row-major (K contiguous)          -- activations in forward/dgrad
+//   A MN-major: global [K, M] row-major (M contiguous)          -- dy^T in wgrad
+//   B K-major : global [N, K] row-major                          -- nn.Linear weight in forward
+//   B MN-major: global [K, N] row-major                          -- weight in dgrad, x in wgrad
+//
+// Kernel shape: persistent, one CTA per SM, 6 warps:
+//   warp 0      TMA producer (one lane)          smem ring of STAGES x (A 128x64 + B BNx64)
+//   warp 1      TMEM allocator + MMA issuer      tcgen05.mma 128xBNx16, two TMEM accumulators
+//   warps 2..5  epilogue                         tcgen05.ld -> (+bias) -> bf16/fp32 -> global
+// The epilogue of tile i overlaps the main loop of tile i+1 through the two accumulators.
+#include "common.cuh"
+#include "launchers.h"
+
+namespace sb {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const __nv_bfloat16* bias;  // optional, length N (EPI_BF16 only)
+  int* status;
+  int num_m_blocks, num_n_blocks, num_k_blocks;
+};
+
+enum { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2 };
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierOffset = STAGES * kStageBytes;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
+  static constexpr int kTotalBytes = kBarrierOffset + (2 * STAGES + 4) * 8 + 16 + 1024 /*align slack*/;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m_blocks, int num_n_blocks, int& mb,
+                                            int& nb) {
+  constexpr int kGroupM = 8;
+  const int tiles_per_group = kGroupM * num_n_blocks;
+  const int group = tile / tiles_per_group;
+  const int first_m = group * kGroupM;
+  const int gm = min(kGroupM, num_m_blocks - first_m);
+  const int t = tile - group * tiles_per_group;
+  mb = first_m + t % gm;
+  nb = t / gm;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                         const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  using L = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512 (power of two)
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 128);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int last_armed[STAGES];
+#pragma unroll
+      for (int s = 0; s < STAGES; ++s) last_armed[s] = -1;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, mb, nb);
+        const int m0 = mb * kBM, n0 = nb * BN;
+        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kStatusTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb_ = sa + L::kABytes;
+          mbar_arrive_expect_tx(&full_bar[stage], L::kStageBytes);
+          last_armed[stage] = (int)phase;
+          const int k0 = kb * kBK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &map_a, &full_bar[stage], k0, m0);
+          } else {
+            tma_load_2d(sa, &map_a, &full_bar[stage], m0, k0);
+            tma_load_2d(sa + 8192, &map_a, &full_bar[stage], m0 + 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb_, &map_b, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb_ + c * 8192, &map_b, &full_bar[stage], n0 + c * 64, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // leave no bulk copy in flight into shared memory that is about to be released
+        for (int s = 0; s < STAGES; ++s)
+          if (last_armed[s] >= 0) mbar_wait(&full_bar[s], (uint32_t)last_armed[s], nullptr, 0);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusTimeoutMma)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + acc * BN;
+      for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        if (!mbar_wait(&full_bar[stage], phase, p.status, kStatusTimeoutMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb_ = sa + L::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            const uint64_t da = A_MN ? umma_smem_desc(sa + kk * 2048, 8192, 1024)
+                                     : umma_smem_desc(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_smem_desc(sb_ + kk * 2048, 8192, 1024)
+                                     : umma_smem_desc(sb_ + kk * 32, 16, 1024);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok && lane == 0) umma_commit(&tmem_full[acc]);
+      __syncwarp();
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5) ------------------------------
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int row_in_tile = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      int mb, nb;
+      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, mb, nb);
+      const int row = mb * kBM + row_in_tile;
+      const int n0 = nb * BN;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusTimeoutEpilogue)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          if constexpr (EPI == EPI_BF16) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 + 8 <= p.N) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+                if (p.bias) {
+                  uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col0 + g * 8);
+                  const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    float2 f = __bfloat1622float2(b2[i]);
+                    v[2 * i] += f.x;
+                    v[2 * i + 1] += f.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+                *reinterpret_cast<uint4*>(crow + g * 8) = o;
+              }
+            }
+          } else {
+            float* crow = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              if (col0 + g * 4 + 4 <= p.N) {
+                float4 o = make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                                       __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+                if constexpr (EPI == EPI_F32_ACC) {
+                  const float4 old = *reinterpret_cast<const float4*>(crow + g * 4);
+                  o.x += old.x;
+                  o.y += old.y;
+                  o.z += old.z;
+                  o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(crow + g * 4) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// 2-D bf16 tensor map: inner extent `inner` (contiguous), outer extent `outer` with row pitch
+// `pitch_elems`; box = box_inner x box_outer, 128-byte swizzle, zero fill out of bounds.
+int make_tensor_map_bf16_2d(CUtensorMap* map, const void* base, long long inner, long long outer,
+                            long long pitch_elems, int box_inner, int box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+static int g_num_sms = 0;
+int num_sms() {
+  if (!g_num_sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_num_sms;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int max_ctas,
+                       cudaStream_t stream) {
+  using L = GemmSmem<BN, STAGES>;
+  auto kernel = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotalBytes);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  int grid = tiles < num_sms() ? tiles : num_sms();
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  kernel<<<grid, 192, L::kTotalBytes, stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+template <int BN, int STAGES>
+static int dispatch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int a_mn, int b_mn,
+                         int epi, int max_ctas, cudaStream_t stream) {
+#define SB_CASE(AM, BM_, E)                                    \
+  if (a_mn == AM && b_mn == BM_ && epi == E)                   \
+    return launch_gemm<BN, STAGES, AM != 0, BM_ != 0, E>(ma, mb, p, max_ctas, stream);
+  SB_CASE(0, 0, EPI_BF16)
+  SB_CASE(0, 1, EPI_BF16)
+  SB_CASE(1, 1, EPI_BF16)
+  SB_CASE(1, 1, EPI_F32_ACC)
+  SB_CASE(1, 1, EPI_F32)
+  SB_CASE(0, 0, EPI_F32)
+  SB_CASE(0, 1, EPI_F32)
+#undef SB_CASE
+  return -2;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi,
+                            int tile_n, int max_ctas, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (a_mn && (M % 8))) return -3;
+  if (epi == EPI_BF16 ? (ldc % 8) : (ldc % 4)) return -3;
+  int BN = tile_n;
+  if (BN != 128 && BN != 256) {
+    // pick the tile width with the better last-wave occupancy
+    const int sms = num_sms();
+    const long long mbk = (M + kBM - 1) / kBM;
+    auto waves_cost = [&](int bn) {
+      long long tiles = mbk * ((N + bn - 1) / bn);
+      long long waves = (tiles + sms - 1) / sms;
+      return (double)waves * bn;  // time ~ waves * tile work
+    };
+    BN = (N >= 256 && waves_cost(256) <= waves_cost(128) * 1.02) ? 256 : 128;
+  }
+  CUtensorMap ma, mb;
+  int r;
+  if (!a_mn) r = make_tensor_map_bf16_2d(&ma, A, K, M, lda, kBK, kBM);
+  else r = make_tensor_map_bf16_2d(&ma, A, M, K, lda, 64, kBK);
+  if (r) return r;
+  if (!b_mn) r = make_tensor_map_bf16_2d(&mb, B, K, N, ldb, kBK, BN);
+  else r = make_tensor_map_bf16_2d(&mb, B, N, K, ldb, 64, kBK);
+  if (r) return r;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.status = status;
+  p.num_m_blocks = (M + kBM - 1) / kBM;
+  p.num_n_blocks = (N + BN - 1) / BN;
+  p.num_k_blocks = (K + kBK - 1) / kBK;
+  if (BN == 256) return dispatch_gemm<256, 4>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
+  return dispatch_gemm<128, 6>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
+}

@@ -1,0 +1,41 @@
+// Plain-C launch entry points of the sm_100a kernels.  The .cu files include no torch header
+// (fast to compile, callable from C, ctypes or the torch bindings in bindings.cpp).
+// Every function returns 0 on success, a cudaError_t / CUresult value, or a negative code:
+//   -1 driver entry point unavailable, -2 unsupported variant, -3 bad shape or alignment.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda.h>
+
+namespace sb {
+int num_sms();
+int make_tensor_map_bf16_2d(CUtensorMap* map, const void* base, long long inner, long long outer,
+                            long long pitch_elems, int box_inner, int box_outer);
+}  // namespace sb
+
+extern "C" {
+
+// ---- gemm_tcgen05.cu ----
+// C[M,N] (+)= A * B^T.  a_mn/b_mn: operand stored with the contraction index strided
+// (A as [K,M], B as [K,N]).  epi: 0 bf16 store (+bias), 1 fp32 accumulate, 2 fp32 store.
+// tile_n: 128, 256 or 0 (auto).  max_ctas: 0 = one CTA per SM.
+int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                 long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
+                 int* status, cudaStream_t stream);
+
+// ---- elementwise.cu ----
+int sb_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out, float* rstd,
+                   int T, int H, float eps, cudaStream_t stream);
+int sb_rmsnorm_bwd_blocks(int T);
+int sb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres, void* dx,
+                   float* dw_partial, float* dw, int dw_accumulate, int T, int H, cudaStream_t stream);
+int sb_rope(void* qkv, const int* pos, const float* cos_tab, const float* sin_tab, int T, int row_stride,
+            int n_heads_rot, int D, int pos_rows, int sec0, int sec1, float sign, cudaStream_t stream);
+int sb_swiglu_fwd(const void* gu, void* out, int T, int I, cudaStream_t stream);
+int sb_swiglu_bwd(const void* gu, const void* dout, void* dgu, int T, int I, cudaStream_t stream);
+int sb_embedding_fwd(const long long* ids, const void* table, void* out, int T, int H, int V,
+                     cudaStream_t stream);
+int sb_embedding_bwd(const long long* ids, const void* dout, float* dtable, int T, int H, int V,
+                     cudaStream_t stream);
+int sb_add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
+
+}  // extern "C"

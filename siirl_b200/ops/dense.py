@@ -1,0 +1,287 @@
+"""Dense transformer ops with autograd: GEMM / linear (tcgen05), RMSNorm, RoPE, SwiGLU, embedding.
+
+CUDA tensors always go to the sm_100a kernels in ``libsiirl_b200.so``; CPU tensors go to the
+plain-PyTorch statements in :mod:`siirl_b200.ops.reference` (differentiated by torch autograd).
+
+Gradient accumulation convention: a parameter may carry a ``main_grad`` attribute — an fp32 view
+into the flat gradient buffer of :class:`siirl_b200.parallel.flat_params.FlatParamStore`.  Backward
+kernels then accumulate into it directly (the weight-gradient GEMM epilogue does ``C += acc``) and
+return no ``.grad``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import lib as _lib
+from . import reference as ref
+
+EPI_BF16, EPI_F32_ACC, EPI_F32 = 0, 1, 2
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, bias: Optional[torch.Tensor] = None,
+         a_mn: bool = False, b_mn: bool = False, epi: int = EPI_BF16, tile_n: int = 0,
+         max_ctas: int = 0) -> torch.Tensor:
+    """``out[M,N] (+)= A @ B^T`` on the tensor cores.
+
+    ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` when ``b_mn``);
+    rows must be contiguous (stride(1) == 1).  ``epi``: EPI_BF16 store bf16 (+bias), EPI_F32_ACC
+    ``out += result`` in fp32, EPI_F32 store fp32.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.stride(-1) == 1 and b.stride(-1) == 1
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, (a.shape, b.shape, a_mn, b_mn)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16 if epi == EPI_BF16 else torch.float32, device=a.device)
+    assert out.shape == (M, N) and out.stride(-1) == 1
+    if not _lib.use_native(a):
+        af = a.float().t() if a_mn else a.float()
+        bf = b.float() if b_mn else b.float().t()
+        res = af @ bf
+        if bias is not None:
+            res = res + bias.float()
+        if epi == EPI_F32_ACC:
+            out += res
+        else:
+            out.copy_(res.to(out.dtype))
+        return out
+    L = _lib.get_lib()
+    rc = L.sb_gemm_bf16(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), M, N, K,
+                        ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)),
+                        ctypes.c_longlong(out.stride(0)), int(a_mn), int(b_mn), int(epi), int(tile_n),
+                        int(max_ctas), _lib.ptr(_lib.status_word(a.device)), _lib.stream())
+    _lib.check(rc, "sb_gemm_bf16")
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        ctx.bias_ref = bias
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, weight, bias=bias)
+        return y.reshape(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).reshape(x.shape)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            mg = getattr(weight, "main_grad", None)
+            if mg is not None:
+                gemm(dy2, x2, out=mg, a_mn=True, b_mn=True, epi=EPI_F32_ACC)
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, epi=EPI_F32).to(weight.dtype)
+        db = None
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            bsum = dy2.float().sum(0)
+            mgb = getattr(ctx.bias_ref, "main_grad", None)
+            if mgb is not None:
+                mgb.add_(bsum)
+            else:
+                db = bsum.to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x @ weight^T + bias`` (nn.Linear convention, weight ``[out, in]``)."""
+    if not x.is_cuda:
+        return F.linear(x, weight, bias)
+    _lib.use_native(x)
+    return _LinearFn.apply(x, weight, bias)
+
+
+# ---------------------------------------------------------------------------------------------
+# RMSNorm (+ residual)
+# ---------------------------------------------------------------------------------------------
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps):
+        L = _lib.get_lib()
+        T, H = x.shape
+        y = torch.empty_like(x)
+        h = torch.empty_like(x) if residual is not None else x
+        h_ret = h if residual is not None else torch.empty(0, dtype=x.dtype, device=x.device)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        rc = L.sb_rmsnorm_fwd(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(weight), _lib.ptr(y),
+                              _lib.ptr(h if residual is not None else None), _lib.ptr(rstd), T, H,
+                              ctypes.c_float(eps), _lib.stream())
+        _lib.check(rc, "sb_rmsnorm_fwd")
+        ctx.save_for_backward(h, weight, rstd)
+        ctx.has_res = residual is not None
+        if residual is None:
+            ctx.mark_non_differentiable(h_ret)
+        return y, h_ret
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        h, weight, rstd = ctx.saved_tensors
+        L = _lib.get_lib()
+        T, H = h.shape
+        dy = dy.contiguous()
+        dx = torch.empty_like(h)
+        nblk = L.sb_rmsnorm_bwd_blocks(T)
+        partial = torch.empty(nblk, H, dtype=torch.float32, device=h.device)
+        mg = getattr(weight, "main_grad", None)
+        dw_buf = mg if mg is not None else torch.empty(H, dtype=torch.float32, device=h.device)
+        dres = dh.contiguous() if (ctx.has_res and dh is not None) else None
+        rc = L.sb_rmsnorm_bwd(_lib.ptr(dy), _lib.ptr(h), _lib.ptr(weight), _lib.ptr(rstd), _lib.ptr(dres),
+                              _lib.ptr(dx), _lib.ptr(partial), _lib.ptr(dw_buf), int(mg is not None), T, H,
+                              _lib.stream())
+        _lib.check(rc, "sb_rmsnorm_bwd")
+        dw = None if mg is not None else dw_buf.to(weight.dtype)
+        return dx, (dx if ctx.has_res else None), dw, None
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None):
+    """Returns ``(y, h)``: ``h = x + residual`` (``x`` itself when no residual) and ``y = rmsnorm(h) * weight``."""
+    if not x.is_cuda:
+        return ref.rmsnorm(x, weight, eps, residual)
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1]).contiguous()
+    r2 = residual.reshape(-1, shp[-1]).contiguous() if residual is not None else None
+    y, h = _RMSNormFn.apply(x2, r2, weight, eps)
+    return y.reshape(shp), (h.reshape(shp) if residual is not None else x)
+
+
+# ---------------------------------------------------------------------------------------------
+# RoPE
+# ---------------------------------------------------------------------------------------------
+rope_tables = ref.rope_tables
+
+
+def _rope_native(qkv: torch.Tensor, n_heads_rot: int, head_dim: int, positions: torch.Tensor, cos_tab, sin_tab,
+                 mrope_section, sign: float) -> None:
+    L = _lib.get_lib()
+    T = qkv.shape[0]
+    pos = positions.to(torch.int32).contiguous()
+    rows = 1 if pos.dim() == 1 else pos.shape[0]
+    s0 = s1 = 0
+    if rows == 3:
+        s0, s1 = mrope_section[0], mrope_section[0] + mrope_section[1]
+    rc = L.sb_rope(_lib.ptr(qkv), _lib.ptr(pos), _lib.ptr(cos_tab), _lib.ptr(sin_tab), T, qkv.stride(0),
+                   n_heads_rot, head_dim, rows, s0, s1, ctypes.c_float(sign), _lib.stream())
+    _lib.check(rc, "sb_rope")
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, n_heads_rot, head_dim, positions, cos_tab, sin_tab, mrope_section):
+        out = qkv.clone()
+        _rope_native(out, n_heads_rot, head_dim, positions, cos_tab, sin_tab, mrope_section, 1.0)
+        ctx.save_for_backward(positions, cos_tab, sin_tab)
+        ctx.meta = (n_heads_rot, head_dim, mrope_section)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        positions, cos_tab, sin_tab = ctx.saved_tensors
+        n_heads_rot, head_dim, mrope_section = ctx.meta
+        d = dout.clone()
+        _rope_native(d, n_heads_rot, head_dim, positions, cos_tab, sin_tab, mrope_section, -1.0)
+        return d, None, None, None, None, None, None
+
+
+def rope(qkv: torch.Tensor, n_heads_rot: int, head_dim: int, positions: torch.Tensor, cos_tab: torch.Tensor,
+         sin_tab: torch.Tensor, mrope_section=None) -> torch.Tensor:
+    """Rotate-half RoPE on the first ``n_heads_rot`` heads of each packed row ``[T, heads*head_dim]``
+    (q heads followed by k heads; the v part is left untouched)."""
+    if not qkv.is_cuda:
+        T = qkv.shape[0]
+        rot = qkv[:, : n_heads_rot * head_dim].reshape(T, n_heads_rot, head_dim)
+        rot = ref.rope(rot, positions, cos_tab, sin_tab, mrope_section)
+        return torch.cat([rot.reshape(T, -1), qkv[:, n_heads_rot * head_dim:]], dim=-1)
+    return _RopeFn.apply(qkv.contiguous(), n_heads_rot, head_dim, positions, cos_tab, sin_tab, mrope_section)
+
+
+# ---------------------------------------------------------------------------------------------
+# SwiGLU
+# ---------------------------------------------------------------------------------------------
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        L = _lib.get_lib()
+        T, I2 = gu.shape
+        out = torch.empty(T, I2 // 2, dtype=gu.dtype, device=gu.device)
+        _lib.check(L.sb_swiglu_fwd(_lib.ptr(gu), _lib.ptr(out), T, I2 // 2, _lib.stream()), "sb_swiglu_fwd")
+        ctx.save_for_backward(gu)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        L = _lib.get_lib()
+        T, I2 = gu.shape
+        dgu = torch.empty_like(gu)
+        _lib.check(L.sb_swiglu_bwd(_lib.ptr(gu), _lib.ptr(dout.contiguous()), _lib.ptr(dgu), T, I2 // 2,
+                                   _lib.stream()), "sb_swiglu_bwd")
+        return dgu
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for a fused projection ``[T, 2I]`` = ``[gate | up]``."""
+    if not gate_up.is_cuda:
+        return ref.swiglu(gate_up)
+    shp = gate_up.shape
+    out = _SwiGLUFn.apply(gate_up.reshape(-1, shp[-1]).contiguous())
+    return out.reshape(*shp[:-1], shp[-1] // 2)
+
+
+# ---------------------------------------------------------------------------------------------
+# Embedding
+# ---------------------------------------------------------------------------------------------
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table):
+        L = _lib.get_lib()
+        T = ids.numel()
+        V, H = table.shape
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+        ids64 = ids.reshape(-1).to(torch.int64).contiguous()
+        _lib.check(L.sb_embedding_fwd(_lib.ptr(ids64), _lib.ptr(table), _lib.ptr(out), T, H, V, _lib.stream()),
+                   "sb_embedding_fwd")
+        ctx.save_for_backward(ids64)
+        ctx.table = table
+        return out.reshape(*ids.shape, H)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids64,) = ctx.saved_tensors
+        table = ctx.table
+        L = _lib.get_lib()
+        V, H = table.shape
+        T = ids64.numel()
+        mg = getattr(table, "main_grad", None)
+        buf = mg if mg is not None else torch.zeros(V, H, dtype=torch.float32, device=table.device)
+        _lib.check(L.sb_embedding_bwd(_lib.ptr(ids64), _lib.ptr(dout.reshape(T, H).contiguous()), _lib.ptr(buf),
+                                      T, H, V, _lib.stream()), "sb_embedding_bwd")
+        return None, (None if mg is not None else buf.to(table.dtype))
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    if not table.is_cuda:
+        return F.embedding(ids, table)
+    return _EmbeddingFn.apply(ids, table)
+
+
+def add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    return a + b
