@@ -2,7 +2,8 @@
 
 Every ``.cu`` under ``csrc/`` is compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a``),
 every ``.cpp`` with g++ through nvcc, and all objects are linked into one shared library that has no
-dependency on torch or Python: its ``extern "C"`` entry points are called through ``ctypes`` (see
+dependency on torch or Python (it shares ``libcudart.so.12`` with torch, so the current device and
+context that torch sets on a thread — autograd worker threads included — are the ones it sees): its ``extern "C"`` entry points are called through ``ctypes`` (see
 ``siirl_b200/ops/lib.py``).  nvcc cross-compiles without a GPU, so this runs on a CPU-only box.
 
 Usage: ``python -m siirl_b200.build_ext [--force] [--verbose]``.
@@ -72,7 +73,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     need_link = bool(stale) or not LIB_PATH.exists() or any(
         o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs)
     if need_link:
-        cmd = [NVCC, *ARCH_FLAGS, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lpthread"]
+        cmd = [NVCC, *ARCH_FLAGS, "-shared", "--cudart", "shared", "-o", str(LIB_PATH), *map(str, objs), "-lpthread"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")

@@ -368,17 +368,25 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (a_mn && (M % 8))) return -3;
   if (epi == EPI_BF16 ? (ldc % 8) : (ldc % 4)) return -3;
+  // The driver-API tensor-map encoder needs a current context on the calling thread; threads
+  // that only ever launched through torch (autograd workers) may not have one bound yet.
+  static thread_local bool tl_context_bound = false;
+  if (!tl_context_bound) {
+    cudaFree(0);
+    tl_context_bound = true;
+  }
   int BN = tile_n;
   if (BN != 128 && BN != 256) {
-    // pick the tile width with the better last-wave occupancy
+    // 256-wide tiles halve the A traffic per FLOP and measured 1.5x faster than 128-wide ones on
+    // B200 for every large shape; the narrow tile only wins when it removes a mostly empty wave.
     const int sms = num_sms();
     const long long mbk = (M + kBM - 1) / kBM;
-    auto waves_cost = [&](int bn) {
+    auto waves_cost = [&](int bn, double per_tile) {
       long long tiles = mbk * ((N + bn - 1) / bn);
       long long waves = (tiles + sms - 1) / sms;
-      return (double)waves * bn;  // time ~ waves * tile work
+      return (double)waves * per_tile;
     };
-    BN = (N >= 256 && waves_cost(256) <= waves_cost(128) * 1.02) ? 256 : 128;
+    BN = (N > 128 && waves_cost(256, 1.0) <= waves_cost(128, 0.75)) ? 256 : 128;
   }
   CUtensorMap ma, mb;
   int r;

@@ -47,6 +47,7 @@ def get_lib() -> ctypes.CDLL:
         if not _LIB_PATH.exists():
             raise NativeLibraryMissing(
                 f"{_LIB_PATH} not found: run `python -m siirl_b200.build_ext` (or __graft_entry__.build())")
+        import torch  # noqa: F401  (loads libcudart.so.12 into the process first)
         _lib = ctypes.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else ctypes.DEFAULT_MODE)
     return _lib
 
