@@ -39,3 +39,27 @@ int sb_embedding_bwd(const long long* ids, const void* dout, float* dtable, int 
 int sb_add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t stream);
 
 }  // extern "C"
+
+extern "C" {
+// ---- rl_algos.cu ----
+int sb_gae_scan(const float* rewards, const float* values, const float* mask, float* adv, float* ret, int B,
+                int R, float gamma, float lam, cudaStream_t stream);
+int sb_grpo_group_adv(const float* rewards, const float* mask, const int* gid, float* scores_ws, float* group_ws,
+                      float* adv, int B, int R, int G, float eps, int norm_by_std, cudaStream_t stream);
+int sb_ppo_token_loss(const float* logp, const float* old_logp, const float* adv, const float* mask,
+                      const float* ref_logp, const float* entropy, const float* w_row, const float* seq_logratio,
+                      float* dlogp, float* dentropy, float* stats, int B, int R, int mode, float clip_lo,
+                      float clip_hi, float clip_c, int use_kl, float kl_coef, float entropy_coef,
+                      float loss_scale, cudaStream_t stream);
+}
+
+extern "C" {
+// ---- fmha_fwd.cu / fmha_bwd.cu ----
+int sb_fmha_fwd(const void* qkv, void* out, float* lse, const int* tile_seq_start, const int* tile_seq_len,
+                const int* tile_q0, int num_tiles, int T, int Hq, int Hkv, int D, int causal, float scale,
+                int* status, cudaStream_t stream);
+int sb_fmha_bwd(const void* qkv, const void* out, const void* d_out, const float* lse, float* delta,
+                float* dq_accum, void* dqkv, const int* tile_seq_start, const int* tile_seq_len,
+                const int* tile_k0, int num_tiles, int T, int Hq, int Hkv, int D, int causal, float scale,
+                int* status, cudaStream_t stream);
+}

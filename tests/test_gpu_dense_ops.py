@@ -89,7 +89,7 @@ def test_rmsnorm_fwd_bwd(H, with_res):
     wr = w.detach().float().requires_grad_()
     hr = xr + rr if with_res else xr
     if with_res:
-        hr = hr.to(torch.bfloat16).float() + (hr - hr.detach())  # kernel rounds h to bf16
+        hr = hr + (hr.to(torch.bfloat16).float() - hr).detach()  # kernel rounds h to bf16
     yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-6) * wr
     ((yr * gy.float()).sum() + (hr * gh.float()).sum()).backward()
     assert _rel_err(y, yr) < 1e-2
