@@ -63,3 +63,33 @@ int sb_fmha_bwd(const void* qkv, const void* out, const void* d_out, const float
                 const int* tile_k0, int num_tiles, int T, int Hq, int Hkv, int D, int causal, float scale,
                 int* status, cudaStream_t stream);
 }
+
+extern "C" {
+// ---- lm_head.cu ----
+int sb_lmhead_stats(const float* logits, long long ld, const long long* labels, float inv_temp, float* logp,
+                    float* entropy, float* lse, int rows, int V, cudaStream_t stream);
+int sb_lmhead_dlogits(const float* logits, long long ld, const long long* labels, const float* lse,
+                      const float* entropy, const float* g_logp, const float* g_ent, float inv_temp, void* dlogits,
+                      long long ldd, int rows, int V, cudaStream_t stream);
+// ---- sampling.cu ----
+int sb_sample(const float* sample_logits, const float* stat_logits, long long ld, float temperature,
+              unsigned long long seed, unsigned long long step, const long long* step_dev, long long* tokens,
+              float* logp, int rows, int V, cudaStream_t stream);
+// ---- optimizer.cu ----
+int sb_sumsq_accumulate(const float* g, long long n, float* out, cudaStream_t stream);
+int sb_adamw_step(float* master, float* m, float* v, const float* grad, void* param_bf16, const float* sumsq,
+                  float* grad_norm_out, long long n, float lr, float beta1, float beta2, float eps,
+                  float weight_decay, int step, float max_norm, float grad_scale, cudaStream_t stream);
+int sb_cast_f32_bf16(const float* src, void* dst, long long n, cudaStream_t stream);
+}
+
+extern "C" {
+// ---- fmha_decode.cu ----
+int sb_kv_append(const void* qkv, int row_stride, const int* seq_ids, const int* positions, const int* block_table,
+                 int max_blocks, void* cache, int T, int Hq, int Hkv, int D, cudaStream_t stream);
+int sb_kv_copy_blocks(void* cache, const int* src, const int* dst, int n_pairs, long long block_elems,
+                      cudaStream_t stream);
+int sb_fmha_decode(const void* q, int row_stride, const void* cache, long long num_blocks, const int* seq_lens,
+                   const int* block_table, int max_blocks, void* out, int B, int Hq, int Hkv, int D, float scale,
+                   int* status, cudaStream_t stream);
+}

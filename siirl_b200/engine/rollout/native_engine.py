@@ -1,0 +1,365 @@
+"""Native rollout engine: paged KV cache, continuous batching, prefix sharing, CUDA-graph decode.
+
+This replaces the vLLM / SGLang engines of the reference (siirl/engine/rollout/vllm_rollout/vllm_rollout_spmd.py,
+siirl/engine/rollout/sglang_rollout/*).  It runs in the same process and on the same weights as the trainer
+(hybrid engine): ``sleep()`` frees the cache arena, ``wake_up()`` re-allocates it.
+
+Scheduling model
+* A request is one prompt with ``n`` samples.  The prompt is prefilled once; its full cache blocks are shared by
+  the ``n`` sequences (reference counts) and only the last, partially filled block is copied per sample.
+* Running sequences decode in lock-step.  Everything a decode step needs (context lengths, block tables, last
+  tokens, finished flags, the sampler's counter) lives in device tensors, so a step is replayed from a CUDA
+  graph; the host looks at the finished flags only every ``sync_interval`` steps, and at that point retires
+  finished sequences, admits waiting requests into the freed slots and grows block tables.
+* Slots of the running batch are fixed-size (``max_num_seqs`` rounded to the captured batch sizes); empty slots
+  have context length 0 and are skipped by the kernels.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ...models.decoder import DecoderLM
+from ...ops import kv_cache as kvc
+from ...ops.attention import SeqInfo
+from ...ops.lm_head import lm_head_logits
+from ...ops.sampling import sample
+
+BLOCK = kvc.BLOCK
+
+
+@dataclass
+class SamplingParams:
+    n: int = 1
+    temperature: float = 1.0
+    top_k: int = -1
+    top_p: float = 1.0
+    max_new_tokens: int = 16
+    eos_token_id: Optional[int] = None
+    ignore_eos: bool = False
+    seed: int = 0
+
+
+@dataclass
+class RolloutOutput:
+    prompt_index: int
+    sample_index: int
+    token_ids: List[int]
+    logprobs: List[float]
+    finish_reason: str  # "stop" (EOS) or "length"
+
+
+@dataclass
+class _Seq:
+    prompt_index: int
+    sample_index: int
+    prompt_len: int
+    max_new: int
+    blocks: List[int] = field(default_factory=list)
+    slot: int = -1
+    generated: int = 0
+
+
+class BlockAllocator:
+    """Reference-counted free list of cache blocks (host side)."""
+
+    def __init__(self, num_blocks: int):
+        self.num_blocks = num_blocks
+        self.free: List[int] = list(range(num_blocks - 1, -1, -1))
+        self.ref = [0] * num_blocks
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise MemoryError("KV cache exhausted")
+        b = self.free.pop()
+        self.ref[b] = 1
+        return b
+
+    def share(self, b: int) -> int:
+        self.ref[b] += 1
+        return b
+
+    def release(self, b: int) -> None:
+        self.ref[b] -= 1
+        if self.ref[b] == 0:
+            self.free.append(b)
+
+    @property
+    def num_free(self) -> int:
+        return len(self.free)
+
+
+class RolloutEngine:
+    def __init__(self, model: DecoderLM, max_num_seqs: int = 256, max_model_len: int = 8192,
+                 num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, sync_interval: int = 16,
+                 use_cuda_graph: bool = True, max_num_batched_tokens: int = 8192):
+        self.model = model
+        self.cfg = model.cfg
+        self.device = model.embed_tokens.device
+        self.dtype = model.embed_tokens.dtype
+        self.max_num_seqs = max_num_seqs
+        self.max_model_len = max_model_len
+        self.max_blocks_per_seq = (max_model_len + BLOCK - 1) // BLOCK
+        self.sync_interval = max(1, sync_interval)
+        self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self._requested_blocks = num_blocks
+        self._mem_util = gpu_memory_utilization
+        self.cache: Optional[torch.Tensor] = None
+        self.alloc: Optional[BlockAllocator] = None
+        self._graphs: Dict[int, object] = {}
+        self._out_buf = None
+        self.stats = {"prefill_tokens": 0, "decode_steps": 0, "generated_tokens": 0}
+        self.wake_up()
+
+    # ---- memory hand-off with the trainer -------------------------------------------------------
+    def _block_bytes(self) -> int:
+        c = self.cfg
+        return c.num_layers * 2 * c.num_kv_heads * BLOCK * c.head_dim * torch.finfo(self.dtype).bits // 8
+
+    def wake_up(self) -> None:
+        if self.cache is not None:
+            return
+        c = self.cfg
+        nb = self._requested_blocks
+        if nb is None:
+            if self.device.type == "cuda":
+                free, _total = torch.cuda.mem_get_info(self.device)
+                nb = max(16, int(free * self._mem_util) // self._block_bytes())
+            else:
+                nb = max(16, self.max_num_seqs * self.max_blocks_per_seq)
+            nb = min(nb, self.max_num_seqs * self.max_blocks_per_seq + 8)
+        self.cache = torch.zeros(c.num_layers, nb, 2, c.num_kv_heads, BLOCK, c.head_dim, dtype=self.dtype,
+                                 device=self.device)
+        self.alloc = BlockAllocator(nb)
+        S = self.max_num_seqs
+        dev = self.device
+        self.block_table = torch.full((S, self.max_blocks_per_seq), -1, dtype=torch.int32, device=dev)
+        self.ctx_len = torch.zeros(S, dtype=torch.int32, device=dev)       # tokens in the cache
+        self.last_token = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.finished = torch.ones(S, dtype=torch.bool, device=dev)
+        self.remaining = torch.zeros(S, dtype=torch.int32, device=dev)     # new tokens still allowed
+        self.step_counter = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.slot_ids = torch.arange(S, dtype=torch.int32, device=dev)
+        self.gen_index = torch.zeros(S, dtype=torch.int32, device=dev)
+        self.hit_eos = torch.zeros(S, dtype=torch.bool, device=dev)
+        self._graphs.clear()
+        self._out_buf = None
+
+    def sleep(self) -> None:
+        """Free the cache arena (the trainer gets the memory back)."""
+        self.cache = None
+        self.alloc = None
+        self._graphs.clear()
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    # ---- prefill --------------------------------------------------------------------------------
+    @torch.no_grad()
+    def _prefill(self, seqs: List[_Seq], prompts: List[List[int]], **mm) -> torch.Tensor:
+        """Prefill one packed batch of distinct prompts (``seqs[i]`` is sample 0 of its prompt); returns the
+        final hidden state of the last token of each prompt ``[len(seqs), H]``."""
+        lens = [len(p) for p in prompts]
+        info = SeqInfo(lens, device=self.device)
+        ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64, device=self.device)
+        seq_ids = torch.repeat_interleave(torch.tensor([s.slot for s in seqs], dtype=torch.int32),
+                                          torch.tensor(lens)).to(self.device)
+        hidden = self.model.forward_cached(ids, info.positions, self.cache, self.block_table, seq_ids,
+                                           prefill_info=info, **mm)
+        last = torch.tensor([c - 1 for c in info.cu_seqlens_cpu[1:]], dtype=torch.int64, device=self.device)
+        self.stats["prefill_tokens"] += sum(lens)
+        return hidden.index_select(0, last)
+
+    # ---- decode ---------------------------------------------------------------------------------
+    def _decode_step(self, sp: SamplingParams, tokens_out: torch.Tensor, logp_out: torch.Tensor) -> None:
+        """One lock-step decode of all slots.  Pure device work (graph-capturable)."""
+        S = self.max_num_seqs
+        active = ~self.finished
+        pos = torch.where(active, self.ctx_len, torch.full_like(self.ctx_len, -1))
+        seq_ids = torch.where(active, self.slot_ids, torch.full_like(self.slot_ids, -1))
+        seq_lens = torch.where(active, self.ctx_len + 1, torch.zeros_like(self.ctx_len))
+        hidden = self.model.forward_cached(self.last_token, pos.clamp(min=0), self.cache, self.block_table, seq_ids,
+                                           seq_lens=seq_lens, rope_positions=pos.clamp(min=0))
+        logits = lm_head_logits(hidden, self.model.head_weight)
+        tok, lp = sample(logits, sp.temperature, sp.top_k, sp.top_p, seed=sp.seed, step_dev=self.step_counter
+                         if self.device.type == "cuda" else None, step=int(self.step_counter.item())
+                         if self.device.type != "cuda" else 0)
+        col = self.gen_index.clamp(max=tokens_out.shape[1] - 1).long()
+        rows = torch.arange(S, device=self.device)
+        pad = self.cfg.pad_token_id
+        tokens_out[rows, col] = torch.where(active, tok, tokens_out[rows, col])
+        logp_out[rows, col] = torch.where(active, lp, logp_out[rows, col])
+        self.gen_index += active.to(torch.int32)
+        self.ctx_len += active.to(torch.int32)
+        self.remaining -= active.to(torch.int32)
+        self.last_token.copy_(torch.where(active, tok, self.last_token))
+        done = self.remaining <= 0
+        if sp.eos_token_id is not None and not sp.ignore_eos:
+            done = done | (tok == sp.eos_token_id)
+            self.hit_eos |= active & (tok == sp.eos_token_id)
+        self.finished |= done
+        self.step_counter += 1
+        _ = pad
+
+    def _run_decode_steps(self, k: int, sp: SamplingParams, tokens_out, logp_out) -> None:
+        if not self.use_cuda_graph:
+            for _ in range(k):
+                self._decode_step(sp, tokens_out, logp_out)
+            return
+        key = (k, sp.temperature, sp.top_k, sp.top_p, sp.seed, sp.eos_token_id, sp.ignore_eos)
+        g = self._graphs.get(key)
+        if g is None:
+            # warm-up on a side stream (allocator and lazy initialisation), then capture k steps as one graph
+            from ...ops import lib as _lib
+            _lib.status_word(self.device)
+            snapshot = [t.clone() for t in (self.ctx_len, self.last_token, self.finished, self.remaining,
+                                            self.step_counter, self.gen_index, self.hit_eos, tokens_out, logp_out)]
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self._decode_step(sp, tokens_out, logp_out)
+            torch.cuda.current_stream().wait_stream(s)
+            for dst, src in zip((self.ctx_len, self.last_token, self.finished, self.remaining, self.step_counter,
+                                 self.gen_index, self.hit_eos, tokens_out, logp_out), snapshot):
+                dst.copy_(src)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(k):
+                    self._decode_step(sp, tokens_out, logp_out)
+            for dst, src in zip((self.ctx_len, self.last_token, self.finished, self.remaining, self.step_counter,
+                                 self.gen_index, self.hit_eos, tokens_out, logp_out), snapshot):
+                dst.copy_(src)
+            self._graphs[key] = g
+        g.replay()
+
+    # ---- public API -------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, **mm) -> List[RolloutOutput]:
+        """Generate ``sp.n`` samples for every prompt (token id lists).  Returns outputs ordered by
+        (prompt_index, sample_index)."""
+        assert self.cache is not None, "engine is asleep: call wake_up()"
+        S, dev = self.max_num_seqs, self.device
+        R = sp.max_new_tokens
+        waiting: List[int] = list(range(len(prompts)))[::-1]
+        results: Dict[tuple, RolloutOutput] = {}
+        slots: List[Optional[_Seq]] = [None] * S
+        if self._out_buf is None or self._out_buf[0].shape[1] != R:
+            self._out_buf = (torch.zeros(S, R, dtype=torch.int64, device=dev),
+                             torch.zeros(S, R, dtype=torch.float32, device=dev))
+            self._graphs.clear()
+        tokens_out, logp_out = self._out_buf
+        tokens_out.zero_()
+        logp_out.zero_()
+        self.gen_index.zero_()
+        self.hit_eos.zero_()
+        self.finished.fill_(True)
+        self.ctx_len.zero_()
+        self.remaining.zero_()
+        self.block_table.fill_(-1)
+
+        def blocks_needed(plen: int) -> int:
+            return (plen + R + BLOCK - 1) // BLOCK
+
+        def retire(slot: int, fin_reason: str, n_gen: int) -> None:
+            seq = slots[slot]
+            toks = tokens_out[slot, :n_gen].tolist()
+            lps = logp_out[slot, :n_gen].tolist()
+            results[(seq.prompt_index, seq.sample_index)] = RolloutOutput(seq.prompt_index, seq.sample_index, toks,
+                                                                         lps, fin_reason)
+            for b in seq.blocks:
+                self.alloc.release(b)
+            slots[slot] = None
+            self.stats["generated_tokens"] += n_gen
+
+        while waiting or any(s is not None for s in slots):
+            # ---- admission: whole prompts (all n samples) while slots and blocks last ----
+            free_slots = [i for i, s in enumerate(slots) if s is None]
+            batch_prompts, batch_seqs, forks, ntok = [], [], [], 0
+            while waiting:
+                pi = waiting[-1]
+                p = list(prompts[pi])
+                if len(p) + R > self.max_model_len:
+                    raise ValueError(f"prompt {pi}: {len(p)} + {R} tokens exceed max_model_len {self.max_model_len}")
+                full = len(p) // BLOCK
+                need = blocks_needed(len(p)) + (sp.n - 1) * (blocks_needed(len(p)) - full)
+                if len(free_slots) < sp.n or self.alloc.num_free < need or (
+                        batch_prompts and ntok + len(p) > self.max_num_batched_tokens):
+                    break
+                waiting.pop()
+                group = []
+                for si in range(sp.n):
+                    seq = _Seq(pi, si, len(p), R, slot=free_slots.pop(0))
+                    slots[seq.slot] = seq
+                    group.append(seq)
+                first = group[0]
+                first.blocks = [self.alloc.alloc() for _ in range(blocks_needed(len(p)))]
+                for other in group[1:]:
+                    other.blocks = [self.alloc.share(b) for b in first.blocks[:full]]
+                    for j in range(full, len(first.blocks)):
+                        nb = self.alloc.alloc()
+                        other.blocks.append(nb)
+                        if j == full and len(p) % BLOCK:
+                            forks.append((first.blocks[j], nb))
+                batch_prompts.append(p)
+                batch_seqs.append(group)
+                ntok += len(p)
+            if not batch_prompts and not any(s is not None for s in slots):
+                raise MemoryError("a single request does not fit into the KV cache / slot budget")
+            if batch_prompts:
+                bt = self.block_table.cpu()
+                for group in batch_seqs:
+                    for seq in group:
+                        bt[seq.slot, : len(seq.blocks)] = torch.tensor(seq.blocks, dtype=torch.int32)
+                self.block_table.copy_(bt)
+                hidden = self._prefill([g[0] for g in batch_seqs], batch_prompts, **mm)
+                if forks:
+                    src = torch.tensor([a for a, _ in forks], dtype=torch.int32, device=dev)
+                    dst = torch.tensor([b for _, b in forks], dtype=torch.int32, device=dev)
+                    for li in range(self.cfg.num_layers):
+                        kvc.kv_copy_blocks(self.cache[li], src, dst)
+                # first token of every sample comes from the prompt's last hidden state
+                rep_idx = torch.tensor([i for i, g in enumerate(batch_seqs) for _ in g], device=dev)
+                logits = lm_head_logits(hidden.index_select(0, rep_idx), self.model.head_weight)
+                tok, lp = sample(logits, sp.temperature, sp.top_k, sp.top_p, seed=sp.seed ^ 0x5bd1e995,
+                                 step=int(self.step_counter.item()))
+                self.step_counter += 1
+                flat = [s for g in batch_seqs for s in g]
+                sl = torch.tensor([s.slot for s in flat], dtype=torch.int64, device=dev)
+                tokens_out[sl, 0] = tok
+                logp_out[sl, 0] = lp
+                self.gen_index[sl] = 1
+                self.ctx_len[sl] = torch.tensor([s.prompt_len for s in flat], dtype=torch.int32, device=dev)
+                self.remaining[sl] = R - 1
+                self.last_token[sl] = tok
+                fin = torch.zeros(len(flat), dtype=torch.bool, device=dev) | (R <= 1)
+                if sp.eos_token_id is not None and not sp.ignore_eos:
+                    eos = tok == sp.eos_token_id
+                    self.hit_eos[sl] = eos
+                    fin = fin | eos
+                else:
+                    self.hit_eos[sl] = False
+                self.finished[sl] = fin
+            # ---- decode until the next host check ----
+            if bool((~self.finished).any().item()):
+                self._run_decode_steps(self.sync_interval, sp, tokens_out, logp_out)
+                self.stats["decode_steps"] += self.sync_interval
+            # ---- retire finished sequences ----
+            fin_cpu = self.finished.cpu().tolist()
+            gen_cpu = self.gen_index.cpu().tolist()
+            eos_cpu = self.hit_eos.cpu().tolist()
+            for slot, seq in enumerate(slots):
+                if seq is not None and fin_cpu[slot]:
+                    retire(slot, "stop" if eos_cpu[slot] else "length", gen_cpu[slot])
+                    self.ctx_len[slot] = 0
+                    self.gen_index[slot] = 0
+                    self.block_table[slot].fill_(-1)
+        return [results[k] for k in sorted(results)]
+
+    def cache_utilization(self) -> float:
+        return 1.0 - self.alloc.num_free / self.alloc.num_blocks if self.alloc else 0.0
+
+
+_ = math

@@ -1,0 +1,208 @@
+"""Architecture description of the decoder families this framework trains and serves.
+
+The reference takes architectures from HF ``config.json`` through transformers / Megatron converters
+(siirl/models/loader.py, siirl/models/mcore/config_converter.py:26-284: dense Llama/Qwen2, Qwen2-MoE, Mixtral,
+Qwen3-MoE, Qwen2.5-VL).  Here one dataclass covers them; ``from_hf_config`` reads the same ``config.json`` and
+``PRESETS`` holds the shapes used by the benchmark configurations (random-init, no checkpoint needed).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import asdict, dataclass, field
+from typing import Any, Dict, List, Optional
+
+
+@dataclass
+class VisionConfig:
+    depth: int = 32
+    hidden_size: int = 1280
+    num_heads: int = 16
+    intermediate_size: int = 3420
+    patch_size: int = 14
+    temporal_patch_size: int = 2
+    in_channels: int = 3
+    spatial_merge_size: int = 2
+    window_size: int = 112
+    fullatt_block_indexes: List[int] = field(default_factory=lambda: [7, 15, 23, 31])
+    out_hidden_size: int = 3584
+
+
+@dataclass
+class DecoderConfig:
+    model_type: str = "qwen2"
+    vocab_size: int = 1024
+    hidden_size: int = 128
+    intermediate_size: int = 352
+    num_layers: int = 2
+    num_heads: int = 4
+    num_kv_heads: int = 2
+    head_dim: int = 32
+    rope_theta: float = 1e4
+    rms_norm_eps: float = 1e-6
+    max_position_embeddings: int = 32768
+    qkv_bias: bool = True           # Qwen2 family
+    qk_norm: bool = False           # Qwen3 family
+    tie_word_embeddings: bool = False
+    mrope_section: Optional[List[int]] = None   # Qwen2-VL multimodal rope (t, h, w halves)
+    # mixture of experts (0 experts = dense)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    # value head (critic / reward model): one scalar per token instead of the vocabulary head
+    value_head: bool = False
+    vision: Optional[VisionConfig] = None
+    image_token_id: int = 151655
+    eos_token_id: int = 2
+    pad_token_id: int = 0
+    bos_token_id: Optional[int] = None
+    initializer_range: float = 0.02
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    @property
+    def q_width(self) -> int:
+        return self.num_heads * self.head_dim
+
+    @property
+    def kv_width(self) -> int:
+        return self.num_kv_heads * self.head_dim
+
+    @property
+    def qkv_width(self) -> int:
+        return self.q_width + 2 * self.kv_width
+
+    def num_parameters(self) -> int:
+        H, I, V = self.hidden_size, self.intermediate_size, self.vocab_size
+        attn = H * self.qkv_width + (self.qkv_width if self.qkv_bias else 0) + self.q_width * H
+        if self.qk_norm:
+            attn += 2 * self.head_dim
+        if self.is_moe:
+            mlp = self.num_experts * 3 * H * self.moe_intermediate_size + self.num_experts * H
+        else:
+            mlp = 3 * H * I
+        per_layer = attn + mlp + 2 * H
+        head = 0 if self.tie_word_embeddings else (H if self.value_head else V * H)
+        return V * H + self.num_layers * per_layer + H + head
+
+    def to_dict(self) -> Dict[str, Any]:
+        return asdict(self)
+
+    # ---- HF interchange -----------------------------------------------------------------------
+    @classmethod
+    def from_hf_config(cls, cfg: Dict[str, Any]) -> "DecoderConfig":
+        text = cfg.get("text_config", cfg)
+        mt = cfg.get("model_type", "qwen2")
+        nh = text["num_attention_heads"]
+        hd = text.get("head_dim") or text["hidden_size"] // nh
+        rope_scaling = text.get("rope_scaling") or cfg.get("rope_scaling") or {}
+        out = cls(
+            model_type=mt,
+            vocab_size=text["vocab_size"],
+            hidden_size=text["hidden_size"],
+            intermediate_size=text.get("intermediate_size", 0),
+            num_layers=text["num_hidden_layers"],
+            num_heads=nh,
+            num_kv_heads=text.get("num_key_value_heads", nh),
+            head_dim=hd,
+            rope_theta=float(text.get("rope_theta", 1e4)),
+            rms_norm_eps=float(text.get("rms_norm_eps", 1e-6)),
+            max_position_embeddings=text.get("max_position_embeddings", 32768),
+            qkv_bias=mt.startswith("qwen2") or bool(text.get("attention_bias", False)),
+            qk_norm=mt.startswith("qwen3"),
+            tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
+            mrope_section=rope_scaling.get("mrope_section"),
+            num_experts=text.get("num_experts", text.get("num_local_experts", 0)) or 0,
+            num_experts_per_tok=text.get("num_experts_per_tok", 0) or 0,
+            moe_intermediate_size=text.get("moe_intermediate_size", 0) or 0,
+            norm_topk_prob=bool(text.get("norm_topk_prob", True)),
+            eos_token_id=(cfg.get("eos_token_id") if isinstance(cfg.get("eos_token_id"), int) else 2) or 2,
+            pad_token_id=cfg.get("pad_token_id") or 0,
+        )
+        if "vision_config" in cfg:
+            vc = cfg["vision_config"]
+            out.vision = VisionConfig(
+                depth=vc.get("depth", 32), hidden_size=vc.get("hidden_size", 1280), num_heads=vc.get("num_heads", 16),
+                intermediate_size=vc.get("intermediate_size", 3420), patch_size=vc.get("patch_size", 14),
+                temporal_patch_size=vc.get("temporal_patch_size", 2), in_channels=vc.get("in_chans", 3),
+                spatial_merge_size=vc.get("spatial_merge_size", 2), window_size=vc.get("window_size", 112),
+                fullatt_block_indexes=vc.get("fullatt_block_indexes", [7, 15, 23, 31]),
+                out_hidden_size=vc.get("out_hidden_size", text["hidden_size"]))
+            out.image_token_id = cfg.get("image_token_id", 151655)
+        return out
+
+    @classmethod
+    def from_pretrained(cls, path: str) -> "DecoderConfig":
+        with open(os.path.join(os.path.expanduser(path), "config.json")) as f:
+            return cls.from_hf_config(json.load(f))
+
+    def to_hf_config(self) -> Dict[str, Any]:
+        arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
+                "llama": "LlamaForCausalLM", "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration"}
+        d = {
+            "architectures": [arch.get(self.model_type, "Qwen2ForCausalLM")], "model_type": self.model_type,
+            "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+            "intermediate_size": self.intermediate_size, "num_hidden_layers": self.num_layers,
+            "num_attention_heads": self.num_heads, "num_key_value_heads": self.num_kv_heads,
+            "head_dim": self.head_dim, "rope_theta": self.rope_theta, "rms_norm_eps": self.rms_norm_eps,
+            "max_position_embeddings": self.max_position_embeddings,
+            "tie_word_embeddings": self.tie_word_embeddings, "hidden_act": "silu", "torch_dtype": "bfloat16",
+            "eos_token_id": self.eos_token_id, "pad_token_id": self.pad_token_id,
+        }
+        if self.is_moe:
+            d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
+        if self.mrope_section:
+            d["rope_scaling"] = {"type": "mrope", "mrope_section": self.mrope_section}
+        return d
+
+
+PRESETS: Dict[str, DecoderConfig] = {
+    # 2-layer gate model used by the CPU/gloo end-to-end test
+    "tiny": DecoderConfig(model_type="qwen2", vocab_size=1024, hidden_size=128, intermediate_size=352, num_layers=2,
+                          num_heads=4, num_kv_heads=2, head_dim=32, rope_theta=1e4, eos_token_id=2),
+    # small GPU smoke model (head_dim 64 path)
+    "tiny-gpu": DecoderConfig(model_type="qwen2", vocab_size=4096, hidden_size=512, intermediate_size=1408,
+                              num_layers=2, num_heads=8, num_kv_heads=2, head_dim=64, rope_theta=1e6, eos_token_id=2),
+    "qwen2.5-0.5b": DecoderConfig(model_type="qwen2", vocab_size=151936, hidden_size=896, intermediate_size=4864,
+                                  num_layers=24, num_heads=14, num_kv_heads=2, head_dim=64, rope_theta=1e6,
+                                  tie_word_embeddings=True, eos_token_id=151645, pad_token_id=151643),
+    "qwen2.5-7b": DecoderConfig(model_type="qwen2", vocab_size=152064, hidden_size=3584, intermediate_size=18944,
+                                num_layers=28, num_heads=28, num_kv_heads=4, head_dim=128, rope_theta=1e6,
+                                eos_token_id=151645, pad_token_id=151643),
+    "qwen3-30b-a3b": DecoderConfig(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, intermediate_size=6144,
+                                   num_layers=48, num_heads=32, num_kv_heads=4, head_dim=128, rope_theta=1e6,
+                                   qkv_bias=False, qk_norm=True, num_experts=128, num_experts_per_tok=8,
+                                   moe_intermediate_size=768, eos_token_id=151645, pad_token_id=151643),
+    "tiny-moe": DecoderConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=128, intermediate_size=352,
+                              num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, qkv_bias=False, qk_norm=True,
+                              num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64),
+    "qwen2.5-vl-7b": DecoderConfig(model_type="qwen2_5_vl", vocab_size=152064, hidden_size=3584,
+                                   intermediate_size=18944, num_layers=28, num_heads=28, num_kv_heads=4, head_dim=128,
+                                   rope_theta=1e6, mrope_section=[16, 24, 24], vision=VisionConfig(),
+                                   eos_token_id=151645, pad_token_id=151643),
+    "tiny-vl": DecoderConfig(model_type="qwen2_5_vl", vocab_size=1024, hidden_size=128, intermediate_size=352,
+                             num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, mrope_section=[4, 6, 6],
+                             vision=VisionConfig(depth=2, hidden_size=64, num_heads=4, intermediate_size=128,
+                                                 patch_size=14, window_size=56, fullatt_block_indexes=[1],
+                                                 out_hidden_size=128), image_token_id=1000),
+}
+
+
+def get_config(name_or_path: str, overrides: Optional[Dict[str, Any]] = None) -> DecoderConfig:
+    """Preset name (``qwen2.5-7b``) or a directory with an HF ``config.json``."""
+    import copy
+    if name_or_path in PRESETS:
+        cfg = copy.deepcopy(PRESETS[name_or_path])
+    else:
+        cfg = DecoderConfig.from_pretrained(name_or_path)
+    for k, v in (overrides or {}).items():
+        hf_alias = {"num_hidden_layers": "num_layers", "num_attention_heads": "num_heads",
+                    "num_key_value_heads": "num_kv_heads"}
+        k = hf_alias.get(k, k)
+        if hasattr(cfg, k):
+            setattr(cfg, k, v)
+    return cfg

@@ -1,0 +1,221 @@
+"""Decoder-only transformer (Llama / Qwen2 / Qwen3 / Qwen3-MoE / Qwen2.5-VL language tower) on packed tokens.
+
+One implementation serves training, log-prob computation and (through ``forward_cached``) the rollout engine.
+Inputs are *packed*: ``input_ids [T]`` with sequence boundaries in a :class:`SeqInfo`, no padding anywhere; this
+is the native layout of every kernel in ``siirl_b200.ops``.  The reference gets the same effect by un-padding
+HF models around flash-attn varlen (siirl/engine/actor/dp_actor.py:87-263, siirl/models/transformers/qwen2.py).
+
+Weights use fused projections (``qkv_proj``, ``gate_up_proj``); ``siirl_b200.models.hf_io`` converts to and from
+the HF names (q_proj/k_proj/v_proj, gate_proj/up_proj) for safetensors checkpoints.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+import torch.utils.checkpoint as ckpt
+
+from .. import ops
+from ..ops.attention import SeqInfo, attention_packed
+from ..ops.lm_head import lm_head_logits, lm_head_logprob_entropy
+from .config import DecoderConfig
+
+
+class _Init:
+    """Seeded initialiser: CPU tensors draw from a CPU generator (bit-reproducible across machines), CUDA
+    tensors from a generator on their own device (fast for multi-billion-parameter random-init models)."""
+
+    def __init__(self, seed: int, device):
+        self.device = torch.device(device)
+        self.gen = torch.Generator(device=self.device if self.device.type == "cuda" else "cpu").manual_seed(seed)
+
+
+def _param(shape, dtype, device, std: float, gen: "_Init") -> nn.Parameter:
+    dev = gen.device if gen.device.type == "cuda" else torch.device("cpu")
+    t = torch.empty(*shape, dtype=torch.float32 if dev.type == "cpu" else dtype, device=dev)
+    if std > 0:
+        t.normal_(0.0, std, generator=gen.gen)
+    elif std == 0:
+        t.zero_()
+    else:
+        t.fill_(1.0)
+    return nn.Parameter(t.to(device=device, dtype=dtype))
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: DecoderConfig, dtype, device, gen):
+        super().__init__()
+        H, std = cfg.hidden_size, cfg.initializer_range
+        self.cfg = cfg
+        self.input_layernorm = _param((H,), dtype, device, -1, gen)
+        self.qkv_proj_weight = _param((cfg.qkv_width, H), dtype, device, std, gen)
+        self.qkv_proj_bias = _param((cfg.qkv_width,), dtype, device, 0, gen) if cfg.qkv_bias else None
+        if cfg.qk_norm:
+            self.q_norm = _param((cfg.head_dim,), dtype, device, -1, gen)
+            self.k_norm = _param((cfg.head_dim,), dtype, device, -1, gen)
+        self.o_proj_weight = _param((H, cfg.q_width), dtype, device, std, gen)
+        self.post_attention_layernorm = _param((H,), dtype, device, -1, gen)
+        if cfg.is_moe:
+            E, I = cfg.num_experts, cfg.moe_intermediate_size
+            self.router_weight = _param((E, H), dtype, device, std, gen)
+            self.experts_gate_up = _param((E, 2 * I, H), dtype, device, std, gen)
+            self.experts_down = _param((E, H, I), dtype, device, std, gen)
+        else:
+            I = cfg.intermediate_size
+            self.gate_up_proj_weight = _param((2 * I, H), dtype, device, std, gen)
+            self.down_proj_weight = _param((H, I), dtype, device, std, gen)
+
+    # ---- pieces shared by the training and the cached (rollout) paths --------------------------
+    def qkv(self, x: torch.Tensor, positions: torch.Tensor, rope) -> torch.Tensor:
+        cfg = self.cfg
+        qkv = ops.linear(x, self.qkv_proj_weight, self.qkv_proj_bias)
+        if cfg.qk_norm:
+            T = qkv.shape[0]
+            nrot = cfg.num_heads + cfg.num_kv_heads
+            qk = qkv[:, : nrot * cfg.head_dim].reshape(T * nrot, cfg.head_dim)
+            qk = qk.reshape(T, nrot, cfg.head_dim)
+            qn, _ = ops.rmsnorm(qk[:, : cfg.num_heads].reshape(-1, cfg.head_dim), self.q_norm, cfg.rms_norm_eps)
+            kn, _ = ops.rmsnorm(qk[:, cfg.num_heads:].reshape(-1, cfg.head_dim), self.k_norm, cfg.rms_norm_eps)
+            qkv = torch.cat([qn.reshape(T, -1), kn.reshape(T, -1), qkv[:, nrot * cfg.head_dim:]], dim=-1)
+        cos, sin = rope
+        return ops.rope(qkv, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, positions, cos, sin, cfg.mrope_section)
+
+    def mlp(self, x: torch.Tensor) -> torch.Tensor:
+        if self.cfg.is_moe:
+            from .moe import moe_forward
+            return moe_forward(x, self.router_weight, self.experts_gate_up, self.experts_down,
+                               self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob)
+        return ops.linear(ops.swiglu(ops.linear(x, self.gate_up_proj_weight)), self.down_proj_weight)
+
+    def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], positions, info: SeqInfo, rope, causal=True):
+        """``h`` is the residual stream, ``delta`` the previous sub-layer output not yet added to it."""
+        cfg = self.cfg
+        x, h = ops.rmsnorm(delta if delta is not None else h, self.input_layernorm, cfg.rms_norm_eps,
+                           residual=h if delta is not None else None)
+        qkv = self.qkv(x, positions, rope)
+        a = attention_packed(qkv, info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=causal)
+        attn_out = ops.linear(a, self.o_proj_weight)
+        x, h = ops.rmsnorm(attn_out, self.post_attention_layernorm, cfg.rms_norm_eps, residual=h)
+        return h, self.mlp(x)
+
+
+class DecoderLM(nn.Module):
+    def __init__(self, cfg: DecoderConfig, dtype=torch.bfloat16, device="cpu", seed: int = 0,
+                 gradient_checkpointing: bool = False):
+        super().__init__()
+        self.cfg = cfg
+        self.dtype = dtype
+        gen = _Init(seed, device)
+        std = cfg.initializer_range
+        self.embed_tokens = _param((cfg.vocab_size, cfg.hidden_size), dtype, device, std, gen)
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, gen) for _ in range(cfg.num_layers)])
+        self.norm = _param((cfg.hidden_size,), dtype, device, -1, gen)
+        if cfg.value_head:
+            self.value_head = _param((1, cfg.hidden_size), dtype, device, std, gen)
+            self.lm_head = None
+        elif cfg.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = _param((cfg.vocab_size, cfg.hidden_size), dtype, device, std, gen)
+        self.gradient_checkpointing = gradient_checkpointing
+        self._rope = None
+        self.vision = None
+        if cfg.vision is not None:
+            from .vision import VisionTower
+            self.vision = VisionTower(cfg.vision, dtype, device, gen)
+
+    # ---- helpers ------------------------------------------------------------------------------
+    def rope_tables(self, device, min_len: int = 0):
+        need = max(min_len, 1)
+        if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need:
+            n = max(need, min(self.cfg.max_position_embeddings, 8192))
+            self._rope = ops.rope_tables(self.cfg.head_dim, n, self.cfg.rope_theta, device=device)
+        return self._rope
+
+    @property
+    def head_weight(self) -> torch.Tensor:
+        return self.lm_head if self.lm_head is not None else self.embed_tokens
+
+    def embed(self, input_ids: torch.Tensor, pixel_values=None, image_grid_thw=None) -> torch.Tensor:
+        h = ops.embedding(input_ids, self.embed_tokens)
+        if self.vision is not None and pixel_values is not None:
+            img = self.vision(pixel_values, image_grid_thw).to(h.dtype)
+            mask = input_ids == self.cfg.image_token_id
+            idx = mask.nonzero(as_tuple=True)[0]
+            h = h.index_copy(0, idx, img[: idx.numel()])
+        return h
+
+    # ---- training / scoring path ---------------------------------------------------------------
+    def forward_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo, pixel_values=None,
+                       image_grid_thw=None) -> torch.Tensor:
+        """Final-norm hidden states ``[T, H]`` of a packed batch."""
+        pmax = int(positions.max().item()) + 1 if positions.numel() else 1
+        rope = self.rope_tables(input_ids.device, pmax)
+        h = self.embed(input_ids, pixel_values, image_grid_thw)
+        delta = None
+        for layer in self.layers:
+            if self.gradient_checkpointing and torch.is_grad_enabled():
+                h, delta = ckpt.checkpoint(layer, h, delta, positions, info, rope, use_reentrant=False)
+            else:
+                h, delta = layer(h, delta, positions, info, rope)
+        out, _ = ops.rmsnorm(delta, self.norm, self.cfg.rms_norm_eps, residual=h)
+        return out
+
+    def logprobs(self, input_ids, positions, info: SeqInfo, labels, temperature: float = 1.0,
+                 with_entropy: bool = True, **mm) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """``log p(labels[t] | prefix)`` and entropy for every packed position (fp32 ``[T]``)."""
+        hidden = self.forward_hidden(input_ids, positions, info, **mm)
+        return lm_head_logprob_entropy(hidden, self.head_weight, labels, temperature, with_entropy)
+
+    def values(self, input_ids, positions, info: SeqInfo, **mm) -> torch.Tensor:
+        """Scalar value per packed position (critic / reward model head)."""
+        hidden = self.forward_hidden(input_ids, positions, info, **mm)
+        return (hidden.float() @ self.value_head.float().t()).squeeze(-1)
+
+    def logits(self, input_ids, positions, info: SeqInfo, **mm) -> torch.Tensor:
+        return lm_head_logits(self.forward_hidden(input_ids, positions, info, **mm), self.head_weight)
+
+    # ---- rollout path (paged KV cache, no autograd) ----------------------------------------------
+    @torch.no_grad()
+    def forward_cached(self, input_ids: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor,
+                       block_table: torch.Tensor, seq_ids: torch.Tensor, *, prefill_info: Optional[SeqInfo] = None,
+                       seq_lens: Optional[torch.Tensor] = None, pixel_values=None, image_grid_thw=None,
+                       rope_positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Runs the decoder on new tokens, appending their K/V to ``cache``.
+
+        Prefill: ``prefill_info`` describes whole prompts packed in ``input_ids`` (attention over the new tokens,
+        causal).  Decode: one token per running sequence, ``seq_lens`` = context lengths including that token
+        (attention against the cache).  ``positions`` are cache positions; ``rope_positions`` (default: same)
+        may differ for multimodal rope.  Returns final-norm hidden states of the new tokens."""
+        from ..ops import kv_cache as kvc
+        cfg = self.cfg
+        rp = positions if rope_positions is None else rope_positions
+        pmax = int(cfg.max_position_embeddings if rp.is_cuda else rp.max().item() + 1)
+        rope = self.rope_tables(input_ids.device, min(pmax, 32768))
+        h = self.embed(input_ids, pixel_values, image_grid_thw)
+        delta = None
+        pos32 = positions.to(torch.int32)
+        for li, layer in enumerate(self.layers):
+            x, h = ops.rmsnorm(delta if delta is not None else h, layer.input_layernorm, cfg.rms_norm_eps,
+                               residual=h if delta is not None else None)
+            qkv = layer.qkv(x, rp, rope)
+            kvc.kv_append(qkv, seq_ids, pos32, block_table, cache[li], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim)
+            if prefill_info is not None:
+                a = attention_packed(qkv, prefill_info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=True)
+            else:
+                a = kvc.decode_attention(qkv, cache[li], seq_lens, block_table, cfg.num_heads, cfg.num_kv_heads,
+                                         cfg.head_dim)
+            attn_out = ops.linear(a, layer.o_proj_weight)
+            x, h = ops.rmsnorm(attn_out, layer.post_attention_layernorm, cfg.rms_norm_eps, residual=h)
+            delta = layer.mlp(x)
+        out, _ = ops.rmsnorm(delta, self.norm, cfg.rms_norm_eps, residual=h)
+        return out
+
+    def named_flat_order(self) -> List[Tuple[str, nn.Parameter]]:
+        return list(self.named_parameters())
+
+
+def build_model(cfg: DecoderConfig, dtype=torch.bfloat16, device="cpu", seed: int = 0,
+                gradient_checkpointing: bool = False) -> DecoderLM:
+    return DecoderLM(cfg, dtype=dtype, device=device, seed=seed, gradient_checkpointing=gradient_checkpointing)

@@ -1,0 +1,84 @@
+"""Paged KV cache ops: append rows of a packed qkv buffer to the cache, fork blocks, decode attention.
+
+Cache layout (one tensor for all layers): ``[layers, num_blocks, 2, Hkv, 64, D]`` bf16; ``block_table`` is
+``int32 [B, max_blocks]`` (-1 = unused).  The CPU path keeps the same layout and uses plain indexing."""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from . import lib as _lib
+
+BLOCK = 64
+
+
+def kv_append(qkv: torch.Tensor, seq_ids: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+              cache_layer: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+    """Write the k and v parts of every row of ``qkv`` ([T, (Hq+2Hkv)*D]) to ``cache_layer`` at
+    ``(sequence seq_ids[t], position positions[t])``."""
+    T = qkv.shape[0]
+    if qkv.is_cuda:
+        L = _lib.get_lib()
+        _lib.check(L.sb_kv_append(_lib.ptr(qkv), qkv.stride(0), _lib.ptr(seq_ids), _lib.ptr(positions),
+                                  _lib.ptr(block_table), block_table.shape[1], _lib.ptr(cache_layer), T, n_heads,
+                                  n_kv_heads, head_dim, _lib.stream()), "sb_kv_append")
+        return
+    valid = (seq_ids >= 0) & (positions >= 0)
+    qkv, seq_ids, positions = qkv[valid], seq_ids[valid], positions[valid]
+    T = qkv.shape[0]
+    blk = block_table[seq_ids.long(), (positions // BLOCK).long()].long()
+    off = (positions % BLOCK).long()
+    k = qkv[:, n_heads * head_dim:(n_heads + n_kv_heads) * head_dim].reshape(T, n_kv_heads, head_dim)
+    v = qkv[:, (n_heads + n_kv_heads) * head_dim:].reshape(T, n_kv_heads, head_dim)
+    cache_layer[blk, 0, :, off] = k
+    cache_layer[blk, 1, :, off] = v
+
+
+def kv_copy_blocks(cache_layer: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:
+    if src.numel() == 0:
+        return
+    if cache_layer.is_cuda:
+        L = _lib.get_lib()
+        block_elems = cache_layer[0].numel()
+        _lib.check(L.sb_kv_copy_blocks(_lib.ptr(cache_layer), _lib.ptr(src), _lib.ptr(dst), src.numel(),
+                                       ctypes.c_longlong(block_elems), _lib.stream()), "sb_kv_copy_blocks")
+        return
+    cache_layer[dst.long()] = cache_layer[src.long()]
+
+
+def decode_attention(q_rows: torch.Tensor, cache_layer: torch.Tensor, seq_lens: torch.Tensor,
+                     block_table: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
+                     scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One query token per sequence against its cached context.  ``q_rows`` is ``[B, >= Hq*D]`` with the q heads in
+    the first ``Hq*D`` columns (a packed qkv row works); ``seq_lens[b]`` counts the current token.  Returns
+    ``[B, Hq*D]``."""
+    B = q_rows.shape[0]
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if out is None:
+        out = torch.empty(B, n_heads * head_dim, dtype=q_rows.dtype, device=q_rows.device)
+    if q_rows.is_cuda:
+        L = _lib.get_lib()
+        assert head_dim in (64, 128), "decode attention kernel supports head_dim 64 and 128"
+        _lib.check(L.sb_fmha_decode(_lib.ptr(q_rows), q_rows.stride(0), _lib.ptr(cache_layer),
+                                    ctypes.c_longlong(cache_layer.shape[0]), _lib.ptr(seq_lens), _lib.ptr(block_table),
+                                    block_table.shape[1], _lib.ptr(out), B, n_heads, n_kv_heads, head_dim,
+                                    ctypes.c_float(scale), _lib.ptr(_lib.status_word(q_rows.device)), _lib.stream()),
+                   "sb_fmha_decode")
+        return out
+    rep = n_heads // n_kv_heads
+    for b in range(B):
+        n = int(seq_lens[b])
+        nb = (n + BLOCK - 1) // BLOCK
+        blks = block_table[b, :nb].long()
+        k = cache_layer[blks, 0].permute(1, 0, 2, 3).reshape(n_kv_heads, nb * BLOCK, head_dim)[:, :n].float()
+        v = cache_layer[blks, 1].permute(1, 0, 2, 3).reshape(n_kv_heads, nb * BLOCK, head_dim)[:, :n].float()
+        q = q_rows[b, : n_heads * head_dim].reshape(n_heads, head_dim).float()
+        k = k.repeat_interleave(rep, dim=0)
+        v = v.repeat_interleave(rep, dim=0)
+        s = torch.einsum("hd,hnd->hn", q, k) * scale
+        p = torch.softmax(s, -1)
+        out[b] = torch.einsum("hn,hnd->hd", p, v).reshape(-1).to(out.dtype)
+    return out
