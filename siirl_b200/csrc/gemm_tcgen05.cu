@@ -366,8 +366,9 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
                             long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi,
                             int tile_n, int max_ctas, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((N % 8) || (K % 8) || (lda % 8) || (ldb % 8) || (a_mn && (M % 8))) return -3;
-  if (epi == EPI_BF16 ? (ldc % 8) : (ldc % 4)) return -3;
+  // TMA needs 16-byte aligned bases and row pitches; the epilogue stores whole 16-byte groups of a row
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return -3;
+  if (epi == EPI_BF16 ? ((ldc % 8) || (N % 8)) : ((ldc % 4) || (N % 4))) return -3;
   // The driver-API tensor-map encoder needs a current context on the calling thread; threads
   // that only ever launched through torch (autograd workers) may not have one bound yet.
   static thread_local bool tl_context_bound = false;

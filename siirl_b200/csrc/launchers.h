@@ -93,3 +93,8 @@ int sb_fmha_decode(const void* q, int row_stride, const void* cache, long long n
                    const int* block_table, int max_blocks, void* out, int B, int Hq, int Hkv, int D, float scale,
                    int* status, cudaStream_t stream);
 }
+
+extern "C" {
+// ---- host/kk_partition.cpp ----
+int sb_kk_partition(const long long* workloads, int n, int k, int equal_size, int* out_part);
+}
