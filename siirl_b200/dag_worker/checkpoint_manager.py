@@ -1,0 +1,96 @@
+"""Step-level checkpoint orchestration.
+
+Layout (reference: siirl/dag_worker/checkpoint_manager.py:53-197):
+
+    {default_local_dir}/global_step_{N}/{role}_agent_{g}/...     one directory per model role (actor, critic)
+    {default_local_dir}/global_step_{N}/data_dp_rank_{r}.pt      dataloader state, written by tp0/pp0 ranks
+    {default_local_dir}/latest_checkpointed_iteration.txt         written LAST by rank 0 (atomic rename) after a barrier
+
+``resume_mode``: ``disable`` | ``auto`` (latest tracker entry if any) | ``resume_path`` (``trainer.resume_from_path``
+names a ``global_step_N`` directory).  Rank 0 resolves the path and broadcasts it."""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..utils.checkpoint.checkpoint_manager import find_latest_ckpt_path, remove_old_checkpoints
+
+
+class CheckpointManager:
+    def __init__(self, worker):
+        self.w = worker
+        self.root = os.path.expanduser(worker.config.trainer.default_local_dir)
+
+    def _roles(self):
+        out = []
+        for key, wk in self.w.workers.items():
+            if key.startswith("actor_rollout_ref_") and getattr(wk, "store", None) is not None:
+                out.append((f"actor_agent_{key.rsplit('_', 1)[-1]}", wk,
+                            self.w.config.actor_rollout_ref.actor.checkpoint.contents,
+                            self.w.config.trainer.max_actor_ckpt_to_keep))
+            elif key.startswith("critic_"):
+                out.append((f"critic_agent_{key.rsplit('_', 1)[-1]}", wk, self.w.config.critic.checkpoint.contents,
+                            self.w.config.trainer.max_critic_ckpt_to_keep))
+        return out
+
+    def save_checkpoint(self, global_step: int) -> str:
+        step_dir = os.path.join(self.root, f"global_step_{global_step}")
+        os.makedirs(step_dir, exist_ok=True)
+        for name, wk, contents, keep in self._roles():
+            wk.save_checkpoint(os.path.join(step_dir, name), None, global_step, keep, contents=contents)
+        dl = self.w.dataloader
+        tp = self.w.config.actor_rollout_ref.rollout.tensor_model_parallel_size
+        if self.w._rank % max(tp, 1) == 0:
+            tmp = os.path.join(step_dir, f"data_dp_rank_{dl.ddp_rank}.pt.tmp")
+            torch.save({"dataloader": dl.state_dict(), "global_step": global_step}, tmp)
+            os.replace(tmp, tmp[:-4])
+        if self.w._dist:
+            dist.barrier()
+        if self.w._rank == 0:
+            tracker = os.path.join(self.root, "latest_checkpointed_iteration.txt")
+            with open(tracker + ".tmp", "w") as f:
+                f.write(str(global_step))
+            os.replace(tracker + ".tmp", tracker)
+            keep = self.w.config.trainer.max_actor_ckpt_to_keep
+            if self.w.config.trainer.remove_previous_ckpt_in_save:
+                keep = 1
+            remove_old_checkpoints(self.root, keep)
+        if self.w._dist:
+            dist.barrier()
+        return step_dir
+
+    def _resolve(self) -> Optional[str]:
+        t = self.w.config.trainer
+        if t.resume_mode == "disable":
+            return None
+        if t.resume_mode == "auto":
+            return find_latest_ckpt_path(self.root)
+        if t.resume_mode == "resume_path":
+            p = t.resume_from_path
+            if not isinstance(p, str) or "global_step_" not in p:
+                raise ValueError("trainer.resume_from_path must name a global_step_N directory")
+            return os.path.expanduser(p)
+        raise ValueError(f"unknown resume_mode '{t.resume_mode}'")
+
+    def load_checkpoint(self) -> int:
+        """Returns the global step to continue from (0 when starting fresh)."""
+        path = self._resolve() if self.w._rank == 0 else None
+        if self.w._dist:
+            box = [path]
+            dist.broadcast_object_list(box, src=0)
+            path = box[0]
+        if not path or not os.path.isdir(path):
+            return 0
+        step = int(path.rstrip("/").split("global_step_")[-1])
+        for name, wk, _, _ in self._roles():
+            d = os.path.join(path, name)
+            if os.path.isdir(d):
+                wk.load_checkpoint(d, None, self.w.config.trainer.del_local_ckpt_after_load)
+        dl = self.w.dataloader
+        f = os.path.join(path, f"data_dp_rank_{dl.ddp_rank}.pt")
+        if os.path.exists(f):
+            dl.load_state_dict(torch.load(f, map_location="cpu", weights_only=False)["dataloader"])
+        return step

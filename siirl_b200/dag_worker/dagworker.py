@@ -1,0 +1,435 @@
+"""DAGWorker: the per-GPU controller.  Every process runs one and walks the same task graph each step
+(multi-controller SPMD; no central driver in the data path).
+
+Structure and handler names follow the reference (siirl/dag_worker/dagworker.py:83-1318): ``init_graph`` builds the
+distributed groups, tokenizer, dataloader, reward manager and the role workers; ``execute_task_graph`` runs the
+training loop; one step is a topological walk over the DAG calling the node functions
+``generate / compute_reward / compute_old_log_prob / compute_ref_log_prob / compute_value / compute_advantage /
+train_critic / train_actor``; data moves between nodes through an in-process cache when the data-parallel width is
+unchanged and through the Data Coordinator otherwise (always for DAPO's filtered samples).
+
+Differences that matter for speed: batches stay on the device between nodes, there is no per-node world barrier
+(only one at the step boundary), metrics are reduced with one packed all-reduce per step.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+from collections import deque
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..data_coordinator import (Batch, DataCoordinator, Dict2Samples, Samples2Dict, init_data_coordinator,
+                                preprocess_dataloader)
+from ..data_coordinator.dataloader import DataLoaderNode, load_tokenizer
+from ..engine.workers import ActorRolloutRefWorker, CriticWorker, RewardModelWorker
+from ..execution.dag import Node, NodeRole, NodeType, TaskGraph
+from ..execution.scheduler.reward import compute_reward as guarded_compute_reward
+from ..execution.scheduler.reward import create_reward_manager
+from ..utils.logger.tracking import Tracking
+from ..utils.metrics.metric_utils import (compute_data_metric, compute_throughput_metrics, compute_timing_metrics,
+                                          reduce_metrics_across_ranks)
+from . import core_algos
+from .checkpoint_manager import CheckpointManager
+from .data_structures import NodeOutput
+from .validator import Validator
+
+
+class _Timer:
+    def __init__(self, name: str, sink: Dict[str, float], sync: bool):
+        self.name, self.sink, self.sync = name, sink, sync
+
+    def __enter__(self):
+        if self.sync and torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.t0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *exc):
+        if self.sync and torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.sink[self.name] = self.sink.get(self.name, 0.0) + time.perf_counter() - self.t0
+
+
+class DAGWorker:
+    def __init__(self, config, process_group_manager=None, taskgraph_mapping: Optional[Dict[int, TaskGraph]] = None,
+                 data_coordinator: Optional[DataCoordinator] = None, device: Optional[torch.device] = None,
+                 comm=None, tokenizer=None):
+        self.config = config
+        self.pgm = process_group_manager
+        self._dist = dist.is_available() and dist.is_initialized()
+        self._rank = dist.get_rank() if self._dist else 0
+        self.world_size = dist.get_world_size() if self._dist else 1
+        mapping = taskgraph_mapping or {}
+        self.taskgraph: Optional[TaskGraph] = mapping.get(self._rank)
+        self.data_coordinator = data_coordinator
+        self.comm = comm
+        self.tokenizer = tokenizer
+        if device is None:
+            want_cuda = (config.trainer.device or "cuda") == "cuda" and torch.cuda.is_available()
+            device = torch.device("cuda", torch.cuda.current_device()) if want_cuda else torch.device("cpu")
+        self.device = torch.device(device)
+        self.enable_perf = bool(config.dag.enable_perf or os.environ.get("SIIRL_ENABLE_PERF"))
+        self.global_steps = 0
+        self.total_training_steps = 0
+        self.internal_data_cache: Dict[str, Batch] = {}
+        self.workers: Dict[str, Any] = {}
+        self.process_groups: Dict[str, Any] = {}
+        self.timing_raw: Dict[str, float] = {}
+        self.tracker: Optional[Tracking] = None
+        self.kl_ctrl_in_reward = None
+        self.history: List[Dict[str, float]] = []
+        self._dapo_gen_batches = 0
+        self._initialized = False
+
+    # ================================================================================================
+    # initialisation
+    # ================================================================================================
+    def init_graph(self) -> None:
+        if self.taskgraph is None:
+            raise RuntimeError(f"rank {self._rank} has no task graph assigned")
+        self._setup_distributed_environment()
+        if self.tokenizer is None:
+            tok_path = self.config.data.tokenizer or self.config.actor_rollout_ref.model.path
+            vocab = self._vocab_size_hint()
+            self.tokenizer = load_tokenizer(tok_path if not self.config.actor_rollout_ref.model.arch_preset else None,
+                                            vocab_size=vocab)
+        self._setup_dataloader()
+        self._setup_reward_managers()
+        self._initialize_node_workers()
+        if self.config.algorithm.use_kl_in_reward:
+            self.kl_ctrl_in_reward = core_algos.get_kl_controller(self.config.algorithm.kl_ctrl)
+        if self.data_coordinator is None:
+            self.data_coordinator = init_data_coordinator(self.config.trainer.nnodes,
+                                                          self.config.actor_rollout_ref.actor.ppo_mini_batch_size,
+                                                          self.world_size, group=None, comm=self.comm,
+                                                          name=f"dc_rank{self._rank}")
+        self.validator = Validator(self)
+        self.checkpoint_manager = CheckpointManager(self)
+        self.global_steps = self.checkpoint_manager.load_checkpoint()
+        if self._rank == 0:
+            t = self.config.trainer
+            self.tracker = Tracking(t.project_name, t.experiment_name, t.logger, config=self.config.to_dict())
+        self._initialized = True
+
+    def _vocab_size_hint(self) -> int:
+        from ..engine.workers import resolve_model_config
+        try:
+            return resolve_model_config(self.config.actor_rollout_ref.model).vocab_size
+        except Exception:  # noqa: BLE001
+            return 1024
+
+    def _setup_distributed_environment(self) -> None:
+        """One ``new_group`` per rank tuple the planner derived (every rank creates every group, in the same
+        order, as torch.distributed requires)."""
+        if not self._dist or self.pgm is None:
+            return
+        for name in sorted(self.pgm.process_group_spec, key=lambda n: int(n.rsplit("_", 1)[-1])):
+            ranks = self.pgm.process_group_spec[name]
+            self.process_groups[name] = None if len(ranks) == self.world_size else dist.new_group(ranks)
+            if len(ranks) == self.world_size:
+                self.process_groups[name] = dist.group.WORLD
+
+    def _node_group(self, node: Node):
+        if not self._dist or self.pgm is None:
+            return None
+        a = self.pgm.get_node_assignment(node.node_id)
+        return self.process_groups.get(a["process_group_name"]) if a else dist.group.WORLD
+
+    def _get_node_dp_info(self, node: Node):
+        """(dp_size, dp_rank, tp_rank, tp_size): ranks are laid out [DP][PP][TP] with TP fastest
+        (reference dagworker.py:1262-1308)."""
+        group = self._node_group(node)
+        gw = dist.get_world_size(group) if self._dist else 1
+        gr = dist.get_rank(group) if self._dist else 0
+        tp = 1
+        if node.node_role == NodeRole.ROLLOUT:
+            tp = max(1, self.config.actor_rollout_ref.rollout.tensor_model_parallel_size)
+        dp = max(1, gw // tp)
+        return dp, gr // tp, gr % tp, tp
+
+    def _setup_dataloader(self) -> None:
+        rollout_nodes = self.taskgraph.get_nodes_by_role(NodeRole.ROLLOUT)
+        tp = self.config.actor_rollout_ref.rollout.tensor_model_parallel_size
+        if rollout_nodes:
+            g = self._node_group(rollout_nodes[0])
+            gw = dist.get_world_size(g) if self._dist else 1
+            gr = dist.get_rank(g) if self._dist else 0
+        else:
+            gw, gr = self.world_size, self._rank
+        self.dataloader = DataLoaderNode(self.config, self.tokenizer, None, gw, gr, tp)
+        t = self.config.trainer
+        steps = self.dataloader.num_train_batches * t.total_epochs
+        self.total_training_steps = t.total_training_steps if t.total_training_steps is not None else steps
+
+    def _setup_reward_managers(self) -> None:
+        self.reward_fn = create_reward_manager(self.config, self.tokenizer, num_examine=0,
+                                               max_resp_len=self.config.data.max_response_length)
+        self.val_reward_fn = create_reward_manager(self.config, self.tokenizer, num_examine=1,
+                                                   max_resp_len=self.config.data.max_response_length)
+
+    def _initialize_node_workers(self) -> None:
+        """One hybrid worker per agent group for actor/rollout/ref nodes, one critic, one reward model."""
+        seed = self.config.trainer.seed
+        for node in self.taskgraph.nodes.values():
+            if node.node_type not in (NodeType.MODEL_TRAIN, NodeType.MODEL_INFERENCE):
+                continue
+            ag = node.agent_group
+            group = self._node_group(node)
+            cfg = node.config.get("intern_config")
+            if node.node_role in (NodeRole.ACTOR, NodeRole.ROLLOUT, NodeRole.REFERENCE):
+                key = f"actor_rollout_ref_{ag}"
+                if key not in self.workers:
+                    roles = {n.node_role for n in self.taskgraph.nodes.values() if n.agent_group == ag}
+                    need_ref = NodeRole.REFERENCE in roles and (
+                        self.config.actor_rollout_ref.actor.use_kl_loss or self.config.algorithm.use_kl_in_reward)
+                    role = "actor_rollout_ref" if need_ref else "actor_rollout"
+                    w = ActorRolloutRefWorker(cfg or self.config.actor_rollout_ref, role, group, self.device,
+                                              self.comm, seed, self.tokenizer)
+                    w.total_training_steps = self.total_training_steps
+                    w.init_model()
+                    self.workers[key] = w
+            elif node.node_role == NodeRole.CRITIC:
+                key = f"critic_{ag}"
+                if key not in self.workers:
+                    w = CriticWorker(cfg or self.config.critic, group, self.device, self.comm, seed,
+                                     rollout_n=self.config.actor_rollout_ref.rollout.n)
+                    w.total_training_steps = self.total_training_steps
+                    w.init_model()
+                    self.workers[key] = w
+            elif node.node_role == NodeRole.REWARD and self.config.reward_model.enable:
+                key = f"reward_{ag}"
+                if key not in self.workers:
+                    w = RewardModelWorker(cfg or self.config.reward_model, group, self.device, self.comm, seed)
+                    w.init_model()
+                    self.workers[key] = w
+        if self.config.reward_model.enable and "reward_0" not in self.workers:
+            w = RewardModelWorker(self.config.reward_model, None, self.device, self.comm, seed)
+            w.init_model()
+            self.workers["reward_0"] = w
+
+    def _arr(self, node: Optional[Node] = None) -> ActorRolloutRefWorker:
+        return self.workers[f"actor_rollout_ref_{node.agent_group if node is not None else 0}"]
+
+    # ================================================================================================
+    # node handlers
+    # ================================================================================================
+    def generate(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
+        node = kwargs.get("cur_node")
+        batch.meta.update({"eos_token_id": getattr(self.tokenizer, "eos_token_id", None),
+                           "pad_token_id": getattr(self.tokenizer, "pad_token_id", 0) or 0,
+                           "global_steps": self.global_steps})
+        out = self._arr(node).generate_sequences(batch.to(self.device))
+        metrics = {"perf/rollout_output_tokens_total": float(out.meta.get("total_output_tokens", 0))}
+        return NodeOutput(out, metrics)
+
+    def compute_reward(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
+        metrics: Dict[str, float] = {}
+        if self.config.reward_model.enable and "reward_0" in self.workers:
+            batch = self.workers["reward_0"].compute_rm_score(batch)
+        reward_tensor, extra = guarded_compute_reward(batch, self.reward_fn)
+        batch["token_level_scores"] = reward_tensor.to(batch["responses"].device)
+        for k, v in (extra or {}).items():
+            if isinstance(v, list) and len(v) == batch.batch_size:
+                batch.set_non_tensor(k, v)
+                if k == "acc":
+                    batch["acc"] = torch.tensor([float(x) for x in v])
+        if "reward_error" in (extra or {}):
+            metrics["reward/errors_total"] = 1.0
+        seq = batch["token_level_scores"].sum(-1)
+        batch["seq_reward"] = seq
+        batch["seq_final_reward"] = seq
+        if "acc" not in batch:
+            batch["acc"] = (seq > 0).float()
+        batch.meta["global_token_num"] = batch["attention_mask"].sum(-1).tolist()
+        return NodeOutput(batch, metrics)
+
+    def compute_old_log_prob(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
+        batch.meta["temperature"] = self.config.actor_rollout_ref.rollout.temperature
+        out = self._arr(kwargs.get("cur_node")).compute_log_prob(batch)
+        metrics = dict(out.meta.pop("metrics", {}))
+        out.pop("entropys")
+        return NodeOutput(out, metrics)
+
+    def compute_ref_log_prob(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
+        a = self.config.actor_rollout_ref.actor
+        if not (a.use_kl_loss or self.config.algorithm.use_kl_in_reward):
+            return NodeOutput(batch, {})
+        batch.meta["temperature"] = self.config.actor_rollout_ref.rollout.temperature
+        return NodeOutput(self._arr(kwargs.get("cur_node")).compute_ref_log_prob(batch), {})
+
+    def compute_value(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
+        node = kwargs.get("cur_node")
+        return NodeOutput(self.workers[f"critic_{node.agent_group if node else 0}"].compute_values(batch), {})
+
+    def compute_advantage(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
+        alg = self.config.algorithm
+        metrics: Dict[str, float] = {}
+        if "response_mask" not in batch:
+            batch["response_mask"] = core_algos.compute_response_mask(batch)
+        if alg.use_kl_in_reward and "old_log_probs" in batch and "ref_log_prob" in batch:
+            batch, kl_metrics = core_algos.apply_kl_penalty(batch, self.kl_ctrl_in_reward, alg.kl_penalty)
+            metrics.update(kl_metrics)
+        else:
+            batch["token_level_rewards"] = batch["token_level_scores"]
+        batch = core_algos.compute_advantage(
+            batch, alg.adv_estimator, gamma=alg.gamma, lam=alg.lam,
+            norm_adv_by_std_in_grpo=alg.norm_adv_by_std_in_grpo, weight_factor_in_cpgd=alg.weight_factor_in_cpgd,
+            use_pf_ppo=alg.use_pf_ppo, pf_ppo_reweight_method=alg.pf_ppo.get("reweight_method", "pow"),
+            pf_ppo_weight_pow=alg.pf_ppo.get("weight_pow", 2.0),
+            multi_turn=self.config.actor_rollout_ref.rollout.multi_turn.enable)
+        return NodeOutput(batch, metrics)
+
+    def train_critic(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
+        node = kwargs.get("cur_node")
+        return NodeOutput(batch, self.workers[f"critic_{node.agent_group if node else 0}"].update_critic(batch))
+
+    def train_actor(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
+        if self.config.trainer.critic_warmup > self.global_steps:
+            return NodeOutput(batch, {})
+        batch.meta["temperature"] = self.config.actor_rollout_ref.rollout.temperature
+        return NodeOutput(batch, self._arr(kwargs.get("cur_node")).update_actor(batch))
+
+    # ================================================================================================
+    # data movement between nodes
+    # ================================================================================================
+    def put_data_to_buffers(self, key: str, data: Batch, source_dp_size: int, dest_dp_size: int,
+                            enforce_buffer: bool = False) -> None:
+        if source_dp_size == dest_dp_size and not enforce_buffer:
+            self.internal_data_cache[key] = data
+            return
+        infos, samples = Dict2Samples(data, key=key)
+        for info in infos:
+            info.dict_info["source_dp_size"] = source_dp_size
+        self.data_coordinator.put_batch(infos, samples, caller_node_id=key)
+
+    def get_data_from_buffers(self, key: str, cur_dp_size: int, cur_dp_rank: int,
+                              batch_size: Optional[int] = None) -> Optional[Batch]:
+        if key in self.internal_data_cache:
+            return self.internal_data_cache.pop(key)
+        n = self.config.actor_rollout_ref.rollout.n
+        adjusted = batch_size or (self.config.data.train_batch_size * n // max(cur_dp_size, 1))
+        flt = lambda info: info.dict_info.get("key") == key  # noqa: E731
+        samples = self.data_coordinator.get_batch_collective(adjusted, cur_dp_rank, cur_dp_size, flt) \
+            if self._dist and self.world_size > 1 else self.data_coordinator.get_batch(adjusted, 0, flt, None)
+        if not samples:
+            return None
+        return Samples2Dict(samples).to(self.device)
+
+    # ================================================================================================
+    # training loop
+    # ================================================================================================
+    def execute_task_graph(self) -> List[Dict[str, float]]:
+        if not self._initialized:
+            self.init_graph()
+        try:
+            self._run_training_loop()
+        finally:
+            if self.tracker is not None:
+                self.tracker.finish()
+        return self.history
+
+    def _maybe_inject_fault(self, node_id: str) -> None:
+        for f in self.config.fault.inject or []:
+            if int(f.get("rank", -1)) == self._rank and int(f.get("step", -1)) == self.global_steps \
+                    and f.get("node", node_id) == node_id and not f.get("_done"):
+                f["_done"] = True
+                kind = f.get("kind", "raise")
+                if kind == "raise":
+                    raise RuntimeError(f"injected fault at rank {self._rank} step {self.global_steps} node {node_id}")
+                if kind == "exit":
+                    sys.stdout.flush()
+                    os._exit(int(f.get("code", 17)))
+                if kind == "sleep":
+                    time.sleep(float(f.get("seconds", 5.0)))
+
+    def _run_training_loop(self) -> None:
+        t = self.config.trainer
+        if t.val_before_train and self.validator.enabled and self.global_steps == 0:
+            val = self.validator.validate()
+            if self._rank == 0 and val and self.tracker:
+                self.tracker.log(val, step=0)
+            if t.val_only:
+                return
+        start_step = self.global_steps
+        per_epoch = self.dataloader.num_train_batches
+        for epoch in range(t.total_epochs):
+            for batch_idx in range(per_epoch):
+                step_index = epoch * per_epoch + batch_idx
+                if step_index < start_step:
+                    continue  # already consumed before the checkpoint we resumed from
+                if self.global_steps >= self.total_training_steps:
+                    return
+                metrics = self._run_training_step(epoch, batch_idx)
+                if metrics is None:
+                    continue
+                self.global_steps += 1
+                is_last = self.global_steps >= self.total_training_steps
+                if self.validator.enabled and t.test_freq > 0 and (is_last or self.global_steps % t.test_freq == 0):
+                    metrics.update(self.validator.validate() or {})
+                if t.save_freq > 0 and (is_last or self.global_steps % t.save_freq == 0):
+                    with _Timer("save_checkpoint", self.timing_raw, False):
+                        self.checkpoint_manager.save_checkpoint(self.global_steps)
+                self.history.append(metrics)
+                if self._rank == 0 and self.tracker is not None:
+                    self.tracker.log(metrics, step=self.global_steps)
+
+    def _run_training_step(self, epoch: int, batch_idx: int) -> Optional[Dict[str, float]]:
+        self.timing_raw = {}
+        metrics: Dict[str, float] = {}
+        n = self.config.actor_rollout_ref.rollout.n
+        with _Timer("step", self.timing_raw, True):
+            with _Timer("data_loading", self.timing_raw, False):
+                batch = preprocess_dataloader(self.dataloader.run(epoch=epoch), n).to(self.device)
+            order = self.taskgraph.get_topological_sort()
+            queue = deque(order)
+            cur: Optional[Batch] = batch
+            prev_dp = None
+            while queue:
+                node = self.taskgraph.nodes[queue.popleft()]
+                dp_size, dp_rank, tp_rank, tp_size = self._get_node_dp_info(node)
+                if prev_dp is not None:
+                    got = self.get_data_from_buffers(node.node_id, dp_size, dp_rank)
+                    if got is None:
+                        # not enough filtered samples yet (DAPO): roll out another generation batch
+                        self._dapo_gen_batches += 1
+                        limit = self.config.algorithm.filter_groups.max_num_gen_batches
+                        if limit > 0 and self._dapo_gen_batches >= limit:
+                            raise RuntimeError(f"{self._dapo_gen_batches} generation batches gave too few usable "
+                                               f"groups; check the reward or raise filter_groups.max_num_gen_batches")
+                        return None
+                    cur = got
+                self._maybe_inject_fault(node.node_id)
+                with _Timer(node.node_id, self.timing_raw, self.enable_perf or node.node_type in (
+                        NodeType.MODEL_TRAIN, NodeType.MODEL_INFERENCE)):
+                    out = node.run(batch=cur, config=self.config, process_group=self._node_group(node),
+                                   agent_group=node.agent_group, cur_tp_rank=tp_rank, tp_size=tp_size, cur_node=node,
+                                   _dag_worker_instance=self)
+                if not isinstance(out, NodeOutput):
+                    out = NodeOutput(out if out is not None else cur, {})
+                metrics.update(out.metrics or {})
+                cur = out.batch
+                if cur is None or cur.batch_size == 0:
+                    self._dapo_gen_batches += 1
+                    return None
+                nxt = self.taskgraph.get_dependents(node.node_id)
+                enforce = node.node_role == NodeRole.DYNAMIC_SAMPLING
+                for child in nxt:
+                    cdp = self._get_node_dp_info(child)[0]
+                    self.put_data_to_buffers(child.node_id, cur, dp_size, cdp, enforce_buffer=enforce)
+                prev_dp = dp_size
+            self._dapo_gen_batches = 0
+        final = cur
+        use_critic = self.config.algorithm.adv_estimator in ("gae", "gae_marft")
+        cpu_view = final.to("cpu")
+        metrics.update(compute_data_metric(cpu_view, use_critic))
+        metrics.update(compute_timing_metrics(cpu_view, self.timing_raw))
+        metrics.update(compute_throughput_metrics(cpu_view, self.timing_raw, 1))
+        metrics = reduce_metrics_across_ranks({k: float(v) for k, v in metrics.items()
+                                               if isinstance(v, (int, float))})
+        metrics["training/global_step"] = self.global_steps + 1
+        metrics["training/epoch"] = epoch
+        return metrics

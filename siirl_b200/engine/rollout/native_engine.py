@@ -135,8 +135,16 @@ class RolloutEngine:
         self.cache = torch.zeros(c.num_layers, nb, 2, c.num_kv_heads, BLOCK, c.head_dim, dtype=self.dtype,
                                  device=self.device)
         self.alloc = BlockAllocator(nb)
-        S = self.max_num_seqs
+        self.num_slots = 0
+        self._graphs.clear()
+        self._out_buf = None
+
+    def _ensure_slots(self, S: int) -> None:
+        """(Re)allocate the per-slot device state for ``S`` concurrent sequences."""
+        if self.num_slots == S:
+            return
         dev = self.device
+        self.num_slots = S
         self.block_table = torch.full((S, self.max_blocks_per_seq), -1, dtype=torch.int32, device=dev)
         self.ctx_len = torch.zeros(S, dtype=torch.int32, device=dev)       # tokens in the cache
         self.last_token = torch.zeros(S, dtype=torch.int64, device=dev)
@@ -176,7 +184,7 @@ class RolloutEngine:
     # ---- decode ---------------------------------------------------------------------------------
     def _decode_step(self, sp: SamplingParams, tokens_out: torch.Tensor, logp_out: torch.Tensor) -> None:
         """One lock-step decode of all slots.  Pure device work (graph-capturable)."""
-        S = self.max_num_seqs
+        S = self.num_slots
         active = ~self.finished
         pos = torch.where(active, self.ctx_len, torch.full_like(self.ctx_len, -1))
         seq_ids = torch.where(active, self.slot_ids, torch.full_like(self.slot_ids, -1))
@@ -241,7 +249,9 @@ class RolloutEngine:
         """Generate ``sp.n`` samples for every prompt (token id lists).  Returns outputs ordered by
         (prompt_index, sample_index)."""
         assert self.cache is not None, "engine is asleep: call wake_up()"
-        S, dev = self.max_num_seqs, self.device
+        dev = self.device
+        S = min(self.max_num_seqs, max(8, (len(prompts) * sp.n + 7) // 8 * 8))
+        self._ensure_slots(S)
         R = sp.max_new_tokens
         waiting: List[int] = list(range(len(prompts)))[::-1]
         results: Dict[tuple, RolloutOutput] = {}

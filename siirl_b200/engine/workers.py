@@ -1,0 +1,488 @@
+"""Role-level workers: actor / rollout / reference (hybrid engine), critic, reward model.
+
+Public methods are the reference's worker API (siirl/engine/fsdp_workers.py:1152-1499, 1713-1815, 2058):
+``init_model``, ``generate_sequences``, ``compute_log_prob``, ``compute_ref_log_prob``, ``update_actor``,
+``compute_values``, ``update_critic``, ``compute_rm_score``, ``save_checkpoint``, ``load_checkpoint``.
+
+What is different underneath: the model is this framework's packed decoder on sm_100a kernels; parameters live in a
+:class:`FlatParamStore` (replicated bf16 working copy, sharded fp32 master + Adam state); rollout is the native
+paged-KV engine that reads the actor's weights in place (weight "resync" is free when rollout TP = 1 and one
+fused regather kernel otherwise); batches stay on the GPU between calls — the reference moves every batch
+GPU->CPU->GPU around each worker call (fsdp_workers.py:1271-1347).
+"""
+from __future__ import annotations
+
+import math
+import time
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..dag_worker import core_algos
+from ..data_coordinator.protocol import Batch
+from ..models.config import DecoderConfig, get_config
+from ..models.decoder import DecoderLM, build_model
+from ..parallel.flat_params import FlatParamStore, lr_at_step
+from ..utils.model_utils.seqlen_balancing import rearrange_micro_batches
+from .packing import PackedBatch, get_response_mask, pack_batch, position_ids_from_mask
+from .rollout.native_engine import RolloutEngine, SamplingParams
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32, "bf16": torch.bfloat16,
+           "fp32": torch.float32}
+
+
+def resolve_model_config(model_args, value_head: bool = False) -> DecoderConfig:
+    name = model_args.arch_preset or model_args.path
+    cfg = get_config(name, dict(model_args.override_config or {}))
+    if value_head:
+        cfg.value_head = True
+        cfg.tie_word_embeddings = False
+    return cfg
+
+
+def _micro_batches(batch: Batch, micro_bs: Optional[int], use_dynamic: bool, max_tokens: int, group=None):
+    """Yield ``(index list, micro batch)`` pairs."""
+    if use_dynamic:
+        lens = batch["attention_mask"].sum(-1).tolist()
+        parts = rearrange_micro_batches(lens, max_tokens, dp_group=group)
+    else:
+        bs = batch.batch_size
+        micro_bs = micro_bs or bs
+        parts = [list(range(s, min(s + micro_bs, bs))) for s in range(0, bs, micro_bs)]
+    return [(p, batch.select_idxs(p)) for p in parts]
+
+
+class _ModelWorkerBase:
+    def __init__(self, config, role: str, process_group=None, device: Optional[torch.device] = None, comm=None,
+                 seed: int = 1):
+        self.config = config
+        self.role = role
+        self.group = process_group
+        self.comm = comm
+        self.seed = seed
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else \
+                torch.device("cpu")
+        self.device = torch.device(device)
+        self.world = dist.get_world_size(process_group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.rank = dist.get_rank(process_group) if self.world > 1 else 0
+        self.model: Optional[DecoderLM] = None
+        self.store: Optional[FlatParamStore] = None
+        self.opt_step = 0
+        self.total_training_steps = 0
+
+    def _dtype(self, model_args) -> torch.dtype:
+        if self.device.type == "cpu":
+            return torch.float32
+        return _DTYPES.get(model_args.fsdp_config.model_dtype, torch.bfloat16)
+
+    def _build(self, model_args, value_head: bool, trainable: bool, seed_offset: int = 0) -> None:
+        mcfg = resolve_model_config(model_args, value_head)
+        self.model_config = mcfg
+        self.model = build_model(mcfg, dtype=self._dtype(model_args), device=self.device,
+                                 seed=self.seed + seed_offset,
+                                 gradient_checkpointing=model_args.enable_gradient_checkpointing and trainable)
+        path = model_args.path
+        if path and not model_args.random_init and not model_args.arch_preset:
+            from ..models.hf_io import load_hf_weights
+            load_hf_weights(self.model, path)
+        if trainable:
+            self.store = FlatParamStore(self.model, group=self.group, comm=self.comm)
+        else:
+            for p in self.model.parameters():
+                p.requires_grad_(False)
+
+    # ---- shared forward ---------------------------------------------------------------------------
+    def _pack(self, mb: Batch) -> PackedBatch:
+        R = mb["responses"].shape[1]
+        return pack_batch(mb["input_ids"].to(self.device), mb["attention_mask"].to(self.device), R)
+
+    def _forward_logprob(self, model: DecoderLM, mb: Batch, temperature: float, with_entropy: bool):
+        pk = self._pack(mb)
+        hidden = model.forward_hidden(pk.input_ids, pk.positions, pk.info)
+        from ..ops.lm_head import lm_head_logprob_entropy
+        lp, ent = lm_head_logprob_entropy(hidden.index_select(0, pk.sel), model.head_weight, pk.labels, temperature,
+                                          with_entropy)
+        return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
+
+    def _optimizer_step(self, optim_cfg, grad_clip: float) -> torch.Tensor:
+        lr = lr_at_step(optim_cfg, self.opt_step, max(self.total_training_steps, optim_cfg.total_training_steps))
+        norm = self.store.step(lr, tuple(optim_cfg.betas), 1e-8, optim_cfg.weight_decay, grad_clip)
+        self.store.zero_grad()
+        self.opt_step += 1
+        self.last_lr = lr
+        return norm
+
+    # ---- checkpoints --------------------------------------------------------------------------------
+    def save_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, global_step: int = 0,
+                        max_ckpt_to_keep: Optional[int] = None, contents=None) -> None:
+        from ..utils.checkpoint.checkpoint_manager import ShardedCheckpointManager
+        ShardedCheckpointManager(self.model, self.store, self.model_config, group=self.group,
+                                 contents=contents).save(local_path, global_step, extra={"opt_step": self.opt_step},
+                                                         max_ckpt_to_keep=max_ckpt_to_keep)
+
+    def load_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None,
+                        del_local_after_load: bool = False) -> None:
+        from ..utils.checkpoint.checkpoint_manager import ShardedCheckpointManager
+        extra = ShardedCheckpointManager(self.model, self.store, self.model_config, group=self.group).load(local_path)
+        if extra:
+            self.opt_step = int(extra.get("opt_step", self.opt_step))
+
+
+class ActorRolloutRefWorker(_ModelWorkerBase):
+    """One class for the roles actor, rollout, ref and their combinations (``actor_rollout_ref`` = hybrid)."""
+
+    def __init__(self, config, role: str = "actor_rollout_ref", process_group=None, device=None, comm=None,
+                 seed: int = 1, tokenizer=None):
+        super().__init__(config, role, process_group, device, comm, seed)
+        assert role in ("actor", "rollout", "ref", "actor_rollout", "actor_rollout_ref")
+        self._is_actor = "actor" in role
+        self._is_rollout = "rollout" in role
+        self._is_ref = "ref" in role
+        self.tokenizer = tokenizer
+        self.ref_model: Optional[DecoderLM] = None
+        self.engine: Optional[RolloutEngine] = None
+        self._normalize_batch_sizes()
+
+    def _normalize_batch_sizes(self) -> None:
+        """Global mini-batch -> per-rank sample count (reference: fsdp_workers.py:211-235)."""
+        a = self.config.actor
+        n = self.config.rollout.n
+        dp = max(self.world // max(a.ulysses_sequence_parallel_size, 1), 1)
+        self.ppo_mini_batch_size = max(1, a.ppo_mini_batch_size * n // dp)
+        micro = a.ppo_micro_batch_size_per_gpu
+        if micro is None and a.ppo_micro_batch_size is not None:
+            micro = max(1, a.ppo_micro_batch_size // dp)
+        self.ppo_micro_batch_size = micro
+        if micro is not None and not a.use_dynamic_bsz:
+            if self.ppo_mini_batch_size % micro != 0:
+                self.ppo_micro_batch_size = math.gcd(self.ppo_mini_batch_size, micro)
+        r = self.config.rollout
+        self.logprob_micro = r.log_prob_micro_batch_size_per_gpu or (
+            max(1, r.log_prob_micro_batch_size // dp) if r.log_prob_micro_batch_size else micro)
+        rf = self.config.ref
+        self.ref_logprob_micro = rf.log_prob_micro_batch_size_per_gpu or (
+            max(1, rf.log_prob_micro_batch_size // dp) if rf.log_prob_micro_batch_size else self.logprob_micro)
+
+    # ---- init ---------------------------------------------------------------------------------------
+    def init_model(self) -> None:
+        margs = self.config.model
+        if self._is_actor or self._is_rollout:
+            self._build(margs, value_head=False, trainable=self._is_actor)
+        if self._is_ref:
+            mcfg = resolve_model_config(margs)
+            self.ref_model = build_model(mcfg, dtype=self._dtype(margs), device=self.device, seed=self.seed)
+            if margs.path and not margs.random_init and not margs.arch_preset:
+                from ..models.hf_io import load_hf_weights
+                load_hf_weights(self.ref_model, margs.path)
+            for p in self.ref_model.parameters():
+                p.requires_grad_(False)
+            if self.model is None:
+                self.model_config = mcfg
+        if self._is_rollout:
+            r = self.config.rollout
+            max_len = r.max_model_len or ((r.prompt_length or 512) + (r.response_length or 512))
+            self.engine = RolloutEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024), max_model_len=max_len,
+                                        gpu_memory_utilization=r.gpu_memory_utilization,
+                                        use_cuda_graph=not r.enforce_eager or self.device.type == "cuda",
+                                        max_num_batched_tokens=r.max_num_batched_tokens,
+                                        **dict(r.engine_kwargs.native or {}))
+            if r.free_cache_engine:
+                self.engine.sleep()
+
+    # ---- rollout -------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def generate_sequences(self, prompts: Batch) -> Batch:
+        """Roll out responses.  Input: left-padded ``input_ids/attention_mask/position_ids`` ``[B, P]`` and
+        ``raw_prompt_ids``; rows with equal ``uid`` that follow each other are samples of one prompt (prefilled
+        once).  Output adds ``prompts, responses, input_ids [B, P+R], attention_mask, position_ids, response_mask,
+        rollout_log_probs``."""
+        r = self.config.rollout
+        t0 = time.time()
+        self.engine.wake_up()
+        meta = prompts.meta
+        validate = bool(meta.get("validate", False))
+        do_sample = bool(meta.get("do_sample", r.do_sample))
+        temperature, top_k, top_p = r.temperature, r.top_k, r.top_p
+        if validate:
+            v = r.val_kwargs
+            temperature, top_k, top_p, do_sample = v.temperature, v.top_k, v.top_p, v.do_sample
+        if not do_sample:
+            temperature = 0.0
+        R = int(meta.get("response_length", r.response_length))
+        ids = prompts["input_ids"]
+        B, P = ids.shape
+        raw = prompts["raw_prompt_ids"] if "raw_prompt_ids" in prompts else [
+            ids[i][prompts["attention_mask"][i].bool()].tolist() for i in range(B)]
+        uid = prompts["uid"].tolist() if "uid" in prompts else list(range(B))
+        groups: List[List[int]] = []
+        for i in range(B):
+            if groups and uid[groups[-1][0]] == uid[i] and list(raw[groups[-1][0]]) == list(raw[i]):
+                groups[-1].append(i)
+            else:
+                groups.append([i])
+        n = len(groups[0])
+        uniform = all(len(g) == n for g in groups)
+        eos = meta.get("eos_token_id", self.model_config.eos_token_id)
+        pad = meta.get("pad_token_id", self.model_config.pad_token_id)
+        sp = SamplingParams(n=n if uniform else 1, temperature=float(temperature), top_k=int(top_k),
+                            top_p=float(top_p), max_new_tokens=R, eos_token_id=eos, ignore_eos=r.ignore_eos,
+                            seed=(r.seed + 7919 * int(meta.get("global_steps", 0)) + 104729 * self.rank) & 0x7FFFFFFF)
+        if uniform:
+            outs = self.engine.generate([list(raw[g[0]]) for g in groups], sp)
+            order = [i for g in groups for i in g]
+        else:
+            outs = self.engine.generate([list(raw[i]) for i in range(B)], sp)
+            order = list(range(B))
+        responses = torch.full((B, R), pad, dtype=torch.int64)
+        logps = torch.zeros(B, R, dtype=torch.float32)
+        for row, o in zip(order, outs):
+            L = len(o.token_ids)
+            responses[row, :L] = torch.tensor(o.token_ids, dtype=torch.int64)
+            logps[row, :L] = torch.tensor(o.logprobs, dtype=torch.float32)
+        dev = ids.device
+        responses, logps = responses.to(dev), logps.to(dev)
+        resp_mask = get_response_mask(responses, eos, dtype=torch.int64)
+        lens = torch.tensor([len(o.token_ids) for o in outs], dtype=torch.int64)
+        len_by_row = torch.zeros(B, dtype=torch.int64)
+        len_by_row[torch.tensor(order)] = lens
+        resp_mask = resp_mask * (torch.arange(R)[None, :] < len_by_row[:, None]).to(dev)
+        attn = torch.cat([prompts["attention_mask"], resp_mask], dim=-1)
+        out = Batch(dict(prompts.tensors), dict(prompts.non_tensors), dict(prompts.meta))
+        out["prompts"] = ids
+        out["responses"] = responses
+        out["input_ids"] = torch.cat([ids, responses], dim=-1)
+        out["attention_mask"] = attn
+        out["position_ids"] = position_ids_from_mask(attn)
+        out["response_mask"] = resp_mask
+        out["rollout_log_probs"] = logps
+        out.meta["timing_generate_s"] = time.time() - t0
+        out.meta["total_output_tokens"] = int(lens.sum())
+        out.meta["total_input_tokens"] = int(prompts["attention_mask"].sum())
+        if r.free_cache_engine:
+            self.engine.sleep()
+        return out
+
+    # ---- scoring ----------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def _logprob_pass(self, model: DecoderLM, data: Batch, micro: Optional[int], dynamic: bool, max_tokens: int,
+                      with_entropy: bool):
+        temperature = float(data.meta.get("temperature", self.config.rollout.temperature)) or 1.0
+        B, R = data["responses"].shape
+        lp_out = torch.zeros(B, R, dtype=torch.float32, device=self.device)
+        ent_out = torch.zeros(B, R, dtype=torch.float32, device=self.device) if with_entropy else None
+        model.eval()
+        for idx, mb in _micro_batches(data, micro, dynamic, max_tokens, self.group):
+            lp, ent = self._forward_logprob(model, mb, temperature, with_entropy)
+            ii = torch.tensor(idx, device=self.device)
+            lp_out[ii] = lp
+            if ent_out is not None:
+                ent_out[ii] = ent
+        return lp_out, ent_out
+
+    def compute_log_prob(self, data: Batch) -> Batch:
+        r = self.config.rollout
+        lp, ent = self._logprob_pass(self.model, data, self.logprob_micro, r.log_prob_use_dynamic_bsz,
+                                     r.log_prob_max_token_len_per_gpu, with_entropy=True)
+        data["old_log_probs"] = lp
+        data["entropys"] = ent
+        m = data["response_mask"].to(ent.device).float()
+        data.meta.setdefault("metrics", {})["actor/entropy"] = float((ent * m).sum() / m.sum().clamp(min=1))
+        return data
+
+    def compute_ref_log_prob(self, data: Batch) -> Batch:
+        rf = self.config.ref
+        model = self.ref_model if self.ref_model is not None else self.model
+        lp, _ = self._logprob_pass(model, data, self.ref_logprob_micro, rf.log_prob_use_dynamic_bsz,
+                                   rf.log_prob_max_token_len_per_gpu, with_entropy=False)
+        data["ref_log_prob"] = lp
+        return data
+
+    # ---- training ------------------------------------------------------------------------------------------
+    def update_actor(self, data: Batch) -> Dict[str, Any]:
+        """PPO / GRPO policy update over ``ppo_epochs`` x mini-batches x micro-batches
+        (reference: siirl/engine/actor/dp_actor.py:349-520).  Returns the metric dict."""
+        a = self.config.actor
+        t0 = time.time()
+        self.model.train()
+        temperature = float(data.meta.get("temperature", self.config.rollout.temperature)) or 1.0
+        loss_mode = a.policy_loss.loss_mode if not a.use_cpgd_loss else "cpgd"
+        policy_loss_fn = core_algos.get_policy_loss_fn(loss_mode)
+        entropy_coeff = a.entropy_coeff
+        need_entropy = entropy_coeff != 0
+        metrics: Dict[str, List[float]] = {}
+        bs = data.batch_size
+        mini = min(self.ppo_mini_batch_size, bs)
+        n_mini = max(1, bs // mini)
+        on_policy = a.ppo_epochs == 1 and n_mini == 1
+        self.store.zero_grad()
+        for _epoch in range(a.ppo_epochs):
+            order = torch.randperm(bs).tolist() if a.shuffle else list(range(bs))
+            for mi in range(n_mini):
+                mini_idx = order[mi * mini:(mi + 1) * mini]
+                mini_batch = data.select_idxs(mini_idx)
+                mbs = _micro_batches(mini_batch, self.ppo_micro_batch_size, a.use_dynamic_bsz,
+                                     a.ppo_max_token_len_per_gpu, self.group)
+                for idx, mb in mbs:
+                    scale = (len(idx) / len(mini_idx)) if a.use_dynamic_bsz else 1.0 / len(mbs)
+                    mask = mb["response_mask"].to(self.device).float()
+                    adv = mb["advantages"].to(self.device).float()
+                    logp, ent = self._forward_logprob(self.model, mb, temperature, need_entropy)
+                    old = logp.detach() if on_policy else mb["old_log_probs"].to(self.device).float()
+                    ref = mb["ref_log_prob"].to(self.device).float() if (a.use_kl_loss and "ref_log_prob" in mb) \
+                        else None
+                    is_w = mb["rollout_is_weights"].to(self.device) if "rollout_is_weights" in mb else None
+                    fused = (logp.is_cuda and loss_mode in ("vanilla", "gspo", "cpgd") and is_w is None
+                             and a.policy_drift_coeff == 0 and not a.kl_loss_type.endswith("+"))
+                    if fused:
+                        from ..ops.rl import ppo_token_loss
+                        lo = a.clip_ratio_low if a.clip_ratio_low is not None else a.clip_ratio
+                        hi = a.clip_ratio_high if a.clip_ratio_high is not None else a.clip_ratio
+                        loss, mm = ppo_token_loss(logp, old, adv, mask, entropy=ent if need_entropy else None,
+                                                  ref_logp=ref, mode=loss_mode, loss_agg_mode=a.loss_agg_mode,
+                                                  clip_lo=lo, clip_hi=hi, clip_c=a.clip_ratio_c,
+                                                  kl_kind=a.kl_loss_type, kl_coef=a.kl_loss_coef if ref is not None
+                                                  else 0.0, entropy_coef=entropy_coeff)
+                        rec = {"actor/pg_loss": mm["pg_loss"], "actor/pg_clipfrac": mm["pg_clipfrac"],
+                               "actor/ppo_kl": mm["ppo_kl"], "actor/pg_clipfrac_lower": mm["pg_clipfrac_lower"]}
+                        if ref is not None:
+                            rec["actor/kl_loss"] = mm["kl_loss"]
+                            rec["actor/kl_coef"] = torch.tensor(a.kl_loss_coef)
+                        if need_entropy:
+                            rec["actor/entropy_loss"] = mm["entropy_loss"]
+                    else:
+                        pg, clipfrac, ppo_kl, clip_lower = policy_loss_fn(old, logp, adv, mask, a.loss_agg_mode, a,
+                                                                          is_w)
+                        loss = pg
+                        rec = {"actor/pg_loss": pg.detach(), "actor/pg_clipfrac": clipfrac.detach(),
+                               "actor/ppo_kl": ppo_kl.detach(), "actor/pg_clipfrac_lower": clip_lower.detach()}
+                        if need_entropy:
+                            el = core_algos.agg_loss(ent, mask, a.loss_agg_mode)
+                            loss = loss - entropy_coeff * el
+                            rec["actor/entropy_loss"] = el.detach()
+                        if ref is not None:
+                            kld = core_algos.kl_penalty(logp, ref, a.kl_loss_type)
+                            kl = core_algos.agg_loss(kld, mask, a.loss_agg_mode)
+                            loss = loss + a.kl_loss_coef * kl
+                            rec["actor/kl_loss"] = kl.detach()
+                            rec["actor/kl_coef"] = torch.tensor(a.kl_loss_coef)
+                        if loss_mode == "cpgd" and a.policy_drift_coeff != 0:
+                            drift = core_algos.cpgd_policy_drift(old, logp, mask, a.loss_agg_mode)
+                            loss = loss + a.policy_drift_coeff * drift
+                            rec["actor/policy_drift"] = drift.detach()
+                    (loss * scale).backward()
+                    for k, v in rec.items():
+                        metrics.setdefault(k, []).append(v)
+                norm = self._optimizer_step(a.optim, a.grad_clip)
+                metrics.setdefault("actor/grad_norm", []).append(norm.detach().clone())
+        out = {k: float(torch.stack([torch.as_tensor(x, dtype=torch.float32, device="cpu") if not
+                                     isinstance(x, torch.Tensor) else x.float().cpu() for x in v]).mean())
+               for k, v in metrics.items()}
+        out["actor/lr"] = self.last_lr
+        if self.device.type == "cuda":
+            out["perf/max_memory_allocated_gb"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
+            out["perf/max_memory_reserved_gb"] = torch.cuda.max_memory_reserved(self.device) / 2 ** 30
+        out["timing_s/update_actor_inner"] = time.time() - t0
+        return out
+
+
+class CriticWorker(_ModelWorkerBase):
+    """Value model (decoder + scalar head) with clipped value loss
+    (reference: siirl/engine/fsdp_workers.py:1506-1815, siirl/engine/critic/dp_critic.py:41-246)."""
+
+    def __init__(self, config, process_group=None, device=None, comm=None, seed: int = 1, rollout_n: int = 1):
+        super().__init__(config, "critic", process_group, device, comm, seed)
+        c = config
+        dp = max(self.world // max(c.ulysses_sequence_parallel_size, 1), 1)
+        self.ppo_mini_batch_size = max(1, c.ppo_mini_batch_size * max(rollout_n, c.rollout_n, 1) // dp)
+        micro = c.ppo_micro_batch_size_per_gpu
+        if micro is None and c.ppo_micro_batch_size is not None:
+            micro = max(1, c.ppo_micro_batch_size // dp)
+        self.ppo_micro_batch_size = micro
+
+    def init_model(self) -> None:
+        self._build(self.config.model, value_head=True, trainable=True, seed_offset=17)
+
+    def _forward_values(self, mb: Batch) -> torch.Tensor:
+        """Values aligned with response tokens ``[B, R]``: the value at the position that predicts token k."""
+        pk = self._pack(mb)
+        hidden = self.model.forward_hidden(pk.input_ids, pk.positions, pk.info)
+        v = (hidden.index_select(0, pk.sel).float() @ self.model.value_head.float().t()).squeeze(-1)
+        return pk.scatter(v)
+
+    @torch.no_grad()
+    def compute_values(self, data: Batch) -> Batch:
+        c = self.config
+        B, R = data["responses"].shape
+        out = torch.zeros(B, R, dtype=torch.float32, device=self.device)
+        self.model.eval()
+        for idx, mb in _micro_batches(data, self.ppo_micro_batch_size, c.use_dynamic_bsz,
+                                      c.forward_max_token_len_per_gpu, self.group):
+            out[torch.tensor(idx, device=self.device)] = self._forward_values(mb)
+        data["values"] = out * data["response_mask"].to(self.device).float()
+        return data
+
+    def update_critic(self, data: Batch) -> Dict[str, Any]:
+        c = self.config
+        self.model.train()
+        metrics: Dict[str, List[torch.Tensor]] = {}
+        bs = data.batch_size
+        mini = min(self.ppo_mini_batch_size, bs)
+        n_mini = max(1, bs // mini)
+        self.store.zero_grad()
+        for _ in range(c.ppo_epochs):
+            order = torch.randperm(bs).tolist() if c.shuffle else list(range(bs))
+            for mi in range(n_mini):
+                mini_idx = order[mi * mini:(mi + 1) * mini]
+                mini_batch = data.select_idxs(mini_idx)
+                mbs = _micro_batches(mini_batch, self.ppo_micro_batch_size, c.use_dynamic_bsz,
+                                     c.ppo_max_token_len_per_gpu, self.group)
+                for idx, mb in mbs:
+                    scale = (len(idx) / len(mini_idx)) if c.use_dynamic_bsz else 1.0 / len(mbs)
+                    mask = mb["response_mask"].to(self.device).float()
+                    vpred = self._forward_values(mb)
+                    vf_loss, vf_clipfrac = core_algos.compute_value_loss(
+                        vpred, mb["returns"].to(self.device).float(), mb["values"].to(self.device).float(), mask,
+                        c.cliprange_value, c.loss_agg_mode)
+                    (vf_loss * scale).backward()
+                    metrics.setdefault("critic/vf_loss", []).append(vf_loss.detach())
+                    metrics.setdefault("critic/vf_clipfrac", []).append(vf_clipfrac.detach())
+                    metrics.setdefault("critic/vpred_mean", []).append(core_algos.masked_mean(vpred.detach(), mask))
+                norm = self._optimizer_step(c.optim, c.grad_clip)
+                metrics.setdefault("critic/grad_norm", []).append(norm.detach().clone())
+        out = {k: float(torch.stack([x.float().cpu() for x in v]).mean()) for k, v in metrics.items()}
+        out["critic/lr"] = self.last_lr
+        return out
+
+
+class RewardModelWorker(_ModelWorkerBase):
+    """Model-based reward: a decoder with a scalar head scores each response at its last valid token
+    (reference: siirl/engine/fsdp_workers.py:1819-2115)."""
+
+    def __init__(self, config, process_group=None, device=None, comm=None, seed: int = 1):
+        super().__init__(config, "reward", process_group, device, comm, seed)
+
+    def init_model(self) -> None:
+        self._build(self.config.model, value_head=True, trainable=False, seed_offset=29)
+
+    @torch.no_grad()
+    def compute_rm_score(self, data: Batch) -> Batch:
+        c = self.config
+        B, R = data["responses"].shape
+        scores = torch.zeros(B, R, dtype=torch.float32, device=self.device)
+        micro = c.micro_batch_size_per_gpu or c.micro_batch_size
+        for idx, mb in _micro_batches(data, micro, c.use_dynamic_bsz, c.forward_max_token_len_per_gpu, self.group):
+            am = mb["attention_mask"].to(self.device)
+            lens = am.sum(-1)
+            from ..ops.attention import SeqInfo
+            info = SeqInfo(lens.tolist(), device=self.device)
+            ids = mb["input_ids"].to(self.device)[am.bool()]
+            v = self.model.values(ids, info.positions, info)
+            last = torch.tensor(info.cu_seqlens_cpu[1:], device=self.device) - 1
+            seq_score = v.index_select(0, last)
+            rl = mb["response_mask"].to(self.device).sum(-1).clamp(min=1) - 1
+            rows = torch.tensor(idx, device=self.device)
+            scores[rows, rl] = seq_score
+        data["rm_scores"] = scores
+        return data

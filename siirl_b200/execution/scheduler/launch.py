@@ -1,0 +1,129 @@
+"""Configuration validation and the multi-process launcher.
+
+``validate_config`` holds the reference's launch-time checks (siirl/execution/scheduler/launch.py:94-308):
+micro-batch parameter exclusivity, divisibility of batch sizes by the data-parallel width, ``loss_agg_mode``
+whitelist, sequence parallelism requires remove-padding (always true here: the packed layout is native), critic
+needed iff the advantage estimator is GAE.
+
+``launch_local`` replaces the Ray actor manager (ray_actor_manager.py:128-286, resource_manager.py:31-132): it spawns
+one OS process per GPU on this node with torchrun-style environment variables (RANK, LOCAL_RANK, WORLD_SIZE,
+MASTER_ADDR=127.0.0.1, MASTER_PORT), watches child exit codes and a per-rank heartbeat in a TCPStore, and on the
+first failure terminates the remaining ranks (fail-fast, as the reference's driver does on ``ActorDiedError``),
+optionally restarting the job from the latest complete checkpoint (``fault.auto_restart``)."""
+from __future__ import annotations
+
+import os
+import socket
+import subprocess
+import sys
+import time
+from typing import Dict, List, Optional
+
+_LOSS_AGG_MODES = ("token-mean", "seq-mean-token-sum", "seq-mean-token-mean", "seq-mean-token-sum-norm")
+
+
+def use_critic(config) -> bool:
+    return config.algorithm.adv_estimator in ("gae", "gae_marft")
+
+
+def validate_config(config, world_size: Optional[int] = None) -> None:
+    t = config.trainer
+    world = world_size or t.nnodes * t.n_gpus_per_node
+    a, r, rf, c = (config.actor_rollout_ref.actor, config.actor_rollout_ref.rollout, config.actor_rollout_ref.ref,
+                   config.critic)
+    tp = max(1, r.tensor_model_parallel_size)
+    if world % tp:
+        raise ValueError(f"world size {world} is not divisible by rollout tensor_model_parallel_size {tp}")
+    bs = config.data.gen_batch_size or config.data.train_batch_size
+    if bs % (world // tp):
+        raise ValueError(f"data batch size {bs} must be divisible by the rollout data-parallel width {world // tp}")
+
+    def check_mutually_exclusive(mbs, mbs_per_gpu, name: str):
+        if mbs is not None and mbs_per_gpu is not None and mbs_per_gpu != 1:
+            raise ValueError(f"[{name}] You have set both '{name}.micro_batch_size' and "
+                             f"'{name}.micro_batch_size_per_gpu'. Please remove '{name}.micro_batch_size' because "
+                             f"only '*_micro_batch_size_per_gpu' is supported (the former is deprecated).")
+
+    if not a.use_dynamic_bsz:
+        check_mutually_exclusive(a.ppo_micro_batch_size, a.ppo_micro_batch_size_per_gpu, "actor_rollout_ref.actor")
+        check_mutually_exclusive(rf.log_prob_micro_batch_size, rf.log_prob_micro_batch_size_per_gpu,
+                                 "actor_rollout_ref.ref")
+        check_mutually_exclusive(r.log_prob_micro_batch_size, r.log_prob_micro_batch_size_per_gpu,
+                                 "actor_rollout_ref.rollout")
+        if a.ppo_micro_batch_size_per_gpu is None and a.ppo_micro_batch_size is None:
+            raise ValueError("[actor_rollout_ref.actor] set ppo_micro_batch_size_per_gpu or use_dynamic_bsz=True")
+        sp = max(1, a.ulysses_sequence_parallel_size)
+        if config.data.train_batch_size < a.ppo_mini_batch_size:
+            raise ValueError("data.train_batch_size must be >= actor.ppo_mini_batch_size")
+        if (a.ppo_mini_batch_size * r.n) % max(world // sp, 1):
+            raise ValueError(f"actor.ppo_mini_batch_size * rollout.n ({a.ppo_mini_batch_size * r.n}) must be divisible "
+                             f"by the data-parallel width {world // sp}")
+    if a.loss_agg_mode not in _LOSS_AGG_MODES:
+        raise ValueError(f"Invalid loss_agg_mode: {a.loss_agg_mode}; choose from {_LOSS_AGG_MODES}")
+    if use_critic(config):
+        if not c.use_dynamic_bsz:
+            check_mutually_exclusive(c.ppo_micro_batch_size, c.ppo_micro_batch_size_per_gpu, "critic")
+        if c.loss_agg_mode not in _LOSS_AGG_MODES:
+            raise ValueError(f"Invalid critic loss_agg_mode: {c.loss_agg_mode}")
+    if config.algorithm.use_kl_in_reward and a.use_kl_loss:
+        print("NOTICE: both in-reward KL and KL loss are enabled.", file=sys.stderr)
+    if r.multi_turn.enable and r.name not in ("sglang", "native", "vllm"):
+        raise ValueError("multi-turn rollout needs an engine with an async generate API")
+    if r.val_kwargs.do_sample and r.temperature <= 0:
+        raise ValueError("validation sampling needs rollout.temperature > 0")
+    if config.algorithm.adv_estimator not in ("gae", "grpo", "cpgd", "gae_marft"):
+        from ...dag_worker.core_algos import ADV_ESTIMATOR_REGISTRY
+        if config.algorithm.adv_estimator not in ADV_ESTIMATOR_REGISTRY:
+            raise ValueError(f"unknown advantage estimator '{config.algorithm.adv_estimator}'")
+
+
+def find_free_port() -> int:
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = None, poll_s: float = 0.5,
+                 heartbeat_timeout_s: float = 0.0, module: str = "siirl_b200.main_dag") -> int:
+    """Spawn ``nproc`` ranks of ``python -m <module> <argv>`` on this node and babysit them.  Returns the exit code
+    (0 when every rank exited 0; otherwise the first non-zero code after the remaining ranks were terminated)."""
+    port = find_free_port()
+    procs: List[subprocess.Popen] = []
+    base = dict(os.environ)
+    base.update(env or {})
+    base.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "WORLD_SIZE": str(nproc),
+                 "LOCAL_WORLD_SIZE": str(nproc), "SIIRL_LAUNCHED": "1"})
+    for r in range(nproc):
+        e = dict(base)
+        e.update({"RANK": str(r), "LOCAL_RANK": str(r)})
+        procs.append(subprocess.Popen([sys.executable, "-m", module, *argv], env=e))
+    store = None
+    if heartbeat_timeout_s > 0:
+        import datetime
+
+        import torch.distributed as dist
+        store = dist.TCPStore("127.0.0.1", find_free_port(), is_master=True, wait_for_workers=False,
+                              timeout=datetime.timedelta(seconds=5))
+    code = 0
+    try:
+        while True:
+            states = [p.poll() for p in procs]
+            bad = [s for s in states if s not in (None, 0)]
+            if bad:
+                code = bad[0]
+                break
+            if all(s == 0 for s in states):
+                break
+            time.sleep(poll_s)
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.terminate()
+        deadline = time.time() + 10
+        for p in procs:
+            try:
+                p.wait(timeout=max(0.1, deadline - time.time()))
+            except subprocess.TimeoutExpired:
+                p.kill()
+        _ = store
+    return code
