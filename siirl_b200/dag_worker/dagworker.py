@@ -83,6 +83,7 @@ class DAGWorker:
         self.kl_ctrl_in_reward = None
         self.history: List[Dict[str, float]] = []
         self._dapo_gen_batches = 0
+        self.last_step_tokens = self.last_h2d_bytes = self.last_d2h_bytes = 0
         self._initialized = False
 
     # ================================================================================================
@@ -383,7 +384,14 @@ class DAGWorker:
         n = self.config.actor_rollout_ref.rollout.n
         with _Timer("step", self.timing_raw, True):
             with _Timer("data_loading", self.timing_raw, False):
-                batch = preprocess_dataloader(self.dataloader.run(epoch=epoch), n).to(self.device)
+                batch = self.dataloader.run(epoch=epoch)
+                self.last_h2d_bytes = 0
+                if not getattr(self, "_bench_prestaged", False):
+                    batch = preprocess_dataloader(batch, n)
+                    if self.device.type == "cuda":
+                        batch = batch.pin_memory()
+                        self.last_h2d_bytes = batch.nbytes()
+                    batch = batch.to(self.device)
             order = self.taskgraph.get_topological_sort()
             queue = deque(order)
             cur: Optional[Batch] = batch
@@ -424,7 +432,13 @@ class DAGWorker:
             self._dapo_gen_batches = 0
         final = cur
         use_critic = self.config.algorithm.adv_estimator in ("gae", "gae_marft")
-        cpu_view = final.to("cpu")
+        keep = [k for k in ("response_mask", "attention_mask", "token_level_scores", "token_level_rewards",
+                            "advantages", "returns", "values") if k in final.tensors]
+        cpu_view = Batch({k: final.tensors[k] for k in keep}, None, final.meta).to("cpu")
+        self.last_step_tokens = int(cpu_view["attention_mask"].sum())
+        self.last_d2h_bytes = cpu_view.nbytes() + 8 * len(metrics) + sum(
+            getattr(w, "engine", None).stats.pop("d2h_bytes", 0) for w in self.workers.values()
+            if getattr(w, "engine", None) is not None)
         metrics.update(compute_data_metric(cpu_view, use_critic))
         metrics.update(compute_timing_metrics(cpu_view, self.timing_raw))
         metrics.update(compute_throughput_metrics(cpu_view, self.timing_raw, 1))

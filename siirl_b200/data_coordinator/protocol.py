@@ -189,6 +189,13 @@ class Batch:
         return Batch({k: v.to(device, non_blocking=True) for k, v in self.tensors.items()}, self.non_tensors,
                      self.meta)
 
+    def pin_memory(self) -> "Batch":
+        return Batch({k: (v.pin_memory() if not v.is_cuda else v) for k, v in self.tensors.items()}, self.non_tensors,
+                     self.meta)
+
+    def nbytes(self) -> int:
+        return sum(v.numel() * v.element_size() for v in self.tensors.values())
+
     def clone(self) -> "Batch":
         return Batch({k: v.clone() for k, v in self.tensors.items()},
                      {k: v.copy() for k, v in self.non_tensors.items()}, copy.deepcopy(self.meta))

@@ -111,6 +111,7 @@ class RolloutEngine:
         self.cache: Optional[torch.Tensor] = None
         self.alloc: Optional[BlockAllocator] = None
         self._graphs: Dict[int, object] = {}
+        self._graph_launches: Dict[int, int] = {}
         self._out_buf = None
         self.stats = {"prefill_tokens": 0, "decode_steps": 0, "generated_tokens": 0}
         self.wake_up()
@@ -234,14 +235,19 @@ class RolloutEngine:
                                  self.gen_index, self.hit_eos, tokens_out, logp_out), snapshot):
                 dst.copy_(src)
             g = torch.cuda.CUDAGraph()
+            before = _lib.launch_count()
             with torch.cuda.graph(g):
                 for _ in range(k):
                     self._decode_step(sp, tokens_out, logp_out)
+            self._graph_launches[key] = _lib.launch_count() - before
+            _lib.add_launches(-self._graph_launches[key])  # capture itself runs nothing
             for dst, src in zip((self.ctx_len, self.last_token, self.finished, self.remaining, self.step_counter,
                                  self.gen_index, self.hit_eos, tokens_out, logp_out), snapshot):
                 dst.copy_(src)
             self._graphs[key] = g
         g.replay()
+        from ...ops import lib as _l
+        _l.add_launches(self._graph_launches.get(key, 0))
 
     # ---- public API -------------------------------------------------------------------------------
     @torch.no_grad()
@@ -277,6 +283,7 @@ class RolloutEngine:
             seq = slots[slot]
             toks = tokens_out[slot, :n_gen].tolist()
             lps = logp_out[slot, :n_gen].tolist()
+            self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + 12 * n_gen
             results[(seq.prompt_index, seq.sample_index)] = RolloutOutput(seq.prompt_index, seq.sample_index, toks,
                                                                          lps, fin_reason)
             for b in seq.blocks:
@@ -360,6 +367,7 @@ class RolloutEngine:
             fin_cpu = self.finished.cpu().tolist()
             gen_cpu = self.gen_index.cpu().tolist()
             eos_cpu = self.hit_eos.cpu().tolist()
+            self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + 6 * S
             for slot, seq in enumerate(slots):
                 if seq is not None and fin_cpu[slot]:
                     retire(slot, "stop" if eos_cpu[slot] else "length", gen_cpu[slot])

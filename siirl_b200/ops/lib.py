@@ -15,8 +15,45 @@ from typing import Optional
 import torch
 
 _LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libsiirl_b200.so"
-_lib: Optional[ctypes.CDLL] = None
+_lib: Optional["_CountingLib"] = None
 _status_words: dict[int, torch.Tensor] = {}
+
+# kernels launched by one call of each entry point (for the launch counter of the benchmark)
+_KERNELS_PER_CALL = {"sb_rmsnorm_bwd": 2, "sb_grpo_group_adv": 4, "sb_fmha_bwd": 3, "sb_kk_partition": 0,
+                     "sb_rmsnorm_bwd_blocks": 0}
+
+
+class _CountingLib:
+    """Thin proxy over the ctypes library that counts kernel launches made through it."""
+
+    def __init__(self, cdll: ctypes.CDLL):
+        self._cdll = cdll
+        self.launches = 0
+        self._cache: dict = {}
+
+    def __getattr__(self, name: str):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._cdll, name)
+            k = _KERNELS_PER_CALL.get(name, 1)
+
+            def counted(*args, _raw=raw, _k=k):
+                self.launches += _k
+                return _raw(*args)
+
+            fn = counted
+            self._cache[name] = fn
+        return fn
+
+
+def launch_count() -> int:
+    """Number of kernels of this library launched so far in this process (graph replays included)."""
+    return _lib.launches if _lib is not None else 0
+
+
+def add_launches(n: int) -> None:
+    if _lib is not None:
+        _lib.launches += n
 
 
 class NativeLibraryMissing(ImportError):
@@ -41,14 +78,15 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
-def get_lib() -> ctypes.CDLL:
+def get_lib() -> "_CountingLib":
     global _lib
     if _lib is None:
         if not _LIB_PATH.exists():
             raise NativeLibraryMissing(
                 f"{_LIB_PATH} not found: run `python -m siirl_b200.build_ext` (or __graft_entry__.build())")
         import torch  # noqa: F401  (loads libcudart.so.12 into the process first)
-        _lib = ctypes.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL") else ctypes.DEFAULT_MODE)
+        _lib = _CountingLib(ctypes.CDLL(str(_LIB_PATH), mode=os.RTLD_GLOBAL if hasattr(os, "RTLD_GLOBAL")
+                                        else ctypes.DEFAULT_MODE))
     return _lib
 
 
