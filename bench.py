@@ -182,6 +182,8 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
+    split = {}
+
     def run_steps(k: int, prestaged: bool):
         """Runs k GRPO steps; returns (tokens on this rank, h2d bytes, d2h bytes)."""
         tokens = h2d = d2h = 0
@@ -197,6 +199,8 @@ def main() -> int:
             worker._bench_prestaged = False
             worker.global_steps += 1
             tokens += int(worker.last_step_tokens)
+            split.clear()
+            split.update({k: round(v, 4) for k, v in worker.timing_raw.items()})
             h2d += int(worker.last_h2d_bytes)
             d2h += int(worker.last_d2h_bytes)
             assert m is not None
@@ -233,6 +237,7 @@ def main() -> int:
 
     ms, tokens_all, launches, _, _, clocks = timed(prestaged=True)
     value = tokens_all / (ms / 1e3)
+    step_split = dict(split)
     e2e = None
     if not args.skip_e2e:
         ms2, tokens2, _, h2d, d2h, _ = timed(prestaged=False)
@@ -254,7 +259,7 @@ def main() -> int:
                        "micro_batch": args.micro_batch, "l2": "inputs larger than L2 (15 GB of weights per pass)",
                        "baseline_note": "vs_baseline divides tokens/s/GPU by the reference's only published absolute "
                                         "number (3473.8 tokens/s/GPU, Qwen2.5-0.5B, 1 GPU of unstated type)"},
-            "clocks": clocks, "gpu_launches": launches, "impl": "native",
+            "clocks": clocks, "gpu_launches": launches, "impl": "native", "step_split_s": step_split,
         }
         if e2e is not None:
             out["e2e"] = e2e

@@ -31,6 +31,10 @@ struct GemmParams {
   const __nv_bfloat16* bias;  // optional, length N (EPI_BF16 only)
   int* status;
   int num_m_blocks, num_n_blocks, num_k_blocks;
+  // split-K: tile t covers k-blocks [ks*kb_per_split, (ks+1)*kb_per_split) and writes slab ks of C
+  // (C + ks * slab_stride elements); a separate kernel sums the slabs.  k_splits == 1 is the normal GEMM.
+  int k_splits, kb_per_split;
+  long long slab_stride;
 };
 
 enum { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2 };
@@ -72,7 +76,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  const int tiles_mn = p.num_m_blocks * p.num_n_blocks;
+  const int num_tiles = tiles_mn * p.k_splits;
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512 (power of two)
 
   if (threadIdx.x == 0) {
@@ -108,9 +113,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int mb, nb;
-        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, mb, nb);
+        const int ks = tile / tiles_mn;
+        tile_coords(tile - ks * tiles_mn, p.num_m_blocks, p.num_n_blocks, mb, nb);
         const int m0 = mb * kBM, n0 = nb * BN;
-        for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+        const int kb0 = ks * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kStatusTimeoutProducer)) {
             ok = false;
             break;
@@ -160,7 +167,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + acc * BN;
-      for (int kb = 0; kb < p.num_k_blocks; ++kb) {
+      const int ks = tile / tiles_mn;
+      const int kb0 = ks * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&full_bar[stage], phase, p.status, kStatusTimeoutMma)) {
           ok = false;
           break;
@@ -175,7 +184,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                                      : umma_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? umma_smem_desc(sb_ + kk * 2048, 8192, 1024)
                                      : umma_smem_desc(sb_ + kk * 32, 16, 1024);
-            umma_bf16_ss(tmem_d, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_bf16_ss(tmem_d, da, db, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
         }
@@ -200,7 +209,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int mb, nb;
-      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, mb, nb);
+      const int ks = tile / tiles_mn;
+      tile_coords(tile - ks * tiles_mn, p.num_m_blocks, p.num_n_blocks, mb, nb);
       const int row = mb * kBM + row_in_tile;
       const int n0 = nb * BN;
       if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusTimeoutEpilogue)) break;
@@ -240,7 +250,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
               }
             }
           } else {
-            float* crow = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col0;
+            float* crow = reinterpret_cast<float*>(p.C) + ks * p.slab_stride + (long long)row * p.ldc + col0;
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
               if (col0 + g * 4 + 4 <= p.N) {
@@ -334,7 +344,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  const int tiles = p.num_m_blocks * p.num_n_blocks * p.k_splits;
   int grid = tiles < num_sms() ? tiles : num_sms();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   kernel<<<grid, 192, L::kTotalBytes, stream>>>(ma, mb, p);
@@ -360,11 +370,62 @@ static int dispatch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
 
 }  // namespace sb
 
+namespace sb {
+// out[m, n] = bf16(sum_s slabs[s, m, n] + bias[n]); one thread per 8 columns
+__global__ void splitk_reduce_kernel(const float* __restrict__ slabs, long long slab_stride, int splits,
+                                     const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out,
+                                     long long ldo, int M, int N) {
+  const int nvec = N / 8;
+  const long long total = (long long)M * nvec;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int m = (int)(idx / nvec), v = (int)(idx % nvec);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < splits; ++s) {
+      const float4* src = reinterpret_cast<const float4*>(slabs + s * slab_stride + (long long)m * N + v * 8);
+      const float4 a = src[0], b = src[1];
+      acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+      acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+    }
+    if (bias) {
+      const uint4 bv = *reinterpret_cast<const uint4*>(bias + v * 8);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(b2[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + (long long)m * ldo + v * 8) = o;
+  }
+}
+}  // namespace sb
+
 using namespace sb;
+
+extern "C" int sb_splitk_reduce(const float* slabs, long long slab_stride, int splits, const void* bias, void* out,
+                                long long ldo, int M, int N, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  if (N % 8 || ldo % 8) return -3;
+  const long long total = (long long)M * (N / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  splitk_reduce_kernel<<<(int)blocks, 256, 0, stream>>>(slabs, slab_stride, splits, (const __nv_bfloat16*)bias,
+                                                       (__nv_bfloat16*)out, ldo, M, N);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                             long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi,
-                            int tile_n, int max_ctas, int* status, cudaStream_t stream) {
+                            int tile_n, int max_ctas, int k_splits, long long slab_stride, int* status,
+                            cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row pitches; the epilogue stores whole 16-byte groups of a row
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return -3;
@@ -405,6 +466,12 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   p.num_m_blocks = (M + kBM - 1) / kBM;
   p.num_n_blocks = (N + BN - 1) / BN;
   p.num_k_blocks = (K + kBK - 1) / kBK;
+  if (k_splits < 1) k_splits = 1;
+  if (k_splits > 1 && epi != EPI_F32) return -2;  // split-K writes fp32 slabs
+  if (k_splits > p.num_k_blocks) k_splits = p.num_k_blocks;
+  p.kb_per_split = (p.num_k_blocks + k_splits - 1) / k_splits;
+  p.k_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+  p.slab_stride = slab_stride;
   if (BN == 256) return dispatch_gemm<256, 4>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
   return dispatch_gemm<128, 6>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
 }

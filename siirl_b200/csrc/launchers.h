@@ -20,7 +20,10 @@ extern "C" {
 // tile_n: 128, 256 or 0 (auto).  max_ctas: 0 = one CTA per SM.
 int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
-                 int* status, cudaStream_t stream);
+                 int k_splits, long long slab_stride, int* status, cudaStream_t stream);
+// out = bf16(sum over `splits` fp32 slabs [M, N] + bias)
+int sb_splitk_reduce(const float* slabs, long long slab_stride, int splits, const void* bias, void* out,
+                     long long ldo, int M, int N, cudaStream_t stream);
 
 // ---- elementwise.cu ----
 int sb_rmsnorm_fwd(const void* x, const void* residual, const void* w, void* y, void* h_out, float* rstd,
@@ -97,4 +100,22 @@ int sb_fmha_decode(const void* q, int row_stride, const void* cache, long long n
 extern "C" {
 // ---- host/kk_partition.cpp ----
 int sb_kk_partition(const long long* workloads, int n, int k, int equal_size, int* out_part);
+}
+
+extern "C" {
+// ---- comm.cu ----
+int sb_symm_alloc(void** out, long long bytes);
+int sb_symm_free(void* p);
+int sb_ipc_get_handle(void* p, unsigned char* out64);
+int sb_ipc_open_handle(const unsigned char* in64, void** out);
+int sb_ipc_close_handle(void* p);
+int sb_ipc_handle_bytes();
+int sb_rs_reduce(void* const* grad_ptrs, int world, int rank, long long lo, long long n, float* out_shard,
+                 float* sumsq, cudaStream_t stream);
+int sb_adamw_allgather(float* master, float* m, float* v, const float* grad, void* const* param_ptrs, int world,
+                       const float* sumsq, float* grad_norm_out, long long lo, long long n, float lr, float beta1,
+                       float beta2, float eps, float weight_decay, int step, float max_norm, float grad_scale,
+                       cudaStream_t stream);
+int sb_segment_pull(void* const* bases, int world, const void* segs, int n_segs, void* out, cudaStream_t stream);
+int sb_flag_barrier(void* const* flag_ptrs, int world, int rank, int epoch, int* status, cudaStream_t stream);
 }

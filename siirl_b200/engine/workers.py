@@ -383,7 +383,14 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         if self.device.type == "cuda":
             out["perf/max_memory_allocated_gb"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30
             out["perf/max_memory_reserved_gb"] = torch.cuda.max_memory_reserved(self.device) / 2 ** 30
-        out["timing_s/update_actor_inner"] = time.time() - t0
+        if self.device.type == "cuda":
+            torch.cuda.synchronize()
+        dt = time.time() - t0
+        out["timing_s/update_actor_inner"] = dt
+        from ..utils.model_utils.flops_counter import FlopsCounter
+        seqlens = data["attention_mask"].sum(-1).tolist()
+        # forward + backward (3x) plus the recompute forward of activation checkpointing is not counted as useful
+        out["perf/mfu/actor"] = FlopsCounter(self.model_config).mfu(seqlens, dt / max(a.ppo_epochs, 1))
         return out
 
 

@@ -24,7 +24,7 @@ EPI_BF16, EPI_F32_ACC, EPI_F32 = 0, 1, 2
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, bias: Optional[torch.Tensor] = None,
          a_mn: bool = False, b_mn: bool = False, epi: int = EPI_BF16, tile_n: int = 0,
-         max_ctas: int = 0) -> torch.Tensor:
+         max_ctas: int = 0, k_splits: int = 1, slab_stride: int = 0) -> torch.Tensor:
     """``out[M,N] (+)= A @ B^T`` on the tensor cores.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` when ``b_mn``);
@@ -43,7 +43,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     assert K == Kb, (a.shape, b.shape, a_mn, b_mn)
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16 if epi == EPI_BF16 else torch.float32, device=a.device)
-    assert out.shape == (M, N) and out.stride(-1) == 1
+    assert (out.shape == (M, N) or k_splits > 1) and out.stride(-1) == 1
     if not _lib.use_native(a):
         af = a.float().t() if a_mn else a.float()
         bf = b.float() if b_mn else b.float().t()
@@ -59,7 +59,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     rc = L.sb_gemm_bf16(_lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), M, N, K,
                         ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)),
                         ctypes.c_longlong(out.stride(0)), int(a_mn), int(b_mn), int(epi), int(tile_n),
-                        int(max_ctas), _lib.ptr(_lib.status_word(a.device)), _lib.stream())
+                        int(max_ctas), int(k_splits), ctypes.c_longlong(slab_stride),
+                        _lib.ptr(_lib.status_word(a.device)), _lib.stream())
     _lib.check(rc, "sb_gemm_bf16")
     return out
 
@@ -102,11 +103,49 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw, db
 
 
+_NUM_SMS = 148
+
+
+def _skinny_splits(M: int, N: int, K: int) -> int:
+    """Split-K factor for a GEMM with few rows (decode): enough (n-tile, k-slice) pairs to give every SM a slice
+    of the weight matrix to stream.  1 means the plain kernel already fills the machine."""
+    n_tiles = (N + 127) // 128 * ((M + 127) // 128)
+    nkb = (K + 63) // 64
+    if n_tiles >= _NUM_SMS or nkb < 8:
+        return 1
+    return max(1, min(nkb // 4, round(_NUM_SMS / n_tiles)))
+
+
+def linear_skinny(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """Inference-only ``x @ W^T + b`` for a handful of rows (one token per running sequence): the contraction is
+    split over CTAs so that all SMs stream the weights, partial sums land in fp32 slabs and one small kernel adds
+    them (and the bias) into the bf16 output."""
+    M, K = x2.shape
+    N = weight.shape[0]
+    splits = _skinny_splits(M, N, K)
+    if splits <= 1:
+        return gemm(x2, weight, bias=bias, tile_n=128 if N <= 128 * _NUM_SMS else 0)
+    nkb = (K + 63) // 64
+    per = (nkb + splits - 1) // splits
+    eff = (nkb + per - 1) // per
+    slabs = torch.empty(eff, M, N, dtype=torch.float32, device=x2.device)
+    gemm(x2, weight, out=slabs[0], epi=EPI_F32, tile_n=128, k_splits=eff, slab_stride=M * N)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
+    L = _lib.get_lib()
+    _lib.check(L.sb_splitk_reduce(_lib.ptr(slabs), ctypes.c_longlong(M * N), eff, _lib.ptr(bias), _lib.ptr(out),
+                                  ctypes.c_longlong(N), M, N, _lib.stream()), "sb_splitk_reduce")
+    return out
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ weight^T + bias`` (nn.Linear convention, weight ``[out, in]``)."""
     if not x.is_cuda:
         return F.linear(x, weight, bias)
     _lib.use_native(x)
+    rows = x.numel() // x.shape[-1]
+    if rows <= 128 and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)):
+        y = linear_skinny(x.reshape(rows, x.shape[-1]).contiguous(), weight, bias)
+        return y.reshape(*x.shape[:-1], weight.shape[0])
     return _LinearFn.apply(x, weight, bias)
 
 

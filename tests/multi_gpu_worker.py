@@ -1,0 +1,73 @@
+"""Body of the multi-GPU checks; launched by tests/test_gpu_multi.py with one process per GPU (torchrun env)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from siirl_b200.models.config import get_config  # noqa: E402
+from siirl_b200.models.decoder import build_model  # noqa: E402
+from siirl_b200.ops import lib  # noqa: E402
+from siirl_b200.ops.attention import SeqInfo  # noqa: E402
+from siirl_b200.parallel.flat_params import FlatParamStore  # noqa: E402
+from siirl_b200.parallel.symm import SymmComm  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    comm = SymmComm.create(dist.group.WORLD)
+    comm.barrier()
+    comm.barrier()
+
+    # 1. fused reduce-scatter + AdamW + all-gather equals the NCCL path
+    cfg = get_config("tiny-gpu")
+    stores = []
+    for use_comm in (True, False):
+        model = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=3)
+        store = FlatParamStore(model, group=dist.group.WORLD, comm=comm if use_comm else None)
+        stores.append((model, store))
+    info = SeqInfo([64 + 16 * rank, 100], device=dev)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    ids = torch.randint(3, cfg.vocab_size, (info.total,), device=dev, generator=g)
+    norms = []
+    for step in range(2):
+        for model, store in stores:
+            store.zero_grad()
+            lp, _ = model.logprobs(ids, info.positions, info, torch.roll(ids, -1), with_entropy=False)
+            (-lp.mean()).backward()
+            norms.append(store.step(lr=1e-3, max_grad_norm=1.0))
+    torch.cuda.synchronize()
+    lib.check_status()
+    a, b = stores[0][1].flat_param.float(), stores[1][1].flat_param.float()
+    err = (a - b).abs().max().item()
+    assert err < 1e-2, f"fused vs NCCL parameters differ by {err}"
+    assert abs(norms[-2].item() - norms[-1].item()) < 1e-2 * max(1.0, norms[-1].item())
+    # replicas agree across ranks
+    chk = stores[0][1].flat_param.float().sum().reshape(1).clone()
+    parts = [torch.zeros_like(chk) for _ in range(world)]
+    dist.all_gather(parts, chk)
+    assert all(torch.equal(parts[0], p) for p in parts), "replicas diverged"
+
+    # 2. row all-to-all-v through peer memory
+    row = 32
+    counts = [[(s + d) % 3 + 1 for d in range(world)] for s in range(world)]
+    send = torch.cat([torch.full((counts[rank][d], row), float(rank * 100 + d), device=dev) for d in range(world)])
+    staging = comm.alloc(64 * row, torch.float32)
+    got = comm.alltoallv_rows(send, counts[rank], staging, counts)
+    want = torch.cat([torch.full((counts[s][rank], row), float(s * 100 + rank), device=dev) for s in range(world)])
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    lib.check_status()
+    dist.barrier()
+    if rank == 0:
+        print("MULTI_GPU_OK", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,157 @@
+"""CPU checks of the model path: packing, decoder, rollout engine, flat parameter store, checkpoints, rewards."""
+import os
+
+import pytest
+import torch
+
+from siirl_b200.data_coordinator import Batch
+from siirl_b200.engine.packing import get_response_mask, pack_batch
+from siirl_b200.engine.reward_manager import DAPORewardManager, NaiveRewardManager
+from siirl_b200.engine.rollout.native_engine import RolloutEngine, SamplingParams
+from siirl_b200.models.config import DecoderConfig, get_config
+from siirl_b200.models.decoder import build_model
+from siirl_b200.models.hf_io import load_hf_weights, save_hf_model
+from siirl_b200.ops.attention import SeqInfo
+from siirl_b200.parallel.flat_params import FlatParamStore, lr_at_step
+from siirl_b200.params import parse_config
+from siirl_b200.data_coordinator.dataloader import SyntheticTokenizer
+from siirl_b200.utils.checkpoint.checkpoint_manager import ShardedCheckpointManager
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    return build_model(get_config("tiny"), dtype=torch.float32, seed=0)
+
+
+def test_pack_batch_indices():
+    P, R = 4, 3
+    ids = torch.tensor([[0, 0, 11, 12, 21, 22, 0], [0, 31, 32, 33, 41, 0, 0]])
+    am = torch.tensor([[0, 0, 1, 1, 1, 1, 0], [0, 1, 1, 1, 1, 0, 0]])
+    pk = pack_batch(ids, am, R)
+    assert pk.input_ids.tolist() == [11, 12, 21, 22, 31, 32, 33, 41]
+    assert pk.positions.tolist() == [0, 1, 2, 3, 0, 1, 2, 3]
+    assert pk.info.seqlens == [4, 4]
+    # position that predicts response token k: last prompt token + k
+    assert pk.sel.tolist() == [1, 2, 6] and pk.labels.tolist() == [21, 22, 41]
+    out = pk.scatter(torch.tensor([1.0, 2.0, 3.0]))
+    assert out.tolist() == [[1.0, 2.0, 0.0], [3.0, 0.0, 0.0]]
+
+
+def test_response_mask_stops_after_first_eos():
+    r = torch.tensor([[5, 2, 7, 2], [5, 6, 7, 8]])
+    assert get_response_mask(r, 2).tolist() == [[1, 1, 0, 0], [1, 1, 1, 1]]
+
+
+def test_packed_forward_equals_per_sequence_forward(tiny):
+    ids = torch.randint(3, 1000, (17,))
+    info = SeqInfo([6, 11])
+    both = tiny.logits(ids, info.positions, info)
+    a = tiny.logits(ids[:6], SeqInfo([6]).positions, SeqInfo([6]))
+    b = tiny.logits(ids[6:], SeqInfo([11]).positions, SeqInfo([11]))
+    torch.testing.assert_close(both, torch.cat([a, b]), rtol=1e-4, atol=1e-4)
+
+
+def test_engine_matches_naive_greedy_with_prefix_sharing(tiny):
+    eng = RolloutEngine(tiny, max_num_seqs=8, max_model_len=256, sync_interval=4)
+    prompts = [[5, 6, 7, 8, 9], list(range(20, 20 + 70))]
+    outs = eng.generate(prompts, SamplingParams(n=2, temperature=0.0, max_new_tokens=6))
+    for o in outs:
+        seq = list(prompts[o.prompt_index])
+        for _ in range(6):
+            info = SeqInfo([len(seq)])
+            seq.append(int(tiny.logits(torch.tensor(seq), info.positions, info)[-1].argmax()))
+        assert o.token_ids == seq[len(prompts[o.prompt_index]):]
+    assert eng.alloc.num_free == eng.alloc.num_blocks
+    eng.sleep()
+    assert eng.cache is None
+    eng.wake_up()
+    assert len(eng.generate([[3, 4]], SamplingParams(max_new_tokens=2))) == 1
+
+
+def test_engine_eos_and_continuous_batching(tiny):
+    eng = RolloutEngine(tiny, max_num_seqs=8, max_model_len=128, sync_interval=2)
+    prompts = [[10 + i, 11, 12] for i in range(10)]          # 10 requests x n=2 > 8 slots -> several admission rounds
+    outs = eng.generate(prompts, SamplingParams(n=2, temperature=1.0, max_new_tokens=5, eos_token_id=7, seed=3))
+    assert len(outs) == 20
+    for o in outs:
+        if o.finish_reason == "stop":
+            assert o.token_ids[-1] == 7
+        else:
+            assert len(o.token_ids) == 5
+    with pytest.raises(ValueError):
+        eng.generate([[1] * 200], SamplingParams(max_new_tokens=5))
+
+
+def test_flat_store_adamw_matches_torch(tiny):
+    m1 = build_model(get_config("tiny"), dtype=torch.float32, seed=1)
+    m2 = build_model(get_config("tiny"), dtype=torch.float32, seed=1)
+    store = FlatParamStore(m1)
+    opt = torch.optim.AdamW(m2.parameters(), lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    ids = torch.randint(3, 1000, (12,))
+    info = SeqInfo([12])
+    for _ in range(3):
+        for m in (m1, m2):
+            lp, _ = m.logprobs(ids, info.positions, info, torch.roll(ids, -1))
+            (-lp.mean()).backward()
+        norm = store.step(lr=1e-3, max_grad_norm=1.0)
+        store.zero_grad()
+        ref_norm = torch.nn.utils.clip_grad_norm_(m2.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad()
+        assert norm.item() == pytest.approx(ref_norm.item(), rel=1e-4)
+    for (n1, p1), (_, p2) in zip(m1.named_parameters(), m2.named_parameters()):
+        torch.testing.assert_close(p1, p2, rtol=1e-4, atol=1e-6, msg=n1)
+
+
+def test_nonfinite_gradient_skips_the_step():
+    m = build_model(get_config("tiny"), dtype=torch.float32, seed=2)
+    store = FlatParamStore(m)
+    before = store.flat_param.clone()
+    store.flat_grad.fill_(float("nan"))
+    store.step(lr=1.0)
+    assert torch.equal(store.flat_param, before)
+
+
+def test_lr_schedules():
+    cfg = parse_config(["actor_rollout_ref.actor.optim.lr=1.0", "actor_rollout_ref.actor.optim.lr_warmup_steps=2",
+                        "actor_rollout_ref.actor.optim.warmup_style=cosine"]).actor_rollout_ref.actor.optim
+    assert lr_at_step(cfg, 0, 10) == 0.5 and lr_at_step(cfg, 1, 10) == 1.0
+    assert lr_at_step(cfg, 10, 10) == pytest.approx(0.0, abs=1e-6)
+    cfg.warmup_style = "constant"
+    assert lr_at_step(cfg, 7, 10) == 1.0
+
+
+def test_hf_roundtrip_and_sharded_checkpoint(tmp_path, tiny):
+    save_hf_model(tiny, str(tmp_path / "hf"))
+    assert DecoderConfig.from_pretrained(str(tmp_path / "hf")).hidden_size == 128
+    m2 = build_model(get_config("tiny"), dtype=torch.float32, seed=99)
+    load_hf_weights(m2, str(tmp_path / "hf"))
+    for (n, a), (_, b) in zip(tiny.named_parameters(), m2.named_parameters()):
+        assert torch.equal(a, b), n
+    m3 = build_model(get_config("tiny"), dtype=torch.float32, seed=5)
+    s3 = FlatParamStore(m3)
+    s3.flat_grad.normal_()
+    s3.step(lr=1e-3)
+    mgr = ShardedCheckpointManager(m3, s3, m3.cfg, contents=["model", "optimizer", "extra", "hf_model"])
+    mgr.save(str(tmp_path / "ck"), global_step=4, extra={"opt_step": 1})
+    assert os.path.exists(tmp_path / "ck" / "huggingface" / "model.safetensors")
+    m4 = build_model(get_config("tiny"), dtype=torch.float32, seed=6)
+    s4 = FlatParamStore(m4)
+    extra = ShardedCheckpointManager(m4, s4, m4.cfg).load(str(tmp_path / "ck"))
+    assert extra["global_step"] == 4 and extra["opt_step"] == 1
+    assert torch.equal(s3.flat_param, s4.flat_param) and torch.equal(s3.exp_avg_sq, s4.exp_avg_sq)
+    assert s4.step_count == 1
+
+
+def test_reward_managers_place_score_at_last_valid_token():
+    tok = SyntheticTokenizer()
+    resp = torch.tensor([tok.encode("12") + [2, 0], tok.encode("7") + [2, 0, 0]])
+    prompts = torch.tensor([tok.encode("5+7="), tok.encode("3+4=")])
+    am = torch.cat([torch.ones(2, 4, dtype=torch.long), torch.tensor([[1, 1, 1, 0], [1, 1, 0, 0]])], -1)
+    b = Batch({"prompts": prompts, "responses": resp, "attention_mask": am},
+              {"data_source": ["synthetic/arith"] * 2, "reward_model": [{"ground_truth": "12"}, {"ground_truth": "8"}]})
+    r = NaiveRewardManager(tok)(b)
+    assert r.tolist() == [[0, 0, 1.0, 0], [0, 0, 0, 0]]
+    cfg = parse_config(["reward_model.overlong_buffer.enable=True", "reward_model.overlong_buffer.len=2"])
+    d = DAPORewardManager(tok, max_resp_len=4, overlong_buffer_cfg=cfg.reward_model.overlong_buffer)(b)
+    assert d[0, 2].item() == pytest.approx(1.0 - 0.5)        # length 3, expected 2 -> exceed 1 of buffer 2

@@ -152,3 +152,18 @@ def test_embedding_fwd_bwd():
     out.backward(g)
     want = torch.zeros(V, H, device=DEV).index_add_(0, ids.reshape(-1), g.reshape(-1, H).float())
     assert _rel_err(table.grad, want) < 1e-2
+
+
+@pytest.mark.parametrize("shape", [(64, 3584, 3584), (7, 3584, 18944), (128, 4608, 3584), (33, 256, 1024)])
+def test_skinny_split_k_linear(shape):
+    M, N, K = shape
+    torch.manual_seed(9)
+    x = (0.5 * torch.randn(M, K, device=DEV)).to(torch.bfloat16)
+    w = (0.05 * torch.randn(N, K, device=DEV)).to(torch.bfloat16)
+    b = torch.randn(N, device=DEV).to(torch.bfloat16)
+    with torch.no_grad():
+        y = ops.linear(x, w, b)
+    lib.check_status()
+    want = x.float() @ w.float().t() + b.float()
+    assert _rel_err(y, want) < 1e-2
+    assert dense._skinny_splits(64, 3584, 18944) > 1
