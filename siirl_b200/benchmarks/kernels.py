@@ -1,0 +1,168 @@
+"""Per-kernel benchmark: one JSON line per case with the achieved rate and the fraction of the measured roofline.
+
+    python -m siirl_b200.benchmarks.kernels --case all            # everything, production shapes
+    python -m siirl_b200.benchmarks.kernels --case gemm --small   # small shapes for a profiler capture
+
+Timing: CUDA events on the launching stream, 3 warm-up iterations, L2 flushed (a 256 MB buffer is overwritten)
+between timed iterations, median of the timed iterations.  Denominators come from ``MEASURED_PEAKS.json`` at the
+repository root when present (copy bandwidth and cuBLAS bf16 throughput measured on this pool), else from the
+fallback figures 6.65 TB/s and 1.59 PFLOP/s."""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from .. import ops
+from ..ops import dense, lib
+from ..ops.attention import SeqInfo, attention_packed
+from ..ops.lm_head import lm_head_logprob_entropy
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    path = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
+
+
+_flush = None
+
+
+def timeit(fn, iters: int = 10, warm: int = 3, flush: bool = True) -> float:
+    global _flush
+    if flush and _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def report(name, ms, flops=None, bytes_=None, **extra):
+    pk = peaks()
+    out = {"kernel": name, "ms": round(ms, 4), **extra}
+    if flops:
+        out["tflops"] = round(flops / ms / 1e9, 1)
+        out["frac_of_%s_gemm_peak" % pk["source"]] = round(flops / ms / 1e9 / pk["tflops"], 3)
+    if bytes_:
+        out["gbs"] = round(bytes_ / ms / 1e6, 1)
+        out["frac_of_%s_copy_bw" % pk["source"]] = round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3)
+    print(json.dumps(out), flush=True)
+
+
+def bench_gemm(small: bool):
+    shapes = [(2048, 4608, 3584)] if small else [(8192, 4608, 3584), (8192, 3584, 3584), (8192, 37888, 3584),
+                                                 (8192, 3584, 18944), (2048, 152064, 3584)]
+    for M, N, K in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * M * N * K
+        report("gemm_bf16_tcgen05 fwd (x W^T)", timeit(lambda: ops.gemm(a, b, out=out)), fl, M=M, N=N, K=K)
+        if small:
+            continue
+        report("cublas bf16 (torch.matmul)", timeit(lambda: torch.matmul(a, b.t(), out=out)), fl, M=M, N=N, K=K)
+        bt = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+        report("gemm_bf16_tcgen05 dgrad layout", timeit(lambda: ops.gemm(a, bt, out=out, b_mn=True)), fl, M=M, N=N, K=K)
+        at = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
+        acc = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+        report("gemm_bf16_tcgen05 wgrad layout (fp32 +=)",
+               timeit(lambda: ops.gemm(at, bt, out=acc, a_mn=True, b_mn=True, epi=dense.EPI_F32_ACC)), fl, M=M, N=N, K=K)
+    lib.check_status()
+
+
+def bench_attention(small: bool):
+    cases = [(28, 4, 128, [1024] * 2)] if small else [(28, 4, 128, [2048] * 8), (28, 4, 128, [640 + 64 * i for i in range(16)]),
+                                                       (28, 4, 128, [16384])]
+    for hq, hkv, d, lens in cases:
+        T = sum(lens)
+        qkv = (0.5 * torch.randn(T, (hq + 2 * hkv) * d, device="cuda")).to(torch.bfloat16).requires_grad_()
+        info = SeqInfo(lens, device="cuda")
+        fl = 4.0 * hq * d * sum(0.5 * s * s for s in lens)
+        with torch.no_grad():
+            report("fmha_fwd (causal, GQA)", timeit(lambda: attention_packed(qkv, info, hq, hkv, d)), fl, T=T,
+                   seqs=len(lens))
+        out = attention_packed(qkv, info, hq, hkv, d)
+        g = torch.randn_like(out)
+
+        def bwd():
+            qkv.grad = None
+            out.backward(g, retain_graph=True)
+
+        report("fmha_bwd (causal, GQA)", timeit(bwd), 2.5 * fl, T=T, seqs=len(lens))
+    lib.check_status()
+
+
+def bench_lm_head(small: bool):
+    T, V, H = (1024, 152064, 3584) if small else (8192, 152064, 3584)
+    h = (0.5 * torch.randn(T, H, device="cuda")).to(torch.bfloat16)
+    w = (0.02 * torch.randn(V, H, device="cuda")).to(torch.bfloat16)
+    y = torch.randint(0, V, (T,), device="cuda")
+    with torch.no_grad():
+        report("lm_head logprob+entropy fwd", timeit(lambda: lm_head_logprob_entropy(h, w, y, 1.0), iters=5),
+               2.0 * T * V * H, T=T, V=V)
+    lib.check_status()
+
+
+def bench_memory_bound(small: bool):
+    T, H, I = (4096, 3584, 18944) if small else (16384, 3584, 18944)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        report("rmsnorm_fwd (+residual)", timeit(lambda: ops.rmsnorm(x, w, 1e-6, residual=r)), bytes_=T * H * 2 * 4, T=T)
+        gu = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+        report("swiglu_fwd", timeit(lambda: ops.swiglu(gu)), bytes_=T * I * 2 * 3, T=T)
+    n = 1 << 28
+    g = torch.randn(n, device="cuda")
+    from ..parallel.flat_params import FlatParamStore
+
+    class _M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.p = torch.nn.Parameter(torch.zeros(n, device="cuda", dtype=torch.bfloat16))
+
+    store = FlatParamStore(_M())
+    store.flat_grad.copy_(g)
+    report("sumsq + adamw (fp32 master/m/v, bf16 copy)", timeit(lambda: store.step(1e-4), iters=5),
+           bytes_=n * (4 + 4 * 4 + 3 * 4 + 2), n=n)
+    lib.check_status()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="all", choices=["all", "gemm", "attention", "lm_head", "memory"])
+    ap.add_argument("--small", action="store_true")
+    a = ap.parse_args()
+    print(json.dumps({"peaks": peaks(), "device": torch.cuda.get_device_name()}))
+    if a.case in ("all", "gemm"):
+        bench_gemm(a.small)
+    if a.case in ("all", "attention"):
+        bench_attention(a.small)
+    if a.case in ("all", "lm_head"):
+        bench_lm_head(a.small)
+    if a.case in ("all", "memory"):
+        bench_memory_bound(a.small)
+
+
+if __name__ == "__main__":
+    main()
+_ = math

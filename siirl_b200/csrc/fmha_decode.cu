@@ -57,6 +57,61 @@ __global__ void kv_copy_blocks_kernel(__nv_bfloat16* __restrict__ cache, const i
 }
 
 // ---------------------------------------------------------------------------------------
+// fused RoPE + cache append (rollout path): rotates the q and k heads of packed qkv rows in place and writes the
+// rotated k and the v heads of every row to its cache slot -- one launch instead of clone + rope + append.
+// One thread handles 8 rotation pairs (i, i + D/2) of one head, or 16 contiguous v elements.
+// ---------------------------------------------------------------------------------------
+__global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride, const int* __restrict__ rope_pos,
+                                      int pos_rows, int sec0, int sec1, const float* __restrict__ cos_tab,
+                                      const float* __restrict__ sin_tab, const int* __restrict__ seq_ids,
+                                      const int* __restrict__ cache_pos, const int* __restrict__ block_table,
+                                      int max_blocks, __nv_bfloat16* __restrict__ cache, int T, int Hq, int Hkv, int D) {
+  const int half = D / 2;
+  const int units_per_head = half / 8;                 // 8 pairs per thread
+  const int heads = Hq + 2 * Hkv;
+  const long long total = (long long)T * heads * units_per_head;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(idx / (heads * units_per_head));
+    int r = (int)(idx % (heads * units_per_head));
+    const int head = r / units_per_head, u = r % units_per_head;
+    const int i0 = u * 8;
+    __nv_bfloat16* base = qkv + (size_t)t * row_stride + (size_t)head * D;
+    uint4 lo = *reinterpret_cast<const uint4*>(base + i0);
+    uint4 hi = *reinterpret_cast<const uint4*>(base + half + i0);
+    const int seq = seq_ids[t], cp = cache_pos[t];
+    const bool to_cache = head >= Hq && seq >= 0 && cp >= 0;
+    if (head < Hq + Hkv) {
+      __nv_bfloat16* a = reinterpret_cast<__nv_bfloat16*>(&lo);
+      __nv_bfloat16* b = reinterpret_cast<__nv_bfloat16*>(&hi);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int i = i0 + k;
+        int prow = 0;
+        if (pos_rows == 3) prow = (i < sec0) ? 0 : (i < sec1 ? 1 : 2);
+        const int p = rope_pos[(size_t)prow * T + t];
+        const float c = cos_tab[(size_t)p * half + i], s = sin_tab[(size_t)p * half + i];
+        const float x = __bfloat162float(a[k]), y = __bfloat162float(b[k]);
+        a[k] = __float2bfloat16(x * c - y * s);
+        b[k] = __float2bfloat16(y * c + x * s);
+      }
+      *reinterpret_cast<uint4*>(base + i0) = lo;
+      *reinterpret_cast<uint4*>(base + half + i0) = hi;
+    }
+    if (to_cache) {
+      const int kv = head >= Hq + Hkv ? 1 : 0;
+      const int h = head - Hq - kv * Hkv;
+      const int blk = block_table[(size_t)seq * max_blocks + cp / kBlk];
+      if (blk >= 0) {
+        __nv_bfloat16* dst = cache + ((((size_t)blk * 2 + kv) * Hkv + h) * kBlk + (cp % kBlk)) * D;
+        *reinterpret_cast<uint4*>(dst + i0) = lo;
+        *reinterpret_cast<uint4*>(dst + half + i0) = hi;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // decode attention
 // ---------------------------------------------------------------------------------------
 struct DecodeParams {
@@ -334,6 +389,22 @@ extern "C" int sb_kv_append(const void* qkv, int row_stride, const int* seq_ids,
   if (blocks > cap) blocks = cap;
   kv_append_kernel<<<(int)blocks, 256, 0, stream>>>((const __nv_bfloat16*)qkv, row_stride, seq_ids, positions,
                                                     block_table, max_blocks, (__nv_bfloat16*)cache, T, Hq, Hkv, D);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_rope_kv_append(void* qkv, int row_stride, const int* rope_pos, int pos_rows, int sec0, int sec1,
+                                 const float* cos_tab, const float* sin_tab, const int* seq_ids, const int* cache_pos,
+                                 const int* block_table, int max_blocks, void* cache, int T, int Hq, int Hkv, int D,
+                                 cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (D % 16) return -3;
+  const long long total = (long long)T * (Hq + 2 * Hkv) * (D / 16);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  rope_kv_append_kernel<<<(int)blocks, 256, 0, stream>>>((__nv_bfloat16*)qkv, row_stride, rope_pos, pos_rows, sec0,
+                                                         sec1, cos_tab, sin_tab, seq_ids, cache_pos, block_table,
+                                                         max_blocks, (__nv_bfloat16*)cache, T, Hq, Hkv, D);
   return (int)cudaGetLastError();
 }
 

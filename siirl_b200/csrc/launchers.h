@@ -77,7 +77,7 @@ int sb_lmhead_dlogits(const float* logits, long long ld, const long long* labels
 // ---- sampling.cu ----
 int sb_sample(const float* sample_logits, const float* stat_logits, long long ld, float temperature,
               unsigned long long seed, unsigned long long step, const long long* step_dev, long long* tokens,
-              float* logp, int rows, int V, cudaStream_t stream);
+              float* logp, int rows, int V, void* workspace, int splits, cudaStream_t stream);
 // ---- optimizer.cu ----
 int sb_sumsq_accumulate(const float* g, long long n, float* out, cudaStream_t stream);
 int sb_adamw_step(float* master, float* m, float* v, const float* grad, void* param_bf16, const float* sumsq,
@@ -90,6 +90,10 @@ extern "C" {
 // ---- fmha_decode.cu ----
 int sb_kv_append(const void* qkv, int row_stride, const int* seq_ids, const int* positions, const int* block_table,
                  int max_blocks, void* cache, int T, int Hq, int Hkv, int D, cudaStream_t stream);
+int sb_rope_kv_append(void* qkv, int row_stride, const int* rope_pos, int pos_rows, int sec0, int sec1,
+                      const float* cos_tab, const float* sin_tab, const int* seq_ids, const int* cache_pos,
+                      const int* block_table, int max_blocks, void* cache, int T, int Hq, int Hkv, int D,
+                      cudaStream_t stream);
 int sb_kv_copy_blocks(void* cache, const int* src, const int* dst, int n_pairs, long long block_elems,
                       cudaStream_t stream);
 int sb_fmha_decode(const void* q, int row_stride, const void* cache, long long num_blocks, const int* seq_lens,

@@ -62,22 +62,24 @@ constexpr int kSampleThreads = 512;
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ sample_logits, const float* __restrict__ stat_logits, long long ld,
               float inv_temp, int greedy, unsigned long long seed, unsigned long long step_host,
-              const long long* __restrict__ step_dev, long long* __restrict__ tokens, float* __restrict__ logp, int V) {
+              const long long* __restrict__ step_dev, long long* __restrict__ tokens, float* __restrict__ logp, int V,
+              int chunk, ArgStat* __restrict__ partial) {
   __shared__ ArgStat red[32];
   const int row = blockIdx.x;
+  const int v_begin = blockIdx.y * chunk, v_end = min(V, v_begin + chunk);
   const unsigned long long step = step_host + (step_dev ? (unsigned long long)*step_dev : 0ull);
   const float* zs = sample_logits + (size_t)row * ld;
   const float* zt = stat_logits + (size_t)row * ld;
   ArgStat st = {-INFINITY, -1, -INFINITY, 0.f};
   const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
-  for (int i = threadIdx.x * 4; i < V; i += kSampleThreads * 4) {
+  for (int i = v_begin + threadIdx.x * 4; i < v_end; i += kSampleThreads * 4) {
     uint4 rnd = make_uint4(0, 0, 0, 0);
     if (!greedy) rnd = philox4x32_10(make_uint4((uint32_t)i, (uint32_t)row, (uint32_t)step, (uint32_t)(step >> 32)), key);
     const uint32_t rr[4] = {rnd.x, rnd.y, rnd.z, rnd.w};
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int j = i + u;
-      if (j >= V) break;
+      if (j >= v_end) break;
       const float x = zt[j] * inv_temp;
       if (x != -INFINITY) {
         if (x > st.m) {
@@ -121,10 +123,39 @@ sample_kernel(const float* __restrict__ sample_logits, const float* __restrict__
       w = merge(w, other);
     }
     if (lane == 0) {
-      const int tok = w.idx < 0 ? 0 : w.idx;
-      tokens[row] = tok;
-      if (logp) logp[row] = zt[tok] * inv_temp - (w.m + __logf(w.s));
+      if (partial) {
+        partial[(size_t)row * gridDim.y + blockIdx.y] = w;
+      } else {
+        const int tok = w.idx < 0 ? 0 : w.idx;
+        tokens[row] = tok;
+        if (logp) logp[row] = zt[tok] * inv_temp - (w.m + __logf(w.s));
+      }
     }
+  }
+}
+
+// merges the per-chunk partial results of one row (one warp per row)
+__global__ void sample_merge_kernel(const ArgStat* __restrict__ partial, int splits, const float* __restrict__ stat_logits,
+                                    long long ld, float inv_temp, long long* __restrict__ tokens,
+                                    float* __restrict__ logp, int rows) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  ArgStat w = {-INFINITY, -1, -INFINITY, 0.f};
+  for (int s = lane; s < splits; s += 32) w = merge(w, partial[(size_t)row * splits + s]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgStat other;
+    other.best = __shfl_xor_sync(0xffffffffu, w.best, o);
+    other.idx = __shfl_xor_sync(0xffffffffu, w.idx, o);
+    other.m = __shfl_xor_sync(0xffffffffu, w.m, o);
+    other.s = __shfl_xor_sync(0xffffffffu, w.s, o);
+    w = merge(w, other);
+  }
+  if (lane == 0) {
+    const int tok = w.idx < 0 ? 0 : w.idx;
+    tokens[row] = tok;
+    if (logp) logp[row] = stat_logits[(size_t)row * ld + tok] * inv_temp - (w.m + __logf(w.s));
   }
 }
 
@@ -134,11 +165,23 @@ using namespace sb;
 
 extern "C" int sb_sample(const float* sample_logits, const float* stat_logits, long long ld, float temperature,
                          unsigned long long seed, unsigned long long step, const long long* step_dev,
-                         long long* tokens, float* logp, int rows, int V, cudaStream_t stream) {
+                         long long* tokens, float* logp, int rows, int V, void* workspace, int splits,
+                         cudaStream_t stream) {
   if (rows == 0) return 0;
   const int greedy = temperature <= 0.f;
   const float inv_temp = greedy ? 1.f : 1.f / temperature;
-  sample_kernel<<<rows, kSampleThreads, 0, stream>>>(sample_logits, stat_logits ? stat_logits : sample_logits, ld,
-                                                     inv_temp, greedy, seed, step, step_dev, tokens, logp, V);
+  const float* zt = stat_logits ? stat_logits : sample_logits;
+  if (!workspace || splits <= 1) {
+    sample_kernel<<<rows, kSampleThreads, 0, stream>>>(sample_logits, zt, ld, inv_temp, greedy, seed, step, step_dev,
+                                                       tokens, logp, V, V, nullptr);
+    return (int)cudaGetLastError();
+  }
+  // vocabulary split over `splits` blocks per row (workspace: rows * splits * 16 bytes), then one merge warp per row
+  const int chunk = ((V + splits - 1) / splits + 3) / 4 * 4;
+  dim3 grid(rows, splits);
+  sample_kernel<<<grid, kSampleThreads, 0, stream>>>(sample_logits, zt, ld, inv_temp, greedy, seed, step, step_dev,
+                                                     tokens, logp, V, chunk, reinterpret_cast<ArgStat*>(workspace));
+  sample_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(reinterpret_cast<const ArgStat*>(workspace), splits, zt, ld,
+                                                          inv_temp, tokens, logp, rows);
   return (int)cudaGetLastError();
 }

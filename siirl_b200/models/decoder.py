@@ -69,6 +69,13 @@ class DecoderLayer(nn.Module):
     # ---- pieces shared by the training and the cached (rollout) paths --------------------------
     def qkv(self, x: torch.Tensor, positions: torch.Tensor, rope) -> torch.Tensor:
         cfg = self.cfg
+        qkv = self.qkv_pre_rope(x)
+        cos, sin = rope
+        return ops.rope(qkv, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, positions, cos, sin, cfg.mrope_section)
+
+    def qkv_pre_rope(self, x: torch.Tensor) -> torch.Tensor:
+        """QKV projection (+ per-head q/k RMSNorm for the Qwen3 family), before rotary embedding."""
+        cfg = self.cfg
         qkv = ops.linear(x, self.qkv_proj_weight, self.qkv_proj_bias)
         if cfg.qk_norm:
             T = qkv.shape[0]
@@ -78,8 +85,7 @@ class DecoderLayer(nn.Module):
             qn, _ = ops.rmsnorm(qk[:, : cfg.num_heads].reshape(-1, cfg.head_dim), self.q_norm, cfg.rms_norm_eps)
             kn, _ = ops.rmsnorm(qk[:, cfg.num_heads:].reshape(-1, cfg.head_dim), self.k_norm, cfg.rms_norm_eps)
             qkv = torch.cat([qn.reshape(T, -1), kn.reshape(T, -1), qkv[:, nrot * cfg.head_dim:]], dim=-1)
-        cos, sin = rope
-        return ops.rope(qkv, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, positions, cos, sin, cfg.mrope_section)
+        return qkv
 
     def mlp(self, x: torch.Tensor) -> torch.Tensor:
         if self.cfg.is_moe:
@@ -195,12 +201,13 @@ class DecoderLM(nn.Module):
         rope = self.rope_tables(input_ids.device, min(pmax, 32768))
         h = self.embed(input_ids, pixel_values, image_grid_thw)
         delta = None
-        pos32 = positions.to(torch.int32)
+        pos32 = positions.to(torch.int32).contiguous()
+        rp32 = rp.to(torch.int32).contiguous()
         for li, layer in enumerate(self.layers):
             x, h = ops.rmsnorm(delta if delta is not None else h, layer.input_layernorm, cfg.rms_norm_eps,
                                residual=h if delta is not None else None)
-            qkv = layer.qkv(x, rp, rope)
-            kvc.kv_append(qkv, seq_ids, pos32, block_table, cache[li], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim)
+            qkv = kvc.rope_kv_append(layer.qkv_pre_rope(x), rp32, rope[0], rope[1], cfg.mrope_section, seq_ids, pos32,
+                                     block_table, cache[li], cfg.num_heads, cfg.num_kv_heads, cfg.head_dim)
             if prefill_info is not None:
                 a = attention_packed(qkv, prefill_info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=True)
             else:

@@ -37,6 +37,30 @@ def kv_append(qkv: torch.Tensor, seq_ids: torch.Tensor, positions: torch.Tensor,
     cache_layer[blk, 1, :, off] = v
 
 
+def rope_kv_append(qkv: torch.Tensor, rope_positions: torch.Tensor, cos_tab: torch.Tensor, sin_tab: torch.Tensor,
+                   mrope_section, seq_ids: torch.Tensor, cache_positions: torch.Tensor, block_table: torch.Tensor,
+                   cache_layer: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Inference-only fusion of RoPE and cache append: rotates the q and k heads of ``qkv`` IN PLACE and writes the
+    rotated k and the v heads to the cache (one kernel on CUDA).  Returns ``qkv``."""
+    if qkv.is_cuda and head_dim % 16 == 0:
+        L = _lib.get_lib()
+        pos = rope_positions.to(torch.int32).contiguous()
+        rows = 1 if pos.dim() == 1 else pos.shape[0]
+        s0 = s1 = 0
+        if rows == 3:
+            s0, s1 = mrope_section[0], mrope_section[0] + mrope_section[1]
+        _lib.check(L.sb_rope_kv_append(_lib.ptr(qkv), qkv.stride(0), _lib.ptr(pos), rows, s0, s1, _lib.ptr(cos_tab),
+                                       _lib.ptr(sin_tab), _lib.ptr(seq_ids), _lib.ptr(cache_positions),
+                                       _lib.ptr(block_table), block_table.shape[1], _lib.ptr(cache_layer),
+                                       qkv.shape[0], n_heads, n_kv_heads, head_dim, _lib.stream()),
+                   "sb_rope_kv_append")
+        return qkv
+    from . import dense
+    qkv = dense.rope(qkv, n_heads + n_kv_heads, head_dim, rope_positions, cos_tab, sin_tab, mrope_section)
+    kv_append(qkv, seq_ids, cache_positions, block_table, cache_layer, n_heads, n_kv_heads, head_dim)
+    return qkv
+
+
 def kv_copy_blocks(cache_layer: torch.Tensor, src: torch.Tensor, dst: torch.Tensor) -> None:
     if src.numel() == 0:
         return

@@ -40,8 +40,11 @@ def sample(logits: torch.Tensor, temperature: float = 1.0, top_k: int = -1, top_
         truncated = _truncate(lf, temperature, top_k, top_p).contiguous()
     tokens = torch.empty(B, dtype=torch.int64, device=lf.device)
     logp = torch.empty(B, dtype=torch.float32, device=lf.device)
+    # few rows, huge vocabulary: split every row over several blocks so the whole GPU reads the logits
+    splits = max(1, min(32, (2 * 148) // max(B, 1), V // 4096))
+    ws = torch.empty(B * splits * 4, dtype=torch.float32, device=lf.device) if splits > 1 else None
     _lib.check(L.sb_sample(_lib.ptr(truncated), _lib.ptr(lf), ctypes.c_longlong(lf.stride(0)),
                            ctypes.c_float(temperature), ctypes.c_ulonglong(seed & (2 ** 64 - 1)),
-                           ctypes.c_ulonglong(step), _lib.ptr(step_dev), _lib.ptr(tokens), _lib.ptr(logp), B, V, _lib.stream()),
-               "sb_sample")
+                           ctypes.c_ulonglong(step), _lib.ptr(step_dev), _lib.ptr(tokens), _lib.ptr(logp), B, V,
+                           _lib.ptr(ws), splits, _lib.stream()), "sb_sample")
     return tokens, logp
