@@ -123,3 +123,10 @@ int sb_adamw_allgather(float* master, float* m, float* v, const float* grad, voi
 int sb_segment_pull(void* const* bases, int world, const void* segs, int n_segs, void* out, cudaStream_t stream);
 int sb_flag_barrier(void* const* flag_ptrs, int world, int rank, int epoch, int* status, cudaStream_t stream);
 }
+
+extern "C" {
+// ---- image_ops.cu ----
+int sb_resize_bilinear_u8(const void* src, void* dst, int N, int H, int W, int C, int OH, int OW, float crop_y0,
+                          float crop_x0, float crop_h, float crop_w, cudaStream_t stream);
+int sb_raster_synth_env(const float* state, void* out, int N, int H, int W, cudaStream_t stream);
+}

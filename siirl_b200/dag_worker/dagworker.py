@@ -248,8 +248,12 @@ class DAGWorker:
         batch.meta["global_token_num"] = batch["attention_mask"].sum(-1).tolist()
         return NodeOutput(batch, metrics)
 
+    def _sampling_temperature(self, batch: Batch) -> float:
+        arr = self.config.actor_rollout_ref
+        return arr.embodied.temperature if batch.meta.get("embodied") else arr.rollout.temperature
+
     def compute_old_log_prob(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
-        batch.meta["temperature"] = self.config.actor_rollout_ref.rollout.temperature
+        batch.meta["temperature"] = self._sampling_temperature(batch)
         out = self._arr(kwargs.get("cur_node")).compute_log_prob(batch)
         metrics = dict(out.meta.pop("metrics", {}))
         out.pop("entropys")
@@ -259,7 +263,7 @@ class DAGWorker:
         a = self.config.actor_rollout_ref.actor
         if not (a.use_kl_loss or self.config.algorithm.use_kl_in_reward):
             return NodeOutput(batch, {})
-        batch.meta["temperature"] = self.config.actor_rollout_ref.rollout.temperature
+        batch.meta["temperature"] = self._sampling_temperature(batch)
         return NodeOutput(self._arr(kwargs.get("cur_node")).compute_ref_log_prob(batch), {})
 
     def compute_value(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
@@ -291,7 +295,7 @@ class DAGWorker:
     def train_actor(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
         if self.config.trainer.critic_warmup > self.global_steps:
             return NodeOutput(batch, {})
-        batch.meta["temperature"] = self.config.actor_rollout_ref.rollout.temperature
+        batch.meta["temperature"] = self._sampling_temperature(batch)
         return NodeOutput(batch, self._arr(kwargs.get("cur_node")).update_actor(batch))
 
     # ================================================================================================

@@ -150,6 +150,9 @@ class PartitionedRLHFDataset(Dataset):
         if "pixel_values" in row:
             item["pixel_values"] = row["pixel_values"]
             item["image_grid_thw"] = row["image_grid_thw"]
+        for k in ("task_id", "trial_id"):          # embodied task-list rows
+            if k in row:
+                item[k] = torch.tensor(int(row[k]), dtype=torch.int64)
         if self.cfg.return_raw_chat:
             item["raw_prompt"] = row.get(self.cfg.prompt_key)
         for k in ("tools_kwargs", "interaction_kwargs"):
@@ -185,6 +188,11 @@ def _synthetic_rows(cfg, tokenizer, is_eval: bool) -> List[Dict[str, Any]]:
             rows.append({"prompt_ids": ids, "data_source": f"synthetic/{kind}",
                          "reward_model": {"style": "rule", "ground_truth": ""},
                          "extra_info": {"index": i, "seed": rng.randint(0, 2 ** 31)}})
+        elif kind == "embodied":
+            ids = tokenizer.encode(f"task {i % 10}")
+            rows.append({"prompt_ids": ids, "data_source": "embodied/synthetic", "task_id": i % 10,
+                         "trial_id": i // 10, "reward_model": {"style": "rule", "ground_truth": ""},
+                         "extra_info": {"index": i}})
         else:
             raise ValueError(f"unknown synthetic dataset '{kind}'")
     return rows

@@ -9,7 +9,7 @@ from typing import Dict, List, Optional, Sequence
 
 class SyntheticTokenizer:
     PAD, BOS, EOS = 0, 1, 2
-    _CHARS = "0123456789+-*/= ()?.,:abcdefghijklmnopqrstuvwxyz\n"
+    _CHARS = "0123456789+-*/= ()?.,:abcdefghijklmnopqrstuvwxyz\n" + "<>{}[]\"'_!#$%&;@|~^ABCDEFGHIJKLMNOPQRSTUVWXYZ\\"
 
     def __init__(self, vocab_size: int = 1024):
         self.vocab_size = vocab_size

@@ -155,6 +155,7 @@ class RolloutEngine:
         self.slot_ids = torch.arange(S, dtype=torch.int32, device=dev)
         self.gen_index = torch.zeros(S, dtype=torch.int32, device=dev)
         self.hit_eos = torch.zeros(S, dtype=torch.bool, device=dev)
+        self.rope_delta = torch.zeros(S, dtype=torch.int32, device=dev)    # cache position - rope position
         self._graphs.clear()
         self._out_buf = None
 
@@ -168,10 +169,22 @@ class RolloutEngine:
 
     # ---- prefill --------------------------------------------------------------------------------
     @torch.no_grad()
-    def _prefill(self, seqs: List[_Seq], prompts: List[List[int]], **mm) -> torch.Tensor:
+    def _prefill(self, seqs: List[_Seq], prompts: List[List[int]], mm_inputs=None) -> torch.Tensor:
         """Prefill one packed batch of distinct prompts (``seqs[i]`` is sample 0 of its prompt); returns the
-        final hidden state of the last token of each prompt ``[len(seqs), H]``."""
+        final hidden state of the last token of each prompt ``[len(seqs), H]``.  ``mm_inputs[i]`` (optional) holds
+        prompt i's ``pixel_values [patches, D]``, ``image_grid_thw [images, 3]`` and ``rope_positions [3, len]``."""
         lens = [len(p) for p in prompts]
+        mm = {}
+        if mm_inputs is not None and any(m for m in mm_inputs):
+            pv = [m["pixel_values"] for m in mm_inputs if m and m.get("pixel_values") is not None]
+            if pv:
+                mm["pixel_values"] = torch.cat([x.to(self.device) for x in pv], 0)
+                mm["image_grid_thw"] = torch.cat([torch.as_tensor(m["image_grid_thw"]).reshape(-1, 3)
+                                                  for m in mm_inputs if m and m.get("pixel_values") is not None], 0)
+            if any(m and m.get("rope_positions") is not None for m in mm_inputs):
+                rp = [torch.as_tensor(m["rope_positions"]) if m and m.get("rope_positions") is not None
+                      else torch.arange(n).expand(3, n) for m, n in zip(mm_inputs, lens)]
+                mm["rope_positions"] = torch.cat(rp, 1).to(self.device)
         info = SeqInfo(lens, device=self.device)
         ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64, device=self.device)
         seq_ids = torch.repeat_interleave(torch.tensor([s.slot for s in seqs], dtype=torch.int32),
@@ -191,7 +204,7 @@ class RolloutEngine:
         seq_ids = torch.where(active, self.slot_ids, torch.full_like(self.slot_ids, -1))
         seq_lens = torch.where(active, self.ctx_len + 1, torch.zeros_like(self.ctx_len))
         hidden = self.model.forward_cached(self.last_token, pos.clamp(min=0), self.cache, self.block_table, seq_ids,
-                                           seq_lens=seq_lens, rope_positions=pos.clamp(min=0))
+                                           seq_lens=seq_lens, rope_positions=(pos - self.rope_delta).clamp(min=0))
         logits = lm_head_logits(hidden, self.model.head_weight)
         tok, lp = sample(logits, sp.temperature, sp.top_k, sp.top_p, seed=sp.seed, step_dev=self.step_counter
                          if self.device.type == "cuda" else None, step=int(self.step_counter.item())
@@ -251,9 +264,12 @@ class RolloutEngine:
 
     # ---- public API -------------------------------------------------------------------------------
     @torch.no_grad()
-    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams, **mm) -> List[RolloutOutput]:
+    def generate(self, prompts: Sequence[Sequence[int]], sp: SamplingParams,
+                 mm_inputs: Optional[Sequence[Optional[dict]]] = None) -> List[RolloutOutput]:
         """Generate ``sp.n`` samples for every prompt (token id lists).  Returns outputs ordered by
-        (prompt_index, sample_index)."""
+        (prompt_index, sample_index).  ``mm_inputs[i]``: multimodal inputs of prompt i (``pixel_values``,
+        ``image_grid_thw``, ``rope_positions [3, len]``, ``rope_delta`` = prompt length minus the next rope
+        position, so that decode continues the multimodal rope numbering)."""
         assert self.cache is not None, "engine is asleep: call wake_up()"
         dev = self.device
         S = min(self.max_num_seqs, max(8, (len(prompts) * sp.n + 7) // 8 * 8))
@@ -274,6 +290,7 @@ class RolloutEngine:
         self.finished.fill_(True)
         self.ctx_len.zero_()
         self.remaining.zero_()
+        self.rope_delta.zero_()
         self.block_table.fill_(-1)
 
         def blocks_needed(plen: int) -> int:
@@ -331,7 +348,8 @@ class RolloutEngine:
                     for seq in group:
                         bt[seq.slot, : len(seq.blocks)] = torch.tensor(seq.blocks, dtype=torch.int32)
                 self.block_table.copy_(bt)
-                hidden = self._prefill([g[0] for g in batch_seqs], batch_prompts, **mm)
+                batch_mm = [mm_inputs[g[0].prompt_index] for g in batch_seqs] if mm_inputs is not None else None
+                hidden = self._prefill([g[0] for g in batch_seqs], batch_prompts, batch_mm)
                 if forks:
                     src = torch.tensor([a for a, _ in forks], dtype=torch.int32, device=dev)
                     dst = torch.tensor([b for _, b in forks], dtype=torch.int32, device=dev)
@@ -350,6 +368,9 @@ class RolloutEngine:
                 self.gen_index[sl] = 1
                 self.ctx_len[sl] = torch.tensor([s.prompt_len for s in flat], dtype=torch.int32, device=dev)
                 self.remaining[sl] = R - 1
+                if mm_inputs is not None:
+                    self.rope_delta[sl] = torch.tensor([int((mm_inputs[s.prompt_index] or {}).get("rope_delta", 0))
+                                                        for s in flat], dtype=torch.int32, device=dev)
                 self.last_token[sl] = tok
                 fin = torch.zeros(len(flat), dtype=torch.bool, device=dev) | (R <= 1)
                 if sp.eos_token_id is not None and not sp.ignore_eos:

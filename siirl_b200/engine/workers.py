@@ -100,7 +100,16 @@ class _ModelWorkerBase:
 
     def _forward_logprob(self, model: DecoderLM, mb: Batch, temperature: float, with_entropy: bool):
         pk = self._pack(mb)
-        hidden = model.forward_hidden(pk.input_ids, pk.positions, pk.info)
+        positions, mm = pk.positions, {}
+        if "images" in mb:                  # embodied rows: one policy image per row, multimodal rope layout
+            proc = self.vla_processor
+            pv, grid = proc.patchify(mb["images"].to(self.device), model.embed_tokens.dtype)
+            first = torch.tensor(pk.info.cu_seqlens_cpu[:-1], device=self.device)
+            img_mask = torch.zeros(pk.input_ids.shape[0], dtype=torch.bool, device=self.device)
+            img_mask[(first[:, None] + torch.arange(proc.tokens_per_image, device=self.device)[None, :]).flatten()] = True
+            mm = {"pixel_values": pv, "image_grid_thw": grid, "image_mask": img_mask}
+            positions = torch.cat([proc.rope_layout(n)[0] for n in pk.info.seqlens], 1).to(self.device)
+        hidden = model.forward_hidden(pk.input_ids, positions, pk.info, **mm)
         from ..ops.lm_head import lm_head_logprob_entropy
         lp, ent = lm_head_logprob_entropy(hidden.index_select(0, pk.sel), model.head_weight, pk.labels, temperature,
                                           with_entropy)
@@ -143,6 +152,10 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         self.tokenizer = tokenizer
         self.ref_model: Optional[DecoderLM] = None
         self.engine: Optional[RolloutEngine] = None
+        self._embodied = bool(getattr(config.actor, "embodied_type", None)) or str(config.rollout.name).startswith(
+            "embodied")
+        self.embodied_rollout = None
+        self.vla_processor = None
         self._normalize_batch_sizes()
 
     def _normalize_batch_sizes(self) -> None:
@@ -183,6 +196,11 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         if self._is_rollout:
             r = self.config.rollout
             max_len = r.max_model_len or ((r.prompt_length or 512) + (r.response_length or 512))
+            if self._embodied:                      # image tokens + task text + one chunk of action tokens
+                e = self.config.embodied
+                v = self.model_config.vision
+                per_image = (e.policy_image_size // (v.patch_size * v.spatial_merge_size)) ** 2
+                max_len = max(max_len, per_image * e.num_images_in_input + 64 + e.action_chunks_len * e.action_token_len)
             self.engine = RolloutEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024), max_model_len=max_len,
                                         gpu_memory_utilization=r.gpu_memory_utilization,
                                         use_cuda_graph=not r.enforce_eager or self.device.type == "cuda",
@@ -190,6 +208,30 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                                         **dict(r.engine_kwargs.native or {}))
             if r.free_cache_engine:
                 self.engine.sleep()
+        if self._embodied:
+            self._init_embodied()
+
+    def _init_embodied(self) -> None:
+        """VLA processor (all roles) and the closed-loop environment rollout (rollout role)."""
+        from ..models.embodied.vla import VLAProcessor
+        emb = self.config.embodied
+        tok = self.tokenizer
+        if tok is None:
+            from ..data_coordinator.dataloader.tokenizer import SyntheticTokenizer
+            tok = SyntheticTokenizer(self.model_config.vocab_size)
+        self.vla_processor = VLAProcessor(self.model_config, tok, image_size=emb.policy_image_size,
+                                          center_crop=emb.center_crop)
+        if self._is_rollout:
+            from .rollout.embodied_rollout import EmbodiedRollout
+            embedder = None
+            if emb.use_video_embedding:
+                from ..utils.embodied.video_emb import VideoEmbedder
+                embedder = VideoEmbedder(img_size=min(emb.embedding_img_size, 224), num_frames=emb.video_num_frames,
+                                         device=self.device, dtype=self._dtype(self.config.model),
+                                         checkpoint=emb.video_embedding_model_path or None)
+            self.embodied_rollout = EmbodiedRollout(self.engine, self.model_config, tok, emb, self.device,
+                                                    seed=self.config.rollout.seed + 104729 * self.rank,
+                                                    video_embedder=embedder)
 
     # ---- rollout -------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -199,6 +241,11 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         once).  Output adds ``prompts, responses, input_ids [B, P+R], attention_mask, position_ids, response_mask,
         rollout_log_probs``."""
         r = self.config.rollout
+        if self.embodied_rollout is not None and "task_id" in prompts:
+            out = self.embodied_rollout.generate_sequences(prompts)
+            if r.free_cache_engine:
+                self.engine.sleep()
+            return out
         t0 = time.time()
         self.engine.wake_up()
         meta = prompts.meta
@@ -269,6 +316,13 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
     def _logprob_pass(self, model: DecoderLM, data: Batch, micro: Optional[int], dynamic: bool, max_tokens: int,
                       with_entropy: bool):
         temperature = float(data.meta.get("temperature", self.config.rollout.temperature)) or 1.0
+        if data["responses"].dim() == 3:    # embodied trajectories: score the executed calls, scatter back
+            from .actor.embodied_actor import flatten_trajectories, scatter_steps
+            Bt, L, _A = data["responses"].shape
+            rows, bi, li = flatten_trajectories(data, int(data.meta.get("actions_per_call",
+                                                                        self.config.embodied.action_chunks_len)))
+            lp, ent = self._logprob_pass(model, rows, micro, dynamic, max_tokens, with_entropy)
+            return scatter_steps(lp, bi, li, Bt, L), (scatter_steps(ent, bi, li, Bt, L) if ent is not None else None)
         B, R = data["responses"].shape
         lp_out = torch.zeros(B, R, dtype=torch.float32, device=self.device)
         ent_out = torch.zeros(B, R, dtype=torch.float32, device=self.device) if with_entropy else None
@@ -315,6 +369,13 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         bs = data.batch_size
         mini = min(self.ppo_mini_batch_size, bs)
         n_mini = max(1, bs // mini)
+        if data["responses"].dim() == 3:    # embodied: executed calls become rows; same number of optimizer steps
+            from .actor.embodied_actor import flatten_trajectories
+            data, _, _ = flatten_trajectories(data, int(data.meta.get("actions_per_call",
+                                                                      self.config.embodied.action_chunks_len)))
+            bs = data.batch_size
+            mini = -(-bs // n_mini)
+            n_mini = max(1, -(-bs // mini))
         on_policy = a.ppo_epochs == 1 and n_mini == 1
         self.store.zero_grad()
         for _epoch in range(a.ppo_epochs):

@@ -48,7 +48,11 @@ def create_reward_manager(config, tokenizer, num_examine: int = 0, max_resp_len:
                      overlong_buffer_cfg=config.reward_model.overlong_buffer)
     if name == "embodied":
         extra.setdefault("action_token_len", config.actor_rollout_ref.embodied.action_token_len)
-        score_fn = kwargs.pop("embodied_score_fn", None) if "embodied_score_fn" in kwargs else None
+        if "embodied_score_fn" in kwargs:
+            score_fn = kwargs.pop("embodied_score_fn")
+        elif score_fn is default_compute_score:
+            from ...utils.reward_score.embodied import compute_embodied_reward
+            score_fn = compute_embodied_reward
     return cls(tokenizer=tokenizer, num_examine=num_examine, compute_score=score_fn,
                reward_fn_key=config.data.reward_fn_key, **extra)
 

@@ -143,22 +143,25 @@ class DecoderLM(nn.Module):
     def head_weight(self) -> torch.Tensor:
         return self.lm_head if self.lm_head is not None else self.embed_tokens
 
-    def embed(self, input_ids: torch.Tensor, pixel_values=None, image_grid_thw=None) -> torch.Tensor:
+    def embed(self, input_ids: torch.Tensor, pixel_values=None, image_grid_thw=None, image_mask=None) -> torch.Tensor:
+        """Token embeddings with vision features written over the image placeholders.  ``image_mask`` names the
+        placeholder positions explicitly; the default (ids equal to ``image_token_id``) is only safe when generated
+        tokens cannot collide with the placeholder id."""
         h = ops.embedding(input_ids, self.embed_tokens)
         if self.vision is not None and pixel_values is not None:
             img = self.vision(pixel_values, image_grid_thw).to(h.dtype)
-            mask = input_ids == self.cfg.image_token_id
+            mask = image_mask if image_mask is not None else input_ids == self.cfg.image_token_id
             idx = mask.nonzero(as_tuple=True)[0]
             h = h.index_copy(0, idx, img[: idx.numel()])
         return h
 
     # ---- training / scoring path ---------------------------------------------------------------
     def forward_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo, pixel_values=None,
-                       image_grid_thw=None) -> torch.Tensor:
+                       image_grid_thw=None, image_mask=None) -> torch.Tensor:
         """Final-norm hidden states ``[T, H]`` of a packed batch."""
         pmax = int(positions.max().item()) + 1 if positions.numel() else 1
         rope = self.rope_tables(input_ids.device, pmax)
-        h = self.embed(input_ids, pixel_values, image_grid_thw)
+        h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask)
         delta = None
         for layer in self.layers:
             if self.gradient_checkpointing and torch.is_grad_enabled():

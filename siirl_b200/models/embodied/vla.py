@@ -1,0 +1,121 @@
+"""Vision-language-action policy pieces on the native VL decoder.
+
+The reference's embodied policies are OpenVLA / OpenVLA-OFT (siirl/models/embodied/*, used by
+siirl/engine/rollout/embodied_rollout.py:312-650): a vision backbone feeds patch embeddings into a causal language
+model and continuous actions are read off discrete tokens — 256 uniform bins over [-1, 1] mapped onto the LAST 256
+ids of the vocabulary, ``action_token_len`` (7) tokens per action and ``action_chunks_len`` actions per model call.
+Here the policy is the framework's own vision tower + decoder (``DecoderLM`` with a ``vision`` config); this module
+holds what surrounds it: the action tokenizer, the device-side image preprocessing (crop + resize kernel,
+normalisation, patch layout of the vision tower) and the prompt layout shared by rollout and training.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ...ops.image import center_crop_box, resize_bilinear
+
+_MEAN = (0.48145466, 0.4578275, 0.40821073)
+_STD = (0.26862954, 0.26130258, 0.27577711)
+
+
+class ActionTokenizer:
+    """Uniform ``n_bins`` discretisation of [lo, hi]; bin b <-> token id ``vocab_size - 1 - b`` (OpenVLA's
+    convention: the least used tail of the vocabulary).  Decoding returns bin centres."""
+
+    def __init__(self, vocab_size: int, n_bins: int = 256, lo: float = -1.0, hi: float = 1.0):
+        self.vocab_size, self.n_bins, self.lo, self.hi = vocab_size, n_bins, lo, hi
+        edges = np.linspace(lo, hi, n_bins)
+        self.centers = torch.tensor((edges[:-1] + edges[1:]) / 2.0, dtype=torch.float32)
+
+    @property
+    def first_action_token(self) -> int:
+        return self.vocab_size - self.n_bins
+
+    def encode(self, actions: torch.Tensor) -> torch.Tensor:
+        a = actions.float().clamp(self.lo, self.hi)
+        b = torch.bucketize(a, torch.linspace(self.lo, self.hi, self.n_bins, device=a.device)).clamp(1, self.n_bins - 1)
+        return self.vocab_size - b
+
+    def decode(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """Any token id maps to an action: ids outside the action range are clamped into it (an untrained policy
+        may sample them), exactly like taking ``clip(vocab - id - 1, 0, n_bins - 2)``."""
+        b = (self.vocab_size - token_ids.long() - 1).clamp(0, self.n_bins - 2)
+        return self.centers.to(token_ids.device)[b]
+
+
+class VLAProcessor:
+    """Builds model inputs for one control step of a batch of environments.
+
+    Prompt layout per step: ``[image placeholders x tokens_per_image] [task text tokens]`` followed, in training,
+    by the ``action_chunks_len * action_token_len`` action tokens.  Rope positions follow the multimodal
+    convention of the VL decoder: an image of a ``g x g`` merged grid advances the position by ``g`` and the text
+    continues from there, so ``rope_delta = tokens_per_image - g`` per image."""
+
+    def __init__(self, model_config, tokenizer, image_size: int = 224, center_crop: bool = True,
+                 max_text_len: int = 48):
+        v = model_config.vision
+        assert v is not None, "the VLA policy needs a decoder with a vision tower"
+        self.cfg, self.tok = model_config, tokenizer
+        self.patch, self.merge, self.tpatch = v.patch_size, v.spatial_merge_size, v.temporal_patch_size
+        unit = self.patch * self.merge
+        self.image_size = max(unit, image_size // unit * unit)
+        self.grid = self.image_size // self.patch
+        self.tokens_per_image = (self.grid // self.merge) ** 2
+        self.center_crop = center_crop
+        self.max_text_len = max_text_len
+        self.image_token_id = model_config.image_token_id
+
+    # ---- images --------------------------------------------------------------------------------------
+    def resize(self, images: torch.Tensor) -> torch.Tensor:
+        """``[N, H, W, 3] uint8`` camera frames -> ``[N, S, S, 3] uint8`` policy input (centre crop of 90 % area when
+        enabled, then bilinear resize; reference: embodied_rollout.py:65-133)."""
+        N, H, W, _ = images.shape
+        crop = center_crop_box(H, W, 0.9) if self.center_crop else None
+        return resize_bilinear(images, (self.image_size, self.image_size), crop)
+
+    def patchify(self, images_u8: torch.Tensor, dtype=torch.bfloat16) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Resized frames ``[N, S, S, 3] uint8`` -> flattened patches ``[N * grid^2, C*T*P*P]`` in the vision tower's
+        order (per image ``(h/m, w/m, m, m)`` patch order, each patch ``C x T x P x P``) and ``grid_thw [N, 3]``."""
+        N, S = images_u8.shape[0], self.image_size
+        x = images_u8.permute(0, 3, 1, 2).float() / 255.0
+        mean = torch.tensor(_MEAN, device=x.device).view(1, 3, 1, 1)
+        std = torch.tensor(_STD, device=x.device).view(1, 3, 1, 1)
+        x = (x - mean) / std
+        g, m, P = self.grid, self.merge, self.patch
+        x = x.reshape(N, 3, g // m, m, P, g // m, m, P).permute(0, 2, 5, 3, 6, 1, 4, 7)   # N, gh, gw, m, m, C, P, P
+        x = x.unsqueeze(6).expand(-1, -1, -1, -1, -1, -1, self.tpatch, -1, -1)            # duplicate along time
+        x = x.reshape(N * g * g, 3 * self.tpatch * P * P)
+        grid = torch.tensor([[1, g, g]] * N, dtype=torch.int64)
+        return x.to(dtype), grid
+
+    # ---- tokens ---------------------------------------------------------------------------------------
+    def text_tokens(self, task_description: str) -> List[int]:
+        ids = self.tok.encode(f"What action should the robot take to {task_description.lower()}?")
+        return list(ids)[: self.max_text_len]
+
+    def prompt_ids(self, task_description: str) -> List[int]:
+        return [self.image_token_id] * self.tokens_per_image + self.text_tokens(task_description)
+
+    def rope_layout(self, prompt_len: int, extra: int = 0) -> Tuple[torch.Tensor, int]:
+        """3-row rope positions of ``[image][text][extra generated tokens]`` and the rope delta of the prompt."""
+        gm = self.grid // self.merge
+        hh = torch.arange(gm).repeat_interleave(gm)
+        ww = torch.arange(gm).repeat(gm)
+        img = torch.stack([torch.zeros(gm * gm, dtype=torch.int64), hh, ww])
+        n_text = prompt_len - self.tokens_per_image + extra
+        txt = (torch.arange(n_text) + gm).expand(3, n_text)
+        return torch.cat([img, txt], 1), self.tokens_per_image - gm
+
+    def mm_inputs(self, images_u8: torch.Tensor, prompt_lens: Sequence[int], dtype=torch.bfloat16) -> List[Dict]:
+        """Per-prompt multimodal inputs for ``RolloutEngine.generate``."""
+        pv, grid = self.patchify(images_u8, dtype)
+        per = self.grid * self.grid
+        out = []
+        for i, n in enumerate(prompt_lens):
+            pos, delta = self.rope_layout(n)
+            out.append({"pixel_values": pv[i * per:(i + 1) * per], "image_grid_thw": grid[i:i + 1],
+                        "rope_positions": pos, "rope_delta": delta})
+        return out

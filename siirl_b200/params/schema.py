@@ -335,6 +335,7 @@ class EnvironmentArgs:
     num_trials_per_task: int = 50
     num_steps_wait: int = 10
     model_family: str = "openvla"
+    env_kwargs: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass
@@ -354,6 +355,9 @@ class EmbodiedArguments:
     unnorm_key: str = "libero_10_no_noops"
     temperature: float = 1.6
     n_gpus_per_node: int = 8
+    policy_image_size: int = 224
+    video_num_frames: int = 8
+    use_video_embedding: bool = True
 
 
 @dataclass

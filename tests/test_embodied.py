@@ -1,0 +1,151 @@
+"""Embodied path on CPU: action tokens, image twins, synthetic environment, vector envs, reward shaping,
+trajectory <-> row views, and the embodied pipeline end to end on one rank."""
+import asyncio
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import torch
+
+from siirl_b200.data_coordinator.protocol import Batch
+from siirl_b200.engine.actor.embodied_actor import (executed_calls, flatten_trajectories, scatter_steps,
+                                                    trajectory_response_mask)
+from siirl_b200.environment.embodied import DummyVectorEnv, SubprocVectorEnv, make_environment
+from siirl_b200.models.embodied.vla import ActionTokenizer
+from siirl_b200.ops.image import (center_crop_box, raster_synth_env_reference, resize_bilinear_reference)
+from siirl_b200.utils.reward_score.embodied import compute_embodied_reward, dbscan
+
+
+def test_action_tokenizer_roundtrip_and_clamp():
+    tok = ActionTokenizer(vocab_size=1024)
+    a = torch.linspace(-1, 1, 101)
+    ids = tok.encode(a)
+    assert ids.min() >= tok.first_action_token and ids.max() <= 1023
+    back = tok.decode(ids)
+    assert (back - a).abs().max() <= 2.0 / 255 + 1e-6
+    assert -1.0 <= float(tok.decode(torch.tensor([5]))) <= 1.0           # non-action ids clamp into the range
+
+
+def test_resize_identity_and_crop_box():
+    img = np.random.RandomState(0).randint(0, 255, (2, 16, 16, 3), dtype=np.uint8)
+    assert np.array_equal(resize_bilinear_reference(img, (16, 16)), img)
+    flat = np.full((1, 32, 32, 3), 77, dtype=np.uint8)
+    assert (resize_bilinear_reference(flat, (8, 8), center_crop_box(32, 32, 0.9)) == 77).all()
+    y0, x0, h, w = center_crop_box(100, 200, 0.81)
+    assert abs(h - 90) < 1e-4 and abs(w - 180) < 1e-4 and abs(y0 - 5) < 1e-4 and abs(x0 - 10) < 1e-4
+
+
+def test_raster_places_goal_and_gripper():
+    st = np.array([[0.25, 0.25, 0.75, 0.75, 1.0, 0, 0, 0]], dtype=np.float32)
+    img = raster_synth_env_reference(st, 64, 64)[0]
+    assert tuple(img[48, 48]) == (30, 200, 60)            # goal centre (u = v = 0.75)
+    assert img[16, 16, 0] > 150 and img[16, 16, 1] < 80   # gripper is red
+    assert img[2, 60, 0] < 80                             # background
+
+
+def test_synthetic_env_reaches_goal_with_oracle_policy():
+    env = make_environment("synthetic", num_envs=4, max_steps=40, image_size=32)
+    obs = asyncio.new_event_loop().run_until_complete(env.reset([0, 1, 2, 3], [0, 0, 0, 0]))
+    assert obs[0]["image"].shape == (32, 32, 3) and "target" in obs[0]["task_description"]
+    loop = asyncio.new_event_loop()
+    for _ in range(40):
+        d = env.state[:, 2:4] - env.state[:, :2]
+        act = np.zeros((4, 7), dtype=np.float32)
+        act[:, :2] = np.clip(d / env.action_scale, -1, 1)
+        obs = loop.run_until_complete(env.step(act))
+        if all(o["done"] for o in obs):
+            break
+    assert all(o["success"] for o in obs) and max(o["step"] for o in obs) < 40
+    # same (task, trial) -> same layout
+    a = loop.run_until_complete(env.reset([3, 3, 3, 3], [1, 1, 2, 2]))
+    assert np.allclose(a[0]["state"], a[1]["state"]) and not np.allclose(a[1]["state"], a[2]["state"])
+
+
+class _Counter:
+    def __init__(self, start):
+        self.x = start
+
+    def reset(self):
+        return {"x": self.x}
+
+    def step(self, a):
+        self.x += int(a)
+        return {"x": self.x}, float(self.x), self.x >= 5, {}
+
+
+def _make_counter(start):
+    return _Counter(start)
+
+
+def test_vector_envs_agree():
+    import functools
+    fns = [functools.partial(_make_counter, s) for s in (0, 3)]
+    for cls in (DummyVectorEnv, SubprocVectorEnv):
+        v = cls(fns)
+        assert [o["x"] for o in v.reset()] == [0, 3]
+        obs, rew, done, info = v.step([2, 2])
+        assert [o["x"] for o in obs] == [2, 5] and rew.tolist() == [2.0, 5.0] and done.tolist() == [False, True]
+        obs, rew, done, info = v.step([1], ids=[0])
+        assert obs[0]["x"] == 3
+        v.close()
+
+
+def test_dbscan_and_shaped_reward():
+    x = np.array([[0, 0], [0.1, 0], [0, 0.1], [5, 5], [5.1, 5], [20, 20]], dtype=np.float64)
+    lab = dbscan(x, eps=0.5, min_samples=2)
+    assert lab[0] == lab[1] == lab[2] and lab[3] == lab[4] and lab[0] != lab[3] and lab[5] == -1
+    emb = torch.tensor([[0.0, 0.0], [0.1, 0.0], [0.2, 0.1], [3.0, 3.0], [9.0, 9.0]])
+    ok = torch.tensor([1, 1, 0, 0, 0])
+    s = compute_embodied_reward(emb, ok, ["t"] * 5)
+    assert s[0] == s[1] == 1.0 and 0.0 < s[4] < s[3] < s[2] <= 0.6
+    assert compute_embodied_reward(emb, torch.zeros(5), ["t"] * 5) == [0.0] * 5     # no success: no shaping
+
+
+def test_flatten_and_scatter_trajectories():
+    B, L, chunk, atl, P = 3, 4, 2, 7, 5
+    A = chunk * atl
+    finish = torch.tensor([8, 3, 1])
+    assert executed_calls(finish, L, chunk).sum(1).tolist() == [4, 2, 1]
+    mask = trajectory_response_mask(finish, L, chunk, atl)
+    assert mask.sum(1).tolist() == [56, 21, 7]
+    data = Batch({"responses": torch.arange(B * L * A).reshape(B, L, A),
+                  "step_input_ids": torch.ones(B, L, P, dtype=torch.long),
+                  "step_attention_mask": torch.ones(B, L, P, dtype=torch.long),
+                  "images": torch.zeros(B, L, 4, 4, 3, dtype=torch.uint8), "finish_step": finish,
+                  "response_mask": mask, "advantages": torch.randn(B, L * A)})
+    rows, bi, li = flatten_trajectories(data, chunk)
+    assert rows.batch_size == 7 and rows["input_ids"].shape == (7, P + A)
+    assert rows["response_mask"][5].tolist() == [1] * 7 + [0] * 7       # trajectory 1, call 1: second action not run
+    back = scatter_steps(rows["advantages"], bi, li, B, L)
+    run_tok = executed_calls(finish, L, chunk).repeat_interleave(A, 1)
+    assert torch.equal(back[run_tok], data["advantages"][run_tok]) and float(back[~run_tok].abs().sum()) == 0
+
+
+def test_embodied_pipeline_two_steps(tmp_path):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, OMP_NUM_THREADS="2", SIIRL_LOG_DIR=str(tmp_path / "log"))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    args = ["algorithm.adv_estimator=grpo", "algorithm.workflow_type=embodied", "data.synthetic=embodied",
+            "data.synthetic_size=32", "data.max_prompt_length=32", "data.max_response_length=32",
+            "data.train_batch_size=4", "actor_rollout_ref.model.arch_preset=tiny-vl", "actor_rollout_ref.rollout.n=4",
+            "actor_rollout_ref.rollout.max_num_seqs=16", "actor_rollout_ref.actor.ppo_mini_batch_size=4",
+            "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8", "actor_rollout_ref.actor.embodied_type=native-vla",
+            "actor_rollout_ref.embodied.env.env_type=synthetic", "actor_rollout_ref.embodied.env.num_envs=8",
+            "actor_rollout_ref.embodied.env.max_steps=8", "actor_rollout_ref.embodied.env.env_kwargs={success_radius: 0.3}",
+            "actor_rollout_ref.embodied.action_chunks_len=2", "actor_rollout_ref.embodied.policy_image_size=56",
+            "actor_rollout_ref.embodied.video_num_frames=2", "actor_rollout_ref.embodied.embedding_img_size=64",
+            "reward_model.reward_manager=embodied", "trainer.n_gpus_per_node=1", "trainer.device=cpu",
+            "trainer.val_before_train=False", "trainer.logger=['jsonl']", "trainer.total_training_steps=2",
+            "trainer.save_freq=-1"]
+    out = subprocess.run([sys.executable, "-m", "siirl_b200.main_dag", *args], env=env, cwd=root, capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    with open(tmp_path / "log" / "metrics.jsonl") as f:
+        m = [json.loads(line) for line in f]
+    assert [r["step"] for r in m] == [1, 2]
+    assert all(0.0 <= r["critic/score/mean"] <= 1.0 for r in m)
+    assert any(r["actor/grad_norm"] > 0 for r in m)          # some group mixes successes and failures
+    assert m[0]["embodied_sampling/initial_trajectories"] == 16.0
+    assert m[0]["response_length/max"] <= 8 * 7
