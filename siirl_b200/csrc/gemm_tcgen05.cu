@@ -35,9 +35,37 @@ struct GemmParams {
   // (C + ks * slab_stride elements); a separate kernel sums the slabs.  k_splits == 1 is the normal GEMM.
   int k_splits, kb_per_split;
   long long slab_stride;
+  const struct ArParams* ar;  // EPI_F32_AR only (device memory)
 };
 
-enum { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2 };
+enum { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_F32_AR = 3 };
+
+// Row-parallel GEMM fused with its all-reduce over peer memory (EPI_F32_AR).  Every rank of a tensor-parallel
+// group runs the same launch on its K-shard.  Per output tile: the fp32 partial goes to this rank's symmetric
+// `partial` buffer (after a local split-K reduction when k_splits > 1) and a ready flag is raised at the tile's
+// owner (tile % world); the owner's epilogue warps wait for the flags (bounded), pull the tile from every peer
+// with plain peer loads, add the bias, convert to bf16 and store the result into every rank's `out`, then raise
+// done flags.  A rank leaves the kernel only when all its tiles are done, so at kernel end `out` is complete
+// locally and `partial` may be overwritten by the next launch.  Flags carry a launch epoch that lives in device
+// memory (`local[0]`, advanced by the last CTA to exit), so replaying the launch from a CUDA graph works.
+constexpr int kArMaxRanks = 16;
+struct ArParams {
+  float* partial[kArMaxRanks];          // fp32 [M, N] per rank
+  __nv_bfloat16* out[kArMaxRanks];      // bf16 [M, ldo] per rank
+  int* ready[kArMaxRanks];              // ready[tile * kArMaxRanks + src] on each rank
+  int* done[kArMaxRanks];               // done[tile] on each rank
+  int* local;                           // [0] epoch, [1] exit counter, [2 + tile] split arrival counters
+  long long ldo;
+  int world, rank;
+};
+
+__device__ __forceinline__ float4 ld_volatile_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 template <int BN, int STAGES>
 struct GemmSmem {
@@ -207,13 +235,32 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     const int row_in_tile = quarter * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
+    // all-reduce state (EPI_F32_AR): tiles whose done flag this CTA still has to see, by loop iteration
+    const int epi_tid = (int)threadIdx.x - 64;
+    volatile uint32_t* ar_smem = tmem_slot + 1;  // [0] "this CTA finishes the tile", [1] abort
+    unsigned long long ar_pending = 0ull;
+    int ar_iter = 0;
+    int ar_epoch = 0;
+    bool ar_ok = true;
+    if constexpr (EPI == EPI_F32_AR) {
+      ar_epoch = p.ar->local[0] + 1;
+      if (epi_tid == 0) ar_smem[1] = 0;
+      epi_bar();
+    }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       int mb, nb;
       const int ks = tile / tiles_mn;
       tile_coords(tile - ks * tiles_mn, p.num_m_blocks, p.num_n_blocks, mb, nb);
       const int row = mb * kBM + row_in_tile;
       const int n0 = nb * BN;
-      if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusTimeoutEpilogue)) break;
+      if constexpr (EPI == EPI_F32_AR) {
+        // the 128 epilogue threads meet at named barriers below: leave the loop together or not at all
+        if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusTimeoutEpilogue)) ar_smem[1] = 1;
+        epi_bar();
+        if (ar_smem[1] != 0) break;
+      } else {
+        if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusTimeoutEpilogue)) break;
+      }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
 #pragma unroll 1
@@ -275,6 +322,116 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         acc = 0;
         acc_phase ^= 1;
       }
+      if constexpr (EPI == EPI_F32_AR) {
+        const ArParams& ar = *p.ar;
+        const int tile_mn = tile - ks * tiles_mn;
+        const int m0 = mb * kBM;
+        constexpr int kVecRow = BN / 8;                 // 8-column groups per tile row
+        constexpr int kItems = 32 * kVecRow;            // per warp: its 32 rows
+        __threadfence();                                // this thread's slab stores, device-wide
+        epi_bar();
+        if (epi_tid == 0) {
+          uint32_t last = 1;
+          if (p.k_splits > 1) {
+            const int prev = atomicAdd(&ar.local[2 + tile_mn], 1);
+            last = (prev == p.k_splits - 1) ? 1u : 0u;
+            if (last) ar.local[2 + tile_mn] = 0;
+          }
+          ar_smem[0] = last;
+        }
+        epi_bar();
+        const bool finisher = ar_smem[0] != 0;
+        epi_bar();                                      // ar_smem[0] may be rewritten by the next tile
+        if (finisher && ar_ok) {
+          float* my_partial = ar.partial[ar.rank];
+          if (p.k_splits > 1) {
+            __threadfence();
+            const float* slabs = reinterpret_cast<const float*>(p.C);
+            for (int it = lane; it < kItems; it += 32) {
+              const int r = m0 + quarter * 32 + it / kVecRow;
+              const int c = n0 + (it % kVecRow) * 8;
+              if (r < p.M && c + 8 <= p.N) {
+                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+                for (int sidx = 0; sidx < p.k_splits; ++sidx) {
+                  const float* src = slabs + sidx * p.slab_stride + (long long)r * p.ldc + c;
+                  const float4 x = ld_volatile_f4(src), y = ld_volatile_f4(src + 4);
+                  a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+                  b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+                }
+                float* dst = my_partial + (long long)r * p.N + c;
+                *reinterpret_cast<float4*>(dst) = a;
+                *reinterpret_cast<float4*>(dst + 4) = b;
+              }
+            }
+          }
+          __threadfence_system();
+          epi_bar();
+          const int owner = tile_mn % ar.world;
+          if (epi_tid == 0) flag_store_release(ar.ready[owner] + tile_mn * kArMaxRanks + ar.rank, ar_epoch);
+          if (owner == ar.rank) {
+            if (epi_tid < ar.world &&
+                !flag_wait_ge(ar.ready[ar.rank] + tile_mn * kArMaxRanks + epi_tid, ar_epoch, p.status))
+              ar_smem[1] = 1;
+            epi_bar();
+            ar_ok = ar_smem[1] == 0;
+            if (ar_ok) {
+              for (int it = lane; it < kItems; it += 32) {
+                const int r = m0 + quarter * 32 + it / kVecRow;
+                const int c = n0 + (it % kVecRow) * 8;
+                if (r < p.M && c + 8 <= p.N) {
+                  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                  for (int k = 0; k < ar.world; ++k) {
+                    const int src_rank = (ar.rank + k) % ar.world;
+                    const float* src = ar.partial[src_rank] + (long long)r * p.N + c;
+                    const float4 x = ld_volatile_f4(src), y = ld_volatile_f4(src + 4);
+                    v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+                    v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+                  }
+                  if (p.bias) {
+                    const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + c);
+                    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      const float2 f = __bfloat1622float2(b2[i]);
+                      v[2 * i] += f.x;
+                      v[2 * i + 1] += f.y;
+                    }
+                  }
+                  uint4 o;
+                  o.x = pack_bf16x2(v[0], v[1]);
+                  o.y = pack_bf16x2(v[2], v[3]);
+                  o.z = pack_bf16x2(v[4], v[5]);
+                  o.w = pack_bf16x2(v[6], v[7]);
+                  for (int q = 0; q < ar.world; ++q)
+                    *reinterpret_cast<uint4*>(ar.out[q] + (long long)r * ar.ldo + c) = o;
+                }
+              }
+              __threadfence_system();
+              epi_bar();
+              if (epi_tid < ar.world) flag_store_release(ar.done[epi_tid] + tile_mn, ar_epoch);
+            }
+          } else if (ar_iter < 64) {
+            ar_pending |= 1ull << ar_iter;
+          } else {
+            if (epi_tid == 0 && !flag_wait_ge(ar.done[ar.rank] + tile_mn, ar_epoch, p.status)) ar_smem[1] = 1;
+            epi_bar();
+            ar_ok = ar_smem[1] == 0;
+          }
+        }
+        ++ar_iter;
+      }
+    }
+    if constexpr (EPI == EPI_F32_AR) {
+      // every tile this CTA handed to a remote owner must be finished before `out` is used and before the
+      // next launch may overwrite `partial`
+      if (epi_tid == 0) {
+        int it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && it < 64; tile += gridDim.x, ++it) {
+          if (!((ar_pending >> it) & 1ull) || !ar_ok) continue;
+          const int tile_mn = tile % tiles_mn;
+          if (!flag_wait_ge(p.ar->done[p.ar->rank] + tile_mn, ar_epoch, p.status)) ar_ok = false;
+        }
+      }
     }
   }
 
@@ -283,6 +440,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if constexpr (EPI == EPI_F32_AR) {
+    if (threadIdx.x == 64) {  // an epilogue thread: it knows the epoch
+      __threadfence();
+      const int prev = atomicAdd(&p.ar->local[1], 1);
+      if (prev == (int)gridDim.x - 1) {
+        p.ar->local[1] = 0;
+        p.ar->local[0] = p.ar->local[0] + 1;
+      }
+    }
   }
 }
 
@@ -364,6 +531,7 @@ static int dispatch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
   SB_CASE(1, 1, EPI_F32)
   SB_CASE(0, 0, EPI_F32)
   SB_CASE(0, 1, EPI_F32)
+  SB_CASE(0, 0, EPI_F32_AR)
 #undef SB_CASE
   return -2;
 }
@@ -422,10 +590,9 @@ extern "C" int sb_splitk_reduce(const float* slabs, long long slab_stride, int s
   return (int)cudaGetLastError();
 }
 
-extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
-                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi,
-                            int tile_n, int max_ctas, int k_splits, long long slab_stride, int* status,
-                            cudaStream_t stream) {
+static int gemm_impl(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
+                     long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
+                     int k_splits, long long slab_stride, const ArParams* ar, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row pitches; the epilogue stores whole 16-byte groups of a row
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return -3;
@@ -467,11 +634,44 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   p.num_n_blocks = (N + BN - 1) / BN;
   p.num_k_blocks = (K + kBK - 1) / kBK;
   if (k_splits < 1) k_splits = 1;
-  if (k_splits > 1 && epi != EPI_F32) return -2;  // split-K writes fp32 slabs
+  if (k_splits > 1 && epi != EPI_F32 && epi != EPI_F32_AR) return -2;  // split-K writes fp32 slabs
   if (k_splits > p.num_k_blocks) k_splits = p.num_k_blocks;
+  p.ar = ar;
+  if (epi == EPI_F32_AR && k_splits > 1) {
+    // the tile finisher waits for peers inside the kernel: with split-K every CTA must own exactly one tile, so
+    // that no wait can sit in front of work another rank is waiting for
+    const int per_tile = num_sms() / (p.num_m_blocks * p.num_n_blocks);
+    if (per_tile < 2) return -5;
+    if (k_splits > per_tile) k_splits = per_tile;
+    max_ctas = 0;
+  }
   p.kb_per_split = (p.num_k_blocks + k_splits - 1) / k_splits;
   p.k_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   p.slab_stride = slab_stride;
   if (BN == 256) return dispatch_gemm<256, 4>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
   return dispatch_gemm<128, 6>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
+}
+
+extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                            long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int epi,
+                            int tile_n, int max_ctas, int k_splits, long long slab_stride, int* status,
+                            cudaStream_t stream) {
+  if (epi == EPI_F32_AR) return -2;
+  return gemm_impl(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, tile_n, max_ctas, k_splits, slab_stride,
+                   nullptr, status, stream);
+}
+
+// out[q] = bf16(sum_r A_r[M, K_r] * B_r[N, K_r]^T + bias) on every rank q of the tensor-parallel group, one launch
+// per rank.  `ar_params` is an ArParams struct in device memory (same buffers on every call of a group);
+// `c_local` receives this rank's fp32 partial: the rank's own `partial` buffer when k_splits == 1, else a local
+// slab buffer of k_splits * slab_stride floats.  N must be a multiple of 8.
+extern "C" int sb_gemm_ar_bf16(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda,
+                               long long ldb, const void* ar_params, void* c_local, int tile_n, int k_splits,
+                               long long slab_stride, int max_tiles, int* status, cudaStream_t stream) {
+  if (N % 8) return -3;
+  int BN = (tile_n == 256) ? 256 : 128;
+  const int tiles_mn = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  if (tiles_mn > max_tiles) return -4;  // flag arrays too small
+  return gemm_impl(A, B, c_local, bias, M, N, K, lda, ldb, (long long)N, 0, 0, EPI_F32_AR, BN, 0, k_splits, slab_stride,
+                   reinterpret_cast<const ArParams*>(ar_params), status, stream);
 }

@@ -18,6 +18,9 @@ extern "C" {
 // C[M,N] (+)= A * B^T.  a_mn/b_mn: operand stored with the contraction index strided
 // (A as [K,M], B as [K,N]).  epi: 0 bf16 store (+bias), 1 fp32 accumulate, 2 fp32 store.
 // tile_n: 128, 256 or 0 (auto).  max_ctas: 0 = one CTA per SM.
+int sb_gemm_ar_bf16(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda, long long ldb,
+                    const void* ar_params, void* c_local, int tile_n, int k_splits, long long slab_stride,
+                    int max_tiles, int* status, cudaStream_t stream);
 int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
                  int k_splits, long long slab_stride, int* status, cudaStream_t stream);

@@ -302,10 +302,12 @@ class DAGWorker:
     # data movement between nodes
     # ================================================================================================
     def put_data_to_buffers(self, key: str, data: Batch, source_dp_size: int, dest_dp_size: int,
-                            enforce_buffer: bool = False) -> None:
+                            enforce_buffer: bool = False, tp_rank: int = 0) -> None:
         if source_dp_size == dest_dp_size and not enforce_buffer:
             self.internal_data_cache[key] = data
             return
+        if tp_rank != 0:
+            return      # tensor-parallel peers hold identical data: only the first rank of a TP group publishes
         infos, samples = Dict2Samples(data, key=key)
         for info in infos:
             info.dict_info["source_dp_size"] = source_dp_size
@@ -431,7 +433,7 @@ class DAGWorker:
                 enforce = node.node_role == NodeRole.DYNAMIC_SAMPLING
                 for child in nxt:
                     cdp = self._get_node_dp_info(child)[0]
-                    self.put_data_to_buffers(child.node_id, cur, dp_size, cdp, enforce_buffer=enforce)
+                    self.put_data_to_buffers(child.node_id, cur, dp_size, cdp, enforce_buffer=enforce, tp_rank=tp_rank)
                 prev_dp = dp_size
             self._dapo_gen_batches = 0
         final = cur

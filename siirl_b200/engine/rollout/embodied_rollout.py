@@ -52,13 +52,11 @@ class EmbodiedRollout:
 
     @staticmethod
     def _run(coro):
+        loop = asyncio.new_event_loop()
         try:
-            loop = asyncio.get_event_loop()
-            if loop.is_running():
-                raise RuntimeError
-        except RuntimeError:
-            loop = asyncio.new_event_loop()
-        return loop.run_until_complete(coro)
+            return loop.run_until_complete(coro)
+        finally:
+            loop.close()
 
     @torch.no_grad()
     def generate_sequences(self, prompts: Batch) -> Batch:

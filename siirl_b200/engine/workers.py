@@ -201,7 +201,12 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 v = self.model_config.vision
                 per_image = (e.policy_image_size // (v.patch_size * v.spatial_merge_size)) ** 2
                 max_len = max(max_len, per_image * e.num_images_in_input + 64 + e.action_chunks_len * e.action_token_len)
-            self.engine = RolloutEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024), max_model_len=max_len,
+            self.tp_model = None
+            tp = max(1, int(r.tensor_model_parallel_size))
+            if tp > 1:
+                self.tp_model = self._build_tp_model(tp, r.max_num_batched_tokens)
+            self.engine = RolloutEngine(self.tp_model or self.model, max_num_seqs=min(r.max_num_seqs, 1024),
+                                        max_model_len=max_len,
                                         gpu_memory_utilization=r.gpu_memory_utilization,
                                         use_cuda_graph=not r.enforce_eager or self.device.type == "cuda",
                                         max_num_batched_tokens=r.max_num_batched_tokens,
@@ -210,6 +215,31 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 self.engine.sleep()
         if self._embodied:
             self._init_embodied()
+
+    def _build_tp_model(self, tp: int, max_tokens: int):
+        """Tensor-parallel rollout: consecutive blocks of ``tp`` ranks of the worker's group form one engine
+        replica (rank layout [DP][TP], TP fastest).  Every rank of the job creates all TP groups in the same
+        order (``new_group`` is collective)."""
+        import torch.distributed as dist
+        from ..models.tp_decoder import TPDecoder
+        from ..parallel.tensor_parallel import TPContext
+        if self.world % tp:
+            raise ValueError(f"rollout.tensor_model_parallel_size={tp} does not divide the group size {self.world}")
+        ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
+        mine = None
+        for b in range(self.world // tp):
+            g = dist.new_group(ranks[b * tp:(b + 1) * tp])
+            if b == self.rank // tp:
+                mine = g
+        comm = None
+        if self.device.type == "cuda":
+            from ..parallel.symm import SymmComm
+            comm = SymmComm.create(mine)
+        H = self.model_config.hidden_size
+        ctx = TPContext(mine, comm, max_rows=max(max_tokens, 256), max_cols=H,
+                        max_tiles=((max(max_tokens, 256) + 127) // 128) * ((H + 127) // 128) + 8)
+        self._tp_size = tp
+        return TPDecoder(self.model, ctx)
 
     def _init_embodied(self) -> None:
         """VLA processor (all roles) and the closed-loop environment rollout (rollout role)."""
@@ -241,6 +271,8 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         once).  Output adds ``prompts, responses, input_ids [B, P+R], attention_mask, position_ids, response_mask,
         rollout_log_probs``."""
         r = self.config.rollout
+        if getattr(self, "tp_model", None) is not None:
+            self.tp_model.sync_weights()        # column-parallel copies follow the trained replica
         if self.embodied_rollout is not None and "task_id" in prompts:
             out = self.embodied_rollout.generate_sequences(prompts)
             if r.free_cache_engine:
@@ -275,7 +307,8 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         pad = meta.get("pad_token_id", self.model_config.pad_token_id)
         sp = SamplingParams(n=n if uniform else 1, temperature=float(temperature), top_k=int(top_k),
                             top_p=float(top_p), max_new_tokens=R, eos_token_id=eos, ignore_eos=r.ignore_eos,
-                            seed=(r.seed + 7919 * int(meta.get("global_steps", 0)) + 104729 * self.rank) & 0x7FFFFFFF)
+                            seed=(r.seed + 7919 * int(meta.get("global_steps", 0))
+                                  + 104729 * (self.rank // getattr(self, "_tp_size", 1))) & 0x7FFFFFFF)
         if uniform:
             outs = self.engine.generate([list(raw[g[0]]) for g in groups], sp)
             order = [i for g in groups for i in g]

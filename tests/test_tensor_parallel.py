@@ -1,0 +1,14 @@
+"""Tensor-parallel rollout on two gloo ranks: row-parallel linear, TP engine vs single-rank engine, weight sync."""
+import os
+import subprocess
+import sys
+
+
+def test_tensor_parallel_two_cpu_ranks():
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, TP_DEVICE="cpu", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29541", os.path.join(here, "tp_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "TP_OK" in out.stdout
