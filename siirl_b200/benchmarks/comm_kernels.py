@@ -1,0 +1,126 @@
+"""Benchmarks of the kernels fused with a collective, against the same op done with library collectives.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node=N --master-addr 127.0.0.1 --master-port 29577 \
+        -m siirl_b200.benchmarks.comm_kernels [--case optimizer|gemm_ar|all] [--numel 1e9]
+
+One JSON line per case from rank 0.  Times are CUDA-event times on the launching stream after 3 warm-up iterations,
+median of the timed iterations, MAX over ranks.  Rooflines: a fused kernel's target time is the slower of
+FLOPs / measured cuBLAS bf16 throughput and bytes crossing NVLink / 770 GB/s (measured peer-copy bandwidth per
+direction per GPU on this pool)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from .kernels import peaks
+
+NVLINK_GBS = 770.0
+
+
+def timeit(fn, iters=10, warm=3) -> float:
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ts = []
+    for _ in range(iters):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    t = torch.tensor([ts[len(ts) // 2]], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def emit(**kw):
+    if dist.get_rank() == 0:
+        print(json.dumps(kw), flush=True)
+
+
+def bench_optimizer(comm, numel: int):
+    from ..parallel.flat_params import FlatParamStore
+    world = dist.get_world_size()
+
+    class _M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.p = torch.nn.Parameter(torch.zeros(numel, device="cuda", dtype=torch.bfloat16))
+
+    res = {}
+    for name, c in (("fused_peer_memory", comm), ("nccl", None)):
+        store = FlatParamStore(_M(), group=dist.group.WORLD, comm=c)
+        store.flat_grad.normal_()
+        res[name] = timeit(lambda: store.step(1e-4), iters=5)
+        del store
+        torch.cuda.empty_cache()
+    shard = numel / world
+    link_bytes = (world - 1) * shard * 4 + (world - 1) * shard * 2      # pulled fp32 grads + pushed bf16 params
+    hbm_bytes = numel * 4 / world * world + shard * (4 * 3 * 2 + 4) + numel * 2
+    target = max(link_bytes / NVLINK_GBS / 1e6, hbm_bytes / peaks()["hbm_gbs"] / 1e6)
+    emit(case="reduce_scatter+adamw+all_gather", numel=numel, world=world, fused_ms=round(res["fused_peer_memory"], 3),
+         nccl_ms=round(res["nccl"], 3), speedup=round(res["nccl"] / res["fused_peer_memory"], 3),
+         roofline_ms=round(target, 3), frac_of_roofline=round(target / res["fused_peer_memory"], 3))
+
+
+def bench_gemm_ar(comm):
+    from .. import ops
+    from ..parallel.tensor_parallel import TPContext
+    world, rank = dist.get_world_size(), dist.get_rank()
+    H = 3584
+    ctx = TPContext(dist.group.WORLD, comm, max_rows=8192, max_cols=H, max_tiles=64 * 28 + 8)
+    pk = peaks()
+    for M, K, what in ((64, 18944, "decode down_proj"), (64, 3584, "decode o_proj"), (128, 18944, "decode down_proj"),
+                       (4096, 18944, "prefill down_proj"), (8192, 3584, "prefill o_proj")):
+        ks = K // world // 64 * 64
+        x = torch.randn(M, ks, device="cuda", dtype=torch.bfloat16)
+        w = (0.02 * torch.randn(H, ks, device="cuda")).to(torch.bfloat16)
+        fused = timeit(lambda: ctx.row_parallel_linear(x, w))
+
+        def lib_path():
+            y = ops.linear(x, w)
+            dist.all_reduce(y)
+            return y
+
+        nccl = timeit(lib_path)
+        flops = 2.0 * M * H * ks
+        link = (world - 1) / world * M * H * (4 + 2)
+        hbm = H * ks * 2
+        target = max(flops / pk["tflops"] / 1e9, link / NVLINK_GBS / 1e6, hbm / pk["hbm_gbs"] / 1e6)
+        emit(case="gemm+all_reduce", shape=what, M=M, N=H, K_per_rank=ks, world=world, fused_ms=round(fused, 4),
+             gemm_plus_nccl_ms=round(nccl, 4), speedup=round(nccl / fused, 3), roofline_ms=round(target, 4),
+             frac_of_roofline=round(target / fused, 3))
+    _ = rank
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", default="all", choices=["all", "optimizer", "gemm_ar"])
+    ap.add_argument("--numel", type=float, default=1e9)
+    a = ap.parse_args()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dist.init_process_group("nccl")
+    from ..ops import lib
+    from ..parallel.symm import SymmComm
+    comm = SymmComm.create(dist.group.WORLD)
+    emit(peaks=peaks(), world=dist.get_world_size(), nvlink_gbs_per_direction=NVLINK_GBS)
+    if a.case in ("all", "gemm_ar"):
+        bench_gemm_ar(comm)
+    if a.case in ("all", "optimizer"):
+        n = int(a.numel) // (8 * dist.get_world_size()) * (8 * dist.get_world_size())
+        bench_optimizer(comm, n)
+    torch.cuda.synchronize()
+    lib.check_status()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -36,6 +36,22 @@ struct GemmParams {
   int k_splits, kb_per_split;
   long long slab_stride;
   const struct ArParams* ar;  // EPI_F32_AR only (device memory)
+  // grouped GEMM (mixture-of-experts), both optional:
+  //  * tile_group[mb] >= 0 selects the group (expert) whose B matrix m-block mb multiplies; B holds the groups
+  //    stacked along its outer dimension, b_group_rows rows each; -1 skips the m-block (padding past the last
+  //    routed row, known only on the device).
+  //  * group_rows[g], group_rows[g+1] (multiples of 64) bound the contraction rows of group g; tiles are
+  //    (g, mb, nb) and C advances by c_group_stride elements per group (per-expert weight gradients).
+  const int* tile_group;
+  long long b_group_rows;
+  const int* group_rows;
+  long long c_group_stride;
+};
+
+struct TileInfo {
+  int m0, n0, kb0, kb1, b_off;
+  long long c_off;
+  bool skip;
 };
 
 enum { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_F32_AR = 3 };
@@ -57,6 +73,9 @@ struct ArParams {
   int* local;                           // [0] epoch, [1] exit counter, [2 + tile] split arrival counters
   long long ldo;
   int world, rank;
+  float* recv[kArMaxRanks];             // one-shot: fp32 [2 (epoch parity)][world (source)][recv_slab] per rank
+  long long recv_slab;                  // floats per (parity, source) slab: >= 128 * N
+  int one_shot;                         // 1: push protocol (M <= 128), 0: owner pull protocol
 };
 
 __device__ __forceinline__ float4 ld_volatile_f4(const float* p) {
@@ -89,6 +108,36 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m_blocks, int num_
   nb = t / gm;
 }
 
+template <int BN>
+__device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int tile, int tiles_mn) {
+  TileInfo t;
+  int mb, nb;
+  const int outer = tile / tiles_mn;  // k-split index, or group index when group_rows is set
+  tile_coords(tile - outer * tiles_mn, p.num_m_blocks, p.num_n_blocks, mb, nb);
+  t.m0 = mb * kBM;
+  t.n0 = nb * BN;
+  t.b_off = 0;
+  t.skip = false;
+  if (p.group_rows) {
+    t.kb0 = p.group_rows[outer] / kBK;
+    t.kb1 = p.group_rows[outer + 1] / kBK;
+    t.c_off = outer * p.c_group_stride;
+    t.skip = t.kb1 <= t.kb0;
+  } else {
+    t.kb0 = outer * p.kb_per_split;
+    t.kb1 = min(t.kb0 + p.kb_per_split, p.num_k_blocks);
+    t.c_off = outer * p.slab_stride;
+    if (p.tile_group) {
+      const int g = p.tile_group[mb];
+      t.skip = g < 0;
+      t.b_off = g < 0 ? 0 : (int)(g * p.b_group_rows);
+    }
+  }
+  return t;
+}
+
+#include "gemm_ar.cuh"
+
 template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -105,7 +154,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tiles_mn = p.num_m_blocks * p.num_n_blocks;
-  const int num_tiles = tiles_mn * p.k_splits;
+  const int num_tiles = tiles_mn * p.k_splits;  // k_splits holds the group count when group_rows is set
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512 (power of two)
 
   if (threadIdx.x == 0) {
@@ -140,11 +189,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int s = 0; s < STAGES; ++s) last_armed[s] = -1;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int mb, nb;
-        const int ks = tile / tiles_mn;
-        tile_coords(tile - ks * tiles_mn, p.num_m_blocks, p.num_n_blocks, mb, nb);
-        const int m0 = mb * kBM, n0 = nb * BN;
-        const int kb0 = ks * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+        const TileInfo ti = tile_info<BN>(p, tile, tiles_mn);
+        if (ti.skip) continue;
+        const int m0 = ti.m0, n0 = ti.n0, kb0 = ti.kb0, kb1 = ti.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kStatusTimeoutProducer)) {
             ok = false;
@@ -162,11 +209,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             tma_load_2d(sa + 8192, &map_a, &full_bar[stage], m0 + 64, k0);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb_, &map_b, &full_bar[stage], k0, n0);
+            tma_load_2d(sb_, &map_b, &full_bar[stage], k0, n0 + ti.b_off);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
-              tma_load_2d(sb_ + c * 8192, &map_b, &full_bar[stage], n0 + c * 64, k0);
+              tma_load_2d(sb_ + c * 8192, &map_b, &full_bar[stage], n0 + c * 64, k0 + ti.b_off);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -189,14 +236,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const TileInfo ti = tile_info<BN>(p, tile, tiles_mn);
+      if (ti.skip) continue;
       if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusTimeoutMma)) {
         ok = false;
         break;
       }
       tc_fence_after();
       const uint32_t tmem_d = tmem_base + acc * BN;
-      const int ks = tile / tiles_mn;
-      const int kb0 = ks * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+      const int kb0 = ti.kb0, kb1 = ti.kb1;
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(&full_bar[stage], phase, p.status, kStatusTimeoutMma)) {
           ok = false;
@@ -248,11 +296,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       epi_bar();
     }
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      int mb, nb;
+      const TileInfo ti = tile_info<BN>(p, tile, tiles_mn);
+      if (ti.skip) continue;
       const int ks = tile / tiles_mn;
-      tile_coords(tile - ks * tiles_mn, p.num_m_blocks, p.num_n_blocks, mb, nb);
-      const int row = mb * kBM + row_in_tile;
-      const int n0 = nb * BN;
+      const int row = ti.m0 + row_in_tile;
+      const int n0 = ti.n0;
       if constexpr (EPI == EPI_F32_AR) {
         // the 128 epilogue threads meet at named barriers below: leave the loop together or not at all
         if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusTimeoutEpilogue)) ar_smem[1] = 1;
@@ -271,7 +319,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const int col0 = n0 + c * 32;
         if (row < p.M && col0 < p.N) {
           if constexpr (EPI == EPI_BF16) {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + ti.c_off + (long long)row * p.ldc + col0;
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               if (col0 + g * 8 + 8 <= p.N) {
@@ -297,7 +345,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
               }
             }
           } else {
-            float* crow = reinterpret_cast<float*>(p.C) + ks * p.slab_stride + (long long)row * p.ldc + col0;
+            float* crow = reinterpret_cast<float*>(p.C) + ti.c_off + (long long)row * p.ldc + col0;
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
               if (col0 + g * 4 + 4 <= p.N) {
@@ -323,101 +371,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         acc_phase ^= 1;
       }
       if constexpr (EPI == EPI_F32_AR) {
-        const ArParams& ar = *p.ar;
-        const int tile_mn = tile - ks * tiles_mn;
-        const int m0 = mb * kBM;
-        constexpr int kVecRow = BN / 8;                 // 8-column groups per tile row
-        constexpr int kItems = 32 * kVecRow;            // per warp: its 32 rows
-        __threadfence();                                // this thread's slab stores, device-wide
-        epi_bar();
-        if (epi_tid == 0) {
-          uint32_t last = 1;
-          if (p.k_splits > 1) {
-            const int prev = atomicAdd(&ar.local[2 + tile_mn], 1);
-            last = (prev == p.k_splits - 1) ? 1u : 0u;
-            if (last) ar.local[2 + tile_mn] = 0;
-          }
-          ar_smem[0] = last;
-        }
-        epi_bar();
-        const bool finisher = ar_smem[0] != 0;
-        epi_bar();                                      // ar_smem[0] may be rewritten by the next tile
-        if (finisher && ar_ok) {
-          float* my_partial = ar.partial[ar.rank];
-          if (p.k_splits > 1) {
-            __threadfence();
-            const float* slabs = reinterpret_cast<const float*>(p.C);
-            for (int it = lane; it < kItems; it += 32) {
-              const int r = m0 + quarter * 32 + it / kVecRow;
-              const int c = n0 + (it % kVecRow) * 8;
-              if (r < p.M && c + 8 <= p.N) {
-                float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
-                for (int sidx = 0; sidx < p.k_splits; ++sidx) {
-                  const float* src = slabs + sidx * p.slab_stride + (long long)r * p.ldc + c;
-                  const float4 x = ld_volatile_f4(src), y = ld_volatile_f4(src + 4);
-                  a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
-                  b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
-                }
-                float* dst = my_partial + (long long)r * p.N + c;
-                *reinterpret_cast<float4*>(dst) = a;
-                *reinterpret_cast<float4*>(dst + 4) = b;
-              }
-            }
-          }
-          __threadfence_system();
-          epi_bar();
-          const int owner = tile_mn % ar.world;
-          if (epi_tid == 0) flag_store_release(ar.ready[owner] + tile_mn * kArMaxRanks + ar.rank, ar_epoch);
-          if (owner == ar.rank) {
-            if (epi_tid < ar.world &&
-                !flag_wait_ge(ar.ready[ar.rank] + tile_mn * kArMaxRanks + epi_tid, ar_epoch, p.status))
-              ar_smem[1] = 1;
-            epi_bar();
-            ar_ok = ar_smem[1] == 0;
-            if (ar_ok) {
-              for (int it = lane; it < kItems; it += 32) {
-                const int r = m0 + quarter * 32 + it / kVecRow;
-                const int c = n0 + (it % kVecRow) * 8;
-                if (r < p.M && c + 8 <= p.N) {
-                  float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                  for (int k = 0; k < ar.world; ++k) {
-                    const int src_rank = (ar.rank + k) % ar.world;
-                    const float* src = ar.partial[src_rank] + (long long)r * p.N + c;
-                    const float4 x = ld_volatile_f4(src), y = ld_volatile_f4(src + 4);
-                    v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
-                    v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
-                  }
-                  if (p.bias) {
-                    const uint4 bv = *reinterpret_cast<const uint4*>(p.bias + c);
-                    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                      const float2 f = __bfloat1622float2(b2[i]);
-                      v[2 * i] += f.x;
-                      v[2 * i + 1] += f.y;
-                    }
-                  }
-                  uint4 o;
-                  o.x = pack_bf16x2(v[0], v[1]);
-                  o.y = pack_bf16x2(v[2], v[3]);
-                  o.z = pack_bf16x2(v[4], v[5]);
-                  o.w = pack_bf16x2(v[6], v[7]);
-                  for (int q = 0; q < ar.world; ++q)
-                    *reinterpret_cast<uint4*>(ar.out[q] + (long long)r * ar.ldo + c) = o;
-                }
-              }
-              __threadfence_system();
-              epi_bar();
-              if (epi_tid < ar.world) flag_store_release(ar.done[epi_tid] + tile_mn, ar_epoch);
-            }
-          } else if (ar_iter < 64) {
-            ar_pending |= 1ull << ar_iter;
-          } else {
-            if (epi_tid == 0 && !flag_wait_ge(ar.done[ar.rank] + tile_mn, ar_epoch, p.status)) ar_smem[1] = 1;
-            epi_bar();
-            ar_ok = ar_smem[1] == 0;
-          }
-        }
+        ar_tile_phase<BN>(p, tile - ks * tiles_mn, ti.m0, n0, quarter, lane, epi_tid, ar_smem, ar_epoch, ar_ok,
+                          ar_pending, ar_iter);
         ++ar_iter;
       }
     }
@@ -590,9 +545,18 @@ extern "C" int sb_splitk_reduce(const float* slabs, long long slab_stride, int s
   return (int)cudaGetLastError();
 }
 
+struct GroupArgs {
+  const int* tile_group;   // per m-block group id (grouped along M), or nullptr
+  long long b_group_rows;  // rows of B's outer dimension per group
+  const int* group_rows;   // num_groups + 1 contraction-row offsets (grouped along K), or nullptr
+  int num_groups;
+  long long c_group_stride;
+};
+
 static int gemm_impl(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                      long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
-                     int k_splits, long long slab_stride, const ArParams* ar, int* status, cudaStream_t stream) {
+                     int k_splits, long long slab_stride, const ArParams* ar, int* status, cudaStream_t stream,
+                     const GroupArgs* grp = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row pitches; the epilogue stores whole 16-byte groups of a row
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return -3;
@@ -622,8 +586,10 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, in
   if (!a_mn) r = make_tensor_map_bf16_2d(&ma, A, K, M, lda, kBK, kBM);
   else r = make_tensor_map_bf16_2d(&ma, A, M, K, lda, 64, kBK);
   if (r) return r;
-  if (!b_mn) r = make_tensor_map_bf16_2d(&mb, B, K, N, ldb, kBK, BN);
-  else r = make_tensor_map_bf16_2d(&mb, B, N, K, ldb, 64, kBK);
+  const bool by_m = grp && grp->tile_group;
+  const long long b_groups = by_m ? grp->num_groups : 1;
+  if (!b_mn) r = make_tensor_map_bf16_2d(&mb, B, K, by_m ? b_groups * grp->b_group_rows : N, ldb, kBK, BN);
+  else r = make_tensor_map_bf16_2d(&mb, B, N, by_m ? b_groups * grp->b_group_rows : K, ldb, 64, kBK);
   if (r) return r;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
@@ -637,6 +603,18 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, in
   if (k_splits > 1 && epi != EPI_F32 && epi != EPI_F32_AR) return -2;  // split-K writes fp32 slabs
   if (k_splits > p.num_k_blocks) k_splits = p.num_k_blocks;
   p.ar = ar;
+  p.tile_group = nullptr;
+  p.group_rows = nullptr;
+  p.b_group_rows = 0;
+  p.c_group_stride = 0;
+  if (grp) {
+    if (k_splits != 1 || epi == EPI_F32_AR) return -2;
+    p.tile_group = grp->tile_group;
+    p.b_group_rows = grp->b_group_rows;
+    p.group_rows = grp->group_rows;
+    p.c_group_stride = grp->c_group_stride;
+    if (grp->group_rows) k_splits = grp->num_groups;  // one "split" per group; the kernel reads its row range
+  }
   if (epi == EPI_F32_AR && k_splits > 1) {
     // the tile finisher waits for peers inside the kernel: with split-K every CTA must own exactly one tile, so
     // that no wait can sit in front of work another rank is waiting for
@@ -647,6 +625,7 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, in
   }
   p.kb_per_split = (p.num_k_blocks + k_splits - 1) / k_splits;
   p.k_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
+  if (grp && grp->group_rows) p.k_splits = grp->num_groups;
   p.slab_stride = slab_stride;
   if (BN == 256) return dispatch_gemm<256, 4>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
   return dispatch_gemm<128, 6>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
@@ -659,6 +638,22 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   if (epi == EPI_F32_AR) return -2;
   return gemm_impl(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, tile_n, max_ctas, k_splits, slab_stride,
                    nullptr, status, stream);
+}
+
+// Grouped GEMM for mixture-of-experts layers, one launch for all experts.
+//  tile_group != null (forward / dgrad): rows of A are sorted by expert and padded so that every 128-row block
+//    belongs to one expert; tile_group[mb] names it (-1: block unused).  B stacks the experts' matrices along its
+//    outer dimension (b_group_rows rows each): [E*N, K] for K-major B, [E*Kc, N] for MN-major B.
+//  group_rows != null (wgrad): C_g[M, N] (+)= sum over rows [group_rows[g], group_rows[g+1]) of A^T B with A
+//    [rows, M] and B [rows, N] MN-major; C advances c_group_stride elements per group.
+extern "C" int sb_gemm_grouped_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                    long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n,
+                                    const int* tile_group, long long b_group_rows, const int* group_rows,
+                                    int num_groups, long long c_group_stride, int* status, cudaStream_t stream) {
+  GroupArgs g{tile_group, b_group_rows, group_rows, num_groups, c_group_stride};
+  if ((!tile_group) == (!group_rows) || num_groups < 1) return -3;
+  return gemm_impl(A, B, C, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, tile_n, 0, 1, 0, nullptr, status, stream,
+                   &g);
 }
 
 // out[q] = bf16(sum_r A_r[M, K_r] * B_r[N, K_r]^T + bias) on every rank q of the tensor-parallel group, one launch

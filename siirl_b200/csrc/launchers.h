@@ -21,6 +21,16 @@ extern "C" {
 int sb_gemm_ar_bf16(const void* A, const void* B, const void* bias, int M, int N, int K, long long lda, long long ldb,
                     const void* ar_params, void* c_local, int tile_n, int k_splits, long long slab_stride,
                     int max_tiles, int* status, cudaStream_t stream);
+int sb_moe_gather_rows(const void* const* src_ptrs, int world, const int* src_rank, const int* src_row,
+                       const float* scale, void* out, int M, int H, cudaStream_t stream);
+int sb_moe_combine(const void* const* y_ptrs, int world, const int* pair_rank, const int* pair_slot, const float* w,
+                   void* out, int T, int k, int H, cudaStream_t stream);
+int sb_moe_pair_dot(const void* const* y_ptrs, int world, const int* pair_rank, const int* pair_slot, const void* dout,
+                    float* dots, int T, int k, int H, cudaStream_t stream);
+int sb_gemm_grouped_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
+                         long long ldc, int a_mn, int b_mn, int epi, int tile_n, const int* tile_group,
+                         long long b_group_rows, const int* group_rows, int num_groups, long long c_group_stride,
+                         int* status, cudaStream_t stream);
 int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
                  int k_splits, long long slab_stride, int* status, cudaStream_t stream);

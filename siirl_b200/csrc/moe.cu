@@ -1,0 +1,161 @@
+// Mixture-of-experts token movement, local or expert-parallel over peer memory (NVLink 5 / NVSwitch).
+//
+// The reference reaches MoE through Megatron-core's token dispatcher (NCCL all-to-all, then a permutation kernel, then
+// grouped GEMM; siirl/models/mcore/config_converter.py, qwen3moe branch).  Here the all-to-all IS the permutation
+// kernel: rows are read straight from the peer that holds them (plain peer loads) and land in the expert-sorted,
+// 128-row-padded layout the grouped tcgen05 GEMM consumes; the way back sums a token's top-k expert outputs while it
+// pulls them.  With one rank the peer table has a single entry and the same kernels do the local permutation.
+//
+//   moe_gather_rows   out[slot] = scale[slot] * src[src_rank[slot]][src_row[slot]]   (zero row when src_row < 0)
+//                     dispatch (forward), and the backward of combine (scale = routing weight)
+//   moe_combine       out[t] = sum_k w[t,k] * y[pair_rank[t,k]][pair_slot[t,k]]
+//                     combine (forward), and the backward of dispatch (w = 1)
+//   moe_pair_dot      dots[t,k] = <dout[t], y[pair_rank[t,k]][pair_slot[t,k]]>         (gradient of the routing weights)
+//
+// One warp per row, 16-byte accesses; H must be a multiple of 8.  No kernel here waits on another GPU: the caller
+// orders producers and consumers with the communicator's barrier.
+#include "common.cuh"
+#include "launchers.h"
+
+namespace sb {
+
+constexpr int kMoeMaxRanks = 16;
+struct MoePeers {
+  const __nv_bfloat16* p[kMoeMaxRanks];
+};
+
+__global__ void moe_gather_rows_kernel(MoePeers src, const int* __restrict__ src_rank, const int* __restrict__ src_row,
+                                       const float* __restrict__ scale, __nv_bfloat16* __restrict__ out, int M, int H) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = H / 8;
+  for (int row = blockIdx.x * warps_per_block + (threadIdx.x >> 5); row < M; row += gridDim.x * warps_per_block) {
+    const int sr = src_row[row];
+    uint4* dst = reinterpret_cast<uint4*>(out + (long long)row * H);
+    if (sr < 0) {
+      for (int v = lane; v < nvec; v += 32) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    const uint4* s = reinterpret_cast<const uint4*>(src.p[src_rank ? src_rank[row] : 0] + (long long)sr * H);
+    if (!scale) {
+      for (int v = lane; v < nvec; v += 32) dst[v] = s[v];
+    } else {
+      const float a = scale[row];
+      for (int v = lane; v < nvec; v += 32) {
+        uint4 x = s[v];
+        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __bfloat1622float2(h2[i]);
+          h2[i] = __floats2bfloat162_rn(f.x * a, f.y * a);
+        }
+        dst[v] = x;
+      }
+    }
+  }
+}
+
+__global__ void moe_combine_kernel(MoePeers y, const int* __restrict__ pair_rank, const int* __restrict__ pair_slot,
+                                   const float* __restrict__ w, __nv_bfloat16* __restrict__ out, int T, int k, int H) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = H / 8;
+  for (int t = blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < T; t += gridDim.x * warps_per_block) {
+    uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * H);
+    for (int v = lane; v < nvec; v += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < k; ++j) {
+        const int slot = pair_slot[t * k + j];
+        if (slot < 0) continue;
+        const float a = w ? w[t * k + j] : 1.f;
+        const uint4 x = reinterpret_cast<const uint4*>(y.p[pair_rank ? pair_rank[t * k + j] : 0] + (long long)slot * H)[v];
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h2[i]);
+          acc[2 * i] += a * f.x;
+          acc[2 * i + 1] += a * f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      dst[v] = o;
+    }
+  }
+}
+
+__global__ void moe_pair_dot_kernel(MoePeers y, const int* __restrict__ pair_rank, const int* __restrict__ pair_slot,
+                                    const __nv_bfloat16* __restrict__ dout, float* __restrict__ dots, int T, int k,
+                                    int H) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = H / 8;
+  const int P = T * k;
+  for (int pr = blockIdx.x * warps_per_block + (threadIdx.x >> 5); pr < P; pr += gridDim.x * warps_per_block) {
+    const int slot = pair_slot[pr];
+    float acc = 0.f;
+    if (slot >= 0) {
+      const uint4* a = reinterpret_cast<const uint4*>(dout + (long long)(pr / k) * H);
+      const uint4* b = reinterpret_cast<const uint4*>(y.p[pair_rank ? pair_rank[pr] : 0] + (long long)slot * H);
+      for (int v = lane; v < nvec; v += 32) {
+        const uint4 xa = a[v], xb = b[v];
+        const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&xa);
+        const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&xb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 fa = __bfloat1622float2(ha[i]), fb = __bfloat1622float2(hb[i]);
+          acc += fa.x * fb.x + fa.y * fb.y;
+        }
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) dots[pr] = acc;
+  }
+}
+
+static int moe_grid(int rows) {
+  int blocks = (rows + 7) / 8;
+  const int cap = 148 * 8;
+  return blocks < 1 ? 1 : (blocks > cap ? cap : blocks);
+}
+
+static bool fill_peers(MoePeers& mp, const void* const* ptrs, int world) {
+  if (world < 1 || world > kMoeMaxRanks) return false;
+  for (int r = 0; r < kMoeMaxRanks; ++r) mp.p[r] = r < world ? reinterpret_cast<const __nv_bfloat16*>(ptrs[r]) : nullptr;
+  return true;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int sb_moe_gather_rows(const void* const* src_ptrs, int world, const int* src_rank, const int* src_row,
+                                  const float* scale, void* out, int M, int H, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  MoePeers mp;
+  if (H % 8 || !fill_peers(mp, src_ptrs, world)) return -3;
+  moe_gather_rows_kernel<<<moe_grid(M), 256, 0, stream>>>(mp, src_rank, src_row, scale, (__nv_bfloat16*)out, M, H);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_moe_combine(const void* const* y_ptrs, int world, const int* pair_rank, const int* pair_slot,
+                              const float* w, void* out, int T, int k, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  MoePeers mp;
+  if (H % 8 || !fill_peers(mp, y_ptrs, world)) return -3;
+  moe_combine_kernel<<<moe_grid(T), 256, 0, stream>>>(mp, pair_rank, pair_slot, w, (__nv_bfloat16*)out, T, k, H);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_moe_pair_dot(const void* const* y_ptrs, int world, const int* pair_rank, const int* pair_slot,
+                               const void* dout, float* dots, int T, int k, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  MoePeers mp;
+  if (H % 8 || !fill_peers(mp, y_ptrs, world)) return -3;
+  moe_pair_dot_kernel<<<moe_grid(T * k), 256, 0, stream>>>(mp, pair_rank, pair_slot, (const __nv_bfloat16*)dout, dots,
+                                                          T, k, H);
+  return (int)cudaGetLastError();
+}

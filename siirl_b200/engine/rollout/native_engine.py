@@ -95,7 +95,14 @@ class BlockAllocator:
 class RolloutEngine:
     def __init__(self, model: DecoderLM, max_num_seqs: int = 256, max_model_len: int = 8192,
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, sync_interval: int = 16,
-                 use_cuda_graph: bool = True, max_num_batched_tokens: int = 8192):
+                 use_cuda_graph: bool = True, max_num_batched_tokens: int = 8192, lockstep_group=None):
+        """``lockstep_group``: ranks whose forward passes contain collectives over DIFFERENT requests (expert
+        parallelism).  They then run the same sequence of prefill / decode calls: a rank without work joins with
+        an empty prefill or an all-inactive decode step, and decode runs eagerly (the barriers of the expert
+        exchange carry a host-side epoch)."""
+        self.lockstep_group = lockstep_group
+        if lockstep_group is not None:
+            use_cuda_graph = False
         self.model = model
         self.cfg = model.cfg
         self.device = model.embed_tokens.device
@@ -273,6 +280,8 @@ class RolloutEngine:
         assert self.cache is not None, "engine is asleep: call wake_up()"
         dev = self.device
         S = min(self.max_num_seqs, max(8, (len(prompts) * sp.n + 7) // 8 * 8))
+        if self.lockstep_group is not None:
+            S = self.max_num_seqs       # every rank of the group decodes the same number of rows
         self._ensure_slots(S)
         R = sp.max_new_tokens
         waiting: List[int] = list(range(len(prompts)))[::-1]
@@ -308,7 +317,15 @@ class RolloutEngine:
             slots[slot] = None
             self.stats["generated_tokens"] += n_gen
 
-        while waiting or any(s is not None for s in slots):
+        def group_any(*flags: bool) -> List[bool]:
+            if self.lockstep_group is None:
+                return list(flags)
+            import torch.distributed as dist
+            t = torch.tensor([float(f) for f in flags], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.lockstep_group)
+            return [bool(v) for v in t.tolist()]
+
+        while group_any(bool(waiting) or any(s is not None for s in slots))[0]:
             # ---- admission: whole prompts (all n samples) while slots and blocks last ----
             free_slots = [i for i, s in enumerate(slots) if s is None]
             batch_prompts, batch_seqs, forks, ntok = [], [], [], 0
@@ -340,8 +357,15 @@ class RolloutEngine:
                 batch_prompts.append(p)
                 batch_seqs.append(group)
                 ntok += len(p)
-            if not batch_prompts and not any(s is not None for s in slots):
+            if waiting and not batch_prompts and not any(s is not None for s in slots):
                 raise MemoryError("a single request does not fit into the KV cache / slot budget")
+            any_prefill, = group_any(bool(batch_prompts))
+            if any_prefill and not batch_prompts:
+                # another rank of the lock-step group prefills: join its collectives with one unrouted token
+                one = SeqInfo([1], device=dev)
+                self.model.forward_cached(torch.zeros(1, dtype=torch.int64, device=dev), one.positions, self.cache,
+                                          self.block_table, torch.full((1,), -1, dtype=torch.int32, device=dev),
+                                          prefill_info=one)
             if batch_prompts:
                 bt = self.block_table.cpu()
                 for group in batch_seqs:
@@ -381,7 +405,7 @@ class RolloutEngine:
                     self.hit_eos[sl] = False
                 self.finished[sl] = fin
             # ---- decode until the next host check ----
-            if bool((~self.finished).any().item()):
+            if group_any(bool((~self.finished).any().item()))[0]:
                 self._run_decode_steps(self.sync_interval, sp, tokens_out, logp_out)
                 self.stats["decode_steps"] += self.sync_interval
             # ---- retire finished sequences ----

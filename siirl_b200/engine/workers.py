@@ -79,6 +79,12 @@ class _ModelWorkerBase:
 
     def _build(self, model_args, value_head: bool, trainable: bool, seed_offset: int = 0) -> None:
         mcfg = resolve_model_config(model_args, value_head)
+        ep = int(getattr(getattr(self.config, "actor", self.config).megatron, "expert_model_parallel_size", 1) or 1) \
+            if mcfg.is_moe else 1
+        if ep > 1:
+            if ep != self.world:
+                raise ValueError(f"expert_model_parallel_size={ep} must equal the worker group size {self.world}")
+            mcfg.ep_size, mcfg.ep_rank = ep, self.rank
         self.model_config = mcfg
         self.model = build_model(mcfg, dtype=self._dtype(model_args), device=self.device,
                                  seed=self.seed + seed_offset,
@@ -87,11 +93,30 @@ class _ModelWorkerBase:
         if path and not model_args.random_init and not model_args.arch_preset:
             from ..models.hf_io import load_hf_weights
             load_hf_weights(self.model, path)
-        if trainable:
+        if ep > 1:
+            self._attach_expert_parallel(model_args)
+        if trainable and ep > 1:
+            from ..parallel.flat_params import ExpertSplitStore
+            self.store = ExpertSplitStore(self.model, group=self.group, comm=self.comm)
+        elif trainable:
             self.store = FlatParamStore(self.model, group=self.group, comm=self.comm)
         else:
             for p in self.model.parameters():
                 p.requires_grad_(False)
+
+    def _attach_expert_parallel(self, model_args) -> None:
+        """One ExpertParallel context per worker (staging buffers sized for the largest packed forward); every MoE
+        layer pads its tokens to the same static bound so that ranks with different batches agree on shapes."""
+        from ..ops.moe import ExpertParallel
+        cfg = self.model_config
+        bound = int(getattr(model_args, "ep_max_tokens", 0) or 0) or 8192
+        width = max(cfg.hidden_size, 2 * cfg.moe_intermediate_size)
+        slots = self.world * bound * cfg.num_experts_per_tok + (cfg.num_experts // self.world + 1) * 128
+        ctx = ExpertParallel(self.group, self.comm if self.device.type == "cuda" else None, max_tokens=bound,
+                             hidden=width, max_slots=slots)
+        for layer in self.model.layers:
+            layer.ep, layer.ep_pad_tokens = ctx, bound
+        self.ep_ctx = ctx
 
     # ---- shared forward ---------------------------------------------------------------------------
     def _pack(self, mb: Batch) -> PackedBatch:
@@ -210,6 +235,8 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                                         gpu_memory_utilization=r.gpu_memory_utilization,
                                         use_cuda_graph=not r.enforce_eager or self.device.type == "cuda",
                                         max_num_batched_tokens=r.max_num_batched_tokens,
+                                        lockstep_group=self.group if getattr(self, "ep_ctx", None) is not None
+                                        and self.world > 1 else None,
                                         **dict(r.engine_kwargs.native or {}))
             if r.free_cache_engine:
                 self.engine.sleep()

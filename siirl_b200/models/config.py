@@ -48,6 +48,10 @@ class DecoderConfig:
     # mixture of experts (0 experts = dense)
     num_experts: int = 0
     num_experts_per_tok: int = 0
+    # expert parallelism (runtime layout, not part of the HF config): this rank hosts experts
+    # [ep_rank * num_experts / ep_size, (ep_rank + 1) * num_experts / ep_size)
+    ep_size: int = 1
+    ep_rank: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     # value head (critic / reward model): one scalar per token instead of the vocabulary head

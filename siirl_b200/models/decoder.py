@@ -28,6 +28,7 @@ class _Init:
 
     def __init__(self, seed: int, device):
         self.device = torch.device(device)
+        self.seed = seed
         self.gen = torch.Generator(device=self.device if self.device.type == "cuda" else "cpu").manual_seed(seed)
 
 
@@ -58,9 +59,15 @@ class DecoderLayer(nn.Module):
         self.post_attention_layernorm = _param((H,), dtype, device, -1, gen)
         if cfg.is_moe:
             E, I = cfg.num_experts, cfg.moe_intermediate_size
+            El = E // max(cfg.ep_size, 1)
             self.router_weight = _param((E, H), dtype, device, std, gen)
-            self.experts_gate_up = _param((E, 2 * I, H), dtype, device, std, gen)
-            self.experts_down = _param((E, H, I), dtype, device, std, gen)
+            if cfg.ep_size > 1:     # every rank draws its own experts: decorrelate the streams by expert range
+                layer_salt = int(torch.randint(0, 2 ** 30, (1,), generator=gen.gen, device=gen.gen.device).item())
+                gen = _Init(layer_salt + 7919 * (cfg.ep_rank + 1), device)
+            self.experts_gate_up = _param((El, 2 * I, H), dtype, device, std, gen)
+            self.experts_down = _param((El, H, I), dtype, device, std, gen)
+            self.ep = None          # ExpertParallel context, attached by the worker
+            self.ep_pad_tokens = 0  # static token bound all ranks pad to (0: token counts are equal already)
         else:
             I = cfg.intermediate_size
             self.gate_up_proj_weight = _param((2 * I, H), dtype, device, std, gen)
@@ -91,7 +98,8 @@ class DecoderLayer(nn.Module):
         if self.cfg.is_moe:
             from .moe import moe_forward
             return moe_forward(x, self.router_weight, self.experts_gate_up, self.experts_down,
-                               self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob)
+                               self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, ep=self.ep,
+                               pad_tokens=self.ep_pad_tokens)
         return ops.linear(ops.swiglu(ops.linear(x, self.gate_up_proj_weight)), self.down_proj_weight)
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], positions, info: SeqInfo, rope, causal=True):

@@ -14,7 +14,10 @@ from .. import ops
 
 def route_topk(x: torch.Tensor, router_weight: torch.Tensor, top_k: int, norm_topk_prob: bool):
     """Router probabilities (fp32 softmax over experts), top-k ids and weights per token."""
-    logits = ops.linear(x, router_weight).float() if x.is_cuda else F.linear(x.float(), router_weight.float())
+    if x.is_cuda and router_weight.shape[0] % 8 == 0:
+        logits = ops.linear(x, router_weight).float()
+    else:       # CPU, or an expert count the 16-byte epilogue stores cannot address
+        logits = F.linear(x.float(), router_weight.float())
     probs = torch.softmax(logits, dim=-1)
     w, idx = torch.topk(probs, top_k, dim=-1)
     if norm_topk_prob:
@@ -22,7 +25,46 @@ def route_topk(x: torch.Tensor, router_weight: torch.Tensor, top_k: int, norm_to
     return w, idx
 
 
+_LOCAL_EP = None
+
+
+def _local_ep():
+    global _LOCAL_EP
+    if _LOCAL_EP is None:
+        from ..ops.moe import ExpertParallel
+        _LOCAL_EP = ExpertParallel()
+    return _LOCAL_EP
+
+
 def moe_forward(x: torch.Tensor, router_weight: torch.Tensor, experts_gate_up: torch.Tensor,
+                experts_down: torch.Tensor, top_k: int, norm_topk_prob: bool = True, ep=None,
+                pad_tokens: int = 0) -> torch.Tensor:
+    """``x [T, H]`` -> ``[T, H]``.  ``experts_gate_up [E_local, 2I, H]``, ``experts_down [E_local, H, I]`` hold the
+    experts hosted by this rank (all of them without expert parallelism); ``router_weight [E, H]`` is replicated.
+    One dispatch (rows pulled into the expert-sorted, 128-padded layout), two grouped GEMMs around SwiGLU, one
+    combine (top-k weighted sum while pulling the rows back); with ``ep`` the pulls cross NVLink."""
+    from ..ops import moe as M
+    ep = ep if ep is not None else _local_ep()
+    T, H = x.shape
+    E = router_weight.shape[0]
+    w, idx = route_topk(x, router_weight, top_k, norm_topk_prob)
+    if ep.world > 1 and pad_tokens:
+        # ranks hold different token counts: pad to the static bound; padding rows are routed nowhere (id -1)
+        assert T <= pad_tokens, f"{T} tokens exceed the expert-parallel bound {pad_tokens}"
+        pad = pad_tokens - T
+        x = torch.cat([x, x.new_zeros(pad, H)])
+        w = torch.cat([w, w.new_zeros(pad, top_k)])
+        idx = torch.cat([idx, idx.new_full((pad, top_k), -1)])
+    all_idx = ep.all_gather(idx.to(torch.int32))
+    w_all = ep.all_gather(w.detach().float()) if ep.world > 1 else w.detach().float().unsqueeze(0)
+    layout = M.build_layout(all_idx, E, ep.world, ep.rank)
+    xs = M.dispatch(x, ep, layout)
+    hs = ops.swiglu(M.grouped_linear(xs, experts_gate_up, layout))
+    ys = M.grouped_linear(hs, experts_down, layout)
+    return M.combine(ys, w, w_all, ep, layout).to(x.dtype)[:T]
+
+
+def moe_forward_reference(x: torch.Tensor, router_weight: torch.Tensor, experts_gate_up: torch.Tensor,
                 experts_down: torch.Tensor, top_k: int, norm_topk_prob: bool = True) -> torch.Tensor:
     """``x [T, H]`` -> ``[T, H]``.  experts_gate_up ``[E, 2I, H]``, experts_down ``[E, H, I]``."""
     T, H = x.shape

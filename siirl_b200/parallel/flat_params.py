@@ -36,15 +36,24 @@ def _round_up(x: int, m: int) -> int:
 
 class FlatParamStore:
     def __init__(self, module: nn.Module, group: Optional[dist.ProcessGroup] = None, comm=None,
-                 optimizer_state: bool = True):
-        params = [(n, p) for n, p in module.named_parameters()]
+                 optimizer_state: bool = True, param_filter=None, local_only: bool = False,
+                 grad_scale: Optional[float] = None):
+        """``param_filter(name) -> bool`` restricts the store to some parameters.  ``local_only`` makes a store
+        whose parameters exist on this rank alone (expert-parallel experts): no reduce-scatter / all-gather, the
+        whole state lives here, ``grad_scale`` (1 / data-parallel width) keeps their update on the same loss
+        scale as the replicated parameters, and the clipping norm comes from the caller (``global_sumsq``)."""
+        params = [(n, p) for n, p in module.named_parameters() if param_filter is None or param_filter(n)]
         if not params:
             raise ValueError("module has no parameters")
         self.module = module
-        self.group = group
-        self.comm = comm  # optional peer-memory communicator (siirl_b200.parallel.symm.SymmComm)
+        self.group = group if not local_only else None
+        self.comm = comm if not local_only else None  # peer-memory communicator (siirl_b200.parallel.symm.SymmComm)
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
+        self.local_only = local_only
+        self.grad_scale = grad_scale
+        if local_only:
+            self.world, self.rank = 1, 0
         first = params[0][1]
         self.device, self.dtype = first.device, first.dtype
         self.names: List[str] = []
@@ -59,7 +68,7 @@ class FlatParamStore:
         self.shard_size = self.total // self.world
         self.lo, self.hi = self.rank * self.shard_size, (self.rank + 1) * self.shard_size
 
-        alloc = comm.alloc if (comm is not None and self.device.type == "cuda") else (
+        alloc = self.comm.alloc if (self.comm is not None and self.device.type == "cuda") else (
             lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
         self.flat_param = alloc(self.total, self.dtype)
         self.flat_grad = alloc(self.total, torch.float32)
@@ -103,17 +112,32 @@ class FlatParamStore:
                 p.grad = None
 
     # ---- optimizer step -----------------------------------------------------------------------
+    def local_sumsq(self) -> torch.Tensor:
+        """Sum of squares of this store's (unscaled) gradients, 1-element fp32 tensor."""
+        self.collect_grads()
+        out = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if self.device.type == "cuda":
+            L = _lib.get_lib()
+            _lib.check(L.sb_sumsq_accumulate(_lib.ptr(self.flat_grad), ctypes.c_longlong(self.flat_grad.numel()),
+                                             _lib.ptr(out), _lib.stream()), "sb_sumsq_accumulate")
+        else:
+            out += self.flat_grad.double().pow(2).sum().float()
+        return out
+
     def step(self, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
-             max_grad_norm: float = 1.0) -> torch.Tensor:
+             max_grad_norm: float = 1.0, extra_sumsq: Optional[torch.Tensor] = None,
+             global_sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One AdamW step on the owned shard; returns the global gradient norm (0-d tensor, no host sync).
-        A non-finite norm leaves parameters and moments untouched."""
+        A non-finite norm leaves parameters and moments untouched.  ``extra_sumsq`` (this rank's share of
+        gradients held by another store) is added to the squared norm before the ranks sum it;
+        ``global_sumsq`` replaces the norm computation altogether (stores of rank-local parameters)."""
         assert self.master is not None, "store was built without optimizer state"
         self.collect_grads()
         self.step_count += 1
         if self.world > 1 and self.comm is not None and self.device.type == "cuda":
-            norm = self.comm.fused_rs_adamw_ag(self, lr, betas, eps, weight_decay, max_grad_norm)
+            norm = self.comm.fused_rs_adamw_ag(self, lr, betas, eps, weight_decay, max_grad_norm, extra_sumsq)
             return norm
-        grad_scale = 1.0 / self.world
+        grad_scale = self.grad_scale if self.grad_scale is not None else 1.0 / self.world
         if self.world > 1:
             shard_grad = self._reduce_scatter()
         else:
@@ -125,8 +149,12 @@ class FlatParamStore:
                                              _lib.ptr(self._sumsq), _lib.stream()), "sb_sumsq_accumulate")
         else:
             self._sumsq += shard_grad.double().pow(2).sum().float()
+        if extra_sumsq is not None:
+            self._sumsq += extra_sumsq
         if self.world > 1:
             dist.all_reduce(self._sumsq, group=self.group)
+        if global_sumsq is not None:
+            self._sumsq.copy_(global_sumsq)
         if self.device.type == "cuda":
             L = _lib.get_lib()
             f = ctypes.c_float
@@ -244,3 +272,32 @@ def lr_at_step(optim_cfg, step: int, total_steps: int) -> float:
         d = (prog - stable_end) / (1 - stable_end)
         return base * (min_ratio + (1 - min_ratio) * 0.5 * (1 + math.cos(math.pi * d)))
     return base
+
+
+class ExpertSplitStore:
+    """Optimizer store of an expert-parallel model: replicated (dense) parameters in a sharded-state
+    :class:`FlatParamStore` over the data-parallel group, this rank's experts in a rank-local store.  One gradient
+    norm over both clips both.  Attribute access falls through to the dense store, so code written against
+    ``FlatParamStore`` (checkpointing, tests) keeps working; the expert store is ``.expert``."""
+
+    def __init__(self, module: nn.Module, group=None, comm=None, is_expert=lambda n: ".experts_" in n):
+        world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+        self.dense = FlatParamStore(module, group, comm, param_filter=lambda n: not is_expert(n))
+        self.expert = FlatParamStore(module, None, None, param_filter=is_expert, local_only=True,
+                                     grad_scale=1.0 / world)
+
+    def __getattr__(self, name):
+        return getattr(self.__dict__["dense"], name)
+
+    def zero_grad(self) -> None:
+        self.dense.zero_grad()
+        self.expert.zero_grad()
+
+    def step(self, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
+             max_grad_norm: float = 1.0) -> torch.Tensor:
+        es = self.expert.local_sumsq()
+        norm = self.dense.step(lr, betas, eps, weight_decay, max_grad_norm, extra_sumsq=es)
+        d = self.dense
+        total = d.comm._sumsq if (d.world > 1 and d.comm is not None and d.device.type == "cuda") else d._sumsq
+        self.expert.step(lr, betas, eps, weight_decay, max_grad_norm, global_sumsq=total)
+        return norm

@@ -119,7 +119,7 @@ class SymmComm:
 
     # ---- fused optimizer step ---------------------------------------------------------------------------
     def fused_rs_adamw_ag(self, store, lr: float, betas, eps: float, weight_decay: float,
-                          max_grad_norm: float) -> torch.Tensor:
+                          max_grad_norm: float, extra_sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
         grads, params = self.peers_of(store.flat_grad), self.peers_of(store.flat_param)
         if self._shard_grad is None or self._shard_grad.numel() != store.shard_size:
             self._shard_grad = torch.empty(store.shard_size, dtype=torch.float32, device=self.device)
@@ -129,6 +129,8 @@ class SymmComm:
         _lib.check(self.L.sb_rs_reduce(grads.ptr_array, self.world, self.rank, ll(store.lo), ll(store.shard_size),
                                        _lib.ptr(self._shard_grad), _lib.ptr(self._sumsq), _lib.stream()),
                    "sb_rs_reduce")
+        if extra_sumsq is not None:
+            self._sumsq += extra_sumsq
         dist.all_reduce(self._sumsq, group=self.group)  # 4 bytes; also orders "all peers have read my gradients"
         _lib.check(self.L.sb_adamw_allgather(
             _lib.ptr(store.master), _lib.ptr(store.exp_avg), _lib.ptr(store.exp_avg_sq), _lib.ptr(self._shard_grad),

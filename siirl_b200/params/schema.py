@@ -108,6 +108,7 @@ class ModelArguments(ProcessorArguments):
     trust_remote_code: bool = False
     hf_hub_token: Optional[str] = None
     use_fast_tokenizer: bool = True
+    ep_max_tokens: int = 0      # expert parallelism: static per-rank token bound of one forward (0: 8192)
     split_special_tokens: bool = False
     model_max_length: Optional[int] = None
     new_special_tokens: Optional[str] = None

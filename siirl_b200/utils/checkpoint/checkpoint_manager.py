@@ -93,6 +93,10 @@ class ShardedCheckpointManager:
                 _atomic_save({"flat": st.flat_param[st.lo:st.hi].detach().cpu(), "lo": st.lo, "hi": st.hi}, mpath)
             if "optimizer" in self.contents and st.master is not None:
                 _atomic_save(st.shard_state_dict(), opath)
+            ex = getattr(st, "expert", None)
+            if ex is not None:      # this rank's experts (expert parallelism): parameters + full local state
+                _atomic_save({"flat": ex.flat_param.detach().cpu(), "state": ex.shard_state_dict()},
+                             os.path.join(directory, f"experts_world_size_{self.world}_rank_{self.rank}.pt"))
         elif "model" in self.contents and self.rank == 0:
             _atomic_save({"state_dict": {k: v.detach().cpu() for k, v in self.model.state_dict().items()}}, mpath)
         if "extra" in self.contents:
@@ -123,6 +127,14 @@ class ShardedCheckpointManager:
         saved_world = manifest["world_size"]
         st = self.store
         mpath, opath, epath = self._names(directory)
+        ex = getattr(st, "expert", None)
+        if ex is not None:
+            if saved_world != self.world:
+                raise ValueError("an expert-parallel checkpoint resumes only on the expert-parallel width that wrote it")
+            e = torch.load(os.path.join(directory, f"experts_world_size_{self.world}_rank_{self.rank}.pt"),
+                           map_location="cpu", weights_only=False)
+            ex.flat_param.copy_(e["flat"].to(ex.device))
+            ex.load_shard_state_dict(e["state"])
         if st is not None:
             if saved_world == self.world and os.path.exists(mpath):
                 m = torch.load(mpath, map_location="cpu", weights_only=False)

@@ -1,0 +1,76 @@
+"""Body of the expert-parallel MoE check, one process per rank (torchrun env).  Every rank holds different tokens
+and E/world experts; output and gradients must equal the single-rank computation with all experts.
+``EP_DEVICE=cpu`` uses gloo (rows move by all_gather), ``EP_DEVICE=cuda`` NCCL + the peer-memory kernels."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from siirl_b200.models.moe import moe_forward, moe_forward_reference  # noqa: E402
+from siirl_b200.ops.moe import ExpertParallel  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    cuda = os.environ.get("EP_DEVICE", "cpu") == "cuda"
+    T, H, I, E, k = 200, 128, 64, 8, 2
+    if cuda:
+        torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+        dist.init_process_group("nccl")
+        dev = torch.device("cuda", torch.cuda.current_device())
+        from siirl_b200.ops import lib
+        from siirl_b200.parallel.symm import SymmComm
+        comm = SymmComm.create(dist.group.WORLD)
+        ep = ExpertParallel(dist.group.WORLD, comm, max_tokens=T, hidden=max(H, 2 * I),
+                            max_slots=world * T * k + (E // world) * 128 + 128)
+        dtype = torch.bfloat16
+    else:
+        dist.init_process_group("gloo")
+        dev, dtype = torch.device("cpu"), torch.float32
+        ep = ExpertParallel(dist.group.WORLD, None)
+    g = torch.Generator().manual_seed(11)
+    rw = (0.5 * torch.randn(E, H, generator=g))
+    gu = (0.1 * torch.randn(E, 2 * I, H, generator=g))
+    dn = (0.1 * torch.randn(E, H, I, generator=g))
+    xs_all = [torch.randn(T, H, generator=g) for _ in range(world)]
+    gout_all = [torch.randn(T, H, generator=g) for _ in range(world)]
+    El = E // world
+    x = xs_all[rank].to(dev, dtype).requires_grad_()
+    gu_l = gu[rank * El:(rank + 1) * El].to(dev, dtype).requires_grad_()
+    dn_l = dn[rank * El:(rank + 1) * El].to(dev, dtype).requires_grad_()
+    y = moe_forward(x, rw.to(dev, dtype), gu_l, dn_l, k, True, ep=ep)
+    y.backward(gout_all[rank].to(dev, dtype))
+    # oracle: all tokens of all ranks through all experts on the CPU in fp32 (bf16-rounded inputs on the GPU arm)
+    rd = (lambda t: t.to(dtype).float()) if cuda else (lambda t: t)
+    xo = [rd(t).requires_grad_() for t in xs_all]
+    guo, dno = rd(gu).requires_grad_(), rd(dn).requires_grad_()
+    for r in range(world):
+        yo = moe_forward_reference(xo[r], rd(rw), guo, dno, k, True)
+        yo.backward(rd(gout_all[r]))
+        if r == rank:
+            y_want = yo.detach()
+    tol = 0.08 if cuda else 1e-4
+
+    def close(a, b, what):
+        err = (a.float().cpu() - b).abs().max().item()
+        scale = b.abs().max().item() + 1e-6
+        assert err <= tol * max(1.0, scale), f"{what}: err {err} (scale {scale})"
+
+    close(y, y_want, "output")
+    close(x.grad, xo[rank].grad, "dx")
+    close(gu_l.grad, guo.grad[rank * El:(rank + 1) * El], "d gate_up")
+    close(dn_l.grad, dno.grad[rank * El:(rank + 1) * El], "d down")
+    if cuda:
+        torch.cuda.synchronize()
+        lib.check_status()
+    dist.barrier()
+    if rank == 0:
+        print("EP_OK")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -65,3 +65,19 @@ def test_injected_rank_failure_stops_the_job(tmp_path):
                timeout=600)
     assert out.returncode == 17
     assert not (tmp_path / "c" / "latest_checkpointed_iteration.txt").exists()
+
+
+def test_moe_expert_parallel_two_ranks(tmp_path):
+    """Qwen3-MoE-style tiny model, experts split over two gloo ranks: dispatch / combine across ranks in training,
+    scoring and the lock-step rollout; the dense part in the sharded-state store, the experts in a rank-local one."""
+    out = _run(["actor_rollout_ref.model.arch_preset=tiny-moe", "actor_rollout_ref.model.ep_max_tokens=512",
+                "actor_rollout_ref.actor.megatron.expert_model_parallel_size=2", "data.max_response_length=16",
+                "actor_rollout_ref.rollout.n=2", "actor_rollout_ref.rollout.max_num_seqs=16",
+                "actor_rollout_ref.actor.use_kl_loss=False", f"trainer.default_local_dir={tmp_path / 'c'}",
+                "trainer.total_training_steps=2", "trainer.save_freq=2"], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    assert all(r["actor/grad_norm"] > 0 for r in m)
+    d = tmp_path / "c" / "global_step_2" / "actor_agent_0"
+    assert (d / "experts_world_size_2_rank_0.pt").exists() and (d / "experts_world_size_2_rank_1.pt").exists()

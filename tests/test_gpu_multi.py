@@ -29,3 +29,14 @@ def test_fused_gemm_allreduce_and_tp_engine():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_OK" in out.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_expert_parallel_dispatch_combine():
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, EP_DEVICE="cuda", NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29547", os.path.join(here, "ep_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "EP_OK" in out.stdout

@@ -12,3 +12,13 @@ def test_tensor_parallel_two_cpu_ranks():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_OK" in out.stdout
+
+
+def test_expert_parallel_two_cpu_ranks():
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, EP_DEVICE="cpu", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29545", os.path.join(here, "ep_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "EP_OK" in out.stdout
