@@ -100,9 +100,38 @@ def bench_gemm_ar(comm):
     _ = rank
 
 
+def bench_ag_gemm(comm):
+    from .. import ops
+    from ..parallel.ag_gemm import AgLinear
+    world, rank = dist.get_world_size(), dist.get_rank()
+    pk = peaks()
+    for M, N, K, what in ((8192, 18944 * 2 // 256 // world * 256 * world, 3584, "gate_up (weights sharded by rows)"),
+                          (8192, 3584 // (256 * world) * 256 * world, 18944, "down_proj (weights sharded by rows)")):
+        ag = AgLinear(dist.group.WORLD, comm, N, K)
+        ag.load_shard((0.02 * torch.randn(ag.rows, K, device="cuda")).to(torch.bfloat16))
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        fused = timeit(lambda: ag(x))
+        full = torch.empty(N * K, device="cuda", dtype=torch.bfloat16)
+
+        def lib_path():
+            dist.all_gather_into_tensor(full, ag.shard.reshape(-1))
+            return ops.linear(x, full.view(N, K))
+
+        nccl = timeit(lib_path)
+        flops = 2.0 * M * N * K
+        link = (world - 1) / world * N * K * 2
+        target = max(flops / pk["tflops"] / 1e9, link / NVLINK_GBS / 1e6)
+        emit(case="all_gather+gemm", shape=what, M=M, N=N, K=K, world=world, fused_ms=round(fused, 4),
+             nccl_all_gather_plus_gemm_ms=round(nccl, 4), speedup=round(nccl / fused, 3),
+             roofline_ms=round(target, 4), frac_of_roofline=round(target / fused, 3))
+        del ag, full
+        torch.cuda.empty_cache()
+    _ = rank
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="all", choices=["all", "optimizer", "gemm_ar"])
+    ap.add_argument("--case", default="all", choices=["all", "optimizer", "gemm_ar", "ag_gemm"])
     ap.add_argument("--numel", type=float, default=1e9)
     a = ap.parse_args()
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
@@ -113,6 +142,8 @@ def main():
     emit(peaks=peaks(), world=dist.get_world_size(), nvlink_gbs_per_direction=NVLINK_GBS)
     if a.case in ("all", "gemm_ar"):
         bench_gemm_ar(comm)
+    if a.case in ("all", "ag_gemm"):
+        bench_ag_gemm(comm)
     if a.case in ("all", "optimizer"):
         n = int(a.numel) // (8 * dist.get_world_size()) * (8 * dist.get_world_size())
         bench_optimizer(comm, n)

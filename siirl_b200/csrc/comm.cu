@@ -211,6 +211,48 @@ extern "C" int sb_adamw_allgather(float* master, float* m, float* v, const float
   return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------
+// strided block pull: the two all-to-alls of Ulysses sequence parallelism (sequence shard <-> head shard) as one
+// launch each.  A block copies `rows` rows of `col_bytes` bytes from a peer's matrix into the local one; pitches
+// and offsets are bytes, all multiples of 16.
+// ---------------------------------------------------------------------------------------
+struct PullBlock {
+  long long src_off, dst_off;       // byte offset of the block's first element
+  long long src_pitch, dst_pitch;   // row pitches in bytes
+  int rows, col_bytes, src_rank, pad;
+};
+constexpr int kMaxPullBlocks = 64;
+struct PullBlocks {
+  PullBlock b[kMaxPullBlocks];
+};
+
+__global__ void block_pull_kernel(PeerPtrs bases, PullBlocks blocks, int n_blocks, unsigned char* __restrict__ out) {
+  const PullBlock& blk = blocks.b[blockIdx.y];
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(bases.p[blk.src_rank]) + blk.src_off;
+  unsigned char* dst = out + blk.dst_off;
+  const int vec_per_row = blk.col_bytes / 16;
+  const long long total = (long long)blk.rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / vec_per_row;
+    const int v = (int)(i % vec_per_row);
+    *reinterpret_cast<uint4*>(dst + r * blk.dst_pitch + v * 16) =
+        *reinterpret_cast<const uint4*>(src + r * blk.src_pitch + v * 16);
+  }
+}
+
+// blocks: host array of n_blocks PullBlock (48 bytes each)
+extern "C" int sb_block_pull(void* const* bases, int world, const void* blocks, int n_blocks, void* out,
+                             cudaStream_t stream) {
+  if (world > kMaxRanks || n_blocks > kMaxPullBlocks) return -3;
+  if (n_blocks == 0) return 0;
+  PullBlocks pb;
+  memcpy(pb.b, blocks, sizeof(PullBlock) * n_blocks);
+  dim3 grid(148 * 4 / n_blocks > 0 ? 148 * 4 / n_blocks : 1, n_blocks);
+  block_pull_kernel<<<grid, 256, 0, stream>>>(to_peers(bases, world), pb, n_blocks, reinterpret_cast<unsigned char*>(out));
+  return (int)cudaGetLastError();
+}
+
 // segs: device array of {src_off, dst_off, bytes, src_rank, pad} (32 bytes each); all offsets / sizes multiples of 16
 extern "C" int sb_segment_pull(void* const* bases, int world, const void* segs, int n_segs, void* out,
                                cudaStream_t stream) {

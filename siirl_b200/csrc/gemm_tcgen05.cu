@@ -46,6 +46,23 @@ struct GemmParams {
   long long b_group_rows;
   const int* group_rows;
   long long c_group_stride;
+  const struct AgParams* ag;  // all-gather of B fused into the GEMM (device memory), or nullptr
+  int ag_copiers;             // number of copier CTAs (== ag->copiers), 0 without ag
+};
+
+// all-gather -> GEMM in one launch: B [N, K] is sharded by rows over the ranks (rows_per_rank each, in symmetric
+// memory).  The first `copiers` CTAs pull the shards chunk by chunk (one chunk = one BN-row n-block) from the peers
+// into the local `staging` copy of B with plain peer loads and count each finished chunk in flags[chunk]; the other
+// CTAs run the tcgen05 GEMM on `staging`, their TMA producers waiting (bounded) for a chunk's count before its
+// first load.  Tiles and chunks start at this rank's own shard, so the math on local rows hides the first transfers.
+constexpr int kAgMaxRanks = 16;
+struct AgParams {
+  const __nv_bfloat16* shard[kAgMaxRanks];  // every rank's shard [rows_per_rank, K], row pitch ld
+  __nv_bfloat16* staging;                   // local [N, K], row pitch ld
+  int* flags;                               // [num_n_blocks] arrival counters (monotonic over launches)
+  int* local;                               // [0] epoch, [1] exit counter
+  long long ld;
+  int world, rank, rows_per_rank, copiers;
 };
 
 struct TileInfo {
@@ -97,8 +114,7 @@ struct GemmSmem {
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int num_m_blocks, int num_n_blocks, int& mb,
-                                            int& nb) {
-  constexpr int kGroupM = 8;
+                                            int& nb, int kGroupM = 8) {
   const int tiles_per_group = kGroupM * num_n_blocks;
   const int group = tile / tiles_per_group;
   const int first_m = group * kGroupM;
@@ -113,7 +129,12 @@ __device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int tile, int
   TileInfo t;
   int mb, nb;
   const int outer = tile / tiles_mn;  // k-split index, or group index when group_rows is set
-  tile_coords(tile - outer * tiles_mn, p.num_m_blocks, p.num_n_blocks, mb, nb);
+  // all-gather mode sweeps more m-blocks per n-block, so that later chunks of B are needed later
+  tile_coords(tile - outer * tiles_mn, p.num_m_blocks, p.num_n_blocks, mb, nb, p.ag ? 32 : 8);
+  if (p.ag) {  // start at the n-blocks of this rank's own shard
+    const int first = (p.ag->rank * p.ag->rows_per_rank) / BN;
+    nb = (nb + first) % p.num_n_blocks;
+  }
   t.m0 = mb * kBM;
   t.n0 = nb * BN;
   t.b_off = 0;
@@ -136,6 +157,75 @@ __device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int tile, int
   return t;
 }
 
+// Copier CTA of the all-gather -> GEMM kernel.  One thread drives bulk asynchronous copies (the TMA engine, without
+// multicast): each n-block chunk of B is one contiguous byte range (row pitch == K) in the owner's shard and in the
+// local staging matrix; pieces of kAgPiece bytes bounce through a ring of shared-memory stages, so a CTA keeps
+// (stages - 1) * kAgPiece bytes in flight over NVLink with no registers involved.  Chunk c belongs to copier
+// c % copiers.  After a chunk's stores have completed the chunk is counted in flags[c].
+constexpr int kAgPiece = 32768;
+
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
+}
+
+template <int BN, int STAGES_BYTES>
+__device__ __forceinline__ void ag_copier(const GemmParams& p, uint8_t* smem, uint64_t* bars, int nbars) {
+  if (threadIdx.x != 0) return;
+  const AgParams& ag = *p.ag;
+  const int nblk = p.num_n_blocks;
+  const int first = (ag.rank * ag.rows_per_rank) / BN;
+  constexpr int kStages = STAGES_BYTES / kAgPiece < 6 ? STAGES_BYTES / kAgPiece : 6;
+  const int S = kStages < nbars ? kStages : nbars;
+  uint32_t phase_bits = 0;  // parity of each stage's barrier
+  bool ok = true;
+  for (int i = blockIdx.x; i < nblk && ok; i += ag.copiers) {
+    const int nb = (first + i) % nblk;
+    const int r0 = nb * BN;
+    const int rows = min(BN, p.N - r0);
+    const int owner = r0 / ag.rows_per_rank;  // rows_per_rank is a multiple of BN: one owner per chunk
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(ag.shard[owner] + (long long)(r0 - owner * ag.rows_per_rank) * ag.ld);
+    uint8_t* dst = reinterpret_cast<uint8_t*>(ag.staging + (long long)r0 * ag.ld);
+    const long long bytes = (long long)rows * ag.ld * 2;
+    const int pieces = (int)((bytes + kAgPiece - 1) / kAgPiece);
+    // software pipeline: loads run S-1 pieces ahead of the stores
+    for (int j = 0; j < pieces + S - 1 && ok; ++j) {
+      if (j < pieces) {
+        const int st = j % S;
+        if (j >= S) tma_store_wait_read<0>();  // the store that last used this stage has read it
+        const uint32_t n = (uint32_t)min((long long)kAgPiece, bytes - (long long)j * kAgPiece);
+        mbar_arrive_expect_tx(&bars[st], n);
+        bulk_g2s(smem + st * kAgPiece, src + (long long)j * kAgPiece, n, &bars[st]);
+      }
+      const int k = j - (S - 1);
+      if (k >= 0 && k < pieces) {
+        const int st = k % S;
+        if (!mbar_wait(&bars[st], (phase_bits >> st) & 1u, p.status, kStatusTimeoutProducer)) {
+          ok = false;
+          break;
+        }
+        phase_bits ^= 1u << st;
+        const uint32_t n = (uint32_t)min((long long)kAgPiece, bytes - (long long)k * kAgPiece);
+        bulk_s2g(dst + (long long)k * kAgPiece, smem + st * kAgPiece, n);
+        tma_store_commit();
+      }
+    }
+    tma_store_wait<0>();  // all stores of the chunk have completed
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence();
+    if (ok) flag_add_release(ag.flags + nb, 1);
+  }
+  tma_store_wait<0>();
+}
+
 #include "gemm_ar.cuh"
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
@@ -154,6 +244,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int tiles_mn = p.num_m_blocks * p.num_n_blocks;
+  const int copiers = p.ag_copiers;
+  const bool is_copier = (int)blockIdx.x < copiers;
+  const int cta0 = (int)blockIdx.x - copiers;       // index among the GEMM CTAs
+  const int nctas = (int)gridDim.x - copiers;
+  const int ag_epoch = p.ag ? p.ag->local[0] + 1 : 0;
   const int num_tiles = tiles_mn * p.k_splits;  // k_splits holds the group count when group_rows is set
   constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512 (power of two)
 
@@ -179,7 +274,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (is_copier) {
+    ag_copier<BN, L::kBarrierOffset>(p, smem, full_bar, STAGES);
+  } else if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int stage = 0;
@@ -188,10 +285,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
       for (int s = 0; s < STAGES; ++s) last_armed[s] = -1;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta0; tile < num_tiles && ok; tile += nctas) {
         const TileInfo ti = tile_info<BN>(p, tile, tiles_mn);
         if (ti.skip) continue;
         const int m0 = ti.m0, n0 = ti.n0, kb0 = ti.kb0, kb1 = ti.kb1;
+        if (p.ag) {
+          // the n-block's rows must have landed in the staging copy (written by copier CTAs through the generic
+          // proxy, read below by TMA through the async proxy)
+          if (!flag_wait_ge(p.ag->flags + n0 / BN, ag_epoch, p.status)) {
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kStatusTimeoutProducer)) {
             ok = false;
@@ -235,7 +341,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = cta0; tile < num_tiles && ok; tile += nctas) {
       const TileInfo ti = tile_info<BN>(p, tile, tiles_mn);
       if (ti.skip) continue;
       if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusTimeoutMma)) {
@@ -295,7 +401,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       if (epi_tid == 0) ar_smem[1] = 0;
       epi_bar();
     }
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    for (int tile = cta0; tile < num_tiles; tile += nctas) {
       const TileInfo ti = tile_info<BN>(p, tile, tiles_mn);
       if (ti.skip) continue;
       const int ks = tile / tiles_mn;
@@ -381,7 +487,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       // next launch may overwrite `partial`
       if (epi_tid == 0) {
         int it = 0;
-        for (int tile = blockIdx.x; tile < num_tiles && it < 64; tile += gridDim.x, ++it) {
+        for (int tile = cta0; tile < num_tiles && it < 64; tile += nctas, ++it) {
           if (!((ar_pending >> it) & 1ull) || !ar_ok) continue;
           const int tile_mn = tile % tiles_mn;
           if (!flag_wait_ge(p.ar->done[p.ar->rank] + tile_mn, ar_epoch, p.status)) ar_ok = false;
@@ -395,6 +501,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (p.ag && threadIdx.x == 0) {
+    __threadfence();
+    const int prev = atomicAdd(&p.ag->local[1], 1);
+    if (prev == (int)gridDim.x - 1) {
+      p.ag->local[1] = 0;
+      p.ag->local[0] = ag_epoch;
+    }
   }
   if constexpr (EPI == EPI_F32_AR) {
     if (threadIdx.x == 64) {  // an epilogue thread: it knows the epoch
@@ -467,8 +581,10 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     configured = true;
   }
   const int tiles = p.num_m_blocks * p.num_n_blocks * p.k_splits;
-  int grid = tiles < num_sms() ? tiles : num_sms();
+  const int avail = num_sms() - p.ag_copiers;
+  int grid = tiles < avail ? tiles : avail;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  grid += p.ag_copiers;
   kernel<<<grid, 192, L::kTotalBytes, stream>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }
@@ -556,7 +672,7 @@ struct GroupArgs {
 static int gemm_impl(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                      long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
                      int k_splits, long long slab_stride, const ArParams* ar, int* status, cudaStream_t stream,
-                     const GroupArgs* grp = nullptr) {
+                     const GroupArgs* grp = nullptr, const AgParams* ag = nullptr, int ag_copiers = 0) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row pitches; the epilogue stores whole 16-byte groups of a row
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return -3;
@@ -603,6 +719,8 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, in
   if (k_splits > 1 && epi != EPI_F32 && epi != EPI_F32_AR) return -2;  // split-K writes fp32 slabs
   if (k_splits > p.num_k_blocks) k_splits = p.num_k_blocks;
   p.ar = ar;
+  p.ag = ag;
+  p.ag_copiers = ag ? ag_copiers : 0;
   p.tile_group = nullptr;
   p.group_rows = nullptr;
   p.b_group_rows = 0;
@@ -654,6 +772,18 @@ extern "C" int sb_gemm_grouped_bf16(const void* A, const void* B, void* C, int M
   if ((!tile_group) == (!group_rows) || num_groups < 1) return -3;
   return gemm_impl(A, B, C, nullptr, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, tile_n, 0, 1, 0, nullptr, status, stream,
                    &g);
+}
+
+// C[M, N] = A[M, K] * B[N, K]^T (+ bias) where B is sharded by rows over the ranks: the launch gathers B into
+// `staging` (local [N, K], row pitch ld) while it multiplies.  `ag_params` is an AgParams struct in device memory.
+// a_mn/b_mn = 0 (forward layout); with b_mn = 1 the staging matrix is read as [N (contraction), K] (dgrad layout:
+// C[M, K] = A[M, N] * B[N, K], chunks along the contraction) -- not offered: the forward layout is the only user.
+extern "C" int sb_ag_gemm_bf16(const void* A, const void* staging, void* C, const void* bias, int M, int N, int K,
+                               long long lda, long long ld, long long ldc, const void* ag_params, int copiers,
+                               int tile_n, int* status, cudaStream_t stream) {
+  if (copiers < 1 || copiers > 64 || (K % 8)) return -3;
+  return gemm_impl(A, staging, C, bias, M, N, K, lda, ld, ldc, 0, 0, EPI_BF16, tile_n == 256 ? 256 : 128, 0, 1, 0,
+                   nullptr, status, stream, nullptr, reinterpret_cast<const AgParams*>(ag_params), copiers);
 }
 
 // out[q] = bf16(sum_r A_r[M, K_r] * B_r[N, K_r]^T + bias) on every rank q of the tensor-parallel group, one launch

@@ -27,6 +27,10 @@ int sb_moe_combine(const void* const* y_ptrs, int world, const int* pair_rank, c
                    void* out, int T, int k, int H, cudaStream_t stream);
 int sb_moe_pair_dot(const void* const* y_ptrs, int world, const int* pair_rank, const int* pair_slot, const void* dout,
                     float* dots, int T, int k, int H, cudaStream_t stream);
+int sb_ag_gemm_bf16(const void* A, const void* staging, void* C, const void* bias, int M, int N, int K, long long lda,
+                    long long ld, long long ldc, const void* ag_params, int copiers, int tile_n, int* status,
+                    cudaStream_t stream);
+int sb_block_pull(void* const* bases, int world, const void* blocks, int n_blocks, void* out, cudaStream_t stream);
 int sb_gemm_grouped_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda, long long ldb,
                          long long ldc, int a_mn, int b_mn, int epi, int tile_n, const int* tile_group,
                          long long b_group_rows, const int* group_rows, int num_groups, long long c_group_stride,

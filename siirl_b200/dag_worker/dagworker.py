@@ -149,6 +149,11 @@ class DAGWorker:
         tp = 1
         if node.node_role == NodeRole.ROLLOUT:
             tp = max(1, self.config.actor_rollout_ref.rollout.tensor_model_parallel_size)
+        elif node.node_role in (NodeRole.ACTOR, NodeRole.REFERENCE):
+            # Ulysses peers work on the same micro-batches
+            tp = max(1, self.config.actor_rollout_ref.actor.ulysses_sequence_parallel_size)
+        elif node.node_role == NodeRole.CRITIC:
+            tp = max(1, self.config.critic.ulysses_sequence_parallel_size)
         dp = max(1, gw // tp)
         return dp, gr // tp, gr % tp, tp
 

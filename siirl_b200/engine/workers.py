@@ -53,6 +53,28 @@ def _micro_batches(batch: Batch, micro_bs: Optional[int], use_dynamic: bool, max
     return [(p, batch.select_idxs(p)) for p in parts]
 
 
+class _GroupSum(torch.autograd.Function):
+    """Sum over a process group whose backward is the same sum (all ranks evaluate the same function of the
+    result)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        y = x.clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        g = dy.clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+def _group_sum(x: torch.Tensor, group) -> torch.Tensor:
+    return _GroupSum.apply(x, group)
+
+
 class _ModelWorkerBase:
     def __init__(self, config, role: str, process_group=None, device: Optional[torch.device] = None, comm=None,
                  seed: int = 1):
@@ -95,6 +117,7 @@ class _ModelWorkerBase:
             load_hf_weights(self.model, path)
         if ep > 1:
             self._attach_expert_parallel(model_args)
+        self._attach_sequence_parallel(self.model)
         if trainable and ep > 1:
             from ..parallel.flat_params import ExpertSplitStore
             self.store = ExpertSplitStore(self.model, group=self.group, comm=self.comm)
@@ -103,6 +126,37 @@ class _ModelWorkerBase:
         else:
             for p in self.model.parameters():
                 p.requires_grad_(False)
+
+    def _attach_sequence_parallel(self, model) -> None:
+        """Ulysses groups are consecutive blocks of ``ulysses_sequence_parallel_size`` ranks of the worker's group;
+        every rank creates all of them in the same order (``new_group`` is collective)."""
+        cfgs = getattr(self.config, "actor", self.config)
+        n = int(getattr(cfgs, "ulysses_sequence_parallel_size", 1) or 1)
+        if n <= 1 or self.world <= 1:
+            return
+        if getattr(self, "_sp_ctx", None) is None:
+            from ..parallel.ulysses import UlyssesSP
+            mc = self.model_config
+            if self.world % n or mc.num_heads % n or mc.num_kv_heads % n:
+                raise ValueError(f"ulysses_sequence_parallel_size={n} must divide the group size {self.world} and the "
+                                 f"head counts {mc.num_heads}/{mc.num_kv_heads}")
+            ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
+            mine = None
+            for b in range(self.world // n):
+                g = dist.new_group(ranks[b * n:(b + 1) * n])
+                if b == self.rank // n:
+                    mine = g
+            comm = None
+            if self.device.type == "cuda":
+                from ..parallel.symm import SymmComm
+                comm = SymmComm.create(mine)
+            r = getattr(self.config, "rollout", None)
+            seq = ((r.prompt_length or 512) + (r.response_length or 512)) if r is not None else 4096
+            tokens = max(int(getattr(cfgs, "ppo_max_token_len_per_gpu", 0) or 0),
+                         int(getattr(cfgs, "ppo_micro_batch_size_per_gpu", 0) or 1) * seq, seq)
+            width = (mc.num_heads + 2 * mc.num_kv_heads) * mc.head_dim
+            self._sp_ctx = UlyssesSP(mine, comm, max_elems=(tokens // n + n) * width)
+        model.attach_sequence_parallel(self._sp_ctx)
 
     def _attach_expert_parallel(self, model_args) -> None:
         """One ExpertParallel context per worker (staging buffers sized for the largest packed forward); every MoE
@@ -136,6 +190,23 @@ class _ModelWorkerBase:
             positions = torch.cat([proc.rope_layout(n)[0] for n in pk.info.seqlens], 1).to(self.device)
         hidden = model.forward_hidden(pk.input_ids, positions, pk.info, **mm)
         from ..ops.lm_head import lm_head_logprob_entropy
+        sp = getattr(model, "sp", None)
+        if sp is not None and sp.sp > 1:
+            # this rank holds rows [lo, hi) of the packed stream: score the selected positions that fall there and
+            # let a differentiable sum over the group complete the [B, R] tensors (every rank then evaluates the
+            # same loss; the backward of the sum returns each rank the gradient of its own entries, sp times)
+            lo, hi, _ = model.sp_slice(pk.input_ids.shape[0])
+            mine = (pk.sel >= lo) & (pk.sel < hi)
+            idx = mine.nonzero(as_tuple=True)[0]
+            lp_l, ent_l = lm_head_logprob_entropy(hidden.index_select(0, pk.sel[idx] - lo), model.head_weight,
+                                                  pk.labels[idx], temperature, with_entropy)
+            N = pk.sel.shape[0]
+            lp = _group_sum(torch.zeros(N, dtype=lp_l.dtype, device=lp_l.device).index_put((idx,), lp_l), sp.group)
+            ent = None
+            if ent_l is not None:
+                ent = _group_sum(torch.zeros(N, dtype=ent_l.dtype, device=ent_l.device).index_put((idx,), ent_l),
+                                 sp.group)
+            return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
         lp, ent = lm_head_logprob_entropy(hidden.index_select(0, pk.sel), model.head_weight, pk.labels, temperature,
                                           with_entropy)
         return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
@@ -216,6 +287,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 load_hf_weights(self.ref_model, margs.path)
             for p in self.ref_model.parameters():
                 p.requires_grad_(False)
+            self._attach_sequence_parallel(self.ref_model)
             if self.model is None:
                 self.model_config = mcfg
         if self._is_rollout:

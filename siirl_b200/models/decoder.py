@@ -108,7 +108,17 @@ class DecoderLayer(nn.Module):
         x, h = ops.rmsnorm(delta if delta is not None else h, self.input_layernorm, cfg.rms_norm_eps,
                            residual=h if delta is not None else None)
         qkv = self.qkv(x, positions, rope)
-        a = attention_packed(qkv, info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=causal)
+        sp = getattr(self, "sp", None)
+        if sp is not None and sp.sp > 1:
+            # Ulysses: rows are this rank's slice of the packed stream; attention sees all rows of heads / sp heads
+            D, n = cfg.head_dim, sp.sp
+            parts = [(0, cfg.num_heads * D), (cfg.num_heads * D, cfg.num_kv_heads * D),
+                     ((cfg.num_heads + cfg.num_kv_heads) * D, cfg.num_kv_heads * D)]
+            a = attention_packed(sp.seq_to_heads(qkv, parts), info, cfg.num_heads // n, cfg.num_kv_heads // n, D,
+                                 causal=causal)
+            a = sp.heads_to_seq(a, [(0, cfg.num_heads * D)])
+        else:
+            a = attention_packed(qkv, info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=causal)
         attn_out = ops.linear(a, self.o_proj_weight)
         x, h = ops.rmsnorm(attn_out, self.post_attention_layernorm, cfg.rms_norm_eps, residual=h)
         return h, self.mlp(x)
@@ -166,9 +176,20 @@ class DecoderLM(nn.Module):
     # ---- training / scoring path ---------------------------------------------------------------
     def forward_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo, pixel_values=None,
                        image_grid_thw=None, image_mask=None) -> torch.Tensor:
-        """Final-norm hidden states ``[T, H]`` of a packed batch."""
+        """Final-norm hidden states ``[T, H]`` of a packed batch.  With sequence parallelism attached
+        (``self.sp``), the packed stream is padded to a multiple of the group size and this rank computes rows
+        ``[rank * T/sp, (rank + 1) * T/sp)``: the result holds those rows only (see ``sp_slice``)."""
         pmax = int(positions.max().item()) + 1 if positions.numel() else 1
         rope = self.rope_tables(input_ids.device, pmax)
+        sp = getattr(self, "sp", None)
+        if sp is not None and sp.sp > 1:
+            assert pixel_values is None, "sequence parallelism with image inputs is not wired"
+            lo, hi, pad = self.sp_slice(input_ids.shape[0])
+            if pad:
+                input_ids = torch.cat([input_ids, input_ids.new_zeros(pad)])
+                positions = torch.cat([positions, positions.new_zeros(*positions.shape[:-1], pad)], dim=-1)
+                info = SeqInfo(list(info.seqlens) + [pad], device=input_ids.device)
+            input_ids, positions = input_ids[lo:hi], positions[..., lo:hi].contiguous()
         h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask)
         delta = None
         for layer in self.layers:
@@ -178,6 +199,19 @@ class DecoderLM(nn.Module):
                 h, delta = layer(h, delta, positions, info, rope)
         out, _ = ops.rmsnorm(delta, self.norm, self.cfg.rms_norm_eps, residual=h)
         return out
+
+    def sp_slice(self, T: int) -> Tuple[int, int, int]:
+        """(first row, end row, padding rows) of this rank's share of a packed stream of ``T`` tokens."""
+        sp = getattr(self, "sp", None)
+        n = sp.sp if sp is not None else 1
+        Tl = (T + n - 1) // n
+        r = sp.rank if sp is not None else 0
+        return r * Tl, (r + 1) * Tl, Tl * n - T
+
+    def attach_sequence_parallel(self, sp) -> None:
+        self.sp = sp
+        for layer in self.layers:
+            layer.sp = sp
 
     def logprobs(self, input_ids, positions, info: SeqInfo, labels, temperature: float = 1.0,
                  with_entropy: bool = True, **mm) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:

@@ -81,3 +81,18 @@ def test_moe_expert_parallel_two_ranks(tmp_path):
     assert all(r["actor/grad_norm"] > 0 for r in m)
     d = tmp_path / "c" / "global_step_2" / "actor_agent_0"
     assert (d / "experts_world_size_2_rank_0.pt").exists() and (d / "experts_world_size_2_rank_1.pt").exists()
+
+
+def test_ulysses_and_tensor_parallel_rollout_two_ranks(tmp_path):
+    """Two ranks as ONE data-parallel replica: tensor-parallel rollout (TP=2), then Ulysses sequence-parallel
+    scoring and training (SP=2).  The generation batch is published by the first TP rank only and both SP ranks
+    receive the same micro-batches."""
+    out = _run(["actor_rollout_ref.rollout.tensor_model_parallel_size=2", "actor_rollout_ref.rollout.max_num_seqs=32",
+                "actor_rollout_ref.actor.ulysses_sequence_parallel_size=2", f"trainer.default_local_dir={tmp_path / 'c'}",
+                "trainer.total_training_steps=2", "trainer.save_freq=-1"], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    for r in m:
+        assert r["actor/grad_norm"] > 0 and 0.0 <= r["critic/score/mean"] <= 1.0
+        assert r["perf/total_num_tokens"] > 8 * 4 * 17

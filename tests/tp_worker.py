@@ -76,6 +76,74 @@ def main():
     if cuda:
         torch.cuda.synchronize()
         lib.check_status()
+    # 3. all-gather -> GEMM: weight rows sharded over the ranks, gathered inside the GEMM launch
+    from siirl_b200.parallel.ag_gemm import AgLinear
+    N2, K2 = 1536 * world, 640
+    w_full = (0.05 * torch.randn(N2, K2, generator=g)).to(dev, dtype)
+    b2 = torch.randn(N2, generator=g).to(dev, dtype)
+    ag = AgLinear(dist.group.WORLD, comm, N2, K2, copiers=8, device=dev, dtype=dtype)
+    ag.load_shard(w_full[rank * ag.rows:(rank + 1) * ag.rows])
+    for M in (300, 64, 1000):
+        x = torch.randn(M, K2, generator=g).to(dev, dtype)
+        y = ag(x, b2)
+        want = x.float() @ w_full.float().t() + b2.float()
+        err = (y.float() - want).abs().max().item()
+        assert err < (0.3 if cuda else 1e-3), f"ag_gemm M={M}: max err {err}"
+    if cuda:
+        torch.cuda.synchronize()
+        lib.check_status()
+    # 4. Ulysses layout switches: sequence shard <-> head shard, forward values and the backward (the other pull)
+    from siirl_b200.parallel.ulysses import UlyssesSP
+    hq, hkv, D, Tl = 4 * world, 2 * world, 16, 24
+    W = (hq + 2 * hkv) * D
+    parts = [(0, hq * D), (hq * D, hkv * D), ((hq + hkv) * D, hkv * D)]
+    usp = UlyssesSP(dist.group.WORLD, comm, max_elems=world * Tl * W)
+    full = torch.randn(world * Tl, W, generator=g).to(dev, dtype)          # same on every rank
+    mine = full[rank * Tl:(rank + 1) * Tl].clone().requires_grad_()
+    heads = usp.seq_to_heads(mine, parts)
+    hl, kl = hq // world * D, hkv // world * D
+    want = torch.cat([full[:, rank * hl:(rank + 1) * hl], full[:, hq * D + rank * kl: hq * D + (rank + 1) * kl],
+                      full[:, (hq + hkv) * D + rank * kl:(hq + hkv) * D + (rank + 1) * kl]], dim=1)
+    assert torch.equal(heads.detach(), want), "seq_to_heads"
+    back = usp.heads_to_seq(heads, parts)
+    assert torch.equal(back.detach(), mine.detach()), "round trip"
+    coef = torch.randn(Tl, W, generator=g).to(dev, dtype)
+    (back * coef).sum().backward()
+    assert torch.allclose(mine.grad.float(), coef.float()), "backward of the two switches is the identity map"
+    if cuda:
+        torch.cuda.synchronize()
+        lib.check_status()
+    # 5. a decoder under sequence parallelism: local rows of the hidden states and summed parameter gradients
+    #    equal the single-rank computation
+    from siirl_b200.ops.attention import SeqInfo
+    cfg5 = get_config("tiny-gpu" if cuda else "tiny")
+    m_full = build_model(cfg5, dtype=dtype, device=dev, seed=9)
+    m_sp = build_model(cfg5, dtype=dtype, device=dev, seed=9)
+    width = (cfg5.num_heads + 2 * cfg5.num_kv_heads) * cfg5.head_dim
+    m_sp.attach_sequence_parallel(UlyssesSP(dist.group.WORLD, comm, max_elems=512 * width))
+    lens = [37, 64, 22]                                   # 123 tokens: not a multiple of the group size
+    info = SeqInfo(lens, device=dev)
+    ids = torch.randint(3, cfg5.vocab_size, (sum(lens),), generator=g).to(dev)
+    coef = torch.randn(sum(lens), cfg5.hidden_size, generator=g).to(dev, dtype)
+    h_full = m_full.forward_hidden(ids, info.positions, info)
+    (h_full.float() * coef.float()).sum().backward()
+    h_loc = m_sp.forward_hidden(ids, info.positions, info)
+    lo, hi, pad = m_sp.sp_slice(sum(lens))
+    n_real = min(hi, sum(lens)) - lo
+    tol5 = 0.1 if cuda else 1e-4
+    assert (h_loc[:n_real].float() - h_full[lo:lo + n_real].float()).abs().max().item() < tol5, "SP hidden rows"
+    (h_loc[:n_real].float() * coef[lo:lo + n_real].float()).sum().backward()
+    for (n1, p1), (_, p2) in zip(m_full.named_parameters(), m_sp.named_parameters()):
+        if p1.grad is None and getattr(p1, "main_grad", None) is None:
+            continue                                      # not on the path of forward_hidden (LM head)
+        g2 = (p2.grad if p2.grad is not None else p2.main_grad).float().clone()
+        dist.all_reduce(g2)
+        g1 = (p1.grad if p1.grad is not None else p1.main_grad).float()
+        err = (g1 - g2).abs().max().item()
+        assert err < (0.05 * max(1.0, g1.abs().max().item()) if cuda else 1e-3), f"SP grad {n1}: {err}"
+    if cuda:
+        torch.cuda.synchronize()
+        lib.check_status()
     dist.barrier()
     if rank == 0:
         print("TP_OK")
