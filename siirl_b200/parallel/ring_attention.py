@@ -1,0 +1,233 @@
+"""Ring (context-parallel) causal attention over peer memory.
+
+Every sequence of the packed batch is cut into ``cp`` equal chunks; rank r holds chunk r of every sequence (its
+``qkv`` rows and a ``SeqInfo`` of the chunk lengths, identical on all ranks).  Causality means rank r attends to
+the K/V chunks of ranks 0..r.  The reference gets this from Megatron-core / Transformer-Engine's NCCL send/recv
+ring (``context_parallel_size`` in siirl/params/model_args.py, MegatronArguments).  Here a rank publishes its
+``qkv`` rows in symmetric memory once and every consumer pulls the K/V columns of the chunk it needs with one
+strided peer-load kernel (``sb_block_pull``), on a side stream while the tcgen05 attention kernel works on the
+previous chunk; partial results are merged with their log-sum-exp.  The backward recomputes block by block with the
+FINAL ``out`` / ``lse`` (as flash attention does), accumulates dQ locally and returns dK/dV of remote chunks to
+their owners through a second pull.
+
+Chunks are assigned contiguously, so rank r does r + 1 blocks of work (no zig-zag balancing).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import lib as _lib
+from ..ops.attention import SeqInfo
+from .ulysses import _PullBlock
+
+
+def _block_fwd(qkv, info: SeqInfo, hq, hkv, d, causal, scale) -> Tuple[torch.Tensor, torch.Tensor]:
+    L = _lib.get_lib()
+    T = qkv.shape[0]
+    out = torch.empty(T, hq * d, dtype=qkv.dtype, device=qkv.device)
+    lse = torch.empty(hq, T, dtype=torch.float32, device=qkv.device)
+    ts, tl, t0, n = info.tiles()
+    _lib.check(L.sb_fmha_fwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(ts), _lib.ptr(tl), _lib.ptr(t0), n,
+                             T, hq, hkv, d, int(causal), ctypes.c_float(scale),
+                             _lib.ptr(_lib.status_word(qkv.device)), _lib.stream()), "sb_fmha_fwd")
+    return out, lse
+
+
+def _block_bwd(qkv, out, lse, dout, info: SeqInfo, hq, hkv, d, causal, scale) -> torch.Tensor:
+    L = _lib.get_lib()
+    T = qkv.shape[0]
+    dqkv = torch.empty_like(qkv)
+    delta = torch.empty(hq, T, dtype=torch.float32, device=qkv.device)
+    dq_acc = torch.empty(T, hq * d, dtype=torch.float32, device=qkv.device)
+    ts, tl, t0, n = info.tiles()
+    _lib.check(L.sb_fmha_bwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(dout), _lib.ptr(lse), _lib.ptr(delta),
+                             _lib.ptr(dq_acc), _lib.ptr(dqkv), _lib.ptr(ts), _lib.ptr(tl), _lib.ptr(t0), n, T, hq, hkv,
+                             d, int(causal), ctypes.c_float(scale), _lib.ptr(_lib.status_word(qkv.device)),
+                             _lib.stream()), "sb_fmha_bwd")
+    return dqkv
+
+
+class RingContext:
+    """Symmetric staging of one context-parallel group: two alternating ``qkv`` buffers and the dK/dV return slots."""
+
+    def __init__(self, group, comm=None, max_rows: int = 0, qkv_width: int = 0, kv_width: int = 0):
+        self.group, self.comm = group, comm
+        self.cp = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.stage = None
+        if comm is not None and self.cp > 1:
+            self.stage = [comm.alloc(max_rows * qkv_width, torch.bfloat16) for _ in range(2)]
+            self.gstage = comm.alloc(self.cp * max_rows * kv_width, torch.bfloat16)
+            self._turn = 0
+            comm.barrier()
+
+    def publish(self, x: torch.Tensor) -> torch.Tensor:
+        buf = self.stage[self._turn]
+        self._turn ^= 1
+        buf[: x.numel()].copy_(x.reshape(-1))
+        self.comm.barrier()
+        return buf
+
+    def pull_cols(self, buf: torch.Tensor, src_rank: int, out: torch.Tensor, src_off_elems: int, dst_off_elems: int,
+                  src_pitch: int, dst_pitch: int, rows: int, cols: int) -> None:
+        """Copy ``rows x cols`` bf16 elements from ``src_rank``'s instance of ``buf`` into ``out``."""
+        blk = (_PullBlock * 1)(_PullBlock(src_off_elems * 2, dst_off_elems * 2, src_pitch * 2, dst_pitch * 2, rows,
+                                          cols * 2, src_rank, 0))
+        L = _lib.get_lib()
+        _lib.check(L.sb_block_pull(self.comm.peers_of(buf).ptr_array, self.cp, blk, 1, _lib.ptr(out), _lib.stream()),
+                   "sb_block_pull")
+
+
+def _merge(out, lse, o_s, lse_s):
+    """Log-sum-exp merge of two partial attention results (``lse`` is ``[heads, T]``, outputs ``[T, heads*d]``)."""
+    new = torch.logaddexp(lse, lse_s)
+    T, hq = out.shape[0], lse.shape[0]
+    wa = torch.exp(lse - new).t().reshape(T, hq, 1)
+    wb = torch.exp(lse_s - new).t().reshape(T, hq, 1)
+    merged = out.float().reshape(T, hq, -1) * wa + o_s.float().reshape(T, hq, -1) * wb
+    return merged.reshape(T, -1).to(out.dtype), new
+
+
+class _RingAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, rc: RingContext, info: SeqInfo, hq, hkv, d, scale):
+        me = rc.rank
+        Tl, W = qkv.shape
+        qw, kvw = hq * d, 2 * hkv * d
+        buf = rc.publish(qkv)
+        side = torch.cuda.Stream()
+        out, lse = _block_fwd(qkv, info, hq, hkv, d, True, scale)        # own chunk: causal
+        nxt = None
+        for s in range(1, me + 1):
+            if nxt is None:
+                nxt = _fetch(rc, buf, qkv, me - s, Tl, W, qw, kvw, side)
+            blk, ev = nxt
+            torch.cuda.current_stream().wait_event(ev)
+            nxt = _fetch(rc, buf, qkv, me - s - 1, Tl, W, qw, kvw, side) if s < me else None
+            o_s, lse_s = _block_fwd(blk, info, hq, hkv, d, False, scale)  # earlier chunk: every key is visible
+            out, lse = _merge(out, lse, o_s, lse_s)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.meta = (rc, info, hq, hkv, d, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        rc, info, hq, hkv, d, scale = ctx.meta
+        me, n = rc.rank, rc.cp
+        Tl, W = qkv.shape
+        qw, kvw = hq * d, 2 * hkv * d
+        dout = dout.contiguous()
+        buf = rc.publish(qkv)
+        side = torch.cuda.Stream()
+        g = _block_bwd(qkv, out, lse, dout, info, hq, hkv, d, True, scale)
+        dq = g[:, :qw].float()
+        dkv = g[:, qw:].float()
+        gs = rc.gstage.view(n, -1)
+        nxt = None
+        for s in range(1, me + 1):
+            if nxt is None:
+                nxt = _fetch(rc, buf, qkv, me - s, Tl, W, qw, kvw, side)
+            blk, ev = nxt
+            torch.cuda.current_stream().wait_event(ev)
+            nxt = _fetch(rc, buf, qkv, me - s - 1, Tl, W, qw, kvw, side) if s < me else None
+            g = _block_bwd(blk, out, lse, dout, info, hq, hkv, d, False, scale)
+            dq += g[:, :qw].float()
+            gs[s, : Tl * kvw].copy_(g[:, qw:].reshape(-1))               # slot s: gradient for the chunk of rank me - s
+        rc.comm.barrier()
+        tmp = torch.empty(Tl, kvw, dtype=qkv.dtype, device=qkv.device)
+        for s in range(1, n - me):                                       # rank me + s used my chunk at its step s
+            rc.pull_cols(rc.gstage, me + s, tmp, s * gs.shape[1], 0, kvw, kvw, Tl, kvw)
+            dkv += tmp.float()
+        rc.comm.barrier()                                                # the return slots may be rewritten
+        return torch.cat([dq, dkv], dim=1).to(qkv.dtype), None, None, None, None, None, None
+
+
+def _fetch(rc: RingContext, buf, qkv, src: int, Tl: int, W: int, qw: int, kvw: int, side):
+    """Block for chunk ``src``: local queries next to the K/V columns pulled from rank ``src`` (on a side stream)."""
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        blk = qkv.clone()
+        rc.pull_cols(buf, src, blk, qw, qw, W, W, Tl, kvw)
+        ev = torch.cuda.Event()
+        ev.record(side)
+    blk.record_stream(torch.cuda.current_stream())
+    return blk, ev
+
+
+def ring_attention(qkv: torch.Tensor, rc: Optional[RingContext], info: SeqInfo, n_heads: int, n_kv_heads: int,
+                   head_dim: int, scale: Optional[float] = None) -> torch.Tensor:
+    """Causal attention of this rank's chunk ``qkv [Tl, (hq + 2 hkv) d]`` against the chunks of ranks ``<= rank``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    from ..ops.attention import attention_packed
+    if rc is None or rc.cp == 1:
+        return attention_packed(qkv, info, n_heads, n_kv_heads, head_dim, causal=True, scale=scale)
+    if qkv.is_cuda and rc.stage is not None:
+        assert head_dim in (64, 128), "ring attention uses the 64/128-wide attention kernels"
+        return _RingAttn.apply(qkv.contiguous(), rc, info, n_heads, n_kv_heads, head_dim, scale)
+    return _ring_attention_gathered(qkv, rc, info, n_heads, n_kv_heads, head_dim, scale)
+
+
+class _GatherRows(torch.autograd.Function):
+    """all_gather along dim 0 whose backward returns every rank the summed gradient of its own rows."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n = dist.get_world_size(group)
+        out = torch.empty(n * x.numel(), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous().reshape(-1), group=group)
+        return out.view(n, *x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        g = dy.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g[dist.get_rank(ctx.group)], None
+
+
+def _ring_attention_gathered(qkv, rc: RingContext, info: SeqInfo, hq, hkv, d, scale):
+    """Library-collective path (CPU / gloo): gather all chunks, attend with an explicit chunk-causal mask."""
+    Tl = qkv.shape[0]
+    allq = _GatherRows.apply(qkv, rc.group)                              # [cp, Tl, W]
+    q = qkv[:, : hq * d].reshape(Tl, hq, d).float()
+    out = torch.zeros(Tl, hq, d, dtype=torch.float32, device=qkv.device)
+    cu = info.cu_seqlens_cpu
+    rep = hq // hkv
+    for i in range(len(cu) - 1):
+        a, b = cu[i], cu[i + 1]
+        if b == a:
+            continue
+        ks, vs, masks = [], [], []
+        for r in range(rc.rank + 1):
+            kv = allq[r, a:b, hq * d:].float()
+            ks.append(kv[:, : hkv * d].reshape(b - a, hkv, d))
+            vs.append(kv[:, hkv * d:].reshape(b - a, hkv, d))
+            m = torch.ones(b - a, b - a, dtype=torch.bool, device=qkv.device)
+            masks.append(torch.tril(m) if r == rc.rank else m)
+        k = torch.cat(ks).repeat_interleave(rep, dim=1)
+        v = torch.cat(vs).repeat_interleave(rep, dim=1)
+        mask = torch.cat(masks, dim=1)
+        sc = torch.einsum("qhd,khd->hqk", q[a:b], k) * scale
+        sc = sc.masked_fill(~mask[None], float("-inf"))
+        out[a:b] = torch.einsum("hqk,khd->qhd", torch.softmax(sc, dim=-1), v)
+    return out.reshape(Tl, hq * d).to(qkv.dtype)
+
+
+def split_for_context_parallel(seqlens, cp: int, rank: int, device=None):
+    """Row indices (into the packed stream), positions and the chunk ``SeqInfo`` of rank ``rank`` when every sequence
+    (length divisible by ``cp``) is cut into ``cp`` contiguous chunks."""
+    idx, pos, lens, start = [], [], [], 0
+    for n in seqlens:
+        assert n % cp == 0, "context parallelism needs sequence lengths divisible by the group size"
+        c = n // cp
+        idx.append(torch.arange(start + rank * c, start + (rank + 1) * c))
+        pos.append(torch.arange(rank * c, (rank + 1) * c))
+        lens.append(c)
+        start += n
+    return torch.cat(idx).to(device), torch.cat(pos).to(device), SeqInfo(lens, device=device)

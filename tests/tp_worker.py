@@ -144,6 +144,29 @@ def main():
     if cuda:
         torch.cuda.synchronize()
         lib.check_status()
+    # 6. ring (context-parallel) attention equals causal attention over the whole sequences, values and gradients
+    from siirl_b200.ops.attention import attention_packed
+    from siirl_b200.parallel.ring_attention import RingContext, ring_attention, split_for_context_parallel
+    hq6, hkv6, d6 = 4, 2, 64
+    W6 = (hq6 + 2 * hkv6) * d6
+    lens6 = [64 * world, 192 * world]
+    T6 = sum(lens6)
+    full6 = (0.5 * torch.randn(T6, W6, generator=g)).to(dev, dtype)
+    go6 = torch.randn(T6, hq6 * d6, generator=g).to(dev, dtype)
+    ref_in = full6.clone().requires_grad_()
+    ref_out = attention_packed(ref_in, SeqInfo(lens6, device=dev), hq6, hkv6, d6, causal=True)
+    ref_out.backward(go6)
+    rows, _, info6 = split_for_context_parallel(lens6, world, rank, device=dev)
+    rc = RingContext(dist.group.WORLD, comm, max_rows=rows.numel(), qkv_width=W6, kv_width=2 * hkv6 * d6)
+    loc = full6[rows].clone().requires_grad_()
+    out6 = ring_attention(loc, rc, info6, hq6, hkv6, d6)
+    out6.backward(go6[rows])
+    t6 = 0.06 if cuda else 1e-4
+    assert (out6.float() - ref_out[rows].float()).abs().max().item() < t6, "ring attention output"
+    assert (loc.grad.float() - ref_in.grad[rows].float()).abs().max().item() < 4 * t6, "ring attention gradient"
+    if cuda:
+        torch.cuda.synchronize()
+        lib.check_status()
     dist.barrier()
     if rank == 0:
         print("TP_OK")
