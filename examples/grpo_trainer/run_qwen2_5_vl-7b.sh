@@ -1,0 +1,19 @@
+#!/usr/bin/env bash
+# GRPO with image inputs (geometry3k), Qwen2.5-VL-7B
+set -euo pipefail
+python3 -m siirl_b200.main_dag \
+    data.train_files=$HOME/data/gsm8k/train.parquet \
+    data.val_files=$HOME/data/gsm8k/test.parquet \
+    data.train_batch_size=512 \
+    data.max_prompt_length=1024 \
+    data.max_response_length=2048 \
+    actor_rollout_ref.model.path=$HOME/models/Qwen2.5-7B-Instruct \
+    actor_rollout_ref.actor.optim.lr=1e-6 \
+    actor_rollout_ref.actor.ppo_mini_batch_size=256 \
+    actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8 \
+    actor_rollout_ref.rollout.n=8 \
+    actor_rollout_ref.rollout.gpu_memory_utilization=0.5 \
+    trainer.n_gpus_per_node=8 trainer.nnodes=1 \
+    trainer.total_epochs=30 trainer.save_freq=10 trainer.test_freq=10 \
+    trainer.logger="[console,jsonl]" trainer.project_name=siirl_b200 \
+    algorithm.adv_estimator=grpo data.train_files=$HOME/data/geo3k/train.parquet data.val_files=$HOME/data/geo3k/test.parquet data.image_key=images actor_rollout_ref.model.path=$HOME/models/Qwen2.5-VL-7B-Instruct trainer.experiment_name=grpo_qwen2.5_vl_7b "$@"

@@ -228,9 +228,49 @@ class DAGWorker:
         batch.meta.update({"eos_token_id": getattr(self.tokenizer, "eos_token_id", None),
                            "pad_token_id": getattr(self.tokenizer, "pad_token_id", 0) or 0,
                            "global_steps": self.global_steps})
-        out = self._arr(node).generate_sequences(batch.to(self.device))
+        worker = self._arr(node)
+        r = self.config.actor_rollout_ref.rollout
+        if (r.multi_turn.enable or r.mode == "async") and worker.engine is not None \
+                and getattr(worker, "embodied_rollout", None) is None:
+            out = self._generate_with_agent_loops(worker, batch).to(self.device)
+        else:
+            out = worker.generate_sequences(batch.to(self.device))
         metrics = {"perf/rollout_output_tokens_total": float(out.meta.get("total_output_tokens", 0))}
+        if "num_turns" in out.non_tensors:
+            turns = [float(t) for t in out.non_tensors["num_turns"]]
+            metrics.update({"num_turns/mean": sum(turns) / max(len(turns), 1), "num_turns/max": max(turns, default=0.0)})
         return NodeOutput(out, metrics)
+
+    def _generate_with_agent_loops(self, worker, batch: Batch) -> Batch:
+        """Asynchronous rollout: one agent loop per sample (single-turn, tool calling, user interactions) against
+        the in-process request server that batches their requests into engine calls
+        (reference: dagworker generate -> AgentLoopManager, siirl/execution/rollout_flow/multiturn/agent_loop)."""
+        import time as _time
+        if getattr(self, "_agent_loops", None) is None:
+            from ..engine.rollout.async_server import AsyncRolloutServer
+            from ..execution.rollout_flow.multiturn.agent_loop.agent_loop import AgentLoopManager
+            from ..execution.rollout_flow.multiturn.tools.tool_registry import initialize_tools_from_config
+            mt = self.config.actor_rollout_ref.rollout.multi_turn
+            tools = initialize_tools_from_config(mt.tool_config_path) if mt.tool_config_path else []
+            interactions = {}
+            if mt.interaction_config_path:
+                from ..execution.rollout_flow.multiturn.interactions.base import initialize_interactions_from_config
+                interactions = initialize_interactions_from_config(mt.interaction_config_path)
+            server = AsyncRolloutServer(worker.engine, self.tokenizer)
+            self._agent_loops = AgentLoopManager(self.config, [server], self.tokenizer, tools, interactions)
+        t0 = _time.time()
+        worker.engine.wake_up()
+        r = self.config.actor_rollout_ref.rollout
+        validate = bool(batch.meta.get("validate", False))
+        sp = {"seed": (r.seed + 7919 * self.global_steps + 104729 * self._rank) & 0x7FFFFFFF}
+        if validate or not r.do_sample:
+            sp["temperature"] = r.val_kwargs.temperature if validate else 0.0
+        out = self._agent_loops.generate_sequences(batch.to("cpu"), sp)
+        if r.free_cache_engine:
+            worker.engine.sleep()
+        out.meta["timing_generate_s"] = _time.time() - t0
+        out.meta["total_output_tokens"] = int(out["attention_mask"][:, -out["responses"].shape[1]:].sum())
+        return out
 
     def compute_reward(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
         metrics: Dict[str, float] = {}

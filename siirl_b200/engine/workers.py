@@ -118,6 +118,9 @@ class _ModelWorkerBase:
         if ep > 1:
             self._attach_expert_parallel(model_args)
         self._attach_sequence_parallel(self.model)
+        if trainable and getattr(model_args, "enable_activation_offload", False) and self.device.type == "cuda":
+            from ..utils.model_utils.activation_offload import ActivationOffload
+            self.model.activation_offload = ActivationOffload()
         if trainable and ep > 1:
             from ..parallel.flat_params import ExpertSplitStore
             self.store = ExpertSplitStore(self.model, group=self.group, comm=self.comm)

@@ -10,6 +10,8 @@ the HF names (q_proj/k_proj/v_proj, gate_proj/up_proj) for safetensors checkpoin
 """
 from __future__ import annotations
 
+import contextlib
+
 from typing import List, Optional, Tuple
 
 import torch
@@ -192,11 +194,14 @@ class DecoderLM(nn.Module):
             input_ids, positions = input_ids[lo:hi], positions[..., lo:hi].contiguous()
         h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask)
         delta = None
-        for layer in self.layers:
-            if self.gradient_checkpointing and torch.is_grad_enabled():
-                h, delta = ckpt.checkpoint(layer, h, delta, positions, info, rope, use_reentrant=False)
-            else:
-                h, delta = layer(h, delta, positions, info, rope)
+        offload = getattr(self, "activation_offload", None)
+        ctx = offload.region() if (offload is not None and torch.is_grad_enabled()) else contextlib.nullcontext()
+        with ctx:   # tensors saved for backward move to pinned host memory when activation offload is attached
+            for layer in self.layers:
+                if self.gradient_checkpointing and torch.is_grad_enabled():
+                    h, delta = ckpt.checkpoint(layer, h, delta, positions, info, rope, use_reentrant=False)
+                else:
+                    h, delta = layer(h, delta, positions, info, rope)
         out, _ = ops.rmsnorm(delta, self.norm, self.cfg.rms_norm_eps, residual=h)
         return out
 

@@ -43,6 +43,19 @@ def default_compute_score(data_source: str, solution_str: str, ground_truth: Any
     if ds in ("searchR1_nq", "searchR1_triviaqa", "searchR1_popqa", "searchR1_hotpotqa", "searchR1_2wikimultihopqa",
               "searchR1_musique", "searchR1_bamboogle", "qa_em"):
         return qa_em.compute_score(solution_str, ground_truth)
+    if ds in ("numina_aops_forum", "numina_synthetic_math", "numina_amc_aime", "numina_synthetic_amc", "numina_cn_k12",
+              "numina_olympiads", "prime_math", "math_verify"):
+        # the reference scores these with sympy / math-verify equivalence; the normalised string match of the MATH
+        # scorer is the dependency-free rule used here
+        return math_score.compute_score(solution_str, ground_truth)
+    if ds in ("codecontests", "apps", "codeforces", "taco", "prime_code"):
+        url = kwargs.get("sandbox_fusion_url")
+        if url:
+            from . import sandbox_fusion
+            return sandbox_fusion.compute_score(url, kwargs.get("concurrent_semaphore"), solution_str, ground_truth,
+                                                continuous=True)
+        from . import prime_code
+        return prime_code.compute_score(solution_str, ground_truth, continuous=True)
     if ds == "synthetic/arith":
         return _arith(solution_str, ground_truth)
     if ds == "synthetic/bernoulli":

@@ -98,3 +98,31 @@ def test_async_server_batches_concurrent_requests_and_manager_collates():
     assert out["attention_mask"][0, :13].sum() == 0 and out["attention_mask"][0, 13:16].sum() == 3
     resp = asyncio.run(server.chat_completion({"messages": [{"role": "user", "content": "1+1="}], "max_tokens": 3}))
     assert resp["choices"][0]["message"]["role"] == "assistant" and resp["usage"]["completion_tokens"] == 3
+
+
+def test_multiturn_pipeline_end_to_end(tmp_path):
+    """GRPO with the rollout node served by agent loops (tool agent + in-process request server) for two steps."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, OMP_NUM_THREADS="2", SIIRL_LOG_DIR=str(tmp_path / "log"))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    args = ["algorithm.adv_estimator=grpo", "data.synthetic=parity", "data.synthetic_size=64",
+            "data.synthetic_min_prompt=16", "data.synthetic_max_prompt=32", "data.max_prompt_length=32",
+            "data.max_response_length=24", "data.train_batch_size=4", "actor_rollout_ref.model.arch_preset=tiny",
+            "actor_rollout_ref.rollout.n=4", "actor_rollout_ref.rollout.max_num_seqs=16",
+            "actor_rollout_ref.rollout.multi_turn.enable=True", "actor_rollout_ref.rollout.multi_turn.max_assistant_turns=2",
+            "actor_rollout_ref.rollout.multi_turn.tool_config_path=examples/multi_turn/gsm8k_tool_config.yaml",
+            "actor_rollout_ref.rollout.prompt_length=32", "actor_rollout_ref.rollout.response_length=24",
+            "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8",
+            "trainer.n_gpus_per_node=1", "trainer.device=cpu", "trainer.val_before_train=False",
+            "trainer.logger=['jsonl']", "trainer.total_training_steps=2", "trainer.save_freq=-1"]
+    out = subprocess.run([sys.executable, "-m", "siirl_b200.main_dag", *args], env=env, cwd=root, capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    with open(tmp_path / "log" / "metrics.jsonl") as f:
+        m = [json.loads(line) for line in f]
+    assert [r["step"] for r in m] == [1, 2] and all(r["num_turns/mean"] >= 1 for r in m)
+    assert all(r["response_length/max"] <= 24 for r in m)
