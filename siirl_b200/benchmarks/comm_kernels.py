@@ -75,7 +75,8 @@ def bench_gemm_ar(comm):
     from ..parallel.tensor_parallel import TPContext
     world, rank = dist.get_world_size(), dist.get_rank()
     H = 3584
-    ctx = TPContext(dist.group.WORLD, comm, max_rows=8192, max_cols=H, max_tiles=64 * 28 + 8)
+    ctx = TPContext(dist.group.WORLD, comm, max_rows=8192, max_cols=H, max_tiles=64 * 28 + 8,
+                    fused_max_rows=1 << 30)     # measure the fused kernel at every size
     pk = peaks()
     for M, K, what in ((64, 18944, "decode down_proj"), (64, 3584, "decode o_proj"), (128, 18944, "decode down_proj"),
                        (4096, 18944, "prefill down_proj"), (8192, 3584, "prefill o_proj")):
