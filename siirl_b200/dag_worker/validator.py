@@ -42,6 +42,17 @@ class Validator:
             reward, _extra = compute_reward(out, w.val_reward_fn)
             seq = reward.sum(-1).cpu().tolist()
             dup = out["padded_duplicate"] if "padded_duplicate" in out else [False] * out.batch_size
+            if out["responses"].dim() == 3:
+                # embodied episodes (reference validator.py, embodied variant): score = task success / shaped
+                # reward, the logged "text" is the task and the episode summary
+                for i in range(out.batch_size):
+                    if dup[i]:
+                        continue
+                    sources.append(str(out["data_source"][i]) if "data_source" in out else "embodied")
+                    inputs.append(str(out.non_tensors.get("task_file_name", ["task"] * out.batch_size)[i]))
+                    outputs.append(f"finish_step={int(out['finish_step'][i])} complete={bool(out['complete'][i])}")
+                    scores.append(float(out["complete"][i]))
+                continue
             P = out["prompts"].shape[1]
             for i in range(out.batch_size):
                 if dup[i]:

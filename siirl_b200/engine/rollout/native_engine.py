@@ -135,6 +135,7 @@ class RolloutEngine:
         nb = self._requested_blocks
         if nb is None:
             if self.device.type == "cuda":
+                torch.cuda.empty_cache()        # cached training blocks would hide free memory from the query
                 free, _total = torch.cuda.mem_get_info(self.device)
                 nb = max(16, int(free * self._mem_util) // self._block_bytes())
             else:

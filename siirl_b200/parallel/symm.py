@@ -178,3 +178,55 @@ class SymmComm:
         self.pull_segments(staging, segs, out)
         self.barrier()
         return out
+
+    # ---- sample redistribution (Data Coordinator) -------------------------------------------------------------
+    def alltoall_samples(self, send):
+        """All-to-all of per-destination sample lists ``send[dst] = [(pos, Sample), ...]`` whose tensors live on this
+        GPU: tensor bytes are packed once into a symmetric staging buffer and every rank pulls the rows addressed to it
+        in ONE kernel (``sb_segment_pull``); only the small descriptors (shapes, dtypes, offsets, non-tensor fields)
+        travel through an object collective.  Replaces the per-sample object-store transfers of the reference
+        (siirl/dag_worker/dagworker.py:1117-1239).  Returns ``recv[src] = [(pos, Sample), ...]``."""
+        from ..data_coordinator.sample import Sample
+        descs = [[] for _ in range(self.world)]
+        chunks, off = [], 0
+        for dst, part in enumerate(send):
+            for pos, s in part:
+                fields = []
+                for k in sorted(s.tensors):
+                    t = s.tensors[k].to(self.device).contiguous()
+                    nb = t.numel() * t.element_size()
+                    pad = (-nb) % 16
+                    raw = t.reshape(-1).view(torch.uint8)
+                    chunks.append(raw if not pad else torch.cat([raw, raw.new_zeros(pad)]))
+                    fields.append((k, str(t.dtype).replace("torch.", ""), tuple(t.shape), off, nb))
+                    off += nb + pad
+                descs[dst].append((pos, fields, s.non_tensors, s.meta))
+        gathered: List[Optional[list]] = [None] * self.world
+        dist.all_gather_object(gathered, (descs, off), group=self.group)
+        need = max(g[1] for g in gathered)
+        stage = getattr(self, "_sample_stage", None)
+        if stage is None or stage.numel() < need:      # same decision on every rank (need is global): collective alloc
+            self._sample_stage = stage = self.alloc(max(need, 1 << 26), torch.uint8)
+        if chunks:
+            stage[:off].copy_(torch.cat(chunks))
+        self.barrier()
+        segs, out_off, plan = [], 0, []
+        for src in range(self.world):
+            for pos, fields, non_t, meta in gathered[src][0][self.rank]:
+                placed = []
+                for k, dt, shape, so, nb in fields:
+                    nb16 = nb + ((-nb) % 16)
+                    segs.append((src, so, out_off, nb16))
+                    placed.append((k, dt, shape, out_off, nb))
+                    out_off += nb16
+                plan.append((src, pos, placed, non_t, meta))
+        out = torch.empty(max(out_off, 16), dtype=torch.uint8, device=self.device)
+        self.pull_segments(stage, segs, out)
+        self.barrier()                                   # peers are done reading my staging buffer
+        recv = [[] for _ in range(self.world)]
+        for src, pos, placed, non_t, meta in plan:
+            tensors = {}
+            for k, dt, shape, o, nb in placed:
+                tensors[k] = out[o:o + nb].view(getattr(torch, dt)).reshape(shape)
+            recv[src].append((pos, Sample(tensors, non_t, meta)))
+        return recv

@@ -63,6 +63,38 @@ def main():
     torch.cuda.synchronize()
     assert torch.equal(got, want)
     lib.check_status()
+
+    # 3. Data Coordinator redistribution through peer memory: every rank publishes samples of different lengths,
+    #    a collective get re-partitions them (balanced) and each rank receives its share bit-exactly
+    from siirl_b200.data_coordinator import DataCoordinator
+    from siirl_b200.data_coordinator.sample import Sample, SampleInfo
+    dc = DataCoordinator(1, 0, world, group=dist.group.WORLD, comm=comm)
+    per_rank = 6
+    infos, samples = [], []
+    for i in range(per_rank):
+        n = 5 + 3 * i + rank
+        ids = torch.arange(n, device=dev) + 1000 * rank + 100 * i
+        samples.append(Sample({"input_ids": ids, "score": torch.tensor([float(rank * 10 + i)], device=dev)},
+                              {"tag": f"r{rank}s{i}"}, {}))
+        infos.append(SampleInfo(sum_tokens=n, dict_info={"key": "k"}))
+    dc.put_batch(infos, samples, caller_node_id="k")
+    got_s = dc.get_batch_collective(per_rank, rank, world, lambda info: info.dict_info.get("key") == "k")
+    assert len(got_s) == per_rank
+    seen = []
+    for smp in got_s:
+        tag = smp.non_tensors["tag"]
+        r, i = int(tag[1]), int(tag[3])
+        n = 5 + 3 * i + r
+        assert smp.tensors["input_ids"].is_cuda
+        assert torch.equal(smp.tensors["input_ids"].cpu(), torch.arange(n) + 1000 * r + 100 * i), tag
+        assert float(smp.tensors["score"]) == float(r * 10 + i)
+        seen.append(tag)
+    all_seen = [None] * world
+    dist.all_gather_object(all_seen, seen)
+    flat = sorted(t for part in all_seen for t in part)
+    assert flat == sorted(f"r{r}s{i}" for r in range(world) for i in range(per_rank)), "a sample was lost or duplicated"
+    torch.cuda.synchronize()
+    lib.check_status()
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK", world)
