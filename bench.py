@@ -129,6 +129,9 @@ def build_config(args, world: int):
         f"data.train_batch_size={bs}", "data.shuffle=True",
         f"actor_rollout_ref.model.arch_preset={args.model}", "actor_rollout_ref.model.random_init=True",
         "actor_rollout_ref.model.enable_gradient_checkpointing=True",
+        # one GPU holds all of the fp32 master weights and Adam moments (91 GB) next to weights, reference copy and
+        # gradients (60 GB): the per-layer checkpoints of a 41k-token micro-batch then go to pinned host memory
+        f"actor_rollout_ref.model.enable_activation_offload={world == 1}",
         f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0",
         f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp}",
         f"actor_rollout_ref.rollout.max_num_seqs={args.prompts_per_gpu * args.n}",

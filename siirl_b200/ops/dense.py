@@ -143,7 +143,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         return F.linear(x, weight, bias)
     _lib.use_native(x)
     rows = x.numel() // x.shape[-1]
-    if rows <= 128 and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)):
+    if rows <= 512 and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)):
         y = linear_skinny(x.reshape(rows, x.shape[-1]).contiguous(), weight, bias)
         return y.reshape(*x.shape[:-1], weight.shape[0])
     return _LinearFn.apply(x, weight, bias)
