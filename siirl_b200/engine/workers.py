@@ -38,6 +38,8 @@ def resolve_model_config(model_args, value_head: bool = False) -> DecoderConfig:
     if value_head:
         cfg.value_head = True
         cfg.tie_word_embeddings = False
+    if int(getattr(model_args, "lora_rank", 0) or 0) > 0:
+        cfg.lora_rank, cfg.lora_alpha = int(model_args.lora_rank), float(model_args.lora_alpha)
     return cfg
 
 
@@ -124,6 +126,13 @@ class _ModelWorkerBase:
         if trainable and ep > 1:
             from ..parallel.flat_params import ExpertSplitStore
             self.store = ExpertSplitStore(self.model, group=self.group, comm=self.comm)
+        elif trainable and mcfg.lora_rank > 0:
+            # only the adapters train: base weights stay out of the gradient / optimizer buffers
+            for n, p in self.model.named_parameters():
+                if "_lora_" not in n:
+                    p.requires_grad_(False)
+            self.store = FlatParamStore(self.model, group=self.group, comm=self.comm,
+                                        param_filter=lambda n: "_lora_" in n)
         elif trainable:
             self.store = FlatParamStore(self.model, group=self.group, comm=self.comm)
         else:
@@ -282,7 +291,9 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         margs = self.config.model
         if self._is_actor or self._is_rollout:
             self._build(margs, value_head=False, trainable=self._is_actor)
-        if self._is_ref:
+        if self._is_ref and self.model is not None and self.model_config.lora_rank > 0:
+            pass        # the reference policy is the actor with its adapters switched off
+        elif self._is_ref:
             mcfg = resolve_model_config(margs)
             self.ref_model = build_model(mcfg, dtype=self._dtype(margs), device=self.device, seed=self.seed)
             if margs.path and not margs.random_init and not margs.arch_preset:
@@ -327,6 +338,8 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         from ..parallel.tensor_parallel import TPContext
         if self.world % tp:
             raise ValueError(f"rollout.tensor_model_parallel_size={tp} does not divide the group size {self.world}")
+        if self.model_config.lora_rank > 0:
+            raise ValueError("tensor-parallel rollout with LoRA adapters is not supported: use tensor_model_parallel_size=1")
         ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
         mine = None
         for b in range(self.world // tp):
@@ -483,8 +496,15 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
     def compute_ref_log_prob(self, data: Batch) -> Batch:
         rf = self.config.ref
         model = self.ref_model if self.ref_model is not None else self.model
-        lp, _ = self._logprob_pass(model, data, self.ref_logprob_micro, rf.log_prob_use_dynamic_bsz,
-                                   rf.log_prob_max_token_len_per_gpu, with_entropy=False)
+        lora_ref = self.ref_model is None and getattr(self.model_config, "lora_rank", 0) > 0
+        if lora_ref:
+            model.set_lora_enabled(False)
+        try:
+            lp, _ = self._logprob_pass(model, data, self.ref_logprob_micro, rf.log_prob_use_dynamic_bsz,
+                                       rf.log_prob_max_token_len_per_gpu, with_entropy=False)
+        finally:
+            if lora_ref:
+                model.set_lora_enabled(True)
         data["ref_log_prob"] = lp
         return data
 

@@ -52,6 +52,9 @@ class DecoderConfig:
     # [ep_rank * num_experts / ep_size, (ep_rank + 1) * num_experts / ep_size)
     ep_size: int = 1
     ep_rank: int = 0
+    # LoRA adapters on the four projections of every layer (0: none); runtime option, not part of the HF config
+    lora_rank: int = 0
+    lora_alpha: float = 16.0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     # value head (critic / reward model): one scalar per token instead of the vocabulary head

@@ -75,6 +75,26 @@ class DecoderLayer(nn.Module):
             self.gate_up_proj_weight = _param((2 * I, H), dtype, device, std, gen)
             self.down_proj_weight = _param((H, I), dtype, device, std, gen)
 
+        self.lora_enabled = True
+        if cfg.lora_rank > 0:
+            # low-rank adapters (reference: peft LoRA, siirl/engine/fsdp_workers.py:824-895): y += (x A^T) B^T * alpha/r;
+            # A is small random, B zero, so training starts at the base model; with the adapters switched off
+            # (``lora_enabled = False``) the same module is the frozen reference policy
+            assert not cfg.is_moe and cfg.lora_rank % 8 == 0, "LoRA: dense layers, rank a multiple of 8"
+            r = cfg.lora_rank
+            for name, (n_out, n_in) in {"qkv_proj": (cfg.qkv_width, H), "o_proj": (H, cfg.q_width),
+                                        "gate_up_proj": (2 * cfg.intermediate_size, H),
+                                        "down_proj": (H, cfg.intermediate_size)}.items():
+                setattr(self, f"{name}_lora_A", _param((r, n_in), dtype, device, 1.0 / r, gen))
+                setattr(self, f"{name}_lora_B", _param((n_out, r), dtype, device, 0, gen))
+
+    def _linear(self, x: torch.Tensor, name: str, bias=None) -> torch.Tensor:
+        y = ops.linear(x, getattr(self, f"{name}_weight"), bias)
+        if self.cfg.lora_rank > 0 and self.lora_enabled:
+            a = ops.linear(x, getattr(self, f"{name}_lora_A"))
+            y = y + ops.linear(a, getattr(self, f"{name}_lora_B")) * (self.cfg.lora_alpha / self.cfg.lora_rank)
+        return y
+
     # ---- pieces shared by the training and the cached (rollout) paths --------------------------
     def qkv(self, x: torch.Tensor, positions: torch.Tensor, rope) -> torch.Tensor:
         cfg = self.cfg
@@ -85,7 +105,7 @@ class DecoderLayer(nn.Module):
     def qkv_pre_rope(self, x: torch.Tensor) -> torch.Tensor:
         """QKV projection (+ per-head q/k RMSNorm for the Qwen3 family), before rotary embedding."""
         cfg = self.cfg
-        qkv = ops.linear(x, self.qkv_proj_weight, self.qkv_proj_bias)
+        qkv = self._linear(x, "qkv_proj", self.qkv_proj_bias)
         if cfg.qk_norm:
             T = qkv.shape[0]
             nrot = cfg.num_heads + cfg.num_kv_heads
@@ -102,7 +122,7 @@ class DecoderLayer(nn.Module):
             return moe_forward(x, self.router_weight, self.experts_gate_up, self.experts_down,
                                self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, ep=self.ep,
                                pad_tokens=self.ep_pad_tokens)
-        return ops.linear(ops.swiglu(ops.linear(x, self.gate_up_proj_weight)), self.down_proj_weight)
+        return self._linear(ops.swiglu(self._linear(x, "gate_up_proj")), "down_proj")
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], positions, info: SeqInfo, rope, causal=True):
         """``h`` is the residual stream, ``delta`` the previous sub-layer output not yet added to it."""
@@ -121,7 +141,7 @@ class DecoderLayer(nn.Module):
             a = sp.heads_to_seq(a, [(0, cfg.num_heads * D)])
         else:
             a = attention_packed(qkv, info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=causal)
-        attn_out = ops.linear(a, self.o_proj_weight)
+        attn_out = self._linear(a, "o_proj")
         x, h = ops.rmsnorm(attn_out, self.post_attention_layernorm, cfg.rms_norm_eps, residual=h)
         return h, self.mlp(x)
 
@@ -213,6 +233,10 @@ class DecoderLM(nn.Module):
         r = sp.rank if sp is not None else 0
         return r * Tl, (r + 1) * Tl, Tl * n - T
 
+    def set_lora_enabled(self, on: bool) -> None:
+        for layer in self.layers:
+            layer.lora_enabled = on
+
     def attach_sequence_parallel(self, sp) -> None:
         self.sp = sp
         for layer in self.layers:
@@ -263,7 +287,7 @@ class DecoderLM(nn.Module):
             else:
                 a = kvc.decode_attention(qkv, cache[li], seq_lens, block_table, cfg.num_heads, cfg.num_kv_heads,
                                          cfg.head_dim)
-            attn_out = ops.linear(a, layer.o_proj_weight)
+            attn_out = layer._linear(a, "o_proj")
             x, h = ops.rmsnorm(attn_out, layer.post_attention_layernorm, cfg.rms_norm_eps, residual=h)
             delta = layer.mlp(x)
         out, _ = ops.rmsnorm(delta, self.norm, cfg.rms_norm_eps, residual=h)

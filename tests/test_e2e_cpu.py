@@ -96,3 +96,17 @@ def test_ulysses_and_tensor_parallel_rollout_two_ranks(tmp_path):
     for r in m:
         assert r["actor/grad_norm"] > 0 and 0.0 <= r["critic/score/mean"] <= 1.0
         assert r["perf/total_num_tokens"] > 8 * 4 * 17
+
+
+def test_lora_adapters_train_against_the_frozen_base(tmp_path):
+    """LoRA: only the adapters are in the optimizer store; the reference policy is the same model with the
+    adapters switched off, so the KL term starts at zero and becomes positive once the adapters move."""
+    out = _run(["actor_rollout_ref.model.lora_rank=8", "actor_rollout_ref.model.lora_alpha=16",
+                "actor_rollout_ref.actor.optim.lr=1e-3", "trainer.n_gpus_per_node=1",
+                f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=3",
+                "trainer.save_freq=-1"], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2, 3]
+    assert m[0]["actor/kl_loss"] == 0.0 and m[2]["actor/kl_loss"] > 0.0
+    assert all(r["actor/grad_norm"] > 0 for r in m)
