@@ -55,6 +55,8 @@ class PartitionedRLHFDataset(Dataset):
         self.rank, self.world = ddp_rank, ddp_world_size
         self.is_eval = is_eval
         self.max_prompt_length = self.cfg.max_prompt_length
+        self._full_config = config if hasattr(config, "actor_rollout_ref") else None
+        self._vl = None
         self.rows: List[Dict[str, Any]] = []
         files = self.cfg.val_files if is_eval else self.cfg.train_files
         if isinstance(files, str):
@@ -133,9 +135,27 @@ class PartitionedRLHFDataset(Dataset):
     def __len__(self) -> int:
         return len(self.rows)
 
+    def _vl_processor(self):
+        """Image processor of the policy's vision tower (built on first use from the model configuration)."""
+        if self._vl is None:
+            from ...models.config import get_config
+            from ...models.vision_processor import VLProcessor
+            m = self._full_config.actor_rollout_ref.model
+            mcfg = get_config(m.arch_preset or m.path, dict(m.override_config or {}))
+            if mcfg.vision is None:
+                raise ValueError("the dataset has images but the model has no vision tower")
+            self._vl = VLProcessor(mcfg, m.image_min_pixels, m.image_max_pixels)
+        return self._vl
+
     def __getitem__(self, idx: int) -> Dict[str, Any]:
         row = self.rows[idx]
         ids = self._prompt_ids(row)
+        mm_inputs = None
+        images = row.get(self.cfg.image_key) if self.cfg.image_key in row else None
+        if images is not None and len(images) > 0 and self._full_config is not None:
+            out = self._vl_processor()(ids, list(images))
+            ids = out["input_ids"]
+            mm_inputs = {"pixel_values": out["pixel_values"], "image_grid_thw": out["image_grid_thw"]}
         input_ids, mask, pos = left_pad(ids, self.max_prompt_length, self.tokenizer.pad_token_id, self.cfg.truncation)
         item: Dict[str, Any] = {
             "input_ids": input_ids, "attention_mask": mask, "position_ids": pos,
@@ -145,8 +165,8 @@ class PartitionedRLHFDataset(Dataset):
             "index": (row.get("extra_info") or {}).get("index", idx),
             "padded_duplicate": bool(row.get("padded_duplicate", False)),
         }
-        if self.cfg.image_key in row and row[self.cfg.image_key] is not None:
-            item["multi_modal_data"] = {"image": row[self.cfg.image_key]}
+        if mm_inputs is not None:
+            item["multi_modal_inputs"] = mm_inputs       # per-sample dict: ragged, travels as a non-tensor field
         if "pixel_values" in row:
             item["pixel_values"] = row["pixel_values"]
             item["image_grid_thw"] = row["image_grid_thw"]
@@ -186,6 +206,15 @@ def _synthetic_rows(cfg, tokenizer, is_eval: bool) -> List[Dict[str, Any]]:
             L = rng.randint(lo, hi)
             ids = [rng.randint(3, vocab - 1) for _ in range(L)]
             rows.append({"prompt_ids": ids, "data_source": f"synthetic/{kind}",
+                         "reward_model": {"style": "rule", "ground_truth": ""},
+                         "extra_info": {"index": i, "seed": rng.randint(0, 2 ** 31)}})
+        elif kind == "vl":
+            L = rng.randint(lo, hi)
+            ids = [rng.randint(3, min(vocab, 1000) - 1) for _ in range(L)]
+            side = cfg.synthetic_image_size
+            img = torch.randint(0, 256, (side, side, 3), dtype=torch.uint8,
+                                generator=torch.Generator().manual_seed(rng.randint(0, 2 ** 31)))
+            rows.append({"prompt_ids": ids, "images": [img], "data_source": "synthetic/parity",
                          "reward_model": {"style": "rule", "ground_truth": ""},
                          "extra_info": {"index": i, "seed": rng.randint(0, 2 ** 31)}})
         elif kind == "embodied":

@@ -139,6 +139,13 @@ class _ModelWorkerBase:
             for p in self.model.parameters():
                 p.requires_grad_(False)
 
+    def _vl_processor(self):
+        if getattr(self, "_vlp", None) is None:
+            from ..models.vision_processor import VLProcessor
+            self._vlp = VLProcessor(self.model_config, self.config.model.image_min_pixels,
+                                    self.config.model.image_max_pixels)
+        return self._vlp
+
     def _attach_sequence_parallel(self, model) -> None:
         """Ulysses groups are consecutive blocks of ``ulysses_sequence_parallel_size`` ranks of the worker's group;
         every rank creates all of them in the same order (``new_group`` is collective)."""
@@ -200,6 +207,23 @@ class _ModelWorkerBase:
             img_mask[(first[:, None] + torch.arange(proc.tokens_per_image, device=self.device)[None, :]).flatten()] = True
             mm = {"pixel_values": pv, "image_grid_thw": grid, "image_mask": img_mask}
             positions = torch.cat([proc.rope_layout(n)[0] for n in pk.info.seqlens], 1).to(self.device)
+        if "multi_modal_inputs" in mb.non_tensors:
+            # vision-language rows: patches of all rows in row order; placeholders are the image-token ids of the
+            # PROMPT part only (a sampled response token may collide with the placeholder id); 3-row rope positions
+            proc = self._vl_processor()
+            mmi = mb.non_tensors["multi_modal_inputs"]
+            R = mb["responses"].shape[1]
+            am = mb["attention_mask"].to(self.device).bool()
+            in_prompt = torch.zeros_like(am)
+            in_prompt[:, : am.shape[1] - R] = True
+            ids2d = mb["input_ids"].to(self.device)
+            img_mask = ((ids2d == self.model_config.image_token_id) & in_prompt)[am]
+            pos_rows = []
+            for i in range(ids2d.shape[0]):
+                pos_rows.append(proc.rope(ids2d[i][am[i]].cpu(), mmi[i]["image_grid_thw"])[0])
+            positions = torch.cat(pos_rows, 1).to(self.device)
+            mm = {"pixel_values": torch.cat([m["pixel_values"] for m in mmi]).to(self.device, model.embed_tokens.dtype),
+                  "image_grid_thw": torch.cat([m["image_grid_thw"] for m in mmi]), "image_mask": img_mask}
         hidden = model.forward_hidden(pk.input_ids, positions, pk.info, **mm)
         from ..ops.lm_head import lm_head_logprob_entropy
         sp = getattr(model, "sp", None)
@@ -424,12 +448,20 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                             top_p=float(top_p), max_new_tokens=R, eos_token_id=eos, ignore_eos=r.ignore_eos,
                             seed=(r.seed + 7919 * int(meta.get("global_steps", 0))
                                   + 104729 * (self.rank // getattr(self, "_tp_size", 1))) & 0x7FFFFFFF)
-        if uniform:
-            outs = self.engine.generate([list(raw[g[0]]) for g in groups], sp)
-            order = [i for g in groups for i in g]
-        else:
-            outs = self.engine.generate([list(raw[i]) for i in range(B)], sp)
-            order = list(range(B))
+        firsts = [g[0] for g in groups] if uniform else list(range(B))
+        mm_inputs = None
+        if "multi_modal_inputs" in prompts.non_tensors:
+            # image prompts: patches, grid and multimodal rope numbering of every prompt (decode continues at
+            # prompt length - rope delta)
+            proc = self._vl_processor()
+            mm_inputs = []
+            for i in firsts:
+                mmi = prompts.non_tensors["multi_modal_inputs"][i]
+                pos, delta = proc.rope(torch.tensor(list(raw[i])), mmi["image_grid_thw"])
+                mm_inputs.append({"pixel_values": mmi["pixel_values"].to(self.model.embed_tokens.dtype),
+                                  "image_grid_thw": mmi["image_grid_thw"], "rope_positions": pos, "rope_delta": delta})
+        outs = self.engine.generate([list(raw[i]) for i in firsts], sp, mm_inputs=mm_inputs)
+        order = [i for g in groups for i in g] if uniform else list(range(B))
         responses = torch.full((B, R), pad, dtype=torch.int64)
         logps = torch.zeros(B, R, dtype=torch.float32)
         for row, o in zip(order, outs):

@@ -519,6 +519,7 @@ class DataArguments:
     synthetic_size: int = 4096
     synthetic_min_prompt: int = 16
     synthetic_max_prompt: int = 32
+    synthetic_image_size: int = 448     # side of the random RGB image of the ``vl`` synthetic set
 
 
 @dataclass
