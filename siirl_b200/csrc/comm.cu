@@ -140,13 +140,31 @@ __global__ void segment_pull_kernel(PeerPtrs bases, const Segment* __restrict__ 
 // ---------------------------------------------------------------------------------------
 // flag barrier: flags[r] on every rank is an int slot per peer; epoch-tagged so a stale value never matches
 // ---------------------------------------------------------------------------------------
-__global__ void flag_barrier_kernel(PeerPtrs flags, int world, int rank, int epoch, int* status) {
+// `limit_ns` bounds the wait: a barrier is where ranks absorb their skew (seconds after long independent phases),
+// so its limit is a launch parameter instead of the short limit of waits inside compute kernels.
+__global__ void flag_barrier_kernel(PeerPtrs flags, int world, int rank, int epoch, int* status,
+                                    unsigned long long limit_ns) {
   const int t = threadIdx.x;
   if (t < world) {
     __threadfence_system();
     flag_store_release(reinterpret_cast<int*>(flags.p[t]) + rank, epoch);  // tell peer t that this rank arrived
+    const int* mine = reinterpret_cast<int*>(flags.p[rank]) + t;
+    const uint64_t t0 = global_timer_ns();
+    bool ok = false;
+    while (!ok) {
+#pragma unroll 1
+      for (int i = 0; i < 64 && !ok; ++i) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        ok = v >= epoch;
+        if (!ok) __nanosleep(128);
+      }
+      if (!ok && global_timer_ns() - t0 > limit_ns) {
+        if (status) atomicCAS(status, 0, (int)kStatusTimeoutFlag);
+        break;
+      }
+    }
   }
-  if (t < world) flag_wait_ge(reinterpret_cast<int*>(flags.p[rank]) + t, epoch, status);
   __syncthreads();
 }
 
@@ -265,8 +283,10 @@ extern "C" int sb_segment_pull(void* const* bases, int world, const void* segs, 
 }
 
 extern "C" int sb_flag_barrier(void* const* flag_ptrs, int world, int rank, int epoch, int* status,
-                               cudaStream_t stream) {
+                               long long limit_ms, cudaStream_t stream) {
   if (world > kMaxRanks) return -3;
-  flag_barrier_kernel<<<1, 32, 0, stream>>>(to_peers(flag_ptrs, world), world, rank, epoch, status);
+  if (limit_ms <= 0) limit_ms = 2000;
+  flag_barrier_kernel<<<1, 32, 0, stream>>>(to_peers(flag_ptrs, world), world, rank, epoch, status,
+                                            (unsigned long long)limit_ms * 1000000ull);
   return (int)cudaGetLastError();
 }

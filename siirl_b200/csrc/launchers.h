@@ -138,7 +138,8 @@ int sb_adamw_allgather(float* master, float* m, float* v, const float* grad, voi
                        float beta2, float eps, float weight_decay, int step, float max_norm, float grad_scale,
                        cudaStream_t stream);
 int sb_segment_pull(void* const* bases, int world, const void* segs, int n_segs, void* out, cudaStream_t stream);
-int sb_flag_barrier(void* const* flag_ptrs, int world, int rank, int epoch, int* status, cudaStream_t stream);
+int sb_flag_barrier(void* const* flag_ptrs, int world, int rank, int epoch, int* status, long long limit_ms,
+                    cudaStream_t stream);
 }
 
 extern "C" {

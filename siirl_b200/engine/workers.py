@@ -139,6 +139,14 @@ class _ModelWorkerBase:
             for p in self.model.parameters():
                 p.requires_grad_(False)
 
+    def _phase_sync(self) -> None:
+        """Align the ranks of the worker group before a phase whose kernels wait on peers with a short bound (tensor /
+        expert / sequence parallel exchanges): the previous phase may have left them seconds apart."""
+        if self.world > 1 and any(getattr(self, a, None) is not None for a in ("tp_model", "ep_ctx", "_sp_ctx")):
+            if getattr(self, "_sync_word", None) is None:
+                self._sync_word = torch.zeros(1, device=self.device)
+            dist.all_reduce(self._sync_word, group=self.group)
+
     def _vl_processor(self):
         if getattr(self, "_vlp", None) is None:
             from ..models.vision_processor import VLProcessor
@@ -410,6 +418,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         once).  Output adds ``prompts, responses, input_ids [B, P+R], attention_mask, position_ids, response_mask,
         rollout_log_probs``."""
         r = self.config.rollout
+        self._phase_sync()
         if getattr(self, "tp_model", None) is not None:
             self.tp_model.sync_weights()        # column-parallel copies follow the trained replica
         if self.embodied_rollout is not None and "task_id" in prompts:
@@ -517,6 +526,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
 
     def compute_log_prob(self, data: Batch) -> Batch:
         r = self.config.rollout
+        self._phase_sync()
         lp, ent = self._logprob_pass(self.model, data, self.logprob_micro, r.log_prob_use_dynamic_bsz,
                                      r.log_prob_max_token_len_per_gpu, with_entropy=True)
         data["old_log_probs"] = lp
@@ -527,6 +537,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
 
     def compute_ref_log_prob(self, data: Batch) -> Batch:
         rf = self.config.ref
+        self._phase_sync()
         model = self.ref_model if self.ref_model is not None else self.model
         lora_ref = self.ref_model is None and getattr(self.model_config, "lora_rank", 0) > 0
         if lora_ref:
@@ -546,6 +557,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         (reference: siirl/engine/actor/dp_actor.py:349-520).  Returns the metric dict."""
         a = self.config.actor
         t0 = time.time()
+        self._phase_sync()
         self.model.train()
         temperature = float(data.meta.get("temperature", self.config.rollout.temperature)) or 1.0
         loss_mode = a.policy_loss.loss_mode if not a.use_cpgd_loss else "cpgd"
@@ -668,6 +680,7 @@ class CriticWorker(_ModelWorkerBase):
 
     @torch.no_grad()
     def compute_values(self, data: Batch) -> Batch:
+        self._phase_sync()
         c = self.config
         B, R = data["responses"].shape
         out = torch.zeros(B, R, dtype=torch.float32, device=self.device)
@@ -679,6 +692,7 @@ class CriticWorker(_ModelWorkerBase):
         return data
 
     def update_critic(self, data: Batch) -> Dict[str, Any]:
+        self._phase_sync()
         c = self.config
         self.model.train()
         metrics: Dict[str, List[torch.Tensor]] = {}
@@ -723,6 +737,7 @@ class RewardModelWorker(_ModelWorkerBase):
 
     @torch.no_grad()
     def compute_rm_score(self, data: Batch) -> Batch:
+        self._phase_sync()
         c = self.config
         B, R = data["responses"].shape
         scores = torch.zeros(B, R, dtype=torch.float32, device=self.device)

@@ -53,6 +53,7 @@ class SymmComm:
         self._shard_grad: Optional[torch.Tensor] = None
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=device)
         self._norm = torch.zeros(1, dtype=torch.float32, device=device)
+        self._sync_word = torch.zeros(1, dtype=torch.float32, device=device)
 
     @classmethod
     def create(cls, group=None) -> "SymmComm":
@@ -107,15 +108,20 @@ class SymmComm:
         return sb
 
     # ---- synchronisation ------------------------------------------------------------------------------
-    def barrier(self, use_flags: bool = True) -> None:
-        """Stream-ordered barrier across the ranks (flag kernel with bounded waits, or a 1-element all-reduce)."""
+    barrier_limit_ms = 30000    # bound of the device-side wait of one barrier
+
+    def barrier(self, use_flags: bool = True, resync: bool = False) -> None:
+        """Stream-ordered barrier across the ranks: flag kernel with a bounded wait, or a 1-element all-reduce.
+        ``resync=True`` puts the all-reduce in front of the flags: use it where ranks arrive after long independent
+        work (rollout, a whole backward pass), so that the bounded device-side wait only ever sees a small skew."""
+        if resync or not use_flags:
+            dist.all_reduce(self._sync_word, group=self.group)
         if use_flags:
             self._epoch += 1
             _lib.check(self.L.sb_flag_barrier(self._flags.ptr_array, self.world, self.rank, self._epoch,
-                                              _lib.ptr(_lib.status_word(self.device)), _lib.stream()),
+                                              _lib.ptr(_lib.status_word(self.device)),
+                                              ctypes.c_longlong(self.barrier_limit_ms), _lib.stream()),
                        "sb_flag_barrier")
-        else:
-            dist.all_reduce(self._norm.clone(), group=self.group)
 
     # ---- fused optimizer step ---------------------------------------------------------------------------
     def fused_rs_adamw_ag(self, store, lr: float, betas, eps: float, weight_decay: float,
@@ -124,7 +130,7 @@ class SymmComm:
         if self._shard_grad is None or self._shard_grad.numel() != store.shard_size:
             self._shard_grad = torch.empty(store.shard_size, dtype=torch.float32, device=self.device)
         f, ll = ctypes.c_float, ctypes.c_longlong
-        self.barrier()                                  # every rank's backward has finished writing its gradients
+        self.barrier(resync=True)                       # every rank's backward has finished writing its gradients
         self._sumsq.zero_()
         _lib.check(self.L.sb_rs_reduce(grads.ptr_array, self.world, self.rank, ll(store.lo), ll(store.shard_size),
                                        _lib.ptr(self._shard_grad), _lib.ptr(self._sumsq), _lib.stream()),
