@@ -103,6 +103,10 @@ class RolloutEngine:
         self.lockstep_group = lockstep_group
         if lockstep_group is not None:
             use_cuda_graph = False
+        # Device memory the engine may use for KV blocks while it is awake (the trainer's fp32 gradient buffer, idle
+        # and about to be zeroed between an optimizer step and the next backward): on a 180 GB part with the Adam
+        # state resident this is what lets all sequences of a step decode in one wave.  Its contents are clobbered.
+        self.borrowed: Optional[torch.Tensor] = None
         self.model = model
         self.cfg = model.cfg
         self.device = model.embed_tokens.device
@@ -115,7 +119,7 @@ class RolloutEngine:
         self.max_num_batched_tokens = max_num_batched_tokens
         self._requested_blocks = num_blocks
         self._mem_util = gpu_memory_utilization
-        self.cache: Optional[torch.Tensor] = None
+        self.cache: Optional[List[torch.Tensor]] = None      # per layer [blocks, 2, Hkv, 64, D]
         self.alloc: Optional[BlockAllocator] = None
         self._graphs: Dict[int, object] = {}
         self._graph_launches: Dict[int, int] = {}
@@ -133,16 +137,32 @@ class RolloutEngine:
             return
         c = self.cfg
         nb = self._requested_blocks
+        esize = torch.finfo(self.dtype).bits // 8
+        lent = 0
+        if self.borrowed is not None and self.borrowed.device == self.device:
+            lent = self.borrowed.numel() * self.borrowed.element_size()
         if nb is None:
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()        # cached training blocks would hide free memory from the query
                 free, _total = torch.cuda.mem_get_info(self.device)
-                nb = max(16, int(free * self._mem_util) // self._block_bytes())
+                nb = max(16, (int(free * self._mem_util) + lent) // self._block_bytes())
             else:
                 nb = max(16, self.max_num_seqs * self.max_blocks_per_seq)
             nb = min(nb, self.max_num_seqs * self.max_blocks_per_seq + 8)
-        self.cache = torch.zeros(c.num_layers, nb, 2, c.num_kv_heads, BLOCK, c.head_dim, dtype=self.dtype,
-                                 device=self.device)
+        # one tensor per layer [nb, 2, Hkv, 64, D]: the first layers live in the borrowed buffer, the rest is new
+        per_layer = nb * 2 * c.num_kv_heads * BLOCK * c.head_dim
+        n_lent = min(c.num_layers, lent // (per_layer * esize)) if lent else 0
+        shape = (nb, 2, c.num_kv_heads, BLOCK, c.head_dim)
+        layers = []
+        if n_lent:
+            flat = self.borrowed.reshape(-1).view(torch.uint8)[: n_lent * per_layer * esize].view(self.dtype)
+            flat.zero_()    # rows past a sequence's length are multiplied by zero weights: they must be finite
+            layers += [flat[i * per_layer:(i + 1) * per_layer].view(shape) for i in range(n_lent)]
+        if n_lent < c.num_layers:
+            own = torch.zeros(c.num_layers - n_lent, *shape, dtype=self.dtype, device=self.device)
+            layers += [own[i] for i in range(c.num_layers - n_lent)]
+        self.cache = layers
+        self.kv_layout = {"blocks": nb, "layers_in_borrowed_memory": n_lent}
         self.alloc = BlockAllocator(nb)
         self.num_slots = 0
         self._graphs.clear()

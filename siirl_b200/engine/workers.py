@@ -356,6 +356,11 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                                         lockstep_group=self.group if getattr(self, "ep_ctx", None) is not None
                                         and self.world > 1 else None,
                                         **dict(r.engine_kwargs.native or {}))
+            if r.free_cache_engine and self._is_actor and getattr(self, "store", None) is not None \
+                    and getattr(r, "kv_borrow_grad_buffer", True):
+                # the fp32 gradient buffer is idle (and zeroed again) between an optimizer step and the next backward,
+                # exactly while the engine is awake: lend it to the KV arena
+                self.engine.borrowed = self.store.flat_grad
             if r.free_cache_engine:
                 self.engine.sleep()
         if self._embodied:

@@ -290,6 +290,7 @@ class RolloutArguments:
     layer_name_map: LayerNameMapArguments = _dc(LayerNameMapArguments)
     seed: int = 0
     mode: str = "sync"
+    kv_borrow_grad_buffer: bool = True     # native: lend the idle fp32 gradient buffer to the KV arena
     multi_turn: MultiTurnArguments = _dc(MultiTurnArguments)
     micro_batch_size: Optional[int] = None
     engine_kwargs: EngineArguments = _dc(EngineArguments)

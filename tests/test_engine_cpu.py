@@ -155,3 +155,32 @@ def test_reward_managers_place_score_at_last_valid_token():
     cfg = parse_config(["reward_model.overlong_buffer.enable=True", "reward_model.overlong_buffer.len=2"])
     d = DAPORewardManager(tok, max_resp_len=4, overlong_buffer_cfg=cfg.reward_model.overlong_buffer)(b)
     assert d[0, 2].item() == pytest.approx(1.0 - 0.5)        # length 3, expected 2 -> exceed 1 of buffer 2
+
+
+def test_kv_arena_in_borrowed_memory_gives_the_same_tokens():
+    """The engine may place KV blocks in a lent buffer (the trainer's idle gradient memory): same greedy output, the
+    lent buffer is clobbered, and after sleep() nothing of it is referenced."""
+    import torch
+
+    from siirl_b200.engine.rollout.native_engine import RolloutEngine, SamplingParams
+    from siirl_b200.models.config import get_config
+    from siirl_b200.models.decoder import build_model
+    cfg = get_config("tiny")
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=2)
+    prompts = [[5 + (3 * i + j) % 900 for j in range(10 + 7 * i)] for i in range(3)]
+    sp = SamplingParams(n=2, temperature=0.0, max_new_tokens=9, ignore_eos=True)
+    plain = RolloutEngine(model, max_num_seqs=8, max_model_len=128, num_blocks=24)
+    want = [o.token_ids for o in plain.generate(prompts, sp)]
+    eng = RolloutEngine(model, max_num_seqs=8, max_model_len=128, num_blocks=24)
+    eng.sleep()
+    per_layer = 24 * 2 * cfg.num_kv_heads * 64 * cfg.head_dim
+    lent = torch.full((per_layer + 100,), float("nan"))          # room for ONE of the two layers, filled with NaN
+    eng.borrowed = lent
+    eng.wake_up()
+    assert eng.kv_layout == {"blocks": 24, "layers_in_borrowed_memory": 1}
+    assert eng.cache[0].data_ptr() == lent.data_ptr()
+    got = [o.token_ids for o in eng.generate(prompts, sp)]
+    assert got == want
+    assert not torch.isnan(lent[:per_layer]).any() and float(lent[:per_layer].abs().sum()) > 0
+    eng.sleep()
+    assert eng.cache is None

@@ -60,7 +60,7 @@ def main():
     ctx2 = TPContext(dist.group.WORLD, comm, max_rows=1024, max_cols=cfg.hidden_size, max_tiles=64)
     tp_model = TPDecoder(model, ctx2)
     engine = RolloutEngine(tp_model, max_num_seqs=8, max_model_len=128, num_blocks=32)
-    assert engine.cache.shape[3] == cfg.num_kv_heads // world
+    assert engine.cache[0].shape[2] == cfg.num_kv_heads // world
     outs = engine.generate(prompts, sp)
     got_tokens = [o.token_ids for o in outs]
     same = sum(int(a == b) for x, y in zip(want_tokens, got_tokens) for a, b in zip(x, y))
