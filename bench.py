@@ -14,6 +14,12 @@ reports why it cannot run here.
 """
 from __future__ import annotations
 
+import os
+
+# one GPU holds weights, reference copy, fp32 gradients and the whole Adam state (151 GB of 180): growing segments
+# instead of fixed-size blocks keeps the remaining memory usable for the 41k-token micro-batches
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
 import argparse
 import json
 import os
@@ -42,6 +48,7 @@ def parse_args():
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--rollout-tp", type=int, default=1)
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--offload", action="store_true", help="keep activation checkpoints in pinned host memory")
     ap.add_argument("--e2e-steps", type=int, default=0, help="steps of the end-to-end region (0: 1 when a step takes "
                     "longer than a minute, else --steps)")
     return ap.parse_args()
@@ -129,9 +136,7 @@ def build_config(args, world: int):
         f"data.train_batch_size={bs}", "data.shuffle=True",
         f"actor_rollout_ref.model.arch_preset={args.model}", "actor_rollout_ref.model.random_init=True",
         "actor_rollout_ref.model.enable_gradient_checkpointing=True",
-        # one GPU holds all of the fp32 master weights and Adam moments (91 GB) next to weights, reference copy and
-        # gradients (60 GB): the per-layer checkpoints of a 41k-token micro-batch then go to pinned host memory
-        f"actor_rollout_ref.model.enable_activation_offload={world == 1}",
+        f"actor_rollout_ref.model.enable_activation_offload={bool(args.offload)}",
         f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0",
         f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp}",
         f"actor_rollout_ref.rollout.max_num_seqs={args.prompts_per_gpu * args.n}",

@@ -219,7 +219,11 @@ class DecoderLM(nn.Module):
         with ctx:   # tensors saved for backward move to pinned host memory when activation offload is attached
             for layer in self.layers:
                 if self.gradient_checkpointing and torch.is_grad_enabled():
-                    h, delta = ckpt.checkpoint(layer, h, delta, positions, info, rope, use_reentrant=False)
+                    if delta is not None:
+                        # fold the pending sub-layer output into the residual stream first: the checkpoint then
+                        # keeps ONE [T, H] tensor per layer instead of two
+                        h, delta = h + delta, None
+                    h, delta = ckpt.checkpoint(layer, h, None, positions, info, rope, use_reentrant=False)
                 else:
                     h, delta = layer(h, delta, positions, info, rope)
         out, _ = ops.rmsnorm(delta, self.norm, self.cfg.rms_norm_eps, residual=h)
