@@ -137,6 +137,9 @@ def build_config(args, world: int):
         f"actor_rollout_ref.model.arch_preset={args.model}", "actor_rollout_ref.model.random_init=True",
         "actor_rollout_ref.model.enable_gradient_checkpointing=True",
         f"actor_rollout_ref.model.enable_activation_offload={bool(args.offload)}",
+        # single GPU: the whole Adam state (8 bytes per parameter) is idle during rollout; in pinned host memory it
+        # leaves room for the KV blocks of all 256 sequences of the step
+        f"actor_rollout_ref.actor.fsdp_config.optimizer_offload={world == 1}",
         f"actor_rollout_ref.rollout.n={args.n}", "actor_rollout_ref.rollout.temperature=1.0",
         f"actor_rollout_ref.rollout.tensor_model_parallel_size={args.rollout_tp}",
         f"actor_rollout_ref.rollout.max_num_seqs={args.prompts_per_gpu * args.n}",

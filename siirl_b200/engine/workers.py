@@ -424,6 +424,9 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         rollout_log_probs``."""
         r = self.config.rollout
         self._phase_sync()
+        if self._is_actor and getattr(self, "store", None) is not None and \
+                self.config.actor.fsdp_config.optimizer_offload:
+            self.store.offload_state()          # Adam moments wait in pinned host memory until the next update
         if getattr(self, "tp_model", None) is not None:
             self.tp_model.sync_weights()        # column-parallel copies follow the trained replica
         if self.embodied_rollout is not None and "task_id" in prompts:

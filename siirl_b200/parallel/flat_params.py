@@ -91,6 +91,31 @@ class FlatParamStore:
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._norm = torch.zeros(1, dtype=torch.float32, device=self.device)
 
+    # ---- optimizer-state offload ------------------------------------------------------------------
+    def offload_state(self) -> None:
+        """Move the Adam moments of the owned shard to pinned host memory and release their device memory (the
+        reference's ``fsdp_config.optimizer_offload``).  They are idle from the end of an optimizer step to the
+        next one; on a single GPU they are 8 bytes per parameter that the rollout's KV arena can use."""
+        if self.master is None or getattr(self, "_offloaded", False) or self.device.type != "cuda":
+            return
+        host = self.__dict__.setdefault("_host_state", {})
+        for name in ("exp_avg", "exp_avg_sq"):
+            t = getattr(self, name)
+            if name not in host:
+                host[name] = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+            host[name].copy_(t, non_blocking=True)
+        torch.cuda.synchronize(self.device)
+        self.exp_avg = self.exp_avg_sq = None
+        self._offloaded = True
+        torch.cuda.empty_cache()
+
+    def reload_state(self) -> None:
+        if not getattr(self, "_offloaded", False):
+            return
+        self.exp_avg = self._host_state["exp_avg"].to(self.device, non_blocking=True)
+        self.exp_avg_sq = self._host_state["exp_avg_sq"].to(self.device, non_blocking=True)
+        self._offloaded = False
+
     # ---- gradients ----------------------------------------------------------------------------
     def zero_grad(self) -> None:
         self.flat_grad.zero_()
@@ -132,6 +157,7 @@ class FlatParamStore:
         gradients held by another store) is added to the squared norm before the ranks sum it;
         ``global_sumsq`` replaces the norm computation altogether (stores of rank-local parameters)."""
         assert self.master is not None, "store was built without optimizer state"
+        self.reload_state()
         self.collect_grads()
         self.step_count += 1
         if self.world > 1 and self.comm is not None and self.device.type == "cuda":
@@ -208,6 +234,7 @@ class FlatParamStore:
 
     # ---- state (sharded checkpoints) ----------------------------------------------------------
     def shard_state_dict(self) -> Dict[str, object]:
+        self.reload_state()
         return {"layout": {"total": self.total, "world": self.world, "rank": self.rank,
                            "offsets": {n: (o, k, list(s)) for n, (o, k, s) in self.offsets.items()}},
                 "master": self.master.cpu() if self.master is not None else None,
@@ -216,6 +243,7 @@ class FlatParamStore:
                 "step": self.step_count}
 
     def load_shard_state_dict(self, state: Dict[str, object]) -> None:
+        self.reload_state()
         lay = state["layout"]
         if lay["total"] != self.total or lay["world"] != self.world:
             raise ValueError("shard layout differs (world size changed?): use load_full_state")
@@ -231,6 +259,7 @@ class FlatParamStore:
     def load_full_state(self, master: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
                         step: int) -> None:
         """Elastic resume: load from unsharded state tensors and keep this rank's shard."""
+        self.reload_state()
         self.master.copy_(master[self.lo:self.hi].to(self.device))
         self.exp_avg.copy_(exp_avg[self.lo:self.hi].to(self.device))
         self.exp_avg_sq.copy_(exp_avg_sq[self.lo:self.hi].to(self.device))
@@ -292,6 +321,10 @@ class ExpertSplitStore:
     def zero_grad(self) -> None:
         self.dense.zero_grad()
         self.expert.zero_grad()
+
+    def offload_state(self) -> None:
+        self.dense.offload_state()
+        self.expert.offload_state()
 
     def step(self, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
              max_grad_norm: float = 1.0) -> torch.Tensor:
