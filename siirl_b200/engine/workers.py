@@ -566,6 +566,8 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         a = self.config.actor
         t0 = time.time()
         self._phase_sync()
+        if hasattr(self.store, "reload_state"):
+            self.store.reload_state(wait=False)     # parked Adam moments stream back while the micro-batches run
         self.model.train()
         temperature = float(data.meta.get("temperature", self.config.rollout.temperature)) or 1.0
         loss_mode = a.policy_loss.loss_mode if not a.use_cpgd_loss else "cpgd"

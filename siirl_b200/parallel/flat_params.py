@@ -109,12 +109,24 @@ class FlatParamStore:
         self._offloaded = True
         torch.cuda.empty_cache()
 
-    def reload_state(self) -> None:
-        if not getattr(self, "_offloaded", False):
-            return
-        self.exp_avg = self._host_state["exp_avg"].to(self.device, non_blocking=True)
-        self.exp_avg_sq = self._host_state["exp_avg_sq"].to(self.device, non_blocking=True)
-        self._offloaded = False
+    def reload_state(self, wait: bool = True) -> None:
+        """Bring the moments back.  ``wait=False`` starts the copies on a side stream (call it when the backward
+        passes begin); the optimizer step, or any later call with ``wait=True``, joins them."""
+        if getattr(self, "_offloaded", False):
+            side = self.__dict__.setdefault("_side_stream", torch.cuda.Stream(self.device))
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self.exp_avg = self._host_state["exp_avg"].to(self.device, non_blocking=True)
+                self.exp_avg_sq = self._host_state["exp_avg_sq"].to(self.device, non_blocking=True)
+                self._reload_event = torch.cuda.Event()
+                self._reload_event.record(side)
+            self._offloaded = False
+        ev = getattr(self, "_reload_event", None)
+        if wait and ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
+            self.exp_avg.record_stream(torch.cuda.current_stream(self.device))
+            self.exp_avg_sq.record_stream(torch.cuda.current_stream(self.device))
+            self._reload_event = None
 
     # ---- gradients ----------------------------------------------------------------------------
     def zero_grad(self) -> None:
@@ -325,6 +337,10 @@ class ExpertSplitStore:
     def offload_state(self) -> None:
         self.dense.offload_state()
         self.expert.offload_state()
+
+    def reload_state(self, wait: bool = True) -> None:
+        self.dense.reload_state(wait)
+        self.expert.reload_state(wait)
 
     def step(self, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
              max_grad_norm: float = 1.0) -> torch.Tensor:
