@@ -107,13 +107,22 @@ _NUM_SMS = 148
 
 
 def _skinny_splits(M: int, N: int, K: int) -> int:
-    """Split-K factor for a GEMM with few rows (decode): enough (n-tile, k-slice) pairs to give every SM a slice
-    of the weight matrix to stream.  1 means the plain kernel already fills the machine."""
+    """Split-K factor for a GEMM with few rows (decode): enough (tile, k-slice) work items to give every SM a
+    slice of the weight matrix to stream, chosen so that the items fill whole waves of the persistent grid (56
+    tiles x 3 slices = 168 items would leave a second wave of 20 CTAs; x 5 = 280 fills 1.9 waves).  1 means the
+    plain kernel already fills the machine."""
     n_tiles = (N + 127) // 128 * ((M + 127) // 128)
     nkb = (K + 63) // 64
     if n_tiles >= _NUM_SMS or nkb < 8:
         return 1
-    return max(1, min(nkb // 4, round(_NUM_SMS / n_tiles)))
+    best, best_score = 1, -1.0
+    for s in range(1, min(nkb // 4, 16) + 1):
+        items = n_tiles * s
+        waves = (items + _NUM_SMS - 1) // _NUM_SMS
+        score = items / (waves * _NUM_SMS) - 0.01 * s       # wave efficiency, mild preference for fewer slabs
+        if score > best_score:
+            best, best_score = s, score
+    return best
 
 
 def linear_skinny(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
