@@ -120,6 +120,7 @@ class _ModelWorkerBase:
         if ep > 1:
             self._attach_expert_parallel(model_args)
         self._attach_sequence_parallel(self.model)
+        self._attach_context_parallel(self.model)
         if trainable and getattr(model_args, "enable_activation_offload", False) and self.device.type == "cuda":
             from ..utils.model_utils.activation_offload import ActivationOffload
             self.model.activation_offload = ActivationOffload()
@@ -142,7 +143,7 @@ class _ModelWorkerBase:
     def _phase_sync(self) -> None:
         """Align the ranks of the worker group before a phase whose kernels wait on peers with a short bound (tensor /
         expert / sequence parallel exchanges): the previous phase may have left them seconds apart."""
-        if self.world > 1 and any(getattr(self, a, None) is not None for a in ("tp_model", "ep_ctx", "_sp_ctx")):
+        if self.world > 1 and any(getattr(self, a, None) is not None for a in ("tp_model", "ep_ctx", "_sp_ctx", "_cp_ctx")):
             if getattr(self, "_sync_word", None) is None:
                 self._sync_word = torch.zeros(1, device=self.device)
             dist.all_reduce(self._sync_word, group=self.group)
@@ -184,6 +185,39 @@ class _ModelWorkerBase:
             width = (mc.num_heads + 2 * mc.num_kv_heads) * mc.head_dim
             self._sp_ctx = UlyssesSP(mine, comm, max_elems=(tokens // n + n) * width)
         model.attach_sequence_parallel(self._sp_ctx)
+
+    def _attach_context_parallel(self, model) -> None:
+        """Ring (context-parallel) attention groups: consecutive blocks of ``megatron.context_parallel_size`` ranks."""
+        cfgs = getattr(self.config, "actor", self.config)
+        n = int(getattr(getattr(cfgs, "megatron", None), "context_parallel_size", 1) or 1)
+        if n <= 1 or self.world <= 1:
+            return
+        if getattr(self, "_sp_ctx", None) is not None:
+            raise ValueError("context parallelism and Ulysses sequence parallelism cannot be combined")
+        if getattr(self, "_cp_ctx", None) is None:
+            from ..parallel.ring_attention import RingContext
+            mc = self.model_config
+            if self.world % n:
+                raise ValueError(f"context_parallel_size={n} must divide the group size {self.world}")
+            ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
+            mine = None
+            for b in range(self.world // n):
+                g = dist.new_group(ranks[b * n:(b + 1) * n])
+                if b == self.rank // n:
+                    mine = g
+            comm = None
+            if self.device.type == "cuda":
+                from ..parallel.symm import SymmComm
+                comm = SymmComm.create(mine)
+            r = getattr(self.config, "rollout", None)
+            seq = ((r.prompt_length or 512) + (r.response_length or 512)) if r is not None else 4096
+            tokens = max(int(getattr(cfgs, "ppo_max_token_len_per_gpu", 0) or 0),
+                         int(getattr(cfgs, "ppo_micro_batch_size_per_gpu", 0) or 1) * seq, seq)
+            rows = tokens // n + 64 * n
+            self._cp_ctx = RingContext(mine, comm, max_rows=rows,
+                                       qkv_width=(mc.num_heads + 2 * mc.num_kv_heads) * mc.head_dim,
+                                       kv_width=2 * mc.num_kv_heads * mc.head_dim)
+        model.attach_context_parallel(self._cp_ctx)
 
     def _attach_expert_parallel(self, model_args) -> None:
         """One ExpertParallel context per worker (staging buffers sized for the largest packed forward); every MoE
@@ -234,22 +268,27 @@ class _ModelWorkerBase:
                   "image_grid_thw": torch.cat([m["image_grid_thw"] for m in mmi]), "image_mask": img_mask}
         hidden = model.forward_hidden(pk.input_ids, positions, pk.info, **mm)
         from ..ops.lm_head import lm_head_logprob_entropy
-        sp = getattr(model, "sp", None)
-        if sp is not None and sp.sp > 1:
-            # this rank holds rows [lo, hi) of the packed stream: score the selected positions that fall there and
-            # let a differentiable sum over the group complete the [B, R] tensors (every rank then evaluates the
-            # same loss; the backward of the sum returns each rank the gradient of its own entries, sp times)
-            lo, hi, _ = model.sp_slice(pk.input_ids.shape[0])
-            mine = (pk.sel >= lo) & (pk.sel < hi)
-            idx = mine.nonzero(as_tuple=True)[0]
-            lp_l, ent_l = lm_head_logprob_entropy(hidden.index_select(0, pk.sel[idx] - lo), model.head_weight,
+        loc = model.local_row_index(pk.info, pk.input_ids.shape[0]) if hasattr(model, "local_row_index") else None
+        if loc is not None:
+            # sequence / context parallelism: this rank computed only the rows listed in ``loc``.  Score the selected
+            # positions that fall there and let a differentiable sum over the group complete the [B, R] tensors
+            # (every rank then evaluates the same loss; the backward of the sum returns each rank the gradient of
+            # its own entries, once per rank of the group)
+            group = (getattr(model, "sp", None) or getattr(model, "cp", None)).group
+            T = pk.input_ids.shape[0]
+            inv = torch.full((T,), -1, dtype=torch.int64, device=self.device)
+            valid = loc >= 0
+            inv[loc[valid]] = torch.arange(loc.shape[0], device=self.device)[valid]
+            where = inv[pk.sel]
+            idx = (where >= 0).nonzero(as_tuple=True)[0]
+            lp_l, ent_l = lm_head_logprob_entropy(hidden.index_select(0, where[idx]), model.head_weight,
                                                   pk.labels[idx], temperature, with_entropy)
             N = pk.sel.shape[0]
-            lp = _group_sum(torch.zeros(N, dtype=lp_l.dtype, device=lp_l.device).index_put((idx,), lp_l), sp.group)
+            lp = _group_sum(torch.zeros(N, dtype=lp_l.dtype, device=lp_l.device).index_put((idx,), lp_l), group)
             ent = None
             if ent_l is not None:
                 ent = _group_sum(torch.zeros(N, dtype=ent_l.dtype, device=ent_l.device).index_put((idx,), ent_l),
-                                 sp.group)
+                                 group)
             return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
         lp, ent = lm_head_logprob_entropy(hidden.index_select(0, pk.sel), model.head_weight, pk.labels, temperature,
                                           with_entropy)
@@ -334,6 +373,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
             for p in self.ref_model.parameters():
                 p.requires_grad_(False)
             self._attach_sequence_parallel(self.ref_model)
+            self._attach_context_parallel(self.ref_model)
             if self.model is None:
                 self.model_config = mcfg
         if self._is_rollout:

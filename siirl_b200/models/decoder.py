@@ -139,6 +139,11 @@ class DecoderLayer(nn.Module):
             a = attention_packed(sp.seq_to_heads(qkv, parts), info, cfg.num_heads // n, cfg.num_kv_heads // n, D,
                                  causal=causal)
             a = sp.heads_to_seq(a, [(0, cfg.num_heads * D)])
+        elif getattr(self, "cp", None) is not None and self.cp.cp > 1:
+            # context parallel: rows are this rank's chunk of every sequence (``info`` = chunk lengths); K/V of the
+            # earlier chunks come from their owners
+            from ..parallel.ring_attention import ring_attention
+            a = ring_attention(qkv, self.cp, info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim)
         else:
             a = attention_packed(qkv, info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=causal)
         attn_out = self._linear(a, "o_proj")
@@ -212,6 +217,14 @@ class DecoderLM(nn.Module):
                 positions = torch.cat([positions, positions.new_zeros(*positions.shape[:-1], pad)], dim=-1)
                 info = SeqInfo(list(info.seqlens) + [pad], device=input_ids.device)
             input_ids, positions = input_ids[lo:hi], positions[..., lo:hi].contiguous()
+        cp = getattr(self, "cp", None)
+        if cp is not None and cp.cp > 1:
+            assert pixel_values is None and positions.dim() == 1, "context parallelism: text-only, 1-D positions"
+            rows, _, info = self.cp_rows(info)
+            keep = rows >= 0
+            safe = rows.clamp(min=0)
+            input_ids = torch.where(keep, input_ids[safe], torch.zeros_like(safe))
+            positions = torch.where(keep, positions[safe], torch.zeros_like(positions[safe]))
         h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask)
         delta = None
         offload = getattr(self, "activation_offload", None)
@@ -236,6 +249,41 @@ class DecoderLM(nn.Module):
         Tl = (T + n - 1) // n
         r = sp.rank if sp is not None else 0
         return r * Tl, (r + 1) * Tl, Tl * n - T
+
+    def cp_rows(self, info: SeqInfo):
+        """Context parallelism: every sequence is padded to a multiple of the group size and cut into equal chunks;
+        this rank holds chunk ``rank`` of each.  Returns (index into the unpadded packed stream of each local row,
+        -1 for padding; the same for use as a mask; the ``SeqInfo`` of the chunk lengths)."""
+        cp = self.cp
+        n, r = cp.cp, cp.rank
+        dev = self.embed_tokens.device
+        idx, lens, start = [], [], 0
+        for L in info.seqlens:
+            c = (L + n - 1) // n
+            j = torch.arange(r * c, (r + 1) * c)
+            idx.append(torch.where(j < L, j + start, torch.full_like(j, -1)))
+            lens.append(c)
+            start += L
+        rows = torch.cat(idx).to(dev) if idx else torch.zeros(0, dtype=torch.int64, device=dev)
+        return rows, rows >= 0, SeqInfo(lens, device=dev)
+
+    def local_row_index(self, info: SeqInfo, T: int) -> Optional[torch.Tensor]:
+        """Index into the packed stream of every row this rank computes (sequence or context parallelism), -1 for
+        padding rows; ``None`` when the rank computes the whole stream."""
+        sp = getattr(self, "sp", None)
+        cp = getattr(self, "cp", None)
+        if sp is not None and sp.sp > 1:
+            lo, hi, _ = self.sp_slice(T)
+            j = torch.arange(lo, hi, device=self.embed_tokens.device)
+            return torch.where(j < T, j, torch.full_like(j, -1))
+        if cp is not None and cp.cp > 1:
+            return self.cp_rows(info)[0]
+        return None
+
+    def attach_context_parallel(self, cp) -> None:
+        self.cp = cp
+        for layer in self.layers:
+            layer.cp = cp
 
     def set_lora_enabled(self, on: bool) -> None:
         for layer in self.layers:

@@ -110,3 +110,16 @@ def test_lora_adapters_train_against_the_frozen_base(tmp_path):
     assert [r["step"] for r in m] == [1, 2, 3]
     assert m[0]["actor/kl_loss"] == 0.0 and m[2]["actor/kl_loss"] > 0.0
     assert all(r["actor/grad_norm"] > 0 for r in m)
+
+
+def test_context_parallel_ring_attention_two_ranks(tmp_path):
+    """Two ranks as one replica with ring (context-parallel) attention in scoring and training: every sequence is cut
+    in two chunks, K/V of the first chunk travel to the second rank, log-probs are summed over the group."""
+    out = _run(["actor_rollout_ref.actor.megatron.context_parallel_size=2", "actor_rollout_ref.rollout.max_num_seqs=32",
+                f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=2", "trainer.save_freq=-1"],
+               tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    for r in m:
+        assert r["actor/grad_norm"] > 0 and abs(r["actor/ppo_kl"]) < 1e-3       # on-policy: same log-probs twice

@@ -1,0 +1,72 @@
+"""Small host-side utilities: file helpers, device switch, rollout request schema, code scorer, activation offload
+(a no-op without CUDA), wave-aware split-K factor."""
+import os
+
+import torch
+
+
+def test_fs_helpers_local(tmp_path):
+    from siirl_b200.utils.extras import fs
+    src = tmp_path / "a" / "x.txt"
+    fs.makedirs(str(src.parent))
+    src.write_text("hello")
+    assert fs.exists(str(src)) and not fs.is_non_local(str(src))
+    fs.copy(str(src), str(tmp_path / "b" / "y.txt"))
+    assert (tmp_path / "b" / "y.txt").read_text() == "hello"
+    fs.copy(str(tmp_path / "a"), str(tmp_path / "c"))
+    assert (tmp_path / "c" / "x.txt").exists()
+    assert fs.copy_to_local(str(src)) == str(src)
+    assert fs.is_non_local("hdfs://nn/path") and len(fs.md5_encode("hdfs://nn/path")) == 32
+    assert fs.get_local_temp_path("hdfs://nn/dir/model", str(tmp_path)).endswith(os.path.join("", "model"))
+
+
+def test_device_helpers():
+    from siirl_b200.utils.extras import device
+    assert device.get_device_name() in ("cuda", "cpu")
+    assert device.get_nccl_backend() in ("nccl", "gloo")
+    assert device.is_npu_available is False
+    device.device_synchronize()
+
+
+def test_rollout_request_schema():
+    from siirl_b200.engine.rollout.schemas import AsyncRolloutRequest, AsyncRolloutRequestStateEnum, FinishReasonTypeEnum
+    r = AsyncRolloutRequest("r0", prompt_ids=[1, 2, 3], max_response_len=6, max_model_len=20)
+    r.add_assistant_tokens([10, 11], [-0.1, -0.2])
+    r.add_observation_tokens([20, 21, 22])
+    r.add_assistant_tokens([12, 13], [-0.3, -0.4])
+    assert r.response_loss_mask == [1, 1, 0, 0, 0, 1, 1] and r.remaining == 0
+    r.finalize({"tool": 1.0}, "tool_calls")
+    assert r.state == AsyncRolloutRequestStateEnum.COMPLETED and len(r.response_ids) == 6
+    assert r.metrics["finish_reason"] == FinishReasonTypeEnum.TOOL_CALL.value and r.reward_scores == {"tool": 1.0}
+
+
+def test_code_scorer_stdin_and_function_modes():
+    from siirl_b200.utils.reward_score import compute_score
+    ok = compute_score("apps", "```python\na, b = map(int, input().split())\nprint(a + b)\n```",
+                       {"inputs": ["1 2\n", "5 7\n"], "outputs": ["3\n", "12\n"]})
+    assert ok["score"] == 1.0 and ok["passed"] == 2
+    half = compute_score("taco", "```python\ndef add(a, b):\n    return a + b\n```",
+                         {"fn_name": "add", "inputs": [[1, 2], [2, 5]], "outputs": [3, 8]})
+    assert half["score"] == 0.5
+    crash = compute_score("codeforces", "```python\nraise SystemExit(3)\n```", {"inputs": ["1\n"], "outputs": ["1\n"]})
+    assert crash["score"] == 0.0
+
+
+def test_activation_offload_is_transparent_on_cpu():
+    from siirl_b200.utils.model_utils.activation_offload import ActivationOffload
+    off = ActivationOffload(min_bytes=0)
+    x = torch.randn(8, 8, requires_grad=True)
+    with off.region():
+        y = (x * x).sum()
+    y.backward()
+    assert torch.allclose(x.grad, 2 * x)
+
+
+def test_split_k_factor_fills_whole_waves():
+    from siirl_b200.ops.dense import _skinny_splits
+    for M, N, K in ((64, 3584, 18944), (256, 3584, 18944), (256, 3584, 3584), (128, 4608, 3584)):
+        s = _skinny_splits(M, N, K)
+        tiles = (N + 127) // 128 * ((M + 127) // 128) * s
+        waves = -(-tiles // 148)
+        assert tiles / (waves * 148) > 0.9, (M, N, K, s)
+    assert _skinny_splits(256, 37888, 3584) == 1            # already more tiles than SMs

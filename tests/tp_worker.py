@@ -167,6 +167,35 @@ def main():
     if cuda:
         torch.cuda.synchronize()
         lib.check_status()
+    # 7. a decoder under context parallelism (ring attention inside every layer): the rows this rank computes equal
+    #    the single-rank hidden states, and summed parameter gradients match
+    m_cp = build_model(cfg5, dtype=dtype, device=dev, seed=9)
+    m_ref = build_model(cfg5, dtype=dtype, device=dev, seed=9)
+    m_cp.attach_context_parallel(RingContext(dist.group.WORLD, comm, max_rows=256, qkv_width=width,
+                                             kv_width=2 * cfg5.num_kv_heads * cfg5.head_dim))
+    lens7 = [37, 64, 23]
+    info7 = SeqInfo(lens7, device=dev)
+    ids7 = torch.randint(3, cfg5.vocab_size, (sum(lens7),), generator=g).to(dev)
+    coef7 = torch.randn(sum(lens7), cfg5.hidden_size, generator=g).to(dev, dtype)
+    ok_cp = (not cuda) or cfg5.head_dim in (64, 128)
+    if ok_cp:
+        h_ref = m_ref.forward_hidden(ids7, info7.positions, info7)
+        (h_ref.float() * coef7.float()).sum().backward()
+        h_cp = m_cp.forward_hidden(ids7, info7.positions, info7)
+        loc = m_cp.local_row_index(info7, sum(lens7))
+        keep = loc >= 0
+        assert (h_cp[keep].float() - h_ref[loc[keep]].float()).abs().max().item() < tol5, "CP hidden rows"
+        (h_cp[keep].float() * coef7[loc[keep]].float()).sum().backward()
+        for (n1, p1), (_, p2) in zip(m_ref.named_parameters(), m_cp.named_parameters()):
+            if p1.grad is None:
+                continue
+            g2 = p2.grad.float().clone()
+            dist.all_reduce(g2)
+            err = (p1.grad.float() - g2).abs().max().item()
+            assert err < (0.05 * max(1.0, p1.grad.float().abs().max().item()) if cuda else 1e-3), f"CP grad {n1}: {err}"
+    if cuda:
+        torch.cuda.synchronize()
+        lib.check_status()
     dist.barrier()
     if rank == 0:
         print("TP_OK")
