@@ -73,7 +73,7 @@ def bench_optimizer(comm, numel: int):
 def bench_gemm_ar(comm):
     from .. import ops
     from ..parallel.tensor_parallel import TPContext
-    world, rank = dist.get_world_size(), dist.get_rank()
+    world = dist.get_world_size()
     H = 3584
     ctx = TPContext(dist.group.WORLD, comm, max_rows=8192, max_cols=H, max_tiles=64 * 28 + 8,
                     fused_max_rows=1 << 30)     # measure the fused kernel at every size
@@ -98,13 +98,12 @@ def bench_gemm_ar(comm):
         emit(case="gemm+all_reduce", shape=what, M=M, N=H, K_per_rank=ks, world=world, fused_ms=round(fused, 4),
              gemm_plus_nccl_ms=round(nccl, 4), speedup=round(nccl / fused, 3), roofline_ms=round(target, 4),
              frac_of_roofline=round(target / fused, 3))
-    _ = rank
 
 
 def bench_ag_gemm(comm):
     from .. import ops
     from ..parallel.ag_gemm import AgLinear
-    world, rank = dist.get_world_size(), dist.get_rank()
+    world = dist.get_world_size()
     pk = peaks()
     for M, N, K, what in ((8192, 18944 * 2 // 256 // world * 256 * world, 3584, "gate_up (weights sharded by rows)"),
                           (8192, 3584 // (256 * world) * 256 * world, 18944, "down_proj (weights sharded by rows)")):
@@ -127,7 +126,6 @@ def bench_ag_gemm(comm):
              roofline_ms=round(target, 4), frac_of_roofline=round(target / fused, 3))
         del ag, full
         torch.cuda.empty_cache()
-    _ = rank
 
 
 def bench_moe_ep(comm):
@@ -171,14 +169,13 @@ def bench_moe_ep(comm):
     emit(case="moe dispatch+combine", T=T, top_k=k, H=H, world=world, fused_ms=round(t_f, 4),
          nccl_all_to_all_ms=round(t_l, 4), speedup=round(t_l / t_f, 3),
          roofline_ms=round(link / NVLINK_GBS / 1e6, 4), frac_of_roofline=round(link / NVLINK_GBS / 1e6 / t_f, 3))
-    _ = pr
 
 
 def bench_ulysses(comm):
     """Sequence <-> head layout switch of Ulysses SP (Qwen2.5-7B qkv width) by one strided pull kernel, against
     NCCL all_to_all_single with the pack / unpack copies the reference does around it."""
     from ..parallel.ulysses import UlyssesSP
-    world, rank = dist.get_world_size(), dist.get_rank()
+    world = dist.get_world_size()
     hq, hkv, D = 28 // world * world, 4 // world * world or world, 128
     Tl = 32768 // world
     W = (hq + 2 * hkv) * D
@@ -204,7 +201,6 @@ def bench_ulysses(comm):
     emit(case="ulysses seq<->head switch (there and back)", tokens_per_rank=Tl, width=W, world=world,
          fused_ms=round(t_f, 4), nccl_all_to_all_ms=round(t_l, 4), speedup=round(t_l / t_f, 3),
          roofline_ms=round(link / NVLINK_GBS / 1e6, 4), frac_of_roofline=round(link / NVLINK_GBS / 1e6 / t_f, 3))
-    _ = rank
 
 
 def bench_samples(comm):

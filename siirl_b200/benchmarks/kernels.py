@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import math
 import os
 
 import torch
@@ -203,4 +202,3 @@ def main():
 
 if __name__ == "__main__":
     main()
-_ = math

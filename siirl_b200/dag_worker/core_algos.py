@@ -13,7 +13,7 @@ and ``@register_policy_loss(name)`` for
 """
 from __future__ import annotations
 
-from typing import Any, Callable, Dict, Optional, Tuple
+from typing import Callable, Dict, Optional, Tuple
 
 import numpy as np
 import torch
@@ -578,4 +578,3 @@ def compute_advantage(batch, adv_estimator, gamma: float = 1.0, lam: float = 1.0
 
 
 __all__ = [n for n in dir() if not n.startswith("_")]
-_ = Any

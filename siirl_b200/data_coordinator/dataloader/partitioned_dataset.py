@@ -12,7 +12,6 @@ from __future__ import annotations
 import random
 from typing import Any, Dict, List, Optional
 
-import numpy as np
 import torch
 from torch.utils.data import Dataset
 
@@ -226,5 +225,3 @@ def _synthetic_rows(cfg, tokenizer, is_eval: bool) -> List[Dict[str, Any]]:
             raise ValueError(f"unknown synthetic dataset '{kind}'")
     return rows
 
-
-_ = np

@@ -16,7 +16,6 @@ Scheduling model
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -445,5 +444,3 @@ class RolloutEngine:
     def cache_utilization(self) -> float:
         return 1.0 - self.alloc.num_free / self.alloc.num_blocks if self.alloc else 0.0
 
-
-_ = math

@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 import importlib
-from typing import Any, Dict, List
+from typing import Dict, List
 
 import yaml
 
@@ -35,5 +35,3 @@ def initialize_tools_from_config(path_or_dict) -> List[BaseTool]:
 def tools_by_name(tools: List[BaseTool]) -> Dict[str, BaseTool]:
     return {t.name: t for t in tools}
 
-
-_ = Any

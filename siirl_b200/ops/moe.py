@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
-from typing import List, Optional
+from typing import Optional
 
 import torch
 
@@ -327,5 +327,3 @@ def combine(ys: torch.Tensor, w: torch.Tensor, w_all: torch.Tensor, ep: ExpertPa
     values (used for the backward of remote rows)."""
     return _Combine.apply(ys, w.float(), w_all, ep, layout)
 
-
-_ = List

@@ -12,7 +12,7 @@ all-gathered copy.
 from __future__ import annotations
 
 import ctypes
-from typing import List, Optional, Tuple
+from typing import List, Tuple
 
 import torch
 import torch.distributed as dist
@@ -126,5 +126,3 @@ def _switch(x: torch.Tensor, sp: UlyssesSP, parts, to_heads: bool) -> torch.Tens
     assert x.shape[1] == Wl
     return sp._pull(x, ts, (Tl, W))
 
-
-_ = Optional

@@ -14,7 +14,6 @@ from __future__ import annotations
 
 import argparse
 import copy
-import dataclasses
 import difflib
 import sys
 import typing
@@ -253,4 +252,3 @@ def pretty(cfg: Any) -> str:
 
 __all__ = ["ConfigError", "parse_config", "parse_overrides", "load_yaml", "apply_dict", "set_by_path",
            "get_by_path", "merge_node_overrides", "finalize", "pretty"]
-_ = dataclasses
