@@ -119,6 +119,7 @@ class _ModelWorkerBase:
             load_hf_weights(self.model, path)
         if ep > 1:
             self._attach_expert_parallel(model_args)
+        pp_filter = self._attach_pipeline_parallel(self.model, trainable)
         self._attach_sequence_parallel(self.model)
         self._attach_context_parallel(self.model)
         if trainable and getattr(model_args, "enable_activation_offload", False) and self.device.type == "cuda":
@@ -134,6 +135,9 @@ class _ModelWorkerBase:
                     p.requires_grad_(False)
             self.store = FlatParamStore(self.model, group=self.group, comm=self.comm,
                                         param_filter=lambda n: "_lora_" in n)
+        elif trainable and pp_filter is not None:
+            # gradients and optimizer state only for this stage's parameters; data parallelism across pipelines
+            self.store = FlatParamStore(self.model, group=self._pp_dp_group, comm=None, param_filter=pp_filter)
         elif trainable:
             self.store = FlatParamStore(self.model, group=self.group, comm=self.comm)
         else:
@@ -143,7 +147,7 @@ class _ModelWorkerBase:
     def _phase_sync(self) -> None:
         """Align the ranks of the worker group before a phase whose kernels wait on peers with a short bound (tensor /
         expert / sequence parallel exchanges): the previous phase may have left them seconds apart."""
-        if self.world > 1 and any(getattr(self, a, None) is not None for a in ("tp_model", "ep_ctx", "_sp_ctx", "_cp_ctx")):
+        if self.world > 1 and any(getattr(self, a, None) is not None for a in ("tp_model", "ep_ctx", "_sp_ctx", "_cp_ctx", "_pp_ctx")):
             if getattr(self, "_sync_word", None) is None:
                 self._sync_word = torch.zeros(1, device=self.device)
             dist.all_reduce(self._sync_word, group=self.group)
@@ -185,6 +189,38 @@ class _ModelWorkerBase:
             width = (mc.num_heads + 2 * mc.num_kv_heads) * mc.head_dim
             self._sp_ctx = UlyssesSP(mine, comm, max_elems=(tokens // n + n) * width)
         model.attach_sequence_parallel(self._sp_ctx)
+
+    def _attach_pipeline_parallel(self, model, trainable: bool):
+        """Pipeline groups are consecutive blocks of ``megatron.pipeline_model_parallel_size`` ranks; the ranks with
+        the same stage index across blocks form the stage's data-parallel group.  Returns the parameter filter of the
+        stage (or ``None`` without pipeline parallelism)."""
+        cfgs = getattr(self.config, "actor", self.config)
+        n = int(getattr(getattr(cfgs, "megatron", None), "pipeline_model_parallel_size", 1) or 1)
+        if n <= 1 or self.world <= 1:
+            return None
+        if getattr(self, "_pp_ctx", None) is None:
+            from ..parallel.pipeline import PipelineContext
+            if self.world % n:
+                raise ValueError(f"pipeline_model_parallel_size={n} must divide the group size {self.world}")
+            ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
+            mine = dp = None
+            for b in range(self.world // n):
+                g = dist.new_group(ranks[b * n:(b + 1) * n])
+                if b == self.rank // n:
+                    mine = g
+            for s_ in range(n):
+                g = dist.new_group(ranks[s_::n])
+                if s_ == self.rank % n:
+                    dp = g
+            self._pp_ctx = PipelineContext(mine, self.model_config.num_layers)
+            self._pp_dp_group = dp
+        model.attach_pipeline_parallel(self._pp_ctx)
+        pc = self._pp_ctx
+        if trainable:
+            for name, p in model.named_parameters():
+                if not pc.owns_param(name):
+                    p.requires_grad_(False)
+        return pc.owns_param
 
     def _attach_context_parallel(self, model) -> None:
         """Ring (context-parallel) attention groups: consecutive blocks of ``megatron.context_parallel_size`` ranks."""
@@ -266,8 +302,26 @@ class _ModelWorkerBase:
             positions = torch.cat(pos_rows, 1).to(self.device)
             mm = {"pixel_values": torch.cat([m["pixel_values"] for m in mmi]).to(self.device, model.embed_tokens.dtype),
                   "image_grid_thw": torch.cat([m["image_grid_thw"] for m in mmi]), "image_mask": img_mask}
-        hidden = model.forward_hidden(pk.input_ids, positions, pk.info, **mm)
         from ..ops.lm_head import lm_head_logprob_entropy
+        pc = getattr(model, "pp", None)
+        if pc is not None and pc.pp > 1:
+            # pipeline parallel: this rank runs its stage; the last stage scores, every stage receives the values,
+            # and a non-last stage ties them to the handle whose backward pulls the activation gradient
+            from ..parallel import pipeline as P
+            hidden, handle = model.forward_hidden_pp(pk.input_ids, positions, pk.info)
+            N = pk.sel.shape[0]
+            lp_l = ent_l = None
+            if pc.is_last:
+                lp_l, ent_l = lm_head_logprob_entropy(hidden.index_select(0, pk.sel), model.head_weight, pk.labels,
+                                                      temperature, with_entropy)
+            vals = P.broadcast_from_last(pc, [lp_l] + ([ent_l] if with_entropy else []), [(N,)] * (2 if with_entropy
+                                         else 1), [torch.float32] * 2, self.device)
+            lp = lp_l if pc.is_last else vals[0]
+            ent = (ent_l if pc.is_last else vals[1]) if with_entropy else None
+            if handle is not None:
+                lp = lp + 0.0 * handle
+            return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
+        hidden = model.forward_hidden(pk.input_ids, positions, pk.info, **mm)
         loc = model.local_row_index(pk.info, pk.input_ids.shape[0]) if hasattr(model, "local_row_index") else None
         if loc is not None:
             # sequence / context parallelism: this rank computed only the rows listed in ``loc``.  Score the selected
@@ -297,6 +351,9 @@ class _ModelWorkerBase:
     def _optimizer_step(self, optim_cfg, grad_clip: float) -> torch.Tensor:
         lr = lr_at_step(optim_cfg, self.opt_step, max(self.total_training_steps, optim_cfg.total_training_steps))
         norm = self.store.step(lr, tuple(optim_cfg.betas), 1e-8, optim_cfg.weight_decay, grad_clip)
+        if getattr(self, "_pp_ctx", None) is not None:
+            from ..parallel.pipeline import sync_stage_weights
+            sync_stage_weights(self.model, self._pp_ctx)     # every replica gets the stages it does not train
         self.store.zero_grad()
         self.opt_step += 1
         self.last_lr = lr
@@ -372,6 +429,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 load_hf_weights(self.ref_model, margs.path)
             for p in self.ref_model.parameters():
                 p.requires_grad_(False)
+            self._attach_pipeline_parallel(self.ref_model, False)
             self._attach_sequence_parallel(self.ref_model)
             self._attach_context_parallel(self.ref_model)
             if self.model is None:

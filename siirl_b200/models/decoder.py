@@ -208,6 +208,8 @@ class DecoderLM(nn.Module):
         ``[rank * T/sp, (rank + 1) * T/sp)``: the result holds those rows only (see ``sp_slice``)."""
         pmax = int(positions.max().item()) + 1 if positions.numel() else 1
         rope = self.rope_tables(input_ids.device, pmax)
+        if getattr(self, "pp", None) is not None and self.pp.pp > 1:
+            raise RuntimeError("pipeline-parallel models are driven through forward_hidden_pp")
         sp = getattr(self, "sp", None)
         if sp is not None and sp.sp > 1:
             assert pixel_values is None, "sequence parallelism with image inputs is not wired"
@@ -241,6 +243,38 @@ class DecoderLM(nn.Module):
                     h, delta = layer(h, delta, positions, info, rope)
         out, _ = ops.rmsnorm(delta, self.norm, self.cfg.rms_norm_eps, residual=h)
         return out
+
+    def forward_hidden_pp(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo):
+        """Pipeline-parallel forward of this rank's stage.  Returns ``(hidden, None)`` on the last stage (final-norm
+        hidden states) and ``(None, handle)`` elsewhere, where ``handle`` is a 0-d tensor whose backward receives
+        the gradient of the activations sent downstream (``None`` without gradient history)."""
+        from ..parallel import pipeline as P
+        pc = self.pp
+        pmax = int(positions.max().item()) + 1 if positions.numel() else 1
+        rope = self.rope_tables(input_ids.device, pmax)
+        T, H = input_ids.shape[0], self.cfg.hidden_size
+        if pc.is_first:
+            h = self.embed(input_ids)
+        else:
+            h = P.recv_from_prev(pc, (T, H), self.embed_tokens.dtype, input_ids.device, torch.is_grad_enabled())
+        delta = None
+        for layer in self.layers[pc.layer_lo:pc.layer_hi]:
+            if self.gradient_checkpointing and torch.is_grad_enabled():
+                if delta is not None:
+                    h, delta = h + delta, None
+                h, delta = ckpt.checkpoint(layer, h, None, positions, info, rope, use_reentrant=False)
+            else:
+                h, delta = layer(h, delta, positions, info, rope)
+        if pc.is_last:
+            if delta is None:       # a stage without layers
+                return ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)[0], None
+            return ops.rmsnorm(delta, self.norm, self.cfg.rms_norm_eps, residual=h)[0], None
+        return None, P.send_to_next(pc, h + delta if delta is not None else h)
+
+    def attach_pipeline_parallel(self, pc) -> None:
+        if self.cfg.tie_word_embeddings:
+            raise ValueError("pipeline parallelism needs untied input / output embeddings")
+        self.pp = pc
 
     def sp_slice(self, T: int) -> Tuple[int, int, int]:
         """(first row, end row, padding rows) of this rank's share of a packed stream of ``T`` tokens."""

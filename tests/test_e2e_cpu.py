@@ -123,3 +123,17 @@ def test_context_parallel_ring_attention_two_ranks(tmp_path):
     assert [r["step"] for r in m] == [1, 2]
     for r in m:
         assert r["actor/grad_norm"] > 0 and abs(r["actor/ppo_kl"]) < 1e-3       # on-policy: same log-probs twice
+
+
+def test_pipeline_parallel_two_stages(tmp_path):
+    """Two ranks as one two-stage pipeline (layers split, activations and their gradients sent point to point, trained
+    stage weights re-broadcast after the update so the rollout engines keep whole, identical replicas)."""
+    out = _run(["actor_rollout_ref.actor.megatron.pipeline_model_parallel_size=2",
+                "actor_rollout_ref.model.override_config={tie_word_embeddings: False}",
+                "actor_rollout_ref.rollout.max_num_seqs=32", f"trainer.default_local_dir={tmp_path / 'c'}",
+                "trainer.total_training_steps=2", "trainer.save_freq=-1"], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    for r in m:
+        assert r["actor/grad_norm"] > 0 and abs(r["actor/ppo_kl"]) < 1e-3

@@ -196,6 +196,45 @@ def main():
     if cuda:
         torch.cuda.synchronize()
         lib.check_status()
+    # 8. pipeline parallelism: stages exchange activations / gradients point to point; every stage's parameter
+    #    gradients equal the single-rank ones, and weight sync after an update restores identical replicas
+    from siirl_b200.parallel.pipeline import PipelineContext, sync_stage_weights
+    cfg8 = get_config("tiny-gpu" if cuda else "tiny", {"tie_word_embeddings": False})
+    m_pp = build_model(cfg8, dtype=dtype, device=dev, seed=4)
+    m_one = build_model(cfg8, dtype=dtype, device=dev, seed=4)
+    pc = PipelineContext(dist.group.WORLD, cfg8.num_layers)
+    m_pp.attach_pipeline_parallel(pc)
+    info8 = SeqInfo([33, 50], device=dev)
+    ids8 = torch.randint(3, cfg8.vocab_size, (83,), generator=g).to(dev)
+    coef8 = torch.randn(83, cfg8.hidden_size, generator=g).to(dev, dtype)
+    h_one = m_one.forward_hidden(ids8, info8.positions, info8)
+    (h_one.float() * coef8.float()).sum().backward()
+    hidden, handle = m_pp.forward_hidden_pp(ids8, info8.positions, info8)
+    if pc.is_last:
+        assert (hidden.float() - h_one.float()).abs().max().item() < tol5, "PP hidden"
+        (hidden.float() * coef8.float()).sum().backward()
+    else:
+        handle.backward()
+    for (n1, p1), (_, p2) in zip(m_one.named_parameters(), m_pp.named_parameters()):
+        if p1.grad is None:
+            continue
+        if pc.owns_param(n1):
+            err = (p1.grad.float() - p2.grad.float()).abs().max().item()
+            assert err < (0.05 * max(1.0, p1.grad.float().abs().max().item()) if cuda else 1e-3), f"PP grad {n1}: {err}"
+        else:
+            assert p2.grad is None, f"{n1} is trained by another stage"
+    with torch.no_grad():
+        for n1, p2 in m_pp.named_parameters():
+            if pc.owns_param(n1):
+                p2.add_(1.0)
+    sync_stage_weights(m_pp, pc)
+    chk = torch.stack([p.float().sum() for p in m_pp.parameters()]).sum().reshape(1)
+    parts = [torch.zeros_like(chk) for _ in range(world)]
+    dist.all_gather(parts, chk)
+    assert all(torch.allclose(parts[0], q) for q in parts), "replicas differ after stage weight sync"
+    if cuda:
+        torch.cuda.synchronize()
+        lib.check_status()
     dist.barrier()
     if rank == 0:
         print("TP_OK")
