@@ -272,6 +272,9 @@ def main() -> int:
                        "parallelism": f"dp{world} (replicated bf16 params, sharded fp32 master/Adam), "
                                       f"rollout tp{args.rollout_tp}",
                        "micro_batch": args.micro_batch, "l2": "inputs larger than L2 (15 GB of weights per pass)",
+                       "memory_plan": {"kv_arena_borrows_idle_grad_buffer": True,
+                                       "adam_moments_in_pinned_host_memory_during_rollout": world == 1,
+                                       "activation_checkpointing": True, "activation_offload": bool(args.offload)},
                        "baseline_note": "vs_baseline divides tokens/s/GPU by the reference's only published absolute "
                                         "number (3473.8 tokens/s/GPU, Qwen2.5-0.5B, 1 GPU of unstated type)"},
             "clocks": clocks, "gpu_launches": launches, "impl": "native", "step_split_s": step_split,
