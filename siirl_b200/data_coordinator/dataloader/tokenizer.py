@@ -1,6 +1,7 @@
 """Tokenizer access.  HF tokenizers are used when a model/tokenizer directory is given; the synthetic tasks of the
 benchmark configurations (no network, no checkpoint) use ``SyntheticTokenizer``: ids 0..2 are pad/bos/eos, digits
-and arithmetic symbols get fixed ids, every other id decodes to ``<id>``."""
+and arithmetic symbols get fixed ids, every other id decodes to ``<id>``.  (The reference loads tokenizers with
+``load_tokenizer`` in siirl/models/loader.py.)"""
 from __future__ import annotations
 
 import os

@@ -1,4 +1,5 @@
-"""Paged KV cache ops: append rows of a packed qkv buffer to the cache, fork blocks, decode attention.
+"""Paged KV cache ops: append rows of a packed qkv buffer to the cache, fork blocks, decode attention (what the
+reference gets from vLLM's paged attention behind siirl/engine/rollout/vllm_rollout/vllm_rollout_spmd.py:261-416).
 
 Cache layout (one tensor for all layers): ``[layers, num_blocks, 2, Hkv, 64, D]`` bf16; ``block_table`` is
 ``int32 [B, max_blocks]`` (-1 = unused).  The CPU path keeps the same layout and uses plain indexing."""

@@ -6,7 +6,10 @@ multiple of 128 rows so that a 128-row GEMM tile never mixes experts.  A rank th
 with device ops from the all-gathered routing table, identically on every rank, without a host synchronisation:
 buffer sizes are static upper bounds and unused 128-row blocks are marked ``-1`` (the GEMM skips them).
 
-CPU tensors take a plain PyTorch path with the same semantics (oracle of the GPU tests, gloo tests)."""
+CPU tensors take a plain PyTorch path with the same semantics (oracle of the GPU tests, gloo tests).
+
+Reference counterpart: Megatron-core's MoE layer configured in siirl/models/mcore/config_converter.py (qwen3moe /
+qwen2moe / mixtral branches: ``moe_token_dispatcher_type="alltoall"``, ``moe_grouped_gemm=True``)."""
 from __future__ import annotations
 
 import ctypes

@@ -1,4 +1,5 @@
-"""MATH-style scorers: last ``\\boxed{...}`` answer, normalised string equality (fractions, units, spacing)."""
+"""MATH-style scorers: last ``\\boxed{...}`` answer, normalised string equality (fractions, units, spacing).
+Behaviour of siirl/utils/reward_score/math.py, math_dapo.py and geo3k.py in the reference."""
 import re
 from typing import Optional
 
