@@ -26,17 +26,24 @@ def main() -> None:
     ap.add_argument("--context", type=int, default=640)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--max-model-len", type=int, default=0, help="engine limit (0: just enough for this run); the "
+                    "training configuration uses prompt + response = 5120")
+    ap.add_argument("--n", type=int, default=1, help="samples per prompt (prefix blocks shared by the n samples)")
     args = ap.parse_args()
     cfg = get_config(args.model, {"num_layers": args.layers} if args.layers else None)
     dev = torch.device("cuda")
     model = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=0)
-    res = {"model": args.model, "layers": cfg.num_layers, "seqs": args.seqs, "context": args.context}
+    res = {"model": args.model, "layers": cfg.num_layers, "seqs": args.seqs, "context": args.context,
+           "max_model_len": args.max_model_len, "n": args.n}
     for graph in ([False] if args.no_graph else [False, True]):
-        eng = RolloutEngine(model, max_num_seqs=args.seqs, max_model_len=args.context + 4 * args.steps + 64,
-                            use_cuda_graph=graph, sync_interval=args.steps)
+        eng = RolloutEngine(model, max_num_seqs=args.seqs,
+                            max_model_len=args.max_model_len or args.context + 4 * args.steps + 64,
+                            use_cuda_graph=graph, sync_interval=args.steps,
+                            max_num_batched_tokens=max(8192, args.seqs // args.n * args.context))
         g = torch.Generator().manual_seed(0)
-        prompts = [torch.randint(3, cfg.vocab_size, (args.context,), generator=g).tolist() for _ in range(args.seqs)]
-        sp = SamplingParams(n=1, temperature=1.0, max_new_tokens=1 + 3 * args.steps, eos_token_id=None)
+        prompts = [torch.randint(3, cfg.vocab_size, (args.context,), generator=g).tolist()
+                   for _ in range(args.seqs // args.n)]
+        sp = SamplingParams(n=args.n, temperature=1.0, max_new_tokens=1 + 3 * args.steps, eos_token_id=None)
         # generate = prefill + first token + 3 rounds of `steps` decode steps; time the last round only
         times = []
         orig = eng._run_decode_steps
