@@ -146,6 +146,23 @@ def bench_memory_bound(small: bool):
     lib.check_status()
 
 
+def bench_gemm_decode(small: bool):
+    """The four projections of a Qwen2.5-7B layer at decode batch sizes, through the path the rollout engine takes
+    (``ops.linear`` without autograd: split-K tcgen05 GEMM + slab reduction).  These are weight-streaming bound: the
+    figure of merit is the fraction of the measured copy bandwidth."""
+    shapes = [(3584, 18944, "down_proj")] if small else [(4608, 3584, "qkv_proj"), (3584, 3584, "o_proj"),
+                                                          (37888, 3584, "gate_up_proj"), (3584, 18944, "down_proj")]
+    for M in ((256,) if small else (64, 256)):
+        for N, K, name in shapes:
+            x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+            with torch.no_grad():
+                ms = timeit(lambda: ops.linear(x, w))
+            report(f"decode {name} (split-K GEMM + reduce)", ms, bytes_=N * K * 2, M=M, N=N, K=K,
+                   k_splits=dense._skinny_splits(M, N, K))
+    lib.check_status()
+
+
 def bench_moe(small: bool):
     """Mixture-of-experts MLP of the Qwen3-30B-A3B shape on one GPU (all experts local): dispatch + two grouped
     tcgen05 GEMMs + SwiGLU + combine, against a loop of per-expert cuBLAS GEMMs (torch.matmul) over the same routing."""
@@ -184,12 +201,14 @@ def bench_moe(small: bool):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", default="all", choices=["all", "gemm", "attention", "lm_head", "memory", "moe"])
+    ap.add_argument("--case", default="all", choices=["all", "gemm", "gemm_decode", "attention", "lm_head", "memory", "moe"])
     ap.add_argument("--small", action="store_true")
     a = ap.parse_args()
     print(json.dumps({"peaks": peaks(), "device": torch.cuda.get_device_name()}))
     if a.case in ("all", "gemm"):
         bench_gemm(a.small)
+    if a.case in ("all", "gemm_decode"):
+        bench_gemm_decode(a.small)
     if a.case in ("all", "attention"):
         bench_attention(a.small)
     if a.case in ("all", "lm_head"):
