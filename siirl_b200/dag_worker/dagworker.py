@@ -304,6 +304,19 @@ class DAGWorker:
         out = self._arr(kwargs.get("cur_node")).compute_log_prob(batch)
         metrics = dict(out.meta.pop("metrics", {}))
         out.pop("entropys")
+        alg = self.config.algorithm
+        if alg.rollout_is and "rollout_log_probs" in out and out["responses"].dim() == 2:
+            # the engine's sampling distribution differs slightly from the trainer's recomputation (kernel numerics,
+            # truncation): weight every token by min(pi_train / pi_rollout, threshold), consumed by the policy loss
+            # as ``rollout_is_weights`` (reference: dp_actor.py:444-465 expects them from the trainer)
+            m = out["response_mask"].to(out["old_log_probs"].device).float()
+            ratio = torch.exp((out["old_log_probs"] - out["rollout_log_probs"].to(out["old_log_probs"].device))
+                              .clamp(-20, 20))
+            out["rollout_is_weights"] = ratio.clamp(max=alg.rollout_is_threshold) * m
+            denom = m.sum().clamp(min=1)
+            metrics["actor/rollout_is_ratio_mean"] = float((ratio * m).sum() / denom)
+            metrics["actor/rollout_is_truncated_frac"] = float(((ratio > alg.rollout_is_threshold).float() * m).sum()
+                                                               / denom)
         return NodeOutput(out, metrics)
 
     def compute_ref_log_prob(self, batch: Batch, config=None, **kwargs) -> NodeOutput:

@@ -468,6 +468,9 @@ class AlgorithmArguments:
     weight_factor_in_cpgd: str = "STD_weight"
     workflow_type: str = "default"
     filter_groups: FilterGroupsArguments = _dc(FilterGroupsArguments)
+    # native: truncated importance sampling between the rollout engine's and the trainer's log-probs
+    rollout_is: bool = False
+    rollout_is_threshold: float = 2.0
     use_pf_ppo: bool = False
     pf_ppo: Dict[str, Any] = field(default_factory=dict)
     embodied_sampling: EmbodiedSamplingConfig = _dc(EmbodiedSamplingConfig)
