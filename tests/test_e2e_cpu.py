@@ -137,3 +137,14 @@ def test_pipeline_parallel_two_stages(tmp_path):
     assert [r["step"] for r in m] == [1, 2]
     for r in m:
         assert r["actor/grad_norm"] > 0 and abs(r["actor/ppo_kl"]) < 1e-3
+
+
+def test_rollout_importance_weights(tmp_path):
+    """algorithm.rollout_is: per-token weights min(pi_train / pi_rollout, threshold) reach the policy loss; engine and
+    trainer agree on CPU, so the ratio is 1 and nothing is truncated."""
+    out = _run(["algorithm.rollout_is=True", "trainer.n_gpus_per_node=1", f"trainer.default_local_dir={tmp_path / 'c'}",
+                "trainer.total_training_steps=1", "trainer.save_freq=-1"], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")[0]
+    assert abs(m["actor/rollout_is_ratio_mean"] - 1.0) < 1e-3 and m["actor/rollout_is_truncated_frac"] == 0.0
+    assert m["actor/grad_norm"] > 0
