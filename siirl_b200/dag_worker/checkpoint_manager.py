@@ -26,7 +26,11 @@ class CheckpointManager:
 
     def _roles(self):
         out = []
+        seen = set()
         for key, wk in self.w.workers.items():
+            if id(wk) in seen:
+                continue            # an agent group that shares another group's instance
+            seen.add(id(wk))
             if key.startswith("actor_rollout_ref_") and getattr(wk, "store", None) is not None:
                 out.append((f"actor_agent_{key.rsplit('_', 1)[-1]}", wk,
                             self.w.config.actor_rollout_ref.actor.checkpoint.contents,

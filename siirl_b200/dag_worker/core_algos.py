@@ -214,45 +214,54 @@ def compute_marft_gae_advantage_return(batch, pre_agent_group_ids, gamma: float,
     ``agent_group_{k}_advantages/returns`` and, for the last agent, ``advantages/returns``."""
     prefix = "agent_group_"
     ids = list(pre_agent_group_ids)
-    rewards = [batch[f"{prefix}{g}_token_level_rewards"] for g in ids] + [batch["token_level_rewards"]]
-    values = [batch[f"{prefix}{g}_values"] for g in ids] + [batch["values"]]
-    masks = [batch[f"{prefix}{g}_response_mask"] for g in ids] + [batch["response_mask"]]
-    n_agents = len(rewards)
-    adv = [torch.zeros_like(v, dtype=torch.float32) for v in values]
-    ret = [torch.zeros_like(v, dtype=torch.float32) for v in values]
+    dev_rewards = [batch[f"{prefix}{g}_token_level_rewards"] for g in ids] + [batch["token_level_rewards"]]
+    dev_values = [batch[f"{prefix}{g}_values"] for g in ids] + [batch["values"]]
+    dev_masks = [batch[f"{prefix}{g}_response_mask"] for g in ids] + [batch["response_mask"]]
+    n_agents = len(dev_rewards)
+    # the scan is sequential over (turn, agent, token): run it on host copies (one transfer per tensor instead of a
+    # device synchronisation per token), then move the results back
+    rewards = [r.detach().float().cpu() for r in dev_rewards]
+    values = [v.detach().float().cpu() for v in dev_values]
+    lens = [m.detach().float().cpu().sum(-1).long().tolist() for m in dev_masks]
+    adv = [torch.zeros_like(v) for v in values]
+    ret = [torch.zeros_like(v) for v in values]
     req = list(batch["request_id"])
     traj_len = list(batch["traj_len"])
     seen = set()
     starts = [i for i, s in enumerate(req) if s not in seen and not seen.add(s)]
-    with torch.no_grad():
-        for b0 in starts:
-            gae = 0.0
-            for t_idx in range(int(traj_len[b0])):
-                row = b0 + t_idx
-                for a in reversed(range(n_agents)):
-                    L = int(masks[a][row].sum().item())
-                    for t in reversed(range(L)):
-                        v = float(values[a][row, t])
-                        if t == L - 1:
-                            rew = float(rewards[a][row, t])
-                            if a == n_agents - 1:
-                                v_next = 0.0 if t_idx == 0 else float(values[0][row - 1, 0])
-                            else:
-                                v_next = float(values[a + 1][row, 0])
-                            delta = rew + gamma * v_next - v
-                        else:
-                            delta = gamma * float(values[a][row, t + 1]) - v
-                        gae = delta + gamma * lam * gae
-                        adv[a][row, t] = gae
-                        ret[a][row, t] = gae + v
-        for a in range(n_agents):
-            adv[a] = masked_whiten(adv[a], masks[a].float())
-            if a < n_agents - 1:
-                batch[f"{prefix}{ids[a]}_advantages"] = adv[a]
-                batch[f"{prefix}{ids[a]}_returns"] = ret[a]
-            else:
-                batch["advantages"] = adv[a]
-                batch["returns"] = ret[a]
+    for b0 in starts:
+        gae = 0.0
+        for t_idx in range(int(traj_len[b0])):
+            row = b0 + t_idx
+            for a in reversed(range(n_agents)):
+                L = int(lens[a][row])
+                if L == 0:
+                    continue
+                v_row = values[a][row, :L].tolist()
+                if a == n_agents - 1:
+                    v_after = 0.0 if t_idx == 0 else float(values[0][row - 1, 0])
+                else:
+                    v_after = float(values[a + 1][row, 0])
+                last_reward = float(rewards[a][row, L - 1])
+                a_row = [0.0] * L
+                for t in reversed(range(L)):
+                    if t == L - 1:
+                        delta = last_reward + gamma * v_after - v_row[t]
+                    else:
+                        delta = gamma * v_row[t + 1] - v_row[t]
+                    gae = delta + gamma * lam * gae
+                    a_row[t] = gae
+                adv[a][row, :L] = torch.tensor(a_row)
+                ret[a][row, :L] = adv[a][row, :L] + values[a][row, :L]
+    for a in range(n_agents):
+        dev = dev_values[a].device
+        adv_a = masked_whiten(adv[a].to(dev), dev_masks[a].float())
+        if a < n_agents - 1:
+            batch[f"{prefix}{ids[a]}_advantages"] = adv_a
+            batch[f"{prefix}{ids[a]}_returns"] = ret[a].to(dev)
+        else:
+            batch["advantages"] = adv_a
+            batch["returns"] = ret[a].to(dev)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -77,6 +77,7 @@ class DAGWorker:
         self.total_training_steps = 0
         self.internal_data_cache: Dict[str, Batch] = {}
         self.workers: Dict[str, Any] = {}
+        self._shared_workers: Dict[str, str] = {}
         self.process_groups: Dict[str, Any] = {}
         self.timing_raw: Dict[str, float] = {}
         self.tracker: Optional[Tracking] = None
@@ -84,6 +85,9 @@ class DAGWorker:
         self.history: List[Dict[str, float]] = []
         self._dapo_gen_batches = 0
         self.last_step_tokens = self.last_h2d_bytes = self.last_d2h_bytes = 0
+        self._multi_agent = False
+        self.multi_agent_loop = None
+        self._agent_ids: List[int] = [0]
         self._initialized = False
 
     # ================================================================================================
@@ -100,7 +104,9 @@ class DAGWorker:
                                             vocab_size=vocab)
         self._setup_dataloader()
         self._setup_reward_managers()
+        self._bind_default_executables()
         self._initialize_node_workers()
+        self._setup_multi_agent_loop()
         if self.config.algorithm.use_kl_in_reward:
             self.kl_ctrl_in_reward = core_algos.get_kl_controller(self.config.algorithm.kl_ctrl)
         if self.data_coordinator is None:
@@ -179,13 +185,50 @@ class DAGWorker:
         self.val_reward_fn = create_reward_manager(self.config, self.tokenizer, num_examine=1,
                                                    max_resp_len=self.config.data.max_response_length)
 
+    def _bind_default_executables(self) -> None:
+        """Nodes of a declarative (YAML / JSON) workflow name no function: bind the handler their role implies
+        (reference: dagworker.py ``_setup_role_worker_mapping`` + node binding in ``_initialize_node_workers``)."""
+        by_role = {
+            (NodeRole.ROLLOUT, False): self.generate, (NodeRole.ROLLOUT, True): self.generate,
+            (NodeRole.REWARD, False): self.compute_reward, (NodeRole.REWARD, True): self.compute_reward,
+            (NodeRole.ADVANTAGE, False): self.compute_advantage, (NodeRole.ADVANTAGE, True): self.compute_advantage,
+            (NodeRole.ACTOR, True): self.compute_old_log_prob, (NodeRole.ACTOR, False): self.train_actor,
+            (NodeRole.REFERENCE, False): self.compute_ref_log_prob, (NodeRole.REFERENCE, True): self.compute_ref_log_prob,
+            (NodeRole.CRITIC, True): self.compute_value, (NodeRole.CRITIC, False): self.train_critic,
+        }
+        for node in self.taskgraph.nodes.values():
+            if node.executable is not None or node.node_type == NodeType.BARRIER_SYNC:
+                continue
+            fn = by_role.get((node.node_role, node.only_forward_compute))
+            if fn is None and node.node_role == NodeRole.DYNAMIC_SAMPLING:
+                from ..user_interface.filter_interface.dapo import dynamic_sampling
+                fn = dynamic_sampling
+            if fn is None:
+                raise RuntimeError(f"node '{node.node_id}' ({node.node_type.value}/{node.node_role.value}) names no "
+                                   f"executable and its role has no default handler")
+            node.executable = fn
+
+    @staticmethod
+    def _agent_option(node: Optional[Node], key: str, default: Any = None) -> Any:
+        opts = getattr(node, "agent_options", None) if node is not None else None
+        if opts is None:
+            return default
+        return opts.get(key, default) if isinstance(opts, dict) else getattr(opts, key, default)
+
     def _initialize_node_workers(self) -> None:
-        """One hybrid worker per agent group for actor/rollout/ref nodes, one critic, one reward model."""
+        """One hybrid worker per agent group for actor/rollout/ref nodes, one critic, one reward model.
+        ``agent_options.share_instance: g`` makes a node use agent group g's worker of the same kind."""
         seed = self.config.trainer.seed
         for node in self.taskgraph.nodes.values():
             if node.node_type not in (NodeType.MODEL_TRAIN, NodeType.MODEL_INFERENCE):
                 continue
             ag = node.agent_group
+            share = self._agent_option(node, "share_instance")
+            if share is not None and int(share) != ag:
+                kind = "critic" if node.node_role == NodeRole.CRITIC else (
+                    "reward" if node.node_role == NodeRole.REWARD else "actor_rollout_ref")
+                self._shared_workers[f"{kind}_{ag}"] = f"{kind}_{int(share)}"
+                continue
             group = self._node_group(node)
             cfg = node.config.get("intern_config")
             if node.node_role in (NodeRole.ACTOR, NodeRole.ROLLOUT, NodeRole.REFERENCE):
@@ -218,9 +261,89 @@ class DAGWorker:
             w = RewardModelWorker(self.config.reward_model, None, self.device, self.comm, seed)
             w.init_model()
             self.workers["reward_0"] = w
+        for alias, target in self._shared_workers.items():
+            if alias in self.workers:
+                continue       # another node of the group built its own instance
+            if target not in self.workers:
+                raise RuntimeError(f"share_instance: no worker '{target}' to share as '{alias}'")
+            self.workers[alias] = self.workers[target]
 
     def _arr(self, node: Optional[Node] = None) -> ActorRolloutRefWorker:
         return self.workers[f"actor_rollout_ref_{node.agent_group if node is not None else 0}"]
+
+    # ================================================================================================
+    # multi-agent workflows (several agent groups, each with its own policy; MARFT)
+    # ================================================================================================
+    def _setup_multi_agent_loop(self) -> None:
+        """With rollout nodes of more than one agent group, generation is one joint loop over the agents
+        (reference: dagworker.py:999-1014 ``_setup_multi_agent_loop``).  Per-agent hooks come from the rollout
+        nodes' ``agent_options``: ``process_path`` (a Python file with ``pre_process(tokenizer, prompt_id, obs,
+        **kw)`` / ``post_process(tokenizer, prompt_id, response_id, **kw)``), ``pre_process_kwargs``,
+        ``post_process_kwargs``, ``env_path: ["file.py:Class"]`` and ``obs_with_env``."""
+        model_nodes = [n for n in self.taskgraph.nodes.values()
+                       if n.node_type in (NodeType.MODEL_TRAIN, NodeType.MODEL_INFERENCE)]
+        self._agent_ids = sorted({n.agent_group for n in model_nodes}) or [0]
+        rollout_nodes = sorted(self.taskgraph.get_nodes_by_role(NodeRole.ROLLOUT), key=lambda n: n.agent_group)
+        groups = sorted({n.agent_group for n in rollout_nodes})
+        if len(groups) < 2:
+            return
+        from ..execution.rollout_flow.multi_agent.multiagent_generate import MultiAgentLoop
+        from ..utils.import_string import import_string, load_module_from_file
+        tok = self.tokenizer
+        pre, post, env_cls, obs_with_env = {}, {}, None, False
+        for node in rollout_nodes:
+            k = node.agent_group
+            path = self._agent_option(node, "process_path")
+            if path:
+                mod = load_module_from_file(path)
+                pk = dict(self._agent_option(node, "pre_process_kwargs") or {})
+                qk = dict(self._agent_option(node, "post_process_kwargs") or {})
+                if hasattr(mod, "pre_process"):
+                    pre[k] = (lambda ids, obs, agent, turn, _f=mod.pre_process, _kw=pk: _f(tok, list(ids), obs, **_kw))
+                if hasattr(mod, "post_process"):
+                    post[k] = (lambda ids, resp, agent, turn, _f=mod.post_process, _kw=qk:
+                               _f(tok, list(ids), list(resp), **_kw))
+            env_path = self._agent_option(node, "env_path")
+            if env_path:
+                env_cls = import_string(env_path[0] if isinstance(env_path, (list, tuple)) else env_path)
+            obs_with_env = obs_with_env or bool(self._agent_option(node, "obs_with_env", False))
+        r = self.config.actor_rollout_ref.rollout
+        self.multi_agent_loop = MultiAgentLoop(
+            {k: self.workers[f"actor_rollout_ref_{k}"] for k in groups}, tok, self.config.data.max_prompt_length,
+            max_turns=r.multi_turn.max_assistant_turns or 1, pre_process=pre, post_process=post,
+            env_factory=env_cls, colocate=True, group=self._node_group(rollout_nodes[0]),
+            use_all_traj=bool(r.multi_turn.use_all_traj), obs_with_env=obs_with_env and env_cls is not None)
+        self._multi_agent = True
+
+    def _agent_prefix(self, node: Optional[Node]) -> str:
+        """Tensors of every agent but the last travel under ``agent_group_{k}_``; the last agent's are unprefixed."""
+        if not self._multi_agent or node is None or node.agent_group == self._agent_ids[-1]:
+            return ""
+        return f"agent_group_{node.agent_group}_"
+
+    def _on_agent_view(self, batch: Batch, node: Optional[Node], fn) -> Batch:
+        """Run ``fn`` (a worker call that reads and writes the plain keys) on agent ``node.agent_group``'s columns."""
+        prefix = self._agent_prefix(node)
+        if not prefix:
+            return fn(batch)
+        view = Batch({k[len(prefix):]: v for k, v in batch.tensors.items() if k.startswith(prefix)},
+                     batch.non_tensors, dict(batch.meta))
+        out = fn(view)
+        for k, v in out.tensors.items():
+            batch.tensors[prefix + k] = v
+        for k, v in out.non_tensors.items():
+            if k not in batch.non_tensors:
+                batch.non_tensors[k] = v
+        batch.meta.update(out.meta)
+        return batch
+
+    def _train_cycle_skips(self, node: Optional[Node]) -> bool:
+        """``agent_options.train_cycle: c``: the agents take turns being trained, c steps each
+        (reference dagworker.py:325-336)."""
+        cycle = self._agent_option(node, "train_cycle")
+        if not cycle or not self._multi_agent:
+            return False
+        return (self.global_steps // int(cycle)) % len(self._agent_ids) != self._agent_ids.index(node.agent_group)
 
     # ================================================================================================
     # node handlers
@@ -230,6 +353,12 @@ class DAGWorker:
         batch.meta.update({"eos_token_id": getattr(self.tokenizer, "eos_token_id", None),
                            "pad_token_id": getattr(self.tokenizer, "pad_token_id", 0) or 0,
                            "global_steps": self.global_steps})
+        if self._multi_agent:
+            if batch.meta.get("multi_agent"):
+                return NodeOutput(batch, {})          # the first rollout node already ran the joint loop
+            out = self.multi_agent_loop.generate_sequence(batch.to("cpu")).to(self.device)
+            return NodeOutput(out, {"perf/rollout_output_tokens_total": float(out.meta.get("total_output_tokens", 0)),
+                                    "num_turns/max": float(max(out.non_tensors["traj_step"])) + 1.0})
         worker = self._arr(node)
         r = self.config.actor_rollout_ref.rollout
         if (r.multi_turn.enable or r.mode == "async") and worker.engine is not None \
@@ -278,7 +407,15 @@ class DAGWorker:
         metrics: Dict[str, float] = {}
         if self.config.reward_model.enable and "reward_0" in self.workers:
             batch = self.workers["reward_0"].compute_rm_score(batch)
-        reward_tensor, extra = guarded_compute_reward(batch, self.reward_fn)
+        if self._multi_agent and self.config.actor_rollout_ref.rollout.agent.rewards_with_env \
+                and "env_score" in batch.non_tensors:
+            # the environment already judged every turn: its score sits on the last response token of the last agent
+            m = batch["response_mask"].float()
+            last = (m.cumsum(-1) == m.sum(-1, keepdim=True)).float() * m
+            score = torch.tensor([float(x) for x in batch.non_tensors["env_score"]], device=m.device)
+            reward_tensor, extra = last * score[:, None], {}
+        else:
+            reward_tensor, extra = guarded_compute_reward(batch, self.reward_fn)
         batch["token_level_scores"] = reward_tensor.to(batch["responses"].device)
         for k, v in (extra or {}).items():
             if isinstance(v, list) and len(v) == batch.batch_size:
@@ -301,9 +438,12 @@ class DAGWorker:
 
     def compute_old_log_prob(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
         batch.meta["temperature"] = self._sampling_temperature(batch)
-        out = self._arr(kwargs.get("cur_node")).compute_log_prob(batch)
+        node = kwargs.get("cur_node")
+        out = self._on_agent_view(batch, node, self._arr(node).compute_log_prob)
         metrics = dict(out.meta.pop("metrics", {}))
-        out.pop("entropys")
+        out.pop(self._agent_prefix(node) + "entropys")
+        if self._agent_prefix(node):
+            return NodeOutput(out, {f"agent_{node.agent_group}_{k}": v for k, v in metrics.items()})
         alg = self.config.algorithm
         if alg.rollout_is and "rollout_log_probs" in out and out["responses"].dim() == 2:
             # the engine's sampling distribution differs slightly from the trainer's recomputation (kernel numerics,
@@ -324,11 +464,13 @@ class DAGWorker:
         if not (a.use_kl_loss or self.config.algorithm.use_kl_in_reward):
             return NodeOutput(batch, {})
         batch.meta["temperature"] = self._sampling_temperature(batch)
-        return NodeOutput(self._arr(kwargs.get("cur_node")).compute_ref_log_prob(batch), {})
+        node = kwargs.get("cur_node")
+        return NodeOutput(self._on_agent_view(batch, node, self._arr(node).compute_ref_log_prob), {})
 
     def compute_value(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
         node = kwargs.get("cur_node")
-        return NodeOutput(self.workers[f"critic_{node.agent_group if node else 0}"].compute_values(batch), {})
+        critic = self.workers[f"critic_{node.agent_group if node else 0}"]
+        return NodeOutput(self._on_agent_view(batch, node, critic.compute_values), {})
 
     def compute_advantage(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
         alg = self.config.algorithm
@@ -340,8 +482,23 @@ class DAGWorker:
             metrics.update(kl_metrics)
         else:
             batch["token_level_rewards"] = batch["token_level_scores"]
+        extra_kw: Dict[str, Any] = {}
+        if self._multi_agent:
+            # only the last agent is scored; the agents before it share that reward (placed on their own last
+            # response token) or get none (reference dagworker.py:586-617)
+            pre_ids = self._agent_ids[:-1]
+            extra_kw["agent_group_ids"] = pre_ids
+            seq = batch["token_level_rewards"].sum(-1)
+            for g in pre_ids:
+                key = f"agent_group_{g}_token_level_rewards"
+                if key not in batch.tensors:
+                    m = batch[f"agent_group_{g}_response_mask"].float()
+                    last = (m.cumsum(-1) == m.sum(-1, keepdim=True)).float() * m
+                    share = seq.to(m.device)[:, None] if alg.share_reward_in_agent else 0.0
+                    batch[key] = last * share
+                batch[f"agent_group_{g}_token_level_scores"] = batch[key].clone()
         batch = core_algos.compute_advantage(
-            batch, alg.adv_estimator, gamma=alg.gamma, lam=alg.lam,
+            batch, alg.adv_estimator, gamma=alg.gamma, lam=alg.lam, **extra_kw,
             norm_adv_by_std_in_grpo=alg.norm_adv_by_std_in_grpo, weight_factor_in_cpgd=alg.weight_factor_in_cpgd,
             use_pf_ppo=alg.use_pf_ppo, pf_ppo_reweight_method=alg.pf_ppo.get("reweight_method", "pow"),
             pf_ppo_weight_pow=alg.pf_ppo.get("weight_pow", 2.0),
@@ -350,13 +507,30 @@ class DAGWorker:
 
     def train_critic(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
         node = kwargs.get("cur_node")
-        return NodeOutput(batch, self.workers[f"critic_{node.agent_group if node else 0}"].update_critic(batch))
+        if self._train_cycle_skips(node):
+            return NodeOutput(batch, {})
+        critic = self.workers[f"critic_{node.agent_group if node else 0}"]
+        metrics: Dict[str, float] = {}
+        self._on_agent_view(batch, node, lambda b: (metrics.update(critic.update_critic(b)), b)[1])
+        return NodeOutput(batch, self._agent_metrics(node, metrics))
 
     def train_actor(self, batch: Batch, config=None, **kwargs) -> NodeOutput:
         if self.config.trainer.critic_warmup > self.global_steps:
             return NodeOutput(batch, {})
+        node = kwargs.get("cur_node")
+        if self._train_cycle_skips(node):
+            return NodeOutput(batch, {})
         batch.meta["temperature"] = self._sampling_temperature(batch)
-        return NodeOutput(batch, self._arr(kwargs.get("cur_node")).update_actor(batch))
+        metrics: Dict[str, float] = {}
+        self._on_agent_view(batch, node, lambda b: (metrics.update(self._arr(node).update_actor(b)), b)[1])
+        return NodeOutput(batch, self._agent_metrics(node, metrics))
+
+    def _agent_metrics(self, node: Optional[Node], metrics: Dict[str, float]) -> Dict[str, float]:
+        """With several agents every model node's metrics carry ``agent_{k}_`` so that they do not overwrite
+        each other (reference dag_utils.py:121-132)."""
+        if not self._multi_agent or node is None:
+            return metrics
+        return {f"agent_{node.agent_group}_{k}": v for k, v in metrics.items()}
 
     # ================================================================================================
     # data movement between nodes

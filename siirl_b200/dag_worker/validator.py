@@ -38,7 +38,17 @@ class Validator:
             batch.meta.update({"validate": True, "eos_token_id": getattr(w.tokenizer, "eos_token_id", None),
                                "pad_token_id": getattr(w.tokenizer, "pad_token_id", 0) or 0,
                                "global_steps": w.global_steps})
-            out = w._arr(None).generate_sequences(batch.to(w.device))
+            if getattr(w, "_multi_agent", False):
+                # joint loop of all agents; each sample is judged on its final turn (rows are latest turn first)
+                out = w.multi_agent_loop.generate_sequence(batch.to("cpu"))
+                first, seen = [], set()
+                for i, rid in enumerate(out.non_tensors["request_id"]):
+                    if rid not in seen:
+                        seen.add(rid)
+                        first.append(i)
+                out = out.select_idxs(first).to(w.device)
+            else:
+                out = w._arr(None).generate_sequences(batch.to(w.device))
             reward, _extra = compute_reward(out, w.val_reward_fn)
             seq = reward.sum(-1).cpu().tolist()
             dup = out["padded_duplicate"] if "padded_duplicate" in out else [False] * out.batch_size

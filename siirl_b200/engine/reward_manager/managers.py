@@ -161,5 +161,30 @@ class EmbodiedRewardManager:
         return {"reward_tensor": reward, "reward_extra_info": extra} if return_dict else reward
 
 
+class BatchRewardManager(NaiveRewardManager):
+    """``reward_model.reward_manager=batch``: the scoring function is called ONCE per batch with lists,
+    ``compute_score(data_sources, solution_strs, ground_truths, extra_infos, **kwargs) -> list of float | dict``
+    (the signature of the reference's custom-reward example, examples/custom_reward/rewardfunc_gsm8k.py:34-60).
+    For functions that batch their own work: a judge model, a remote verifier, vectorised checks."""
+
+    def _score_all(self, batch, plens, rlens):
+        cpu = batch.to("cpu") if batch["responses"].is_cuda else batch
+        n = cpu.batch_size
+        texts, gts, sources, extras = [], [], [], []
+        for i in range(n):
+            texts.append(self.tokenizer.decode(cpu["responses"][i, :int(rlens[i])].tolist(), skip_special_tokens=True))
+            rm = cpu["reward_model"][i] if "reward_model" in cpu else {}
+            gts.append(rm.get("ground_truth") if isinstance(rm, dict) else None)
+            sources.append(cpu[self.reward_fn_key][i] if self.reward_fn_key in cpu else "unknown")
+            extras.append(dict(cpu["extra_info"][i] or {}) if "extra_info" in cpu else {})
+        scores = self.compute_score(data_sources=sources, solution_strs=texts, ground_truths=gts, extra_infos=extras,
+                                    **self.reward_kwargs)
+        scores = list(scores)
+        if len(scores) != n:
+            raise ValueError(f"batch reward function returned {len(scores)} scores for {n} samples")
+        return scores
+
+
 REWARD_MANAGERS: Dict[str, Any] = {"naive": NaiveRewardManager, "dapo": DAPORewardManager,
-                                   "parallel": ParallelRewardManager, "embodied": EmbodiedRewardManager}
+                                   "parallel": ParallelRewardManager, "embodied": EmbodiedRewardManager,
+                                   "batch": BatchRewardManager}
