@@ -148,3 +148,51 @@ def test_rollout_importance_weights(tmp_path):
     m = _metrics(tmp_path / "log")[0]
     assert abs(m["actor/rollout_is_ratio_mean"] - 1.0) < 1e-3 and m["actor/rollout_is_truncated_frac"] == 0.0
     assert m["actor/grad_norm"] > 0
+
+
+_SMALL = ["data.max_response_length=16", "trainer.total_training_steps=2"]
+
+
+def test_ppo_with_critic_and_warmup(tmp_path):
+    """GAE pipeline: value model scored before the update, critic trained every step, the actor only after
+    ``trainer.critic_warmup`` steps; KL to the reference folded into the reward."""
+    out = _run(["algorithm.adv_estimator=gae", "critic.model.arch_preset=tiny", "critic.ppo_mini_batch_size=8",
+                "critic.ppo_micro_batch_size_per_gpu=4", "algorithm.use_kl_in_reward=True",
+                "actor_rollout_ref.actor.use_kl_loss=False", "actor_rollout_ref.rollout.n=2",
+                "trainer.critic_warmup=1", f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.save_freq=2",
+                *_SMALL], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    assert "actor/grad_norm" not in m[0] and m[1]["actor/grad_norm"] > 0
+    for r in m:
+        assert r["critic/vf_loss"] > 0 and "critic/values/mean" in r and "actor/reward_kl_penalty" in r
+    assert (tmp_path / "c" / "global_step_2" / "critic_agent_0" / "manifest.json").exists()
+
+
+def test_dapo_dynamic_sampling_and_overlong_penalty(tmp_path):
+    out = _run(["algorithm.workflow_type=dapo", "algorithm.filter_groups.enable=True",
+                "algorithm.filter_groups.metric=seq_reward", "algorithm.filter_groups.max_num_gen_batches=8",
+                "reward_model.reward_manager=dapo", "reward_model.overlong_buffer.enable=True",
+                "reward_model.overlong_buffer.len=4", "actor_rollout_ref.actor.clip_ratio_low=0.2",
+                "actor_rollout_ref.actor.clip_ratio_high=0.28", "data.gen_batch_size=12",
+                "actor_rollout_ref.actor.use_kl_loss=False", f"trainer.default_local_dir={tmp_path / 'c'}", *_SMALL],
+               tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    for r in m:
+        assert 0 < r["dapo_sampling/kept_trajectories_ratio"] <= 1.0
+        assert r["dapo_sampling/final_trajectories"] <= r["dapo_sampling/initial_trajectories"]
+        assert r["critic/score/min"] < 0          # the overlong penalty makes full-length responses negative
+        assert r["actor/grad_norm"] > 0
+
+
+@pytest.mark.parametrize("variant", [["actor_rollout_ref.actor.policy_loss.loss_mode=gspo"],
+                                     ["algorithm.adv_estimator=cpgd"]], ids=["gspo", "cpgd"])
+def test_gspo_and_cpgd_variants(tmp_path, variant):
+    out = _run([*variant, f"trainer.default_local_dir={tmp_path / 'c'}", *_SMALL], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    assert all(r["actor/grad_norm"] > 0 for r in m)
