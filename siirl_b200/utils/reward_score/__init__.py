@@ -2,8 +2,8 @@
 
 Signature kept from the reference (siirl/utils/reward_score/__init__.py:19-98):
 ``compute_score(data_source, solution_str, ground_truth, extra_info=None) -> float | dict`` (a dict must hold
-``"score"``).  Scorers: gsm8k, math (boxed answers, normalised string match), math_dapo, geo3k, search-R1 style
-exact match, plus the synthetic tasks of the benchmark configurations (arith, parity, bernoulli, length)."""
+``"score"``).  Scorers: gsm8k, math (boxed answers, normalised string match), math_dapo, geo3k, math_verify / prime_math
+(numeric and element-wise equivalence), search-R1 style exact match, plus the synthetic tasks of the benchmark configurations (arith, parity, bernoulli, length)."""
 from __future__ import annotations
 
 import random
@@ -45,9 +45,10 @@ def default_compute_score(data_source: str, solution_str: str, ground_truth: Any
         return qa_em.compute_score(solution_str, ground_truth)
     if ds in ("numina_aops_forum", "numina_synthetic_math", "numina_amc_aime", "numina_synthetic_amc", "numina_cn_k12",
               "numina_olympiads", "prime_math", "math_verify"):
-        # the reference scores these with sympy / math-verify equivalence; the normalised string match of the MATH
-        # scorer is the dependency-free rule used here
-        return math_score.compute_score(solution_str, ground_truth)
+        # the reference scores these with sympy / math-verify; here: string, exact-rational / numeric and
+        # element-wise (tuple, set, interval) equivalence from math_verify.py
+        from . import math_verify
+        return math_verify.compute_score(solution_str, ground_truth)
     if ds in ("codecontests", "apps", "codeforces", "taco", "prime_code"):
         url = kwargs.get("sandbox_fusion_url")
         if url:

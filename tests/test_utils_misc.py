@@ -70,3 +70,26 @@ def test_split_k_factor_fills_whole_waves():
         waves = -(-tiles // 148)
         assert tiles / (waves * 148) > 0.9, (M, N, K, s)
     assert _skinny_splits(256, 37888, 3584) == 1            # already more tiles than SMs
+
+
+def test_math_equivalence_scorer():
+    from siirl_b200.utils.reward_score import compute_score
+    from siirl_b200.utils.reward_score.math_verify import is_equiv, to_number
+    from fractions import Fraction
+    same = [("\\frac{1}{2}", "0.5"), ("\\dfrac{3}{4}", "75\\%"), ("1,234", "1234"), ("2\\sqrt{2}", "\\sqrt{8}"),
+            ("x=5", "5"), ("(1,2)", "(1, 2)"), ("\\{1,2\\}", "\\{2,1\\}"), ("3\\pi", "9.42477796"),
+            ("1\\frac{1}{2}", "1.5"), ("2^{10}", "1024"), ("10 cm", "10"), ("\\frac{\\sqrt{3}}{2}", "0.8660254"),
+            ("-\\frac{2}{3}", "-0.666667"), ("3, 1", "1, 3"), ("\\sqrt[3]{8}", "2"), ("90^\\circ", "90"),
+            ("\\frac{2}{3}", "0.67"), ("(1,000, 2)", "(1000,2)"), ("\\text{yes}", "yes")]
+    different = [("(1,2)", "(2,1)"), ("[0,1)", "[0,1]"), ("x+1", "1+x"), ("12", "13"), ("\\frac{2}{3}", "0.7"),
+                 ("\\{1,2\\}", "\\{1,3\\}"), ("\\frac{1}{0}", "1")]
+    for a, b in same:
+        assert is_equiv(a, b), (a, b)
+        assert is_equiv(b, a), (b, a)
+    for a, b in different:
+        assert not is_equiv(a, b), (a, b)
+    assert to_number("\\frac{3}{6}") == Fraction(1, 2)
+    assert to_number("__import__('os')") is None and to_number("9**9**9") is None and to_number("x") is None
+    assert compute_score("prime_math", "thus \\boxed{\\frac{2}{4}}", "0.5") == 1.0
+    assert compute_score("math_verify", "The answer is 7.", "\\boxed{7}") == 1.0
+    assert compute_score("numina_olympiads", "no box here", "7") == 0.0
