@@ -1,9 +1,8 @@
 """Built-in tools: GSM8K answer checker, Geo3K checker, calculator, local-corpus search, sandboxed Python.
 
 Counterparts of the reference's gsm8k / geo3k / search / sandbox-fusion / MCP tools
-(siirl/execution/rollout_flow/multiturn/tools/*).  Tools that need a remote service in the reference (retrieval
-server, Sandbox Fusion, MCP servers) take a ``url`` in their config and raise a clear error when it is unset; the
-offline variants below (``LocalSearchTool`` over an in-memory corpus, ``PythonSandboxTool`` in a subprocess with a
+(siirl/execution/rollout_flow/multiturn/tools/*).  The service-backed tools (retrieval server, Sandbox Fusion, MCP
+servers) are in ``remote_tools.py``; the offline variants below (``LocalSearchTool`` over an in-memory corpus, ``PythonSandboxTool`` in a subprocess with a
 time limit) make multi-turn training runnable without network."""
 from __future__ import annotations
 

@@ -13,9 +13,14 @@ from .schemas import OpenAIFunctionToolSchema
 
 def get_tool_class(name: str):
     mod, _, cls = name.rpartition(".")
-    if not mod:
-        mod = "siirl_b200.execution.rollout_flow.multiturn.tools.builtin_tools"
-    return getattr(importlib.import_module(mod), cls)
+    if mod:
+        return getattr(importlib.import_module(mod), cls)
+    pkg = "siirl_b200.execution.rollout_flow.multiturn.tools"
+    for sub in ("builtin_tools", "remote_tools"):
+        m = importlib.import_module(f"{pkg}.{sub}")
+        if hasattr(m, cls):
+            return getattr(m, cls)
+    raise AttributeError(f"no built-in tool class named '{cls}'")
 
 
 def initialize_tools_from_config(path_or_dict) -> List[BaseTool]:

@@ -126,3 +126,89 @@ def test_multiturn_pipeline_end_to_end(tmp_path):
         m = [json.loads(line) for line in f]
     assert [r["step"] for r in m] == [1, 2] and all(r["num_turns/mean"] >= 1 for r in m)
     assert all(r["response_length/max"] <= 24 for r in m)
+
+
+def test_service_backed_tools_against_a_local_server(tmp_path):
+    """Search, Sandbox Fusion and MCP tools talk to one in-process HTTP server that answers in each service's format."""
+    import asyncio
+    import json
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+
+    from siirl_b200.execution.rollout_flow.multiturn.tools.remote_tools import TokenBucket
+    from siirl_b200.execution.rollout_flow.multiturn.tools.tool_registry import initialize_tools_from_config, tools_by_name
+
+    calls = []
+
+    class H(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            calls.append((self.path, body))
+            if self.path == "/retrieve":
+                out = {"result": [[{"document": {"contents": f"T{i}\nabout {q}"}, "score": 1.0 - i * 0.1}
+                                   for i in range(body["topk"])] for q in body["queries"]]}
+            elif self.path == "/run_code":
+                out = {"status": "Success", "run_result": {"stdout": "42\n", "stderr": "", "return_code": 0}}
+            else:
+                m = body["method"]
+                if m == "initialize":
+                    res = {"protocolVersion": "2025-03-26", "capabilities": {}, "serverInfo": {"name": "t"}}
+                elif m == "tools/list":
+                    res = {"tools": [{"name": "web_search", "inputSchema": {"type": "object"}}]}
+                elif m == "tools/call":
+                    res = {"content": [{"type": "text", "text": json.dumps(
+                        {"results": [{"title": "A", "content": body["params"]["arguments"]["query"]}]})}]}
+                else:
+                    res = None
+                out = {"jsonrpc": "2.0", "id": body["id"], "result": res}
+            data = json.dumps(out).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(data)))
+            self.end_headers()
+            self.wfile.write(data)
+
+    srv = HTTPServer(("127.0.0.1", 0), H)
+    port = srv.server_address[1]
+    th = threading.Thread(target=srv.serve_forever, daemon=True)
+    th.start()
+    try:
+        mcp_cfg = tmp_path / "mcp.json"
+        mcp_cfg.write_text(json.dumps({"mcpServers": {"s": {"url": f"http://127.0.0.1:{port}/mcp"}}}))
+
+        def schema(name, **props):
+            return {"type": "function", "function": {"name": name, "description": name, "parameters": {
+                "type": "object", "properties": {k: {"type": v} for k, v in props.items()}, "required": list(props)}}}
+        tools = tools_by_name(initialize_tools_from_config({"tools": [
+            {"class_name": "SearchTool", "config": {"retrieval_service_url": f"http://127.0.0.1:{port}/retrieve",
+                                                    "topk": 2, "rate_limit": 100},
+             "tool_schema": schema("search", query_list="array")},
+            {"class_name": "SandboxFusionTool", "config": {"sandbox_fusion_url": f"http://127.0.0.1:{port}/run_code"},
+             "tool_schema": schema("code_interpreter", code="string")},
+            {"class_name": "McpSearchTool", "config": {"mcp_servers_config_path": str(mcp_cfg)},
+             "tool_schema": schema("web_search", query="string")}]}))
+
+        async def go():
+            a = await tools["search"].execute("i", {"query_list": ["cats", "dogs"]})
+            b = await tools["code_interpreter"].execute("i", {"code": "print(42)"})
+            c = await tools["web_search"].execute("i", {"query": "b200"})
+            d = await tools["search"].execute("i", {"query_list": []})
+            return a, b, c, d
+        a, b, c, d = asyncio.run(go())
+        text = json.loads(a[0])["result"]
+        assert "Doc 1 (Title: T0)\nabout cats" in text and "about dogs" in text and a[2]["documents"] == 4
+        assert b[0] == "42" and b[2]["status"] == "Success"
+        assert c[0] == "A: b200" and c[2]["status"] == "success"
+        assert d[2]["status"] == "bad_request"
+        methods = [body.get("method") for path, body in calls if path == "/mcp"]
+        assert methods == ["initialize", "tools/list", "tools/call"]
+    finally:
+        srv.shutdown()
+    tb = TokenBucket(rate=50, capacity=1)
+    import time
+    t0 = time.monotonic()
+    assert all(tb.acquire(1.0) for _ in range(4))
+    assert time.monotonic() - t0 >= 0.05          # 3 refills at 50 per second
