@@ -27,6 +27,10 @@ int sb_moe_combine(const void* const* y_ptrs, int world, const int* pair_rank, c
                    void* out, int T, int k, int H, cudaStream_t stream);
 int sb_moe_pair_dot(const void* const* y_ptrs, int world, const int* pair_rank, const int* pair_slot, const void* dout,
                     float* dots, int T, int k, int H, cudaStream_t stream);
+int sb_moe_route_topk(const void* logits, int is_bf16, int ld, float* w, int* idx, int T, int E, int k, int norm,
+                      cudaStream_t stream);
+int sb_moe_route_topk_bwd(const void* logits, int is_bf16, int ld, const int* idx, const float* dw, float* dlogits,
+                          int T, int E, int k, int norm, cudaStream_t stream);
 int sb_ag_gemm_bf16(const void* A, const void* staging, void* C, const void* bias, int M, int N, int K, long long lda,
                     long long ld, long long ldc, const void* ag_params, int copiers, int tile_n, int* status,
                     cudaStream_t stream);

@@ -159,3 +159,158 @@ extern "C" int sb_moe_pair_dot(const void* const* y_ptrs, int world, const int* 
                                                           T, k, H);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------
+// router: softmax over experts + top-k (+ renormalisation) in one pass, and its backward
+// ---------------------------------------------------------------------------------------
+// One warp per token; lane l holds experts l, l+32, ... (E <= 32 * kRouteMaxPerLane).  Ties go to the lower
+// expert id.  Forward keeps nothing but (weights, ids): the backward recomputes the softmax from the logits.
+constexpr int kRouteMaxPerLane = 8;
+
+template <typename T>
+__device__ __forceinline__ float route_load(const T* p);
+template <>
+__device__ __forceinline__ float route_load<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float route_load<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+template <typename T>
+__device__ __forceinline__ float route_softmax(const T* row, int E, int lane, float (&p)[kRouteMaxPerLane]) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    const int e = lane + 32 * i;
+    p[i] = e < E ? route_load(row + e) : -INFINITY;
+    mx = fmaxf(mx, p[i]);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    p[i] = (lane + 32 * i < E) ? __expf(p[i] - mx) : 0.f;
+    sum += p[i];
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.f / sum;
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) p[i] *= inv;
+  return inv;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_route_topk_kernel(const T* __restrict__ logits, int ld, float* __restrict__ w,
+                                                             int* __restrict__ idx, int Tn, int E, int k, int norm) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < Tn; t += warps) {
+    float p[kRouteMaxPerLane];
+    route_softmax(logits + (size_t)t * ld, E, lane, p);
+    float sel_sum = 0.f, my_w = 0.f;
+    int my_id = -1;
+    for (int j = 0; j < k; ++j) {
+      float best = -1.f;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < kRouteMaxPerLane; ++i) {
+        const int e = lane + 32 * i;
+        if (e < E && p[i] > best) { best = p[i]; best_e = e; }   // ascending e in a lane: the first maximum wins
+      }
+#pragma unroll
+      for (int o = 16; o; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+      if ((best_e & 31) == lane) {                        // taken: never selected again (probabilities are >= 0)
+#pragma unroll
+        for (int i = 0; i < kRouteMaxPerLane; ++i)
+          if (i == (best_e >> 5)) p[i] = -1.f;
+      }
+      sel_sum += best;
+      if (lane == j) { my_w = best; my_id = best_e; }
+    }
+    if (lane < k) {
+      w[(size_t)t * k + lane] = norm ? my_w / sel_sum : my_w;
+      idx[(size_t)t * k + lane] = my_id;
+    }
+  }
+}
+
+// dlogits = p * (dp - sum_e dp_e p_e), with dp_e = (dw_e - sum_j dw_j w_j) / S for selected e (S = sum of the
+// selected probabilities; without renormalisation dp_e = dw_e), 0 elsewhere.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_route_topk_bwd_kernel(const T* __restrict__ logits, int ld,
+                                                                 const int* __restrict__ idx, const float* __restrict__ dw,
+                                                                 float* __restrict__ dlogits, int Tn, int E, int k, int norm) {
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < Tn; t += warps) {
+    float p[kRouteMaxPerLane], dp[kRouteMaxPerLane];
+    route_softmax(logits + (size_t)t * ld, E, lane, p);
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) dp[i] = 0.f;
+    // lanes < k hold one selected expert each
+    const int my_e = lane < k ? idx[(size_t)t * k + lane] : -1;
+    const float my_dw = lane < k ? dw[(size_t)t * k + lane] : 0.f;
+    float S = 0.f, dot = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int e = __shfl_sync(0xffffffffu, my_e, j);
+      const float g = __shfl_sync(0xffffffffu, my_dw, j);
+      float mine = 0.f;
+#pragma unroll
+      for (int i = 0; i < kRouteMaxPerLane; ++i)
+        if (i == (e >> 5)) mine = p[i];
+      const float pe = __shfl_sync(0xffffffffu, mine, e & 31);
+      S += pe;
+      dot += g * pe;
+    }
+    float acc = 0.f;
+    // with renormalisation: w_j = p_j / S  =>  dp_e = (dw_e - sum_j dw_j p_j / S) / S on the selected set
+    const float mean = norm ? dot / S : 0.f;
+    const float invS = norm ? 1.f / S : 1.f;
+    for (int j = 0; j < k; ++j) {
+      const int e = __shfl_sync(0xffffffffu, my_e, j);
+      const float g = __shfl_sync(0xffffffffu, my_dw, j);
+      if ((e & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < kRouteMaxPerLane; ++i)
+          if (i == (e >> 5)) dp[i] = (g - mean) * invS;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) acc += dp[i] * p[i];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E) dlogits[(size_t)t * E + e] = p[i] * (dp[i] - acc);
+    }
+  }
+}
+
+extern "C" int sb_moe_route_topk(const void* logits, int is_bf16, int ld, float* w, int* idx, int T, int E, int k,
+                                 int norm, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || E > 32 * kRouteMaxPerLane || k < 1 || k > 32 || k > E) return -3;
+  const int grid = moe_grid(T);
+  if (is_bf16)
+    moe_route_topk_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)logits, ld, w, idx, T, E, k, norm);
+  else
+    moe_route_topk_kernel<<<grid, 256, 0, stream>>>((const float*)logits, ld, w, idx, T, E, k, norm);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_moe_route_topk_bwd(const void* logits, int is_bf16, int ld, const int* idx, const float* dw,
+                                     float* dlogits, int T, int E, int k, int norm, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 1 || E > 32 * kRouteMaxPerLane || k < 1 || k > 32 || k > E) return -3;
+  const int grid = moe_grid(T);
+  if (is_bf16)
+    moe_route_topk_bwd_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)logits, ld, idx, dw, dlogits, T, E, k, norm);
+  else
+    moe_route_topk_bwd_kernel<<<grid, 256, 0, stream>>>((const float*)logits, ld, idx, dw, dlogits, T, E, k, norm);
+  return (int)cudaGetLastError();
+}

@@ -15,14 +15,11 @@ from .. import ops
 def route_topk(x: torch.Tensor, router_weight: torch.Tensor, top_k: int, norm_topk_prob: bool):
     """Router probabilities (fp32 softmax over experts), top-k ids and weights per token."""
     if x.is_cuda and router_weight.shape[0] % 8 == 0:
-        logits = ops.linear(x, router_weight).float()
+        logits = ops.linear(x, router_weight)          # bf16; the routing kernel does its softmax in fp32
     else:       # CPU, or an expert count the 16-byte epilogue stores cannot address
         logits = F.linear(x.float(), router_weight.float())
-    probs = torch.softmax(logits, dim=-1)
-    w, idx = torch.topk(probs, top_k, dim=-1)
-    if norm_topk_prob:
-        w = w / w.sum(-1, keepdim=True)
-    return w, idx
+    from ..ops.moe import route_topk as _route
+    return _route(logits, top_k, norm_topk_prob)
 
 
 _LOCAL_EP = None

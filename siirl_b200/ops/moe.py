@@ -330,3 +330,57 @@ def combine(ys: torch.Tensor, w: torch.Tensor, w_all: torch.Tensor, ep: ExpertPa
     values (used for the backward of remote rows)."""
     return _Combine.apply(ys, w.float(), w_all, ep, layout)
 
+
+
+# ---------------------------------------------------------------------------------------------
+# router: softmax + top-k (+ renormalisation) and its backward in one kernel each
+# ---------------------------------------------------------------------------------------------
+_ROUTE_MAX_EXPERTS = 256
+
+
+def route_topk_reference(logits: torch.Tensor, top_k: int, norm_topk_prob: bool):
+    """fp32 softmax over experts, top-k probabilities (renormalised to sum 1 if asked) and expert ids."""
+    probs = torch.softmax(logits.float(), dim=-1)
+    w, idx = torch.topk(probs, top_k, dim=-1)
+    if norm_topk_prob:
+        w = w / w.sum(-1, keepdim=True)
+    return w, idx
+
+
+class _RouteTopk(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits: torch.Tensor, top_k: int, norm: bool):
+        T, E = logits.shape
+        lg = logits if logits.stride(-1) == 1 else logits.contiguous()
+        w = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+        idx = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+        L = _lib.get_lib()
+        _lib.check(L.sb_moe_route_topk(_lib.ptr(lg), int(lg.dtype == torch.bfloat16), lg.stride(0), _lib.ptr(w),
+                                       _lib.ptr(idx), T, E, top_k, int(norm), _lib.stream()), "sb_moe_route_topk")
+        ctx.save_for_backward(lg, idx)
+        ctx.norm, ctx.top_k = bool(norm), top_k
+        ctx.mark_non_differentiable(idx)
+        return w, idx
+
+    @staticmethod
+    def backward(ctx, dw, _didx):
+        lg, idx = ctx.saved_tensors
+        T, E = lg.shape
+        dlog = torch.empty(T, E, dtype=torch.float32, device=lg.device)
+        L = _lib.get_lib()
+        _lib.check(L.sb_moe_route_topk_bwd(_lib.ptr(lg), int(lg.dtype == torch.bfloat16), lg.stride(0), _lib.ptr(idx),
+                                           _lib.ptr(dw.float().contiguous()), _lib.ptr(dlog), T, E, ctx.top_k,
+                                           int(ctx.norm), _lib.stream()), "sb_moe_route_topk_bwd")
+        return dlog.to(lg.dtype), None, None
+
+
+def route_topk(logits: torch.Tensor, top_k: int, norm_topk_prob: bool = True):
+    """``logits [T, E]`` (bf16 or fp32) -> ``(weights [T, k] fp32, expert ids [T, k] int64)``.  On a GPU one warp per
+    token does the softmax, the k arg-max rounds (ties to the lower expert id) and the renormalisation; the backward
+    recomputes the softmax from the logits.  Replaces softmax + topk + sum + div (4 launches and two ``[T, E]`` fp32
+    temporaries) of the library path."""
+    if logits.is_cuda and logits.shape[1] <= _ROUTE_MAX_EXPERTS and top_k <= 32 \
+            and logits.dtype in (torch.bfloat16, torch.float32):
+        w, idx = _RouteTopk.apply(logits, top_k, norm_topk_prob)
+        return w, idx.long()
+    return route_topk_reference(logits, top_k, norm_topk_prob)

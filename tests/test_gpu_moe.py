@@ -55,3 +55,31 @@ def test_grouped_wgrad_accumulates_into_main_grad():
     for e in range(E):
         want = 1.0 + dy[rows[e]:rows[e + 1]].float().t() @ xs[rows[e]:rows[e + 1]].float()
         assert (W.main_grad[e] - want).abs().max().item() < 0.05 * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("T,E,k,norm,dtype", [(257, 128, 8, True, torch.float32), (64, 8, 2, False, torch.float32),
+                                             (1000, 60, 4, True, torch.bfloat16), (5, 256, 32, True, torch.float32),
+                                             (33, 4, 1, True, torch.float32)])
+def test_route_topk_kernel_matches_fp32_reference(T, E, k, norm, dtype):
+    from siirl_b200.ops import lib
+    from siirl_b200.ops.moe import route_topk, route_topk_reference
+    g = torch.Generator().manual_seed(T + E)
+    logits = (2.0 * torch.randn(T, E, generator=g)).to(dtype)
+    dw = torch.randn(T, k, generator=g)
+    lg = logits.cuda().requires_grad_()
+    w, idx = route_topk(lg, k, norm)
+    (w * dw.cuda()).sum().backward()
+    torch.cuda.synchronize()
+    lib.check_status()
+    lo = logits.float().requires_grad_()
+    wo, io = route_topk_reference(lo, k, norm)
+    (wo * dw).sum().backward()
+    assert idx.dtype == torch.int64 and w.dtype == torch.float32
+    # the selected SET must carry the same probabilities (bf16 logits can tie: compare sorted weights, and ids where
+    # the probabilities are distinct)
+    assert torch.allclose(w.cpu(), wo, rtol=1e-4, atol=1e-6)
+    pk = torch.softmax(logits.float(), -1).topk(min(k + 1, E), -1).values          # incl. the first one left out
+    distinct = (pk[:, :-1] - pk[:, 1:]).abs().min(-1).values > 1e-7 if E > 1 else torch.ones(T, dtype=torch.bool)
+    assert torch.equal(idx.cpu()[distinct], io[distinct])
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert torch.allclose(lg.grad.float().cpu()[distinct], lo.grad[distinct], rtol=tol, atol=tol * 1e-1)
