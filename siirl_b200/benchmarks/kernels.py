@@ -196,6 +196,14 @@ def bench_moe(small: bool):
         t_own = timeit(lambda: moe_forward(x, rw, gu, dn, k, True), iters=5)
     report("moe_mlp fwd: dispatch + grouped tcgen05 GEMMs + combine", t_own, fl, T=T, E=E, top_k=k,
            per_expert_cublas_loop_ms=round(t_lib, 4), speedup_vs_loop=round(t_lib / t_own, 3))
+    # router: one kernel against softmax + topk + sum + div on the same bf16 logits
+    from ..ops.moe import route_topk as route_kernel, route_topk_reference
+    logits = torch.randn(T, E, device="cuda").to(torch.bfloat16)
+    with torch.no_grad():
+        t_ref = timeit(lambda: route_topk_reference(logits, k, True), iters=10)
+        t_k = timeit(lambda: route_kernel(logits, k, True), iters=10)
+    print(json.dumps({"kernel": "moe_route_topk fwd", "ms": round(t_k, 4), "T": T, "E": E, "top_k": k,
+                      "library_softmax_topk_ms": round(t_ref, 4), "speedup": round(t_ref / t_k, 2)}))
     lib.check_status()
 
 
