@@ -163,7 +163,7 @@ def bench_gemm_decode(small: bool):
     lib.check_status()
 
 
-def bench_moe(small: bool):
+def bench_moe(small: bool, skip_library: bool = False):
     """Mixture-of-experts MLP of the Qwen3-30B-A3B shape on one GPU (all experts local): dispatch + two grouped
     tcgen05 GEMMs + SwiGLU + combine, against a loop of per-expert cuBLAS GEMMs (torch.matmul) over the same routing."""
     from ..models.moe import moe_forward, route_topk
@@ -192,7 +192,7 @@ def bench_moe(small: bool):
         return torch.zeros(T, H, dtype=ys.dtype, device="cuda").index_add_(0, order // k, ys)
 
     with torch.no_grad():
-        t_lib = timeit(library_loop, iters=5)
+        t_lib = float("nan") if skip_library else timeit(library_loop, iters=5)
         t_own = timeit(lambda: moe_forward(x, rw, gu, dn, k, True), iters=5)
     report("moe_mlp fwd: dispatch + grouped tcgen05 GEMMs + combine", t_own, fl, T=T, E=E, top_k=k,
            per_expert_cublas_loop_ms=round(t_lib, 4), speedup_vs_loop=round(t_lib / t_own, 3))
@@ -211,6 +211,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", default="all", choices=["all", "gemm", "gemm_decode", "attention", "lm_head", "memory", "moe"])
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--skip-library", action="store_true", help="moe: time only this repo's path (short launch lists)")
     a = ap.parse_args()
     print(json.dumps({"peaks": peaks(), "device": torch.cuda.get_device_name()}))
     if a.case in ("all", "gemm"):
@@ -224,7 +225,7 @@ def main():
     if a.case in ("all", "memory"):
         bench_memory_bound(a.small)
     if a.case in ("all", "moe"):
-        bench_moe(a.small)
+        bench_moe(a.small, a.skip_library)
 
 
 if __name__ == "__main__":

@@ -31,6 +31,10 @@ int sb_moe_route_topk(const void* logits, int is_bf16, int ld, float* w, int* id
                       cudaStream_t stream);
 int sb_moe_route_topk_bwd(const void* logits, int is_bf16, int ld, const int* idx, const float* dw, float* dlogits,
                           int T, int E, int k, int norm, cudaStream_t stream);
+int sb_moe_build_layout(const int* idx, int P, int E, int world, int rank, int T, int k, int capacity,
+                        int* chunk_counts, int* starts, int* rank_base, int* pair_rank, int* pair_slot,
+                        long long* slot_pair, int* slot_src_rank, int* slot_src_row, int* tile_group, int* group_rows,
+                        cudaStream_t stream);
 int sb_ag_gemm_bf16(const void* A, const void* staging, void* C, const void* bias, int M, int N, int K, long long lda,
                     long long ld, long long ldc, const void* ag_params, int copiers, int tile_n, int* status,
                     cudaStream_t stream);

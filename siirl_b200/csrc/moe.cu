@@ -314,3 +314,145 @@ extern "C" int sb_moe_route_topk_bwd(const void* logits, int is_bf16, int ld, co
     moe_route_topk_bwd_kernel<<<grid, 256, 0, stream>>>((const float*)logits, ld, idx, dw, dlogits, T, E, k, norm);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------
+// expert-sorted, 128-padded slot layout from the routing table: three launches
+// ---------------------------------------------------------------------------------------
+// Pair p = (src_rank * T + t) * k + j routes token t of src_rank to expert idx[p] (negative: padding token, gets
+// no slot).  Experts are laid out in id order, each padded to a multiple of 128 rows; inside an expert the pairs
+// keep ascending p (what a stable sort by expert gives), so the layout is deterministic.
+//   count:  per-chunk histograms (chunk = 1024 consecutive pairs) + initial values of the slot arrays
+//   scan:   per-expert exclusive scan over chunks, padded expert starts, per-rank bases, block -> expert table
+//   place:  stable rank inside the chunk (warp match + per-warp counts), slot of every pair, owner's slot arrays
+constexpr int kLayoutChunk = 1024;
+constexpr int kLayoutMaxE = 256;   // real experts; one dummy expert for padding tokens is appended
+
+__global__ void __launch_bounds__(kLayoutChunk) moe_layout_count_kernel(
+    const int* __restrict__ idx, int P, int E, int* __restrict__ chunk_counts, long long* __restrict__ slot_pair,
+    int* __restrict__ slot_src_rank, int* __restrict__ slot_src_row, int capacity) {
+  __shared__ int hist[kLayoutMaxE + 1];
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * kLayoutChunk + threadIdx.x;
+  if (p < P) {
+    int e = idx[p];
+    if (e < 0 || e >= E) e = E;
+    atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) chunk_counts[(size_t)blockIdx.x * (E + 1) + e] = hist[e];
+  for (int s = blockIdx.x * blockDim.x + threadIdx.x; s < capacity; s += gridDim.x * blockDim.x) {
+    slot_pair[s] = -1;
+    slot_src_rank[s] = 0;
+    slot_src_row[s] = -1;
+  }
+}
+
+__global__ void __launch_bounds__(1024) moe_layout_scan_kernel(int* __restrict__ chunk_counts, int n_chunks, int E,
+                                                               int world, int rank, int capacity,
+                                                               int* __restrict__ starts, int* __restrict__ rank_base,
+                                                               int* __restrict__ tile_group,
+                                                               int* __restrict__ group_rows) {
+  __shared__ int counts[kLayoutMaxE + 1];
+  __shared__ int s_starts[kLayoutMaxE + 2];
+  const int El = E / world;
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) {
+    int running = 0;
+    for (int c = 0; c < n_chunks; ++c) {
+      const int v = chunk_counts[(size_t)c * (E + 1) + e];
+      chunk_counts[(size_t)c * (E + 1) + e] = running;
+      running += v;
+    }
+    counts[e] = running;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e <= E; ++e) {
+      s_starts[e] = acc;
+      acc += (counts[e] + 127) / 128 * 128;
+    }
+    s_starts[E + 1] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= E + 1; e += blockDim.x) starts[e] = s_starts[e];
+  for (int r = threadIdx.x; r <= world; r += blockDim.x) rank_base[r] = s_starts[r * El];
+  const int base = s_starts[rank * El];
+  // padded end of my local experts in local coordinates: s_starts[rank*El + i + 1] - base
+  for (int i = threadIdx.x; i <= El; i += blockDim.x) {
+    const int v = i == 0 ? 0 : s_starts[rank * El + i] - base;
+    group_rows[i] = v < capacity ? v : capacity;
+  }
+  for (int b = threadIdx.x; b < capacity / 128; b += blockDim.x) {
+    const int row = b * 128;
+    int g = 0;   // number of local experts whose padded end is <= row
+    while (g < El && s_starts[rank * El + g + 1] - base <= row) ++g;
+    tile_group[b] = g < El ? g : -1;
+  }
+}
+
+__global__ void __launch_bounds__(kLayoutChunk) moe_layout_place_kernel(
+    const int* __restrict__ idx, int P, int E, int world, int rank, int T, int k, int capacity,
+    const int* __restrict__ chunk_offsets, const int* __restrict__ starts, const int* __restrict__ rank_base,
+    int* __restrict__ pair_rank, int* __restrict__ pair_slot, long long* __restrict__ slot_pair,
+    int* __restrict__ slot_src_rank, int* __restrict__ slot_src_row) {
+  __shared__ int wc[kLayoutChunk / 32][kLayoutMaxE + 2];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < (kLayoutChunk / 32) * (kLayoutMaxE + 2); i += blockDim.x) (&wc[0][0])[i] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * kLayoutChunk + threadIdx.x;
+  int e = E + 1;                                    // lanes past the end: a key of their own, never placed
+  if (p < P) {
+    e = idx[p];
+    if (e < 0 || e >= E) e = E;
+  }
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (rank_in_warp == 0) wc[warp][e] = __popc(peers);
+  __syncthreads();
+  for (int x = threadIdx.x; x <= E; x += blockDim.x) {
+    int running = 0;
+    for (int w = 0; w < kLayoutChunk / 32; ++w) {
+      const int v = wc[w][x];
+      wc[w][x] = running;
+      running += v;
+    }
+  }
+  __syncthreads();
+  if (p >= P) return;
+  const int El = E / world;
+  const int rank_in_e = chunk_offsets[(size_t)blockIdx.x * (E + 1) + e] + wc[warp][e] + rank_in_warp;
+  const int host = e / El;                          // == world for padding pairs
+  if (host >= world) {
+    pair_rank[p] = world - 1;
+    pair_slot[p] = -1;
+    return;
+  }
+  const int lslot = starts[e] + rank_in_e - rank_base[host];
+  pair_rank[p] = host;
+  pair_slot[p] = lslot < capacity ? lslot : -1;
+  if (host == rank && lslot < capacity) {
+    slot_pair[lslot] = p;
+    slot_src_rank[lslot] = p / (T * k);
+    slot_src_row[lslot] = (p / k) % T;
+  }
+}
+
+// scratch: chunk_counts [n_chunks * (E + 1)], starts [E + 2], rank_base [world + 1] (all int32)
+extern "C" int sb_moe_build_layout(const int* idx, int P, int E, int world, int rank, int T, int k, int capacity,
+                                   int* chunk_counts, int* starts, int* rank_base, int* pair_rank, int* pair_slot,
+                                   long long* slot_pair, int* slot_src_rank, int* slot_src_row, int* tile_group,
+                                   int* group_rows, cudaStream_t stream) {
+  if (P <= 0 || E < 1 || E > kLayoutMaxE || world < 1 || E % world || rank < 0 || rank >= world || capacity % 128 ||
+      capacity <= 0 || T <= 0 || k <= 0)
+    return -3;
+  const int n_chunks = (P + kLayoutChunk - 1) / kLayoutChunk;
+  moe_layout_count_kernel<<<n_chunks, kLayoutChunk, 0, stream>>>(idx, P, E, chunk_counts, slot_pair, slot_src_rank,
+                                                                slot_src_row, capacity);
+  moe_layout_scan_kernel<<<1, 1024, 0, stream>>>(chunk_counts, n_chunks, E, world, rank, capacity, starts, rank_base,
+                                                 tile_group, group_rows);
+  moe_layout_place_kernel<<<n_chunks, kLayoutChunk, 0, stream>>>(idx, P, E, world, rank, T, k, capacity, chunk_counts,
+                                                                starts, rank_base, pair_rank, pair_slot, slot_pair,
+                                                                slot_src_rank, slot_src_row);
+  return (int)cudaGetLastError();
+}

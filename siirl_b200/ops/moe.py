@@ -50,6 +50,43 @@ class MoeLayout:
         return self.pair_rank[lo:lo + T * k], self.pair_slot[lo:lo + T * k]
 
 
+_LAYOUT_MAX_EXPERTS = 256
+_FUSED_LAYOUT = True        # tests flip this to compare the kernels with the device-op construction below
+
+
+def _build_layout_fused(all_idx: torch.Tensor, num_experts: int, world: int, rank: int,
+                        capacity: Optional[int]) -> "MoeLayout":
+    """The same layout from three launches (histogram per 1024-pair chunk, scan, stable placement) instead of the
+    ~70 small device ops and the sort of the construction in ``build_layout``."""
+    W, T, k = all_idx.shape
+    dev = all_idx.device
+    El = num_experts // world
+    P = W * T * k
+    if capacity is None:
+        capacity = (P + El * BLOCK_ROWS + BLOCK_ROWS - 1) // BLOCK_ROWS * BLOCK_ROWS
+    idx = all_idx.reshape(-1)
+    idx = idx if idx.dtype == torch.int32 else idx.to(torch.int32)
+    idx = idx.contiguous()
+    n_chunks = (P + 1023) // 1024
+    i32 = dict(dtype=torch.int32, device=dev)
+    scratch = torch.empty(n_chunks * (num_experts + 1) + (num_experts + 2) + (world + 1), **i32)
+    chunk_counts = scratch[:n_chunks * (num_experts + 1)]
+    starts = scratch[n_chunks * (num_experts + 1):n_chunks * (num_experts + 1) + num_experts + 2]
+    rank_base = scratch[n_chunks * (num_experts + 1) + num_experts + 2:]
+    pair = torch.empty(2, P, **i32)
+    slot_src = torch.empty(2, capacity, **i32)
+    slot_pair = torch.empty(capacity, dtype=torch.int64, device=dev)
+    tile_group = torch.empty(capacity // BLOCK_ROWS, **i32)
+    group_rows = torch.empty(El + 1, **i32)
+    L = _lib.get_lib()
+    _lib.check(L.sb_moe_build_layout(_lib.ptr(idx), P, num_experts, world, rank, T, k, capacity, _lib.ptr(chunk_counts),
+                                     _lib.ptr(starts), _lib.ptr(rank_base), _lib.ptr(pair[0]), _lib.ptr(pair[1]),
+                                     _lib.ptr(slot_pair), _lib.ptr(slot_src[0]), _lib.ptr(slot_src[1]),
+                                     _lib.ptr(tile_group), _lib.ptr(group_rows), _lib.stream()), "sb_moe_build_layout")
+    return MoeLayout(world, rank, num_experts, k, T, capacity, pair[0], pair[1], slot_src[0], slot_src[1], slot_pair,
+                     tile_group, group_rows)
+
+
 def build_layout(all_idx: torch.Tensor, num_experts: int, world: int, rank: int,
                  capacity: Optional[int] = None) -> MoeLayout:
     """``all_idx [world, T, k]`` expert ids of every rank's tokens (all-gathered routing table).  Negative ids mark
@@ -59,6 +96,8 @@ def build_layout(all_idx: torch.Tensor, num_experts: int, world: int, rank: int,
     dev = all_idx.device
     El = num_experts // world
     P = W * T * k
+    if all_idx.is_cuda and num_experts <= _LAYOUT_MAX_EXPERTS and _FUSED_LAYOUT:
+        return _build_layout_fused(all_idx, num_experts, world, rank, capacity)
     flat = all_idx.reshape(-1).long()
     real_experts = num_experts
     flat = torch.where(flat < 0, torch.full_like(flat, real_experts), flat)     # padding -> a dummy last expert

@@ -83,3 +83,29 @@ def test_route_topk_kernel_matches_fp32_reference(T, E, k, norm, dtype):
     assert torch.equal(idx.cpu()[distinct], io[distinct])
     tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
     assert torch.allclose(lg.grad.float().cpu()[distinct], lo.grad[distinct], rtol=tol, atol=tol * 1e-1)
+
+
+@pytest.mark.parametrize("W,T,k,E,rank,cap", [(1, 300, 2, 8, 0, None), (2, 1000, 4, 16, 1, None), (4, 513, 8, 128, 2, None),
+                                              (1, 64, 1, 4, 0, None), (2, 700, 2, 256, 0, 1024), (1, 5000, 8, 128, 0, None)])
+def test_fused_layout_kernels_match_device_op_construction(W, T, k, E, rank, cap):
+    from siirl_b200.ops import lib
+    from siirl_b200.ops import moe as M
+    g = torch.Generator().manual_seed(W * 1000 + T)
+    idx = torch.randint(0, E, (W, T, k), generator=g, dtype=torch.int32)
+    idx[:, T - T // 7:, :] = -1                     # padding tokens at the end of every rank's rows
+    if E >= 8:
+        idx[idx == 3] = 5                           # an expert without tokens
+    idx = idx.cuda()
+    fused = M.build_layout(idx, E, W, rank, cap)
+    torch.cuda.synchronize()
+    lib.check_status()
+    M._FUSED_LAYOUT = False
+    try:
+        ref = M.build_layout(idx, E, W, rank, cap)
+    finally:
+        M._FUSED_LAYOUT = True
+    assert fused.capacity == ref.capacity
+    for name in ("pair_rank", "pair_slot", "slot_src_rank", "slot_src_row", "slot_pair", "tile_group", "group_rows"):
+        a, b = getattr(fused, name), getattr(ref, name)
+        assert a.dtype == b.dtype and a.shape == b.shape, name
+        assert torch.equal(a, b), name
