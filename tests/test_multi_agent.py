@@ -124,6 +124,19 @@ def test_import_string_forms(tmp_path):
     assert import_string(f"{f}:Env") is import_string(f"{f}:Env")
 
 
+def test_code_workflow_variant_loads_and_its_env_scores():
+    g = DAGConfigLoader.load_from_file(WORKFLOW.replace("workflow_marft.yaml", "workflow_marft_code.yaml"))
+    env_ref = g.nodes["rollout_actor"].agent_options["env_path"][0]
+    env = import_string(os.path.join(ROOT, env_ref.split(":")[0]) + ":" + env_ref.split(":")[1])()
+    env.reset()
+    spec = json.dumps({"inputs": ["1 2\n", "5 7\n"], "outputs": ["3\n", "12\n"]})
+    good = "```python\na, b = map(int, input().split())\nprint(a + b)\n```"
+    obs, score, stop = env.step(["plan: add them", good], spec)
+    assert score == 1.0 and stop and len(obs) == 2 and "All tests pass" in obs[1]
+    obs, score, stop = env.step(["plan", "```python\nprint(3)\n```"], spec)
+    assert score == 0.5 and not stop
+
+
 def test_example_workflow_file_loads():
     g = DAGConfigLoader.load_from_file(WORKFLOW)
     assert sorted({n.agent_group for n in g.nodes.values()}) == [0, 1]
