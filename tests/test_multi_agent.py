@@ -174,7 +174,7 @@ def test_two_agent_marft_training_run(tmp_path):
             "actor_rollout_ref.rollout.multi_turn.max_assistant_turns=2",
             "actor_rollout_ref.rollout.multi_turn.use_all_traj=True", "trainer.n_gpus_per_node=1",
             "trainer.device=cpu", "trainer.val_before_train=False", "trainer.logger=['jsonl']",
-            "trainer.total_training_steps=2", "trainer.save_freq=2", f"trainer.default_local_dir={tmp_path / 'ck'}"]
+            "trainer.total_training_steps=2", "trainer.save_freq=2", "trainer.test_freq=2", f"trainer.default_local_dir={tmp_path / 'ck'}"]
     out = subprocess.run([sys.executable, "-m", "siirl_b200.main_dag", *args], env=env, cwd=ROOT, capture_output=True,
                          text=True, timeout=900)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
@@ -188,6 +188,7 @@ def test_two_agent_marft_training_run(tmp_path):
         assert r["agent_0_critic/grad_norm"] > 0 and r["agent_1_critic/grad_norm"] > 0
         assert 0.0 <= r["critic/score/mean"] <= 1.0
         assert r["num_turns/max"] <= 2
+    assert "val-core/all/reward/mean" in m[1]          # validation runs the joint loop too
     step = tmp_path / "ck" / "global_step_2"
     assert (step / "actor_agent_0").is_dir() and (step / "actor_agent_1").is_dir()
     assert (step / "critic_agent_0").is_dir() and not (step / "critic_agent_1").exists()
