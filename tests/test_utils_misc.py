@@ -93,3 +93,11 @@ def test_math_equivalence_scorer():
     assert compute_score("prime_math", "thus \\boxed{\\frac{2}{4}}", "0.5") == 1.0
     assert compute_score("math_verify", "The answer is 7.", "\\boxed{7}") == 1.0
     assert compute_score("numina_olympiads", "no box here", "7") == 0.0
+
+
+def test_memory_helpers_on_cpu():
+    from siirl_b200.utils.memory_utils import memory_report, release_memory, reset_peak_stats
+    rep = memory_report()
+    assert set(rep) == {"allocated_gib", "reserved_gib", "max_allocated_gib", "free_gib", "total_gib"}
+    assert release_memory() >= 0.0
+    reset_peak_stats()
