@@ -357,8 +357,15 @@ class DAGWorker:
             if batch.meta.get("multi_agent"):
                 return NodeOutput(batch, {})          # the first rollout node already ran the joint loop
             out = self.multi_agent_loop.generate_sequence(batch.to("cpu")).to(self.device)
+            # turns used per sample = chronological index of its latest turn + 1 (rows are latest turn first)
+            first_rows = {}
+            for rid, st in zip(out.non_tensors["request_id"], out.non_tensors["traj_step"]):
+                first_rows.setdefault(rid, int(st) + 1)
+            turns = list(first_rows.values())
+            scores = [float(x) for x in out.non_tensors["env_score"]]
             return NodeOutput(out, {"perf/rollout_output_tokens_total": float(out.meta.get("total_output_tokens", 0)),
-                                    "num_turns/max": float(max(out.non_tensors["traj_step"])) + 1.0})
+                                    "num_turns/max": float(max(turns)), "num_turns/mean": sum(turns) / len(turns),
+                                    "env/score_mean": sum(scores) / max(len(scores), 1)})
         worker = self._arr(node)
         r = self.config.actor_rollout_ref.rollout
         if (r.multi_turn.enable or r.mode == "async") and worker.engine is not None \

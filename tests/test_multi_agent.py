@@ -187,7 +187,7 @@ def test_two_agent_marft_training_run(tmp_path):
     for r in m:
         assert r["agent_0_critic/grad_norm"] > 0 and r["agent_1_critic/grad_norm"] > 0
         assert 0.0 <= r["critic/score/mean"] <= 1.0
-        assert r["num_turns/max"] <= 2
+        assert 1 <= r["num_turns/mean"] <= r["num_turns/max"] <= 2 and 0.0 <= r["env/score_mean"] <= 1.0
     assert "val-core/all/reward/mean" in m[1]          # validation runs the joint loop too
     step = tmp_path / "ck" / "global_step_2"
     assert (step / "actor_agent_0").is_dir() and (step / "actor_agent_1").is_dir()
