@@ -583,9 +583,15 @@ class DAGWorker:
     def _maybe_inject_fault(self, node_id: str) -> None:
         for f in self.config.fault.inject or []:
             if int(f.get("rank", -1)) == self._rank and int(f.get("step", -1)) == self.global_steps \
-                    and f.get("node", node_id) == node_id and not f.get("_done"):
+                    and f.get("node", node_id) == node_id and not f.get("_done") \
+                    and int(f.get("restart", 0)) == int(os.environ.get("SIIRL_RESTART_COUNT", "0")):
                 f["_done"] = True
                 kind = f.get("kind", "raise")
+                if kind == "drop_heartbeat":
+                    # play a hung rank: stop reporting and stall; the launcher's watchdog has to end the job
+                    from ..execution.scheduler.launch import stop_heartbeat
+                    stop_heartbeat()
+                    time.sleep(float(f.get("seconds", 60.0)))
                 if kind == "raise":
                     raise RuntimeError(f"injected fault at rank {self._rank} step {self.global_steps} node {node_id}")
                 if kind == "exit":

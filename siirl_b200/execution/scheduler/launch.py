@@ -83,6 +83,71 @@ def find_free_port() -> int:
         return s.getsockname()[1]
 
 
+HEARTBEAT_EXIT_CODE = 124       # the job was stopped because a rank went silent (same code as timeout(1))
+
+
+def stale_ranks(store, ranks: List[int], timeout_s: float) -> List[int]:
+    """Ranks whose last heartbeat (``hb/<rank>`` = wall-clock seconds, written by ``start_heartbeat``) is older than
+    ``timeout_s``.  A rank that has not written yet (still importing, building its model) is not stale."""
+    now = time.time()
+    out = []
+    for r in ranks:
+        key = f"hb/{r}"
+        try:
+            if not store.check([key]):
+                continue
+            last = float(store.get(key).decode())
+        except Exception:  # noqa: BLE001 - a store hiccup must not take the job down
+            continue
+        if now - last > timeout_s:
+            out.append(r)
+    return out
+
+
+class Heartbeat:
+    """Daemon thread of a rank that writes ``hb/<rank>`` every ``interval_s`` seconds; ``stop()`` ends it (also what
+    the ``drop_heartbeat`` fault injection calls to play a hung rank)."""
+
+    def __init__(self, port: int, rank: int, interval_s: float = 1.0):
+        import datetime
+        import threading
+
+        import torch.distributed as dist
+        self._store = dist.TCPStore("127.0.0.1", port, is_master=False, timeout=datetime.timedelta(seconds=30))
+        self._key, self._interval = f"hb/{rank}", max(0.05, float(interval_s))
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, name="siirl-heartbeat", daemon=True)
+        self._thread.start()
+
+    def _run(self) -> None:
+        while not self._stop.is_set():
+            try:
+                self._store.set(self._key, repr(time.time()))
+            except Exception:  # noqa: BLE001 - the launcher went away; nothing left to report to
+                return
+            self._stop.wait(self._interval)
+
+    def stop(self) -> None:
+        self._stop.set()
+
+
+_HEARTBEAT: Optional[Heartbeat] = None
+
+
+def start_heartbeat(interval_s: float = 1.0) -> Optional[Heartbeat]:
+    """Called by every rank at start-up; a no-op unless the launcher asked for heartbeats."""
+    global _HEARTBEAT
+    port = os.environ.get("SIIRL_HEARTBEAT_PORT")
+    if port and _HEARTBEAT is None:
+        _HEARTBEAT = Heartbeat(int(port), int(os.environ.get("RANK", "0")), interval_s)
+    return _HEARTBEAT
+
+
+def stop_heartbeat() -> None:
+    if _HEARTBEAT is not None:
+        _HEARTBEAT.stop()
+
+
 def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = None, poll_s: float = 0.5,
                  heartbeat_timeout_s: float = 0.0, module: str = "siirl_b200.main_dag") -> int:
     """Spawn ``nproc`` ranks of ``python -m <module> <argv>`` on this node and babysit them.  Returns the exit code
@@ -93,17 +158,19 @@ def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = No
     base.update(env or {})
     base.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "WORLD_SIZE": str(nproc),
                  "LOCAL_WORLD_SIZE": str(nproc), "SIIRL_LAUNCHED": "1"})
-    for r in range(nproc):
-        e = dict(base)
-        e.update({"RANK": str(r), "LOCAL_RANK": str(r)})
-        procs.append(subprocess.Popen([sys.executable, "-m", module, *argv], env=e))
     store = None
     if heartbeat_timeout_s > 0:
         import datetime
 
         import torch.distributed as dist
-        store = dist.TCPStore("127.0.0.1", find_free_port(), is_master=True, wait_for_workers=False,
+        hb_port = find_free_port()
+        store = dist.TCPStore("127.0.0.1", hb_port, is_master=True, wait_for_workers=False,
                               timeout=datetime.timedelta(seconds=5))
+        base["SIIRL_HEARTBEAT_PORT"] = str(hb_port)
+    for r in range(nproc):
+        e = dict(base)
+        e.update({"RANK": str(r), "LOCAL_RANK": str(r)})
+        procs.append(subprocess.Popen([sys.executable, "-m", module, *argv], env=e))
     code = 0
     try:
         while True:
@@ -114,6 +181,13 @@ def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = No
                 break
             if all(s == 0 for s in states):
                 break
+            if store is not None:
+                stale = stale_ranks(store, [r for r, s in enumerate(states) if s is None], heartbeat_timeout_s)
+                if stale:
+                    print(f"[siirl_b200] no heartbeat from rank(s) {stale} for {heartbeat_timeout_s:.0f} s: stopping "
+                          f"the job", file=sys.stderr)
+                    code = HEARTBEAT_EXIT_CODE
+                    break
             time.sleep(poll_s)
     finally:
         for p in procs:

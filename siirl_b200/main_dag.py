@@ -74,6 +74,8 @@ def init_distributed(config: SiiRLArguments) -> int:
 
 def run_rank(config: SiiRLArguments):
     from .dag_worker.dagworker import DAGWorker
+    from .execution.scheduler.launch import start_heartbeat
+    start_heartbeat(config.fault.heartbeat_interval_s)
     world = init_distributed(config)
     validate_config(config, world)
     _, assignment, pgm = plan(config, world)
@@ -103,7 +105,11 @@ def main(argv: Optional[List[str]] = None) -> int:
         return 0
     restarts = 0
     while True:
-        code = launch_local(argv, nproc)
+        run_argv = list(argv)
+        if restarts > 0 and config.trainer.resume_mode == "disable":
+            run_argv.append("trainer.resume_mode=auto")       # a relaunch continues from the latest checkpoint
+        code = launch_local(run_argv, nproc, env={"SIIRL_RESTART_COUNT": str(restarts)},
+                            heartbeat_timeout_s=config.fault.heartbeat_timeout_s)
         if code == 0 or not config.fault.auto_restart or restarts >= config.fault.max_restarts:
             return code
         restarts += 1

@@ -599,10 +599,14 @@ class ProfilerArguments:
 class FaultArguments:
     """Host-side fault injection (native addition; the reference is fail-fast only).
     ``inject`` entries look like ``{"rank": 1, "step": 2, "node": "actor_train", "kind": "raise"}``;
-    kinds: raise, exit, sleep, drop_heartbeat, corrupt_ckpt_shard."""
+    kinds: raise, exit, sleep, drop_heartbeat (the rank stops reporting and stalls for ``seconds``).  An entry fires
+    once per launch; ``restart: k`` limits it to the k-th relaunch of ``auto_restart`` (default 0: the first launch).
+    ``heartbeat_timeout_s > 0`` makes the launcher stop the job (exit code 124) when a running rank has not reported
+    for that long; with ``auto_restart`` a failed job is relaunched from the latest checkpoint up to ``max_restarts``
+    times."""
     inject: List[Dict[str, Any]] = field(default_factory=list)
     heartbeat_interval_s: float = 1.0
-    heartbeat_timeout_s: float = 30.0
+    heartbeat_timeout_s: float = 0.0
     auto_restart: bool = False
     max_restarts: int = 0
 

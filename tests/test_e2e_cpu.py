@@ -196,3 +196,31 @@ def test_gspo_and_cpgd_variants(tmp_path, variant):
     m = _metrics(tmp_path / "log")
     assert [r["step"] for r in m] == [1, 2]
     assert all(r["actor/grad_norm"] > 0 for r in m)
+
+
+def test_silent_rank_is_detected_by_the_heartbeat_watchdog(tmp_path):
+    """Rank 1 stops reporting and stalls before the reward node: the launcher ends the job with code 124 long before
+    the stall (60 s) is over."""
+    import time
+    t0 = time.time()
+    out = _run([f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=2",
+                "fault.heartbeat_timeout_s=3", "fault.heartbeat_interval_s=0.5",
+                "fault.inject=[{rank: 1, step: 0, node: function_reward, kind: drop_heartbeat, seconds: 60}]",
+                *_SMALL], tmp_path / "log", timeout=600)
+    assert out.returncode == 124, out.stdout[-1000:] + out.stderr[-3000:]
+    assert "no heartbeat from rank(s) [1]" in out.stderr
+    assert time.time() - t0 < 55
+
+
+def test_auto_restart_resumes_from_the_latest_checkpoint(tmp_path):
+    """Rank 0 exits at step 2 of the first launch; the job is relaunched once, resumes at step 2 and finishes."""
+    ck = tmp_path / "c"
+    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=3", "trainer.save_freq=1",
+                "fault.auto_restart=True", "fault.max_restarts=1",
+                "fault.inject=[{rank: 0, step: 2, node: actor_train, kind: exit, code: 9}]",
+                "data.max_response_length=16"], tmp_path / "log", timeout=900)
+    assert out.returncode == 0, out.stdout[-1000:] + out.stderr[-3000:]
+    assert "restart 1/1" in out.stderr
+    steps = [r["step"] for r in _metrics(tmp_path / "log")]
+    assert steps[-1] == 3 and steps.count(3) == 1 and 1 in steps and 2 in steps
+    assert (ck / "latest_checkpointed_iteration.txt").read_text().strip() == "3"
