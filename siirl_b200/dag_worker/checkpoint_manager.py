@@ -16,7 +16,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-from ..utils.checkpoint.checkpoint_manager import find_latest_ckpt_path, remove_old_checkpoints
+from ..utils.checkpoint.checkpoint_manager import find_latest_complete_ckpt_path, remove_old_checkpoints
 
 
 class CheckpointManager:
@@ -71,7 +71,8 @@ class CheckpointManager:
         if t.resume_mode == "disable":
             return None
         if t.resume_mode == "auto":
-            return find_latest_ckpt_path(self.root)
+            # a damaged latest checkpoint (a shard cut short by a crash or a full disk) falls back to the one before
+            return find_latest_complete_ckpt_path(self.root)
         if t.resume_mode == "resume_path":
             p = t.resume_from_path
             if not isinstance(p, str) or "global_step_" not in p:

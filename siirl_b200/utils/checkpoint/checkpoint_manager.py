@@ -58,6 +58,60 @@ def find_latest_ckpt_path(root: str) -> Optional[str]:
     return path if os.path.isdir(path) else None
 
 
+def checkpoint_problems(step_dir: str) -> List[str]:
+    """Structural check of one ``global_step_N`` directory: every role directory has a readable manifest, all the
+    model shards of the world size that wrote it, and no truncated ``.pt`` file (``torch.save`` writes zip archives,
+    whose directory sits at the end of the file).  Returns the list of problems found (empty = complete)."""
+    import glob
+    import zipfile
+    problems: List[str] = []
+    roles = [d for d in sorted(os.listdir(step_dir)) if os.path.isdir(os.path.join(step_dir, d)) and "_agent_" in d]
+    if not roles:
+        problems.append("no role directory")
+    for role in roles:
+        d = os.path.join(step_dir, role)
+        try:
+            with open(os.path.join(d, "manifest.json")) as f:
+                manifest = json.load(f)
+        except (OSError, ValueError) as e:
+            problems.append(f"{role}: manifest unreadable ({type(e).__name__})")
+            continue
+        world = int(manifest.get("world_size", 1))
+        if "model" in manifest.get("contents", []):
+            shards = glob.glob(os.path.join(d, f"model_world_size_{world}_rank_*.pt"))
+            need = world if manifest.get("offsets") else 1
+            if len(shards) < need:
+                problems.append(f"{role}: {len(shards)} of {need} model shards")
+        for f in glob.glob(os.path.join(d, "*.pt")):
+            if os.path.getsize(f) == 0 or not zipfile.is_zipfile(f):
+                problems.append(f"{role}: {os.path.basename(f)} is truncated or not a torch archive")
+    return problems
+
+
+def find_latest_complete_ckpt_path(root: str, log=print) -> Optional[str]:
+    """The newest checkpoint that passes ``checkpoint_problems``: the tracked step first, then older steps."""
+    first = find_latest_ckpt_path(root)
+    if not os.path.isdir(root):
+        return None
+    steps = sorted((int(d.split("_")[-1]) for d in os.listdir(root)
+                    if d.startswith("global_step_") and d.split("_")[-1].isdigit()), reverse=True)
+    candidates = ([first] if first else []) + [os.path.join(root, f"global_step_{s}") for s in steps]
+    seen = set()
+    tracked = int(first.rstrip("/").split("_")[-1]) if first else None
+    for path in candidates:
+        if path in seen or not os.path.isdir(path):
+            continue
+        seen.add(path)
+        step = int(path.rstrip("/").split("_")[-1])
+        if tracked is not None and step > tracked:
+            continue                    # newer than the tracker: its save never completed
+        problems = checkpoint_problems(path)
+        if not problems:
+            return path
+        log(f"[checkpoint] skipping {path}: " + "; ".join(problems))
+    return None
+
+
 def remove_old_checkpoints(root: str, keep: int) -> None:
     if keep is None or keep <= 0:
         return

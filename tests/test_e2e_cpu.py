@@ -224,3 +224,22 @@ def test_auto_restart_resumes_from_the_latest_checkpoint(tmp_path):
     steps = [r["step"] for r in _metrics(tmp_path / "log")]
     assert steps[-1] == 3 and steps.count(3) == 1 and 1 in steps and 2 in steps
     assert (ck / "latest_checkpointed_iteration.txt").read_text().strip() == "3"
+
+
+def test_resume_falls_back_when_the_latest_checkpoint_is_damaged(tmp_path):
+    from siirl_b200.utils.checkpoint.checkpoint_manager import checkpoint_problems, find_latest_complete_ckpt_path
+    ck = tmp_path / "c"
+    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=2", "trainer.save_freq=1",
+                "data.max_response_length=16"], tmp_path / "log1")
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert checkpoint_problems(str(ck / "global_step_2")) == []
+    shard = ck / "global_step_2" / "actor_agent_0" / "model_world_size_2_rank_1.pt"
+    data = shard.read_bytes()
+    shard.write_bytes(data[:len(data) // 2])                       # cut short, as after a crash or a full disk
+    probs = checkpoint_problems(str(ck / "global_step_2"))
+    assert len(probs) == 1 and "model_world_size_2_rank_1.pt" in probs[0]
+    assert find_latest_complete_ckpt_path(str(ck), log=lambda *_: None) == str(ck / "global_step_1")
+    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=3", "trainer.resume_mode=auto",
+                "data.max_response_length=16"], tmp_path / "log2")
+    assert out.returncode == 0, out.stderr[-3000:]
+    assert [r["step"] for r in _metrics(tmp_path / "log2")] == [2, 3]      # continued after step 1
