@@ -33,9 +33,14 @@ struct PeerPtrs {
 // ---------------------------------------------------------------------------------------
 // reduce-scatter (pull) + squared norm
 // ---------------------------------------------------------------------------------------
+// `status` (optional): the device's status word.  When an earlier kernel of the stream gave up a bounded wait (the
+// barrier in front of this reduction, for one) the peers' gradients may be incomplete: the squared norm is made
+// infinite, which the ranks share through the norm all-reduce, so that every rank skips this optimizer step.
 __global__ void rs_reduce_kernel(PeerPtrs grads, int world, int rank, long long lo, long long n,
-                                 float* __restrict__ out_shard, float* __restrict__ sumsq) {
+                                 float* __restrict__ out_shard, float* __restrict__ sumsq, const int* status) {
   float ss = 0.f;
+  if (status && blockIdx.x == 0 && threadIdx.x == 0 && *reinterpret_cast<const volatile int*>(status) != 0)
+    atomicAdd(sumsq, __int_as_float(0x7f800000));
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -205,11 +210,11 @@ extern "C" int sb_ipc_handle_bytes() { return (int)sizeof(cudaIpcMemHandle_t); }
 
 // ---- fused collectives ---------------------------------------------------------------------------
 extern "C" int sb_rs_reduce(void* const* grad_ptrs, int world, int rank, long long lo, long long n, float* out_shard,
-                            float* sumsq, cudaStream_t stream) {
+                            float* sumsq, const int* status, cudaStream_t stream) {
   if (world > kMaxRanks || (n % 4) || (lo % 4)) return -3;
   if (n == 0) return 0;
   rs_reduce_kernel<<<comm_grid(n / 4, 256, 4), 256, 0, stream>>>(to_peers(grad_ptrs, world), world, rank, lo, n,
-                                                                 out_shard, sumsq);
+                                                                 out_shard, sumsq, status);
   return (int)cudaGetLastError();
 }
 

@@ -1,7 +1,7 @@
 // Cross-rank phase of the row-parallel GEMM fused with its all-reduce (included by gemm_tcgen05.cu inside namespace
 // sb; runs in the 128 epilogue threads of the CTA that completed an output tile).  Two protocols:
 //
-//  one-shot (ar.one_shot, decode-sized M <= 128): the finisher adds the local split-K slabs and PUSHES the fp32 tile
+//  one-shot (ar.one_shot; decode batches, and every size in a group of two): the finisher adds the local split-K slabs and PUSHES the fp32 tile
 //    into every rank's receive slab (remote stores do not stall), raises the tile's flag on every rank, waits for the
 //    flags of all ranks in its own array and sums the received tiles from LOCAL memory into the bf16 output.  Receive
 //    slabs alternate with the launch epoch, so a rank one launch ahead never overwrites data still being read; it

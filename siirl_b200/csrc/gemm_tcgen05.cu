@@ -91,8 +91,8 @@ struct ArParams {
   long long ldo;
   int world, rank;
   float* recv[kArMaxRanks];             // one-shot: fp32 [2 (epoch parity)][world (source)][recv_slab] per rank
-  long long recv_slab;                  // floats per (parity, source) slab: >= 128 * N
-  int one_shot;                         // 1: push protocol (M <= 128), 0: owner pull protocol
+  long long recv_slab;                  // floats per (parity, source) slab: >= rows of the largest one-shot call * N
+  int one_shot;                         // 1: push protocol, 0: owner pull protocol
 };
 
 __device__ __forceinline__ float4 ld_volatile_f4(const float* p) {

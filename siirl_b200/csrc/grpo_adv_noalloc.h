@@ -17,6 +17,9 @@
 //                   (s_b = sum_t rewards[b,t]; unbiased std; a group of one uses mean 0, std 1;
 //                   norm_by_std == 0 leaves out the division)
 //
+// A row whose gid lies outside [0, G) belongs to no group: the kernels skip it when they accumulate the group
+// statistics (nothing is read or written out of bounds) and its advantage row is written as zeros.
+//
 // Limits: B <= kGrpoNoAllocMaxRows and G <= kGrpoNoAllocMaxGroups.  Larger sizes are refused with
 // kGrpoNoAllocTooLarge and a message on stderr; nothing is launched.
 //
@@ -28,6 +31,10 @@
 //
 // First call on a device: the first call made while a given device is current looks up the device address of the
 // scratch array for that device (a synchronous runtime query).  Make that first call outside any stream capture.
+//
+// Host threads: the per-device address cache is filled without a lock.  Two host threads that make their first call
+// on the same device at the same time both look the address up and both store the same value, which is harmless;
+// the GPU-side sharing rule below applies to them like to any two calls.
 //
 // Sharing: all calls on one device use the same scratch, which keeps whatever the previous call left; the part
 // that must start from zero is cleared at the beginning of every call.  Two calls whose work overlaps on the GPU

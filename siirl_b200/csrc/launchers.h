@@ -140,7 +140,7 @@ int sb_ipc_open_handle(const unsigned char* in64, void** out);
 int sb_ipc_close_handle(void* p);
 int sb_ipc_handle_bytes();
 int sb_rs_reduce(void* const* grad_ptrs, int world, int rank, long long lo, long long n, float* out_shard,
-                 float* sumsq, cudaStream_t stream);
+                 float* sumsq, const int* status, cudaStream_t stream);
 int sb_adamw_allgather(float* master, float* m, float* v, const float* grad, void* const* param_ptrs, int world,
                        const float* sumsq, float* grad_norm_out, long long lo, long long n, float lr, float beta1,
                        float beta2, float eps, float weight_decay, int step, float max_norm, float grad_scale,
@@ -148,6 +148,15 @@ int sb_adamw_allgather(float* master, float* m, float* v, const float* grad, voi
 int sb_segment_pull(void* const* bases, int world, const void* segs, int n_segs, void* out, cudaStream_t stream);
 int sb_flag_barrier(void* const* flag_ptrs, int world, int rank, int epoch, int* status, long long limit_ms,
                     cudaStream_t stream);
+}
+
+extern "C" {
+// ---- decode_state.cu ----
+int sb_decode_prepare(const void* finished, const int* ctx_len, const int* rope_delta, int* pos, int* seq_ids,
+                      int* seq_lens, int* rope_pos, int S, cudaStream_t stream);
+int sb_decode_commit(const long long* tok, const float* lp, void* finished, void* hit_eos, int* ctx_len,
+                     int* remaining, int* gen_index, long long* last_token, long long* tokens_out, float* logp_out,
+                     long long* step_counter, int S, int R, long long eos, cudaStream_t stream);
 }
 
 extern "C" {

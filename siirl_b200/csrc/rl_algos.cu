@@ -287,7 +287,8 @@ extern "C" int sb_grpo_group_adv(const float* rewards, const float* mask, const 
                                  float* group_ws, float* adv, int B, int R, int G, float eps, int norm_by_std,
                                  cudaStream_t stream) {
   if (B == 0 || R == 0) return 0;
-  cudaMemsetAsync(group_ws, 0, sizeof(float) * 3 * G, stream);
+  const cudaError_t me = cudaMemsetAsync(group_ws, 0, sizeof(float) * 3 * G, stream);
+  if (me != cudaSuccess) return (int)me;
   row_sum_kernel<<<(B * 32 + 127) / 128, 128, 0, stream>>>(rewards, scores_ws, B, R);
   group_accum_kernel<<<(B + 127) / 128, 128, 0, stream>>>(scores_ws, gid, group_ws, B, G, 0);
   group_accum_kernel<<<(B + 127) / 128, 128, 0, stream>>>(scores_ws, gid, group_ws, B, G, 1);

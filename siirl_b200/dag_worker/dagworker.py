@@ -30,8 +30,10 @@ from ..execution.dag import Node, NodeRole, NodeType, TaskGraph
 from ..execution.scheduler.reward import compute_reward as guarded_compute_reward
 from ..execution.scheduler.reward import create_reward_manager
 from ..utils.logger.tracking import Tracking
+from ..utils.debug.profile import Profiler, mark_end_range, mark_start_range
 from ..utils.metrics.metric_utils import (compute_data_metric, compute_throughput_metrics, compute_timing_metrics,
-                                          reduce_metrics_across_ranks)
+                                          format_core_performance_metrics, reduce_metrics_across_ranks,
+                                          write_rank_performance_csv)
 from . import core_algos
 from .checkpoint_manager import CheckpointManager
 from .data_structures import NodeOutput
@@ -85,6 +87,9 @@ class DAGWorker:
         self.history: List[Dict[str, float]] = []
         self._dapo_gen_batches = 0
         self.last_step_tokens = self.last_h2d_bytes = self.last_d2h_bytes = 0
+        # per-call generation settings that win over the rollout config for the following steps, e.g.
+        # {"response_length": 128, "do_sample": False} (read by ``ActorRolloutRefWorker.generate_sequences``)
+        self.rollout_meta_overrides: Dict[str, Any] = {}
         self._multi_agent = False
         self.multi_agent_loop = None
         self._agent_ids: List[int] = [0]
@@ -115,6 +120,9 @@ class DAGWorker:
                                                           self.world_size, group=None, comm=self.comm,
                                                           name=f"dc_rank{self._rank}")
         self.validator = Validator(self)
+        # torch.profiler window on the steps / ranks named by ``profiler.*``; node handlers run inside NVTX ranges
+        # while it (or ``dag.enable_perf``) is on (reference: dagworker.py:206-212, 421-442)
+        self.profiler = Profiler(self.config.profiler, self._rank)
         self.checkpoint_manager = CheckpointManager(self)
         self.global_steps = self.checkpoint_manager.load_checkpoint()
         if self._rank == 0:
@@ -353,6 +361,7 @@ class DAGWorker:
         batch.meta.update({"eos_token_id": getattr(self.tokenizer, "eos_token_id", None),
                            "pad_token_id": getattr(self.tokenizer, "pad_token_id", 0) or 0,
                            "global_steps": self.global_steps})
+        batch.meta.update(self.rollout_meta_overrides)
         if self._multi_agent:
             if batch.meta.get("multi_agent"):
                 return NodeOutput(batch, {})          # the first rollout node already ran the joint loop
@@ -575,6 +584,7 @@ class DAGWorker:
             self.init_graph()
         try:
             self._run_training_loop()
+            self.checkpoint_manager.finalize()      # publish a checkpoint that was still being written
         finally:
             if self.tracker is not None:
                 self.tracker.finish()
@@ -617,7 +627,11 @@ class DAGWorker:
                     continue  # already consumed before the checkpoint we resumed from
                 if self.global_steps >= self.total_training_steps:
                     return
+                self.profiler.start_step(self.global_steps)
                 metrics = self._run_training_step(epoch, batch_idx)
+                trace = self.profiler.stop_step(self.global_steps)
+                if trace and self._rank == 0:
+                    print(f"[siirl_b200] profiler trace of step {self.global_steps}: {trace}", file=sys.stderr)
                 if metrics is None:
                     continue
                 self.global_steps += 1
@@ -631,6 +645,27 @@ class DAGWorker:
                 if self._rank == 0 and self.tracker is not None:
                     self.tracker.log(metrics, step=self.global_steps)
 
+    def train_step(self, epoch: int = 0, batch_idx: int = 0) -> Optional[Dict[str, float]]:
+        """One training step outside ``execute_task_graph`` (benchmarks, notebooks, tests): next dataloader batch ->
+        host-to-device copy -> DAG walk -> metrics on the host.  Returns ``None`` when the step produced too few
+        usable samples (DAPO) and has to be repeated with another generation batch."""
+        if not self._initialized:
+            self.init_graph()
+        metrics = self._run_training_step(epoch, batch_idx)
+        if metrics is not None:
+            self.global_steps += 1
+            self.history.append(metrics)
+        return metrics
+
+    def _check_kernel_status(self) -> None:
+        """Every bounded device-side wait (mbarrier, flag, peer) reports through one status word per GPU; a step whose
+        kernels gave up a wait has worked on incomplete data and must not be accepted.  Raises ``KernelStatusError``,
+        which ends the rank with a non-zero code so that the launcher's fail-fast / auto-restart takes over."""
+        if self.device.type != "cuda":
+            return
+        from ..ops import lib as _lib
+        _lib.check_status(self.device)
+
     def _run_training_step(self, epoch: int, batch_idx: int) -> Optional[Dict[str, float]]:
         self.timing_raw = {}
         metrics: Dict[str, float] = {}
@@ -639,12 +674,11 @@ class DAGWorker:
             with _Timer("data_loading", self.timing_raw, False):
                 batch = self.dataloader.run(epoch=epoch)
                 self.last_h2d_bytes = 0
-                if not getattr(self, "_bench_prestaged", False):
-                    batch = preprocess_dataloader(batch, n)
-                    if self.device.type == "cuda":
-                        batch = batch.pin_memory()
-                        self.last_h2d_bytes = batch.nbytes()
-                    batch = batch.to(self.device)
+                batch = preprocess_dataloader(batch, n)
+                if self.device.type == "cuda":
+                    batch = batch.pin_memory()
+                    self.last_h2d_bytes = batch.nbytes()
+                batch = batch.to(self.device)
             order = self.taskgraph.get_topological_sort()
             queue = deque(order)
             cur: Optional[Batch] = batch
@@ -664,11 +698,13 @@ class DAGWorker:
                         return None
                     cur = got
                 self._maybe_inject_fault(node.node_id)
+                nvtx = mark_start_range(node.node_id) if (self.enable_perf or self.profiler.prof is not None) else None
                 with _Timer(node.node_id, self.timing_raw, self.enable_perf or node.node_type in (
                         NodeType.MODEL_TRAIN, NodeType.MODEL_INFERENCE)):
                     out = node.run(batch=cur, config=self.config, process_group=self._node_group(node),
                                    agent_group=node.agent_group, cur_tp_rank=tp_rank, tp_size=tp_size, cur_node=node,
                                    _dag_worker_instance=self)
+                mark_end_range(nvtx)
                 if not isinstance(out, NodeOutput):
                     out = NodeOutput(out if out is not None else cur, {})
                 metrics.update(out.metrics or {})
@@ -683,6 +719,7 @@ class DAGWorker:
                     self.put_data_to_buffers(child.node_id, cur, dp_size, cdp, enforce_buffer=enforce, tp_rank=tp_rank)
                 prev_dp = dp_size
             self._dapo_gen_batches = 0
+        self._check_kernel_status()
         final = cur
         use_critic = self.config.algorithm.adv_estimator in ("gae", "gae_marft")
         keep = [k for k in ("response_mask", "attention_mask", "token_level_scores", "token_level_rewards",
@@ -695,8 +732,17 @@ class DAGWorker:
         metrics.update(compute_data_metric(cpu_view, use_critic))
         metrics.update(compute_timing_metrics(cpu_view, self.timing_raw))
         metrics.update(compute_throughput_metrics(cpu_view, self.timing_raw, 1))
-        metrics = reduce_metrics_across_ranks({k: float(v) for k, v in metrics.items()
-                                               if isinstance(v, (int, float))})
+        numeric = {k: float(v) for k, v in metrics.items() if isinstance(v, (int, float))}
+        if self.enable_perf:
+            # every rank's own numbers side by side, before they are reduced (reference: dag_utils.py:684-772)
+            model = os.path.basename(os.path.normpath(self.config.actor_rollout_ref.model.path or
+                                                      self.config.actor_rollout_ref.model.arch_preset or "model"))
+            if getattr(self, "_perf_dir", None) is None:
+                self._perf_dir = os.path.join("performance_logs", model, time.strftime("%Y-%m-%d-%H-%M-%S"))
+            write_rank_performance_csv(numeric, self.global_steps + 1, self._rank, self.world_size, self._perf_dir)
+        metrics = reduce_metrics_across_ranks(numeric)
         metrics["training/global_step"] = self.global_steps + 1
         metrics["training/epoch"] = epoch
+        if self._rank == 0 and self.config.trainer.logger and "console" in list(self.config.trainer.logger):
+            print(format_core_performance_metrics(metrics, self.global_steps + 1, self.enable_perf), flush=True)
         return metrics

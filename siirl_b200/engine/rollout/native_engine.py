@@ -183,6 +183,9 @@ class RolloutEngine:
         self.gen_index = torch.zeros(S, dtype=torch.int32, device=dev)
         self.hit_eos = torch.zeros(S, dtype=torch.bool, device=dev)
         self.rope_delta = torch.zeros(S, dtype=torch.int32, device=dev)    # cache position - rope position
+        # inputs of one decode forward, rewritten by the prepare kernel every step
+        self._step_bufs = {k: torch.zeros(S, dtype=torch.int32, device=dev)
+                           for k in ("pos", "seq_ids", "seq_lens", "rope_pos")}
         self._graphs.clear()
         self._out_buf = None
 
@@ -226,6 +229,8 @@ class RolloutEngine:
     def _decode_step(self, sp: SamplingParams, tokens_out: torch.Tensor, logp_out: torch.Tensor) -> None:
         """One lock-step decode of all slots.  Pure device work (graph-capturable)."""
         S = self.num_slots
+        if self.device.type == "cuda":
+            return self._decode_step_native(sp, tokens_out, logp_out)
         active = ~self.finished
         pos = torch.where(active, self.ctx_len, torch.full_like(self.ctx_len, -1))
         seq_ids = torch.where(active, self.slot_ids, torch.full_like(self.slot_ids, -1))
@@ -252,6 +257,29 @@ class RolloutEngine:
         self.finished |= done
         self.step_counter += 1
         _ = pad
+
+    def _decode_step_native(self, sp: SamplingParams, tokens_out: torch.Tensor, logp_out: torch.Tensor) -> None:
+        """The same step on CUDA: two bookkeeping kernels (``csrc/decode_state.cu``) around forward, LM head and
+        sampler; no element-wise torch launches."""
+        import ctypes
+
+        from ...ops import lib as _lib
+        L = _lib.get_lib()
+        S = self.num_slots
+        st = self._step_bufs
+        _lib.check(L.sb_decode_prepare(_lib.ptr(self.finished), _lib.ptr(self.ctx_len), _lib.ptr(self.rope_delta),
+                                       _lib.ptr(st["pos"]), _lib.ptr(st["seq_ids"]), _lib.ptr(st["seq_lens"]),
+                                       _lib.ptr(st["rope_pos"]), S, _lib.stream()), "sb_decode_prepare")
+        hidden = self.model.forward_cached(self.last_token, st["pos"], self.cache, self.block_table, st["seq_ids"],
+                                           seq_lens=st["seq_lens"], rope_positions=st["rope_pos"])
+        logits = lm_head_logits(hidden, self.model.head_weight)
+        tok, lp = sample(logits, sp.temperature, sp.top_k, sp.top_p, seed=sp.seed, step_dev=self.step_counter)
+        eos = -1 if (sp.eos_token_id is None or sp.ignore_eos) else int(sp.eos_token_id)
+        _lib.check(L.sb_decode_commit(_lib.ptr(tok), _lib.ptr(lp), _lib.ptr(self.finished), _lib.ptr(self.hit_eos),
+                                      _lib.ptr(self.ctx_len), _lib.ptr(self.remaining), _lib.ptr(self.gen_index),
+                                      _lib.ptr(self.last_token), _lib.ptr(tokens_out), _lib.ptr(logp_out),
+                                      _lib.ptr(self.step_counter), S, tokens_out.shape[1], ctypes.c_longlong(eos),
+                                      _lib.stream()), "sb_decode_commit")
 
     def _run_decode_steps(self, k: int, sp: SamplingParams, tokens_out, logp_out) -> None:
         if not self.use_cuda_graph:

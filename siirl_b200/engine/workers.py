@@ -361,18 +361,38 @@ class _ModelWorkerBase:
 
     # ---- checkpoints --------------------------------------------------------------------------------
     def save_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None, global_step: int = 0,
-                        max_ckpt_to_keep: Optional[int] = None, contents=None) -> None:
+                        max_ckpt_to_keep: Optional[int] = None, contents=None, async_save: bool = False):
+        """Write this rank's shard files under ``local_path`` (and copy them to ``hdfs_path`` when given).  Returns a
+        handle whose ``wait()`` must be called before the checkpoint is declared complete (asynchronous saves write
+        in a background thread; reference API: siirl/engine/fsdp_workers.py:1452-1499)."""
         from ..utils.checkpoint.checkpoint_manager import ShardedCheckpointManager
-        ShardedCheckpointManager(self.model, self.store, self.model_config, group=self.group,
-                                 contents=contents).save(local_path, global_step, extra={"opt_step": self.opt_step},
-                                                         max_ckpt_to_keep=max_ckpt_to_keep)
+        return ShardedCheckpointManager(self.model, self.store, self.model_config, group=self.group, contents=contents,
+                                        tokenizer=getattr(self, "tokenizer", None)).save(
+            local_path, global_step, extra={"opt_step": self.opt_step}, max_ckpt_to_keep=max_ckpt_to_keep,
+            async_save=async_save, hdfs_path=hdfs_path)
 
     def load_checkpoint(self, local_path: str, hdfs_path: Optional[str] = None,
                         del_local_after_load: bool = False) -> None:
+        """Load from ``local_path``; when it does not exist and ``hdfs_path`` is given the directory is fetched from
+        there first.  ``del_local_after_load`` removes the local copy afterwards (every rank has read its shard)."""
+        import os
+        import shutil
+
         from ..utils.checkpoint.checkpoint_manager import ShardedCheckpointManager
+        if hdfs_path and not os.path.isdir(local_path):
+            from ..utils.extras import fs
+            if self.rank == 0:
+                fs.copy(hdfs_path, local_path)
+            if self.world > 1:
+                dist.barrier(group=self.group)
         extra = ShardedCheckpointManager(self.model, self.store, self.model_config, group=self.group).load(local_path)
         if extra:
             self.opt_step = int(extra.get("opt_step", self.opt_step))
+        if del_local_after_load:
+            if self.world > 1:
+                dist.barrier(group=self.group)
+            if self.rank == 0:
+                shutil.rmtree(local_path, ignore_errors=True)
 
 
 class ActorRolloutRefWorker(_ModelWorkerBase):

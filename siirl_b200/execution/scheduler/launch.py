@@ -83,6 +83,25 @@ def find_free_port() -> int:
         return s.getsockname()[1]
 
 
+def host_store(timeout_s: float = 300.0, attempts: int = 8):
+    """A TCPStore server on a free loopback port, owned by the calling process: ``(store, port)``.  Picking a free
+    port and binding it later are two steps, and another job on the machine may take the port in between, so the
+    bind is retried on a fresh port when it fails."""
+    import datetime
+
+    import torch.distributed as dist
+    last: Optional[BaseException] = None
+    for _ in range(attempts):
+        port = find_free_port()
+        try:
+            store = dist.TCPStore("127.0.0.1", port, is_master=True, wait_for_workers=False,
+                                  timeout=datetime.timedelta(seconds=timeout_s))
+            return store, port
+        except (RuntimeError, OSError) as e:      # address already in use
+            last = e
+    raise RuntimeError(f"could not bind a rendezvous port after {attempts} attempts: {last}")
+
+
 HEARTBEAT_EXIT_CODE = 124       # the job was stopped because a rank went silent (same code as timeout(1))
 
 
@@ -152,20 +171,17 @@ def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = No
                  heartbeat_timeout_s: float = 0.0, module: str = "siirl_b200.main_dag") -> int:
     """Spawn ``nproc`` ranks of ``python -m <module> <argv>`` on this node and babysit them.  Returns the exit code
     (0 when every rank exited 0; otherwise the first non-zero code after the remaining ranks were terminated)."""
-    port = find_free_port()
+    # The launcher hosts the rendezvous store itself (the ranks join as clients, the way torchrun's agent does it):
+    # the port is bound here, by the process that chose it, so no other job can take it before rank 0 starts.
+    rdzv_store, port = host_store()
     procs: List[subprocess.Popen] = []
     base = dict(os.environ)
     base.update(env or {})
     base.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "WORLD_SIZE": str(nproc),
-                 "LOCAL_WORLD_SIZE": str(nproc), "SIIRL_LAUNCHED": "1"})
+                 "LOCAL_WORLD_SIZE": str(nproc), "SIIRL_LAUNCHED": "1", "TORCHELASTIC_USE_AGENT_STORE": "True"})
     store = None
     if heartbeat_timeout_s > 0:
-        import datetime
-
-        import torch.distributed as dist
-        hb_port = find_free_port()
-        store = dist.TCPStore("127.0.0.1", hb_port, is_master=True, wait_for_workers=False,
-                              timeout=datetime.timedelta(seconds=5))
+        store, hb_port = host_store(timeout_s=5.0)
         base["SIIRL_HEARTBEAT_PORT"] = str(hb_port)
     for r in range(nproc):
         e = dict(base)
@@ -199,5 +215,5 @@ def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = No
                 p.wait(timeout=max(0.1, deadline - time.time()))
             except subprocess.TimeoutExpired:
                 p.kill()
-        _ = store
+        _ = (store, rdzv_store)
     return code

@@ -106,8 +106,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     restarts = 0
     while True:
         run_argv = list(argv)
-        if restarts > 0 and config.trainer.resume_mode == "disable":
-            run_argv.append("trainer.resume_mode=auto")       # a relaunch continues from the latest checkpoint
+        if restarts > 0:
+            # a relaunch continues from the newest complete checkpoint of this job when there is one (also when the
+            # first launch started from ``resume_from_path``: reloading that path would repeat the steps since)
+            from .utils.checkpoint.checkpoint_manager import find_latest_complete_ckpt_path
+            root = os.path.expanduser(config.trainer.default_local_dir)
+            if config.trainer.resume_mode == "disable" or find_latest_complete_ckpt_path(root, log=lambda *_: None):
+                run_argv.append("trainer.resume_mode=auto")
         code = launch_local(run_argv, nproc, env={"SIIRL_RESTART_COUNT": str(restarts)},
                             heartbeat_timeout_s=config.fault.heartbeat_timeout_s)
         if code == 0 or not config.fault.auto_restart or restarts >= config.fault.max_restarts:

@@ -59,12 +59,13 @@ def to_hf_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
         yield "score.weight", model.value_head.data
 
 
-def save_hf_model(model, out_dir: str, max_shard_bytes: int = 4 << 30, tokenizer=None) -> None:
-    """Write ``config.json`` + sharded ``model-xxxxx-of-yyyyy.safetensors`` + index."""
+def save_hf_model(model, out_dir: str, max_shard_bytes: int = 4 << 30, tokenizer=None, tensors=None) -> None:
+    """Write ``config.json`` + sharded ``model-xxxxx-of-yyyyy.safetensors`` + index.  ``tensors``: a snapshot of
+    ``to_hf_state(model)`` taken earlier (asynchronous saves export the weights as they were at the snapshot)."""
     from safetensors.torch import save_file
     os.makedirs(out_dir, exist_ok=True)
     shards, cur, cur_bytes = [], {}, 0
-    for name, t in to_hf_state(model):
+    for name, t in (tensors if tensors is not None else to_hf_state(model)):
         t = t.detach().to("cpu").contiguous().clone()
         nbytes = t.numel() * t.element_size()
         if cur and cur_bytes + nbytes > max_shard_bytes:

@@ -133,7 +133,8 @@ class SymmComm:
         self.barrier(resync=True)                       # every rank's backward has finished writing its gradients
         self._sumsq.zero_()
         _lib.check(self.L.sb_rs_reduce(grads.ptr_array, self.world, self.rank, ll(store.lo), ll(store.shard_size),
-                                       _lib.ptr(self._shard_grad), _lib.ptr(self._sumsq), _lib.stream()),
+                                       _lib.ptr(self._shard_grad), _lib.ptr(self._sumsq),
+                                       _lib.ptr(_lib.status_word(self.device)), _lib.stream()),
                    "sb_rs_reduce")
         if extra_sumsq is not None:
             self._sumsq += extra_sumsq

@@ -35,16 +35,20 @@ class TPContext:
     row-parallel layer (tokens per forward x hidden size)."""
 
     def __init__(self, group, comm=None, max_rows: int = 8192, max_cols: int = 8192, max_tiles: int = 8192,
-                 fused_max_rows: int = 128):
+                 fused_max_rows: int = 128, one_shot_rows: int = 0):
         self.group = group
         self.world = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
         self.comm = comm
         self.max_rows, self.max_cols, self.max_tiles = max_rows, max_cols, max_tiles
-        # Measured on 2 x B200: the push protocol (M <= 128) beats GEMM + NCCL all-reduce by 1.2-1.4x; the owner-pull
-        # protocol for larger M is still 0.4-0.8x of the library path, so prefill-sized calls use the library
-        # collective unless this bound is raised.
+        # Two protocols (csrc/gemm_ar.cuh).  Push ("one shot"): every rank stores its fp32 partial tile into every
+        # peer's receive slab and each rank sums locally; (world - 1) x M x N x 4 bytes leave each GPU, which for two
+        # ranks is all an all-reduce can do anyway, so a group of two uses it at every size; larger groups use it up
+        # to 512 rows (decode batches).  Owner pull ("two shot") moves 2 x (world - 1) / world x M x N x 4 bytes but
+        # measured 0.4-0.8x of GEMM + NCCL all-reduce at prefill sizes, so beyond ``fused_max_rows`` rows such groups
+        # take the library collective.
         self.fused_max_rows = fused_max_rows
+        self.one_shot_rows = min(max_rows, one_shot_rows or (max_rows if self.world == 2 else 512))
         self._params: Dict[tuple, torch.Tensor] = {}
         self._slabs: Optional[torch.Tensor] = None
         if comm is not None and self.world > 1:
@@ -53,7 +57,7 @@ class TPContext:
             self.out = comm.alloc(n, torch.bfloat16)
             self.ready = comm.alloc(max_tiles * _MAX_RANKS, torch.int32)
             self.done = comm.alloc(max_tiles, torch.int32)
-            self.recv = comm.alloc(2 * self.world * 128 * max_cols, torch.float32)
+            self.recv = comm.alloc(2 * self.world * self.one_shot_rows * max_cols, torch.float32)
             self.local = torch.zeros(2 + max_tiles, dtype=torch.int32, device=comm.device)
             # split-K slabs of the decode path: at most one 128 x 128 tile per SM
             self._slabs = torch.empty(160 * 128 * 128, dtype=torch.float32, device=comm.device)
@@ -75,7 +79,7 @@ class TPContext:
                     arr[r] = p
             s.local = self.local.data_ptr()
             s.ldo, s.world, s.rank = N, self.world, self.rank
-            s.recv_slab, s.one_shot = 128 * self.max_cols, int(one_shot)
+            s.recv_slab, s.one_shot = self.one_shot_rows * self.max_cols, int(one_shot)
             raw = bytes(s)
             t = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(c.device)
             self._params[(N, one_shot)] = t
@@ -99,7 +103,8 @@ class TPContext:
         from ..ops.dense import _skinny_splits, linear
         M, K = x.shape
         N = w_shard.shape[0]
-        if M > self.fused_max_rows:
+        one_shot = M <= self.one_shot_rows
+        if not one_shot and M > self.fused_max_rows:
             y = linear(x, w_shard)
             dist.all_reduce(y, group=self.group)
             return y + bias if bias is not None else y
@@ -118,7 +123,7 @@ class TPContext:
         else:
             c_local, stride = self.partial, 0
         _lib.check(L.sb_gemm_ar_bf16(_lib.ptr(x), _lib.ptr(w_shard), _lib.ptr(bias), M, N, K, ll(x.stride(0)),
-                                     ll(w_shard.stride(0)), _lib.ptr(self._ar_params(N, M <= 128)), _lib.ptr(c_local), tile_n,
+                                     ll(w_shard.stride(0)), _lib.ptr(self._ar_params(N, one_shot)), _lib.ptr(c_local), tile_n,
                                      splits, ll(stride), self.max_tiles, _lib.ptr(_lib.status_word(x.device)),
                                      _lib.stream()), "sb_gemm_ar_bf16")
         return self.out[: M * N].view(M, N)

@@ -77,27 +77,53 @@ def checkpoint_problems(step_dir: str) -> List[str]:
             problems.append(f"{role}: manifest unreadable ({type(e).__name__})")
             continue
         world = int(manifest.get("world_size", 1))
-        if "model" in manifest.get("contents", []):
-            shards = glob.glob(os.path.join(d, f"model_world_size_{world}_rank_*.pt"))
-            need = world if manifest.get("offsets") else 1
-            if len(shards) < need:
-                problems.append(f"{role}: {len(shards)} of {need} model shards")
+        contents = manifest.get("contents", [])
+        sharded = bool(manifest.get("offsets"))
+        wanted = []
+        if "model" in contents:
+            wanted.append(("model", world if sharded else 1))
+        if "optimizer" in contents and sharded and manifest.get("has_optimizer_state", True):
+            wanted.append(("optim", world))
+        if "extra" in contents:
+            wanted.append(("extra_state", world))
+        if manifest.get("expert_parallel"):
+            wanted.append(("experts", world))
+        for kind, need in wanted:
+            have = {os.path.basename(f) for f in glob.glob(os.path.join(d, f"{kind}_world_size_{world}_rank_*.pt"))}
+            missing = [r for r in range(need) if f"{kind}_world_size_{world}_rank_{r}.pt" not in have]
+            if missing:
+                problems.append(f"{role}: {kind} shards of ranks {missing[:8]} missing ({need - len(missing)} of {need})")
         for f in glob.glob(os.path.join(d, "*.pt")):
             if os.path.getsize(f) == 0 or not zipfile.is_zipfile(f):
                 problems.append(f"{role}: {os.path.basename(f)} is truncated or not a torch archive")
+    data_files = glob.glob(os.path.join(step_dir, "data_dp_rank_*.pt"))
+    if not data_files:
+        problems.append("no dataloader state (data_dp_rank_*.pt)")
+    for f in data_files:
+        if os.path.getsize(f) == 0 or not zipfile.is_zipfile(f):
+            problems.append(f"{os.path.basename(f)} is truncated or not a torch archive")
     return problems
 
 
 def find_latest_complete_ckpt_path(root: str, log=print) -> Optional[str]:
-    """The newest checkpoint that passes ``checkpoint_problems``: the tracked step first, then older steps."""
+    """The newest checkpoint that passes ``checkpoint_problems``: the tracked step first, then older steps.  The
+    tracker file is written last, after every rank has finished its files: without one no save has ever completed
+    (a crash during the first save leaves step directories that may look whole), so nothing is resumed."""
     first = find_latest_ckpt_path(root)
     if not os.path.isdir(root):
+        return None
+    if not os.path.exists(os.path.join(root, "latest_checkpointed_iteration.txt")):
+        if any(d.startswith("global_step_") for d in os.listdir(root)):
+            log(f"[checkpoint] {root} has step directories but no latest_checkpointed_iteration.txt: no save ever "
+                f"completed, starting fresh")
         return None
     steps = sorted((int(d.split("_")[-1]) for d in os.listdir(root)
                     if d.startswith("global_step_") and d.split("_")[-1].isdigit()), reverse=True)
     candidates = ([first] if first else []) + [os.path.join(root, f"global_step_{s}") for s in steps]
     seen = set()
-    tracked = int(first.rstrip("/").split("_")[-1]) if first else None
+    with open(os.path.join(root, "latest_checkpointed_iteration.txt")) as f:
+        txt = f.read().strip()
+    tracked = int(txt) if txt.isdigit() else None
     for path in candidates:
         if path in seen or not os.path.isdir(path):
             continue
@@ -121,6 +147,39 @@ def remove_old_checkpoints(root: str, keep: int) -> None:
         shutil.rmtree(os.path.join(root, f"global_step_{s}"), ignore_errors=True)
 
 
+class PendingSave:
+    """Handle of one rank's checkpoint write: done already (synchronous save) or running in a thread.  ``wait()``
+    joins the thread and re-raises what it raised."""
+
+    def __init__(self, fn, run_async: bool):
+        self._error: Optional[BaseException] = None
+        self._thread = None
+        if not run_async:
+            fn()
+            return
+        import threading
+
+        def guarded():
+            try:
+                fn()
+            except BaseException as e:  # noqa: BLE001  (re-raised on the caller's thread by wait())
+                self._error = e
+
+        self._thread = threading.Thread(target=guarded, name="siirl-ckpt-writer", daemon=False)
+        self._thread.start()
+
+    def done(self) -> bool:
+        return self._thread is None or not self._thread.is_alive()
+
+    def wait(self) -> None:
+        if self._thread is not None:
+            self._thread.join()
+            self._thread = None
+        if self._error is not None:
+            err, self._error = self._error, None
+            raise err
+
+
 class ShardedCheckpointManager:
     def __init__(self, model, store, model_config, group=None, contents: Optional[List[str]] = None,
                  tokenizer=None):
@@ -138,42 +197,73 @@ class ShardedCheckpointManager:
                 os.path.join(d, f"extra_state_world_size_{w}_rank_{r}.pt"))
 
     def save(self, directory: str, global_step: int = 0, extra: Optional[Dict[str, Any]] = None,
-             max_ckpt_to_keep: Optional[int] = None) -> None:
+             max_ckpt_to_keep: Optional[int] = None, async_save: bool = False,
+             hdfs_path: Optional[str] = None) -> "PendingSave":
+        """Write this rank's files.  The state is snapshotted to host memory before the call returns; with
+        ``async_save`` the files are written by a background thread (reference: the Megatron manager's async save,
+        siirl/utils/checkpoint/megatron_checkpoint_manager.py:356-543) and the caller must ``wait()`` on the returned
+        handle before it declares the checkpoint complete.  ``hdfs_path``: after the local files are in place this
+        rank's files are also copied there (``hdfs dfs -put``; any path ``utils.extras.fs.copy`` accepts)."""
         os.makedirs(directory, exist_ok=True)
         mpath, opath, epath = self._names(directory)
         st = self.store
+        jobs: List[Any] = []            # (object, path) pairs, all tensors already on the host
         if st is not None:
             if "model" in self.contents:
-                _atomic_save({"flat": st.flat_param[st.lo:st.hi].detach().cpu(), "lo": st.lo, "hi": st.hi}, mpath)
+                jobs.append(({"flat": st.flat_param[st.lo:st.hi].detach().cpu(), "lo": st.lo, "hi": st.hi}, mpath))
             if "optimizer" in self.contents and st.master is not None:
-                _atomic_save(st.shard_state_dict(), opath)
+                jobs.append((st.shard_state_dict(), opath))
             ex = getattr(st, "expert", None)
             if ex is not None:      # this rank's experts (expert parallelism): parameters + full local state
-                _atomic_save({"flat": ex.flat_param.detach().cpu(), "state": ex.shard_state_dict()},
-                             os.path.join(directory, f"experts_world_size_{self.world}_rank_{self.rank}.pt"))
+                jobs.append(({"flat": ex.flat_param.detach().cpu(), "state": ex.shard_state_dict()},
+                             os.path.join(directory, f"experts_world_size_{self.world}_rank_{self.rank}.pt")))
         elif "model" in self.contents and self.rank == 0:
-            _atomic_save({"state_dict": {k: v.detach().cpu() for k, v in self.model.state_dict().items()}}, mpath)
+            jobs.append(({"state_dict": {k: v.detach().cpu() for k, v in self.model.state_dict().items()}}, mpath))
         if "extra" in self.contents:
-            _atomic_save({"global_step": global_step, "rng": get_rng_state(), "extra": extra or {}}, epath)
+            jobs.append(({"global_step": global_step, "rng": get_rng_state(), "extra": extra or {}}, epath))
+        manifest = None
         if self.rank == 0:
             manifest = {"world_size": self.world, "global_step": global_step,
                         "dtype": str(st.dtype) if st is not None else None,
                         "total": st.total if st is not None else None,
                         "offsets": {n: [o, k, list(s)] for n, (o, k, s) in st.offsets.items()} if st else None,
                         "model_config": self.model_config.to_dict() if self.model_config is not None else None,
+                        "has_optimizer_state": bool(st is not None and st.master is not None),
+                        "expert_parallel": bool(st is not None and getattr(st, "expert", None) is not None),
                         "contents": self.contents}
-            tmp = os.path.join(directory, "manifest.json.tmp")
-            with open(tmp, "w") as f:
-                json.dump(manifest, f)
-            os.replace(tmp, os.path.join(directory, "manifest.json"))
-            hf_dir = os.path.join(directory, "huggingface")
-            os.makedirs(hf_dir, exist_ok=True)
-            if "hf_model" in self.contents:
-                from ...models.hf_io import save_hf_model
-                save_hf_model(self.model, hf_dir, tokenizer=self.tokenizer)
-            elif self.model_config is not None:
-                with open(os.path.join(hf_dir, "config.json"), "w") as f:
-                    json.dump(self.model_config.to_hf_config(), f, indent=1)
+        hf_state = None
+        if self.rank == 0 and "hf_model" in self.contents and async_save:
+            # the exporter reads the live parameters: snapshot them now, the next optimizer step may run meanwhile
+            from ...models.hf_io import to_hf_state
+            hf_state = [(n, t.detach().to("cpu").clone()) for n, t in to_hf_state(self.model)]
+
+        def write() -> None:
+            written = []
+            for obj, path in jobs:
+                _atomic_save(obj, path)
+                written.append(path)
+            if manifest is not None:
+                tmp = os.path.join(directory, "manifest.json.tmp")
+                with open(tmp, "w") as f:
+                    json.dump(manifest, f)
+                os.replace(tmp, os.path.join(directory, "manifest.json"))
+                written.append(os.path.join(directory, "manifest.json"))
+                hf_dir = os.path.join(directory, "huggingface")
+                os.makedirs(hf_dir, exist_ok=True)
+                if "hf_model" in self.contents:
+                    from ...models.hf_io import save_hf_model
+                    save_hf_model(self.model, hf_dir, tokenizer=self.tokenizer, tensors=hf_state)
+                elif self.model_config is not None:
+                    with open(os.path.join(hf_dir, "config.json"), "w") as f:
+                        json.dump(self.model_config.to_hf_config(), f, indent=1)
+                written.append(hf_dir)
+            if hdfs_path:
+                from ..extras import fs
+                fs.makedirs(hdfs_path)
+                for path in written:
+                    fs.copy(path, hdfs_path.rstrip("/") + "/" + os.path.basename(path))
+
+        return PendingSave(write, async_save)
 
     def load(self, directory: str) -> Optional[Dict[str, Any]]:
         with open(os.path.join(directory, "manifest.json")) as f:
@@ -198,6 +288,11 @@ class ShardedCheckpointManager:
                 if os.path.exists(opath) and st.master is not None:
                     st.load_shard_state_dict(torch.load(opath, map_location="cpu", weights_only=False))
                 elif st.master is not None:
+                    if "optimizer" in manifest.get("contents", []) and manifest.get("has_optimizer_state", True):
+                        # the other ranks load their Adam moments and step count: starting this shard from zero
+                        # would give the shards different bias corrections
+                        raise FileNotFoundError(f"{opath}: the checkpoint lists optimizer state but this rank's "
+                                                f"shard is missing")
                     st.sync_master_from_params()
             else:
                 self._load_resharded(directory, saved_world, manifest)

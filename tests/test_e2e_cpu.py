@@ -37,7 +37,9 @@ def _metrics(log_dir):
 
 def test_grpo_two_ranks_three_steps_and_resume(tmp_path):
     ck = tmp_path / "ckpt"
-    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=3", "trainer.save_freq=2"],
+    remote = tmp_path / "remote"        # stands in for an hdfs:// directory (the copy helper takes local paths too)
+    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=3", "trainer.save_freq=2",
+                "actor_rollout_ref.actor.checkpoint.async_save=True", f"trainer.default_hdfs_dir={remote}"],
                tmp_path / "log1")
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     m = _metrics(tmp_path / "log1")
@@ -52,9 +54,16 @@ def test_grpo_two_ranks_three_steps_and_resume(tmp_path):
     step3 = ck / "global_step_3" / "actor_agent_0"
     assert (step3 / "manifest.json").exists() and (step3 / "model_world_size_2_rank_1.pt").exists()
     assert (ck / "global_step_3" / "data_dp_rank_1.pt").exists()
-    # resume: continues at step 4 and stops at 4
-    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=4", "trainer.resume_mode=auto"],
-               tmp_path / "log2")
+    # the asynchronous writers were joined before the tracker was written, and every file went to the remote copy
+    from siirl_b200.utils.checkpoint.checkpoint_manager import checkpoint_problems
+    assert checkpoint_problems(str(ck / "global_step_3")) == []
+    assert (remote / "latest_checkpointed_iteration.txt").read_text().strip() == "3"
+    assert checkpoint_problems(str(remote / "global_step_3")) == []
+    # resume on a machine with an empty local directory: the tracked step is fetched from the remote copy;
+    # continues at step 4 and stops at 4
+    fresh = tmp_path / "fresh"
+    out = _run([f"trainer.default_local_dir={fresh}", f"trainer.default_hdfs_dir={remote}",
+                "trainer.total_training_steps=4", "trainer.resume_mode=auto"], tmp_path / "log2")
     assert out.returncode == 0, out.stderr[-4000:]
     assert [r["step"] for r in _metrics(tmp_path / "log2")] == [4]
 
@@ -239,6 +248,19 @@ def test_resume_falls_back_when_the_latest_checkpoint_is_damaged(tmp_path):
     probs = checkpoint_problems(str(ck / "global_step_2"))
     assert len(probs) == 1 and "model_world_size_2_rank_1.pt" in probs[0]
     assert find_latest_complete_ckpt_path(str(ck), log=lambda *_: None) == str(ck / "global_step_1")
+    # an optimizer shard that is absent is a problem too (the other ranks would load theirs)
+    optim = ck / "global_step_1" / "actor_agent_0" / "optim_world_size_2_rank_0.pt"
+    kept = optim.read_bytes()
+    optim.unlink()
+    assert any("optim" in p for p in checkpoint_problems(str(ck / "global_step_1")))
+    assert find_latest_complete_ckpt_path(str(ck), log=lambda *_: None) is None
+    optim.write_bytes(kept)
+    # without the tracker file no save ever completed: nothing is resumed
+    tracker = ck / "latest_checkpointed_iteration.txt"
+    text = tracker.read_text()
+    tracker.unlink()
+    assert find_latest_complete_ckpt_path(str(ck), log=lambda *_: None) is None
+    tracker.write_text(text)
     out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=3", "trainer.resume_mode=auto",
                 "data.max_response_length=16"], tmp_path / "log2")
     assert out.returncode == 0, out.stderr[-3000:]

@@ -9,12 +9,18 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+def _port() -> str:
+    """A port that is free now: other jobs share the machine, fixed port numbers collide."""
+    from siirl_b200.execution.scheduler.launch import find_free_port
+    return str(find_free_port())
+
+
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
 def test_peer_memory_collectives():
     n = min(torch.cuda.device_count(), 8)
     here = os.path.dirname(os.path.abspath(__file__))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", "29533", os.path.join(here, "multi_gpu_worker.py")]
+           "127.0.0.1", "--master-port", _port(), os.path.join(here, "multi_gpu_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "MULTI_GPU_OK" in out.stdout
@@ -25,7 +31,7 @@ def test_fused_gemm_allreduce_and_tp_engine():
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ, TP_DEVICE="cuda", NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29543", os.path.join(here, "tp_worker.py")]
+           "127.0.0.1", "--master-port", _port(), os.path.join(here, "tp_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_OK" in out.stdout
@@ -36,7 +42,7 @@ def test_expert_parallel_dispatch_combine():
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ, EP_DEVICE="cuda", NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29547", os.path.join(here, "ep_worker.py")]
+           "127.0.0.1", "--master-port", _port(), os.path.join(here, "ep_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "EP_OK" in out.stdout

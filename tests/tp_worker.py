@@ -35,7 +35,7 @@ def main():
     # 1. row-parallel linear == full linear, decode-sized and prefill-sized, repeated (launch epochs advance)
     g = torch.Generator().manual_seed(7)
     K = 1024 * world
-    for M in (8, 64, 128, 300, 8):
+    for M in (8, 64, 128, 300, 512, 1000, 8):
         x = torch.randn(M, K, generator=g).to(dev, dtype)
         w = (0.05 * torch.randn(H, K, generator=g)).to(dev, dtype)
         b = torch.randn(H, generator=g).to(dev, dtype)
