@@ -107,17 +107,57 @@ def bench_attention(small: bool):
             out.backward(g, retain_graph=True)
 
         report("fmha_bwd (causal, GQA)", timeit(bwd), 2.5 * fl, T=T, seqs=len(lens))
+        if small:
+            continue
+        try:        # the library bar on the same box and shapes: flash-attn's varlen kernels (what the reference calls)
+            from flash_attn import flash_attn_varlen_func
+        except Exception:  # noqa: BLE001
+            continue
+        q = qkv.detach()[:, : hq * d].reshape(T, hq, d).contiguous().requires_grad_()
+        k = qkv.detach()[:, hq * d:(hq + hkv) * d].reshape(T, hkv, d).contiguous().requires_grad_()
+        v = qkv.detach()[:, (hq + hkv) * d:].reshape(T, hkv, d).contiguous().requires_grad_()
+        cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        mx = max(lens)
+        with torch.no_grad():
+            report("flash_attn 2.8 varlen fwd (library bar)",
+                   timeit(lambda: flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, causal=True)), fl, T=T, seqs=len(lens))
+        o2 = flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, causal=True)
+        g2 = torch.randn_like(o2)
+
+        def bwd2():
+            q.grad = k.grad = v.grad = None
+            o2.backward(g2, retain_graph=True)
+
+        report("flash_attn 2.8 varlen bwd (library bar)", timeit(bwd2), 2.5 * fl, T=T, seqs=len(lens))
     lib.check_status()
 
 
 def bench_lm_head(small: bool):
+    """Log-prob + entropy over the 152k vocabulary: the GEMM whose epilogue folds the softmax statistics (no logits in
+    memory) against the earlier GEMM -> fp32 logits -> row-reduction form, forward and forward + backward."""
+    from ..ops import lm_head as LM
     T, V, H = (1024, 152064, 3584) if small else (8192, 152064, 3584)
-    h = (0.5 * torch.randn(T, H, device="cuda")).to(torch.bfloat16)
-    w = (0.02 * torch.randn(V, H, device="cuda")).to(torch.bfloat16)
+    h = (0.5 * torch.randn(T, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    w = (0.02 * torch.randn(V, H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    w.main_grad = torch.zeros(V, H, device="cuda", dtype=torch.float32)
     y = torch.randint(0, V, (T,), device="cuda")
-    with torch.no_grad():
-        report("lm_head logprob+entropy fwd", timeit(lambda: lm_head_logprob_entropy(h, w, y, 1.0), iters=5),
-               2.0 * T * V * H, T=T, V=V)
+    g = torch.randn(T, device="cuda")
+    for fused in ((True,) if small else (True, False)):
+        LM.FUSED_EPILOGUE = fused
+        tag = "fused epilogue" if fused else "fp32 logits chunk + reduction kernel"
+        with torch.no_grad():
+            report(f"lm_head logprob+entropy fwd ({tag})",
+                   timeit(lambda: lm_head_logprob_entropy(h, w, y, 1.0), iters=5), 2.0 * T * V * H, T=T, V=V)
+        if small:
+            continue
+
+        def fb():
+            h.grad = None
+            lp, ent = lm_head_logprob_entropy(h, w, y, 1.0)
+            (lp * g + 0.01 * ent).sum().backward()
+
+        report(f"lm_head fwd+bwd ({tag})", timeit(fb, iters=3), 2.0 * T * V * H * 4, T=T, V=V)
+    LM.FUSED_EPILOGUE = True
     lib.check_status()
 
 
@@ -158,8 +198,14 @@ def bench_gemm_decode(small: bool):
             w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
             with torch.no_grad():
                 ms = timeit(lambda: ops.linear(x, w))
-            report(f"decode {name} (split-K GEMM + reduce)", ms, bytes_=N * K * 2, M=M, N=N, K=K,
-                   k_splits=dense._skinny_splits(M, N, K))
+            report(f"decode {name}" + (" (weights in the A operand, transposed store)" if M > 128 else
+                                       " (split-K GEMM + reduce)"), ms, bytes_=N * K * 2, M=M, N=N, K=K)
+            if M > 128:
+                dense.SWAP_OPERANDS_ABOVE_128_ROWS = False
+                with torch.no_grad():
+                    ms = timeit(lambda: ops.linear(x, w))
+                dense.SWAP_OPERANDS_ABOVE_128_ROWS = True
+                report(f"decode {name} (x in the A operand: two 128-row blocks)", ms, bytes_=N * K * 2, M=M, N=N, K=K)
     lib.check_status()
 
 

@@ -48,6 +48,14 @@ struct GemmParams {
   long long c_group_stride;
   const struct AgParams* ag;  // all-gather of B fused into the GEMM (device memory), or nullptr
   int ag_copiers;             // number of copier CTAs (== ag->copiers), 0 without ag
+  // vocabulary GEMM epilogues (EPI_LMSTAT / EPI_DLOGITS): rows are tokens, columns vocabulary entries
+  const long long* labels;    // [M] target id per row (< 0 or >= N: no target)
+  float inv_temp;             // logits are multiplied by this before the softmax
+  float4* lm_partial;         // EPI_LMSTAT out: [M, num_n_blocks] (max, sum exp(z - max), sum exp(z - max) * z, z[label] or -inf)
+  const float* lm_lse;        // EPI_DLOGITS in: [M] log-sum-exp, entropy (or null), d loss / d logp, d loss / d entropy (or null)
+  const float* lm_ent;
+  const float* lm_glogp;
+  const float* lm_gent;
 };
 
 // all-gather -> GEMM in one launch: B [N, K] is sharded by rows over the ranks (rows_per_rank each, in symmetric
@@ -71,7 +79,12 @@ struct TileInfo {
   bool skip;
 };
 
-enum { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_F32_AR = 3 };
+// EPI_BF16_T / EPI_F32_T store the tile TRANSPOSED (C[col * ldc + row]): the "swap A and B" form of a GEMM with few
+// tokens, where the weight matrix rides in the 128-row A operand (every weight byte is fetched once) and all tokens
+// sit in the B operand.  EPI_LMSTAT reduces each row of a vocabulary tile to online-softmax partial statistics and
+// EPI_DLOGITS turns the tile into the gradient of the logits; neither writes fp32 logits to memory.
+enum { EPI_BF16 = 0, EPI_F32_ACC = 1, EPI_F32 = 2, EPI_F32_AR = 3, EPI_BF16_T = 4, EPI_F32_T = 5, EPI_LMSTAT = 6,
+       EPI_DLOGITS = 7 };
 
 // Row-parallel GEMM fused with its all-reduce over peer memory (EPI_F32_AR).  Every rank of a tensor-parallel
 // group runs the same launch on its K-shard.  Per output tile: the fp32 partial goes to this rank's symmetric
@@ -417,6 +430,110 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if constexpr (EPI == EPI_BF16_T || EPI == EPI_F32_T) {
+        // lane = output column (weight row), register = output row (token): 32 lanes store 32 neighbouring elements
+        float bv = 0.f;
+        if constexpr (EPI == EPI_BF16_T) {
+          if (p.bias && row < p.M) bv = __bfloat162float(p.bias[row]);
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;  // uniform over the CTA: the remaining columns are tokens that do not exist
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.M) {
+            if constexpr (EPI == EPI_BF16_T) {
+              __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(p.C) + ti.c_off + row;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) cb[(long long)(col0 + i) * p.ldc] = __float2bfloat16(__uint_as_float(r[i]) + bv);
+            } else {
+              float* cf = reinterpret_cast<float*>(p.C) + ti.c_off + row;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) cf[(long long)(col0 + i) * p.ldc] = __uint_as_float(r[i]);
+            }
+          }
+        }
+      } else if constexpr (EPI == EPI_LMSTAT) {
+        // two sweeps over this thread's row of the tile in TMEM: row maximum, then the sums relative to it
+        constexpr float kLog2e = 1.4426950408889634f;
+        const float sc2 = p.inv_temp * kLog2e;
+        const long long y = row < p.M ? p.labels[row] : -1;
+        float m2 = -INFINITY;  // maximum of z * log2(e)
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) m2 = fmaxf(m2, __uint_as_float(r[i]) * sc2);
+        }
+        float ssum = 0.f, tsum = 0.f, zl = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (col0 + i < p.N) {
+              const float v = __uint_as_float(r[i]);
+              const float e = exp2f(v * sc2 - m2);
+              ssum += e;
+              tsum += e * (v * p.inv_temp);
+              if ((long long)(col0 + i) == y) zl = v * p.inv_temp;
+            }
+          }
+        }
+        if (row < p.M)
+          p.lm_partial[(long long)row * p.num_n_blocks + n0 / BN] = make_float4(m2 * (1.f / kLog2e), ssum, tsum, zl);
+      } else if constexpr (EPI == EPI_DLOGITS) {
+        // d z_j = g_logp * (1[j = y] - p_j) - g_H * p_j * (z_j - lse + H), times 1/temperature for d logits_j
+        const bool rv = row < p.M;
+        const long long y = rv ? p.labels[row] : -1;
+        const float l = rv ? p.lm_lse[row] : 0.f;
+        const float glp = (rv && y >= 0 && y < p.N) ? p.lm_glogp[row] : 0.f;
+        const float ge = (rv && p.lm_gent) ? p.lm_gent[row] : 0.f;
+        const float H = (rv && p.lm_ent) ? p.lm_ent[row] : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.N) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (rv) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (col0 + g * 8 + 8 <= p.N) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const float x = __uint_as_float(r[g * 8 + i]) * p.inv_temp;
+                  const float pj = __expf(x - l);
+                  const float onehot = ((long long)(col0 + g * 8 + i) == y) ? 1.f : 0.f;
+                  v[i] = (glp * (onehot - pj) - ge * pj * (x - l + H)) * p.inv_temp;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+                *reinterpret_cast<uint4*>(crow + g * 8) = o;
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -469,6 +586,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
           }
         }
+      }
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
@@ -603,6 +721,10 @@ static int dispatch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const Gem
   SB_CASE(0, 0, EPI_F32)
   SB_CASE(0, 1, EPI_F32)
   SB_CASE(0, 0, EPI_F32_AR)
+  SB_CASE(0, 0, EPI_BF16_T)
+  SB_CASE(0, 0, EPI_F32_T)
+  SB_CASE(0, 0, EPI_LMSTAT)
+  SB_CASE(0, 0, EPI_DLOGITS)
 #undef SB_CASE
   return -2;
 }
@@ -669,14 +791,29 @@ struct GroupArgs {
   long long c_group_stride;
 };
 
+struct LmArgs {
+  const long long* labels;
+  float inv_temp;
+  void* partial;
+  const float *lse, *ent, *glogp, *gent;
+};
+
 static int gemm_impl(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                      long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
                      int k_splits, long long slab_stride, const ArParams* ar, int* status, cudaStream_t stream,
-                     const GroupArgs* grp = nullptr, const AgParams* ag = nullptr, int ag_copiers = 0) {
+                     const GroupArgs* grp = nullptr, const AgParams* ag = nullptr, int ag_copiers = 0,
+                     const LmArgs* lm = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   // TMA needs 16-byte aligned bases and row pitches; the epilogue stores whole 16-byte groups of a row
-  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)C & 15)) return -3;
-  if (epi == EPI_BF16 ? ((ldc % 8) || (N % 8)) : ((ldc % 4) || (N % 4))) return -3;
+  if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15)) return -3;
+  if (epi == EPI_BF16_T || epi == EPI_F32_T || epi == EPI_LMSTAT) {
+    // element-wise (transposed) stores or no matrix output at all
+  } else if (epi == EPI_BF16 || epi == EPI_DLOGITS) {
+    if (((uintptr_t)C & 15) || (ldc % 8) || (N % 8)) return -3;
+  } else {
+    if (((uintptr_t)C & 15) || (ldc % 4) || (N % 4)) return -3;
+  }
+  if ((epi == EPI_LMSTAT || epi == EPI_DLOGITS) && !lm) return -3;
   // The driver-API tensor-map encoder needs a current context on the calling thread; threads
   // that only ever launched through torch (autograd workers) may not have one bound yet.
   static thread_local bool tl_context_bound = false;
@@ -716,9 +853,15 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, in
   p.num_n_blocks = (N + BN - 1) / BN;
   p.num_k_blocks = (K + kBK - 1) / kBK;
   if (k_splits < 1) k_splits = 1;
-  if (k_splits > 1 && epi != EPI_F32 && epi != EPI_F32_AR) return -2;  // split-K writes fp32 slabs
+  if (k_splits > 1 && epi != EPI_F32 && epi != EPI_F32_AR && epi != EPI_F32_T) return -2;  // split-K writes fp32 slabs
   if (k_splits > p.num_k_blocks) k_splits = p.num_k_blocks;
   p.ar = ar;
+  p.labels = nullptr; p.inv_temp = 1.f; p.lm_partial = nullptr;
+  p.lm_lse = p.lm_ent = p.lm_glogp = p.lm_gent = nullptr;
+  if (lm) {
+    p.labels = lm->labels; p.inv_temp = lm->inv_temp; p.lm_partial = reinterpret_cast<float4*>(lm->partial);
+    p.lm_lse = lm->lse; p.lm_ent = lm->ent; p.lm_glogp = lm->glogp; p.lm_gent = lm->gent;
+  }
   p.ag = ag;
   p.ag_copiers = ag ? ag_copiers : 0;
   p.tile_group = nullptr;
@@ -756,6 +899,28 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   if (epi == EPI_F32_AR) return -2;
   return gemm_impl(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, epi, tile_n, max_ctas, k_splits, slab_stride,
                    nullptr, status, stream);
+}
+
+// Vocabulary GEMM fused with the softmax statistics: logits[M, N] = A[M, K] * B[N, K]^T are reduced tile by tile in
+// the epilogue, `partial` receives [M, ceil(N / 256)] float4 (max, sum exp, sum exp * z, z[label]) of z = logits *
+// inv_temp; sb_lmhead_merge (lm_head.cu) folds them into log p(label), entropy and log-sum-exp per row.
+extern "C" int sb_gemm_lmstat_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                   const long long* labels, float inv_temp, void* partial, int* status,
+                                   cudaStream_t stream) {
+  LmArgs lm{labels, inv_temp, partial, nullptr, nullptr, nullptr, nullptr};
+  return gemm_impl(A, B, partial, nullptr, M, N, K, lda, ldb, 0, 0, 0, EPI_LMSTAT, 256, 0, 1, 0, nullptr, status, stream,
+                   nullptr, nullptr, 0, &lm);
+}
+
+// The same GEMM recomputed for backward: the epilogue writes bf16 d_logits[M, ldd] from the per-row log-sum-exp,
+// entropy (optional), d loss / d logp and d loss / d entropy (optional).
+extern "C" int sb_gemm_dlogits_bf16(const void* A, const void* B, void* dlogits, int M, int N, int K, long long lda,
+                                    long long ldb, long long ldd, const long long* labels, float inv_temp,
+                                    const float* lse, const float* ent, const float* g_logp, const float* g_ent,
+                                    int* status, cudaStream_t stream) {
+  LmArgs lm{labels, inv_temp, nullptr, lse, ent, g_logp, g_ent};
+  return gemm_impl(A, B, dlogits, nullptr, M, N, K, lda, ldb, ldd, 0, 0, EPI_DLOGITS, 256, 0, 1, 0, nullptr, status, stream,
+                   nullptr, nullptr, 0, &lm);
 }
 
 // Grouped GEMM for mixture-of-experts layers, one launch for all experts.

@@ -46,6 +46,11 @@ int sb_gemm_grouped_bf16(const void* A, const void* B, void* C, int M, int N, in
 int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, long long lda,
                  long long ldb, long long ldc, int a_mn, int b_mn, int epi, int tile_n, int max_ctas,
                  int k_splits, long long slab_stride, int* status, cudaStream_t stream);
+int sb_gemm_lmstat_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                        const long long* labels, float inv_temp, void* partial, int* status, cudaStream_t stream);
+int sb_gemm_dlogits_bf16(const void* A, const void* B, void* dlogits, int M, int N, int K, long long lda, long long ldb,
+                         long long ldd, const long long* labels, float inv_temp, const float* lse, const float* ent,
+                         const float* g_logp, const float* g_ent, int* status, cudaStream_t stream);
 // out = bf16(sum over `splits` fp32 slabs [M, N] + bias)
 int sb_splitk_reduce(const float* slabs, long long slab_stride, int splits, const void* bias, void* out,
                      long long ldo, int M, int N, cudaStream_t stream);
@@ -94,6 +99,8 @@ int sb_fmha_bwd(const void* qkv, const void* out, const void* d_out, const float
 
 extern "C" {
 // ---- lm_head.cu ----
+int sb_lmhead_merge(const void* partial, int tiles, const long long* labels, float* logp, float* entropy, float* lse,
+                    int rows, int V, cudaStream_t stream);
 int sb_lmhead_stats(const float* logits, long long ld, const long long* labels, float inv_temp, float* logp,
                     float* entropy, float* lse, int rows, int V, cudaStream_t stream);
 int sb_lmhead_dlogits(const float* logits, long long ld, const long long* labels, const float* lse,

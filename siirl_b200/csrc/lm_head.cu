@@ -139,9 +139,50 @@ lmhead_dlogits_kernel(const float* __restrict__ logits, long long ld, const long
   }
 }
 
+// Folds the per-tile partial statistics written by the vocabulary GEMM's epilogue (EPI_LMSTAT in gemm_tcgen05.cu):
+// partial[row, tile] = (max, sum exp(z - max), sum exp(z - max) * z, z[label] or -inf).  One warp per row.
+__global__ void lmhead_merge_kernel(const float4* __restrict__ partial, int tiles, const long long* __restrict__ labels,
+                                    float* __restrict__ logp, float* __restrict__ entropy, float* __restrict__ lse_out,
+                                    int rows, int V) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  OnlineStat st = {-INFINITY, 0.f, 0.f};
+  float zl = -INFINITY;
+  for (int t = lane; t < tiles; t += 32) {
+    const float4 q = partial[(size_t)row * tiles + t];
+    st = merge(st, OnlineStat{q.x, q.y, q.z});
+    zl = fmaxf(zl, q.w);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    OnlineStat other;
+    other.m = __shfl_xor_sync(0xffffffffu, st.m, o);
+    other.s = __shfl_xor_sync(0xffffffffu, st.s, o);
+    other.t = __shfl_xor_sync(0xffffffffu, st.t, o);
+    st = merge(st, other);
+    zl = fmaxf(zl, __shfl_xor_sync(0xffffffffu, zl, o));
+  }
+  if (lane == 0) {
+    const float lse = st.m + __logf(st.s);
+    const long long y = labels[row];
+    logp[row] = (y >= 0 && y < V && zl != -INFINITY) ? zl - lse : 0.f;
+    if (entropy) entropy[row] = lse - st.t / st.s;
+    if (lse_out) lse_out[row] = lse;
+  }
+}
+
 }  // namespace sb
 
 using namespace sb;
+
+extern "C" int sb_lmhead_merge(const void* partial, int tiles, const long long* labels, float* logp, float* entropy,
+                               float* lse, int rows, int V, cudaStream_t stream) {
+  if (rows == 0) return 0;
+  lmhead_merge_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(reinterpret_cast<const float4*>(partial), tiles, labels, logp,
+                                                         entropy, lse, rows, V);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int sb_lmhead_stats(const float* logits, long long ld, const long long* labels, float inv_temp,
                                float* logp, float* entropy, float* lse, int rows, int V, cudaStream_t stream) {

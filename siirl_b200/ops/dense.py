@@ -20,6 +20,7 @@ from . import lib as _lib
 from . import reference as ref
 
 EPI_BF16, EPI_F32_ACC, EPI_F32 = 0, 1, 2
+EPI_BF16_T, EPI_F32_T = 4, 5        # transposed stores of the "weights in the A operand" form (see linear_skinny)
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *, bias: Optional[torch.Tensor] = None,
@@ -104,6 +105,7 @@ class _LinearFn(torch.autograd.Function):
 
 
 _NUM_SMS = 148
+SWAP_OPERANDS_ABOVE_128_ROWS = True     # benchmarks flip this to time both forms
 
 
 def _skinny_splits(M: int, N: int, K: int) -> int:
@@ -125,12 +127,60 @@ def _skinny_splits(M: int, N: int, K: int) -> int:
     return best
 
 
+def _best_splits(n_tiles: int, nkb: int) -> int:
+    """Split-K factor that fills whole waves of the persistent grid with ``n_tiles`` output tiles of ``nkb``
+    k-blocks (1: no split)."""
+    if n_tiles >= _NUM_SMS or nkb < 8:
+        return 1
+    best, best_score = 1, -1.0
+    for s in range(1, min(nkb // 4, 16) + 1):
+        items = n_tiles * s
+        waves = (items + _NUM_SMS - 1) // _NUM_SMS
+        score = items / (waves * _NUM_SMS) - 0.01 * s
+        if score > best_score:
+            best, best_score = s, score
+    return best
+
+
+def _linear_weights_as_a(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """``x @ W^T + b`` for 129..512 rows with the operands swapped: the weight matrix goes through the 128-row A
+    operand and up to 256 rows of ``x`` form one B tile, so every weight byte is fetched from memory once per 256
+    rows (with x in the A operand each 128-row block of x re-reads the weights); the epilogue stores the tile
+    transposed."""
+    M, K = x2.shape
+    N = weight.shape[0]
+    L = _lib.get_lib()
+    ll = ctypes.c_longlong
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=x2.device)
+    n_tiles = (N + 127) // 128 * ((M + 255) // 256)
+    nkb = (K + 63) // 64
+    splits = _best_splits(n_tiles, nkb)
+    status = _lib.ptr(_lib.status_word(x2.device))
+    if splits <= 1:
+        # arguments in the kernel's terms: A = weight [N, K], B = x [M, K], C^T stored into out [M, N]
+        _lib.check(L.sb_gemm_bf16(_lib.ptr(weight), _lib.ptr(x2), _lib.ptr(out), _lib.ptr(bias), N, M, K,
+                                  ll(weight.stride(0)), ll(x2.stride(0)), ll(out.stride(0)), 0, 0, EPI_BF16_T, 256, 0,
+                                  1, ll(0), status, _lib.stream()), "sb_gemm_bf16")
+        return out
+    per = (nkb + splits - 1) // splits
+    eff = (nkb + per - 1) // per
+    slabs = torch.empty(eff, M, N, dtype=torch.float32, device=x2.device)
+    _lib.check(L.sb_gemm_bf16(_lib.ptr(weight), _lib.ptr(x2), _lib.ptr(slabs), None, N, M, K, ll(weight.stride(0)),
+                              ll(x2.stride(0)), ll(N), 0, 0, EPI_F32_T, 256, 0, eff, ll(M * N), status, _lib.stream()),
+               "sb_gemm_bf16")
+    _lib.check(L.sb_splitk_reduce(_lib.ptr(slabs), ll(M * N), eff, _lib.ptr(bias), _lib.ptr(out), ll(N), M, N,
+                                  _lib.stream()), "sb_splitk_reduce")
+    return out
+
+
 def linear_skinny(x2: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
     """Inference-only ``x @ W^T + b`` for a handful of rows (one token per running sequence): the contraction is
     split over CTAs so that all SMs stream the weights, partial sums land in fp32 slabs and one small kernel adds
     them (and the bias) into the bf16 output."""
     M, K = x2.shape
     N = weight.shape[0]
+    if M > 128 and N % 8 == 0 and weight.stride(-1) == 1 and SWAP_OPERANDS_ABOVE_128_ROWS:
+        return _linear_weights_as_a(x2, weight, bias)
     splits = _skinny_splits(M, N, K)
     if splits <= 1:
         return gemm(x2, weight, bias=bias, tile_n=128 if N <= 128 * _NUM_SMS else 0)

@@ -1,10 +1,16 @@
 """Fused LM-head log-prob + entropy: ``(logp[T], entropy[T]) = f(hidden[T,H], weight[V,H], labels[T])``.
 
-The ``[T, V]`` logits are never kept: tokens are processed in chunks, each chunk's logits go from the tcgen05
-vocabulary GEMM (fp32) straight into a one-pass online-softmax kernel, and backward recomputes the chunk,
-turns it into bf16 d_logits and feeds the two gradient GEMMs (``d_weight`` accumulates in fp32 in the GEMM
-epilogue).  API and semantics of the reference's ``linear_cross_entropy``
-(siirl/utils/kernel/linear_cross_entropy.py:40-117): logits are divided by ``temperature`` first."""
+Forward: the vocabulary GEMM (tcgen05, 128 x 256 tiles) reduces every row of every tile to online-softmax partial
+statistics in its epilogue -- (max, sum exp, sum exp * z, z[label]) read from the accumulator in TMEM -- and writes
+only those ``[T, V / 256]`` partials; a merge kernel folds them into log p(label), entropy and log-sum-exp.  No
+logits reach memory.  Backward recomputes the GEMM with an epilogue that writes the bf16 gradient of the logits
+directly (from the saved log-sum-exp / entropy and the incoming gradients), chunk by chunk, and feeds the two gradient
+GEMMs (``d_weight`` accumulates in fp32 in the GEMM epilogue).  API and semantics of the reference's
+``linear_cross_entropy`` (siirl/utils/kernel/linear_cross_entropy.py:40-117; kernels siirl/utils/kernel/kernels.py:
+153-287 forward, 1263-1375 backward): logits are divided by ``temperature`` first.
+
+``FUSED_EPILOGUE = False`` selects the earlier two-kernel form (fp32 logits chunk in memory, then a row-reduction
+kernel), kept as the comparison point of ``benchmarks/kernels.py``."""
 from __future__ import annotations
 
 import ctypes
@@ -17,6 +23,8 @@ from . import lib as _lib
 from . import reference as ref
 
 _f = ctypes.c_float
+FUSED_EPILOGUE = True
+_TILE_V = 256           # vocabulary columns per GEMM tile of the fused epilogues
 
 
 def _chunk_rows(V: int, budget_bytes: int = 1 << 30) -> int:
@@ -35,9 +43,27 @@ class _LmHeadFn(torch.autograd.Function):
         logp = torch.empty(T, dtype=torch.float32, device=hidden.device)
         ent = torch.empty(T, dtype=torch.float32, device=hidden.device) if with_entropy else None
         lse = torch.empty(T, dtype=torch.float32, device=hidden.device)
-        rows = min(_chunk_rows(V), max(T, 1))
-        logits = torch.empty(rows, V, dtype=torch.float32, device=hidden.device)
-        for s in range(0, T, rows):
+        ctx.fused = bool(FUSED_EPILOGUE and V % 8 == 0)
+        if ctx.fused:
+            tiles = (V + _TILE_V - 1) // _TILE_V
+            rows = min(16384, max(T, 1))
+            partial = torch.empty(rows * tiles * 4, dtype=torch.float32, device=hidden.device)
+            ll = ctypes.c_longlong
+            for s in range(0, T, rows):
+                e = min(s + rows, T)
+                h = hidden[s:e]
+                _lib.check(L.sb_gemm_lmstat_bf16(_lib.ptr(h), _lib.ptr(weight), e - s, V, H, ll(h.stride(0)),
+                                                 ll(weight.stride(0)), _lib.ptr(labels[s:e]), _f(inv_t),
+                                                 _lib.ptr(partial), _lib.ptr(_lib.status_word(hidden.device)),
+                                                 _lib.stream()), "sb_gemm_lmstat_bf16")
+                _lib.check(L.sb_lmhead_merge(_lib.ptr(partial), tiles, _lib.ptr(labels[s:e]), _lib.ptr(logp[s:e]),
+                                             _lib.ptr(ent[s:e] if ent is not None else None), _lib.ptr(lse[s:e]),
+                                             e - s, V, _lib.stream()), "sb_lmhead_merge")
+            rows = min(max(128, ((1 << 30) // (2 * V)) // 128 * 128), max(T, 1))    # backward: bf16 d_logits chunk
+        else:
+            rows = min(_chunk_rows(V), max(T, 1))
+            logits = torch.empty(rows, V, dtype=torch.float32, device=hidden.device)
+        for s in (range(0, T, rows) if not ctx.fused else ()):
             e = min(s + rows, T)
             lg = logits[: e - s]
             dense.gemm(hidden[s:e], weight, out=lg, epi=dense.EPI_F32)
@@ -65,17 +91,28 @@ class _LmHeadFn(torch.autograd.Function):
         need_dw = ctx.needs_input_grad[1]
         dw_acc = mg if mg is not None else (torch.zeros(V, H, dtype=torch.float32, device=hidden.device)
                                             if need_dw else None)
-        logits = torch.empty(rows, V, dtype=torch.float32, device=hidden.device)
+        logits = None if ctx.fused else torch.empty(rows, V, dtype=torch.float32, device=hidden.device)
         dlogits = torch.empty(rows, V, dtype=torch.bfloat16, device=hidden.device)
+        ll = ctypes.c_longlong
         for s in range(0, T, rows):
             e = min(s + rows, T)
-            lg, dl = logits[: e - s], dlogits[: e - s]
-            dense.gemm(hidden[s:e], weight, out=lg, epi=dense.EPI_F32)
-            _lib.check(L.sb_lmhead_dlogits(
-                _lib.ptr(lg), ctypes.c_longlong(V), _lib.ptr(labels[s:e]), _lib.ptr(lse[s:e]),
-                _lib.ptr(ent[s:e] if with_entropy else None), _lib.ptr(g_logp[s:e]),
-                _lib.ptr(g_ent[s:e] if g_ent is not None else None), _f(inv_t), _lib.ptr(dl), ctypes.c_longlong(V),
-                e - s, V, _lib.stream()), "sb_lmhead_dlogits")
+            dl = dlogits[: e - s]
+            if ctx.fused:
+                h = hidden[s:e]
+                _lib.check(L.sb_gemm_dlogits_bf16(
+                    _lib.ptr(h), _lib.ptr(weight), _lib.ptr(dl), e - s, V, H, ll(h.stride(0)), ll(weight.stride(0)),
+                    ll(V), _lib.ptr(labels[s:e]), _f(inv_t), _lib.ptr(lse[s:e]),
+                    _lib.ptr(ent[s:e] if with_entropy else None), _lib.ptr(g_logp[s:e]),
+                    _lib.ptr(g_ent[s:e] if g_ent is not None else None),
+                    _lib.ptr(_lib.status_word(hidden.device)), _lib.stream()), "sb_gemm_dlogits_bf16")
+            else:
+                lg = logits[: e - s]
+                dense.gemm(hidden[s:e], weight, out=lg, epi=dense.EPI_F32)
+                _lib.check(L.sb_lmhead_dlogits(
+                    _lib.ptr(lg), ctypes.c_longlong(V), _lib.ptr(labels[s:e]), _lib.ptr(lse[s:e]),
+                    _lib.ptr(ent[s:e] if with_entropy else None), _lib.ptr(g_logp[s:e]),
+                    _lib.ptr(g_ent[s:e] if g_ent is not None else None), _f(inv_t), _lib.ptr(dl),
+                    ctypes.c_longlong(V), e - s, V, _lib.stream()), "sb_lmhead_dlogits")
             if dh is not None:
                 dense.gemm(dl, weight, out=dh[s:e], b_mn=True)
             if need_dw:

@@ -154,7 +154,9 @@ def test_embedding_fwd_bwd():
     assert _rel_err(table.grad, want) < 1e-2
 
 
-@pytest.mark.parametrize("shape", [(64, 3584, 3584), (7, 3584, 18944), (128, 4608, 3584), (33, 256, 1024)])
+@pytest.mark.parametrize("shape", [(64, 3584, 3584), (7, 3584, 18944), (128, 4608, 3584), (33, 256, 1024),
+                                   (200, 4608, 3584), (256, 3584, 18944), (256, 37888, 3584), (300, 1000, 1024),
+                                   (512, 3584, 1792), (129, 136, 64)])
 def test_skinny_split_k_linear(shape):
     M, N, K = shape
     torch.manual_seed(9)
@@ -166,7 +168,17 @@ def test_skinny_split_k_linear(shape):
     lib.check_status()
     want = x.float() @ w.float().t() + b.float()
     assert _rel_err(y, want) < 1e-2
+    # no row or column of the (possibly transposed-store) tile went astray: element-wise bound, bf16 output rounding
+    assert (y.float() - want).abs().max().item() < 0.05 * want.abs().max().item() + 0.05
     assert dense._skinny_splits(64, 3584, 18944) > 1
+    if M > 128:     # the operand-swapped form and the plain form agree
+        dense.SWAP_OPERANDS_ABOVE_128_ROWS = False
+        try:
+            with torch.no_grad():
+                y2 = ops.linear(x, w, b)
+        finally:
+            dense.SWAP_OPERANDS_ABOVE_128_ROWS = True
+        assert _rel_err(y, y2) < 1e-2
 
 
 def test_optimizer_state_offload_round_trip():

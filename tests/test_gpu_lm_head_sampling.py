@@ -17,8 +17,11 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
-@pytest.mark.parametrize("T,V,H,temp", [(37, 1000, 128, 1.0), (300, 5003 // 8 * 8, 256, 0.7)])
-def test_lm_head_fwd_bwd(T, V, H, temp):
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("T,V,H,temp", [(37, 1000, 128, 1.0), (300, 5003 // 8 * 8, 256, 0.7), (257, 2048, 192, 1.3)])
+def test_lm_head_fwd_bwd(T, V, H, temp, fused, monkeypatch):
+    from siirl_b200.ops import lm_head
+    monkeypatch.setattr(lm_head, "FUSED_EPILOGUE", fused)
     torch.manual_seed(0)
     h = (0.5 * torch.randn(T, H, device=DEV)).to(torch.bfloat16).requires_grad_()
     w = (0.2 * torch.randn(V, H, device=DEV)).to(torch.bfloat16).requires_grad_()
