@@ -79,6 +79,7 @@ def bench_gemm_ar(comm):
                     fused_max_rows=1 << 30)     # measure the fused kernel at every size
     pk = peaks()
     for M, K, what in ((64, 18944, "decode down_proj"), (64, 3584, "decode o_proj"), (128, 18944, "decode down_proj"),
+                       (256, 18944, "decode down_proj"), (512, 18944, "decode down_proj"), (512, 3584, "decode o_proj"),
                        (4096, 18944, "prefill down_proj"), (8192, 3584, "prefill o_proj")):
         ks = K // world // 64 * 64
         x = torch.randn(M, ks, device="cuda", dtype=torch.bfloat16)
@@ -95,7 +96,8 @@ def bench_gemm_ar(comm):
         link = (world - 1) / world * M * H * (4 + 2)
         hbm = H * ks * 2
         target = max(flops / pk["tflops"] / 1e9, link / NVLINK_GBS / 1e6, hbm / pk["hbm_gbs"] / 1e6)
-        emit(case="gemm+all_reduce", shape=what, M=M, N=H, K_per_rank=ks, world=world, fused_ms=round(fused, 4),
+        emit(case="gemm+all_reduce", shape=what, protocol="push (one shot)" if M <= ctx.one_shot_rows else "owner pull",
+             M=M, N=H, K_per_rank=ks, world=world, fused_ms=round(fused, 4),
              gemm_plus_nccl_ms=round(nccl, 4), speedup=round(nccl / fused, 3), roofline_ms=round(target, 4),
              frac_of_roofline=round(target / fused, 3))
 

@@ -36,10 +36,14 @@ struct PeerPtrs {
 // `status` (optional): the device's status word.  When an earlier kernel of the stream gave up a bounded wait (the
 // barrier in front of this reduction, for one) the peers' gradients may be incomplete: the squared norm is made
 // infinite, which the ranks share through the norm all-reduce, so that every rank skips this optimizer step.
+// `accumulate`: out_shard += sum instead of out_shard = sum (per-layer reductions of a sharded-parameter store, one per
+// micro-batch); `sumsq` may be null then.
 __global__ void rs_reduce_kernel(PeerPtrs grads, int world, int rank, long long lo, long long n,
-                                 float* __restrict__ out_shard, float* __restrict__ sumsq, const int* status) {
+                                 float* __restrict__ out_shard, float* __restrict__ sumsq, const int* status,
+                                 int accumulate) {
   float ss = 0.f;
-  if (status && blockIdx.x == 0 && threadIdx.x == 0 && *reinterpret_cast<const volatile int*>(status) != 0)
+  if (sumsq && status && blockIdx.x == 0 && threadIdx.x == 0 &&
+      *reinterpret_cast<const volatile int*>(status) != 0)
     atomicAdd(sumsq, __int_as_float(0x7f800000));
   const long long n4 = n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
@@ -49,9 +53,14 @@ __global__ void rs_reduce_kernel(PeerPtrs grads, int world, int rank, long long 
       const float4 v = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + lo)[i];
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
+    if (accumulate) {
+      const float4 o = reinterpret_cast<const float4*>(out_shard)[i];
+      acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
+    }
     reinterpret_cast<float4*>(out_shard)[i] = acc;
     ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
   }
+  if (!sumsq) return;
   __shared__ float red[32];
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -214,7 +223,17 @@ extern "C" int sb_rs_reduce(void* const* grad_ptrs, int world, int rank, long lo
   if (world > kMaxRanks || (n % 4) || (lo % 4)) return -3;
   if (n == 0) return 0;
   rs_reduce_kernel<<<comm_grid(n / 4, 256, 4), 256, 0, stream>>>(to_peers(grad_ptrs, world), world, rank, lo, n,
-                                                                 out_shard, sumsq, status);
+                                                                 out_shard, sumsq, status, 0);
+  return (int)cudaGetLastError();
+}
+
+// out_shard[0, n) += sum over ranks of grads[r][lo, lo + n): the gradient reduce-scatter of one parameter unit
+extern "C" int sb_rs_reduce_acc(void* const* grad_ptrs, int world, int rank, long long lo, long long n,
+                                float* out_shard, cudaStream_t stream) {
+  if (world > kMaxRanks || (n % 4) || (lo % 4)) return -3;
+  if (n == 0) return 0;
+  rs_reduce_kernel<<<comm_grid(n / 4, 256, 4), 256, 0, stream>>>(to_peers(grad_ptrs, world), world, rank, lo, n,
+                                                                 out_shard, nullptr, nullptr, 1);
   return (int)cudaGetLastError();
 }
 

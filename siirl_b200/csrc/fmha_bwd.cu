@@ -250,21 +250,40 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     if (step + 1 < total_steps) {
       if (tid == 0) issue_loads(step + 1);
     }
-    // ---- dQ tile (lane = query row) -> fp32 reduction buffer ----
+    // ---- dQ tile -> fp32 reduction buffer ----
+    // TMEM hands every thread one query row (lane = row).  Adding that row to global memory from its own thread would
+    // make each warp instruction touch 32 rows, 16 bytes each: 32 partial-line atomics.  The tile is therefore turned
+    // through shared memory (the P^T / dS^T buffers, which the MMAs of this step have finished reading): rows are
+    // written as 16-byte pieces at slot (piece ^ (row & 31)), read back with lane = piece, and each warp instruction
+    // adds one whole 512-byte row, four full lines.
     {
-      const int qp = q0 + tid;
-      const bool row_valid = qp < seq_len;
-      float* qrow = p.dq_accum + (size_t)(seq_start + (row_valid ? qp : 0)) * (size_t)(p.Hq * D) + (size_t)h * D;
+      float4* stage = reinterpret_cast<float4*>(sPt);  // [128 rows][32 pieces] = 64 KB = sPt + sDst
+      static_assert(L::kDstOff == L::kPtOff + L::kSq, "the dQ staging tile spans the P^T and dS^T buffers");
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(tm_st + lane_off + c * 32, r);
         tmem_ld_wait();
-        if (row_valid) {
 #pragma unroll
-          for (int g = 0; g < 8; ++g)
-            red_add_v4(qrow + c * 32 + g * 4, __uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
-                       __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+        for (int g = 0; g < 8; ++g) {
+          const int piece = c * 8 + g;
+          stage[tid * (D / 4) + (piece ^ (tid & (D / 4 - 1)))] =
+              make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]), __uint_as_float(r[g * 4 + 2]),
+                          __uint_as_float(r[g * 4 + 3]));
+        }
+      }
+      __syncwarp();  // a warp reads back only the 32 rows its own lanes wrote
+      const int lane = tid & 31;
+      const int row0 = warp * 32;
+      if (lane < D / 4) {
+#pragma unroll 4
+        for (int rr = 0; rr < 32; ++rr) {
+          const int row = row0 + rr;
+          const int qp = q0 + row;
+          if (qp >= seq_len) break;
+          const float4 v = stage[row * (D / 4) + (lane ^ (row & (D / 4 - 1)))];
+          float* dst = p.dq_accum + (size_t)(seq_start + qp) * (size_t)(p.Hq * D) + (size_t)h * D + lane * 4;
+          red_add_v4(dst, v.x, v.y, v.z, v.w);
         }
       }
     }

@@ -148,6 +148,8 @@ int sb_ipc_close_handle(void* p);
 int sb_ipc_handle_bytes();
 int sb_rs_reduce(void* const* grad_ptrs, int world, int rank, long long lo, long long n, float* out_shard,
                  float* sumsq, const int* status, cudaStream_t stream);
+int sb_rs_reduce_acc(void* const* grad_ptrs, int world, int rank, long long lo, long long n, float* out_shard,
+                     cudaStream_t stream);
 int sb_adamw_allgather(float* master, float* m, float* v, const float* grad, void* const* param_ptrs, int world,
                        const float* sumsq, float* grad_norm_out, long long lo, long long n, float lr, float beta1,
                        float beta2, float eps, float weight_decay, int step, float max_norm, float grad_scale,

@@ -406,6 +406,7 @@ class DAGWorker:
             server = AsyncRolloutServer(worker.engine, self.tokenizer)
             self._agent_loops = AgentLoopManager(self.config, [server], self.tokenizer, tools, interactions)
         t0 = _time.time()
+        worker._full_weights(True)
         worker.engine.wake_up()
         r = self.config.actor_rollout_ref.rollout
         validate = bool(batch.meta.get("validate", False))
@@ -415,6 +416,7 @@ class DAGWorker:
         out = self._agent_loops.generate_sequences(batch.to("cpu"), sp)
         if r.free_cache_engine:
             worker.engine.sleep()
+            worker._full_weights(False)
         out.meta["timing_generate_s"] = _time.time() - t0
         out.meta["total_output_tokens"] = int(out["attention_mask"][:, -out["responses"].shape[1]:].sum())
         return out

@@ -138,11 +138,35 @@ class _ModelWorkerBase:
         elif trainable and pp_filter is not None:
             # gradients and optimizer state only for this stage's parameters; data parallelism across pipelines
             self.store = FlatParamStore(self.model, group=self._pp_dp_group, comm=None, param_filter=pp_filter)
+        elif trainable and self._zero3():
+            self.store = self._shard_params(self.model, model_args, trainable=True)
         elif trainable:
             self.store = FlatParamStore(self.model, group=self.group, comm=self.comm)
         else:
             for p in self.model.parameters():
                 p.requires_grad_(False)
+
+    def _zero3(self) -> bool:
+        """``fsdp_config.sharding=zero3``: parameters, gradients and optimizer state sharded over the worker group
+        (FSDP FULL_SHARD of the reference); ``zero2`` (default) keeps a bf16 replica of the parameters per rank."""
+        cfgs = getattr(self.config, "actor", self.config)
+        fc = getattr(cfgs, "fsdp_config", None)
+        return str(getattr(fc, "sharding", "zero2")).lower() in ("zero3", "full_shard", "fsdp")
+
+    def _shard_params(self, model, model_args, trainable: bool):
+        from ..parallel.sharded_params import ShardedParamStore
+        mc = self.model_config
+        if mc.is_moe or mc.lora_rank > 0 or getattr(self, "_pp_ctx", None) is not None:
+            raise ValueError("fsdp_config.sharding=zero3 supports dense models without LoRA or pipeline parallelism; "
+                             "use zero2 (replicated bf16 weights, sharded optimizer state) for those")
+        if trainable and not model.gradient_checkpointing:
+            raise ValueError("fsdp_config.sharding=zero3 needs model.enable_gradient_checkpointing=True: a layer's "
+                             "weights are regathered for its backward pass, which recomputes the layer")
+        if not trainable:
+            for p in model.parameters():
+                p.requires_grad_(False)
+        return ShardedParamStore(model, group=self.group, comm=self.comm if self.device.type == "cuda" else None,
+                                 optimizer_state=trainable, trainable=trainable)
 
     def _phase_sync(self) -> None:
         """Align the ranks of the worker group before a phase whose kernels wait on peers with a short bound (tensor /
@@ -449,6 +473,9 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 load_hf_weights(self.ref_model, margs.path)
             for p in self.ref_model.parameters():
                 p.requires_grad_(False)
+            self.ref_store = None
+            if self._zero3() and self.world > 1:
+                self.ref_store = self._shard_params(self.ref_model, margs, trainable=False)
             self._attach_pipeline_parallel(self.ref_model, False)
             self._attach_sequence_parallel(self.ref_model)
             self._attach_context_parallel(self.ref_model)
@@ -464,6 +491,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 max_len = max(max_len, per_image * e.num_images_in_input + 64 + e.action_chunks_len * e.action_token_len)
             self.tp_model = None
             tp = max(1, int(r.tensor_model_parallel_size))
+            self._full_weights(True)        # the engine (and its tensor-parallel slices) reads whole weights
             if tp > 1:
                 self.tp_model = self._build_tp_model(tp, r.max_num_batched_tokens)
             self.engine = RolloutEngine(self.tp_model or self.model, max_num_seqs=min(r.max_num_seqs, 1024),
@@ -481,8 +509,21 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 self.engine.borrowed = self.store.flat_grad
             if r.free_cache_engine:
                 self.engine.sleep()
+                self._full_weights(False)
         if self._embodied:
             self._init_embodied()
+
+    def _full_weights(self, on: bool) -> None:
+        """Parameter-sharded actor: regather the shards into a whole replica for the rollout engine (the train ->
+        rollout weight resync of the reference's sharding managers, siirl/engine/sharding_manager/fsdp_vllm.py:
+        113-159) and give the memory back afterwards.  A no-op for replicated weights."""
+        st = getattr(self, "store", None)
+        if st is None or not hasattr(st, "materialize_full"):
+            return
+        if on:
+            st.materialize_full()
+        else:
+            st.release_full()
 
     def _build_tp_model(self, tp: int, max_tokens: int):
         """Tensor-parallel rollout: consecutive blocks of ``tp`` ranks of the worker's group form one engine
@@ -545,12 +586,14 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         if self._is_actor and getattr(self, "store", None) is not None and \
                 self.config.actor.fsdp_config.optimizer_offload:
             self.store.offload_state()          # Adam moments wait in pinned host memory until the next update
+        self._full_weights(True)
         if getattr(self, "tp_model", None) is not None:
             self.tp_model.sync_weights()        # column-parallel copies follow the trained replica
         if self.embodied_rollout is not None and "task_id" in prompts:
             out = self.embodied_rollout.generate_sequences(prompts)
             if r.free_cache_engine:
                 self.engine.sleep()
+                self._full_weights(False)
             return out
         t0 = time.time()
         self.engine.wake_up()
@@ -624,6 +667,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         out.meta["total_input_tokens"] = int(prompts["attention_mask"].sum())
         if r.free_cache_engine:
             self.engine.sleep()
+            self._full_weights(False)
         return out
 
     # ---- scoring ----------------------------------------------------------------------------------------
@@ -653,6 +697,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
     def compute_log_prob(self, data: Batch) -> Batch:
         r = self.config.rollout
         self._phase_sync()
+        self._full_weights(False)       # sharded parameters: scoring gathers layer by layer
         lp, ent = self._logprob_pass(self.model, data, self.logprob_micro, r.log_prob_use_dynamic_bsz,
                                      r.log_prob_max_token_len_per_gpu, with_entropy=True)
         data["old_log_probs"] = lp
@@ -684,6 +729,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         a = self.config.actor
         t0 = time.time()
         self._phase_sync()
+        self._full_weights(False)
         if hasattr(self.store, "reload_state"):
             self.store.reload_state(wait=False)     # parked Adam moments stream back while the micro-batches run
         self.model.train()

@@ -127,6 +127,9 @@ class DecoderLayer(nn.Module):
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], positions, info: SeqInfo, rope, causal=True):
         """``h`` is the residual stream, ``delta`` the previous sub-layer output not yet added to it."""
         cfg = self.cfg
+        z3 = getattr(self, "zero3", None)
+        if z3 is not None:      # parameter-sharded training state: assemble this layer's weights (prefetched)
+            z3.fetch(self.zero3_index)
         x, h = ops.rmsnorm(delta if delta is not None else h, self.input_layernorm, cfg.rms_norm_eps,
                            residual=h if delta is not None else None)
         qkv = self.qkv(x, positions, rope)
@@ -231,13 +234,17 @@ class DecoderLM(nn.Module):
         delta = None
         offload = getattr(self, "activation_offload", None)
         ctx = offload.region() if (offload is not None and torch.is_grad_enabled()) else contextlib.nullcontext()
+        z3 = getattr(self.layers[0], "zero3", None) if len(self.layers) else None
         with ctx:   # tensors saved for backward move to pinned host memory when activation offload is attached
-            for layer in self.layers:
+            for li, layer in enumerate(self.layers):
                 if self.gradient_checkpointing and torch.is_grad_enabled():
                     if delta is not None:
                         # fold the pending sub-layer output into the residual stream first: the checkpoint then
                         # keeps ONE [T, H] tensor per layer instead of two
                         h, delta = h + delta, None
+                    if z3 is not None and z3.trainable and h.requires_grad:
+                        # the layer's input gradient is the last thing its backward produces: reduce-scatter then
+                        h.register_hook(z3.make_reduce_hook(li))
                     h, delta = ckpt.checkpoint(layer, h, None, positions, info, rope, use_reentrant=False)
                 else:
                     h, delta = layer(h, delta, positions, info, rope)

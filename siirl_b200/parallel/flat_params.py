@@ -37,11 +37,13 @@ def _round_up(x: int, m: int) -> int:
 class FlatParamStore:
     def __init__(self, module: nn.Module, group: Optional[dist.ProcessGroup] = None, comm=None,
                  optimizer_state: bool = True, param_filter=None, local_only: bool = False,
-                 grad_scale: Optional[float] = None):
+                 grad_scale: Optional[float] = None, param_alloc=None, with_grad: bool = True):
         """``param_filter(name) -> bool`` restricts the store to some parameters.  ``local_only`` makes a store
         whose parameters exist on this rank alone (expert-parallel experts): no reduce-scatter / all-gather, the
         whole state lives here, ``grad_scale`` (1 / data-parallel width) keeps their update on the same loss
-        scale as the replicated parameters, and the clipping norm comes from the caller (``global_sumsq``)."""
+        scale as the replicated parameters, and the clipping norm comes from the caller (``global_sumsq``).
+        ``param_alloc(numel, dtype)`` allocates the flat parameter buffer (a rank-local store whose parameters the
+        peers read: symmetric memory); ``with_grad=False`` builds no gradient buffer (frozen models)."""
         params = [(n, p) for n, p in module.named_parameters() if param_filter is None or param_filter(n)]
         if not params:
             raise ValueError("module has no parameters")
@@ -70,13 +72,15 @@ class FlatParamStore:
 
         alloc = self.comm.alloc if (self.comm is not None and self.device.type == "cuda") else (
             lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
-        self.flat_param = alloc(self.total, self.dtype)
-        self.flat_grad = alloc(self.total, torch.float32)
+        self.flat_param = (param_alloc or alloc)(self.total, self.dtype)
+        self.flat_grad = alloc(self.total, torch.float32) if with_grad else torch.zeros(0, device=self.device)
         for n, p in params:
             o, k, shp = self.offsets[n]
             view = self.flat_param[o:o + k].view(shp)
             view.copy_(p.data)
             p.data = view
+            if not with_grad:
+                continue
             g = self.flat_grad[o:o + k].view(shp)
             p.main_grad = g
             if self.dtype == torch.float32:

@@ -232,7 +232,9 @@ class ShardedCheckpointManager:
                         "expert_parallel": bool(st is not None and getattr(st, "expert", None) is not None),
                         "contents": self.contents}
         hf_state = None
-        if self.rank == 0 and "hf_model" in self.contents and async_save:
+        if "hf_model" in self.contents and hasattr(st, "materialize_full"):
+            st.materialize_full()       # parameter-sharded store: the exporter needs whole weights (a collective)
+        if self.rank == 0 and "hf_model" in self.contents and (async_save or hasattr(st, "materialize_full")):
             # the exporter reads the live parameters: snapshot them now, the next optimizer step may run meanwhile
             from ...models.hf_io import to_hf_state
             hf_state = [(n, t.detach().to("cpu").clone()) for n, t in to_hf_state(self.model)]
@@ -263,6 +265,8 @@ class ShardedCheckpointManager:
                 for path in written:
                     fs.copy(path, hdfs_path.rstrip("/") + "/" + os.path.basename(path))
 
+        if "hf_model" in self.contents and hasattr(st, "release_full"):
+            st.release_full()
         return PendingSave(write, async_save)
 
     def load(self, directory: str) -> Optional[Dict[str, Any]]:
@@ -279,6 +283,8 @@ class ShardedCheckpointManager:
                            map_location="cpu", weights_only=False)
             ex.flat_param.copy_(e["flat"].to(ex.device))
             ex.load_shard_state_dict(e["state"])
+            if hasattr(st, "invalidate"):
+                st.invalidate()
         if st is not None:
             if saved_world == self.world and os.path.exists(mpath):
                 m = torch.load(mpath, map_location="cpu", weights_only=False)

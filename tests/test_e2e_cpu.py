@@ -68,6 +68,25 @@ def test_grpo_two_ranks_three_steps_and_resume(tmp_path):
     assert [r["step"] for r in _metrics(tmp_path / "log2")] == [4]
 
 
+def test_grpo_with_sharded_parameters(tmp_path):
+    """``fsdp_config.sharding=zero3``: actor and reference weights sharded over the two ranks, gathered layer by layer
+    for scoring and training and regathered whole for the rollout engine; save and resume included."""
+    ck = tmp_path / "c"
+    extra = ["actor_rollout_ref.actor.fsdp_config.sharding=zero3",
+             "actor_rollout_ref.model.enable_gradient_checkpointing=True", "data.max_response_length=16"]
+    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=2", "trainer.save_freq=2", *extra],
+               tmp_path / "log1")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log1")
+    assert [r["step"] for r in m] == [1, 2]
+    assert all(r["actor/grad_norm"] > 0 for r in m)
+    assert (ck / "global_step_2" / "actor_agent_0" / "experts_world_size_2_rank_1.pt").exists()
+    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=3", "trainer.resume_mode=auto",
+                *extra], tmp_path / "log2")
+    assert out.returncode == 0, out.stderr[-4000:]
+    assert [r["step"] for r in _metrics(tmp_path / "log2")] == [3]
+
+
 def test_injected_rank_failure_stops_the_job(tmp_path):
     out = _run([f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=2",
                 "fault.inject=[{rank: 1, step: 0, node: function_reward, kind: exit, code: 17}]"], tmp_path / "log",

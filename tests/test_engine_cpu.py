@@ -184,3 +184,17 @@ def test_kv_arena_in_borrowed_memory_gives_the_same_tokens():
     assert not torch.isnan(lent[:per_layer]).any() and float(lent[:per_layer].abs().sum()) > 0
     eng.sleep()
     assert eng.cache is None
+
+
+def test_parameter_sharded_store_matches_replicated_on_gloo_ranks():
+    """ZeRO-3 style store (``fsdp_config.sharding=zero3``) against the replicated one, two gloo ranks."""
+    import subprocess
+    import sys
+    from siirl_b200.execution.scheduler.launch import find_free_port
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, Z3_DEVICE="cpu", OMP_NUM_THREADS="2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(find_free_port()), os.path.join(here, "zero3_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "ZERO3_OK" in out.stdout

@@ -46,3 +46,15 @@ def test_expert_parallel_dispatch_combine():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "EP_OK" in out.stdout
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+def test_parameter_sharded_store_matches_replicated():
+    n = min(torch.cuda.device_count(), 4)
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, Z3_DEVICE="cuda", NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", _port(), os.path.join(here, "zero3_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "ZERO3_OK" in out.stdout
