@@ -262,11 +262,13 @@ class DAGWorker:
             elif node.node_role == NodeRole.REWARD and self.config.reward_model.enable:
                 key = f"reward_{ag}"
                 if key not in self.workers:
-                    w = RewardModelWorker(cfg or self.config.reward_model, group, self.device, self.comm, seed)
+                    w = RewardModelWorker(cfg or self.config.reward_model, group, self.device, self.comm, seed,
+                                          input_tokenizer=self.tokenizer)
                     w.init_model()
                     self.workers[key] = w
         if self.config.reward_model.enable and "reward_0" not in self.workers:
-            w = RewardModelWorker(self.config.reward_model, None, self.device, self.comm, seed)
+            w = RewardModelWorker(self.config.reward_model, None, self.device, self.comm, seed,
+                                  input_tokenizer=self.tokenizer)
             w.init_model()
             self.workers["reward_0"] = w
         for alias, target in self._shared_workers.items():

@@ -28,6 +28,18 @@ class AsyncActorRolloutRefWorker(ActorRolloutRefWorker):
     async def sleep(self) -> None:
         await self.server.sleep()
 
+    def start_http_server(self, host: str = "127.0.0.1", port: int = 0) -> str:
+        """Serve the engine over an OpenAI-compatible HTTP API (``/v1/chat/completions``, ``/v1/completions``,
+        ``/generate``); returns ``host:port``."""
+        from .rollout.http_server import OpenAIHttpServer
+        self.http = OpenAIHttpServer(self.server, host, port, model_name=str(self.config.model.path or "native"))
+        return self.http.start()
+
+    def start_zmq_server(self, address: str = "tcp://127.0.0.1:0") -> str:
+        from .rollout.http_server import ZmqRolloutServer
+        self.zmq = ZmqRolloutServer(self.server, address)
+        return self.zmq.address
+
     def generate_many(self, prompts: List[List[int]], sampling_params: Dict[str, Any]) -> List[Dict[str, Any]]:
         """Synchronous convenience for callers without an event loop."""
         async def run():

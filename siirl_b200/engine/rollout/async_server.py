@@ -65,7 +65,7 @@ class AsyncRolloutServer:
                                     eos_token_id=sp0.get("eos_token_id"), seed=int(sp0.get("seed", 0)) + self.num_batches)
                 prompts = [batch[i][0] for i in idxs]
                 try:
-                    outs = await asyncio.to_thread(self.engine.generate, prompts, sp)
+                    outs = await asyncio.to_thread(self._generate_on_engine_device, prompts, sp)
                     self.num_batches += 1
                     for i, o in zip(idxs, outs):
                         batch[i][2].set_result({"token_ids": o.token_ids, "logprobs": o.logprobs,
@@ -76,6 +76,14 @@ class AsyncRolloutServer:
                             batch[i][2].set_exception(e)
             await asyncio.sleep(0)
 
+    def _generate_on_engine_device(self, prompts, sp):
+        """Engine call from a worker thread: a new thread starts on CUDA device 0, the engine may live elsewhere."""
+        dev = getattr(self.engine, "device", None)
+        if dev is not None and getattr(dev, "type", "cpu") == "cuda":
+            import torch
+            torch.cuda.set_device(dev)
+        return self.engine.generate(prompts, sp)
+
     async def chat_completion(self, request: Dict[str, Any]) -> Dict[str, Any]:
         """OpenAI ``/v1/chat/completions``-shaped request and response (messages, max_tokens, temperature, top_p)."""
         assert self.tokenizer is not None, "chat_completion needs a tokenizer"
@@ -84,12 +92,16 @@ class AsyncRolloutServer:
         if isinstance(ids, dict):
             ids = ids["input_ids"]
         sp = {"temperature": request.get("temperature", 1.0), "top_p": request.get("top_p", 1.0),
+              "top_k": request.get("top_k", -1), "seed": request.get("seed", 0),
               "max_new_tokens": request.get("max_tokens", 256), "eos_token_id": getattr(self.tokenizer, "eos_token_id", None)}
         out = await self.generate(uuid.uuid4().hex, list(ids), sp)
         text = self.tokenizer.decode(out["token_ids"], skip_special_tokens=True)
+        choice = {"index": 0, "message": {"role": "assistant", "content": text}, "finish_reason": out["finish_reason"]}
+        if request.get("logprobs"):
+            choice["logprobs"] = {"content": [{"token": self.tokenizer.decode([t]), "logprob": lp}
+                                              for t, lp in zip(out["token_ids"], out["logprobs"])]}
         return {"id": "chatcmpl-" + uuid.uuid4().hex[:12], "object": "chat.completion", "created": int(time.time()),
                 "model": request.get("model", "native"),
-                "choices": [{"index": 0, "message": {"role": "assistant", "content": text},
-                             "finish_reason": out["finish_reason"]}],
+                "choices": [choice],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out["token_ids"]),
                           "total_tokens": len(ids) + len(out["token_ids"])}}

@@ -901,13 +901,68 @@ class CriticWorker(_ModelWorkerBase):
 
 class RewardModelWorker(_ModelWorkerBase):
     """Model-based reward: a decoder with a scalar head scores each response at its last valid token
-    (reference: siirl/engine/fsdp_workers.py:1819-2115)."""
+    (reference: siirl/engine/fsdp_workers.py:1819-2115).
 
-    def __init__(self, config, process_group=None, device=None, comm=None, seed: int = 1):
+    When the reward model was trained with another tokenizer / chat template than the policy
+    (``reward_model.model.input_tokenizer`` names the policy's tokenizer, ``reward_model.model.rm_tokenizer`` or the
+    model directory the reward model's), every sample is re-encoded first: the response is decoded with the policy's
+    tokenizer, appended to the raw chat as the assistant turn, rendered with the reward model's chat template and
+    tokenised with the reward model's tokenizer (reference: ``_switch_chat_template``, fsdp_workers.py:1997-2056, and
+    ``re_encode_by_rm_tokenizer``, siirl/engine/reward_model/megatron/reward_model.py:59-122)."""
+
+    def __init__(self, config, process_group=None, device=None, comm=None, seed: int = 1, input_tokenizer=None,
+                 rm_tokenizer=None):
         super().__init__(config, "reward", process_group, device, comm, seed)
+        self.input_tokenizer = input_tokenizer      # the policy's tokenizer (decodes responses)
+        self.rm_tokenizer = rm_tokenizer            # the reward model's own tokenizer (None: same as the policy's)
 
     def init_model(self) -> None:
         self._build(self.config.model, value_head=True, trainable=False, seed_offset=29)
+        m = self.config.model
+        if self.rm_tokenizer is None and (m.rm_tokenizer or (m.input_tokenizer and m.path and not m.arch_preset)):
+            from ..data_coordinator.dataloader.tokenizer import load_tokenizer
+            self.rm_tokenizer = load_tokenizer(m.rm_tokenizer or m.path, vocab_size=self.model_config.vocab_size)
+        if self.input_tokenizer is None and m.input_tokenizer:
+            from ..data_coordinator.dataloader.tokenizer import load_tokenizer
+            self.input_tokenizer = load_tokenizer(m.input_tokenizer, vocab_size=self.model_config.vocab_size)
+
+    @property
+    def switches_template(self) -> bool:
+        return self.rm_tokenizer is not None and self.input_tokenizer is not None \
+            and self.rm_tokenizer is not self.input_tokenizer
+
+    def switch_chat_template(self, data: Batch) -> Batch:
+        """Re-encode every (prompt chat, response) pair for the reward model: right-padded ``input_ids`` /
+        ``attention_mask`` of width ``reward_model.max_length`` (default: the policy batch's width), truncated on the
+        right."""
+        src, dst = self.input_tokenizer, self.rm_tokenizer
+        B, R = data["responses"].shape
+        width = int(self.config.max_length or data["attention_mask"].shape[-1])
+        raw = data.non_tensors.get("raw_prompt")
+        pad = getattr(dst, "pad_token_id", 0) or 0
+        ids = torch.full((B, width), pad, dtype=torch.int64)
+        mask = torch.zeros(B, width, dtype=torch.int64)
+        am = data["attention_mask"].cpu()
+        resp = data["responses"].cpu()
+        P = am.shape[-1] - R
+        eos = getattr(src, "eos_token", None)
+        for i in range(B):
+            n = int(am[i, -R:].sum())
+            text = src.decode(resp[i, :n].tolist())
+            if eos:
+                text = text.replace(eos, "")
+            if raw is not None:
+                chat = [dict(m) for m in (raw[i].tolist() if hasattr(raw[i], "tolist") else list(raw[i]))]
+            else:       # no structured chat kept: the decoded prompt is the user turn
+                chat = [{"role": "user", "content": src.decode(data["input_ids"][i, :P][am[i, :P].bool()].tolist())}]
+            chat.append({"role": "assistant", "content": text})
+            rendered = dst.apply_chat_template(chat, add_generation_prompt=False, tokenize=False)
+            enc = dst(rendered, add_special_tokens=False)["input_ids"]
+            enc = list(enc[0]) if enc and isinstance(enc[0], (list, tuple)) else list(enc)
+            enc = enc[:width]
+            ids[i, : len(enc)] = torch.tensor(enc, dtype=torch.int64)
+            mask[i, : len(enc)] = 1
+        return Batch({"input_ids": ids, "attention_mask": mask}, None, {})
 
     @torch.no_grad()
     def compute_rm_score(self, data: Batch) -> Batch:
@@ -916,17 +971,22 @@ class RewardModelWorker(_ModelWorkerBase):
         B, R = data["responses"].shape
         scores = torch.zeros(B, R, dtype=torch.float32, device=self.device)
         micro = c.micro_batch_size_per_gpu or c.micro_batch_size
-        for idx, mb in _micro_batches(data, micro, c.use_dynamic_bsz, c.forward_max_token_len_per_gpu, self.group):
+        rl_all = data["response_mask"].to(self.device).sum(-1).clamp(min=1) - 1
+        src = data
+        if self.switches_template:
+            src = self.switch_chat_template(data)
+        from ..ops.attention import SeqInfo
+        for idx, mb in _micro_batches(src, micro, c.use_dynamic_bsz, c.forward_max_token_len_per_gpu, self.group):
             am = mb["attention_mask"].to(self.device)
-            lens = am.sum(-1)
-            from ..ops.attention import SeqInfo
+            lens = am.sum(-1).clamp(min=1)
             info = SeqInfo(lens.tolist(), device=self.device)
-            ids = mb["input_ids"].to(self.device)[am.bool()]
+            keep = am.bool()
+            keep[:, 0] |= am.sum(-1) == 0           # an empty row still contributes one (padding) token
+            ids = mb["input_ids"].to(self.device)[keep]
             v = self.model.values(ids, info.positions, info)
             last = torch.tensor(info.cu_seqlens_cpu[1:], device=self.device) - 1
             seq_score = v.index_select(0, last)
-            rl = mb["response_mask"].to(self.device).sum(-1).clamp(min=1) - 1
             rows = torch.tensor(idx, device=self.device)
-            scores[rows, rl] = seq_score
+            scores[rows, rl_all[rows]] = seq_score
         data["rm_scores"] = scores
         return data

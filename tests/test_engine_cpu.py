@@ -198,3 +198,41 @@ def test_parameter_sharded_store_matches_replicated_on_gloo_ranks():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "ZERO3_OK" in out.stdout
+
+
+def test_reward_model_reencodes_with_its_own_tokenizer_and_template():
+    """A reward model with another chat template scores the re-rendered conversation and the score lands on the
+    response's last valid token of the policy batch."""
+    from siirl_b200.engine.workers import RewardModelWorker
+
+    class RmTok(SyntheticTokenizer):
+        def apply_chat_template(self, messages, add_generation_prompt=True, tokenize=False, **_):
+            text = "".join(f"[{m['role']}] {m['content']} ;" for m in messages)
+            return self.encode(text) if tokenize else text
+
+    cfg = parse_config(["reward_model.enable=True", "reward_model.model.arch_preset=tiny", "reward_model.max_length=64",
+                        "reward_model.model.random_init=True", "trainer.device=cpu"])
+    src, dst = SyntheticTokenizer(1024), RmTok(1024)
+    w = RewardModelWorker(cfg.reward_model, None, torch.device("cpu"), None, 1, input_tokenizer=src, rm_tokenizer=dst)
+    w.init_model()
+    P = 8
+    prompt = torch.tensor([[0, 0] + src.encode("1+2=?a")] * 3)
+    resp = torch.tensor([src.encode("3") + [2, 0, 0, 0, 0], src.encode("12") + [2, 0, 0, 0], src.encode("123456")])
+    rmask = torch.tensor([[1, 1, 0, 0, 0, 0], [1, 1, 1, 0, 0, 0], [1] * 6])
+    am = torch.cat([(prompt != 0).long(), rmask], 1)
+    b = Batch({"input_ids": torch.cat([prompt, resp], 1), "attention_mask": am, "responses": resp,
+               "response_mask": rmask}, None, {})
+    assert w.switches_template
+    rm_in = w.switch_chat_template(b)
+    texts = [dst.decode(rm_in["input_ids"][i][rm_in["attention_mask"][i].bool()].tolist()) for i in range(3)]
+    assert texts == ["[user] 1+2=?a ;[assistant] 3 ;", "[user] 1+2=?a ;[assistant] 12 ;",
+                     "[user] 1+2=?a ;[assistant] 123456 ;"]
+    scores = w.compute_rm_score(b)["rm_scores"]
+    nz = scores.nonzero().tolist()
+    assert nz == [[0, 1], [1, 2], [2, 5]]
+    assert len({round(float(scores[i, j]), 6) for i, j in nz}) == 3       # three different conversations
+    # same tokenizer on both sides: the policy's token ids are scored as they are
+    w2 = RewardModelWorker(cfg.reward_model, None, torch.device("cpu"), None, 1, input_tokenizer=src)
+    w2.init_model()
+    assert not w2.switches_template
+    assert w2.compute_rm_score(b)["rm_scores"].nonzero().tolist() == nz

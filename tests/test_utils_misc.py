@@ -2,6 +2,7 @@
 (a no-op without CUDA), wave-aware split-K factor."""
 import os
 
+import pytest
 import torch
 
 
@@ -35,9 +36,69 @@ def test_rollout_request_schema():
     r.add_observation_tokens([20, 21, 22])
     r.add_assistant_tokens([12, 13], [-0.3, -0.4])
     assert r.response_loss_mask == [1, 1, 0, 0, 0, 1, 1] and r.remaining == 0
-    r.finalize({"tool": 1.0}, "tool_calls")
+    assert r.input_ids == [1, 2, 3, 10, 11, 20, 21, 22, 12, 13] and r.position_ids == list(range(10))
+    with pytest.raises(ValueError):
+        r.finalize(None, {"tool": 1.0}, "tool_calls")      # a conversation cannot end in a tool call
+    r.finalize(None, {"tool": 1.0}, "length")
     assert r.state == AsyncRolloutRequestStateEnum.COMPLETED and len(r.response_ids) == 6
-    assert r.metrics["finish_reason"] == FinishReasonTypeEnum.TOOL_CALL.value and r.reward_scores == {"tool": 1.0}
+    assert r.metrics["finish_reason"] == FinishReasonTypeEnum.LENGTH.value and r.reward_scores == {"tool": 1.0}
+    assert r.response_position_ids == [3, 4, 5, 6, 7, 8]
+
+
+def test_rollout_request_message_state_machine():
+    """Messages join the conversation as token deltas; assistant tokens carry loss mask 1, everything else 0; the
+    incrementally built ids equal one full rendering (no tokenisation drift with this template)."""
+    from siirl_b200.data_coordinator.dataloader import SyntheticTokenizer
+    from siirl_b200.engine.rollout.schemas import AsyncRolloutRequest, AsyncRolloutRequestStateEnum as St
+    tok = SyntheticTokenizer(1024)
+    r = AsyncRolloutRequest.create("r1", [{"role": "user", "content": "2+3=?"}], tok, max_response_len=64,
+                                   max_model_len=256)
+    assert tok.decode(r.prompt_ids) == "user:2+3=?\n" and tok.decode(r.generation_prompt_ids) == "assistant:"
+    ids = r.get_generation_prompt_ids(tok)
+    assert tok.decode(ids) == "user:2+3=?\nassistant:" and r.state == St.RUNNING
+    assert r.get_generation_prompt_ids(tok) == ids                     # the header is appended once
+    gen = tok.encode("calc(2+3)\n")
+    r.add_assistant_message(tok, "calc(2+3)", tool_calls=[{"name": "calc"}], token_ids=gen, logprobs=[-0.5] * len(gen))
+    assert r.state == St.TOOL_CALLING
+    r.add_tool_response_messages(tok, ["5"])
+    r.get_generation_prompt_ids(tok)
+    r.add_assistant_message(tok, "5")                                  # re-tokenised from the text
+    r.add_user_message(tok, "thanks")
+    assert r.state == St.INTERACTING
+    r.get_generation_prompt_ids(tok)                                   # header with no answer: finalize takes it back
+    r.finalize(tok, {"acc": 1.0}, "stop")
+    text = tok.decode(r.input_ids)
+    assert text == "user:2+3=?\nassistant:calc(2+3)\ntool:5\nassistant:5\nuser:thanks\n"
+    assert "tokenization_diffs" not in r.metrics
+    masked = tok.decode([t for t, m in zip(r.input_ids, r.loss_mask) if m])
+    assert masked == "calc(2+3)\n5\n"
+    assert len(r.response_ids) == len(r.response_loss_mask) == len(r.response_logprobs) == len(r.response_position_ids)
+    assert r.prompt_ids + r.response_ids == r.input_ids
+    # a template that renders the history differently from the deltas is reported
+    class Drifting(SyntheticTokenizer):
+        def apply_chat_template(self, messages, add_generation_prompt=True, tokenize=False, **kw):
+            text = "".join(f"{m['role']}:{m['content']}\n" for m in messages)
+            if len(messages) > 3:
+                text = text.replace("assistant:", "assistant: ")        # only in long histories
+            if add_generation_prompt:
+                text += "assistant:"
+            return self.encode(text) if tokenize else text
+    d = Drifting(1024)
+    q = AsyncRolloutRequest.create("r2", [{"role": "user", "content": "a"}], d, tokenization_sanity_check_mode="strict")
+    for turn in ("b", "c"):
+        q.get_generation_prompt_ids(d)
+        q.add_assistant_message(d, turn)
+        q.add_user_message(d, "again")
+    q.finalize(d)
+    assert q.metrics.get("tokenization_diffs", 0) > 0
+    q2 = AsyncRolloutRequest.create("r3", [{"role": "user", "content": "a"}], d,
+                                    tokenization_sanity_check_mode="ignore_strippable")
+    for turn in ("b", "c"):
+        q2.get_generation_prompt_ids(d)
+        q2.add_assistant_message(d, turn)
+        q2.add_user_message(d, "again")
+    q2.finalize(d)
+    assert "tokenization_diffs" not in q2.metrics                      # the drift is whitespace only
 
 
 def test_code_scorer_stdin_and_function_modes():
