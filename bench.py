@@ -43,7 +43,7 @@ import threading
 METRIC = "grpo_tokens_per_second"
 BASELINE_TOKENS_PER_S_PER_GPU = 3473.837  # reference quick-start log (Qwen2.5-0.5B, 1 GPU, step 2)
 SHORT_RESPONSE = 128                       # response limit of the short warm-up steps
-AUTO_SHARDS_PARAMS = False                 # what --param-sharding auto means on two or more GPUs
+AUTO_SHARDS_PARAMS = True                  # what --param-sharding auto means on two or more GPUs (the named configuration)
 
 
 def parse_args():

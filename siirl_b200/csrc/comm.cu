@@ -300,7 +300,13 @@ extern "C" int sb_segment_pull(void* const* bases, int world, const void* segs, 
                                cudaStream_t stream) {
   if (world > kMaxRanks) return -3;
   if (n_segs == 0) return 0;
-  dim3 grid(16, n_segs < 2048 ? n_segs : 2048);
+  // enough CTAs to keep the NVLink loads of all SMs busy whether the table has two large segments (a parameter
+  // gather) or thousands of small ones (sample redistribution)
+  const int gy = n_segs < 2048 ? n_segs : 2048;
+  int gx = (num_sms() * 8 + gy - 1) / gy;
+  if (gx < 1) gx = 1;
+  if (gx > 1024) gx = 1024;
+  dim3 grid(gx, gy);
   segment_pull_kernel<<<grid, 256, 0, stream>>>(to_peers(bases, world), reinterpret_cast<const Segment*>(segs), n_segs,
                                                 reinterpret_cast<unsigned char*>(out));
   return (int)cudaGetLastError();

@@ -151,8 +151,18 @@ class PartitionedRLHFDataset(Dataset):
         ids = self._prompt_ids(row)
         mm_inputs = None
         images = row.get(self.cfg.image_key) if self.cfg.image_key in row else None
-        if images is not None and len(images) > 0 and self._full_config is not None:
-            out = self._vl_processor()(ids, list(images))
+        videos = row.get(self.cfg.video_key) if self.cfg.video_key in row else None
+        has_img = images is not None and len(images) > 0
+        has_vid = videos is not None and len(videos) > 0
+        if (has_img or has_vid) and self._full_config is not None:
+            frames = []
+            if has_vid:
+                from .vision_utils import process_video
+                m = self._full_config.actor_rollout_ref.model
+                frames = [v if isinstance(v, torch.Tensor) and v.dim() == 4 else
+                          process_video(v if isinstance(v, dict) else {"video": v}, max_pixels=m.image_max_pixels,
+                                        min_pixels=m.image_min_pixels) for v in videos]
+            out = self._vl_processor()(ids, list(images) if has_img else [], frames)
             ids = out["input_ids"]
             mm_inputs = {"pixel_values": out["pixel_values"], "image_grid_thw": out["image_grid_thw"]}
         input_ids, mask, pos = left_pad(ids, self.max_prompt_length, self.tokenizer.pad_token_id, self.cfg.truncation)

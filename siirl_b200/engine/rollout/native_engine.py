@@ -60,20 +60,36 @@ class _Seq:
     blocks: List[int] = field(default_factory=list)
     slot: int = -1
     generated: int = 0
+    prefilled: int = 0          # prompt tokens whose K/V are in the cache (first sample of a group)
 
 
 class BlockAllocator:
-    """Reference-counted free list of cache blocks (host side)."""
+    """Reference-counted free list of cache blocks (host side) with a prefix cache on top.
+
+    A full block of prompt tokens can be *registered* under the hash of the whole token prefix it ends.  When its last
+    user releases it, a registered block is not freed but parked in an LRU list: a later prompt that starts with the
+    same tokens takes it back (``lookup``) instead of prefilling them again; ``alloc`` evicts the least recently used
+    parked block when the free list is empty.  Cached blocks are valid for one set of weights: the engine drops the
+    allocator (and with it the cache) every time it goes to sleep."""
 
     def __init__(self, num_blocks: int):
+        from collections import OrderedDict
         self.num_blocks = num_blocks
         self.free: List[int] = list(range(num_blocks - 1, -1, -1))
         self.ref = [0] * num_blocks
+        self.by_hash: Dict[int, int] = {}          # prefix hash -> block
+        self.hash_of: Dict[int, int] = {}          # block -> prefix hash
+        self.parked = OrderedDict()                # zero-reference registered blocks, oldest first
+        self.hits = self.misses = 0
 
     def alloc(self) -> int:
-        if not self.free:
+        if self.free:
+            b = self.free.pop()
+        elif self.parked:
+            b, _ = self.parked.popitem(last=False)
+            del self.by_hash[self.hash_of.pop(b)]
+        else:
             raise MemoryError("KV cache exhausted")
-        b = self.free.pop()
         self.ref[b] = 1
         return b
 
@@ -84,17 +100,47 @@ class BlockAllocator:
     def release(self, b: int) -> None:
         self.ref[b] -= 1
         if self.ref[b] == 0:
-            self.free.append(b)
+            if b in self.hash_of:
+                self.parked[b] = None
+            else:
+                self.free.append(b)
+
+    def register(self, key: int, b: int) -> None:
+        if key not in self.by_hash and b not in self.hash_of:
+            self.by_hash[key] = b
+            self.hash_of[b] = key
+
+    def lookup(self, key: int) -> Optional[int]:
+        """Block cached under ``key`` with one more reference, or ``None``."""
+        b = self.by_hash.get(key)
+        if b is None:
+            self.misses += 1
+            return None
+        self.hits += 1
+        if self.ref[b] == 0:
+            self.parked.pop(b, None)
+        self.ref[b] += 1
+        return b
 
     @property
     def num_free(self) -> int:
-        return len(self.free)
+        return len(self.free) + len(self.parked)
+
+
+def _prefix_hashes(tokens: Sequence[int], n_blocks: int) -> List[int]:
+    """Hash of tokens[0 : (j + 1) * BLOCK] for j < n_blocks, chained so that each costs one block of hashing."""
+    out, h = [], 0
+    for j in range(n_blocks):
+        h = hash((h, tuple(tokens[j * BLOCK:(j + 1) * BLOCK])))
+        out.append(h)
+    return out
 
 
 class RolloutEngine:
     def __init__(self, model: DecoderLM, max_num_seqs: int = 256, max_model_len: int = 8192,
                  num_blocks: Optional[int] = None, gpu_memory_utilization: float = 0.5, sync_interval: int = 16,
-                 use_cuda_graph: bool = True, max_num_batched_tokens: int = 8192, lockstep_group=None):
+                 use_cuda_graph: bool = True, max_num_batched_tokens: int = 8192, lockstep_group=None,
+                 enable_chunked_prefill: bool = False, enable_prefix_caching: bool = True):
         """``lockstep_group``: ranks whose forward passes contain collectives over DIFFERENT requests (expert
         parallelism).  They then run the same sequence of prefill / decode calls: a rank without work joins with
         an empty prefill or an all-inactive decode step, and decode runs eagerly (the barriers of the expert
@@ -102,6 +148,13 @@ class RolloutEngine:
         self.lockstep_group = lockstep_group
         if lockstep_group is not None:
             use_cuda_graph = False
+            enable_chunked_prefill = enable_prefix_caching = False      # every rank must prefill the same shapes
+        # Chunked prefill: a prompt longer than ``max_num_batched_tokens`` enters the cache in several engine
+        # iterations (decode steps of the running sequences in between) instead of one oversized batch.  Prefix
+        # caching: full prompt blocks are kept under the hash of their token prefix and reused by later prompts of
+        # the same wake period (multi-turn conversations re-send their history; n-sample groups already share blocks).
+        self.enable_chunked_prefill = bool(enable_chunked_prefill)
+        self.enable_prefix_caching = bool(enable_prefix_caching)
         # Device memory the engine may use for KV blocks while it is awake (the trainer's fp32 gradient buffer, idle
         # and about to be zeroed between an optimizer step and the next backward): on a 180 GB part with the Adam
         # state resident this is what lets all sequences of a step decode in one wave.  Its contents are clobbered.
@@ -199,11 +252,15 @@ class RolloutEngine:
 
     # ---- prefill --------------------------------------------------------------------------------
     @torch.no_grad()
-    def _prefill(self, seqs: List[_Seq], prompts: List[List[int]], mm_inputs=None) -> torch.Tensor:
-        """Prefill one packed batch of distinct prompts (``seqs[i]`` is sample 0 of its prompt); returns the
-        final hidden state of the last token of each prompt ``[len(seqs), H]``.  ``mm_inputs[i]`` (optional) holds
-        prompt i's ``pixel_values [patches, D]``, ``image_grid_thw [images, 3]`` and ``rope_positions [3, len]``."""
-        lens = [len(p) for p in prompts]
+    def _prefill(self, seqs: List[_Seq], chunks: List[List[int]], starts: Optional[List[int]] = None,
+                 mm_inputs=None) -> torch.Tensor:
+        """Prefill one packed batch: ``chunks[i]`` are the next tokens of the prompt of ``seqs[i]`` (sample 0 of its
+        group), ``starts[i]`` how many of its tokens the cache holds already (a prefix-cache hit or earlier chunks;
+        default 0 = whole prompts).  Returns the final hidden state of the last token of each chunk
+        ``[len(seqs), H]``.  ``mm_inputs[i]`` (optional, whole prompts only) holds prompt i's ``pixel_values
+        [patches, D]``, ``image_grid_thw [images, 3]`` and ``rope_positions [3, len]``."""
+        lens = [len(p) for p in chunks]
+        starts = list(starts) if starts is not None else [0] * len(chunks)
         mm = {}
         if mm_inputs is not None and any(m for m in mm_inputs):
             pv = [m["pixel_values"] for m in mm_inputs if m and m.get("pixel_values") is not None]
@@ -216,10 +273,16 @@ class RolloutEngine:
                       else torch.arange(n).expand(3, n) for m, n in zip(mm_inputs, lens)]
                 mm["rope_positions"] = torch.cat(rp, 1).to(self.device)
         info = SeqInfo(lens, device=self.device)
-        ids = torch.tensor([t for p in prompts for t in p], dtype=torch.int64, device=self.device)
+        ids = torch.tensor([t for p in chunks for t in p], dtype=torch.int64, device=self.device)
         seq_ids = torch.repeat_interleave(torch.tensor([s.slot for s in seqs], dtype=torch.int32),
                                           torch.tensor(lens)).to(self.device)
-        hidden = self.model.forward_cached(ids, info.positions, self.cache, self.block_table, seq_ids,
+        positions = info.positions
+        if any(starts):
+            positions = torch.cat([torch.arange(st, st + n, dtype=torch.int32) for st, n in zip(starts, lens)]).to(
+                self.device)
+            mm["prefix_lens"] = starts
+            mm["prefill_slots"] = [s.slot for s in seqs]
+        hidden = self.model.forward_cached(ids, positions, self.cache, self.block_table, seq_ids,
                                            prefill_info=info, **mm)
         last = torch.tensor([c - 1 for c in info.cu_seqlens_cpu[1:]], dtype=torch.int64, device=self.device)
         self.stats["prefill_tokens"] += sum(lens)
@@ -373,19 +436,43 @@ class RolloutEngine:
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.lockstep_group)
             return [bool(v) for v in t.tolist()]
 
+        pending: List[List[_Seq]] = []      # admitted groups whose prompt is not completely in the cache yet
+        chunked = self.enable_chunked_prefill and mm_inputs is None
+        use_cache = self.enable_prefix_caching and mm_inputs is None
         while group_any(bool(waiting) or any(s is not None for s in slots))[0]:
-            # ---- admission: whole prompts (all n samples) while slots and blocks last ----
+            # ---- prefill work of this iteration: continue started prompts, then admit new ones (all n samples of a
+            # prompt at once) while slots, blocks and the token budget last ----
             free_slots = [i for i, s in enumerate(slots) if s is None]
-            batch_prompts, batch_seqs, forks, ntok = [], [], [], 0
-            while waiting:
+            budget = self.max_num_batched_tokens
+            jobs: List[tuple] = []          # (group, first token, end token) of the prompt range to prefill now
+            for group in pending:
+                lead = group[0]
+                take = min(budget, lead.prompt_len - lead.prefilled)
+                if take > 0:
+                    jobs.append((group, lead.prefilled, lead.prefilled + take))
+                    budget -= take
+            new_groups: List[List[_Seq]] = []
+            while waiting and budget > 0:
                 pi = waiting[-1]
                 p = list(prompts[pi])
                 if len(p) + R > self.max_model_len:
                     raise ValueError(f"prompt {pi}: {len(p)} + {R} tokens exceed max_model_len {self.max_model_len}")
                 full = len(p) // BLOCK
-                need = blocks_needed(len(p)) + (sp.n - 1) * (blocks_needed(len(p)) - full)
+                hit: List[int] = []
+                if use_cache and full:
+                    # leave at least one token to prefill: its hidden state samples the first response token
+                    keys = _prefix_hashes(p, full if len(p) % BLOCK else full - 1)
+                    for k in keys:
+                        b = self.alloc.lookup(k)
+                        if b is None:
+                            break
+                        hit.append(b)
+                need = blocks_needed(len(p)) - len(hit) + (sp.n - 1) * (blocks_needed(len(p)) - full)
+                todo = len(p) - len(hit) * BLOCK
                 if len(free_slots) < sp.n or self.alloc.num_free < need or (
-                        batch_prompts and ntok + len(p) > self.max_num_batched_tokens):
+                        not chunked and jobs and todo > budget):
+                    for b in hit:
+                        self.alloc.release(b)
                     break
                 waiting.pop()
                 group = []
@@ -394,41 +481,62 @@ class RolloutEngine:
                     slots[seq.slot] = seq
                     group.append(seq)
                 first = group[0]
-                first.blocks = [self.alloc.alloc() for _ in range(blocks_needed(len(p)))]
+                first.blocks = hit + [self.alloc.alloc() for _ in range(blocks_needed(len(p)) - len(hit))]
+                first.prefilled = len(hit) * BLOCK
+                self.stats["prefix_cache_hit_tokens"] = self.stats.get("prefix_cache_hit_tokens", 0) + first.prefilled
                 for other in group[1:]:
                     other.blocks = [self.alloc.share(b) for b in first.blocks[:full]]
                     for j in range(full, len(first.blocks)):
-                        nb = self.alloc.alloc()
-                        other.blocks.append(nb)
-                        if j == full and len(p) % BLOCK:
-                            forks.append((first.blocks[j], nb))
-                batch_prompts.append(p)
-                batch_seqs.append(group)
-                ntok += len(p)
-            if waiting and not batch_prompts and not any(s is not None for s in slots):
+                        other.blocks.append(self.alloc.alloc())
+                take = min(budget, todo) if chunked else todo
+                jobs.append((group, first.prefilled, first.prefilled + take))
+                budget -= take
+                new_groups.append(group)
+            pending += new_groups
+            if waiting and not jobs and not any(s is not None for s in slots):
                 raise MemoryError("a single request does not fit into the KV cache / slot budget")
-            any_prefill, = group_any(bool(batch_prompts))
-            if any_prefill and not batch_prompts:
+            any_prefill, = group_any(bool(jobs))
+            if any_prefill and not jobs:
                 # another rank of the lock-step group prefills: join its collectives with one unrouted token
                 one = SeqInfo([1], device=dev)
                 self.model.forward_cached(torch.zeros(1, dtype=torch.int64, device=dev), one.positions, self.cache,
                                           self.block_table, torch.full((1,), -1, dtype=torch.int32, device=dev),
                                           prefill_info=one)
-            if batch_prompts:
-                bt = self.block_table.cpu()
-                for group in batch_seqs:
-                    for seq in group:
-                        bt[seq.slot, : len(seq.blocks)] = torch.tensor(seq.blocks, dtype=torch.int32)
-                self.block_table.copy_(bt)
-                batch_mm = [mm_inputs[g[0].prompt_index] for g in batch_seqs] if mm_inputs is not None else None
-                hidden = self._prefill([g[0] for g in batch_seqs], batch_prompts, batch_mm)
+            if jobs:
+                if new_groups:
+                    bt = self.block_table.cpu()
+                    for group in new_groups:
+                        for seq in group:
+                            bt[seq.slot, : len(seq.blocks)] = torch.tensor(seq.blocks, dtype=torch.int32)
+                    self.block_table.copy_(bt)
+                batch_mm = [mm_inputs[g[0].prompt_index] for g, _, _ in jobs] if mm_inputs is not None else None
+                hidden = self._prefill([g[0] for g, _, _ in jobs],
+                                       [list(prompts[g[0].prompt_index])[a:b] for g, a, b in jobs],
+                                       [a for _, a, _ in jobs], batch_mm)
+                done_rows, batch_seqs, forks = [], [], []
+                for row, (group, _a, b) in enumerate(jobs):
+                    lead = group[0]
+                    lead.prefilled = b
+                    if b < lead.prompt_len:
+                        continue
+                    done_rows.append(row)
+                    batch_seqs.append(group)
+                    plen = lead.prompt_len
+                    full = plen // BLOCK
+                    if plen % BLOCK:
+                        forks += [(lead.blocks[full], other.blocks[full]) for other in group[1:]]
+                    if use_cache:
+                        for j, k in enumerate(_prefix_hashes(list(prompts[lead.prompt_index]), full)):
+                            self.alloc.register(k, lead.blocks[j])
+                pending = [g for g in pending if g[0].prefilled < g[0].prompt_len]
                 if forks:
                     src = torch.tensor([a for a, _ in forks], dtype=torch.int32, device=dev)
                     dst = torch.tensor([b for _, b in forks], dtype=torch.int32, device=dev)
                     for li in range(self.cfg.num_layers):
                         kvc.kv_copy_blocks(self.cache[li], src, dst)
+            if jobs and batch_seqs:
                 # first token of every sample comes from the prompt's last hidden state
-                rep_idx = torch.tensor([i for i, g in enumerate(batch_seqs) for _ in g], device=dev)
+                rep_idx = torch.tensor([done_rows[i] for i, g in enumerate(batch_seqs) for _ in g], device=dev)
                 logits = lm_head_logits(hidden.index_select(0, rep_idx), self.model.head_weight)
                 tok, lp = sample(logits, sp.temperature, sp.top_k, sp.top_p, seed=sp.seed ^ 0x5bd1e995,
                                  step=int(self.step_counter.item()))
@@ -461,8 +569,9 @@ class RolloutEngine:
             gen_cpu = self.gen_index.cpu().tolist()
             eos_cpu = self.hit_eos.cpu().tolist()
             self.stats["d2h_bytes"] = self.stats.get("d2h_bytes", 0) + 6 * S
+            prefilling = {s.slot for g in pending for s in g}
             for slot, seq in enumerate(slots):
-                if seq is not None and fin_cpu[slot]:
+                if seq is not None and fin_cpu[slot] and slot not in prefilling:
                     retire(slot, "stop" if eos_cpu[slot] else "length", gen_cpu[slot])
                     self.ctx_len[slot] = 0
                     self.gen_index[slot] = 0

@@ -479,6 +479,9 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
             self._attach_pipeline_parallel(self.ref_model, False)
             self._attach_sequence_parallel(self.ref_model)
             self._attach_context_parallel(self.ref_model)
+            if self.config.ref.fsdp_config.param_offload and self.device.type == "cuda" and self.ref_store is None:
+                from ..utils.model_utils.fsdp_utils import offload_model_to_cpu
+                offload_model_to_cpu(self.ref_model)
             if self.model is None:
                 self.model_config = mcfg
         if self._is_rollout:
@@ -499,6 +502,8 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                                         gpu_memory_utilization=r.gpu_memory_utilization,
                                         use_cuda_graph=not r.enforce_eager or self.device.type == "cuda",
                                         max_num_batched_tokens=r.max_num_batched_tokens,
+                                        enable_chunked_prefill=bool(r.enable_chunked_prefill),
+                                        enable_prefix_caching=bool(getattr(r, "enable_prefix_caching", True)),
                                         lockstep_group=self.group if getattr(self, "ep_ctx", None) is not None
                                         and self.world > 1 else None,
                                         **dict(r.engine_kwargs.native or {}))
@@ -711,14 +716,22 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         self._phase_sync()
         model = self.ref_model if self.ref_model is not None else self.model
         lora_ref = self.ref_model is None and getattr(self.model_config, "lora_rank", 0) > 0
+        offload = (self.ref_model is not None and rf.fsdp_config.param_offload and self.device.type == "cuda"
+                   and getattr(self, "ref_store", None) is None)
         if lora_ref:
             model.set_lora_enabled(False)
+        if offload:         # the frozen policy lives in pinned host memory between its scoring passes
+            from ..utils.model_utils.fsdp_utils import load_model_to_gpu
+            load_model_to_gpu(model)
         try:
             lp, _ = self._logprob_pass(model, data, self.ref_logprob_micro, rf.log_prob_use_dynamic_bsz,
                                        rf.log_prob_max_token_len_per_gpu, with_entropy=False)
         finally:
             if lora_ref:
                 model.set_lora_enabled(True)
+            if offload:
+                from ..utils.model_utils.fsdp_utils import offload_model_to_cpu
+                offload_model_to_cpu(model)
         data["ref_log_prob"] = lp
         return data
 

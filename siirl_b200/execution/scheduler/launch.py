@@ -26,6 +26,44 @@ def use_critic(config) -> bool:
     return config.algorithm.adv_estimator in ("gae", "gae_marft")
 
 
+_WARNED: set = set()
+
+
+def _warn_once(key: str, message: str) -> None:
+    if key not in _WARNED and os.environ.get("RANK", "0") == "0":
+        _WARNED.add(key)
+        print(f"[siirl_b200] WARNING: {key}: {message}", file=sys.stderr)
+
+
+def _warn_unsupported_keys(config) -> None:
+    """Keys of the reference's configuration that parse but act differently here: say so once instead of silently
+    doing something else."""
+    arr = config.actor_rollout_ref
+    for name, fc in (("actor_rollout_ref.actor", arr.actor.fsdp_config), ("critic", config.critic.fsdp_config)):
+        if fc.param_offload:
+            _warn_once(f"{name}.fsdp_config.param_offload", "trainable weights stay on the GPU (the rollout engine "
+                       "reads them in place); use fsdp_config.sharding=zero3 to cut their footprint, "
+                       "optimizer_offload for the Adam state, ref.fsdp_config.param_offload for the frozen policy")
+        if int(fc.fsdp_size) not in (-1, 0, 1) and int(fc.fsdp_size) != config.trainer.n_gpus_per_node * \
+                config.trainer.nnodes:
+            _warn_once(f"{name}.fsdp_config.fsdp_size", "hybrid sharding (shard inside groups of fsdp_size ranks, "
+                       "replicate across them) is not implemented: state is sharded over the whole worker group")
+    m = arr.model
+    if getattr(m, "use_remove_padding", False) is False and "use_remove_padding" in getattr(config, "_explicit", ()):
+        _warn_once("actor_rollout_ref.model.use_remove_padding", "sequences are always packed without padding")
+    if getattr(m, "use_fused_kernels", False) is False and "use_fused_kernels" in getattr(config, "_explicit", ()):
+        _warn_once("actor_rollout_ref.model.use_fused_kernels", "the fused LM-head log-prob / entropy kernel is "
+                   "always used on GPUs")
+    if arr.actor.strategy == "megatron" or config.critic.strategy == "megatron":
+        mg = arr.actor.megatron
+        if int(mg.tensor_model_parallel_size or 1) > 1 and not getattr(mg, "_native_tp", True):
+            _warn_once("actor.megatron.tensor_model_parallel_size", "training tensor parallelism is mapped to the "
+                       "native column/row-parallel layers")
+        if mg.virtual_pipeline_model_parallel_size:
+            _warn_once("actor.megatron.virtual_pipeline_model_parallel_size", "interleaved pipeline stages are not "
+                       "implemented: every rank holds one contiguous stage")
+
+
 def validate_config(config, world_size: Optional[int] = None) -> None:
     t = config.trainer
     world = world_size or t.nnodes * t.n_gpus_per_node
@@ -65,6 +103,7 @@ def validate_config(config, world_size: Optional[int] = None) -> None:
             check_mutually_exclusive(c.ppo_micro_batch_size, c.ppo_micro_batch_size_per_gpu, "critic")
         if c.loss_agg_mode not in _LOSS_AGG_MODES:
             raise ValueError(f"Invalid critic loss_agg_mode: {c.loss_agg_mode}")
+    _warn_unsupported_keys(config)
     if config.algorithm.use_kl_in_reward and a.use_kl_loss:
         print("NOTICE: both in-reward KL and KL loss are enabled.", file=sys.stderr)
     if r.multi_turn.enable and r.name not in ("sglang", "native", "vllm"):

@@ -102,7 +102,8 @@ class TPDecoder:
     def forward_cached(self, input_ids: torch.Tensor, positions: torch.Tensor, cache: torch.Tensor,
                        block_table: torch.Tensor, seq_ids: torch.Tensor, *, prefill_info: Optional[SeqInfo] = None,
                        seq_lens: Optional[torch.Tensor] = None, pixel_values=None, image_grid_thw=None,
-                       rope_positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       rope_positions: Optional[torch.Tensor] = None, prefix_lens=None,
+                       prefill_slots=None) -> torch.Tensor:
         """Same contract as ``DecoderLM.forward_cached``; ``cache`` holds this rank's KV heads only."""
         from ..ops import kv_cache as kvc
         cfg, tp = self.cfg, self.tp
@@ -120,7 +121,11 @@ class TPDecoder:
             qkv = kvc.rope_kv_append(self._qkv_pre_rope(layer, t, x), rp32, rope[0], rope[1], cfg.mrope_section,
                                      seq_ids, pos32, block_table, cache[li], cfg.num_heads, cfg.num_kv_heads,
                                      cfg.head_dim)
-            if prefill_info is not None:
+            if prefill_info is not None and prefix_lens is not None and any(int(p) > 0 for p in prefix_lens):
+                # chunked prefill / prefix-cache hit: the chunk attends to the tokens already in the cache as well
+                a = kvc.prefill_attention_with_prefix(qkv, prefill_info.seqlens, prefix_lens, prefill_slots, cache[li],
+                                                      block_table, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim)
+            elif prefill_info is not None:
                 a = attention_packed(qkv, prefill_info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=True)
             else:
                 a = kvc.decode_attention(qkv, cache[li], seq_lens, block_table, cfg.num_heads, cfg.num_kv_heads,

@@ -75,11 +75,40 @@ class VLProcessor:
         x = x.unsqueeze(5).expand(-1, -1, -1, -1, -1, self.tpatch, -1, -1)
         return x.reshape(gh * gw, 3 * self.tpatch * P * P).contiguous(), torch.tensor([[1, gh, gw]])
 
-    def __call__(self, prompt_ids: Sequence[int], images: Sequence[Any]) -> Dict[str, Any]:
-        """Expands each single placeholder ``image_token_id`` of ``prompt_ids`` to the image's token count."""
+    def process_video(self, frames: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``frames [F, 3, H, W]`` in [0, 1] (sides already multiples of patch * merge, e.g. from
+        ``dataloader.vision_utils.process_video``) -> (patches ``[t*gh*gw, 3*T*P*P]``, grid ``[1, 3]`` = (t, gh, gw))
+        with ``t = F / temporal_patch_size`` (the last frame is repeated to fill the last temporal patch)."""
+        x = frames.float()
+        Fn, _, H, W = x.shape
+        unit = self.patch * self.merge
+        if H % unit or W % unit:
+            h2, w2 = smart_resize(H, W, unit, self.min_pixels, self.max_pixels)
+            x = F.interpolate(x, size=(h2, w2), mode="bilinear", align_corners=False, antialias=True)
+            H, W = h2, w2
+        if Fn % self.tpatch:
+            x = torch.cat([x, x[-1:].expand(self.tpatch - Fn % self.tpatch, -1, -1, -1)])
+        t = x.shape[0] // self.tpatch
+        mean = torch.tensor(_MEAN).view(1, 3, 1, 1)
+        std = torch.tensor(_STD).view(1, 3, 1, 1)
+        x = (x.clamp(0, 1) - mean) / std
+        P, m = self.patch, self.merge
+        gh, gw = H // P, W // P
+        # [t, T, C, gh/m, m, P, gw/m, m, P] -> (t, gh/m, gw/m, m, m, C, T, P, P)
+        x = x.reshape(t, self.tpatch, 3, gh // m, m, P, gw // m, m, P).permute(0, 3, 6, 4, 7, 2, 1, 5, 8)
+        return x.reshape(t * gh * gw, 3 * self.tpatch * P * P).contiguous(), torch.tensor([[t, gh, gw]])
+
+    def __call__(self, prompt_ids: Sequence[int], images: Sequence[Any], videos: Sequence[Any] = ()) -> Dict[str, Any]:
+        """Expands each single placeholder ``image_token_id`` of ``prompt_ids`` to the token count of the next visual
+        input.  Videos (frame tensors ``[F, 3, H, W]``) follow the images and use the same placeholder and the same
+        vision tower, with a temporal grid dimension > 1."""
         pv, grids = [], []
         for im in images:
             p, g = self.process_image(im)
+            pv.append(p)
+            grids.append(g)
+        for vid in videos:
+            p, g = self.process_video(vid)
             pv.append(p)
             grids.append(g)
         grid = torch.cat(grids) if grids else torch.zeros(0, 3, dtype=torch.int64)

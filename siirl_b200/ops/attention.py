@@ -46,9 +46,20 @@ class SeqInfo:
             self._pos = pos.to(self.device) if self.device is not None else pos
         return self._pos
 
-    def tiles(self):
+    def tiles(self, q_start: Optional[Sequence[int]] = None):
         """(seq_start, seq_len, offset) int32 device tensors, one entry per 128-row tile; longest
-        sequences' last tiles first so the heaviest causal tiles start early."""
+        sequences' last tiles first so the heaviest causal tiles start early.  ``q_start[i]`` (a multiple of 128)
+        leaves out the query tiles of sequence i below that row: chunked prefill computes only the new rows."""
+        if q_start is not None:
+            start, length, off = [], [], []
+            for i, n in enumerate(self.seqlens):
+                for t0 in range(int(q_start[i]) // 128 * 128, n, 128):
+                    start.append(self.cu_seqlens_cpu[i])
+                    length.append(n)
+                    off.append(t0)
+            order = sorted(range(len(off)), key=lambda k: -off[k])
+            mk = lambda xs: torch.tensor([xs[k] for k in order], dtype=torch.int32, device=self.device)  # noqa: E731
+            return (mk(start), mk(length), mk(off), len(off))
         if self._tiles is None:
             start, length, off = [], [], []
             for i, n in enumerate(self.seqlens):
@@ -64,12 +75,12 @@ class SeqInfo:
 
 class _AttnFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, qkv, info: SeqInfo, hq, hkv, d, causal, scale):
+    def forward(ctx, qkv, info: SeqInfo, hq, hkv, d, causal, scale, q_start=None):
         L = _lib.get_lib()
         T = qkv.shape[0]
         out = torch.empty(T, hq * d, dtype=qkv.dtype, device=qkv.device)
         lse = torch.empty(hq, T, dtype=torch.float32, device=qkv.device)
-        ts, tl, t0, n = info.tiles()
+        ts, tl, t0, n = info.tiles(q_start)
         rc = L.sb_fmha_fwd(_lib.ptr(qkv), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(ts), _lib.ptr(tl), _lib.ptr(t0), n, T,
                            hq, hkv, d, int(causal), ctypes.c_float(scale), _lib.ptr(_lib.status_word(qkv.device)),
                            _lib.stream())
@@ -94,7 +105,7 @@ class _AttnFn(torch.autograd.Function):
                            d, int(causal), ctypes.c_float(scale), _lib.ptr(_lib.status_word(qkv.device)),
                            _lib.stream())
         _lib.check(rc, "sb_fmha_bwd")
-        return dqkv, None, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None, None
 
 
 def _pad_heads(qkv: torch.Tensor, n_heads_total: int, d: int, d_pad: int) -> torch.Tensor:
@@ -104,8 +115,10 @@ def _pad_heads(qkv: torch.Tensor, n_heads_total: int, d: int, d_pad: int) -> tor
 
 
 def attention_packed(qkv: torch.Tensor, info: SeqInfo, n_heads: int, n_kv_heads: int, head_dim: int,
-                     causal: bool = True, scale: Optional[float] = None) -> torch.Tensor:
-    """Attention over a packed batch; returns ``[T, n_heads * head_dim]``."""
+                     causal: bool = True, scale: Optional[float] = None,
+                     q_start: Optional[Sequence[int]] = None) -> torch.Tensor:
+    """Attention over a packed batch; returns ``[T, n_heads * head_dim]``.  ``q_start`` (inference only): rows of
+    sequence i below ``q_start[i] // 128 * 128`` are not computed (their output rows are undefined)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     T = qkv.shape[0]
     if not qkv.is_cuda:
@@ -115,10 +128,12 @@ def attention_packed(qkv: torch.Tensor, info: SeqInfo, n_heads: int, n_kv_heads:
                                    causal=causal, scale=scale)
         return out.reshape(T, n_heads * head_dim)
     _lib.use_native(qkv)
+    if q_start is not None:
+        assert not (torch.is_grad_enabled() and qkv.requires_grad), "q_start is an inference-only option"
     if head_dim in (64, 128):
-        return _AttnFn.apply(qkv.contiguous(), info, n_heads, n_kv_heads, head_dim, causal, scale)
+        return _AttnFn.apply(qkv.contiguous(), info, n_heads, n_kv_heads, head_dim, causal, scale, q_start)
     d_pad = 64 if head_dim < 64 else 128
     assert head_dim <= 128, "head_dim > 128 is not supported"
     padded = _pad_heads(qkv, n_heads + 2 * n_kv_heads, head_dim, d_pad)
-    out = _AttnFn.apply(padded, info, n_heads, n_kv_heads, d_pad, causal, scale)
+    out = _AttnFn.apply(padded, info, n_heads, n_kv_heads, d_pad, causal, scale, q_start)
     return out.reshape(T, n_heads, d_pad)[..., :head_dim].reshape(T, n_heads * head_dim)

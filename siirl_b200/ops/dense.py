@@ -72,6 +72,9 @@ class _LinearFn(torch.autograd.Function):
         ctx.save_for_backward(x, weight)
         ctx.has_bias = bias is not None
         ctx.bias_ref = bias
+        # the parameter object itself: under activation checkpointing the saved tensor comes back as a detached
+        # alias without the ``main_grad`` attribute
+        ctx.weight_ref = weight
         x2 = x.reshape(-1, x.shape[-1])
         y = gemm(x2, weight, bias=bias)
         return y.reshape(*x.shape[:-1], weight.shape[0])
@@ -88,7 +91,7 @@ class _LinearFn(torch.autograd.Function):
             dx = gemm(dy2, weight, b_mn=True).reshape(x.shape)
         dw = None
         if ctx.needs_input_grad[1]:
-            mg = getattr(weight, "main_grad", None)
+            mg = getattr(ctx.weight_ref, "main_grad", None)
             if mg is not None:
                 gemm(dy2, x2, out=mg, a_mn=True, b_mn=True, epi=EPI_F32_ACC)
             else:
@@ -225,6 +228,7 @@ class _RMSNormFn(torch.autograd.Function):
                               ctypes.c_float(eps), _lib.stream())
         _lib.check(rc, "sb_rmsnorm_fwd")
         ctx.save_for_backward(h, weight, rstd)
+        ctx.weight_ref = weight
         ctx.has_res = residual is not None
         if residual is None:
             ctx.mark_non_differentiable(h_ret)
@@ -239,7 +243,7 @@ class _RMSNormFn(torch.autograd.Function):
         dx = torch.empty_like(h)
         nblk = L.sb_rmsnorm_bwd_blocks(T)
         partial = torch.empty(nblk, H, dtype=torch.float32, device=h.device)
-        mg = getattr(weight, "main_grad", None)
+        mg = getattr(ctx.weight_ref, "main_grad", None)
         dw_buf = mg if mg is not None else torch.empty(H, dtype=torch.float32, device=h.device)
         dres = dh.contiguous() if (ctx.has_res and dh is not None) else None
         rc = L.sb_rmsnorm_bwd(_lib.ptr(dy), _lib.ptr(h), _lib.ptr(weight), _lib.ptr(rstd), _lib.ptr(dres),

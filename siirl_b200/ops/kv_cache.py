@@ -107,3 +107,34 @@ def decode_attention(q_rows: torch.Tensor, cache_layer: torch.Tensor, seq_lens: 
         p = torch.softmax(s, -1)
         out[b] = torch.einsum("hn,hnd->hd", p, v).reshape(-1).to(out.dtype)
     return out
+
+
+def prefill_attention_with_prefix(qkv: torch.Tensor, chunk_lens, prefix_lens, slots, cache_layer: torch.Tensor,
+                                  block_table: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int) -> torch.Tensor:
+    """Causal attention of freshly projected chunk rows against (cached prefix + chunk) -- chunked prefill and prompts
+    whose first blocks were found in the prefix cache.  ``qkv [sum(chunk_lens), (Hq+2Hkv)*D]`` holds the chunk rows
+    (their K/V must already be in the cache, appended by ``rope_kv_append``); sequence ``i`` sits in cache slot
+    ``slots[i]`` with ``prefix_lens[i]`` earlier tokens.  K/V of all ``prefix + chunk`` positions are read back from
+    the paged cache into one packed buffer, the packed-attention kernel computes only the query tiles that contain
+    chunk rows, and the chunk rows of the result are returned ``[sum(chunk_lens), Hq*D]``."""
+    from .attention import SeqInfo, attention_packed
+    dev = qkv.device
+    qw, kw = n_heads * head_dim, n_kv_heads * head_dim
+    totals = [int(p) + int(c) for p, c in zip(prefix_lens, chunk_lens)]
+    full = torch.zeros(sum(totals), qw + 2 * kw, dtype=qkv.dtype, device=dev)
+    row, crow, keep = 0, 0, []
+    for p_, c_, t_, slot in zip(prefix_lens, chunk_lens, totals, slots):
+        nb = (t_ + BLOCK - 1) // BLOCK
+        blks = block_table[int(slot), :nb].long()
+        kv = cache_layer.index_select(0, blks)                      # [nb, 2, Hkv, 64, D]
+        k = kv[:, 0].permute(0, 2, 1, 3).reshape(nb * BLOCK, kw)[:t_]
+        v = kv[:, 1].permute(0, 2, 1, 3).reshape(nb * BLOCK, kw)[:t_]
+        full[row:row + t_, qw:qw + kw] = k
+        full[row:row + t_, qw + kw:] = v
+        full[row + int(p_):row + t_, :qw] = qkv[crow:crow + int(c_), :qw]
+        keep.append(torch.arange(row + int(p_), row + t_, device=dev))
+        row += t_
+        crow += int(c_)
+    out = attention_packed(full, SeqInfo(totals, device=dev), n_heads, n_kv_heads, head_dim, causal=True,
+                           q_start=[int(p) for p in prefix_lens])
+    return out.index_select(0, torch.cat(keep))

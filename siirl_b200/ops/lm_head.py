@@ -71,6 +71,7 @@ class _LmHeadFn(torch.autograd.Function):
                                          _lib.ptr(logp[s:e]), _lib.ptr(ent[s:e] if ent is not None else None),
                                          _lib.ptr(lse[s:e]), e - s, V, _lib.stream()), "sb_lmhead_stats")
         ctx.save_for_backward(hidden, weight, labels, lse, ent if ent is not None else lse)
+        ctx.weight_ref = weight
         ctx.meta = (inv_t, with_entropy, rows)
         if ent is None:
             ent = torch.zeros(0, device=hidden.device)
@@ -87,7 +88,7 @@ class _LmHeadFn(torch.autograd.Function):
         g_logp = g_logp.float().contiguous()
         g_ent = g_ent.float().contiguous() if (with_entropy and g_ent is not None and g_ent.numel() == T) else None
         dh = torch.empty_like(hidden) if ctx.needs_input_grad[0] else None
-        mg = getattr(weight, "main_grad", None)
+        mg = getattr(ctx.weight_ref, "main_grad", None)
         need_dw = ctx.needs_input_grad[1]
         dw_acc = mg if mg is not None else (torch.zeros(V, H, dtype=torch.float32, device=hidden.device)
                                             if need_dw else None)

@@ -277,12 +277,12 @@ class ShardedParamStore:
         slot, other = unit % 2, (unit + 1) % 2
         mine = self.grad_shard[unit * self.piece:(unit + 1) * self.piece]
         lo = self.rank * self.piece
-        if self.dtype == torch.float32:
-            # plain autograd may have replaced p.grad by a fresh tensor: fold it into the slot
-            for _, p in self.unit_params[unit]:
-                if p.grad is not None and p.grad.data_ptr() != p.main_grad.data_ptr():
-                    p.main_grad.add_(p.grad)
-                    p.grad = p.main_grad
+        # gradients that arrived through plain autograd (CPU ops; a backward that did not find ``main_grad``) instead
+        # of being accumulated by the kernels: fold them into the slot
+        for _, p in self.unit_params[unit]:
+            if p.grad is not None and p.grad.data_ptr() != p.main_grad.data_ptr():
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                p.grad = p.main_grad if self.dtype == torch.float32 else None
         self._barrier()                                    # all ranks wrote this unit and finished reading the other slot
         if self._grad_dirty[other]:
             self.grad_slots[other].zero_()

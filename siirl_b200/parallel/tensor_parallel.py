@@ -100,7 +100,7 @@ class TPContext:
             if bias is not None:
                 y = y + bias.float()
             return y.to(x.dtype)
-        from ..ops.dense import _skinny_splits, linear
+        from ..ops.dense import _best_splits, linear
         M, K = x.shape
         N = w_shard.shape[0]
         one_shot = M <= self.one_shot_rows
@@ -112,7 +112,8 @@ class TPContext:
         x = x.contiguous()
         tile_n = 128
         tiles_mn = (M + 127) // 128 * ((N + tile_n - 1) // tile_n)
-        splits = min(_skinny_splits(M, N, K), max(1, 148 // tiles_mn)) if M <= 128 else 1
+        # split-K only while every (tile, slice) item gets its own CTA: a tile's finisher waits for peers in the kernel
+        splits = min(_best_splits(tiles_mn, (K + 63) // 64), max(1, 148 // tiles_mn))
         L = _lib.get_lib()
         ll = ctypes.c_longlong
         if splits > 1:

@@ -285,6 +285,7 @@ class RolloutArguments:
     log_prob_use_dynamic_bsz: bool = False
     disable_log_stats: bool = True
     enable_chunked_prefill: bool = True
+    enable_prefix_caching: bool = True      # reuse cached full prompt blocks across requests of one rollout phase
     trust_remote_code: bool = True
     val_kwargs: EvalSamplingArguments = _dc(EvalSamplingArguments)
     layer_name_map: LayerNameMapArguments = _dc(LayerNameMapArguments)

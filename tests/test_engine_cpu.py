@@ -236,3 +236,36 @@ def test_reward_model_reencodes_with_its_own_tokenizer_and_template():
     w2.init_model()
     assert not w2.switches_template
     assert w2.compute_rm_score(b)["rm_scores"].nonzero().tolist() == nz
+
+
+def test_chunked_prefill_and_prefix_cache_give_the_same_tokens(tiny):
+    """Prompts longer than the token budget enter the cache in chunks, and a second round of requests that repeat the
+    first round's prompts (a multi-turn conversation re-sending its history) reuses the cached prompt blocks; greedy
+    tokens equal the plain engine's in every mode."""
+    cfg = get_config("tiny")
+    m = build_model(cfg, dtype=torch.float32, device="cpu", seed=1)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 1000, (n,), generator=g).tolist() for n in (300, 70, 200, 129)]
+    ext = [p + [7, 8, 9] for p in prompts]
+    sp = SamplingParams(n=2, temperature=0.0, max_new_tokens=6, ignore_eos=True)
+    plain = RolloutEngine(m, max_num_seqs=8, max_model_len=512, num_blocks=64, enable_prefix_caching=False)
+    want, want2 = ([o.token_ids for o in plain.generate(ps, sp)] for ps in (prompts, ext))
+    chunked = RolloutEngine(m, max_num_seqs=8, max_model_len=512, num_blocks=64, max_num_batched_tokens=100,
+                            enable_chunked_prefill=True, enable_prefix_caching=False)
+    assert [o.token_ids for o in chunked.generate(prompts, sp)] == want
+    assert chunked.stats["prefill_tokens"] == sum(len(p) for p in prompts)
+    cached = RolloutEngine(m, max_num_seqs=8, max_model_len=512, num_blocks=64)
+    assert [o.token_ids for o in cached.generate(prompts, sp)] == want
+    assert [o.token_ids for o in cached.generate(ext, sp)] == want2
+    assert cached.stats["prefix_cache_hit_tokens"] == 256 + 64 + 192 + 128       # every full prompt block was reused
+    both = RolloutEngine(m, max_num_seqs=8, max_model_len=512, num_blocks=64, max_num_batched_tokens=64,
+                         enable_chunked_prefill=True)
+    assert [o.token_ids for o in both.generate(prompts, sp)] == want
+    assert [o.token_ids for o in both.generate(ext, sp)] == want2
+    # parked blocks are evicted when the free list runs dry: a small arena still serves new prompts
+    small = RolloutEngine(m, max_num_seqs=4, max_model_len=512, num_blocks=14)
+    for round_ in range(3):
+        ps = [torch.randint(3, 1000, (150,), generator=g).tolist() for _ in range(2)]
+        outs = small.generate(ps, SamplingParams(n=1, temperature=0.0, max_new_tokens=4, ignore_eos=True))
+        assert len(outs) == 2 and all(len(o.token_ids) == 4 for o in outs)
+    assert small.alloc.num_free == 14

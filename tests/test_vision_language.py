@@ -5,6 +5,7 @@ import os
 import subprocess
 import sys
 
+import pytest
 import torch
 
 from siirl_b200.models.config import get_config
@@ -78,3 +79,41 @@ def test_vl_grpo_pipeline(tmp_path):
     with open(tmp_path / "log" / "metrics.jsonl") as f:
         m = [json.loads(line) for line in f]
     assert [r["step"] for r in m] == [1, 2] and any(r["actor/grad_norm"] > 0 for r in m)
+
+
+def test_video_inputs_sampling_patching_and_forward():
+    """Videos: frame sampling rules, resize to multiples of 28, temporal patches (grid t > 1), placeholder expansion,
+    3-row rope positions over the (t, h, w) grid, and a forward pass through the vision tower and the decoder."""
+    import numpy as np
+
+    from siirl_b200.data_coordinator.dataloader.vision_utils import process_image, process_video, sample_frame_indices
+    from siirl_b200.models.config import get_config
+    from siirl_b200.models.decoder import build_model
+    from siirl_b200.models.vision_processor import VLProcessor
+    from siirl_b200.ops.attention import SeqInfo
+    frames = [np.random.randint(0, 255, (60, 90, 3), dtype=np.uint8) for _ in range(5)]
+    v = process_video({"video": frames}, min_pixels=28 * 28, max_pixels=56 * 56)
+    assert v.shape[0] == 6 and v.shape[2] % 28 == 0 and v.shape[3] % 28 == 0       # odd frame count is padded to even
+    clip = np.random.rand(40, 3, 64, 64).astype(np.float32)
+    v2 = process_video({"video": clip, "nframes": 8}, min_pixels=28 * 28, max_pixels=56 * 56)
+    assert tuple(v2.shape) == (8, 3, 56, 56)
+    idx = sample_frame_indices(300, 30.0, fps=2.0)                                  # 10 s at 2 frames per second
+    assert len(idx) == 20 and idx[0] == 0 and idx[-1] == 299
+    assert len(sample_frame_indices(30, 30.0, fps=2.0)) == 4                        # never fewer than min_frames
+    with pytest.raises(ValueError):
+        process_video({"video": clip}, nframes=4, fps=1.0)
+    img = process_image(np.random.randint(0, 255, (100, 37, 3), dtype=np.uint8), max_pixels=56 * 56, min_pixels=28 * 28)
+    assert img.shape[1] % 28 == 0 and img.shape[2] % 28 == 0 and float(img.max()) <= 1.0
+    cfg = get_config("tiny-vl")
+    proc = VLProcessor(cfg, 28 * 28, 56 * 56)
+    out = proc([5, 6, cfg.image_token_id, 7], [], [v2])
+    t, gh, gw = out["image_grid_thw"][0].tolist()
+    assert t == 8 // cfg.vision.temporal_patch_size and out["pixel_values"].shape[0] == t * gh * gw
+    assert len(out["input_ids"]) == 3 + t * gh * gw // cfg.vision.spatial_merge_size ** 2
+    ids = torch.tensor(out["input_ids"])
+    pos, delta = proc.rope(ids, out["image_grid_thw"])
+    assert pos.shape == (3, ids.numel()) and int(pos[0].max()) < ids.numel()       # the time row advances per grid t
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=0)
+    h = model.forward_hidden(ids, pos, SeqInfo([ids.numel()]), pixel_values=out["pixel_values"],
+                             image_grid_thw=out["image_grid_thw"])
+    assert h.shape == (ids.numel(), cfg.hidden_size) and torch.isfinite(h).all()
