@@ -3,12 +3,14 @@
 // (siirl/engine/actor/dp_actor.py:87-263 through HF flash_attention_2).
 //
 // One CTA owns one 128-row K/V tile of one kv head and walks over the q heads of its GQA group and the
-// query tiles that can attend to it.  Per step, with thread r = kv row r = TMEM lane r:
-//   S^T  = K Q^T,  dP^T = V dO^T                     two 128x128xD MMAs into TMEM
-//   P^T  = exp2(S^T*c - LSE),  dS^T = P^T (dP^T - Delta) * scale      -> bf16, swizzled smem
-//   dV  += P^T dO        dK += dS^T Q                 accumulate in TMEM over all steps (no atomics)
-//   dQ_i = dS K                                        read back and reduced into an fp32 buffer with red.add
-// Q and dO tiles are read by the second group of MMAs through MN-major descriptors of the same shared
+// query tiles that can attend to it.  Per step (TMEM lane r = query row r of the current query tile):
+//   S  = Q K^T,  dP = dO V^T                          two 128x128xD MMAs into TMEM
+//   P  = exp2(S*c - LSE),  dS = P (dP - Delta) * scale            -> bf16, swizzled smem ([q][kv])
+//   dV += P^T dO        dK += dS^T Q                  accumulate in TMEM over all steps (no atomics);
+//                                                      P^T / dS^T are P / dS read through MN-major descriptors
+//   dQ_i = dS K                                        read back, turned through smem and added to an fp32
+//                                                      buffer one whole row per warp instruction
+// Q, dO and K tiles are read by the second group of MMAs through MN-major descriptors of the same shared
 // memory that the first group read K-major, so nothing is transposed in memory.
 #include "common.cuh"
 #include "launchers.h"
@@ -48,8 +50,20 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr int kBwdThreads = 256;
+
+// 256 threads = 8 warps.  Warp w works on TMEM lanes 32 * (w % 4) .. +31 (the hardware's lane quarter of a warp) and
+// on column half w / 4 of every tile it reads, so two warps share each scheduler and cover each other's latencies.
+// Thread <-> query row: lane r of the S / dP / dQ tiles is query row r, so the row's log-sum-exp and delta are two
+// registers; dV / dK tiles have lane = kv row.
 template <int D>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do,
                 FmhaBwdParams p) {
   using L = BwdSmem<D>;
@@ -64,17 +78,17 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   uint8_t* sV = smem + L::kVOff;
   uint8_t* sQ = smem + L::kQOff;
   uint8_t* sDo = smem + L::kDoOff;
-  uint8_t* sPt = smem + L::kPtOff;
-  uint8_t* sDst = smem + L::kDstOff;
-  float* sLse = reinterpret_cast<float*>(smem + L::kLseOff);
-  float* sDelta = sLse + 128;
+  uint8_t* sP = smem + L::kPtOff;    // P  [q rows][kv cols], bf16, 128-byte swizzle, two 64-column chunks
+  uint8_t* sDs = smem + L::kDstOff;  // dS, same layout
   uint64_t* bar_kv = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* bar_ld = bar_kv + 1;
   uint64_t* bar_mma = bar_kv + 2;
   uint64_t* bar_mma2 = bar_kv + 3;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_kv + 4);
 
-  const int tid = threadIdx.x, warp = tid >> 5;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int quarter = warp & 3, half = warp >> 2;
+  const int r = quarter * 32 + lane;  // row of the tile this thread owns (query row, or kv row for dK / dV)
   const int tile = blockIdx.x, kvh = blockIdx.y;
   const int seq_start = p.tile_seq_start[tile], seq_len = p.tile_seq_len[tile], k0 = p.tile_k0[tile];
   const int rep = p.Hq / p.Hkv;
@@ -101,8 +115,8 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_st = tmem_base, tm_dpt = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
-  const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 384;
+  const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
 
   auto issue_loads = [&](int step) {
     const int h = kvh * rep + step / steps_per_head;
@@ -115,18 +129,6 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       tma_load_2d(sDo + c * 16384, &map_do, bar_ld, h * D + c * 64, row);
     }
   };
-  auto load_stats = [&](int step) {
-    const int h = kvh * rep + step / steps_per_head;
-    const int qi = i_start + step % steps_per_head;
-    const int qp = qi * 128 + tid;
-    float l = 0.f, d = 0.f;
-    if (qp < seq_len) {
-      l = p.lse[(size_t)h * p.T + seq_start + qp] * 1.4426950408889634f;
-      d = p.delta[(size_t)h * p.T + seq_start + qp];
-    }
-    sLse[tid] = l;
-    sDelta[tid] = d;
-  };
 
   if (tid == 0 && total_steps > 0) {
     mbar_arrive_expect_tx(bar_kv, 2 * L::kTile);
@@ -137,41 +139,45 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     }
     issue_loads(0);
   }
-  if (total_steps > 0) load_stats(0);
-  __syncthreads();
 
-  constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);
-  constexpr uint32_t idesc_kmn = umma_idesc_bf16(128, D, 0, 1);
-  constexpr uint32_t idesc_mnmn = umma_idesc_bf16(128, D, 1, 1);
-  const int kp = k0 + tid;  // this thread's kv position
+  constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);    // both operands K-major, N = 128
+  constexpr uint32_t idesc_kmn = umma_idesc_bf16(128, D, 0, 1);     // A K-major, B MN-major, N = D
+  constexpr uint32_t idesc_mnmn = umma_idesc_bf16(128, D, 1, 1);    // both MN-major, N = D
   bool ok = true;
 
   for (int step = 0; step < total_steps && ok; ++step) {
     const int h = kvh * rep + step / steps_per_head;
     const int qi = i_start + step % steps_per_head;
     const int q0 = qi * 128;
-    // ---- S^T = K Q^T and dP^T = V dO^T ----
+    // ---- S = Q K^T and dP = dO V^T (lane = query row, column = kv position) ----
     if (tid == 0) {
       bool w = true;
       if (step == 0) w = mbar_wait(bar_kv, 0, p.status, kStatusTimeoutMma);
       w = w && mbar_wait(bar_ld, step & 1, p.status, kStatusTimeoutMma);
       if (w) {
         tc_fence_after();
-        const uint32_t ak = smem_u32(sK), av = smem_u32(sV), bq = smem_u32(sQ), bdo = smem_u32(sDo);
+        const uint32_t ak = smem_u32(sK), av = smem_u32(sV), aq = smem_u32(sQ), ado = smem_u32(sDo);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_bf16_ss(tm_st, umma_smem_desc(ak + off, 16, 1024), umma_smem_desc(bq + off, 16, 1024), idesc_kk,
+          umma_bf16_ss(tm_s, umma_smem_desc(aq + off, 16, 1024), umma_smem_desc(ak + off, 16, 1024), idesc_kk,
                        kk ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk / 4) * 16384 + (kk % 4) * 32;
-          umma_bf16_ss(tm_dpt, umma_smem_desc(av + off, 16, 1024), umma_smem_desc(bdo + off, 16, 1024), idesc_kk,
+          umma_bf16_ss(tm_dp, umma_smem_desc(ado + off, 16, 1024), umma_smem_desc(av + off, 16, 1024), idesc_kk,
                        kk ? 1u : 0u);
         }
       }
       umma_commit(bar_mma);
+    }
+    // this row's statistics travel while the MMAs run
+    const int qp = q0 + r;
+    float lse2 = 0.f, dlt = 0.f;
+    if (qp < seq_len) {
+      lse2 = p.lse[(size_t)h * p.T + seq_start + qp] * 1.4426950408889634f;
+      dlt = p.delta[(size_t)h * p.T + seq_start + qp];
     }
     if (!__all_sync(0xffffffffu, mbar_wait(bar_mma, step & 1, p.status, kStatusTimeoutEpilogue))) {
       ok = false;
@@ -179,36 +185,50 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     }
     tc_fence_after();
 
-    // ---- P^T and dS^T for this thread's kv row ----
+    // ---- P and dS for this thread's query row, its half of the kv columns ----
+    // masks are only needed on the diagonal tile (causal) and on tiles that stick out of the sequence
+    const bool need_mask = (p.causal && q0 < k0 + 128) || q0 + 128 > seq_len || k0 + 128 > seq_len;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int cc = 0; cc < 2; ++cc) {
+      const int c = half * 2 + cc;  // 32-column chunk of the 128 kv columns
       uint32_t rs[32], rd[32];
-      tmem_ld_32x32(tm_st + lane_off + c * 32, rs);
-      tmem_ld_32x32(tm_dpt + lane_off + c * 32, rd);
+      tmem_ld_32x32(tm_s + lane_off + c * 32, rs);
+      tmem_ld_32x32(tm_dp + lane_off + c * 32, rd);
       tmem_ld_wait();
       uint32_t pp[16], dd[16];
+      if (!need_mask) {
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        float pv[2], dv[2];
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int qc = c * 32 + i + u;
-          const int qp = q0 + qc;
-          const bool valid = qp < seq_len && kp < seq_len && (!p.causal || qp >= kp);
-          const float s = __uint_as_float(rs[i + u]) * p.scale_log2;
-          const float prob = valid ? exp2f(s - sLse[qc]) : 0.f;
-          pv[u] = prob;
-          dv[u] = prob * (__uint_as_float(rd[i + u]) - sDelta[qc]) * p.scale;
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse2));
+          const float d0 = p0 * (__uint_as_float(rd[i]) - dlt) * p.scale;
+          const float d1 = p1 * (__uint_as_float(rd[i + 1]) - dlt) * p.scale;
+          pp[i / 2] = pack_bf16x2(p0, p1);
+          dd[i / 2] = pack_bf16x2(d0, d1);
         }
-        pp[i / 2] = pack_bf16x2(pv[0], pv[1]);
-        dd[i / 2] = pack_bf16x2(dv[0], dv[1]);
+      } else {
+        const bool row_ok = qp < seq_len;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int kp = k0 + c * 32 + i + u;
+            const bool valid = row_ok && kp < seq_len && (!p.causal || qp >= kp);
+            const float prob = valid ? ex2_approx(fmaf(__uint_as_float(rs[i + u]), p.scale_log2, -lse2)) : 0.f;
+            pv[u] = prob;
+            dv[u] = prob * (__uint_as_float(rd[i + u]) - dlt) * p.scale;
+          }
+          pp[i / 2] = pack_bf16x2(pv[0], pv[1]);
+          dd[i / 2] = pack_bf16x2(dv[0], dv[1]);
+        }
       }
-      // columns [c*32, c*32+32) of row tid: chunk = c/2, 16-byte pieces (c%2)*4 .. +3
-      uint8_t* prow = sPt + (c >> 1) * 16384 + tid * 128;
-      uint8_t* drow = sDst + (c >> 1) * 16384 + tid * 128;
+      // columns [c*32, c*32+32) of row r: 64-column chunk c/2, 16-byte pieces (c%2)*4 .. +3, swizzled by the row
+      uint8_t* prow = sP + (c >> 1) * 16384 + r * 128;
+      uint8_t* drow = sDs + (c >> 1) * 16384 + r * 128;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const int piece = ((c & 1) * 4 + q) ^ (tid & 7);
+        const int piece = ((c & 1) * 4 + q) ^ (r & 7);
         *reinterpret_cast<uint4*>(prow + (piece << 4)) = make_uint4(pp[q * 4], pp[q * 4 + 1], pp[q * 4 + 2], pp[q * 4 + 3]);
         *reinterpret_cast<uint4*>(drow + (piece << 4)) = make_uint4(dd[q * 4], dd[q * 4 + 1], dd[q * 4 + 2], dd[q * 4 + 3]);
       }
@@ -220,24 +240,23 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     // ---- dV += P^T dO,  dK += dS^T Q,  dQ = dS K ----
     if (tid == 0) {
       tc_fence_after();
-      const uint32_t apt = smem_u32(sPt), adst = smem_u32(sDst);
+      const uint32_t ap = smem_u32(sP), ads = smem_u32(sDs);
       const uint32_t bdo = smem_u32(sDo), bq = smem_u32(sQ), bk = smem_u32(sK);
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {  // contraction over 128 query rows
-        const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
-        umma_bf16_ss(tm_dv, umma_smem_desc(apt + aoff, 16, 1024), umma_smem_desc(bdo + kk * 2048, 16384, 1024),
-                     idesc_kmn, (step | kk) ? 1u : 0u);
+      for (int kk = 0; kk < 8; ++kk) {  // contraction over 128 query rows; A = P^T read MN-major from P
+        umma_bf16_ss(tm_dv, umma_smem_desc(ap + kk * 2048, 16384, 1024), umma_smem_desc(bdo + kk * 2048, 16384, 1024),
+                     idesc_mnmn, (step | kk) ? 1u : 0u);
       }
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
-        const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
-        umma_bf16_ss(tm_dk, umma_smem_desc(adst + aoff, 16, 1024), umma_smem_desc(bq + kk * 2048, 16384, 1024),
-                     idesc_kmn, (step | kk) ? 1u : 0u);
+        umma_bf16_ss(tm_dk, umma_smem_desc(ads + kk * 2048, 16384, 1024), umma_smem_desc(bq + kk * 2048, 16384, 1024),
+                     idesc_mnmn, (step | kk) ? 1u : 0u);
       }
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) {  // contraction over 128 kv rows; A = dS read MN-major from dS^T
-        umma_bf16_ss(tm_st, umma_smem_desc(adst + kk * 2048, 16384, 1024),
-                     umma_smem_desc(bk + kk * 2048, 16384, 1024), idesc_mnmn, kk ? 1u : 0u);
+      for (int kk = 0; kk < 8; ++kk) {  // contraction over 128 kv rows; A = dS K-major, B = K read MN-major
+        const uint32_t aoff = (kk / 4) * 16384 + (kk % 4) * 32;
+        umma_bf16_ss(tm_s, umma_smem_desc(ads + aoff, 16, 1024), umma_smem_desc(bk + kk * 2048, 16384, 1024), idesc_kmn,
+                     kk ? 1u : 0u);
       }
       umma_commit(bar_mma2);
     }
@@ -246,62 +265,60 @@ fmha_bwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       break;
     }
     tc_fence_after();
-    // Q / dO / stats of the next step can stream in while dQ is written out
-    if (step + 1 < total_steps) {
-      if (tid == 0) issue_loads(step + 1);
-    }
+    // Q / dO of the next step stream in while dQ is written out
+    if (step + 1 < total_steps && tid == 0) issue_loads(step + 1);
+
     // ---- dQ tile -> fp32 reduction buffer ----
-    // TMEM hands every thread one query row (lane = row).  Adding that row to global memory from its own thread would
-    // make each warp instruction touch 32 rows, 16 bytes each: 32 partial-line atomics.  The tile is therefore turned
-    // through shared memory (the P^T / dS^T buffers, which the MMAs of this step have finished reading): rows are
-    // written as 16-byte pieces at slot (piece ^ (row & 31)), read back with lane = piece, and each warp instruction
-    // adds one whole 512-byte row, four full lines.
+    // TMEM hands every thread one query row.  Adding a row to global memory from its own thread would make each warp
+    // instruction touch 32 rows, 16 bytes each.  The tile is turned through shared memory instead (the P / dS
+    // buffers, which the MMAs above have finished reading): 16-byte pieces at slot (piece ^ (row & 31)), read back
+    // with lane = piece, so that each warp instruction adds one whole row of D floats.
     {
-      float4* stage = reinterpret_cast<float4*>(sPt);  // [128 rows][32 pieces] = 64 KB = sPt + sDst
-      static_assert(L::kDstOff == L::kPtOff + L::kSq, "the dQ staging tile spans the P^T and dS^T buffers");
+      float4* stage = reinterpret_cast<float4*>(sP);  // [128 rows][D / 4 pieces] fp32 = 64 KB at D = 128
+      static_assert(L::kDstOff == L::kPtOff + L::kSq, "the dQ staging tile spans the P and dS buffers");
+      constexpr int kPieces = D / 4;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tm_st + lane_off + c * 32, r);
+      for (int cc = 0; cc < D / 64; ++cc) {
+        const int c = half * (D / 64) + cc;  // 32-column chunk of the D columns
+        uint32_t rq[32];
+        tmem_ld_32x32(tm_s + lane_off + c * 32, rq);
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 8; ++g) {
           const int piece = c * 8 + g;
-          stage[tid * (D / 4) + (piece ^ (tid & (D / 4 - 1)))] =
-              make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]), __uint_as_float(r[g * 4 + 2]),
-                          __uint_as_float(r[g * 4 + 3]));
+          stage[r * kPieces + (piece ^ (r & (kPieces - 1)))] =
+              make_float4(__uint_as_float(rq[g * 4]), __uint_as_float(rq[g * 4 + 1]), __uint_as_float(rq[g * 4 + 2]),
+                          __uint_as_float(rq[g * 4 + 3]));
         }
       }
-      __syncwarp();  // a warp reads back only the 32 rows its own lanes wrote
-      const int lane = tid & 31;
-      const int row0 = warp * 32;
-      if (lane < D / 4) {
+      tc_fence_before();
+      __syncthreads();
+      if (lane < kPieces) {
 #pragma unroll 4
-        for (int rr = 0; rr < 32; ++rr) {
-          const int row = row0 + rr;
-          const int qp = q0 + row;
-          if (qp >= seq_len) break;
-          const float4 v = stage[row * (D / 4) + (lane ^ (row & (D / 4 - 1)))];
-          float* dst = p.dq_accum + (size_t)(seq_start + qp) * (size_t)(p.Hq * D) + (size_t)h * D + lane * 4;
+        for (int rr = 0; rr < 16; ++rr) {
+          const int row = warp * 16 + rr;
+          const int qrow = q0 + row;
+          if (qrow >= seq_len) break;
+          const float4 v = stage[row * kPieces + (lane ^ (row & (kPieces - 1)))];
+          float* dst = p.dq_accum + (size_t)(seq_start + qrow) * (size_t)(p.Hq * D) + (size_t)h * D + lane * 4;
           red_add_v4(dst, v.x, v.y, v.z, v.w);
         }
       }
     }
-    tc_fence_before();
-    __syncthreads();
-    if (step + 1 < total_steps) load_stats(step + 1);
-    __syncthreads();
+    __syncthreads();  // the staging tile is free again before the next step's P / dS are written
   }
 
-  // ---- dK, dV tiles -> bf16 into the packed gradient buffer ----
-  ok = __all_sync(0xffffffffu, ok);
+  // ---- dK, dV tiles (lane = kv row) -> bf16 into the packed gradient buffer ----
+  ok = __syncthreads_and(ok ? 1 : 0) != 0;
   if (ok) {
+    const int kp = k0 + r;
     const bool row_valid = kp < seq_len;
     const size_t width = (size_t)(p.Hq + 2 * p.Hkv) * D;
     __nv_bfloat16* krow = p.dqkv + (size_t)(seq_start + (row_valid ? kp : 0)) * width + kcol;
     __nv_bfloat16* vrow = p.dqkv + (size_t)(seq_start + (row_valid ? kp : 0)) * width + vcol;
 #pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
+    for (int cc = 0; cc < D / 64; ++cc) {
+      const int c = half * (D / 64) + cc;
       uint32_t rk[32], rv[32];
       if (total_steps > 0) {
         tmem_ld_32x32(tm_dk + lane_off + c * 32, rk);
@@ -387,7 +404,7 @@ static int launch_bwd(const CUtensorMap& mqkv, const CUtensorMap& mdo, const Fmh
     configured = true;
   }
   dim3 grid(num_tiles, p.Hkv);
-  kernel<<<grid, 128, L::kTotal, stream>>>(mqkv, mdo, p);
+  kernel<<<grid, kBwdThreads, L::kTotal, stream>>>(mqkv, mdo, p);
   return (int)cudaGetLastError();
 }
 

@@ -57,6 +57,10 @@ class DecoderConfig:
     lora_alpha: float = 16.0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    # shared expert (Qwen2-MoE, DeepSeek-style): a dense SwiGLU MLP every token passes through, added to the routed
+    # experts' output; ``shared_expert_gate`` multiplies it by sigmoid(x . g) (Qwen2-MoE)
+    shared_expert_intermediate_size: int = 0
+    shared_expert_gate: bool = False
     # value head (critic / reward model): one scalar per token instead of the vocabulary head
     value_head: bool = False
     vision: Optional[VisionConfig] = None
@@ -89,6 +93,7 @@ class DecoderConfig:
             attn += 2 * self.head_dim
         if self.is_moe:
             mlp = self.num_experts * 3 * H * self.moe_intermediate_size + self.num_experts * H
+            mlp += 3 * H * self.shared_expert_intermediate_size + (H if self.shared_expert_gate else 0)
         else:
             mlp = 3 * H * I
         per_layer = attn + mlp + 2 * H
@@ -126,9 +131,18 @@ class DecoderConfig:
             num_experts_per_tok=text.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=text.get("moe_intermediate_size", 0) or 0,
             norm_topk_prob=bool(text.get("norm_topk_prob", True)),
+            shared_expert_intermediate_size=text.get("shared_expert_intermediate_size", 0) or 0,
+            shared_expert_gate=mt == "qwen2_moe" and bool(text.get("shared_expert_intermediate_size", 0)),
             eos_token_id=(cfg.get("eos_token_id") if isinstance(cfg.get("eos_token_id"), int) else 2) or 2,
             pad_token_id=cfg.get("pad_token_id") or 0,
         )
+        if mt == "mixtral":
+            # Mixtral's experts use the dense intermediate size; its router renormalises the top-k weights
+            out.moe_intermediate_size = text.get("intermediate_size", 0)
+            out.norm_topk_prob = True
+            out.qkv_bias = False
+        if mt == "qwen2_moe":
+            out.norm_topk_prob = bool(text.get("norm_topk_prob", False))
         if "vision_config" in cfg:
             vc = cfg["vision_config"]
             out.vision = VisionConfig(
@@ -148,7 +162,8 @@ class DecoderConfig:
 
     def to_hf_config(self) -> Dict[str, Any]:
         arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
-                "llama": "LlamaForCausalLM", "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration"}
+                "llama": "LlamaForCausalLM", "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration",
+                "mixtral": "MixtralForCausalLM", "qwen2_moe": "Qwen2MoeForCausalLM"}
         d = {
             "architectures": [arch.get(self.model_type, "Qwen2ForCausalLM")], "model_type": self.model_type,
             "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
@@ -159,9 +174,14 @@ class DecoderConfig:
             "tie_word_embeddings": self.tie_word_embeddings, "hidden_act": "silu", "torch_dtype": "bfloat16",
             "eos_token_id": self.eos_token_id, "pad_token_id": self.pad_token_id,
         }
-        if self.is_moe:
+        if self.is_moe and self.model_type == "mixtral":
+            d.update(num_local_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     intermediate_size=self.moe_intermediate_size)
+        elif self.is_moe:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob)
+            if self.shared_expert_intermediate_size:
+                d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
         if self.mrope_section:
             d["rope_scaling"] = {"type": "mrope", "mrope_section": self.mrope_section}
         return d
@@ -184,6 +204,23 @@ PRESETS: Dict[str, DecoderConfig] = {
                                    num_layers=48, num_heads=32, num_kv_heads=4, head_dim=128, rope_theta=1e6,
                                    qkv_bias=False, qk_norm=True, num_experts=128, num_experts_per_tok=8,
                                    moe_intermediate_size=768, eos_token_id=151645, pad_token_id=151643),
+    "mixtral-8x7b": DecoderConfig(model_type="mixtral", vocab_size=32000, hidden_size=4096, intermediate_size=14336,
+                                  num_layers=32, num_heads=32, num_kv_heads=8, head_dim=128, rope_theta=1e6,
+                                  qkv_bias=False, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=14336,
+                                  rms_norm_eps=1e-5, eos_token_id=2, pad_token_id=0),
+    "qwen1.5-moe-a2.7b": DecoderConfig(model_type="qwen2_moe", vocab_size=151936, hidden_size=2048,
+                                       intermediate_size=5632, num_layers=24, num_heads=16, num_kv_heads=16,
+                                       head_dim=128, rope_theta=1e6, qkv_bias=True, num_experts=60,
+                                       num_experts_per_tok=4, moe_intermediate_size=1408, norm_topk_prob=False,
+                                       shared_expert_intermediate_size=5632, shared_expert_gate=True,
+                                       eos_token_id=151645, pad_token_id=151643),
+    "tiny-mixtral": DecoderConfig(model_type="mixtral", vocab_size=1024, hidden_size=128, intermediate_size=64,
+                                  num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, qkv_bias=False,
+                                  num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64),
+    "tiny-qwen2-moe": DecoderConfig(model_type="qwen2_moe", vocab_size=1024, hidden_size=128, intermediate_size=352,
+                                    num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, num_experts=8,
+                                    num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=False,
+                                    shared_expert_intermediate_size=96, shared_expert_gate=True),
     "tiny-moe": DecoderConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=128, intermediate_size=352,
                               num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, qkv_bias=False, qk_norm=True,
                               num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64),

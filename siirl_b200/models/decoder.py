@@ -70,6 +70,13 @@ class DecoderLayer(nn.Module):
             self.experts_down = _param((El, H, I), dtype, device, std, gen)
             self.ep = None          # ExpertParallel context, attached by the worker
             self.ep_pad_tokens = 0  # static token bound all ranks pad to (0: token counts are equal already)
+            if cfg.shared_expert_intermediate_size > 0:
+                # shared expert (Qwen2-MoE / DeepSeek style): dense, replicated on every rank
+                Is = cfg.shared_expert_intermediate_size
+                self.shared_gate_up_weight = _param((2 * Is, H), dtype, device, std, gen)
+                self.shared_down_weight = _param((H, Is), dtype, device, std, gen)
+                if cfg.shared_expert_gate:
+                    self.shared_expert_gate_weight = _param((1, H), dtype, device, std, gen)
         else:
             I = cfg.intermediate_size
             self.gate_up_proj_weight = _param((2 * I, H), dtype, device, std, gen)
@@ -119,9 +126,16 @@ class DecoderLayer(nn.Module):
     def mlp(self, x: torch.Tensor) -> torch.Tensor:
         if self.cfg.is_moe:
             from .moe import moe_forward
-            return moe_forward(x, self.router_weight, self.experts_gate_up, self.experts_down,
-                               self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, ep=self.ep,
-                               pad_tokens=self.ep_pad_tokens)
+            y = moe_forward(x, self.router_weight, self.experts_gate_up, self.experts_down,
+                            self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, ep=self.ep,
+                            pad_tokens=self.ep_pad_tokens)
+            if self.cfg.shared_expert_intermediate_size > 0:
+                s = ops.linear(ops.swiglu(ops.linear(x, self.shared_gate_up_weight)), self.shared_down_weight)
+                if self.cfg.shared_expert_gate:
+                    g = torch.sigmoid(x.float() @ self.shared_expert_gate_weight.float().t())
+                    s = (s.float() * g).to(s.dtype)
+                y = y + s
+            return y
         return self._linear(ops.swiglu(self._linear(x, "gate_up_proj")), "down_proj")
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], positions, info: SeqInfo, rope, causal=True):

@@ -17,6 +17,16 @@ import torch
 from .config import DecoderConfig
 
 
+def _moe_names(cfg: DecoderConfig) -> Dict[str, str]:
+    """HF parameter names of the routed experts: Mixtral says ``block_sparse_moe.experts.N.w1 / w3 / w2`` where the
+    Qwen MoE families say ``mlp.experts.N.gate_proj / up_proj / down_proj``."""
+    if cfg.model_type == "mixtral":
+        return {"router": "block_sparse_moe.gate.weight", "expert": "block_sparse_moe.experts.{e}.{w}.weight",
+                "gate": "w1", "up": "w3", "down": "w2"}
+    return {"router": "mlp.gate.weight", "expert": "mlp.experts.{e}.{w}.weight", "gate": "gate_proj",
+            "up": "up_proj", "down": "down_proj"}
+
+
 def to_hf_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
     cfg: DecoderConfig = model.cfg
     qw, kw = cfg.q_width, cfg.kv_width
@@ -40,12 +50,21 @@ def to_hf_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
         yield p + "post_attention_layernorm.weight", layer.post_attention_layernorm.data
         if cfg.is_moe:
             I = cfg.moe_intermediate_size
-            yield p + "mlp.gate.weight", layer.router_weight.data
+            names = _moe_names(cfg)
+            yield p + names["router"], layer.router_weight.data
             for e in range(cfg.num_experts):
                 gu = layer.experts_gate_up.data[e]
-                yield p + f"mlp.experts.{e}.gate_proj.weight", gu[:I]
-                yield p + f"mlp.experts.{e}.up_proj.weight", gu[I:]
-                yield p + f"mlp.experts.{e}.down_proj.weight", layer.experts_down.data[e]
+                yield p + names["expert"].format(e=e, w=names["gate"]), gu[:I]
+                yield p + names["expert"].format(e=e, w=names["up"]), gu[I:]
+                yield p + names["expert"].format(e=e, w=names["down"]), layer.experts_down.data[e]
+            if cfg.shared_expert_intermediate_size > 0:
+                Is = cfg.shared_expert_intermediate_size
+                sgu = layer.shared_gate_up_weight.data
+                yield p + "mlp.shared_expert.gate_proj.weight", sgu[:Is]
+                yield p + "mlp.shared_expert.up_proj.weight", sgu[Is:]
+                yield p + "mlp.shared_expert.down_proj.weight", layer.shared_down_weight.data
+                if cfg.shared_expert_gate:
+                    yield p + "mlp.shared_expert_gate.weight", layer.shared_expert_gate_weight.data
         else:
             I = cfg.intermediate_size
             gu = layer.gate_up_proj_weight.data
@@ -139,11 +158,19 @@ def load_hf_weights(model, path: str, strict: bool = True) -> None:
             put(layer.o_proj_weight.data, get(p + "self_attn.o_proj.weight"))
             put(layer.post_attention_layernorm.data, get(p + "post_attention_layernorm.weight"))
             if cfg.is_moe:
-                put(layer.router_weight.data, get(p + "mlp.gate.weight"))
+                names = _moe_names(cfg)
+                put(layer.router_weight.data, get(p + names["router"]))
                 for e in range(cfg.num_experts):
-                    put(layer.experts_gate_up.data[e], torch.cat([get(p + f"mlp.experts.{e}.gate_proj.weight"),
-                                                                  get(p + f"mlp.experts.{e}.up_proj.weight")], 0))
-                    put(layer.experts_down.data[e], get(p + f"mlp.experts.{e}.down_proj.weight"))
+                    put(layer.experts_gate_up.data[e],
+                        torch.cat([get(p + names["expert"].format(e=e, w=names["gate"])),
+                                   get(p + names["expert"].format(e=e, w=names["up"]))], 0))
+                    put(layer.experts_down.data[e], get(p + names["expert"].format(e=e, w=names["down"])))
+                if cfg.shared_expert_intermediate_size > 0:
+                    put(layer.shared_gate_up_weight.data, torch.cat([get(p + "mlp.shared_expert.gate_proj.weight"),
+                                                                     get(p + "mlp.shared_expert.up_proj.weight")], 0))
+                    put(layer.shared_down_weight.data, get(p + "mlp.shared_expert.down_proj.weight"))
+                    if cfg.shared_expert_gate:
+                        put(layer.shared_expert_gate_weight.data, get(p + "mlp.shared_expert_gate.weight"))
             else:
                 put(layer.gate_up_proj_weight.data, torch.cat([get(p + "mlp.gate_proj.weight"),
                                                                get(p + "mlp.up_proj.weight")], 0))
