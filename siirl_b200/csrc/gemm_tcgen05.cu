@@ -500,7 +500,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const bool rv = row < p.M;
         const long long y = rv ? p.labels[row] : -1;
         const float l = rv ? p.lm_lse[row] : 0.f;
-        const float glp = (rv && y >= 0 && y < p.N) ? p.lm_glogp[row] : 0.f;
+        // y == -2: the target exists but in another rank's vocabulary slice (vocabulary-parallel LM head): the
+        // softmax term of its gradient still applies here, the one-hot term never matches
+        const float glp = (rv && ((y >= 0 && y < p.N) || y == -2)) ? p.lm_glogp[row] : 0.f;
         const float ge = (rv && p.lm_gent) ? p.lm_gent[row] : 0.f;
         const float H = (rv && p.lm_ent) ? p.lm_ent[row] : 0.f;
 #pragma unroll 1

@@ -167,7 +167,8 @@ class DAGWorker:
             # Ulysses peers work on the same micro-batches
             a = self.config.actor_rollout_ref.actor
             tp = max(1, a.ulysses_sequence_parallel_size, int(a.megatron.context_parallel_size or 1),
-                     int(a.megatron.pipeline_model_parallel_size or 1))
+                     int(a.megatron.pipeline_model_parallel_size or 1),
+                     int(a.megatron.tensor_model_parallel_size or 1) if a.strategy == "megatron" else 1)
         elif node.node_role == NodeRole.CRITIC:
             tp = max(1, self.config.critic.ulysses_sequence_parallel_size)
         dp = max(1, gw // tp)

@@ -13,6 +13,7 @@ GPU->CPU->GPU around each worker call (fsdp_workers.py:1271-1347).
 from __future__ import annotations
 
 import math
+import os
 import time
 from typing import Any, Dict, List, Optional
 
@@ -119,6 +120,7 @@ class _ModelWorkerBase:
             load_hf_weights(self.model, path)
         if ep > 1:
             self._attach_expert_parallel(model_args)
+        self._attach_tensor_parallel(self.model)
         pp_filter = self._attach_pipeline_parallel(self.model, trainable)
         self._attach_sequence_parallel(self.model)
         self._attach_context_parallel(self.model)
@@ -140,6 +142,10 @@ class _ModelWorkerBase:
             self.store = FlatParamStore(self.model, group=self._pp_dp_group, comm=None, param_filter=pp_filter)
         elif trainable and self._zero3():
             self.store = self._shard_params(self.model, model_args, trainable=True)
+        elif trainable and getattr(self, "_tp_train", None) is not None:
+            # tensor-parallel trainer: every rank owns its slices; gradients and optimizer state are shared with the
+            # ranks that hold the same slices (same index in their tensor-parallel group)
+            self.store = FlatParamStore(self.model, group=self._tp_dp_group, comm=self._tp_dp_comm)
         elif trainable:
             self.store = FlatParamStore(self.model, group=self.group, comm=self.comm)
         else:
@@ -171,7 +177,7 @@ class _ModelWorkerBase:
     def _phase_sync(self) -> None:
         """Align the ranks of the worker group before a phase whose kernels wait on peers with a short bound (tensor /
         expert / sequence parallel exchanges): the previous phase may have left them seconds apart."""
-        if self.world > 1 and any(getattr(self, a, None) is not None for a in ("tp_model", "ep_ctx", "_sp_ctx", "_cp_ctx", "_pp_ctx")):
+        if self.world > 1 and any(getattr(self, a, None) is not None for a in ("tp_model", "ep_ctx", "_sp_ctx", "_cp_ctx", "_pp_ctx", "_tp_train")):
             if getattr(self, "_sync_word", None) is None:
                 self._sync_word = torch.zeros(1, device=self.device)
             dist.all_reduce(self._sync_word, group=self.group)
@@ -182,6 +188,52 @@ class _ModelWorkerBase:
             self._vlp = VLProcessor(self.model_config, self.config.model.image_min_pixels,
                                     self.config.model.image_max_pixels)
         return self._vlp
+
+    def _train_tp_size(self) -> int:
+        cfgs = getattr(self.config, "actor", self.config)
+        mg = getattr(cfgs, "megatron", None)
+        if str(getattr(cfgs, "strategy", "fsdp")) != "megatron" or mg is None:
+            return 1
+        return max(1, int(mg.tensor_model_parallel_size or 1))
+
+    def _attach_tensor_parallel(self, model) -> None:
+        """Megatron-style tensor (and sequence) parallel training (``strategy=megatron``,
+        ``megatron.tensor_model_parallel_size``, ``megatron.sequence_parallel``): consecutive blocks of ``tp`` ranks
+        form a tensor-parallel group, the ranks with the same index across blocks the data-parallel group of those
+        slices.  Every rank of the job creates all groups in the same order (``new_group`` is collective)."""
+        n = self._train_tp_size()
+        if n <= 1 or self.world <= 1:
+            return
+        cfgs = getattr(self.config, "actor", self.config)
+        if getattr(self, "_tp_train", None) is None:
+            from ..parallel.megatron_tp import TPTrainContext
+            if self.world % n:
+                raise ValueError(f"megatron.tensor_model_parallel_size={n} must divide the group size {self.world}")
+            for name in ("ulysses_sequence_parallel_size",):
+                if int(getattr(cfgs, name, 1) or 1) > 1:
+                    raise ValueError("tensor-parallel training cannot be combined with Ulysses sequence parallelism")
+            mg = cfgs.megatron
+            if int(mg.pipeline_model_parallel_size or 1) > 1 or int(mg.context_parallel_size or 1) > 1:
+                raise ValueError("tensor-parallel training cannot be combined with pipeline / context parallelism yet")
+            ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
+            mine = dp = None
+            for b in range(self.world // n):
+                g = dist.new_group(ranks[b * n:(b + 1) * n])
+                if b == self.rank // n:
+                    mine = g
+            for i in range(n):
+                g = dist.new_group(ranks[i::n])
+                if i == self.rank % n:
+                    dp = g
+            self._tp_train = TPTrainContext(mine, sequence_parallel=bool(mg.sequence_parallel))
+            self._tp_train_size = n
+            self._tp_dp_group = dp
+            self._tp_dp_comm = None
+            if self.device.type == "cuda" and self.world // n > 1:
+                from ..parallel.symm import SymmComm
+                self._tp_dp_comm = SymmComm.create(dp)
+        from ..parallel.megatron_tp import shard_decoder
+        shard_decoder(model, self._tp_train)
 
     def _attach_sequence_parallel(self, model) -> None:
         """Ulysses groups are consecutive blocks of ``ulysses_sequence_parallel_size`` ranks of the worker's group;
@@ -368,12 +420,15 @@ class _ModelWorkerBase:
                 ent = _group_sum(torch.zeros(N, dtype=ent_l.dtype, device=ent_l.device).index_put((idx,), ent_l),
                                  group)
             return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
-        lp, ent = lm_head_logprob_entropy(hidden.index_select(0, pk.sel), model.head_weight, pk.labels, temperature,
-                                          with_entropy)
+        lp, ent = model.token_logprobs(hidden.index_select(0, pk.sel), pk.labels, temperature, with_entropy)
         return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
 
     def _optimizer_step(self, optim_cfg, grad_clip: float) -> torch.Tensor:
         lr = lr_at_step(optim_cfg, self.opt_step, max(self.total_training_steps, optim_cfg.total_training_steps))
+        if getattr(self, "_tp_train", None) is not None:
+            from ..parallel.megatron_tp import allreduce_sequence_parallel_grads
+            self.store.collect_grads()
+            allreduce_sequence_parallel_grads(self.model, self._tp_train)
         norm = self.store.step(lr, tuple(optim_cfg.betas), 1e-8, optim_cfg.weight_decay, grad_clip)
         if getattr(self, "_pp_ctx", None) is not None:
             from ..parallel.pipeline import sync_stage_weights
@@ -390,7 +445,14 @@ class _ModelWorkerBase:
         handle whose ``wait()`` must be called before the checkpoint is declared complete (asynchronous saves write
         in a background thread; reference API: siirl/engine/fsdp_workers.py:1452-1499)."""
         from ..utils.checkpoint.checkpoint_manager import ShardedCheckpointManager
-        return ShardedCheckpointManager(self.model, self.store, self.model_config, group=self.group, contents=contents,
+        group = self.group
+        if getattr(self, "_tp_train", None) is not None:
+            # one sub-directory per tensor-parallel index: inside it the shards of that slice's data-parallel group
+            local_path = os.path.join(local_path, f"tp_rank_{self._tp_train.rank}")
+            hdfs_path = f"{hdfs_path.rstrip('/')}/tp_rank_{self._tp_train.rank}" if hdfs_path else None
+            group = self._tp_dp_group
+            contents = [c for c in (contents or ["model", "optimizer", "extra"]) if c != "hf_model"]
+        return ShardedCheckpointManager(self.model, self.store, self.model_config, group=group, contents=contents,
                                         tokenizer=getattr(self, "tokenizer", None)).save(
             local_path, global_step, extra={"opt_step": self.opt_step}, max_ckpt_to_keep=max_ckpt_to_keep,
             async_save=async_save, hdfs_path=hdfs_path)
@@ -403,13 +465,18 @@ class _ModelWorkerBase:
         import shutil
 
         from ..utils.checkpoint.checkpoint_manager import ShardedCheckpointManager
+        group = self.group
+        if getattr(self, "_tp_train", None) is not None:
+            local_path = os.path.join(local_path, f"tp_rank_{self._tp_train.rank}")
+            hdfs_path = f"{hdfs_path.rstrip('/')}/tp_rank_{self._tp_train.rank}" if hdfs_path else None
+            group = self._tp_dp_group
         if hdfs_path and not os.path.isdir(local_path):
             from ..utils.extras import fs
             if self.rank == 0:
                 fs.copy(hdfs_path, local_path)
             if self.world > 1:
                 dist.barrier(group=self.group)
-        extra = ShardedCheckpointManager(self.model, self.store, self.model_config, group=self.group).load(local_path)
+        extra = ShardedCheckpointManager(self.model, self.store, self.model_config, group=group).load(local_path)
         if extra:
             self.opt_step = int(extra.get("opt_step", self.opt_step))
         if del_local_after_load:
@@ -442,7 +509,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         """Global mini-batch -> per-rank sample count (reference: fsdp_workers.py:211-235)."""
         a = self.config.actor
         n = self.config.rollout.n
-        dp = max(self.world // max(a.ulysses_sequence_parallel_size, 1), 1)
+        dp = max(self.world // max(a.ulysses_sequence_parallel_size, self._train_tp_size(), 1), 1)
         self.ppo_mini_batch_size = max(1, a.ppo_mini_batch_size * n // dp)
         micro = a.ppo_micro_batch_size_per_gpu
         if micro is None and a.ppo_micro_batch_size is not None:
@@ -473,6 +540,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 load_hf_weights(self.ref_model, margs.path)
             for p in self.ref_model.parameters():
                 p.requires_grad_(False)
+            self._attach_tensor_parallel(self.ref_model)    # a tensor-parallel trainer scores with sliced weights too
             self.ref_store = None
             if self._zero3() and self.world > 1:
                 self.ref_store = self._shard_params(self.ref_model, margs, trainable=False)
@@ -495,6 +563,9 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
             self.tp_model = None
             tp = max(1, int(r.tensor_model_parallel_size))
             self._full_weights(True)        # the engine (and its tensor-parallel slices) reads whole weights
+            if getattr(self, "_tp_train", None) is not None and tp == 1:
+                raise ValueError("a tensor-parallel trainer needs rollout.tensor_model_parallel_size equal to "
+                                 "megatron.tensor_model_parallel_size (the engine runs on the trainer's slices)")
             if tp > 1:
                 self.tp_model = self._build_tp_model(tp, r.max_num_batched_tokens)
             self.engine = RolloutEngine(self.tp_model or self.model, max_num_seqs=min(r.max_num_seqs, 1024),
@@ -537,6 +608,20 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
         import torch.distributed as dist
         from ..models.tp_decoder import TPDecoder
         from ..parallel.tensor_parallel import TPContext
+        if getattr(self, "_tp_train", None) is not None:
+            # the trainer is tensor parallel already: the engine runs on the very same slices
+            if tp != self._tp_train_size:
+                raise ValueError(f"rollout.tensor_model_parallel_size={tp} must equal the trainer's "
+                                 f"megatron.tensor_model_parallel_size={self._tp_train_size}")
+            comm = None
+            if self.device.type == "cuda":
+                from ..parallel.symm import SymmComm
+                comm = SymmComm.create(self._tp_train.group)
+            H = self.model_config.hidden_size
+            ctx = TPContext(self._tp_train.group, comm, max_rows=max(max_tokens, 256), max_cols=H,
+                            max_tiles=((max(max_tokens, 256) + 127) // 128) * ((H + 127) // 128) + 8)
+            self._tp_size = tp
+            return TPDecoder(self.model, ctx, presharded=True)
         if self.world % tp:
             raise ValueError(f"rollout.tensor_model_parallel_size={tp} does not divide the group size {self.world}")
         if self.model_config.lora_rank > 0:

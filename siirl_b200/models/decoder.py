@@ -136,6 +136,11 @@ class DecoderLayer(nn.Module):
                     s = (s.float() * g).to(s.dtype)
                 y = y + s
             return y
+        tp = getattr(self, "tp", None)
+        if tp is not None:
+            from ..parallel.megatron_tp import enter_parallel_block, leave_parallel_block
+            y = self._linear(ops.swiglu(self._linear(enter_parallel_block(x, tp), "gate_up_proj")), "down_proj")
+            return leave_parallel_block(y, tp)
         return self._linear(ops.swiglu(self._linear(x, "gate_up_proj")), "down_proj")
 
     def forward(self, h: torch.Tensor, delta: Optional[torch.Tensor], positions, info: SeqInfo, rope, causal=True):
@@ -144,8 +149,12 @@ class DecoderLayer(nn.Module):
         z3 = getattr(self, "zero3", None)
         if z3 is not None:      # parameter-sharded training state: assemble this layer's weights (prefetched)
             z3.fetch(self.zero3_index)
+        tp = getattr(self, "tp", None)      # tensor-parallel training: ``cfg`` holds the local head / FFN counts
         x, h = ops.rmsnorm(delta if delta is not None else h, self.input_layernorm, cfg.rms_norm_eps,
                            residual=h if delta is not None else None)
+        if tp is not None:
+            from ..parallel.megatron_tp import enter_parallel_block
+            x = enter_parallel_block(x, tp)
         qkv = self.qkv(x, positions, rope)
         sp = getattr(self, "sp", None)
         if sp is not None and sp.sp > 1:
@@ -164,6 +173,9 @@ class DecoderLayer(nn.Module):
         else:
             a = attention_packed(qkv, info, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, causal=causal)
         attn_out = self._linear(a, "o_proj")
+        if tp is not None:
+            from ..parallel.megatron_tp import leave_parallel_block
+            attn_out = leave_parallel_block(attn_out, tp)
         x, h = ops.rmsnorm(attn_out, self.post_attention_layernorm, cfg.rms_norm_eps, residual=h)
         return h, self.mlp(x)
 
@@ -244,7 +256,22 @@ class DecoderLM(nn.Module):
             safe = rows.clamp(min=0)
             input_ids = torch.where(keep, input_ids[safe], torch.zeros_like(safe))
             positions = torch.where(keep, positions[safe], torch.zeros_like(positions[safe]))
+        tp = getattr(self, "tp", None)
+        sp_rows = None
+        if tp is not None and tp.sequence_parallel:
+            # Megatron sequence parallelism: between the tensor-parallel blocks every rank keeps 1 / tp of the token
+            # rows.  The packed stream is padded (one dummy sequence) to a multiple of the group size.
+            assert pixel_values is None, "sequence-parallel training with image inputs is not wired"
+            sp_rows = input_ids.shape[0]
+            pad = (-sp_rows) % tp.size
+            if pad:
+                input_ids = torch.cat([input_ids, input_ids.new_zeros(pad)])
+                positions = torch.cat([positions, positions.new_zeros(*positions.shape[:-1], pad)], dim=-1)
+                info = SeqInfo(list(info.seqlens) + [pad], device=input_ids.device)
         h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask)
+        if sp_rows is not None:
+            from ..parallel.megatron_tp import take_rows_for_sp
+            h = take_rows_for_sp(h, tp)
         delta = None
         offload = getattr(self, "activation_offload", None)
         ctx = offload.region() if (offload is not None and torch.is_grad_enabled()) else contextlib.nullcontext()
@@ -263,7 +290,21 @@ class DecoderLM(nn.Module):
                 else:
                     h, delta = layer(h, delta, positions, info, rope)
         out, _ = ops.rmsnorm(delta, self.norm, self.cfg.rms_norm_eps, residual=h)
+        if sp_rows is not None:
+            from ..parallel.megatron_tp import gather_rows_from_sp
+            out = gather_rows_from_sp(out, tp)[:sp_rows]
         return out
+
+    def token_logprobs(self, hidden: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
+                       with_entropy: bool = True):
+        """``log p(label)`` and entropy from final hidden states: the fused LM-head kernel, or its vocabulary-parallel
+        form when this rank holds a slice of the head (tensor-parallel training with ``vocab_parallel``)."""
+        vr = getattr(self, "vocab_range", None)
+        if vr is not None:
+            from ..parallel.megatron_tp import vocab_parallel_logprob_entropy
+            lp, ent = vocab_parallel_logprob_entropy(hidden, self.lm_head, labels, vr[0], self.tp.group, temperature)
+            return lp, (ent if with_entropy else None)
+        return lm_head_logprob_entropy(hidden, self.head_weight, labels, temperature, with_entropy)
 
     def forward_hidden_pp(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo):
         """Pipeline-parallel forward of this rank's stage.  Returns ``(hidden, None)`` on the last stage (final-norm
@@ -353,7 +394,7 @@ class DecoderLM(nn.Module):
                  with_entropy: bool = True, **mm) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """``log p(labels[t] | prefix)`` and entropy for every packed position (fp32 ``[T]``)."""
         hidden = self.forward_hidden(input_ids, positions, info, **mm)
-        return lm_head_logprob_entropy(hidden, self.head_weight, labels, temperature, with_entropy)
+        return self.token_logprobs(hidden, labels, temperature, with_entropy)
 
     def values(self, input_ids, positions, info: SeqInfo, **mm) -> torch.Tensor:
         """Scalar value per packed position (critic / reward model head)."""

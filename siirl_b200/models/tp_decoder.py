@@ -27,8 +27,12 @@ class _TPLayer:
 
 
 class TPDecoder:
-    def __init__(self, model: DecoderLM, tp: TPContext):
-        cfg = model.cfg
+    def __init__(self, model: DecoderLM, tp: TPContext, presharded: bool = False):
+        """``presharded``: ``model`` was cut into tensor-parallel slices for training already
+        (``parallel.megatron_tp.shard_decoder`` with the same group); the engine then reads those parameters in place
+        and ``sync_weights`` has nothing to copy."""
+        cfg = getattr(model, "full_cfg", model.cfg)
+        self.presharded = bool(presharded)
         w = tp.world
         if cfg.is_moe:
             raise NotImplementedError("tensor-parallel rollout of MoE layers: use expert parallelism instead")
@@ -59,6 +63,17 @@ class TPDecoder:
     @torch.no_grad()
     def sync_weights(self) -> None:
         """Refresh the per-rank copies of the column-parallel weights from the replica (after an optimizer step)."""
+        if self.presharded:
+            self.layers = []
+            for layer in self.full.layers:
+                t = _TPLayer()
+                t.qkv_w = layer.qkv_proj_weight.detach()
+                t.qkv_b = layer.qkv_proj_bias.detach() if layer.qkv_proj_bias is not None else None
+                t.gate_up_w = layer.gate_up_proj_weight.detach()
+                t.o_w = layer.o_proj_weight.detach()
+                t.down_w = layer.down_proj_weight.detach()
+                self.layers.append(t)
+            return
         c, w, r = self.full_cfg, self.tp.world, self.tp.rank
         D = c.head_dim
         hq, hk, I = c.num_heads // w, c.num_kv_heads // w, c.intermediate_size // w

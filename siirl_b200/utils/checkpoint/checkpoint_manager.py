@@ -68,7 +68,11 @@ def checkpoint_problems(step_dir: str) -> List[str]:
     roles = [d for d in sorted(os.listdir(step_dir)) if os.path.isdir(os.path.join(step_dir, d)) and "_agent_" in d]
     if not roles:
         problems.append("no role directory")
+    expanded = []
     for role in roles:
+        subs = sorted(x for x in os.listdir(os.path.join(step_dir, role)) if x.startswith("tp_rank_"))
+        expanded += [os.path.join(role, x) for x in subs] if subs else [role]
+    for role in expanded:
         d = os.path.join(step_dir, role)
         try:
             with open(os.path.join(d, "manifest.json")) as f:

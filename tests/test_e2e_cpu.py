@@ -87,6 +87,27 @@ def test_grpo_with_sharded_parameters(tmp_path):
     assert [r["step"] for r in _metrics(tmp_path / "log2")] == [3]
 
 
+def test_grpo_with_megatron_tensor_and_sequence_parallel_training(tmp_path):
+    """``strategy=megatron`` with tensor_model_parallel_size=2 and sequence_parallel: both ranks hold half of every
+    projection, train and score on the slices, the rollout engine decodes on the same slices; save and resume."""
+    ck = tmp_path / "c"
+    extra = ["actor_rollout_ref.actor.strategy=megatron",
+             "actor_rollout_ref.actor.megatron.tensor_model_parallel_size=2",
+             "actor_rollout_ref.actor.megatron.sequence_parallel=True",
+             "actor_rollout_ref.rollout.tensor_model_parallel_size=2", "data.max_response_length=16"]
+    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=2", "trainer.save_freq=2", *extra],
+               tmp_path / "log1")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log1")
+    assert [r["step"] for r in m] == [1, 2]
+    assert all(r["actor/grad_norm"] > 0 and r["actor/grad_norm"] == r["actor/grad_norm"] for r in m)
+    assert (ck / "global_step_2" / "actor_agent_0" / "tp_rank_1" / "manifest.json").exists()
+    out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=3", "trainer.resume_mode=auto",
+                *extra], tmp_path / "log2")
+    assert out.returncode == 0, out.stderr[-4000:]
+    assert [r["step"] for r in _metrics(tmp_path / "log2")] == [3]
+
+
 def test_injected_rank_failure_stops_the_job(tmp_path):
     out = _run([f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=2",
                 "fault.inject=[{rank: 1, step: 0, node: function_reward, kind: exit, code: 17}]"], tmp_path / "log",

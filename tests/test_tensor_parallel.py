@@ -22,3 +22,17 @@ def test_expert_parallel_two_cpu_ranks():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "EP_OK" in out.stdout
+
+
+def test_tensor_parallel_training_matches_the_whole_model():
+    import os
+    import subprocess
+    import sys
+
+    from siirl_b200.execution.scheduler.launch import find_free_port
+    here = os.path.dirname(os.path.abspath(__file__))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(find_free_port()), os.path.join(here, "tp_train_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "TP_TRAIN_OK" in out.stdout
