@@ -75,9 +75,14 @@ def bench_gemm(small: bool):
         b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
         out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
         fl = 2.0 * M * N * K
-        report("gemm_bf16_tcgen05 fwd (x W^T)", timeit(lambda: ops.gemm(a, b, out=out)), fl, M=M, N=N, K=K)
+        report("gemm_bf16_tcgen05 fwd (x W^T), CTA-pair kernel", timeit(lambda: ops.gemm(a, b, out=out)), fl, M=M, N=N,
+               K=K)
         if small:
             continue
+        dense.set_pair_kernel(False)
+        report("gemm_bf16_tcgen05 fwd (x W^T), one-CTA kernel", timeit(lambda: ops.gemm(a, b, out=out)), fl, M=M, N=N,
+               K=K)
+        dense.set_pair_kernel(True)
         report("cublas bf16 (torch.matmul)", timeit(lambda: torch.matmul(a, b.t(), out=out)), fl, M=M, N=N, K=K)
         bt = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
         report("gemm_bf16_tcgen05 dgrad layout", timeit(lambda: ops.gemm(a, bt, out=out, b_mn=True)), fl, M=M, N=N, K=K)

@@ -239,6 +239,173 @@ __device__ __forceinline__ void ag_copier(const GemmParams& p, uint8_t* smem, ui
   tma_store_wait<0>();
 }
 
+// Epilogue of one output tile: this thread owns row `row` of the tile (TMEM lane) and sweeps the BN accumulator
+// columns starting at TMEM address `taddr` in chunks of 32.  Shared by the one-CTA and the CTA-pair kernels.
+template <int BN, int EPI>
+__device__ __forceinline__ void gemm_epilogue_tile(const GemmParams& p, const TileInfo& ti, uint32_t taddr, int row) {
+  const int n0 = ti.n0;
+  if constexpr (EPI == EPI_BF16_T || EPI == EPI_F32_T) {
+    // lane = output column (weight row), register = output row (token): 32 lanes store 32 neighbouring elements
+    float bv = 0.f;
+    if constexpr (EPI == EPI_BF16_T) {
+      if (p.bias && row < p.M) bv = __bfloat162float(p.bias[row]);
+    }
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col0 = n0 + c * 32;
+      if (col0 >= p.N) break;  // uniform over the CTA: the remaining columns are tokens that do not exist
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + c * 32, r);
+      tmem_ld_wait();
+      if (row < p.M) {
+        if constexpr (EPI == EPI_BF16_T) {
+          __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(p.C) + ti.c_off + row;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) cb[(long long)(col0 + i) * p.ldc] = __float2bfloat16(__uint_as_float(r[i]) + bv);
+        } else {
+          float* cf = reinterpret_cast<float*>(p.C) + ti.c_off + row;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) cf[(long long)(col0 + i) * p.ldc] = __uint_as_float(r[i]);
+        }
+      }
+    }
+  } else if constexpr (EPI == EPI_LMSTAT) {
+    // two sweeps over this thread's row of the tile in TMEM: row maximum, then the sums relative to it
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float sc2 = p.inv_temp * kLog2e;
+    const long long y = row < p.M ? p.labels[row] : -1;
+    float m2 = -INFINITY;  // maximum of z * log2(e)
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col0 = n0 + c * 32;
+      if (col0 >= p.N) break;
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) m2 = fmaxf(m2, __uint_as_float(r[i]) * sc2);
+    }
+    float ssum = 0.f, tsum = 0.f, zl = -INFINITY;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col0 = n0 + c * 32;
+      if (col0 >= p.N) break;
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + c * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        if (col0 + i < p.N) {
+          const float v = __uint_as_float(r[i]);
+          const float e = exp2f(v * sc2 - m2);
+          ssum += e;
+          tsum += e * (v * p.inv_temp);
+          if ((long long)(col0 + i) == y) zl = v * p.inv_temp;
+        }
+      }
+    }
+    if (row < p.M)
+      p.lm_partial[(long long)row * p.num_n_blocks + n0 / BN] = make_float4(m2 * (1.f / kLog2e), ssum, tsum, zl);
+  } else if constexpr (EPI == EPI_DLOGITS) {
+    // d z_j = g_logp * (1[j = y] - p_j) - g_H * p_j * (z_j - lse + H), times 1/temperature for d logits_j
+    const bool rv = row < p.M;
+    const long long y = rv ? p.labels[row] : -1;
+    const float l = rv ? p.lm_lse[row] : 0.f;
+    // y == -2: the target exists but in another rank's vocabulary slice (vocabulary-parallel LM head): the
+    // softmax term of its gradient still applies here, the one-hot term never matches
+    const float glp = (rv && ((y >= 0 && y < p.N) || y == -2)) ? p.lm_glogp[row] : 0.f;
+    const float ge = (rv && p.lm_gent) ? p.lm_gent[row] : 0.f;
+    const float H = (rv && p.lm_ent) ? p.lm_ent[row] : 0.f;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col0 = n0 + c * 32;
+      if (col0 >= p.N) break;
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + c * 32, r);
+      tmem_ld_wait();
+      if (rv) {
+        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (col0 + g * 8 + 8 <= p.N) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float x = __uint_as_float(r[g * 8 + i]) * p.inv_temp;
+              const float pj = __expf(x - l);
+              const float onehot = ((long long)(col0 + g * 8 + i) == y) ? 1.f : 0.f;
+              v[i] = (glp * (onehot - pj) - ge * pj * (x - l + H)) * p.inv_temp;
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]);
+            o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]);
+            o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(crow + g * 8) = o;
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    tmem_ld_32x32(taddr + c * 32, r);
+    tmem_ld_wait();
+    const int col0 = n0 + c * 32;
+    if (row < p.M && col0 < p.N) {
+      if constexpr (EPI == EPI_BF16) {
+        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + ti.c_off + (long long)row * p.ldc + col0;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (col0 + g * 8 + 8 <= p.N) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+            if (p.bias) {
+              uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col0 + g * 8);
+              const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                float2 f = __bfloat1622float2(b2[i]);
+                v[2 * i] += f.x;
+                v[2 * i + 1] += f.y;
+              }
+            }
+            uint4 o;
+            o.x = pack_bf16x2(v[0], v[1]);
+            o.y = pack_bf16x2(v[2], v[3]);
+            o.z = pack_bf16x2(v[4], v[5]);
+            o.w = pack_bf16x2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(crow + g * 8) = o;
+          }
+        }
+      } else {
+        float* crow = reinterpret_cast<float*>(p.C) + ti.c_off + (long long)row * p.ldc + col0;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          if (col0 + g * 4 + 4 <= p.N) {
+            float4 o = make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
+                                   __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
+            if constexpr (EPI == EPI_F32_ACC) {
+              const float4 old = *reinterpret_cast<const float4*>(crow + g * 4);
+              o.x += old.x;
+              o.y += old.y;
+              o.z += old.z;
+              o.w += old.w;
+            }
+            *reinterpret_cast<float4*>(crow + g * 4) = o;
+          }
+        }
+      }
+    }
+  }
+  }
+}
+
 #include "gemm_ar.cuh"
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
@@ -430,166 +597,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      if constexpr (EPI == EPI_BF16_T || EPI == EPI_F32_T) {
-        // lane = output column (weight row), register = output row (token): 32 lanes store 32 neighbouring elements
-        float bv = 0.f;
-        if constexpr (EPI == EPI_BF16_T) {
-          if (p.bias && row < p.M) bv = __bfloat162float(p.bias[row]);
-        }
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col0 = n0 + c * 32;
-          if (col0 >= p.N) break;  // uniform over the CTA: the remaining columns are tokens that do not exist
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          if (row < p.M) {
-            if constexpr (EPI == EPI_BF16_T) {
-              __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(p.C) + ti.c_off + row;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < p.N) cb[(long long)(col0 + i) * p.ldc] = __float2bfloat16(__uint_as_float(r[i]) + bv);
-            } else {
-              float* cf = reinterpret_cast<float*>(p.C) + ti.c_off + row;
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (col0 + i < p.N) cf[(long long)(col0 + i) * p.ldc] = __uint_as_float(r[i]);
-            }
-          }
-        }
-      } else if constexpr (EPI == EPI_LMSTAT) {
-        // two sweeps over this thread's row of the tile in TMEM: row maximum, then the sums relative to it
-        constexpr float kLog2e = 1.4426950408889634f;
-        const float sc2 = p.inv_temp * kLog2e;
-        const long long y = row < p.M ? p.labels[row] : -1;
-        float m2 = -INFINITY;  // maximum of z * log2(e)
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col0 = n0 + c * 32;
-          if (col0 >= p.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (col0 + i < p.N) m2 = fmaxf(m2, __uint_as_float(r[i]) * sc2);
-        }
-        float ssum = 0.f, tsum = 0.f, zl = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col0 = n0 + c * 32;
-          if (col0 >= p.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (col0 + i < p.N) {
-              const float v = __uint_as_float(r[i]);
-              const float e = exp2f(v * sc2 - m2);
-              ssum += e;
-              tsum += e * (v * p.inv_temp);
-              if ((long long)(col0 + i) == y) zl = v * p.inv_temp;
-            }
-          }
-        }
-        if (row < p.M)
-          p.lm_partial[(long long)row * p.num_n_blocks + n0 / BN] = make_float4(m2 * (1.f / kLog2e), ssum, tsum, zl);
-      } else if constexpr (EPI == EPI_DLOGITS) {
-        // d z_j = g_logp * (1[j = y] - p_j) - g_H * p_j * (z_j - lse + H), times 1/temperature for d logits_j
-        const bool rv = row < p.M;
-        const long long y = rv ? p.labels[row] : -1;
-        const float l = rv ? p.lm_lse[row] : 0.f;
-        // y == -2: the target exists but in another rank's vocabulary slice (vocabulary-parallel LM head): the
-        // softmax term of its gradient still applies here, the one-hot term never matches
-        const float glp = (rv && ((y >= 0 && y < p.N) || y == -2)) ? p.lm_glogp[row] : 0.f;
-        const float ge = (rv && p.lm_gent) ? p.lm_gent[row] : 0.f;
-        const float H = (rv && p.lm_ent) ? p.lm_ent[row] : 0.f;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col0 = n0 + c * 32;
-          if (col0 >= p.N) break;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          if (rv) {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (col0 + g * 8 + 8 <= p.N) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float x = __uint_as_float(r[g * 8 + i]) * p.inv_temp;
-                  const float pj = __expf(x - l);
-                  const float onehot = ((long long)(col0 + g * 8 + i) == y) ? 1.f : 0.f;
-                  v[i] = (glp * (onehot - pj) - ge * pj * (x - l + H)) * p.inv_temp;
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[0], v[1]);
-                o.y = pack_bf16x2(v[2], v[3]);
-                o.z = pack_bf16x2(v[4], v[5]);
-                o.w = pack_bf16x2(v[6], v[7]);
-                *reinterpret_cast<uint4*>(crow + g * 8) = o;
-              }
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-          if constexpr (EPI == EPI_BF16) {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + ti.c_off + (long long)row * p.ldc + col0;
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (col0 + g * 8 + 8 <= p.N) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-                if (p.bias) {
-                  uint4 bv = *reinterpret_cast<const uint4*>(p.bias + col0 + g * 8);
-                  const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&bv);
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    float2 f = __bfloat1622float2(b2[i]);
-                    v[2 * i] += f.x;
-                    v[2 * i + 1] += f.y;
-                  }
-                }
-                uint4 o;
-                o.x = pack_bf16x2(v[0], v[1]);
-                o.y = pack_bf16x2(v[2], v[3]);
-                o.z = pack_bf16x2(v[4], v[5]);
-                o.w = pack_bf16x2(v[6], v[7]);
-                *reinterpret_cast<uint4*>(crow + g * 8) = o;
-              }
-            }
-          } else {
-            float* crow = reinterpret_cast<float*>(p.C) + ti.c_off + (long long)row * p.ldc + col0;
-#pragma unroll
-            for (int g = 0; g < 8; ++g) {
-              if (col0 + g * 4 + 4 <= p.N) {
-                float4 o = make_float4(__uint_as_float(r[g * 4]), __uint_as_float(r[g * 4 + 1]),
-                                       __uint_as_float(r[g * 4 + 2]), __uint_as_float(r[g * 4 + 3]));
-                if constexpr (EPI == EPI_F32_ACC) {
-                  const float4 old = *reinterpret_cast<const float4*>(crow + g * 4);
-                  o.x += old.x;
-                  o.y += old.y;
-                  o.z += old.z;
-                  o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(crow + g * 4) = o;
-              }
-            }
-          }
-        }
-      }
-      }
+      gemm_epilogue_tile<BN, EPI>(p, ti, taddr, row);
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
       if (++acc == 2) {
@@ -640,6 +648,272 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     }
   }
+}
+
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair variant: clusters of two CTAs share one 256 x 256 output tile through tcgen05 cta_group::2.
+// Each CTA stages its own 128 rows of A and its own 128 of the tile's 256 B rows (its TMA loads count on the leader's
+// mbarrier; nothing is broadcast between the CTAs), the leader's MMA thread issues one 256 x 256 x 16 instruction per
+// k-step that reads both CTAs' shared memory, and each CTA's TMEM receives the accumulator rows of its own 128 A
+// rows.  Per SM and k-block this moves 32 KB through shared memory for 2 x 128 x 256 x 64 multiply-adds where the
+// one-CTA kernel moves 48 KB, and the freed shared memory makes the pipeline six stages deep instead of four.
+// Tiles are (k-split, m-pair-block, n-block); split-K writes fp32 slabs like the one-CTA kernel.
+// ---------------------------------------------------------------------------------------
+constexpr int kPairBN = 256;
+constexpr int kPairStages = 6;
+constexpr int kPairHalfBytes = 128 * kBK * 2;            // one operand half of one stage: 16 KB
+constexpr int kPairStageBytes = 2 * kPairHalfBytes;      // A half + B half per CTA
+constexpr int kPairBarrierOffset = kPairStages * kPairStageBytes;
+constexpr int kPairSmemBytes = kPairBarrierOffset + (2 * kPairStages + 4) * 8 + 16 + 1024;
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kPairBarrierOffset);   // used in the leader CTA only
+  uint64_t* empty_bar = full_bar + kPairStages;                                  // one copy per CTA
+  uint64_t* tmem_full = empty_bar + kPairStages;                                 // one copy per CTA
+  uint64_t* tmem_empty = tmem_full + 2;                                          // used in the leader CTA only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = (int)blockIdx.x >> 1;
+  const int npairs = (int)gridDim.x >> 1;
+  const int num_m2 = (p.M + 255) / 256;
+  const int num_n = (p.N + kPairBN - 1) / kPairBN;
+  const int tiles_mn = num_m2 * num_n;
+  const int num_tiles = tiles_mn * p.k_splits;
+  constexpr uint32_t kTmemCols = 2 * kPairBN;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 256);  // the epilogue threads of both CTAs
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // the partner's barriers are initialised before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_of = [&](int tile, int& m0, int& n0, int& kb0, int& kb1, long long& c_off) {
+    const int ks = tile / tiles_mn;
+    int mb, nb;
+    tile_coords(tile - ks * tiles_mn, num_m2, num_n, mb, nb, 4);
+    m0 = mb * 256;
+    n0 = nb * kPairBN;
+    kb0 = ks * p.kb_per_split;
+    kb1 = min(kb0 + p.kb_per_split, p.num_k_blocks);
+    c_off = ks * p.slab_stride;
+  };
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int armed = 0;  // stages this CTA has ever issued loads into (for the abort path)
+      for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+        int m0, n0, kb0, kb1;
+        long long c_off;
+        tile_of(tile, m0, n0, kb0, kb1, c_off);
+        const int my_m0 = m0 + (int)rank * 128;   // this CTA's 128 rows of A
+        const int my_n0 = n0 + (int)rank * 128;   // this CTA's 128 of the tile's 256 B rows
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, p.status, kStatusTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * kPairStageBytes;
+          uint8_t* sb_ = sa + kPairHalfBytes;
+          const uint32_t bar = mapa_shared(smem_u32(&full_bar[stage]), 0);  // the leader's barrier counts all bytes
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * kPairStageBytes);
+          const int k0 = kb * kBK;
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(sa, &map_a, bar, k0, my_m0);
+          } else {
+            tma_load_2d_pair(sa, &map_a, bar, my_m0, k0);
+            tma_load_2d_pair(sa + 8192, &map_a, bar, my_m0 + 64, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(sb_, &map_b, bar, k0, my_n0);
+          } else {
+            tma_load_2d_pair(sb_, &map_b, bar, my_n0, k0);
+            tma_load_2d_pair(sb_ + 8192, &map_b, bar, my_n0 + 64, k0);
+          }
+          if (armed < kPairStages) ++armed;
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      (void)armed;
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(256, kPairBN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      // cluster addresses of the barriers this thread signals in both CTAs
+      for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
+        int m0, n0, kb0, kb1;
+        long long c_off;
+        tile_of(tile, m0, n0, kb0, kb1, c_off);
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, p.status, kStatusTimeoutMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * kPairBN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, p.status, kStatusTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sa = smem_u32(smem + stage * kPairStageBytes);
+            const uint32_t sb_ = sa + kPairHalfBytes;
+#pragma unroll
+            for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+              const uint64_t da = A_MN ? umma_smem_desc(sa + kk * 2048, 8192, 1024)
+                                       : umma_smem_desc(sa + kk * 32, 16, 1024);
+              const uint64_t db = B_MN ? umma_smem_desc(sb_ + kk * 2048, 8192, 1024)
+                                       : umma_smem_desc(sb_ + kk * 32, 16, 1024);
+              umma_bf16_ss_pair(tmem_d, da, db, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+            }
+            // free the stage in both CTAs once these MMAs have read it
+            const uint32_t eb = smem_u32(&empty_bar[stage]);
+            umma_commit_pair(mapa_shared(eb, 0));
+            umma_commit_pair(mapa_shared(eb, 1));
+          }
+          __syncwarp();
+          if (++stage == kPairStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok && lane == 0) {
+          const uint32_t fb = smem_u32(&tmem_full[acc]);
+          umma_commit_pair(mapa_shared(fb, 0));
+          umma_commit_pair(mapa_shared(fb, 1));
+        }
+        __syncwarp();
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (warps 2..5 of both CTAs) ------------------------------
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = pair; tile < num_tiles; tile += npairs) {
+      TileInfo ti;
+      tile_of(tile, ti.m0, ti.n0, ti.kb0, ti.kb1, ti.c_off);
+      ti.m0 += (int)rank * 128;
+      ti.b_off = 0;
+      ti.skip = false;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, p.status, kStatusTimeoutEpilogue)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kPairBN;
+      gemm_epilogue_tile<kPairBN, EPI>(p, ti, taddr, ti.m0 + row_in_tile);
+      tc_fence_before();
+      mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[acc]), 0));  // the accumulator is free: tell the leader
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();  // neither CTA releases shared memory or TMEM while the other may still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+static bool g_pair_enabled = true;
+static int g_pair_max_clusters[8] = {0};
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, cudaStream_t stream) {
+  auto kernel = gemm_bf16_pair_kernel<A_MN, B_MN, EPI>;
+  static bool configured = false;
+  static int max_clusters = 0;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * num_sms(), 1, 1);
+    cfg.blockDim = dim3(192, 1, 1);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaOccupancyMaxActiveClusters(&max_clusters, kernel, &cfg);
+    if (e != cudaSuccess || max_clusters < 1) {
+      cudaGetLastError();
+      max_clusters = num_sms() / 2;
+    }
+    configured = true;
+  }
+  const int tiles = ((p.M + 255) / 256) * ((p.N + kPairBN - 1) / kPairBN) * p.k_splits;
+  const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  kernel<<<2 * clusters, 192, kPairSmemBytes, stream>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+static int dispatch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int a_mn, int b_mn, int epi,
+                         cudaStream_t stream) {
+#define SB_PAIR(AM, BM_, E)                  \
+  if (a_mn == AM && b_mn == BM_ && epi == E) \
+    return launch_pair<AM != 0, BM_ != 0, E>(ma, mb, p, stream);
+  SB_PAIR(0, 0, EPI_BF16)
+  SB_PAIR(0, 1, EPI_BF16)
+  SB_PAIR(1, 1, EPI_F32_ACC)
+  SB_PAIR(1, 1, EPI_F32)
+  SB_PAIR(0, 0, EPI_F32)
+  SB_PAIR(0, 0, EPI_BF16_T)
+  SB_PAIR(0, 0, EPI_F32_T)
+  SB_PAIR(0, 0, EPI_LMSTAT)
+  SB_PAIR(0, 0, EPI_DLOGITS)
+#undef SB_PAIR
+  return -2;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -890,8 +1164,30 @@ static int gemm_impl(const void* A, const void* B, void* C, const void* bias, in
   p.k_splits = (p.num_k_blocks + p.kb_per_split - 1) / p.kb_per_split;
   if (grp && grp->group_rows) p.k_splits = grp->num_groups;
   p.slab_stride = slab_stride;
+  // one 256 x 256 tile per CTA pair: worth it when the output has at least two 128-row blocks and the caller did
+  // not pin the tile width or the grid (tensor-parallel all-reduce, all-gather and grouped modes keep the one-CTA kernel)
+  const bool pair_ok = !grp && !ag && !ar && epi != EPI_F32_AR && M > 128 && N >= 128 && tile_n != 128 && max_ctas == 0;
+  if (g_pair_enabled && pair_ok) {
+    // CTA-pair kernel: its operand boxes are 128 rows wide whatever the one-CTA kernel would have chosen
+    CUtensorMap pa, pb;
+    if (!a_mn) r = make_tensor_map_bf16_2d(&pa, A, K, M, lda, kBK, 128);
+    else r = make_tensor_map_bf16_2d(&pa, A, M, K, lda, 64, kBK);
+    if (r) return r;
+    if (!b_mn) r = make_tensor_map_bf16_2d(&pb, B, K, N, ldb, kBK, 128);
+    else r = make_tensor_map_bf16_2d(&pb, B, N, K, ldb, 64, kBK);
+    if (r) return r;
+    const int rc = dispatch_pair(pa, pb, p, a_mn, b_mn, epi, stream);
+    if (rc != -2) return rc;
+  }
   if (BN == 256) return dispatch_gemm<256, 4>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
   return dispatch_gemm<128, 6>(ma, mb, p, a_mn, b_mn, epi, max_ctas, stream);
+}
+
+// 0 routes every GEMM through the one-CTA kernel (benchmarks compare the two; a fallback switch)
+extern "C" int sb_gemm_set_pair_kernel(int enabled) {
+  const int old = g_pair_enabled ? 1 : 0;
+  g_pair_enabled = enabled != 0;
+  return old;
 }
 
 extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,

@@ -66,6 +66,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, *
     return out
 
 
+def set_pair_kernel(enabled: bool) -> bool:
+    """Route GEMMs with at least two 128-row blocks through the CTA-pair kernel (``cta_group::2``: two SMs share one
+    256 x 256 tile) or, when off, through the one-CTA kernel.  Returns the previous setting (benchmarks time both)."""
+    return bool(_lib.get_lib().sb_gemm_set_pair_kernel(int(bool(enabled))))
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):

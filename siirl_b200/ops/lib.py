@@ -20,7 +20,7 @@ _status_words: dict[int, torch.Tensor] = {}
 
 # kernels launched by one call of each entry point (for the launch counter of the benchmark)
 _KERNELS_PER_CALL = {"sb_rmsnorm_bwd": 2, "sb_grpo_group_adv": 4, "sb_fmha_bwd": 3, "sb_kk_partition": 0,
-                     "sb_rmsnorm_bwd_blocks": 0}
+                     "sb_rmsnorm_bwd_blocks": 0, "sb_gemm_set_pair_kernel": 0}
 
 
 class _CountingLib:
