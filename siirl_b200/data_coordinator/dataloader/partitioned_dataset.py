@@ -138,12 +138,12 @@ class PartitionedRLHFDataset(Dataset):
         """Image processor of the policy's vision tower (built on first use from the model configuration)."""
         if self._vl is None:
             from ...models.config import get_config
-            from ...models.vision_processor import VLProcessor
+            from ...models.vision_processor import make_vl_processor
             m = self._full_config.actor_rollout_ref.model
             mcfg = get_config(m.arch_preset or m.path, dict(m.override_config or {}))
-            if mcfg.vision is None:
+            if mcfg.vision is None and mcfg.vit is None:
                 raise ValueError("the dataset has images but the model has no vision tower")
-            self._vl = VLProcessor(mcfg, m.image_min_pixels, m.image_max_pixels)
+            self._vl = make_vl_processor(mcfg, m.image_min_pixels, m.image_max_pixels)
         return self._vl
 
     def __getitem__(self, idx: int) -> Dict[str, Any]:

@@ -184,9 +184,9 @@ class _ModelWorkerBase:
 
     def _vl_processor(self):
         if getattr(self, "_vlp", None) is None:
-            from ..models.vision_processor import VLProcessor
-            self._vlp = VLProcessor(self.model_config, self.config.model.image_min_pixels,
-                                    self.config.model.image_max_pixels)
+            from ..models.vision_processor import make_vl_processor
+            self._vlp = make_vl_processor(self.model_config, self.config.model.image_min_pixels,
+                                          self.config.model.image_max_pixels)
         return self._vlp
 
     def _train_tp_size(self) -> int:

@@ -29,6 +29,33 @@ class VisionConfig:
 
 
 @dataclass
+class ViTConfig:
+    image_size: int = 448
+    patch_size: int = 14
+    hidden_size: int = 1024
+    num_heads: int = 16
+    intermediate_size: int = 4096
+    depth: int = 24
+    in_channels: int = 3
+    class_token: bool = True
+    num_register_tokens: int = 0        # DINOv2 "reg4" models
+    layer_scale: bool = True            # learnable per-channel scale on both residual branches
+    norm_type: str = "layer_norm"       # or "rms_norm" (InternViT-6B)
+    qkv_bias: bool = True
+    norm_eps: float = 1e-6
+    final_norm: bool = False            # timm ViTs end in a LayerNorm; InternVL reads the raw last layer
+    select_layer: int = -1              # hidden state handed on: -1 last layer, -2 the one before (Prismatic)
+
+    @property
+    def num_patches(self) -> int:
+        return (self.image_size // self.patch_size) ** 2
+
+    @property
+    def num_prefix_tokens(self) -> int:
+        return (1 if self.class_token else 0) + self.num_register_tokens
+
+
+@dataclass
 class DecoderConfig:
     model_type: str = "qwen2"
     vocab_size: int = 1024
@@ -64,6 +91,13 @@ class DecoderConfig:
     # value head (critic / reward model): one scalar per token instead of the vocabulary head
     value_head: bool = False
     vision: Optional[VisionConfig] = None
+    # InternVL family: a plain ViT tower whose 2x2 pixel-shuffled patches pass an MLP projector; ``hf_naming`` picks
+    # the checkpoint's parameter names ("hf": transformers' own classes, "internvl_chat": the upstream remote-code
+    # layout with ``vision_model / mlp1 / language_model``, whose language model may be InternLM2 with fused ``wqkv``)
+    vit: Optional[ViTConfig] = None
+    downsample_ratio: float = 0.5
+    hf_naming: str = "hf"
+    llm_type: str = ""
     image_token_id: int = 151655
     eos_token_id: int = 2
     pad_token_id: int = 0
@@ -106,8 +140,10 @@ class DecoderConfig:
     # ---- HF interchange -----------------------------------------------------------------------
     @classmethod
     def from_hf_config(cls, cfg: Dict[str, Any]) -> "DecoderConfig":
-        text = cfg.get("text_config", cfg)
+        text = cfg.get("text_config") or cfg.get("llm_config") or cfg
         mt = cfg.get("model_type", "qwen2")
+        if mt in ("internvl", "internvl_chat"):
+            return cls._from_internvl_config(cfg)
         nh = text["num_attention_heads"]
         hd = text.get("head_dim") or text["hidden_size"] // nh
         rope_scaling = text.get("rope_scaling") or cfg.get("rope_scaling") or {}
@@ -156,6 +192,40 @@ class DecoderConfig:
         return out
 
     @classmethod
+    def _from_internvl_config(cls, cfg: Dict[str, Any]) -> "DecoderConfig":
+        """``internvl`` (transformers' classes: ``text_config`` + ``vision_config`` with list-valued sizes) and
+        ``internvl_chat`` (upstream remote code: ``llm_config`` + ``vision_config``; the language model is InternLM2,
+        Qwen2 or Llama)."""
+        native = cfg.get("model_type") == "internvl"
+        text = dict(cfg.get("text_config") or cfg.get("llm_config") or {})
+        llm_type = text.get("model_type", "qwen2")
+        base = dict(text)
+        base["model_type"] = "qwen2" if llm_type == "qwen2" else "llama"
+        if llm_type == "internlm2":
+            base["attention_bias"] = bool(text.get("bias", False))
+        out = cls.from_hf_config(base)
+        out.model_type = "internvl" if native else "internvl_chat"
+        out.llm_type = llm_type
+        out.hf_naming = "hf" if native else "internvl_chat"
+        out.tie_word_embeddings = bool(text.get("tie_word_embeddings", False))
+        vc = cfg.get("vision_config", {})
+
+        def one(v, default):
+            v = vc.get(v, default)
+            return int(v[0]) if isinstance(v, (list, tuple)) else int(v)
+        out.vit = ViTConfig(
+            image_size=one("image_size", 448), patch_size=one("patch_size", 14), hidden_size=vc.get("hidden_size", 1024),
+            num_heads=vc.get("num_attention_heads", 16), intermediate_size=vc.get("intermediate_size", 4096),
+            depth=vc.get("num_hidden_layers", 24), class_token=True, layer_scale=True,
+            norm_type=vc.get("norm_type", "layer_norm"),
+            qkv_bias=bool(vc.get("attention_bias", False) if native else vc.get("qkv_bias", True)),
+            norm_eps=float(vc.get("layer_norm_eps", 1e-6)), final_norm=False,
+            select_layer=int(cfg.get("vision_feature_layer", cfg.get("select_layer", -1))))
+        out.downsample_ratio = float(cfg.get("downsample_ratio", 0.5))
+        out.image_token_id = int(cfg.get("image_token_id", cfg.get("img_context_token_id", 151667)))
+        return out
+
+    @classmethod
     def from_pretrained(cls, path: str) -> "DecoderConfig":
         with open(os.path.join(os.path.expanduser(path), "config.json")) as f:
             return cls.from_hf_config(json.load(f))
@@ -184,6 +254,26 @@ class DecoderConfig:
                 d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
         if self.mrope_section:
             d["rope_scaling"] = {"type": "mrope", "mrope_section": self.mrope_section}
+        if self.vit is not None:
+            v = self.vit
+            text = dict(d, model_type=self.llm_type or "qwen2")
+            text.pop("architectures", None)
+            vision = {"hidden_size": v.hidden_size, "num_hidden_layers": v.depth, "num_attention_heads": v.num_heads,
+                      "intermediate_size": v.intermediate_size, "norm_type": v.norm_type, "layer_norm_eps": v.norm_eps}
+            if self.hf_naming == "hf":
+                vision.update(image_size=[v.image_size] * 2, patch_size=[v.patch_size] * 2, attention_bias=v.qkv_bias,
+                              model_type="internvl_vision")
+                return {"architectures": ["InternVLForConditionalGeneration"], "model_type": "internvl",
+                        "text_config": text, "vision_config": vision, "image_token_id": self.image_token_id,
+                        "downsample_ratio": self.downsample_ratio, "vision_feature_layer": v.select_layer,
+                        "tie_word_embeddings": self.tie_word_embeddings, "torch_dtype": "bfloat16"}
+            vision.update(image_size=v.image_size, patch_size=v.patch_size, qkv_bias=v.qkv_bias)
+            if self.llm_type == "internlm2":
+                text["bias"] = self.qkv_bias
+            return {"architectures": ["InternVLChatModel"], "model_type": "internvl_chat", "llm_config": text,
+                    "vision_config": vision, "img_context_token_id": self.image_token_id,
+                    "downsample_ratio": self.downsample_ratio, "select_layer": v.select_layer,
+                    "torch_dtype": "bfloat16"}
         return d
 
 
@@ -233,6 +323,22 @@ PRESETS: Dict[str, DecoderConfig] = {
                              vision=VisionConfig(depth=2, hidden_size=64, num_heads=4, intermediate_size=128,
                                                  patch_size=14, window_size=56, fullatt_block_indexes=[1],
                                                  out_hidden_size=128), image_token_id=1000),
+    # InternVL2.5-8B: InternViT-300M-448px + InternLM2.5-7B
+    "internvl2.5-8b": DecoderConfig(model_type="internvl_chat", llm_type="internlm2", hf_naming="internvl_chat",
+                                    vocab_size=92553, hidden_size=4096, intermediate_size=14336, num_layers=32,
+                                    num_heads=32, num_kv_heads=8, head_dim=128, rope_theta=1e6, qkv_bias=False,
+                                    rms_norm_eps=1e-5, vit=ViTConfig(), image_token_id=92546, eos_token_id=92542,
+                                    pad_token_id=2),
+    # InternVL3-8B in transformers' layout: InternViT-300M + Qwen2.5-7B
+    "internvl3-8b": DecoderConfig(model_type="internvl", llm_type="qwen2", vocab_size=151674, hidden_size=3584,
+                                  intermediate_size=18944, num_layers=28, num_heads=28, num_kv_heads=4, head_dim=128,
+                                  rope_theta=1e6, vit=ViTConfig(), image_token_id=151667, eos_token_id=151645,
+                                  pad_token_id=151643),
+    "tiny-internvl": DecoderConfig(model_type="internvl", llm_type="qwen2", vocab_size=1024, hidden_size=128,
+                                   intermediate_size=352, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32,
+                                   vit=ViTConfig(image_size=56, patch_size=14, hidden_size=64, num_heads=2,
+                                                 intermediate_size=128, depth=2, qkv_bias=False),
+                                   image_token_id=1000),
     "tiny-vl-gpu": DecoderConfig(model_type="qwen2_5_vl", vocab_size=2048, hidden_size=256, intermediate_size=512,
                                  num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64, mrope_section=[8, 12, 12],
                                  vision=VisionConfig(depth=2, hidden_size=128, num_heads=2, intermediate_size=256,

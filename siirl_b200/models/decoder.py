@@ -107,6 +107,8 @@ class DecoderLayer(nn.Module):
         cfg = self.cfg
         qkv = self.qkv_pre_rope(x)
         cos, sin = rope
+        if cfg.mrope_section is None and positions.dim() == 2:
+            positions = positions[0]            # three equal rows from a multimodal processor of a 1-D rope family
         return ops.rope(qkv, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, positions, cos, sin, cfg.mrope_section)
 
     def qkv_pre_rope(self, x: torch.Tensor) -> torch.Tensor:
@@ -204,6 +206,9 @@ class DecoderLM(nn.Module):
         if cfg.vision is not None:
             from .vision import VisionTower
             self.vision = VisionTower(cfg.vision, dtype, device, gen)
+        elif cfg.vit is not None:
+            from .internvl import InternVLVision
+            self.vision = InternVLVision(cfg.vit, cfg.hidden_size, cfg.downsample_ratio, dtype, device, gen)
 
     # ---- helpers ------------------------------------------------------------------------------
     def rope_tables(self, device, min_len: int = 0):
@@ -425,6 +430,8 @@ class DecoderLM(nn.Module):
         h = self.embed(input_ids, pixel_values, image_grid_thw)
         delta = None
         pos32 = positions.to(torch.int32).contiguous()
+        if cfg.mrope_section is None and rp.dim() == 2:
+            rp = rp[0]
         rp32 = rp.to(torch.int32).contiguous()
         for li, layer in enumerate(self.layers):
             x, h = ops.rmsnorm(delta if delta is not None else h, layer.input_layernorm, cfg.rms_norm_eps,

@@ -27,7 +27,8 @@ def _moe_names(cfg: DecoderConfig) -> Dict[str, str]:
             "up": "up_proj", "down": "down_proj"}
 
 
-def to_hf_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
+def _decoder_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Language-model parameters under transformers' causal-LM names (``model.layers.N...``, ``lm_head.weight``)."""
     cfg: DecoderConfig = model.cfg
     qw, kw = cfg.q_width, cfg.kv_width
     yield "model.embed_tokens.weight", model.embed_tokens.data
@@ -78,6 +79,147 @@ def to_hf_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
         yield "score.weight", model.value_head.data
 
 
+# ---- family-specific names ----------------------------------------------------------------------------------------
+def _llm_names(cfg: DecoderConfig) -> Tuple[str, str]:
+    """(prefix replacing ``model.``, name of the vocabulary head) of the language model inside a checkpoint."""
+    if cfg.vit is not None and cfg.hf_naming == "internvl_chat":
+        return "language_model.model.", ("language_model.output.weight" if cfg.llm_type == "internlm2"
+                                         else "language_model.lm_head.weight")
+    if cfg.vit is not None or cfg.vision is not None:
+        return "model.language_model.", "lm_head.weight"
+    return "model.", "lm_head.weight"
+
+
+_INTERNLM2 = {"self_attn.o_proj": "attention.wo", "mlp.gate_proj": "feed_forward.w1", "mlp.up_proj": "feed_forward.w3",
+              "mlp.down_proj": "feed_forward.w2", "input_layernorm": "attention_norm",
+              "post_attention_layernorm": "ffn_norm", "embed_tokens": "tok_embeddings"}
+
+
+def _fuse_wqkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cfg: DecoderConfig) -> torch.Tensor:
+    """InternLM2's ``wqkv``: per KV head, its group of query heads, then the key head, then the value head."""
+    hkv, g, d = cfg.num_kv_heads, cfg.num_heads // cfg.num_kv_heads, cfg.head_dim
+    tail = q.shape[1:]
+    return torch.cat([q.reshape(hkv, g, d, *tail), k.reshape(hkv, 1, d, *tail), v.reshape(hkv, 1, d, *tail)],
+                     1).reshape((g + 2) * hkv * d, *tail)
+
+
+def _split_wqkv(w: torch.Tensor, cfg: DecoderConfig) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    hkv, g, d = cfg.num_kv_heads, cfg.num_heads // cfg.num_kv_heads, cfg.head_dim
+    tail = w.shape[1:]
+    w = w.reshape(hkv, g + 2, d, *tail)
+    return (w[:, :g].reshape(hkv * g * d, *tail), w[:, g].reshape(hkv * d, *tail), w[:, g + 1].reshape(hkv * d, *tail))
+
+
+def _vit_state(vision, names: str) -> Iterator[Tuple[str, torch.Tensor]]:
+    """InternVL tower + projector; ``names``: "hf" (transformers' classes) or "internvl_chat" (upstream layout)."""
+    enc, proj = vision.encoder, vision.projector
+    vc = enc.cfg
+    H, P = vc.hidden_size, vc.patch_size
+    conv = enc.patch_embed_weight.data[:, :enc.patch_dim].unflatten(1, (vc.in_channels, P, P))      # a view
+    hf = names == "hf"
+    e = "model.vision_tower.embeddings." if hf else "vision_model.embeddings."
+    yield e + ("cls_token" if hf else "class_embedding"), enc.prefix_tokens.data[:1].reshape(1, 1, H)
+    yield e + ("position_embeddings" if hf else "position_embedding"), enc.position_embedding.data[None]
+    yield e + ("patch_embeddings.projection.weight" if hf else "patch_embedding.weight"), conv
+    yield e + ("patch_embeddings.projection.bias" if hf else "patch_embedding.bias"), enc.patch_embed_bias.data
+    for i, b in enumerate(enc.blocks):
+        p = f"model.vision_tower.encoder.layer.{i}." if hf else f"vision_model.encoder.layers.{i}."
+        if hf:
+            for j, x in enumerate("qkv"):
+                yield p + f"attention.{x}_proj.weight", b.qkv_weight.data[j * H:(j + 1) * H]
+                if b.qkv_bias is not None:
+                    yield p + f"attention.{x}_proj.bias", b.qkv_bias.data[j * H:(j + 1) * H]
+        else:
+            yield p + "attn.qkv.weight", b.qkv_weight.data
+            if b.qkv_bias is not None:
+                yield p + "attn.qkv.bias", b.qkv_bias.data
+        a = "attention.projection_layer." if hf else "attn.proj."
+        yield p + a + "weight", b.proj_weight.data
+        yield p + a + "bias", b.proj_bias.data
+        for fc in ("fc1", "fc2"):
+            yield p + f"mlp.{fc}.weight", getattr(b, fc + "_weight").data
+            yield p + f"mlp.{fc}.bias", getattr(b, fc + "_bias").data
+        for ours, theirs in (("norm1", "layernorm_before" if hf else "norm1"), ("norm2", "layernorm_after" if hf else "norm2")):
+            yield p + theirs + ".weight", getattr(b, ours + "_weight").data
+            if getattr(b, ours + "_bias") is not None:
+                yield p + theirs + ".bias", getattr(b, ours + "_bias").data
+        if vc.layer_scale:
+            yield p + ("lambda_1" if hf else "ls1"), b.ls1.data
+            yield p + ("lambda_2" if hf else "ls2"), b.ls2.data
+    m = ["model.multi_modal_projector.layer_norm.", "model.multi_modal_projector.linear_1.",
+         "model.multi_modal_projector.linear_2."] if hf else ["mlp1.0.", "mlp1.1.", "mlp1.3."]
+    yield m[0] + "weight", proj.norm_weight.data
+    yield m[0] + "bias", proj.norm_bias.data
+    yield m[1] + "weight", proj.fc0_weight.data
+    yield m[1] + "bias", proj.fc0_bias.data
+    yield m[2] + "weight", proj.fc1_weight.data
+    yield m[2] + "bias", proj.fc1_bias.data
+
+
+def _qwen_visual_state(vision, prefix: str = "model.visual.") -> Iterator[Tuple[str, torch.Tensor]]:
+    """Qwen2.5-VL tower under transformers' names (``visual.patch_embed.proj``: a 3-D convolution weight)."""
+    vc = vision.cfg
+    H, I = vc.hidden_size, vc.intermediate_size
+    yield prefix + "patch_embed.proj.weight", vision.patch_embed_weight.data[:, :vision.patch_dim].unflatten(
+        1, (vc.in_channels, vc.temporal_patch_size, vc.patch_size, vc.patch_size))
+    for i, b in enumerate(vision.blocks):
+        p = prefix + f"blocks.{i}."
+        yield p + "norm1.weight", b.norm1.data
+        yield p + "norm2.weight", b.norm2.data
+        yield p + "attn.qkv.weight", b.qkv_weight.data
+        yield p + "attn.qkv.bias", b.qkv_bias.data
+        yield p + "attn.proj.weight", b.proj_weight.data
+        yield p + "attn.proj.bias", b.proj_bias.data
+        yield p + "mlp.gate_proj.weight", b.gate_up_weight.data[:I]
+        yield p + "mlp.gate_proj.bias", b.gate_up_bias.data[:I]
+        yield p + "mlp.up_proj.weight", b.gate_up_weight.data[I:]
+        yield p + "mlp.up_proj.bias", b.gate_up_bias.data[I:]
+        yield p + "mlp.down_proj.weight", b.down_weight.data
+        yield p + "mlp.down_proj.bias", b.down_bias.data
+    yield prefix + "merger.ln_q.weight", vision.merger_norm.data
+    yield prefix + "merger.mlp.0.weight", vision.merger_fc1_weight.data
+    yield prefix + "merger.mlp.0.bias", vision.merger_fc1_bias.data
+    yield prefix + "merger.mlp.2.weight", vision.merger_fc2_weight.data
+    yield prefix + "merger.mlp.2.bias", vision.merger_fc2_bias.data
+
+
+def _hf_targets(model) -> Iterator[Tuple[str, object]]:
+    """(checkpoint name, view into the model's parameter) for every tensor of the family's HF checkpoint; InternLM2's
+    fused ``wqkv`` comes as the tuple of its three views."""
+    cfg: DecoderConfig = model.cfg
+    prefix, head = _llm_names(cfg)
+    internlm2 = cfg.vit is not None and cfg.hf_naming == "internvl_chat" and cfg.llm_type == "internlm2"
+    held: Dict[str, torch.Tensor] = {}
+    for name, t in _decoder_state(model):
+        if name == "lm_head.weight":
+            yield head, t
+            continue
+        if name.startswith("model."):
+            name = prefix + name[len("model."):]
+        if internlm2:
+            if ".self_attn." in name and name.split(".")[-2] in ("q_proj", "k_proj", "v_proj"):
+                held[name.split(".")[-2][0]] = t
+                if len(held) == 3:
+                    yield name[: name.index("self_attn.")] + "attention.wqkv." + name.split(".")[-1], (
+                        held["q"], held["k"], held["v"])
+                    held = {}
+                continue
+            for ours, theirs in _INTERNLM2.items():
+                name = name.replace(ours, theirs)
+        yield name, t
+    vision = getattr(model, "vision", None)
+    if vision is not None and cfg.vit is not None:
+        yield from _vit_state(vision, cfg.hf_naming)
+    elif vision is not None:
+        yield from _qwen_visual_state(vision)
+
+
+def to_hf_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
+    """Every parameter under the names of the family's HF checkpoint (language model, then the vision tower)."""
+    for name, t in _hf_targets(model):
+        yield name, (_fuse_wqkv(*t, model.cfg) if isinstance(t, tuple) else t)
+
+
 def save_hf_model(model, out_dir: str, max_shard_bytes: int = 4 << 30, tokenizer=None, tensors=None) -> None:
     """Write ``config.json`` + sharded ``model-xxxxx-of-yyyyy.safetensors`` + index.  ``tensors``: a snapshot of
     ``to_hf_state(model)`` taken earlier (asynchronous saves export the weights as they were at the snapshot)."""
@@ -125,59 +267,46 @@ def _open_all(path: str):
     return [safe_open(os.path.join(path, f), framework="pt", device="cpu") for f in files]
 
 
+_ALIASES = (("model.language_model.", "model."), ("model.language_model.", "language_model.model."),
+            ("model.visual.", "visual."), ("model.vision_tower.", "vision_tower."),
+            ("model.multi_modal_projector.", "multi_modal_projector."), ("model.", "model.language_model."))
+
+
 def load_hf_weights(model, path: str, strict: bool = True) -> None:
-    """Fill a :class:`DecoderLM` from an HF safetensors directory (every rank reads the files it needs itself —
-    no rank-0 broadcast as in siirl/utils/model_utils/fsdp_utils.py:437-513)."""
+    """Fill a :class:`DecoderLM` (language model and vision tower) from an HF safetensors directory; every rank reads
+    the files it needs itself -- no rank-0 broadcast as in siirl/utils/model_utils/fsdp_utils.py:437-513.  Names are
+    those ``to_hf_state`` writes; checkpoints written by older transformers releases (``model.layers`` beside
+    ``visual``) resolve through aliases.  A missing vocabulary head falls back to the embedding (tied checkpoints)."""
     handles = _open_all(path)
     where = {k: h for h in handles for k in h.keys()}
+    cfg: DecoderConfig = model.cfg
+    head = _llm_names(cfg)[1]
 
     def get(name: str):
-        if name not in where:
-            if strict:
-                raise KeyError(f"{name} missing in {path}")
-            return None
-        return where[name].get_tensor(name)
+        if name in where:
+            return where[name].get_tensor(name)
+        for a, b in _ALIASES:
+            if name.startswith(a) and (b + name[len(a):]) in where:
+                alt = b + name[len(a):]
+                return where[alt].get_tensor(alt)
+        return None
 
-    cfg: DecoderConfig = model.cfg
-
-    def put(dst: torch.Tensor, src):
-        if src is not None:
-            dst.copy_(src.to(dst.dtype))
-
+    embed = None
     with torch.no_grad():
-        put(model.embed_tokens.data, get("model.embed_tokens.weight"))
-        for i, layer in enumerate(model.layers):
-            p = f"model.layers.{i}."
-            put(layer.input_layernorm.data, get(p + "input_layernorm.weight"))
-            put(layer.qkv_proj_weight.data, torch.cat([get(p + f"self_attn.{x}_proj.weight") for x in "qkv"], 0))
-            if layer.qkv_proj_bias is not None:
-                put(layer.qkv_proj_bias.data, torch.cat([get(p + f"self_attn.{x}_proj.bias") for x in "qkv"], 0))
-            if cfg.qk_norm:
-                put(layer.q_norm.data, get(p + "self_attn.q_norm.weight"))
-                put(layer.k_norm.data, get(p + "self_attn.k_norm.weight"))
-            put(layer.o_proj_weight.data, get(p + "self_attn.o_proj.weight"))
-            put(layer.post_attention_layernorm.data, get(p + "post_attention_layernorm.weight"))
-            if cfg.is_moe:
-                names = _moe_names(cfg)
-                put(layer.router_weight.data, get(p + names["router"]))
-                for e in range(cfg.num_experts):
-                    put(layer.experts_gate_up.data[e],
-                        torch.cat([get(p + names["expert"].format(e=e, w=names["gate"])),
-                                   get(p + names["expert"].format(e=e, w=names["up"]))], 0))
-                    put(layer.experts_down.data[e], get(p + names["expert"].format(e=e, w=names["down"])))
-                if cfg.shared_expert_intermediate_size > 0:
-                    put(layer.shared_gate_up_weight.data, torch.cat([get(p + "mlp.shared_expert.gate_proj.weight"),
-                                                                     get(p + "mlp.shared_expert.up_proj.weight")], 0))
-                    put(layer.shared_down_weight.data, get(p + "mlp.shared_expert.down_proj.weight"))
-                    if cfg.shared_expert_gate:
-                        put(layer.shared_expert_gate_weight.data, get(p + "mlp.shared_expert_gate.weight"))
+        for name, dst in _hf_targets(model):
+            src = get(name)
+            if src is None and name == head and embed is not None:
+                src = embed
+            if src is None and name == "score.weight":
+                continue                                  # a value head initialised from a causal-LM checkpoint
+            if src is None:
+                if strict:
+                    raise KeyError(f"{name} missing in {path}")
+                continue
+            if name.endswith("embed_tokens.weight") or name.endswith("tok_embeddings.weight"):
+                embed = src
+            if isinstance(dst, tuple):
+                for d, part in zip(dst, _split_wqkv(src, cfg)):
+                    d.copy_(part.to(d.dtype))
             else:
-                put(layer.gate_up_proj_weight.data, torch.cat([get(p + "mlp.gate_proj.weight"),
-                                                               get(p + "mlp.up_proj.weight")], 0))
-                put(layer.down_proj_weight.data, get(p + "mlp.down_proj.weight"))
-        put(model.norm.data, get("model.norm.weight"))
-        if getattr(model, "lm_head", None) is not None:
-            src = where.get("lm_head.weight")
-            put(model.lm_head.data, get("lm_head.weight") if src is not None else get("model.embed_tokens.weight"))
-        if cfg.value_head and "score.weight" in where:
-            put(model.value_head.data, get("score.weight"))
+                dst.copy_(src.reshape(dst.shape).to(dst.dtype))

@@ -128,6 +128,8 @@ class TPDecoder:
         h = self.full.embed(input_ids, pixel_values, image_grid_thw)
         delta = None
         pos32 = positions.to(torch.int32).contiguous()
+        if cfg.mrope_section is None and rp.dim() == 2:
+            rp = rp[0]
         rp32 = rp.to(torch.int32).contiguous()
         for li, layer in enumerate(self.full.layers):
             t = self.layers[li]

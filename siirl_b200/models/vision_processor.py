@@ -132,3 +132,15 @@ class VLProcessor:
         """3-row rope positions of one sequence and its rope delta (= length - next position)."""
         pos = mrope_positions(ids, self.image_token_id, grid, self.merge)
         return pos, int(ids.numel() - (int(pos.max()) + 1)) if ids.numel() else 0
+
+
+def make_vl_processor(cfg: DecoderConfig, min_pixels: int = 32 * 32, max_pixels: int = 768 * 768):
+    """Image processor matching the model's vision tower: native-resolution patches for Qwen2.5-VL, 448-pixel tiles for
+    the InternVL family (``max_pixels`` bounds the tile count there)."""
+    if cfg.vit is not None:
+        from .internvl import InternVLProcessor
+        s = cfg.vit.image_size
+        return InternVLProcessor(cfg, 1, max(1, min(12, max_pixels // (s * s))))
+    if cfg.vision is None:
+        raise ValueError("the model has no vision tower")
+    return VLProcessor(cfg, min_pixels, max_pixels)

@@ -9,7 +9,6 @@ on the tcgen05 GEMM; LayerNorm / GELU are plain PyTorch element-wise statements.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -18,33 +17,7 @@ import torch.nn.functional as F
 
 from .. import ops
 from ..ops.attention import SeqInfo, attention_packed
-
-
-@dataclass
-class ViTConfig:
-    image_size: int = 448
-    patch_size: int = 14
-    hidden_size: int = 1024
-    num_heads: int = 16
-    intermediate_size: int = 4096
-    depth: int = 24
-    in_channels: int = 3
-    class_token: bool = True
-    num_register_tokens: int = 0        # DINOv2 "reg4" models
-    layer_scale: bool = True            # learnable per-channel scale on both residual branches
-    norm_type: str = "layer_norm"       # or "rms_norm" (InternViT-6B)
-    qkv_bias: bool = True
-    norm_eps: float = 1e-6
-    final_norm: bool = False            # timm ViTs end in a LayerNorm; InternVL reads the raw last layer
-    select_layer: int = -1              # hidden state handed on: -1 last layer, -2 the one before (Prismatic)
-
-    @property
-    def num_patches(self) -> int:
-        return (self.image_size // self.patch_size) ** 2
-
-    @property
-    def num_prefix_tokens(self) -> int:
-        return (1 if self.class_token else 0) + self.num_register_tokens
+from .config import ViTConfig
 
 
 class ViTBlock(nn.Module):
