@@ -31,12 +31,15 @@ class EmbodiedRollout:
                  video_embedder=None):
         self.engine, self.cfg, self.device = engine, embodied_cfg, torch.device(device)
         self.model_config = model_config
-        self.actions = ActionTokenizer(model_config.vocab_size)
+        self.actions = ActionTokenizer(model_config.action_vocab_size or model_config.vocab_size,
+                                       n_bins=model_config.n_action_bins)
         self.proc = VLAProcessor(model_config, tokenizer, image_size=getattr(embodied_cfg, "policy_image_size", 224),
                                  center_crop=embodied_cfg.center_crop)
         self.chunk = embodied_cfg.action_chunks_len
         self.atl = embodied_cfg.action_token_len
         self.seed = seed
+        from ...models.embodied.vla import uses_parallel_decode
+        self.parallel = uses_parallel_decode(embodied_cfg, model_config)
         self.env = None
         self.video_embedder = video_embedder
 
@@ -49,6 +52,12 @@ class EmbodiedRollout:
                                         num_steps_wait=e.num_steps_wait, model_family=e.model_family,
                                         device=str(self.device), **dict(getattr(e, "env_kwargs", None) or {}))
         return self.env
+
+    def _full_model(self):
+        m = self.engine.model
+        if hasattr(m, "full"):
+            raise ValueError("parallel action decoding runs on the whole model: set rollout.tensor_model_parallel_size=1")
+        return m
 
     @staticmethod
     def _run(coro):
@@ -95,13 +104,18 @@ class EmbodiedRollout:
                 frames = torch.stack([torch.as_tensor(obs[k]["image"]) for k in act_rows]).to(dev)
                 imgs = self.proc.resize(frames.contiguous())
                 p_list = [prompt_ids[rows[k]] for k in act_rows]
-                mm = self.proc.mm_inputs(imgs, [len(p) for p in p_list], self.engine.model.embed_tokens.dtype)
-                sp = SamplingParams(n=1, temperature=temperature, max_new_tokens=A, ignore_eos=True,
-                                    seed=(self.seed + 7919 * int(meta.get("global_steps", 0)) + 31 * l + g0)
-                                    & 0x7FFFFFFF)
-                outs = self.engine.generate(p_list, sp, mm_inputs=mm)
-                tok = torch.tensor([o.token_ids for o in outs], dtype=torch.int64, device=dev)
-                lp = torch.tensor([o.logprobs for o in outs], dtype=torch.float32, device=dev)
+                step_seed = (self.seed + 7919 * int(meta.get("global_steps", 0)) + 31 * l + g0) & 0x7FFFFFFF
+                if self.parallel:
+                    # OpenVLA-OFT: the whole chunk from one forward pass over [prompt][A zero vectors]
+                    from ...models.embodied.vla import oft_parallel_decode
+                    gen = torch.Generator(device=dev).manual_seed(step_seed)
+                    tok, lp = oft_parallel_decode(self._full_model(), self.proc, p_list, imgs, A, temperature, gen)
+                else:
+                    mm = self.proc.mm_inputs(imgs, [len(p) for p in p_list], self.engine.model.embed_tokens.dtype)
+                    sp = SamplingParams(n=1, temperature=temperature, max_new_tokens=A, ignore_eos=True, seed=step_seed)
+                    outs = self.engine.generate(p_list, sp, mm_inputs=mm)
+                    tok = torch.tensor([o.token_ids for o in outs], dtype=torch.int64, device=dev)
+                    lp = torch.tensor([o.logprobs for o in outs], dtype=torch.float32, device=dev)
                 gen_tokens += tok.numel()
                 gi = torch.tensor([rows[k] for k in act_rows], device=dev)
                 out_resp[gi, l], out_logp[gi, l], out_img[gi, l] = tok, lp, imgs

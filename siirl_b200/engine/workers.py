@@ -357,10 +357,23 @@ class _ModelWorkerBase:
             proc = self.vla_processor
             pv, grid = proc.patchify(mb["images"].to(self.device), model.embed_tokens.dtype)
             first = torch.tensor(pk.info.cu_seqlens_cpu[:-1], device=self.device)
-            img_mask = torch.zeros(pk.input_ids.shape[0], dtype=torch.bool, device=self.device)
-            img_mask[(first[:, None] + torch.arange(proc.tokens_per_image, device=self.device)[None, :]).flatten()] = True
+            img_mask = proc.image_mask(first, pk.input_ids.shape[0])
             mm = {"pixel_values": pv, "image_grid_thw": grid, "image_mask": img_mask}
             positions = torch.cat([proc.rope_layout(n)[0] for n in pk.info.seqlens], 1).to(self.device)
+            from ..models.embodied.vla import action_id_range, oft_action_logits, uses_parallel_decode
+            if uses_parallel_decode(self.config.embodied, self.model_config):
+                # OpenVLA-OFT: the action positions enter as zero vectors and are scored where they stand, over
+                # the action bins only (reference: siirl/engine/actor/embodied_actor.py:137-148)
+                act_rows = pk.sel + 1
+                zero_mask = torch.zeros(pk.input_ids.shape[0], dtype=torch.bool, device=self.device)
+                zero_mask[act_rows] = True
+                hidden = model.forward_hidden(pk.input_ids, positions, pk.info, zero_mask=zero_mask, **mm)
+                logits = oft_action_logits(model, hidden.index_select(0, act_rows), temperature)
+                logp = torch.log_softmax(logits, -1)
+                lo, hi = action_id_range(self.model_config)
+                lp = logp.gather(1, (pk.labels - lo).clamp(0, hi - lo - 1)[:, None])[:, 0]
+                ent = -(logp.exp() * logp).sum(-1) if with_entropy else None
+                return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
         if "multi_modal_inputs" in mb.non_tensors:
             # vision-language rows: patches of all rows in row order; placeholders are the image-token ids of the
             # PROMPT part only (a sampled response token may collide with the placeholder id); 3-row rope positions
@@ -557,8 +570,11 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
             max_len = r.max_model_len or ((r.prompt_length or 512) + (r.response_length or 512))
             if self._embodied:                      # image tokens + task text + one chunk of action tokens
                 e = self.config.embodied
-                v = self.model_config.vision
-                per_image = (e.policy_image_size // (v.patch_size * v.spatial_merge_size)) ** 2
+                if self.model_config.prismatic is not None:
+                    per_image = self.model_config.prismatic.tokens_per_image + 1
+                else:
+                    v = self.model_config.vision
+                    per_image = (e.policy_image_size // (v.patch_size * v.spatial_merge_size)) ** 2
                 max_len = max(max_len, per_image * e.num_images_in_input + 64 + e.action_chunks_len * e.action_token_len)
             self.tp_model = None
             tp = max(1, int(r.tensor_model_parallel_size))

@@ -45,6 +45,8 @@ class ViTConfig:
     norm_eps: float = 1e-6
     final_norm: bool = False            # timm ViTs end in a LayerNorm; InternVL reads the raw last layer
     select_layer: int = -1              # hidden state handed on: -1 last layer, -2 the one before (Prismatic)
+    class_pos_embed: bool = True        # False: positions for the patches only (timm ``no_embed_class``, DINOv2)
+    act: str = "gelu"                   # or "gelu_tanh"
 
     @property
     def num_patches(self) -> int:
@@ -53,6 +55,30 @@ class ViTConfig:
     @property
     def num_prefix_tokens(self) -> int:
         return (1 if self.class_token else 0) + self.num_register_tokens
+
+
+@dataclass
+class PrismaticConfig:
+    """OpenVLA's vision side: a DINOv2 ViT and (fused backbone) a SigLIP ViT over the same image, patch features
+    concatenated along the channel axis, then a GELU MLP into the language model width."""
+    featurizer: ViTConfig = field(default_factory=lambda: ViTConfig(
+        image_size=224, patch_size=14, hidden_size=1024, num_heads=16, intermediate_size=4096, depth=24,
+        class_token=True, num_register_tokens=4, layer_scale=True, final_norm=True, select_layer=-2,
+        class_pos_embed=False))
+    fused_featurizer: Optional[ViTConfig] = field(default_factory=lambda: ViTConfig(
+        image_size=224, patch_size=14, hidden_size=1152, num_heads=16, intermediate_size=4304, depth=27,
+        class_token=False, layer_scale=False, final_norm=True, select_layer=-2))
+    num_images_in_input: int = 1
+    timm_model_ids: List[str] = field(default_factory=lambda: ["vit_large_patch14_reg4_dinov2.lvd142m",
+                                                                "vit_so400m_patch14_siglip_224"])
+
+    @property
+    def vision_dim(self) -> int:
+        return self.featurizer.hidden_size + (self.fused_featurizer.hidden_size if self.fused_featurizer else 0)
+
+    @property
+    def tokens_per_image(self) -> int:
+        return self.featurizer.num_patches
 
 
 @dataclass
@@ -98,6 +124,11 @@ class DecoderConfig:
     downsample_ratio: float = 0.5
     hf_naming: str = "hf"
     llm_type: str = ""
+    # OpenVLA / OpenVLA-OFT: Prismatic vision backbone; actions are the last ``n_action_bins`` ids below
+    # ``action_vocab_size`` (the tokenizer's size: the embedding matrix is padded beyond it)
+    prismatic: Optional[PrismaticConfig] = None
+    action_vocab_size: int = 0
+    n_action_bins: int = 256
     image_token_id: int = 151655
     eos_token_id: int = 2
     pad_token_id: int = 0
@@ -144,6 +175,8 @@ class DecoderConfig:
         mt = cfg.get("model_type", "qwen2")
         if mt in ("internvl", "internvl_chat"):
             return cls._from_internvl_config(cfg)
+        if mt in ("openvla", "prismatic"):
+            return cls._from_openvla_config(cfg)
         nh = text["num_attention_heads"]
         hd = text.get("head_dim") or text["hidden_size"] // nh
         rope_scaling = text.get("rope_scaling") or cfg.get("rope_scaling") or {}
@@ -226,6 +259,39 @@ class DecoderConfig:
         return out
 
     @classmethod
+    def _from_openvla_config(cls, cfg: Dict[str, Any]) -> "DecoderConfig":
+        """``openvla`` / ``prismatic`` configs (siirl/models/embodied/openvla_oft/configuration_prismatic.py): the
+        vision towers are named by their timm ids, the language model is a Llama-2 ``text_config`` whose embedding
+        matrix is padded to ``pad_to_multiple_of`` rows."""
+        text = dict(cfg.get("text_config") or {})
+        text.setdefault("model_type", "llama")
+        text.setdefault("vocab_size", 32000)
+        for k, v in (("hidden_size", 4096), ("intermediate_size", 11008), ("num_hidden_layers", 32),
+                     ("num_attention_heads", 32), ("rms_norm_eps", 1e-6)):
+            text.setdefault(k, v)
+        mult = int(cfg.get("pad_to_multiple_of", 64))
+        tok_vocab = int(text["vocab_size"])
+        # a new pad token follows the tokenizer's entries; the matrix is then padded to a multiple of ``mult``
+        text["vocab_size"] = (tok_vocab + 1 + mult - 1) // mult * mult if tok_vocab % mult == 0 else tok_vocab
+        out = cls.from_hf_config(text)
+        out.model_type = "openvla"
+        out.llm_type = "llama"
+        out.action_vocab_size = tok_vocab if tok_vocab % mult == 0 else int(cfg.get("action_vocab_size", tok_vocab))
+        out.n_action_bins = int(cfg.get("n_action_bins", 256))
+        out.pad_token_id = int(cfg.get("pad_token_id", 32000))
+        out.image_token_id = out.pad_token_id
+        out.bos_token_id = int(text.get("bos_token_id", 1))
+        ids = list(cfg.get("timm_model_ids") or PrismaticConfig().timm_model_ids)
+        sizes = list(cfg.get("image_sizes") or [224, 224])
+        towers = [vit_from_timm_id(i, int(s)) for i, s in zip(ids, sizes)]
+        if "vit_overrides" in cfg:                   # reduced towers of test checkpoints
+            towers = [ViTConfig(**o) for o in cfg["vit_overrides"]]
+        fused = bool(cfg.get("use_fused_vision_backbone", len(towers) > 1))
+        out.prismatic = PrismaticConfig(featurizer=towers[0], fused_featurizer=towers[1] if fused else None,
+                                        num_images_in_input=int(cfg.get("num_images_in_input", 1)), timm_model_ids=ids)
+        return out
+
+    @classmethod
     def from_pretrained(cls, path: str) -> "DecoderConfig":
         with open(os.path.join(os.path.expanduser(path), "config.json")) as f:
             return cls.from_hf_config(json.load(f))
@@ -254,6 +320,18 @@ class DecoderConfig:
                 d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
         if self.mrope_section:
             d["rope_scaling"] = {"type": "mrope", "mrope_section": self.mrope_section}
+        if self.prismatic is not None:
+            pc = self.prismatic
+            towers = [pc.featurizer] + ([pc.fused_featurizer] if pc.fused_featurizer else [])
+            text = dict(d, model_type="llama", vocab_size=self.action_vocab_size or self.vocab_size)
+            text.pop("architectures", None)
+            return {"architectures": ["OpenVLAForActionPrediction"], "model_type": "openvla", "text_config": text,
+                    "timm_model_ids": pc.timm_model_ids[: len(towers)], "image_sizes": [t.image_size for t in towers],
+                    "use_fused_vision_backbone": pc.fused_featurizer is not None,
+                    "vit_overrides": [asdict(t) for t in towers], "n_action_bins": self.n_action_bins,
+                    "pad_to_multiple_of": 64, "pad_token_id": self.pad_token_id,
+                    "num_images_in_input": pc.num_images_in_input, "action_vocab_size": self.action_vocab_size,
+                    "torch_dtype": "bfloat16"}
         if self.vit is not None:
             v = self.vit
             text = dict(d, model_type=self.llm_type or "qwen2")
@@ -275,6 +353,23 @@ class DecoderConfig:
                     "downsample_ratio": self.downsample_ratio, "select_layer": v.select_layer,
                     "torch_dtype": "bfloat16"}
         return d
+
+
+def vit_from_timm_id(model_id: str, image_size: int = 224) -> ViTConfig:
+    """Shapes of the timm vision transformers the Prismatic backbones name (no timm import: the architectures are
+    public and fixed)."""
+    if "dinov2" in model_id:
+        large = "large" in model_id
+        return ViTConfig(image_size=image_size, patch_size=14, hidden_size=1024 if large else 768,
+                         num_heads=16 if large else 12, intermediate_size=4096 if large else 3072,
+                         depth=24 if large else 12, class_token=True, num_register_tokens=4 if "reg4" in model_id else 0,
+                         layer_scale=True, final_norm=True, select_layer=-2, class_pos_embed="reg4" not in model_id)
+    if "siglip" in model_id:
+        so = "so400m" in model_id
+        return ViTConfig(image_size=image_size, patch_size=14 if so else 16, hidden_size=1152 if so else 768,
+                         num_heads=16 if so else 12, intermediate_size=4304 if so else 3072, depth=27 if so else 12,
+                         class_token=False, layer_scale=False, final_norm=True, select_layer=-2)
+    raise ValueError(f"unknown vision backbone {model_id}")
 
 
 PRESETS: Dict[str, DecoderConfig] = {
@@ -339,6 +434,23 @@ PRESETS: Dict[str, DecoderConfig] = {
                                    vit=ViTConfig(image_size=56, patch_size=14, hidden_size=64, num_heads=2,
                                                  intermediate_size=128, depth=2, qkv_bias=False),
                                    image_token_id=1000),
+    # OpenVLA-7B / OpenVLA-OFT: DINOv2-L/14 (4 registers) + SigLIP-so400m/14 at 224 px, Llama-2-7B
+    "openvla-7b": DecoderConfig(model_type="openvla", llm_type="llama", vocab_size=32064, hidden_size=4096,
+                                intermediate_size=11008, num_layers=32, num_heads=32, num_kv_heads=32, head_dim=128,
+                                rope_theta=1e4, rms_norm_eps=1e-6, qkv_bias=False, prismatic=PrismaticConfig(),
+                                action_vocab_size=32000, image_token_id=32000, pad_token_id=32000, eos_token_id=2,
+                                bos_token_id=1, max_position_embeddings=2048),
+    "tiny-openvla": DecoderConfig(model_type="openvla", llm_type="llama", vocab_size=1088, hidden_size=128,
+                                  intermediate_size=352, num_layers=2, num_heads=4, num_kv_heads=4, head_dim=32,
+                                  qkv_bias=False, action_vocab_size=1024, image_token_id=1024, pad_token_id=1024,
+                                  bos_token_id=1, prismatic=PrismaticConfig(
+                                      featurizer=ViTConfig(image_size=56, patch_size=14, hidden_size=64, num_heads=2,
+                                                           intermediate_size=128, depth=3, num_register_tokens=4,
+                                                           final_norm=True, select_layer=-2, class_pos_embed=False),
+                                      fused_featurizer=ViTConfig(image_size=56, patch_size=14, hidden_size=72,
+                                                                 num_heads=2, intermediate_size=96, depth=3,
+                                                                 class_token=False, layer_scale=False, final_norm=True,
+                                                                 select_layer=-2))),
     "tiny-vl-gpu": DecoderConfig(model_type="qwen2_5_vl", vocab_size=2048, hidden_size=256, intermediate_size=512,
                                  num_layers=2, num_heads=4, num_kv_heads=2, head_dim=64, mrope_section=[8, 12, 12],
                                  vision=VisionConfig(depth=2, hidden_size=128, num_heads=2, intermediate_size=256,

@@ -206,6 +206,9 @@ class DecoderLM(nn.Module):
         if cfg.vision is not None:
             from .vision import VisionTower
             self.vision = VisionTower(cfg.vision, dtype, device, gen)
+        elif cfg.prismatic is not None:
+            from .embodied.prismatic import PrismaticVision
+            self.vision = PrismaticVision(cfg.prismatic, cfg.hidden_size, dtype, device, gen)
         elif cfg.vit is not None:
             from .internvl import InternVLVision
             self.vision = InternVLVision(cfg.vit, cfg.hidden_size, cfg.downsample_ratio, dtype, device, gen)
@@ -222,11 +225,15 @@ class DecoderLM(nn.Module):
     def head_weight(self) -> torch.Tensor:
         return self.lm_head if self.lm_head is not None else self.embed_tokens
 
-    def embed(self, input_ids: torch.Tensor, pixel_values=None, image_grid_thw=None, image_mask=None) -> torch.Tensor:
+    def embed(self, input_ids: torch.Tensor, pixel_values=None, image_grid_thw=None, image_mask=None,
+              zero_mask=None) -> torch.Tensor:
         """Token embeddings with vision features written over the image placeholders.  ``image_mask`` names the
         placeholder positions explicitly; the default (ids equal to ``image_token_id``) is only safe when generated
-        tokens cannot collide with the placeholder id."""
+        tokens cannot collide with the placeholder id.  Rows of ``zero_mask`` enter the model as zero vectors (the
+        action placeholders of OpenVLA-OFT's parallel decoding)."""
         h = ops.embedding(input_ids, self.embed_tokens)
+        if zero_mask is not None:
+            h = h * (~zero_mask).to(h.dtype)[:, None]
         if self.vision is not None and pixel_values is not None:
             img = self.vision(pixel_values, image_grid_thw).to(h.dtype)
             mask = image_mask if image_mask is not None else input_ids == self.cfg.image_token_id
@@ -236,7 +243,7 @@ class DecoderLM(nn.Module):
 
     # ---- training / scoring path ---------------------------------------------------------------
     def forward_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo, pixel_values=None,
-                       image_grid_thw=None, image_mask=None) -> torch.Tensor:
+                       image_grid_thw=None, image_mask=None, zero_mask=None) -> torch.Tensor:
         """Final-norm hidden states ``[T, H]`` of a packed batch.  With sequence parallelism attached
         (``self.sp``), the packed stream is padded to a multiple of the group size and this rank computes rows
         ``[rank * T/sp, (rank + 1) * T/sp)``: the result holds those rows only (see ``sp_slice``)."""
@@ -273,7 +280,7 @@ class DecoderLM(nn.Module):
                 input_ids = torch.cat([input_ids, input_ids.new_zeros(pad)])
                 positions = torch.cat([positions, positions.new_zeros(*positions.shape[:-1], pad)], dim=-1)
                 info = SeqInfo(list(info.seqlens) + [pad], device=input_ids.device)
-        h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask)
+        h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask, zero_mask)
         if sp_rows is not None:
             from ..parallel.megatron_tp import take_rows_for_sp
             h = take_rows_for_sp(h, tp)

@@ -56,17 +56,28 @@ class VLAProcessor:
 
     def __init__(self, model_config, tokenizer, image_size: int = 224, center_crop: bool = True,
                  max_text_len: int = 48):
+        self.cfg, self.tok = model_config, tokenizer
+        self.center_crop = center_crop
+        self.max_text_len = max_text_len
+        self.image_token_id = model_config.image_token_id
+        self.prismatic = model_config.prismatic
+        self.image_offset = 0               # tokens in front of the image placeholders
+        if self.prismatic is not None:
+            # OpenVLA layout: [BOS][patch features of the image][text]; plain 1-D rope positions
+            pc = self.prismatic
+            self.image_size = pc.featurizer.image_size
+            self.patch, self.merge, self.tpatch = pc.featurizer.patch_size, 1, 1
+            self.grid = self.image_size // self.patch
+            self.tokens_per_image = pc.tokens_per_image
+            self.image_offset = 1
+            return
         v = model_config.vision
         assert v is not None, "the VLA policy needs a decoder with a vision tower"
-        self.cfg, self.tok = model_config, tokenizer
         self.patch, self.merge, self.tpatch = v.patch_size, v.spatial_merge_size, v.temporal_patch_size
         unit = self.patch * self.merge
         self.image_size = max(unit, image_size // unit * unit)
         self.grid = self.image_size // self.patch
         self.tokens_per_image = (self.grid // self.merge) ** 2
-        self.center_crop = center_crop
-        self.max_text_len = max_text_len
-        self.image_token_id = model_config.image_token_id
 
     # ---- images --------------------------------------------------------------------------------------
     def resize(self, images: torch.Tensor) -> torch.Tensor:
@@ -80,6 +91,10 @@ class VLAProcessor:
         """Resized frames ``[N, S, S, 3] uint8`` -> flattened patches ``[N * grid^2, C*T*P*P]`` in the vision tower's
         order (per image ``(h/m, w/m, m, m)`` patch order, each patch ``C x T x P x P``) and ``grid_thw [N, 3]``."""
         N, S = images_u8.shape[0], self.image_size
+        if self.prismatic is not None:
+            from .prismatic import normalize_for_towers
+            x = normalize_for_towers(images_u8, self.prismatic.fused_featurizer is not None)
+            return x.to(dtype), torch.tensor([[1, self.grid, self.grid]] * N, dtype=torch.int64)
         x = images_u8.permute(0, 3, 1, 2).float() / 255.0
         mean = torch.tensor(_MEAN, device=x.device).view(1, 3, 1, 1)
         std = torch.tensor(_STD, device=x.device).view(1, 3, 1, 1)
@@ -93,14 +108,35 @@ class VLAProcessor:
 
     # ---- tokens ---------------------------------------------------------------------------------------
     def text_tokens(self, task_description: str) -> List[int]:
-        ids = self.tok.encode(f"What action should the robot take to {task_description.lower()}?")
+        q = f"What action should the robot take to {task_description.lower()}?"
+        if self.prismatic is not None:          # OpenVLA's prompt template
+            q = f"In: {q}\nOut:"
+        ids = self.tok.encode(q)
+        bos = self.cfg.bos_token_id
+        if self.prismatic is not None and bos is not None and len(ids) and ids[0] == bos:
+            ids = ids[1:]                       # the layout places BOS itself
         return list(ids)[: self.max_text_len]
 
     def prompt_ids(self, task_description: str) -> List[int]:
-        return [self.image_token_id] * self.tokens_per_image + self.text_tokens(task_description)
+        img = [self.image_token_id] * self.tokens_per_image
+        if self.prismatic is not None:
+            bos = self.cfg.bos_token_id if self.cfg.bos_token_id is not None else 1
+            return [bos] + img + self.text_tokens(task_description)
+        return img + self.text_tokens(task_description)
+
+    def image_mask(self, first_rows: torch.Tensor, total_rows: int) -> torch.Tensor:
+        """Placeholder positions of a packed batch whose sequences start at ``first_rows``."""
+        dev = first_rows.device
+        mask = torch.zeros(total_rows, dtype=torch.bool, device=dev)
+        at = first_rows[:, None] + self.image_offset + torch.arange(self.tokens_per_image, device=dev)[None, :]
+        mask[at.flatten()] = True
+        return mask
 
     def rope_layout(self, prompt_len: int, extra: int = 0) -> Tuple[torch.Tensor, int]:
         """3-row rope positions of ``[image][text][extra generated tokens]`` and the rope delta of the prompt."""
+        if self.prismatic is not None:
+            n = prompt_len + extra
+            return torch.arange(n).expand(3, n).contiguous(), 0
         gm = self.grid // self.merge
         hh = torch.arange(gm).repeat_interleave(gm)
         ww = torch.arange(gm).repeat(gm)
@@ -112,10 +148,72 @@ class VLAProcessor:
     def mm_inputs(self, images_u8: torch.Tensor, prompt_lens: Sequence[int], dtype=torch.bfloat16) -> List[Dict]:
         """Per-prompt multimodal inputs for ``RolloutEngine.generate``."""
         pv, grid = self.patchify(images_u8, dtype)
-        per = self.grid * self.grid
+        per = 1 if self.prismatic is not None else self.grid * self.grid
         out = []
         for i, n in enumerate(prompt_lens):
             pos, delta = self.rope_layout(n)
             out.append({"pixel_values": pv[i * per:(i + 1) * per], "image_grid_thw": grid[i:i + 1],
                         "rope_positions": pos, "rope_delta": delta})
         return out
+
+
+# ---- OpenVLA-OFT parallel decoding ------------------------------------------------------------------------------
+def action_id_range(model_config) -> Tuple[int, int]:
+    """[lo, hi) of the action token ids: the last ``n_action_bins`` ids of the tokenizer's vocabulary (the embedding
+    matrix may be padded beyond it)."""
+    hi = int(model_config.action_vocab_size or model_config.vocab_size)
+    return hi - int(model_config.n_action_bins), hi
+
+
+def uses_parallel_decode(embodied_cfg, model_config) -> bool:
+    """OpenVLA-OFT reads a whole action chunk off ONE forward pass: the action positions enter as zero vectors and
+    the logits at those positions, restricted to the action ids, give the tokens
+    (siirl/models/embodied/openvla_oft/modeling_prismatic.py:1552-1706).  OpenVLA decodes token by token."""
+    explicit = getattr(embodied_cfg, "parallel_decode", None)
+    if explicit is not None:
+        return bool(explicit)
+    return str(getattr(embodied_cfg, "embodied_type", "")) == "openvla-oft" and model_config.prismatic is not None
+
+
+def oft_action_logits(model, hidden_rows: torch.Tensor, temperature: float) -> torch.Tensor:
+    """Hidden states at the action positions -> fp32 logits over the action bins ``[N, n_action_bins]``."""
+    from ... import ops
+    lo, hi = action_id_range(model.cfg)
+    logits = ops.linear(hidden_rows, model.head_weight[lo:hi]).float()
+    return logits / max(float(temperature), 1e-6)
+
+
+@torch.no_grad()
+def oft_parallel_decode(model, proc: "VLAProcessor", prompts: Sequence[Sequence[int]], images_u8: torch.Tensor,
+                        n_action_tokens: int, temperature: float, generator: Optional[torch.Generator] = None
+                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One forward pass per control step: returns (action token ids ``[N, A]``, their log-probs ``[N, A]`` under the
+    distribution over the action bins).  ``temperature`` 0 takes the arg-max."""
+    from ...ops.attention import SeqInfo
+    dev = images_u8.device
+    A = n_action_tokens
+    lo, _ = action_id_range(model.cfg)
+    pad = model.cfg.pad_token_id or 0
+    lens = [len(p) + A for p in prompts]
+    ids = torch.tensor([t for p in prompts for t in list(p) + [pad] * A], dtype=torch.int64, device=dev)
+    info = SeqInfo(lens, device=dev)
+    first = torch.tensor(info.cu_seqlens_cpu[:-1], device=dev)
+    ends = torch.tensor(info.cu_seqlens_cpu[1:], device=dev)
+    act_rows = (ends[:, None] - A + torch.arange(A, device=dev)[None, :]).flatten()
+    zero_mask = torch.zeros(ids.shape[0], dtype=torch.bool, device=dev)
+    zero_mask[act_rows] = True
+    pv, grid = proc.patchify(images_u8, model.embed_tokens.dtype)
+    if proc.prismatic is None:
+        positions = torch.cat([proc.rope_layout(len(p), A)[0] for p in prompts], 1).to(dev)
+    else:
+        positions = info.positions
+    hidden = model.forward_hidden(ids, positions, info, pixel_values=pv, image_grid_thw=grid,
+                                  image_mask=proc.image_mask(first, ids.shape[0]), zero_mask=zero_mask)
+    logits = oft_action_logits(model, hidden.index_select(0, act_rows), temperature if temperature > 0 else 1.0)
+    logp = torch.log_softmax(logits, -1)
+    if temperature > 0:
+        pick = torch.multinomial(logp.exp(), 1, generator=generator)[:, 0]
+    else:
+        pick = logp.argmax(-1)
+    lp = logp.gather(1, pick[:, None])[:, 0]
+    return (pick + lo).reshape(len(prompts), A), lp.reshape(len(prompts), A)

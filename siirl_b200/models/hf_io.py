@@ -82,6 +82,8 @@ def _decoder_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
 # ---- family-specific names ----------------------------------------------------------------------------------------
 def _llm_names(cfg: DecoderConfig) -> Tuple[str, str]:
     """(prefix replacing ``model.``, name of the vocabulary head) of the language model inside a checkpoint."""
+    if cfg.prismatic is not None:
+        return "language_model.model.", "language_model.lm_head.weight"
     if cfg.vit is not None and cfg.hf_naming == "internvl_chat":
         return "language_model.model.", ("language_model.output.weight" if cfg.llm_type == "internlm2"
                                          else "language_model.lm_head.weight")
@@ -156,6 +158,44 @@ def _vit_state(vision, names: str) -> Iterator[Tuple[str, torch.Tensor]]:
     yield m[2] + "bias", proj.fc1_bias.data
 
 
+def _timm_vit_state(enc, prefix: str) -> Iterator[Tuple[str, torch.Tensor]]:
+    """A :class:`ViTEncoder` under timm's ``VisionTransformer`` names (LayerScale as ``lsN.scale_factor``, the name
+    OpenVLA checkpoints carry after the reference's patch, siirl/models/embodied/openvla_oft/modeling_prismatic.py:56-64)."""
+    vc = enc.cfg
+    P = vc.patch_size
+    if vc.class_token:
+        yield prefix + "cls_token", enc.prefix_tokens.data[:1][None]
+    if vc.num_register_tokens:
+        yield prefix + "reg_token", enc.prefix_tokens.data[(1 if vc.class_token else 0):][None]
+    yield prefix + "pos_embed", enc.position_embedding.data[None]
+    yield prefix + "patch_embed.proj.weight", enc.patch_embed_weight.data[:, :enc.patch_dim].unflatten(
+        1, (vc.in_channels, P, P))
+    yield prefix + "patch_embed.proj.bias", enc.patch_embed_bias.data
+    for i, b in enumerate(enc.blocks):
+        p = prefix + f"blocks.{i}."
+        for ours, theirs in (("norm1", "norm1"), ("qkv", "attn.qkv"), ("proj", "attn.proj"), ("norm2", "norm2"),
+                             ("fc1", "mlp.fc1"), ("fc2", "mlp.fc2")):
+            yield p + theirs + ".weight", getattr(b, ours + "_weight").data
+            if getattr(b, ours + "_bias", None) is not None:
+                yield p + theirs + ".bias", getattr(b, ours + "_bias").data
+        if vc.layer_scale:
+            yield p + "ls1.scale_factor", b.ls1.data
+            yield p + "ls2.scale_factor", b.ls2.data
+    if vc.final_norm:
+        yield prefix + "norm.weight", enc.norm_weight.data
+        if enc.norm_bias is not None:
+            yield prefix + "norm.bias", enc.norm_bias.data
+
+
+def _prismatic_state(vision) -> Iterator[Tuple[str, torch.Tensor]]:
+    yield from _timm_vit_state(vision.featurizer, "vision_backbone.featurizer.")
+    if vision.fused_featurizer is not None:
+        yield from _timm_vit_state(vision.fused_featurizer, "vision_backbone.fused_featurizer.")
+    for i in range(vision.projector.n):
+        yield f"projector.fc{i + 1}.weight", getattr(vision.projector, f"fc{i}_weight").data
+        yield f"projector.fc{i + 1}.bias", getattr(vision.projector, f"fc{i}_bias").data
+
+
 def _qwen_visual_state(vision, prefix: str = "model.visual.") -> Iterator[Tuple[str, torch.Tensor]]:
     """Qwen2.5-VL tower under transformers' names (``visual.patch_embed.proj``: a 3-D convolution weight)."""
     vc = vision.cfg
@@ -208,7 +248,9 @@ def _hf_targets(model) -> Iterator[Tuple[str, object]]:
                 name = name.replace(ours, theirs)
         yield name, t
     vision = getattr(model, "vision", None)
-    if vision is not None and cfg.vit is not None:
+    if vision is not None and cfg.prismatic is not None:
+        yield from _prismatic_state(vision)
+    elif vision is not None and cfg.vit is not None:
         yield from _vit_state(vision, cfg.hf_naming)
     elif vision is not None:
         yield from _qwen_visual_state(vision)
@@ -285,6 +327,9 @@ def load_hf_weights(model, path: str, strict: bool = True) -> None:
     def get(name: str):
         if name in where:
             return where[name].get_tensor(name)
+        if name.endswith(".scale_factor") and name[: -len("scale_factor")] + "gamma" in where:
+            alt = name[: -len("scale_factor")] + "gamma"             # timm's own name of the LayerScale vector
+            return where[alt].get_tensor(alt)
         for a, b in _ALIASES:
             if name.startswith(a) and (b + name[len(a):]) in where:
                 alt = b + name[len(a):]

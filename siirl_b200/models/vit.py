@@ -9,6 +9,7 @@ on the tcgen05 GEMM; LayerNorm / GELU are plain PyTorch element-wise statements.
 """
 from __future__ import annotations
 
+import math
 from typing import Optional
 
 import torch
@@ -55,12 +56,17 @@ class ViTEncoder(nn.Module):
         n_prefix = cfg.num_prefix_tokens
         self.prefix_tokens = _param((max(n_prefix, 1), H), dtype, device, 0.02, gen) if n_prefix else None
         # learned positions for the class token (when present) and the patches; register tokens carry none (DINOv2)
-        self.position_embedding = _param(((1 if cfg.class_token else 0) + cfg.num_patches, H), dtype, device, 0.02, gen)
+        self.pos_has_class = cfg.class_token and cfg.class_pos_embed
+        self.position_embedding = _param(((1 if self.pos_has_class else 0) + cfg.num_patches, H), dtype, device, 0.02, gen)
         self.blocks = nn.ModuleList([ViTBlock(cfg, dtype, device, gen, _param) for _ in range(cfg.depth)])
         if cfg.final_norm:
             self.norm_weight = _param((H,), dtype, device, -1, gen)
             self.norm_bias = _param((H,), dtype, device, 0, gen) if cfg.norm_type == "layer_norm" else None
         self.head_dim = H // cfg.num_heads
+        # the attention kernels take head widths 32 / 64 / 128: other widths (SigLIP-so400m: 72) run zero-padded to
+        # the next one, which changes neither the scores nor the kept output columns
+        self.kernel_head_dim = next((d for d in (32, 64, 128) if d >= self.head_dim), None)
+        assert self.kernel_head_dim is not None, "vision head width above 128"
 
     def _norm(self, x, w, b):
         if self.cfg.norm_type == "layer_norm":
@@ -88,28 +94,35 @@ class ViTEncoder(nn.Module):
             x = F.pad(x, (0, self.patch_dim_padded - x.shape[-1]))
         h = ops.linear(x.reshape(N * L, -1), self.patch_embed_weight, self.patch_embed_bias).reshape(N, L, -1)
         pos = self.position_embedding
-        if cfg.class_token:
+        if self.pos_has_class:
             h = h + pos[1:][None]
         else:
             h = h + pos[None]
         n_prefix = cfg.num_prefix_tokens
         if n_prefix:
             pre = self.prefix_tokens[None].expand(N, -1, -1)
-            if cfg.class_token:
+            if self.pos_has_class:
                 pre = torch.cat([pre[:, :1] + pos[:1][None], pre[:, 1:]], 1)
             h = torch.cat([pre, h], 1)
         S = h.shape[1]
-        H, D = cfg.hidden_size, self.head_dim
+        H, D, Dk = cfg.hidden_size, self.head_dim, self.kernel_head_dim
+        nh = cfg.num_heads
+        scale = 1.0 / math.sqrt(D)
         info = SeqInfo([S] * N, device=dev)
         h = h.reshape(N * S, H)
         stop = cfg.depth + cfg.select_layer + 1 if cfg.select_layer < 0 else cfg.select_layer
         for blk in self.blocks[:stop]:
             y = ops.linear(self._norm(h, blk.norm1_weight, blk.norm1_bias), blk.qkv_weight, blk.qkv_bias)
-            a = attention_packed(y, info, cfg.num_heads, cfg.num_heads, D, causal=False)
+            if Dk != D:
+                y = F.pad(y.reshape(-1, 3 * nh, D), (0, Dk - D)).reshape(-1, 3 * nh * Dk)
+            a = attention_packed(y, info, nh, nh, Dk, causal=False, scale=scale)
+            if Dk != D:
+                a = a.reshape(-1, nh, Dk)[:, :, :D].reshape(-1, H)
             a = ops.linear(a, blk.proj_weight, blk.proj_bias)
             h = h + (a * blk.ls1 if cfg.layer_scale else a)
             y = ops.linear(self._norm(h, blk.norm2_weight, blk.norm2_bias), blk.fc1_weight, blk.fc1_bias)
-            y = ops.linear(F.gelu(y.float()).to(y.dtype), blk.fc2_weight, blk.fc2_bias)
+            y = ops.linear(F.gelu(y.float(), approximate="tanh" if cfg.act == "gelu_tanh" else "none").to(y.dtype),
+                           blk.fc2_weight, blk.fc2_bias)
             h = h + (y * blk.ls2 if cfg.layer_scale else y)
         if cfg.final_norm and stop == cfg.depth:
             h = self._norm(h, self.norm_weight, self.norm_bias)
@@ -131,7 +144,7 @@ class MLPProjector(nn.Module):
     """``[LayerNorm] -> Linear -> GELU -> Linear [-> GELU -> Linear]`` from vision width to the language model width."""
 
     def __init__(self, in_dim: int, out_dim: int, dtype, device, gen, pre_norm: bool = True, hidden: Optional[int] = None,
-                 layers: int = 2):
+                 layers: int = 2, hidden_dims=None):
         super().__init__()
         from .decoder import _param
         self.pre_norm = pre_norm
@@ -139,7 +152,7 @@ class MLPProjector(nn.Module):
             self.norm_weight = _param((in_dim,), dtype, device, -1, gen)
             self.norm_bias = _param((in_dim,), dtype, device, 0, gen)
         hidden = hidden or out_dim
-        dims = [in_dim] + [hidden] * (layers - 1) + [out_dim]
+        dims = [in_dim] + (list(hidden_dims) if hidden_dims is not None else [hidden] * (layers - 1)) + [out_dim]
         self.n = layers
         for i in range(layers):
             setattr(self, f"fc{i}_weight", _param((dims[i + 1], dims[i]), dtype, device, 0.02, gen))

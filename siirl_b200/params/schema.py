@@ -359,6 +359,9 @@ class EmbodiedArguments:
     temperature: float = 1.6
     n_gpus_per_node: int = 8
     policy_image_size: int = 224
+    # None: OpenVLA-OFT's one-pass chunk decoding when embodied_type is "openvla-oft" and the policy has the Prismatic
+    # backbone, token-by-token decoding otherwise
+    parallel_decode: Optional[bool] = None
     video_num_frames: int = 8
     use_video_embedding: bool = True
 

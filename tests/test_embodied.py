@@ -7,6 +7,7 @@ import subprocess
 import sys
 
 import numpy as np
+import pytest
 import torch
 
 from siirl_b200.data_coordinator.protocol import Batch
@@ -123,15 +124,20 @@ def test_flatten_and_scatter_trajectories():
     assert torch.equal(back[run_tok], data["advantages"][run_tok]) and float(back[~run_tok].abs().sum()) == 0
 
 
-def test_embodied_pipeline_two_steps(tmp_path):
+@pytest.mark.parametrize("policy", ["native-vla", "openvla-oft"])
+def test_embodied_pipeline_two_steps(tmp_path, policy):
+    """``native-vla``: the framework's VL decoder decoding action tokens one by one; ``openvla-oft``: the Prismatic
+    backbone (DINOv2 + SigLIP towers) with one-pass chunk decoding and scoring over the action bins."""
+    preset = "tiny-vl" if policy == "native-vla" else "tiny-openvla"
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, OMP_NUM_THREADS="2", SIIRL_LOG_DIR=str(tmp_path / "log"))
     env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
     args = ["algorithm.adv_estimator=grpo", "algorithm.workflow_type=embodied", "data.synthetic=embodied",
             "data.synthetic_size=32", "data.max_prompt_length=32", "data.max_response_length=32",
-            "data.train_batch_size=4", "actor_rollout_ref.model.arch_preset=tiny-vl", "actor_rollout_ref.rollout.n=4",
+            "data.train_batch_size=4", f"actor_rollout_ref.model.arch_preset={preset}", "actor_rollout_ref.rollout.n=4",
+            f"actor_rollout_ref.embodied.embodied_type={policy}",
             "actor_rollout_ref.rollout.max_num_seqs=16", "actor_rollout_ref.actor.ppo_mini_batch_size=4",
-            "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8", "actor_rollout_ref.actor.embodied_type=native-vla",
+            "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8", f"actor_rollout_ref.actor.embodied_type={policy}",
             "actor_rollout_ref.embodied.env.env_type=synthetic", "actor_rollout_ref.embodied.env.num_envs=8",
             "actor_rollout_ref.embodied.env.max_steps=8", "actor_rollout_ref.embodied.env.env_kwargs={success_radius: 0.3}",
             "actor_rollout_ref.embodied.action_chunks_len=2", "actor_rollout_ref.embodied.policy_image_size=56",

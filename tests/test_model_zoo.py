@@ -177,3 +177,108 @@ def test_qwen2_5_vl_matches_transformers(tmp_path):
                                     position_ids=pos[:, None, :]).logits[0].float(), -1)
         got = _mm_logprobs_ours(model, ids, pixels, grid, positions=pos)
     assert (got - want).abs().max().item() < 5e-4, (got - want).abs().max().item()
+
+
+def _timm_vit_reference(sd, prefix, cfg, images):
+    """Plain-PyTorch statement of timm's ``VisionTransformer.get_intermediate_layers(n={depth - 2})`` from a state
+    dict with timm names: patch convolution, positions on the patches (and on the class token unless
+    ``no_embed_class``), [class, registers, patches], pre-norm blocks with LayerScale, output of the second-to-last
+    block without the final norm, prefix tokens dropped."""
+    import torch.nn.functional as F
+    g = lambda n: sd[prefix + n].float()  # noqa: E731
+    x = F.conv2d(images, g("patch_embed.proj.weight"), g("patch_embed.proj.bias"), stride=cfg.patch_size)
+    x = x.flatten(2).transpose(1, 2)
+    N = x.shape[0]
+    pre = []
+    if cfg.class_token:
+        pre.append(g("cls_token").expand(N, -1, -1))
+    if cfg.num_register_tokens:
+        pre.append(g("reg_token").expand(N, -1, -1))
+    if cfg.class_token and cfg.class_pos_embed:
+        x = torch.cat([pre[0], x], 1) + g("pos_embed")
+        x = torch.cat([x[:, :1]] + pre[1:] + [x[:, 1:]], 1)
+    else:
+        x = torch.cat(pre + [x + g("pos_embed")], 1)
+    nh, H = cfg.num_heads, cfg.hidden_size
+    for i in range(cfg.depth - 1):
+        b = f"blocks.{i}."
+        y = F.layer_norm(x, (H,), g(b + "norm1.weight"), g(b + "norm1.bias"), cfg.norm_eps)
+        q, k, v = F.linear(y, g(b + "attn.qkv.weight"), g(b + "attn.qkv.bias")).reshape(N, -1, 3, nh, H // nh).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(N, -1, H)
+        a = F.linear(a, g(b + "attn.proj.weight"), g(b + "attn.proj.bias"))
+        x = x + (a * g(b + "ls1.scale_factor") if cfg.layer_scale else a)
+        y = F.layer_norm(x, (H,), g(b + "norm2.weight"), g(b + "norm2.bias"), cfg.norm_eps)
+        y = F.linear(F.gelu(F.linear(y, g(b + "mlp.fc1.weight"), g(b + "mlp.fc1.bias"))), g(b + "mlp.fc2.weight"), g(b + "mlp.fc2.bias"))
+        x = x + (y * g(b + "ls2.scale_factor") if cfg.layer_scale else y)
+    return x[:, cfg.num_prefix_tokens:]
+
+
+def test_openvla_prismatic_backbone_and_checkpoint(tmp_path):
+    """DINOv2 (class + 4 register tokens, LayerScale, positions on patches only) and SigLIP (no class token, head width
+    outside the attention kernel's set) towers against the timm forward stated in plain PyTorch on the exported
+    weights; fused projector; OpenVLA checkpoint names round-trip."""
+    import torch.nn.functional as F
+    from safetensors.torch import load_file
+    from siirl_b200.models.hf_io import to_hf_state
+    cfg = get_config("tiny-openvla")
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=11)
+    with torch.no_grad():
+        for n, p in model.vision.named_parameters():
+            if n.endswith("bias") or ".ls" in n:
+                p.copy_(0.2 * torch.randn(p.shape, generator=torch.Generator().manual_seed(len(n))) + (0.7 if ".ls" in n else 0))
+    save_hf_model(model, str(tmp_path))
+    sd = load_file(str(tmp_path / "model.safetensors"))
+    assert {"vision_backbone.featurizer.reg_token", "vision_backbone.fused_featurizer.pos_embed", "projector.fc3.bias",
+            "language_model.lm_head.weight", "vision_backbone.featurizer.blocks.0.ls1.scale_factor"} <= set(sd)
+    assert "vision_backbone.fused_featurizer.cls_token" not in sd
+    assert sd["vision_backbone.featurizer.pos_embed"].shape == (1, 16, 64)         # patches only
+    pc = cfg.prismatic
+    x = torch.randn(3, 6, 56, 56, generator=torch.Generator().manual_seed(5))
+    with torch.no_grad():
+        got = model.vision(x)
+        f1 = _timm_vit_reference(sd, "vision_backbone.featurizer.", pc.featurizer, x[:, :3])
+        f2 = _timm_vit_reference(sd, "vision_backbone.fused_featurizer.", pc.fused_featurizer, x[:, 3:])
+        f = torch.cat([f1, f2], 2)
+        for i in (1, 2, 3):
+            f = F.linear(f, sd[f"projector.fc{i}.weight"], sd[f"projector.fc{i}.bias"])
+            if i < 3:
+                f = F.gelu(f)
+    assert got.shape == (3 * 16, cfg.hidden_size)
+    assert torch.allclose(got, f.reshape(-1, cfg.hidden_size), atol=2e-5), (got - f.reshape(-1, cfg.hidden_size)).abs().max()
+    cfg2 = DecoderConfig.from_pretrained(str(tmp_path))
+    assert cfg2.prismatic is not None and cfg2.action_vocab_size == 1024 and cfg2.vocab_size == cfg.vocab_size
+    again = build_model(cfg2, dtype=torch.float32, device="cpu", seed=2)
+    load_hf_weights(again, str(tmp_path))
+    for (n1, a), (n2, b) in zip(to_hf_state(model), to_hf_state(again)):
+        assert n1 == n2 and torch.equal(a, b), n1
+
+
+def test_oft_parallel_decode_matches_scoring():
+    """The one-pass chunk decoding of OpenVLA-OFT: tokens come from the action bins, their log-probs are those the
+    training-side statement (zero vectors at the action positions, soft-max over the bins) assigns."""
+    from siirl_b200.data_coordinator.dataloader.tokenizer import SyntheticTokenizer
+    from siirl_b200.models.embodied.vla import VLAProcessor, action_id_range, oft_action_logits, oft_parallel_decode
+    cfg = get_config("tiny-openvla")
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=3)
+    proc = VLAProcessor(cfg, SyntheticTokenizer(cfg.action_vocab_size), image_size=56)
+    prompts = [proc.prompt_ids("pick up the red block"), proc.prompt_ids("open the drawer")]
+    assert prompts[0][0] == cfg.bos_token_id and prompts[0][1:17] == [cfg.image_token_id] * 16
+    imgs = torch.randint(0, 255, (2, 56, 56, 3), dtype=torch.uint8, generator=torch.Generator().manual_seed(1))
+    A = 14
+    tok, lp = oft_parallel_decode(model, proc, prompts, imgs, A, 1.0, torch.Generator().manual_seed(0))
+    lo, hi = action_id_range(cfg)
+    assert (lo, hi) == (768, 1024) and tok.shape == (2, A) and bool(((tok >= lo) & (tok < hi)).all())
+    greedy, glp = oft_parallel_decode(model, proc, prompts, imgs, A, 0.0)
+    assert bool((glp >= lp - 1e-6).all())                  # the arg-max is at least as likely as any sample
+    # scoring side, one sequence at a time, sampled tokens in place (their embeddings must not matter)
+    for i, p in enumerate(prompts):
+        ids = torch.tensor(list(p) + tok[i].tolist())
+        info = SeqInfo([ids.numel()])
+        zero = torch.zeros(ids.numel(), dtype=torch.bool)
+        zero[-A:] = True
+        pv, grid = proc.patchify(imgs[i:i + 1], torch.float32)
+        with torch.no_grad():
+            h = model.forward_hidden(ids, info.positions, info, pixel_values=pv, image_grid_thw=grid,
+                                     image_mask=proc.image_mask(torch.tensor([0]), ids.numel()), zero_mask=zero)
+            logp = torch.log_softmax(oft_action_logits(model, h[-A:], 1.0), -1)
+        assert torch.allclose(logp.gather(1, (tok[i] - lo)[:, None])[:, 0], lp[i], atol=1e-5)
