@@ -26,15 +26,20 @@ def main() -> None:
     ap.add_argument("--context", type=int, default=640)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--decode-kernel", default="", choices=["", "simple", "split"],
+                    help="decode attention kernel (default: the package's)")
     ap.add_argument("--max-model-len", type=int, default=0, help="engine limit (0: just enough for this run); the "
                     "training configuration uses prompt + response = 5120")
     ap.add_argument("--n", type=int, default=1, help="samples per prompt (prefix blocks shared by the n samples)")
     args = ap.parse_args()
+    if args.decode_kernel:
+        from ..ops import kv_cache
+        kv_cache.set_decode_kernel(args.decode_kernel)
     cfg = get_config(args.model, {"num_layers": args.layers} if args.layers else None)
     dev = torch.device("cuda")
     model = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=0)
     res = {"model": args.model, "layers": cfg.num_layers, "seqs": args.seqs, "context": args.context,
-           "max_model_len": args.max_model_len, "n": args.n}
+           "max_model_len": args.max_model_len, "n": args.n, "decode_kernel": args.decode_kernel or "default"}
     for graph in ([False] if args.no_graph else [False, True]):
         eng = RolloutEngine(model, max_num_seqs=args.seqs,
                             max_model_len=args.max_model_len or args.context + 4 * args.steps + 64,

@@ -131,6 +131,13 @@ int sb_kv_copy_blocks(void* cache, const int* src, const int* dst, int n_pairs, 
 int sb_fmha_decode(const void* q, int row_stride, const void* cache, long long num_blocks, const int* seq_lens,
                    const int* block_table, int max_blocks, void* out, int B, int Hq, int Hkv, int D, float scale,
                    int* status, cudaStream_t stream);
+// ---- fmha_decode_split.cu ----
+// Persistent split-K/V variant of sb_fmha_decode.  Workspaces in floats: ws_o = B * Hq * chunks * D and
+// ws_lse = B * Hq * chunks with chunks = ceil(max_blocks / sb_fmha_decode_chunk_tiles()).
+int sb_fmha_decode_chunk_tiles();
+int sb_fmha_decode_split(const void* q, int row_stride, const void* cache, long long num_blocks, const int* seq_lens,
+                         const int* block_table, int max_blocks, void* out, float* ws_o, float* ws_lse, int B, int Hq,
+                         int Hkv, int D, float scale, int* status, cudaStream_t stream);
 }
 
 extern "C" {

@@ -74,6 +74,32 @@ def kv_copy_blocks(cache_layer: torch.Tensor, src: torch.Tensor, dst: torch.Tens
     cache_layer[dst.long()] = cache_layer[src.long()]
 
 
+# "split": persistent warp-specialised kernel with split K/V (csrc/fmha_decode_split.cu); "simple": one CTA per
+# (sequence, kv head) (csrc/fmha_decode.cu)
+DECODE_KERNEL = "simple"
+_split_ws: dict = {}
+
+
+def set_decode_kernel(name: str) -> None:
+    global DECODE_KERNEL
+    assert name in ("simple", "split")
+    DECODE_KERNEL = name
+
+
+def _split_workspace(device, B: int, n_heads: int, max_blocks: int, head_dim: int):
+    """Partial outputs and log-sum-exps of the chunks of long sequences; one buffer per shape, allocated on first
+    use (before any CUDA-graph capture replays it)."""
+    chunk = int(_lib.get_lib().sb_fmha_decode_chunk_tiles())
+    chunks = (max_blocks + chunk - 1) // chunk
+    key = (device, B, n_heads, chunks, head_dim)
+    ws = _split_ws.get(key)
+    if ws is None:
+        ws = (torch.empty(B * n_heads * chunks * head_dim, dtype=torch.float32, device=device),
+              torch.empty(B * n_heads * chunks, dtype=torch.float32, device=device))
+        _split_ws[key] = ws
+    return ws
+
+
 def decode_attention(q_rows: torch.Tensor, cache_layer: torch.Tensor, seq_lens: torch.Tensor,
                      block_table: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                      scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -87,6 +113,15 @@ def decode_attention(q_rows: torch.Tensor, cache_layer: torch.Tensor, seq_lens: 
     if q_rows.is_cuda:
         L = _lib.get_lib()
         assert head_dim in (64, 128), "decode attention kernel supports head_dim 64 and 128"
+        if DECODE_KERNEL == "split" and q_rows.stride(0) % head_dim == 0:
+            ws_o, ws_lse = _split_workspace(q_rows.device, B, n_heads, block_table.shape[1], head_dim)
+            _lib.check(L.sb_fmha_decode_split(_lib.ptr(q_rows), q_rows.stride(0), _lib.ptr(cache_layer),
+                                              ctypes.c_longlong(cache_layer.shape[0]), _lib.ptr(seq_lens),
+                                              _lib.ptr(block_table), block_table.shape[1], _lib.ptr(out),
+                                              _lib.ptr(ws_o), _lib.ptr(ws_lse), B, n_heads, n_kv_heads, head_dim,
+                                              ctypes.c_float(scale), _lib.ptr(_lib.status_word(q_rows.device)),
+                                              _lib.stream()), "sb_fmha_decode_split")
+            return out
         _lib.check(L.sb_fmha_decode(_lib.ptr(q_rows), q_rows.stride(0), _lib.ptr(cache_layer),
                                     ctypes.c_longlong(cache_layer.shape[0]), _lib.ptr(seq_lens), _lib.ptr(block_table),
                                     block_table.shape[1], _lib.ptr(out), B, n_heads, n_kv_heads, head_dim,

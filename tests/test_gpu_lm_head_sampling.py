@@ -95,6 +95,46 @@ def test_decode_attention_matches_eager(D, hq, hkv):
     assert out[4].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("D,hq,hkv", [(128, 28, 4), (64, 14, 2), (128, 32, 4), (128, 8, 8)])
+def test_split_decode_attention_matches_eager(D, hq, hkv):
+    """Persistent split-K/V decode kernel: contexts below one chunk (written directly), across several chunks
+    (partials + merge), ragged lengths, an empty slot, and more work items than SMs."""
+    torch.manual_seed(5)
+    lens = [1, 64, 65, 200, 0, 1024, 1025, 2300, 3000, 777] + [1500 + 37 * i for i in range(40)]
+    B = len(lens)
+    max_blocks = 48
+    need = sum((n + kvc.BLOCK - 1) // kvc.BLOCK for n in lens)
+    nblocks = need + 8
+    cache = (0.5 * torch.randn(nblocks, 2, hkv, kvc.BLOCK, D, device=DEV)).to(torch.bfloat16)
+    order = torch.randperm(nblocks)
+    table = torch.full((B, max_blocks), -1, dtype=torch.int32)
+    at = 0
+    for i, n in enumerate(lens):
+        nb = (n + kvc.BLOCK - 1) // kvc.BLOCK
+        table[i, :nb] = order[at:at + nb].to(torch.int32)
+        at += nb
+    table = table.to(DEV)
+    seq_lens = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    q = (0.5 * torch.randn(B, (hq + 2 * hkv) * D, device=DEV)).to(torch.bfloat16)
+    kvc.set_decode_kernel("split")
+    try:
+        out = kvc.decode_attention(q, cache, seq_lens, table, hq, hkv, D)
+        lib.check_status()
+        again = kvc.decode_attention(q, cache, seq_lens, table, hq, hkv, D)      # barriers / workspace reuse
+        lib.check_status()
+    finally:
+        kvc.set_decode_kernel("simple")
+    simple = kvc.decode_attention(q, cache, seq_lens, table, hq, hkv, D)
+    lib.check_status()
+    want = kvc.decode_attention(q.cpu().float(), cache.cpu().float(), seq_lens.cpu(), table.cpu().clamp(min=0), hq, hkv, D)
+    assert torch.equal(out, again)
+    live = [i for i, n in enumerate(lens) if n > 0]
+    for i in live:
+        assert _rel(out[i].cpu(), want[i]) < 2e-2, (i, lens[i])
+    assert _rel(out[live].cpu(), simple[live].cpu()) < 1e-2
+    assert out[4].abs().max().item() == 0
+
+
 def test_kv_append_and_fork():
     torch.manual_seed(4)
     hq, hkv, D = 4, 2, 64
