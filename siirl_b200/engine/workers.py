@@ -142,6 +142,9 @@ class _ModelWorkerBase:
             self.store = FlatParamStore(self.model, group=self._pp_dp_group, comm=None, param_filter=pp_filter)
         elif trainable and self._zero3():
             self.store = self._shard_params(self.model, model_args, trainable=True)
+        elif trainable and self._hybrid_shard_groups()[0] is not None:
+            sg, rg, sc = self._hybrid_shard_groups()
+            self.store = FlatParamStore(self.model, group=sg, comm=sc, replica_group=rg)
         elif trainable and getattr(self, "_tp_train", None) is not None:
             # tensor-parallel trainer: every rank owns its slices; gradients and optimizer state are shared with the
             # ranks that hold the same slices (same index in their tensor-parallel group)
@@ -159,6 +162,42 @@ class _ModelWorkerBase:
         fc = getattr(cfgs, "fsdp_config", None)
         return str(getattr(fc, "sharding", "zero2")).lower() in ("zero3", "full_shard", "fsdp")
 
+    def _hybrid_shard_groups(self):
+        """``fsdp_config.fsdp_size`` = k with 1 < k < group size: hybrid sharding (FSDP HYBRID_SHARD,
+        siirl/engine/fsdp_workers.py:151-156).  Consecutive blocks of k ranks shard the training state; the ranks with
+        the same index across blocks hold the same shard and sum their gradients.  Returns (shard group, replica
+        group, peer-memory communicator of the shard group), all None when the whole group shards.  Every rank
+        creates all groups in the same order (``new_group`` is collective)."""
+        if getattr(self, "_hsdp", None) is not None:
+            return self._hsdp
+        cfgs = getattr(self.config, "actor", self.config)
+        fc = getattr(cfgs, "fsdp_config", None)
+        k = int(getattr(fc, "fsdp_size", -1) or -1)
+        self._hsdp = (None, None, None)
+        if k <= 1 or k >= self.world or self.world <= 1:
+            return self._hsdp
+        if self.world % k:
+            raise ValueError(f"fsdp_config.fsdp_size={k} must divide the worker group size {self.world}")
+        if any(getattr(self, a, None) is not None for a in ("_tp_train", "_pp_ctx", "ep_ctx")):
+            raise ValueError("fsdp_config.fsdp_size (hybrid sharding) cannot be combined with tensor / pipeline / "
+                             "expert parallel training")
+        ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
+        shard = rep = None
+        for b in range(self.world // k):
+            g = dist.new_group(ranks[b * k:(b + 1) * k])
+            if b == self.rank // k:
+                shard = g
+        for i in range(k):
+            g = dist.new_group(ranks[i::k])
+            if i == self.rank % k:
+                rep = g
+        comm = None
+        if self.device.type == "cuda":
+            from ..parallel.symm import SymmComm
+            comm = SymmComm.create(shard)
+        self._hsdp = (shard, rep, comm)
+        return self._hsdp
+
     def _shard_params(self, model, model_args, trainable: bool):
         from ..parallel.sharded_params import ShardedParamStore
         mc = self.model_config
@@ -171,6 +210,10 @@ class _ModelWorkerBase:
         if not trainable:
             for p in model.parameters():
                 p.requires_grad_(False)
+        sg, rg, sc = self._hybrid_shard_groups()
+        if sg is not None:
+            return ShardedParamStore(model, group=sg, comm=sc, optimizer_state=trainable, trainable=trainable,
+                                     replica_group=rg)
         return ShardedParamStore(model, group=self.group, comm=self.comm if self.device.type == "cuda" else None,
                                  optimizer_state=trainable, trainable=trainable)
 

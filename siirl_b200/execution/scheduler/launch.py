@@ -44,10 +44,6 @@ def _warn_unsupported_keys(config) -> None:
             _warn_once(f"{name}.fsdp_config.param_offload", "trainable weights stay on the GPU (the rollout engine "
                        "reads them in place); use fsdp_config.sharding=zero3 to cut their footprint, "
                        "optimizer_offload for the Adam state, ref.fsdp_config.param_offload for the frozen policy")
-        if int(fc.fsdp_size) not in (-1, 0, 1) and int(fc.fsdp_size) != config.trainer.n_gpus_per_node * \
-                config.trainer.nnodes:
-            _warn_once(f"{name}.fsdp_config.fsdp_size", "hybrid sharding (shard inside groups of fsdp_size ranks, "
-                       "replicate across them) is not implemented: state is sharded over the whole worker group")
     m = arr.model
     if getattr(m, "use_remove_padding", False) is False and "use_remove_padding" in getattr(config, "_explicit", ()):
         _warn_once("actor_rollout_ref.model.use_remove_padding", "sequences are always packed without padding")

@@ -37,11 +37,14 @@ def _round_up(x: int, m: int) -> int:
 class FlatParamStore:
     def __init__(self, module: nn.Module, group: Optional[dist.ProcessGroup] = None, comm=None,
                  optimizer_state: bool = True, param_filter=None, local_only: bool = False,
-                 grad_scale: Optional[float] = None, param_alloc=None, with_grad: bool = True):
+                 grad_scale: Optional[float] = None, param_alloc=None, with_grad: bool = True,
+                 replica_group: Optional[dist.ProcessGroup] = None):
         """``param_filter(name) -> bool`` restricts the store to some parameters.  ``local_only`` makes a store
         whose parameters exist on this rank alone (expert-parallel experts): no reduce-scatter / all-gather, the
         whole state lives here, ``grad_scale`` (1 / data-parallel width) keeps their update on the same loss
         scale as the replicated parameters, and the clipping norm comes from the caller (``global_sumsq``).
+        ``replica_group`` (hybrid sharding, FSDP's HYBRID_SHARD): the state is sharded over ``group`` and replicated
+        over ``replica_group``; gradients are summed across the replicas before the shard group's reduce-scatter.
         ``param_alloc(numel, dtype)`` allocates the flat parameter buffer (a rank-local store whose parameters the
         peers read: symmetric memory); ``with_grad=False`` builds no gradient buffer (frozen models)."""
         params = [(n, p) for n, p in module.named_parameters() if param_filter is None or param_filter(n)]
@@ -53,6 +56,8 @@ class FlatParamStore:
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
         self.rank = dist.get_rank(group) if self.world > 1 else 0
         self.local_only = local_only
+        self.replica_group = replica_group if not local_only else None
+        self.replicas = dist.get_world_size(replica_group) if self.replica_group is not None else 1
         self.grad_scale = grad_scale
         if local_only:
             self.world, self.rank = 1, 0
@@ -176,10 +181,13 @@ class FlatParamStore:
         self.reload_state()
         self.collect_grads()
         self.step_count += 1
+        if self.replicas > 1:
+            dist.all_reduce(self.flat_grad, group=self.replica_group)     # every shard group now holds the total
+        grad_scale = self.grad_scale if self.grad_scale is not None else 1.0 / (self.world * self.replicas)
         if self.world > 1 and self.comm is not None and self.device.type == "cuda":
-            norm = self.comm.fused_rs_adamw_ag(self, lr, betas, eps, weight_decay, max_grad_norm, extra_sumsq)
+            norm = self.comm.fused_rs_adamw_ag(self, lr, betas, eps, weight_decay, max_grad_norm, extra_sumsq,
+                                               grad_scale=grad_scale)
             return norm
-        grad_scale = self.grad_scale if self.grad_scale is not None else 1.0 / self.world
         if self.world > 1:
             shard_grad = self._reduce_scatter()
         else:

@@ -53,8 +53,13 @@ class _ShardHolder(nn.Module):
 
 class ShardedParamStore:
     def __init__(self, module: nn.Module, group: Optional[dist.ProcessGroup] = None, comm=None,
-                 optimizer_state: bool = True, trainable: bool = True, layers_attr: str = "layers"):
+                 optimizer_state: bool = True, trainable: bool = True, layers_attr: str = "layers",
+                 replica_group: Optional[dist.ProcessGroup] = None):
         self.module = module
+        # hybrid sharding: pieces are sharded over ``group`` and replicated over ``replica_group``, whose members
+        # hold the same pieces and sum their gradients before the optimizer step
+        self.replica_group = replica_group
+        self.replicas = dist.get_world_size(replica_group) if replica_group is not None else 1
         self.group = group
         self.comm = comm
         self.world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
@@ -92,7 +97,8 @@ class ShardedParamStore:
         self.root: Optional[FlatParamStore] = None
         if rest:
             self.root = FlatParamStore(module, group=group, comm=comm, optimizer_state=optimizer_state and trainable,
-                                       param_filter=lambda n: not n.startswith(prefix), with_grad=trainable)
+                                       param_filter=lambda n: not n.startswith(prefix), with_grad=trainable,
+                                       replica_group=replica_group)
 
         # ---- this rank's pieces ------------------------------------------------------------------------------------
         sym = (lambda n, dt: comm.alloc(n, dt)) if (self._cuda and comm is not None and self.world > 1) else None
@@ -108,7 +114,8 @@ class ShardedParamStore:
                 holder.pieces.data[i * self.piece:(i + 1) * self.piece].copy_(staging[lo:lo + self.piece])
         del staging
         self.local = FlatParamStore(holder, group=None, comm=None, optimizer_state=optimizer_state and trainable,
-                                    local_only=True, grad_scale=1.0 / self.world, param_alloc=sym, with_grad=trainable)
+                                    local_only=True, grad_scale=1.0 / (self.world * self.replicas), param_alloc=sym,
+                                    with_grad=trainable)
         self._holder = holder
         self.param_shard = self.local.flat_param          # [L * piece], symmetric on GPUs
         self.grad_shard = self.local.flat_grad            # fp32 [L * piece]
@@ -332,6 +339,8 @@ class ShardedParamStore:
         assert self.trainable and self.local.master is not None
         # squared norm of the (summed, unscaled) unit gradients this rank owns; the pieces partition the units, so
         # the sum over ranks is the units' squared norm
+        if self.replicas > 1:
+            dist.all_reduce(self.local.flat_grad, group=self.replica_group)
         mine = self.local.local_sumsq()
         if self.root is not None:
             norm = self.root.step(lr, betas, eps, weight_decay, max_grad_norm, extra_sumsq=mine)
@@ -341,7 +350,7 @@ class ShardedParamStore:
             total = mine.clone()
             if self.world > 1:
                 dist.all_reduce(total, group=self.group)
-            norm = total.sqrt()[0] / self.world
+            norm = total.sqrt()[0] / (self.world * self.replicas)
         self.local.step(lr, betas, eps, weight_decay, max_grad_norm, global_sumsq=total)
         self._resident.clear()                             # gathered copies are stale now
         self._last_unit = None

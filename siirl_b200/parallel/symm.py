@@ -125,7 +125,8 @@ class SymmComm:
 
     # ---- fused optimizer step ---------------------------------------------------------------------------
     def fused_rs_adamw_ag(self, store, lr: float, betas, eps: float, weight_decay: float,
-                          max_grad_norm: float, extra_sumsq: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          max_grad_norm: float, extra_sumsq: Optional[torch.Tensor] = None,
+                          grad_scale: Optional[float] = None) -> torch.Tensor:
         grads, params = self.peers_of(store.flat_grad), self.peers_of(store.flat_param)
         if self._shard_grad is None or self._shard_grad.numel() != store.shard_size:
             self._shard_grad = torch.empty(store.shard_size, dtype=torch.float32, device=self.device)
@@ -143,7 +144,8 @@ class SymmComm:
             _lib.ptr(store.master), _lib.ptr(store.exp_avg), _lib.ptr(store.exp_avg_sq), _lib.ptr(self._shard_grad),
             params.ptr_array, self.world, _lib.ptr(self._sumsq), _lib.ptr(self._norm), ll(store.lo),
             ll(store.shard_size), f(lr), f(betas[0]), f(betas[1]), f(eps), f(weight_decay), store.step_count,
-            f(max_grad_norm if max_grad_norm else 0.0), f(1.0 / self.world), _lib.stream()), "sb_adamw_allgather")
+            f(max_grad_norm if max_grad_norm else 0.0), f(grad_scale if grad_scale is not None else 1.0 / self.world),
+            _lib.stream()), "sb_adamw_allgather")
         self.barrier()                                  # every peer's stores into my replica have landed
         return self._norm[0]
 

@@ -305,3 +305,23 @@ def test_resume_falls_back_when_the_latest_checkpoint_is_damaged(tmp_path):
                 "data.max_response_length=16"], tmp_path / "log2")
     assert out.returncode == 0, out.stderr[-3000:]
     assert [r["step"] for r in _metrics(tmp_path / "log2")] == [2, 3]      # continued after step 1
+
+
+def test_grpo_with_hybrid_sharding(tmp_path):
+    """``fsdp_config.fsdp_size=2`` on four ranks (FSDP's HYBRID_SHARD): state sharded inside blocks of two ranks and
+    replicated across the blocks, with the replicated-weights store and with the parameter-sharded one; save and
+    resume.  (That the stores compute the same update as four-way sharding is checked on the stores directly.)"""
+    base = ["trainer.n_gpus_per_node=4", "data.max_response_length=16",
+            "actor_rollout_ref.model.enable_gradient_checkpointing=True",
+            "actor_rollout_ref.actor.fsdp_config.fsdp_size=2"]
+    out = _run([*base, "trainer.total_training_steps=1"], tmp_path / "zero2")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    assert _metrics(tmp_path / "zero2")[0]["actor/grad_norm"] > 0
+    z3 = [*base, "actor_rollout_ref.actor.fsdp_config.sharding=zero3", f"trainer.default_local_dir={tmp_path / 'c'}"]
+    out = _run([*z3, "trainer.total_training_steps=2", "trainer.save_freq=2"], tmp_path / "zero3")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "zero3")
+    assert [r["step"] for r in m] == [1, 2] and all(r["actor/grad_norm"] > 0 for r in m)
+    out = _run([*z3, "trainer.total_training_steps=3", "trainer.resume_mode=auto"], tmp_path / "resume")
+    assert out.returncode == 0, out.stderr[-4000:]
+    assert [r["step"] for r in _metrics(tmp_path / "resume")] == [3]

@@ -200,6 +200,21 @@ def test_parameter_sharded_store_matches_replicated_on_gloo_ranks():
     assert "ZERO3_OK" in out.stdout
 
 
+def test_hybrid_sharded_stores_match_full_sharding_on_four_gloo_ranks():
+    """``fsdp_size=2`` on four ranks: state sharded inside pairs of ranks, replicated across the pairs; the replicated-
+    weights store and the parameter-sharded store both reproduce the four-way sharded run."""
+    import subprocess
+    import sys
+    from siirl_b200.execution.scheduler.launch import find_free_port
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, Z3_DEVICE="cpu", Z3_HYBRID="2", OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", str(find_free_port()), os.path.join(here, "zero3_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "ZERO3_OK" in out.stdout
+
+
 def test_reward_model_reencodes_with_its_own_tokenizer_and_template():
     """A reward model with another chat template scores the re-rendered conversation and the score lands on the
     response's last valid token of the policy batch."""
