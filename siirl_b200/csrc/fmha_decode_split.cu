@@ -239,90 +239,190 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
       if (t1 <= t0) continue;
       const int n = t1 - t0;
       float m_ref = -INFINITY, l_run = 0.f;
-      for (int t = 0; t < n; ++t) {
-        const uint32_t tn = tile_no + t;
-        const int sb_ = tn & 1;
-        if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb_], (tn >> 1) & 1, p.status, kStatusTimeoutEpilogue))) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        float sv[kSBlk];
-        {
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32(tmem_s + sb_ * 64, r0);
-          tmem_ld_32x32(tmem_s + sb_ * 64 + 32, r1);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            sv[i] = __uint_as_float(r0[i]) * p.scale_log2;
-            sv[32 + i] = __uint_as_float(r1[i]) * p.scale_log2;
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s_empty[sb_]);   // the MMA warp may overwrite this S buffer
-        const int kv0 = (t0 + t) * kSBlk;
-        if (kv0 + kSBlk > ctx) {
-#pragma unroll
-          for (int i = 0; i < kSBlk; ++i)
-            if (kv0 + i >= ctx) sv[i] = -INFINITY;
-        }
-        float m_tile = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < kSBlk; ++i) m_tile = fmaxf(m_tile, sv[i]);
-        if (t == 0) {
-          m_ref = (m_tile == -INFINITY) ? 0.f : m_tile;
-        } else if (__any_sync(0xffffffffu, row_valid && m_tile > m_ref + 8.f)) {
-          // rare: raise the reference maximum and rescale the accumulator; PV(t-1) must have finished
-          const uint32_t tp = tn - 1;
-          if (!__all_sync(0xffffffffu, mbar_wait(&p_empty[tp & 1], (tp >> 1) & 1, p.status, kStatusTimeoutEpilogue))) {
+      if (rep <= 8) {
+        // Narrow groups (at most 8 query heads per kv head): the scores are read in the accumulator-fragment layout,
+        // where the 4 threads 4r .. 4r+3 share row r and hold 16 of its 64 columns each, so the exponentials of a
+        // tile are spread over the whole warp instead of sitting in `rep` lanes.  m_ref is kept per row (equal in
+        // the 4 threads), l_run is a per-thread partial sum that is reduced at the end of the item.
+        const int frow = lane >> 2, fq = lane & 3;
+        const bool fvalid = frow < rep;
+        for (int t = 0; t < n; ++t) {
+          const uint32_t tn = tile_no + t;
+          const int sb_ = tn & 1;
+          if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb_], (tn >> 1) & 1, p.status, kStatusTimeoutEpilogue))) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const float m_new = fmaxf(m_ref, m_tile);
-          const float alpha = exp2f(m_ref - m_new);
-          l_run *= alpha;
-          m_ref = m_new;
-#pragma unroll 1
-          for (int cc = 0; cc < D / 32; ++cc) {
+          float sv[16];
+          {
             uint32_t r[32];
-            tmem_ld_32x32(tmem_o + cc * 32, r);
+            tmem_ld_16x256_x8(tmem_s + sb_ * 64, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tmem_o + cc * 32, r);
+            for (int i = 0; i < 8; ++i) {
+              sv[2 * i] = __uint_as_float(r[4 * i]) * p.scale_log2;
+              sv[2 * i + 1] = __uint_as_float(r[4 * i + 1]) * p.scale_log2;
+            }
           }
-          tmem_st_wait();
           tc_fence_before();
-        }
-        float rsum = 0.f;
-        uint32_t pk[kSBlk / 2];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_empty[sb_]);
+          const int kv0 = (t0 + t) * kSBlk;
+          if (kv0 + kSBlk > ctx) {
 #pragma unroll
-        for (int i = 0; i < kSBlk; i += 2) {
-          const float p0 = exp2f(sv[i] - m_ref), p1 = exp2f(sv[i + 1] - m_ref);
-          rsum += p0 + p1;
-          pk[i / 2] = pack_bf16x2(p0, p1);
-        }
-        l_run += rsum;
-        // P buffer (tn & 1) was read by PV(tn - 2)
-        if (!__all_sync(0xffffffffu, mbar_wait(&p_empty[sb_], ((tn >> 1) & 1) ^ 1, p.status, kStatusTimeoutEpilogue))) {
-          ok = false;
-          break;
-        }
-        {
-          uint8_t* prow = sP + sb_ * L::kPBytes + lane * 128;
-#pragma unroll
-          for (int piece = 0; piece < 8; ++piece) {
-            uint4 v = make_uint4(pk[piece * 4], pk[piece * 4 + 1], pk[piece * 4 + 2], pk[piece * 4 + 3]);
-            if (!row_valid) v = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(prow + ((piece ^ (lane & 7)) << 4)) = v;
+            for (int i = 0; i < 8; ++i) {
+              const int col = kv0 + 8 * i + 2 * fq;
+              if (col >= ctx) sv[2 * i] = -INFINITY;
+              if (col + 1 >= ctx) sv[2 * i + 1] = -INFINITY;
+            }
           }
+          float m_tile = -INFINITY;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) m_tile = fmaxf(m_tile, sv[i]);
+          m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 1));
+          m_tile = fmaxf(m_tile, __shfl_xor_sync(0xffffffffu, m_tile, 2));
+          if (t == 0) {
+            m_ref = (m_tile == -INFINITY) ? 0.f : m_tile;
+          } else if (__any_sync(0xffffffffu, fvalid && m_tile > m_ref + 8.f)) {
+            const uint32_t tp = tn - 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(&p_empty[tp & 1], (tp >> 1) & 1, p.status, kStatusTimeoutEpilogue))) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const float m_new = fmaxf(m_ref, m_tile);
+            const float alpha_f = exp2f(m_ref - m_new);
+            l_run *= alpha_f;
+            m_ref = m_new;
+            // the accumulator is addressed one row per lane: lane r takes the factor of row r from thread 4r
+            float alpha = __shfl_sync(0xffffffffu, alpha_f, (lane * 4) & 31);
+            if (lane >= 8) alpha = 1.f;
+#pragma unroll 1
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t r[32];
+              tmem_ld_32x32(tmem_o + cc * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32(tmem_o + cc * 32, r);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+          }
+          uint32_t pk[8];
+          float rsum = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float p0 = exp2f(sv[2 * i] - m_ref), p1 = exp2f(sv[2 * i + 1] - m_ref);
+            rsum += p0 + p1;
+            pk[i] = fvalid ? pack_bf16x2(p0, p1) : 0u;
+          }
+          l_run += rsum;
+          if (!__all_sync(0xffffffffu, mbar_wait(&p_empty[sb_], ((tn >> 1) & 1) ^ 1, p.status, kStatusTimeoutEpilogue))) {
+            ok = false;
+            break;
+          }
+          {
+            uint8_t* prow = sP + sb_ * L::kPBytes + frow * 128 + fq * 4;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) *reinterpret_cast<uint32_t*>(prow + ((i ^ frow) << 4)) = pk[i];
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_full[sb_]);
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[sb_]);
+        // row totals, then hand row r's statistics to lane r (the output below is addressed one row per lane)
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+        l_run = __shfl_sync(0xffffffffu, l_run, (lane * 4) & 31);
+        m_ref = __shfl_sync(0xffffffffu, m_ref, (lane * 4) & 31);
+      } else {
+        for (int t = 0; t < n; ++t) {
+          const uint32_t tn = tile_no + t;
+          const int sb_ = tn & 1;
+          if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb_], (tn >> 1) & 1, p.status, kStatusTimeoutEpilogue))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          float sv[kSBlk];
+          {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(tmem_s + sb_ * 64, r0);
+            tmem_ld_32x32(tmem_s + sb_ * 64 + 32, r1);
+            tmem_ld_wait();
+  #pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              sv[i] = __uint_as_float(r0[i]) * p.scale_log2;
+              sv[32 + i] = __uint_as_float(r1[i]) * p.scale_log2;
+            }
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_empty[sb_]);   // the MMA warp may overwrite this S buffer
+          const int kv0 = (t0 + t) * kSBlk;
+          if (kv0 + kSBlk > ctx) {
+  #pragma unroll
+            for (int i = 0; i < kSBlk; ++i)
+              if (kv0 + i >= ctx) sv[i] = -INFINITY;
+          }
+          float m_tile = -INFINITY;
+  #pragma unroll
+          for (int i = 0; i < kSBlk; ++i) m_tile = fmaxf(m_tile, sv[i]);
+          if (t == 0) {
+            m_ref = (m_tile == -INFINITY) ? 0.f : m_tile;
+          } else if (__any_sync(0xffffffffu, row_valid && m_tile > m_ref + 8.f)) {
+            // rare: raise the reference maximum and rescale the accumulator; PV(t-1) must have finished
+            const uint32_t tp = tn - 1;
+            if (!__all_sync(0xffffffffu, mbar_wait(&p_empty[tp & 1], (tp >> 1) & 1, p.status, kStatusTimeoutEpilogue))) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const float m_new = fmaxf(m_ref, m_tile);
+            const float alpha = exp2f(m_ref - m_new);
+            l_run *= alpha;
+            m_ref = m_new;
+  #pragma unroll 1
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t r[32];
+              tmem_ld_32x32(tmem_o + cc * 32, r);
+              tmem_ld_wait();
+  #pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32(tmem_o + cc * 32, r);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+          }
+          float rsum = 0.f;
+          uint32_t pk[kSBlk / 2];
+  #pragma unroll
+          for (int i = 0; i < kSBlk; i += 2) {
+            const float p0 = exp2f(sv[i] - m_ref), p1 = exp2f(sv[i + 1] - m_ref);
+            rsum += p0 + p1;
+            pk[i / 2] = pack_bf16x2(p0, p1);
+          }
+          l_run += rsum;
+          // P buffer (tn & 1) was read by PV(tn - 2)
+          if (!__all_sync(0xffffffffu, mbar_wait(&p_empty[sb_], ((tn >> 1) & 1) ^ 1, p.status, kStatusTimeoutEpilogue))) {
+            ok = false;
+            break;
+          }
+          {
+            uint8_t* prow = sP + sb_ * L::kPBytes + lane * 128;
+  #pragma unroll
+            for (int piece = 0; piece < 8; ++piece) {
+              uint4 v = make_uint4(pk[piece * 4], pk[piece * 4 + 1], pk[piece * 4 + 2], pk[piece * 4 + 3]);
+              if (!row_valid) v = make_uint4(0, 0, 0, 0);
+              *reinterpret_cast<uint4*>(prow + ((piece ^ (lane & 7)) << 4)) = v;
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_full[sb_]);
+        }
       }
       if (!ok) break;
       tile_no += n;

@@ -627,7 +627,29 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                                  "megatron.tensor_model_parallel_size (the engine runs on the trainer's slices)")
             if tp > 1:
                 self.tp_model = self._build_tp_model(tp, r.max_num_batched_tokens)
-            self.engine = RolloutEngine(self.tp_model or self.model, max_num_seqs=min(r.max_num_seqs, 1024),
+            if str(r.name).lower() == "hf" or self.model_config.is_mla:
+                # cache-free generation through the training forward: the reference's ``rollout.name=hf``, and the
+                # families whose attention has no paged-cache kernel (multi-head latent attention)
+                from .rollout.recompute_engine import RecomputeEngine
+                if tp > 1:
+                    raise ValueError("the cache-free rollout runs on whole weights: set "
+                                     "rollout.tensor_model_parallel_size=1")
+                self.engine = RecomputeEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024), max_model_len=max_len)
+            else:
+                self.engine = self._paged_engine(r, max_len)
+            if r.free_cache_engine and self._is_actor and getattr(self, "store", None) is not None \
+                    and getattr(r, "kv_borrow_grad_buffer", True) and hasattr(self.engine, "borrowed"):
+                # the fp32 gradient buffer is idle (and zeroed again) between an optimizer step and the next backward,
+                # exactly while the engine is awake: lend it to the KV arena
+                self.engine.borrowed = self.store.flat_grad
+            if r.free_cache_engine:
+                self.engine.sleep()
+                self._full_weights(False)
+        if self._embodied:
+            self._init_embodied()
+
+    def _paged_engine(self, r, max_len: int):
+        return RolloutEngine(self.tp_model or self.model, max_num_seqs=min(r.max_num_seqs, 1024),
                                         max_model_len=max_len,
                                         gpu_memory_utilization=r.gpu_memory_utilization,
                                         use_cuda_graph=not r.enforce_eager or self.device.type == "cuda",
@@ -637,16 +659,6 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                                         lockstep_group=self.group if getattr(self, "ep_ctx", None) is not None
                                         and self.world > 1 else None,
                                         **dict(r.engine_kwargs.native or {}))
-            if r.free_cache_engine and self._is_actor and getattr(self, "store", None) is not None \
-                    and getattr(r, "kv_borrow_grad_buffer", True):
-                # the fp32 gradient buffer is idle (and zeroed again) between an optimizer step and the next backward,
-                # exactly while the engine is awake: lend it to the KV arena
-                self.engine.borrowed = self.store.flat_grad
-            if r.free_cache_engine:
-                self.engine.sleep()
-                self._full_weights(False)
-        if self._embodied:
-            self._init_embodied()
 
     def _full_weights(self, on: bool) -> None:
         """Parameter-sharded actor: regather the shards into a whole replica for the rollout engine (the train ->

@@ -114,6 +114,23 @@ class DecoderConfig:
     # experts' output; ``shared_expert_gate`` multiplies it by sigmoid(x . g) (Qwen2-MoE)
     shared_expert_intermediate_size: int = 0
     shared_expert_gate: bool = False
+    # multi-head latent attention (DeepSeek-V2/V3, Kimi-VL's language model): keys and values are expanded from a
+    # ``kv_lora_rank``-wide latent; each head has ``qk_nope_head_dim`` position-free and ``qk_rope_head_dim`` rotary
+    # query/key dimensions (the rotary key is shared by all heads) and ``v_head_dim`` value dimensions
+    kv_lora_rank: int = 0
+    q_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    rope_interleave: bool = True
+    # DeepSeek-V3 routing: sigmoid scores, a per-expert selection bias, group-limited top-k, scaled weights; the first
+    # ``first_k_dense_replace`` layers keep a dense MLP
+    scoring_func: str = "softmax"
+    topk_method: str = "greedy"
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    first_k_dense_replace: int = 0
     # value head (critic / reward model): one scalar per token instead of the vocabulary head
     value_head: bool = False
     vision: Optional[VisionConfig] = None
@@ -138,6 +155,18 @@ class DecoderConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    @property
+    def rope_dim(self) -> int:
+        """Width the rotary embedding acts on."""
+        return self.qk_rope_head_dim if self.is_mla else self.head_dim
+
+    def layer_is_moe(self, layer_idx: int) -> bool:
+        return self.is_moe and layer_idx >= self.first_k_dense_replace
 
     @property
     def q_width(self) -> int:
@@ -177,6 +206,11 @@ class DecoderConfig:
             return cls._from_internvl_config(cfg)
         if mt in ("openvla", "prismatic"):
             return cls._from_openvla_config(cfg)
+        if mt == "kimi_vl":
+            out = cls.from_hf_config(dict(cfg["text_config"], model_type="deepseek_v3"))
+            out.model_type = "kimi_vl"
+            out.image_token_id = int(cfg.get("media_placeholder_token_id", 163605))
+            return out
         nh = text["num_attention_heads"]
         hd = text.get("head_dim") or text["hidden_size"] // nh
         rope_scaling = text.get("rope_scaling") or cfg.get("rope_scaling") or {}
@@ -205,6 +239,25 @@ class DecoderConfig:
             eos_token_id=(cfg.get("eos_token_id") if isinstance(cfg.get("eos_token_id"), int) else 2) or 2,
             pad_token_id=cfg.get("pad_token_id") or 0,
         )
+        if mt in ("deepseek_v3", "deepseek_v2"):
+            out.qkv_bias = bool(text.get("attention_bias", False))
+            out.kv_lora_rank = int(text.get("kv_lora_rank") or 0)
+            out.q_lora_rank = int(text.get("q_lora_rank") or 0)
+            out.qk_nope_head_dim = int(text.get("qk_nope_head_dim", 128))
+            out.qk_rope_head_dim = int(text.get("qk_rope_head_dim", 64))
+            out.v_head_dim = int(text.get("v_head_dim", 128))
+            out.rope_interleave = bool(text.get("rope_interleave", True))
+            out.head_dim = out.qk_nope_head_dim + out.qk_rope_head_dim
+            out.num_experts = int(text.get("n_routed_experts") or 0)
+            out.scoring_func = text.get("scoring_func", "sigmoid" if mt == "deepseek_v3" else "softmax")
+            out.topk_method = text.get("topk_method", "noaux_tc" if mt == "deepseek_v3" else "greedy")
+            out.n_group = int(text.get("n_group") or 1)
+            out.topk_group = int(text.get("topk_group") or 1)
+            out.routed_scaling_factor = float(text.get("routed_scaling_factor", 1.0))
+            out.first_k_dense_replace = int(text.get("first_k_dense_replace", 0))
+            out.norm_topk_prob = bool(text.get("norm_topk_prob", True))
+            out.shared_expert_intermediate_size = int(text.get("n_shared_experts") or 0) * out.moe_intermediate_size
+            out.shared_expert_gate = False
         if mt == "mixtral":
             # Mixtral's experts use the dense intermediate size; its router renormalises the top-k weights
             out.moe_intermediate_size = text.get("intermediate_size", 0)
@@ -299,7 +352,8 @@ class DecoderConfig:
     def to_hf_config(self) -> Dict[str, Any]:
         arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
                 "llama": "LlamaForCausalLM", "qwen2_5_vl": "Qwen2_5_VLForConditionalGeneration",
-                "mixtral": "MixtralForCausalLM", "qwen2_moe": "Qwen2MoeForCausalLM"}
+                "mixtral": "MixtralForCausalLM", "qwen2_moe": "Qwen2MoeForCausalLM",
+                "deepseek_v3": "DeepseekV3ForCausalLM"}
         d = {
             "architectures": [arch.get(self.model_type, "Qwen2ForCausalLM")], "model_type": self.model_type,
             "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
@@ -310,7 +364,19 @@ class DecoderConfig:
             "tie_word_embeddings": self.tie_word_embeddings, "hidden_act": "silu", "torch_dtype": "bfloat16",
             "eos_token_id": self.eos_token_id, "pad_token_id": self.pad_token_id,
         }
-        if self.is_moe and self.model_type == "mixtral":
+        if self.is_mla:
+            d.update(kv_lora_rank=self.kv_lora_rank, q_lora_rank=self.q_lora_rank or None,
+                     qk_nope_head_dim=self.qk_nope_head_dim, qk_rope_head_dim=self.qk_rope_head_dim,
+                     v_head_dim=self.v_head_dim, rope_interleave=self.rope_interleave, attention_bias=self.qkv_bias,
+                     qk_head_dim=self.qk_nope_head_dim + self.qk_rope_head_dim, head_dim=self.qk_rope_head_dim)
+        if self.is_moe and self.model_type in ("deepseek_v3", "kimi_vl"):
+            d.update(n_routed_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
+                     n_shared_experts=self.shared_expert_intermediate_size // max(self.moe_intermediate_size, 1),
+                     n_group=self.n_group, topk_group=self.topk_group, scoring_func=self.scoring_func,
+                     topk_method=self.topk_method, routed_scaling_factor=self.routed_scaling_factor,
+                     first_k_dense_replace=self.first_k_dense_replace)
+        elif self.is_moe and self.model_type == "mixtral":
             d.update(num_local_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      intermediate_size=self.moe_intermediate_size)
         elif self.is_moe:
@@ -406,6 +472,30 @@ PRESETS: Dict[str, DecoderConfig] = {
                                     num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, num_experts=8,
                                     num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=False,
                                     shared_expert_intermediate_size=96, shared_expert_gate=True),
+    # DeepSeek-V3 (671B, 37B active): MLA + 256 routed / 1 shared experts, 3 dense layers
+    "deepseek-v3": DecoderConfig(model_type="deepseek_v3", vocab_size=129280, hidden_size=7168, intermediate_size=18432,
+                                 num_layers=61, num_heads=128, num_kv_heads=128, head_dim=192, rope_theta=1e4,
+                                 qkv_bias=False, kv_lora_rank=512, q_lora_rank=1536, qk_nope_head_dim=128,
+                                 qk_rope_head_dim=64, v_head_dim=128, num_experts=256, num_experts_per_tok=8,
+                                 moe_intermediate_size=2048, shared_expert_intermediate_size=2048, n_group=8,
+                                 topk_group=4, scoring_func="sigmoid", topk_method="noaux_tc",
+                                 routed_scaling_factor=2.5, first_k_dense_replace=3, eos_token_id=1, pad_token_id=0),
+    # Moonlight-16B-A3B, the language model of Kimi-VL-A3B
+    "moonlight-16b-a3b": DecoderConfig(model_type="deepseek_v3", vocab_size=163840, hidden_size=2048,
+                                       intermediate_size=11264, num_layers=27, num_heads=16, num_kv_heads=16,
+                                       head_dim=192, rope_theta=5e4, qkv_bias=False, kv_lora_rank=512, q_lora_rank=0,
+                                       qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, num_experts=64,
+                                       num_experts_per_tok=6, moe_intermediate_size=1408,
+                                       shared_expert_intermediate_size=2816, n_group=1, topk_group=1,
+                                       scoring_func="sigmoid", topk_method="noaux_tc", routed_scaling_factor=2.446,
+                                       first_k_dense_replace=1, eos_token_id=163585, pad_token_id=163839),
+    "tiny-deepseek-v3": DecoderConfig(model_type="deepseek_v3", vocab_size=1024, hidden_size=128, intermediate_size=352,
+                                      num_layers=3, num_heads=4, num_kv_heads=4, head_dim=48, qkv_bias=False,
+                                      kv_lora_rank=32, q_lora_rank=48, qk_nope_head_dim=32, qk_rope_head_dim=16,
+                                      v_head_dim=32, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                                      shared_expert_intermediate_size=64, n_group=2, topk_group=1,
+                                      scoring_func="sigmoid", topk_method="noaux_tc", routed_scaling_factor=2.5,
+                                      first_k_dense_replace=1),
     "tiny-moe": DecoderConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=128, intermediate_size=352,
                               num_layers=2, num_heads=4, num_kv_heads=2, head_dim=32, qkv_bias=False, qk_norm=True,
                               num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64),

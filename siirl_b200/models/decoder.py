@@ -11,6 +11,7 @@ the HF names (q_proj/k_proj/v_proj, gate_proj/up_proj) for safetensors checkpoin
 from __future__ import annotations
 
 import contextlib
+import math
 
 from typing import List, Optional, Tuple
 
@@ -47,22 +48,44 @@ def _param(shape, dtype, device, std: float, gen: "_Init") -> nn.Parameter:
 
 
 class DecoderLayer(nn.Module):
-    def __init__(self, cfg: DecoderConfig, dtype, device, gen):
+    def __init__(self, cfg: DecoderConfig, dtype, device, gen, layer_idx: int = 0):
         super().__init__()
         H, std = cfg.hidden_size, cfg.initializer_range
         self.cfg = cfg
+        self.layer_idx = layer_idx
+        self.is_moe = cfg.layer_is_moe(layer_idx)
         self.input_layernorm = _param((H,), dtype, device, -1, gen)
-        self.qkv_proj_weight = _param((cfg.qkv_width, H), dtype, device, std, gen)
-        self.qkv_proj_bias = _param((cfg.qkv_width,), dtype, device, 0, gen) if cfg.qkv_bias else None
-        if cfg.qk_norm:
-            self.q_norm = _param((cfg.head_dim,), dtype, device, -1, gen)
-            self.k_norm = _param((cfg.head_dim,), dtype, device, -1, gen)
-        self.o_proj_weight = _param((H, cfg.q_width), dtype, device, std, gen)
+        if cfg.is_mla:
+            # multi-head latent attention: queries (optionally through a low-rank bottleneck), one projection to the
+            # KV latent plus the shared rotary key, and the expansion of the latent to per-head keys and values
+            nh, dq = cfg.num_heads, cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
+            if cfg.q_lora_rank > 0:
+                self.q_a_proj_weight = _param((cfg.q_lora_rank, H), dtype, device, std, gen)
+                self.q_a_layernorm = _param((cfg.q_lora_rank,), dtype, device, -1, gen)
+                self.q_b_proj_weight = _param((nh * dq, cfg.q_lora_rank), dtype, device, std, gen)
+            else:
+                self.q_proj_weight = _param((nh * dq, H), dtype, device, std, gen)
+            self.kv_a_proj_weight = _param((cfg.kv_lora_rank + cfg.qk_rope_head_dim, H), dtype, device, std, gen)
+            self.kv_a_layernorm = _param((cfg.kv_lora_rank,), dtype, device, -1, gen)
+            self.kv_b_proj_weight = _param((nh * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank), dtype,
+                                           device, std, gen)
+            self.o_proj_weight = _param((H, nh * cfg.v_head_dim), dtype, device, std, gen)
+            self.qkv_proj_bias = None
+        else:
+            self.qkv_proj_weight = _param((cfg.qkv_width, H), dtype, device, std, gen)
+            self.qkv_proj_bias = _param((cfg.qkv_width,), dtype, device, 0, gen) if cfg.qkv_bias else None
+            if cfg.qk_norm:
+                self.q_norm = _param((cfg.head_dim,), dtype, device, -1, gen)
+                self.k_norm = _param((cfg.head_dim,), dtype, device, -1, gen)
+            self.o_proj_weight = _param((H, cfg.q_width), dtype, device, std, gen)
         self.post_attention_layernorm = _param((H,), dtype, device, -1, gen)
-        if cfg.is_moe:
+        if self.is_moe:
             E, I = cfg.num_experts, cfg.moe_intermediate_size
             El = E // max(cfg.ep_size, 1)
             self.router_weight = _param((E, H), dtype, device, std, gen)
+            if cfg.topk_method == "noaux_tc":
+                # selection bias of the auxiliary-loss-free load balancing (kept in fp32, not trained by the loss)
+                self.router_bias = nn.Parameter(torch.zeros(E, dtype=torch.float32, device=device), requires_grad=False)
             if cfg.ep_size > 1:     # every rank draws its own experts: decorrelate the streams by expert range
                 layer_salt = int(torch.randint(0, 2 ** 30, (1,), generator=gen.gen, device=gen.gen.device).item())
                 gen = _Init(layer_salt + 7919 * (cfg.ep_rank + 1), device)
@@ -87,7 +110,7 @@ class DecoderLayer(nn.Module):
             # low-rank adapters (reference: peft LoRA, siirl/engine/fsdp_workers.py:824-895): y += (x A^T) B^T * alpha/r;
             # A is small random, B zero, so training starts at the base model; with the adapters switched off
             # (``lora_enabled = False``) the same module is the frozen reference policy
-            assert not cfg.is_moe and cfg.lora_rank % 8 == 0, "LoRA: dense layers, rank a multiple of 8"
+            assert not cfg.is_moe and not cfg.is_mla and cfg.lora_rank % 8 == 0, "LoRA: dense layers, rank a multiple of 8"
             r = cfg.lora_rank
             for name, (n_out, n_in) in {"qkv_proj": (cfg.qkv_width, H), "o_proj": (H, cfg.q_width),
                                         "gate_up_proj": (2 * cfg.intermediate_size, H),
@@ -111,6 +134,58 @@ class DecoderLayer(nn.Module):
             positions = positions[0]            # three equal rows from a multimodal processor of a 1-D rope family
         return ops.rope(qkv, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, positions, cos, sin, cfg.mrope_section)
 
+    def mla_qkv(self, x: torch.Tensor, positions: torch.Tensor, rope):
+        """Per-head queries / keys ``[T, nh, nope + rope]`` (rotary part rotated) and values ``[T, nh, v]`` of
+        multi-head latent attention (reference path: HF DeepseekV3Attention as patched by
+        siirl/models/transformers/kimi_vl.py:120-225)."""
+        cfg = self.cfg
+        T = x.shape[0]
+        nh, dn, dr, dv = cfg.num_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        if cfg.q_lora_rank > 0:
+            qa, _ = ops.rmsnorm(ops.linear(x, self.q_a_proj_weight), self.q_a_layernorm, cfg.rms_norm_eps)
+            q = ops.linear(qa, self.q_b_proj_weight)
+        else:
+            q = ops.linear(x, self.q_proj_weight)
+        q = q.reshape(T, nh, dn + dr)
+        ckv = ops.linear(x, self.kv_a_proj_weight)
+        c, k_pe = ckv[:, : cfg.kv_lora_rank], ckv[:, cfg.kv_lora_rank:]
+        cn, _ = ops.rmsnorm(c.contiguous(), self.kv_a_layernorm, cfg.rms_norm_eps)
+        kv = ops.linear(cn, self.kv_b_proj_weight).reshape(T, nh, dn + dv)
+        pe = torch.cat([q[:, :, dn:], k_pe.reshape(T, 1, dr)], 1)               # [T, nh + 1, dr]
+        if cfg.rope_interleave:
+            # checkpoints store rotary pairs interleaved (2i, 2i+1); the rotate-half kernel wants (i, i + dr/2)
+            pe = pe.reshape(T, nh + 1, dr // 2, 2).transpose(-1, -2).reshape(T, nh + 1, dr)
+        if positions.dim() == 2:
+            positions = positions[0]
+        cos, sin = rope
+        pe = ops.rope(pe.reshape(T, (nh + 1) * dr).contiguous(), nh + 1, dr, positions, cos, sin, None)
+        pe = pe.reshape(T, nh + 1, dr)
+        qf = torch.cat([q[:, :, :dn], pe[:, :nh]], -1)
+        kf = torch.cat([kv[:, :, :dn], pe[:, nh:].expand(T, nh, dr)], -1)
+        return qf, kf, kv[:, :, dn:]
+
+    def mla_attention(self, x: torch.Tensor, positions: torch.Tensor, info: SeqInfo, rope, causal=True) -> torch.Tensor:
+        from ..ops.attention import attention_wide_heads
+        cfg = self.cfg
+        q, k, v = self.mla_qkv(x, positions, rope)
+        scale = 1.0 / math.sqrt(cfg.qk_nope_head_dim + cfg.qk_rope_head_dim)
+        sp = getattr(self, "sp", None)
+        if sp is not None and sp.sp > 1:
+            # Ulysses (the switch the reference patches into Kimi-VL's attention,
+            # siirl/models/transformers/kimi_vl.py:172-221): rows are this rank's slice of the packed stream; one
+            # all-to-all hands every rank all rows of heads / sp heads, a second one brings the outputs back
+            T, nh, n = x.shape[0], cfg.num_heads, sp.sp
+            dq, dv = q.shape[-1], v.shape[-1]
+            packed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], -1)
+            parts = [(0, nh * dq), (nh * dq, nh * dq), (2 * nh * dq, nh * dv)]
+            full = sp.seq_to_heads(packed, parts)
+            Tf, hl = full.shape[0], nh // n
+            qf, kf, vf = full.split([hl * dq, hl * dq, hl * dv], -1)
+            a = attention_wide_heads(qf.reshape(Tf, hl, dq), kf.reshape(Tf, hl, dq), vf.reshape(Tf, hl, dv), info,
+                                     causal=causal, scale=scale).reshape(Tf, hl * dv)
+            return sp.heads_to_seq(a, [(0, nh * dv)])
+        return attention_wide_heads(q, k, v, info, causal=causal, scale=scale).reshape(x.shape[0], -1)
+
     def qkv_pre_rope(self, x: torch.Tensor) -> torch.Tensor:
         """QKV projection (+ per-head q/k RMSNorm for the Qwen3 family), before rotary embedding."""
         cfg = self.cfg
@@ -126,11 +201,14 @@ class DecoderLayer(nn.Module):
         return qkv
 
     def mlp(self, x: torch.Tensor) -> torch.Tensor:
-        if self.cfg.is_moe:
-            from .moe import moe_forward
+        if self.is_moe:
+            from .moe import moe_forward, route_deepseek
+            routed = None
+            if self.cfg.scoring_func == "sigmoid" or self.cfg.n_group > 1:
+                routed = route_deepseek(x, self.router_weight, getattr(self, "router_bias", None), self.cfg)
             y = moe_forward(x, self.router_weight, self.experts_gate_up, self.experts_down,
                             self.cfg.num_experts_per_tok, self.cfg.norm_topk_prob, ep=self.ep,
-                            pad_tokens=self.ep_pad_tokens)
+                            pad_tokens=self.ep_pad_tokens, routed=routed)
             if self.cfg.shared_expert_intermediate_size > 0:
                 s = ops.linear(ops.swiglu(ops.linear(x, self.shared_gate_up_weight)), self.shared_down_weight)
                 if self.cfg.shared_expert_gate:
@@ -157,6 +235,10 @@ class DecoderLayer(nn.Module):
         if tp is not None:
             from ..parallel.megatron_tp import enter_parallel_block
             x = enter_parallel_block(x, tp)
+        if cfg.is_mla:
+            attn_out = self._linear(self.mla_attention(x, positions, info, rope, causal), "o_proj")
+            x, h = ops.rmsnorm(attn_out, self.post_attention_layernorm, cfg.rms_norm_eps, residual=h)
+            return h, self.mlp(x)
         qkv = self.qkv(x, positions, rope)
         sp = getattr(self, "sp", None)
         if sp is not None and sp.sp > 1:
@@ -191,7 +273,7 @@ class DecoderLM(nn.Module):
         gen = _Init(seed, device)
         std = cfg.initializer_range
         self.embed_tokens = _param((cfg.vocab_size, cfg.hidden_size), dtype, device, std, gen)
-        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, gen) for _ in range(cfg.num_layers)])
+        self.layers = nn.ModuleList([DecoderLayer(cfg, dtype, device, gen, i) for i in range(cfg.num_layers)])
         self.norm = _param((cfg.hidden_size,), dtype, device, -1, gen)
         if cfg.value_head:
             self.value_head = _param((1, cfg.hidden_size), dtype, device, std, gen)
@@ -218,7 +300,7 @@ class DecoderLM(nn.Module):
         need = max(min_len, 1)
         if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need:
             n = max(need, min(self.cfg.max_position_embeddings, 8192))
-            self._rope = ops.rope_tables(self.cfg.head_dim, n, self.cfg.rope_theta, device=device)
+            self._rope = ops.rope_tables(self.cfg.rope_dim, n, self.cfg.rope_theta, device=device)
         return self._rope
 
     @property

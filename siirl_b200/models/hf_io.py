@@ -35,10 +35,21 @@ def _decoder_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
     for i, layer in enumerate(model.layers):
         p = f"model.layers.{i}."
         yield p + "input_layernorm.weight", layer.input_layernorm.data
-        w = layer.qkv_proj_weight.data
-        yield p + "self_attn.q_proj.weight", w[:qw]
-        yield p + "self_attn.k_proj.weight", w[qw:qw + kw]
-        yield p + "self_attn.v_proj.weight", w[qw + kw:]
+        if cfg.is_mla:
+            if cfg.q_lora_rank > 0:
+                yield p + "self_attn.q_a_proj.weight", layer.q_a_proj_weight.data
+                yield p + "self_attn.q_a_layernorm.weight", layer.q_a_layernorm.data
+                yield p + "self_attn.q_b_proj.weight", layer.q_b_proj_weight.data
+            else:
+                yield p + "self_attn.q_proj.weight", layer.q_proj_weight.data
+            yield p + "self_attn.kv_a_proj_with_mqa.weight", layer.kv_a_proj_weight.data
+            yield p + "self_attn.kv_a_layernorm.weight", layer.kv_a_layernorm.data
+            yield p + "self_attn.kv_b_proj.weight", layer.kv_b_proj_weight.data
+        else:
+            w = layer.qkv_proj_weight.data
+            yield p + "self_attn.q_proj.weight", w[:qw]
+            yield p + "self_attn.k_proj.weight", w[qw:qw + kw]
+            yield p + "self_attn.v_proj.weight", w[qw + kw:]
         if layer.qkv_proj_bias is not None:
             b = layer.qkv_proj_bias.data
             yield p + "self_attn.q_proj.bias", b[:qw]
@@ -49,10 +60,12 @@ def _decoder_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
             yield p + "self_attn.k_norm.weight", layer.k_norm.data
         yield p + "self_attn.o_proj.weight", layer.o_proj_weight.data
         yield p + "post_attention_layernorm.weight", layer.post_attention_layernorm.data
-        if cfg.is_moe:
+        if getattr(layer, "is_moe", cfg.is_moe):
             I = cfg.moe_intermediate_size
             names = _moe_names(cfg)
             yield p + names["router"], layer.router_weight.data
+            if hasattr(layer, "router_bias"):
+                yield p + "mlp.gate.e_score_correction_bias", layer.router_bias.data
             for e in range(cfg.num_experts):
                 gu = layer.experts_gate_up.data[e]
                 yield p + names["expert"].format(e=e, w=names["gate"]), gu[:I]
@@ -61,9 +74,10 @@ def _decoder_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
             if cfg.shared_expert_intermediate_size > 0:
                 Is = cfg.shared_expert_intermediate_size
                 sgu = layer.shared_gate_up_weight.data
-                yield p + "mlp.shared_expert.gate_proj.weight", sgu[:Is]
-                yield p + "mlp.shared_expert.up_proj.weight", sgu[Is:]
-                yield p + "mlp.shared_expert.down_proj.weight", layer.shared_down_weight.data
+                sh = "mlp.shared_experts." if cfg.is_mla or cfg.scoring_func == "sigmoid" else "mlp.shared_expert."
+                yield p + sh + "gate_proj.weight", sgu[:Is]
+                yield p + sh + "up_proj.weight", sgu[Is:]
+                yield p + sh + "down_proj.weight", layer.shared_down_weight.data
                 if cfg.shared_expert_gate:
                     yield p + "mlp.shared_expert_gate.weight", layer.shared_expert_gate_weight.data
         else:

@@ -6,6 +6,8 @@ expert and runs each expert's two GEMMs on the tcgen05 GEMM (the expert-parallel
 ``siirl_b200.parallel.expert_parallel``)."""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 import torch.nn.functional as F
 
@@ -25,6 +27,33 @@ def route_topk(x: torch.Tensor, router_weight: torch.Tensor, top_k: int, norm_to
 _LOCAL_EP = None
 
 
+def route_deepseek(x: torch.Tensor, router_weight: torch.Tensor, bias: Optional[torch.Tensor], cfg):
+    """DeepSeek-V3 router (public architecture; the reference reaches it through Megatron's ``moe_router_*`` options,
+    siirl/models/mcore/config_converter.py:187-275): sigmoid (or soft-max) scores; experts are CHOSEN by score plus
+    the load-balancing bias, restricted to the ``topk_group`` best of ``n_group`` expert groups (a group's rank is the
+    sum of its two best biased scores); the mixing WEIGHTS are the unbiased scores of the chosen experts, normalised
+    and multiplied by ``routed_scaling_factor``.  Returns ``(w [T, k] fp32, idx [T, k] int64)``."""
+    T = x.shape[0]
+    E, k = router_weight.shape[0], cfg.num_experts_per_tok
+    logits = x.float() @ router_weight.float().t()
+    scores = torch.sigmoid(logits) if cfg.scoring_func == "sigmoid" else torch.softmax(logits, -1)
+    choice = scores + bias.float()[None] if bias is not None else scores
+    if cfg.n_group > 1:
+        grp = choice.reshape(T, cfg.n_group, E // cfg.n_group)
+        if bias is not None:
+            rank = grp.topk(min(2, grp.shape[-1]), dim=-1).values.sum(-1)
+        else:
+            rank = grp.max(-1).values
+        keep = torch.zeros_like(rank).scatter_(1, rank.topk(cfg.topk_group, dim=-1, sorted=False).indices, 1.0)
+        mask = keep[:, :, None].expand(T, cfg.n_group, E // cfg.n_group).reshape(T, E) > 0
+        choice = choice.masked_fill(~mask, 0.0 if bias is not None else float("-inf"))
+    idx = choice.detach().topk(k, dim=-1, sorted=False).indices
+    w = scores.gather(1, idx)
+    if cfg.norm_topk_prob and k > 1:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return w * cfg.routed_scaling_factor, idx
+
+
 def _local_ep():
     global _LOCAL_EP
     if _LOCAL_EP is None:
@@ -35,7 +64,7 @@ def _local_ep():
 
 def moe_forward(x: torch.Tensor, router_weight: torch.Tensor, experts_gate_up: torch.Tensor,
                 experts_down: torch.Tensor, top_k: int, norm_topk_prob: bool = True, ep=None,
-                pad_tokens: int = 0) -> torch.Tensor:
+                pad_tokens: int = 0, routed=None) -> torch.Tensor:
     """``x [T, H]`` -> ``[T, H]``.  ``experts_gate_up [E_local, 2I, H]``, ``experts_down [E_local, H, I]`` hold the
     experts hosted by this rank (all of them without expert parallelism); ``router_weight [E, H]`` is replicated.
     One dispatch (rows pulled into the expert-sorted, 128-padded layout), two grouped GEMMs around SwiGLU, one
@@ -44,7 +73,8 @@ def moe_forward(x: torch.Tensor, router_weight: torch.Tensor, experts_gate_up: t
     ep = ep if ep is not None else _local_ep()
     T, H = x.shape
     E = router_weight.shape[0]
-    w, idx = route_topk(x, router_weight, top_k, norm_topk_prob)
+    # ``routed``: (weights, expert ids) from a family-specific router instead of soft-max top-k
+    w, idx = routed if routed is not None else route_topk(x, router_weight, top_k, norm_topk_prob)
     if ep.world > 1 and pad_tokens:
         # ranks hold different token counts: pad to the static bound; padding rows are routed nowhere (id -1)
         assert T <= pad_tokens, f"{T} tokens exceed the expert-parallel bound {pad_tokens}"

@@ -137,3 +137,33 @@ def attention_packed(qkv: torch.Tensor, info: SeqInfo, n_heads: int, n_kv_heads:
     padded = _pad_heads(qkv, n_heads + 2 * n_kv_heads, head_dim, d_pad)
     out = _AttnFn.apply(padded, info, n_heads, n_kv_heads, d_pad, causal, scale, q_start)
     return out.reshape(T, n_heads, d_pad)[..., :head_dim].reshape(T, n_heads * head_dim)
+
+
+def attention_wide_heads(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, info: SeqInfo, causal: bool = True,
+                         scale: Optional[float] = None) -> torch.Tensor:
+    """Attention with query/key width and value width outside the tcgen05 kernels' set (multi-head latent attention:
+    192 / 128).  ``q, k [T, nh, dq]``, ``v [T, nh, dv]`` packed -> ``[T, nh, dv]``.  On GPUs this is a library call
+    (the flash-attn variable-length kernel with the values zero-padded to ``dq``, as the reference does in
+    siirl/models/transformers/kimi_vl.py:172-221; PyTorch's fused attention per sequence when flash-attn is absent);
+    on CPU the eager statement."""
+    T, nh, dq = q.shape
+    dv = v.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(dq)
+    if not q.is_cuda:
+        return ref.attention_varlen(q, k, v, torch.tensor(info.cu_seqlens_cpu), causal=causal, scale=scale).to(q.dtype)
+    import torch.nn.functional as F
+    vp = F.pad(v, (0, dq - dv)) if dv < dq else v
+    try:
+        from flash_attn import flash_attn_varlen_func
+        cu = torch.tensor(info.cu_seqlens_cpu, dtype=torch.int32, device=q.device)
+        mx = max(info.seqlens) if len(info.seqlens) else 0
+        out = flash_attn_varlen_func(q, k, vp, cu, cu, mx, mx, softmax_scale=scale, causal=causal)
+    except ImportError:
+        outs, at = [], 0
+        for n in info.seqlens:
+            o = F.scaled_dot_product_attention(q[at:at + n].transpose(0, 1)[None], k[at:at + n].transpose(0, 1)[None],
+                                               vp[at:at + n].transpose(0, 1)[None], is_causal=causal, scale=scale)
+            outs.append(o[0].transpose(0, 1))
+            at += n
+        out = torch.cat(outs) if outs else q.new_zeros(0, nh, dq)
+    return out[..., :dv]

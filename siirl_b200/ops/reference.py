@@ -63,12 +63,12 @@ def attention_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqle
                      causal: bool = True, scale: Optional[float] = None,
                      window: Optional[int] = None) -> torch.Tensor:
     """Packed variable-length attention.  q [T, Hq, D], k/v [T, Hkv, D]; sequences are
-    the slices cu_seqlens[i]:cu_seqlens[i+1].  GQA by head repetition.  Returns [T, Hq, D]."""
+    the slices cu_seqlens[i]:cu_seqlens[i+1].  GQA by head repetition.  Returns [T, Hq, Dv]."""
     T, hq, D = q.shape
     hkv = k.shape[1]
     rep = hq // hkv
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    out = torch.empty_like(q)
+    out = q.new_empty(T, hq, v.shape[-1])      # the value width may differ from the query / key width
     cs = cu_seqlens.tolist()
     for i in range(len(cs) - 1):
         a, b = cs[i], cs[i + 1]

@@ -257,8 +257,8 @@ class EngineArguments:
 
 @dataclass
 class RolloutArguments:
-    # "native" is this framework's paged-KV engine; the reference names (vllm, sglang, hf) are
-    # accepted and all map to it.
+    # "native" is this framework's paged-KV engine; the reference names vllm and sglang map to it, "hf" selects the
+    # cache-free engine that generates through the training forward (engine/rollout/recompute_engine.py).
     name: str = "vllm"
     temperature: float = 1.0
     top_k: int = -1

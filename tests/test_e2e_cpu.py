@@ -325,3 +325,19 @@ def test_grpo_with_hybrid_sharding(tmp_path):
     out = _run([*z3, "trainer.total_training_steps=3", "trainer.resume_mode=auto"], tmp_path / "resume")
     assert out.returncode == 0, out.stderr[-4000:]
     assert [r["step"] for r in _metrics(tmp_path / "resume")] == [3]
+
+
+def test_grpo_with_deepseek_v3_family(tmp_path):
+    """Multi-head latent attention + DeepSeek-V3 routing (sigmoid scores, selection bias, expert groups, shared expert,
+    a dense first layer) through rollout (cache-free engine), scoring and training on two ranks; save and resume."""
+    ck = tmp_path / "c"
+    extra = ["actor_rollout_ref.model.arch_preset=tiny-deepseek-v3", "data.max_response_length=8",
+             f"trainer.default_local_dir={ck}"]
+    out = _run([*extra, "trainer.total_training_steps=2", "trainer.save_freq=2"], tmp_path / "log1")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log1")
+    assert [r["step"] for r in m] == [1, 2]
+    assert all(r["actor/grad_norm"] > 0 and r["actor/grad_norm"] == r["actor/grad_norm"] for r in m)
+    out = _run([*extra, "trainer.total_training_steps=3", "trainer.resume_mode=auto"], tmp_path / "log2")
+    assert out.returncode == 0, out.stderr[-4000:]
+    assert [r["step"] for r in _metrics(tmp_path / "log2")] == [3]

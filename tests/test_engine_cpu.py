@@ -284,3 +284,22 @@ def test_chunked_prefill_and_prefix_cache_give_the_same_tokens(tiny):
         outs = small.generate(ps, SamplingParams(n=1, temperature=0.0, max_new_tokens=4, ignore_eos=True))
         assert len(outs) == 2 and all(len(o.token_ids) == 4 for o in outs)
     assert small.alloc.num_free == 14
+
+
+def test_cache_free_engine_equals_the_paged_engine_and_serves_latent_attention():
+    """``rollout.name=hf``: generation through the training forward gives the paged engine's greedy tokens and
+    log-probs; it also serves the multi-head-latent-attention family, which has no paged-cache kernel."""
+    from siirl_b200.engine.rollout.recompute_engine import RecomputeEngine
+    model = build_model(get_config("tiny"), dtype=torch.float32, device="cpu", seed=1)
+    prompts = [[5, 6, 7, 8], [9, 10, 11], [100, 200, 300, 400, 500]]
+    sp = SamplingParams(n=2, temperature=0.0, max_new_tokens=7, eos_token_id=2)
+    a = RecomputeEngine(model, max_num_seqs=4).generate(prompts, sp)
+    eng = RolloutEngine(model, max_num_seqs=8, max_model_len=64)
+    eng.wake_up()
+    b = eng.generate(prompts, sp)
+    assert [(o.prompt_index, o.sample_index, o.token_ids) for o in a] == \
+        [(o.prompt_index, o.sample_index, o.token_ids) for o in b]
+    assert max(abs(x - y) for o, p in zip(a, b) for x, y in zip(o.logprobs, p.logprobs)) < 1e-5
+    mla = build_model(get_config("tiny-deepseek-v3"), dtype=torch.float32, device="cpu", seed=2)
+    outs = RecomputeEngine(mla).generate(prompts[:2], SamplingParams(n=1, temperature=1.0, max_new_tokens=5, seed=3))
+    assert [len(o.token_ids) for o in outs] == [5, 5] and all(o.finish_reason == "length" for o in outs)

@@ -17,10 +17,14 @@ def _logprobs_ours(model, ids):
     return torch.log_softmax(logits.float(), -1)
 
 
-@pytest.mark.parametrize("preset", ["tiny", "tiny-mixtral", "tiny-qwen2-moe", "tiny-moe"])
+@pytest.mark.parametrize("preset", ["tiny", "tiny-mixtral", "tiny-qwen2-moe", "tiny-moe", "tiny-deepseek-v3"])
 def test_family_matches_transformers(preset, tmp_path):
     cfg = get_config(preset)
     model = build_model(cfg, dtype=torch.float32, device="cpu", seed=4)
+    with torch.no_grad():                      # a non-trivial selection bias where the family has one
+        for n, p in model.named_parameters():
+            if n.endswith("router_bias"):
+                p.copy_(0.05 * torch.randn(p.shape, generator=torch.Generator().manual_seed(7)))
     save_hf_model(model, str(tmp_path))
     try:
         hf = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path), torch_dtype=torch.float32,

@@ -144,6 +144,25 @@ def main():
     if cuda:
         torch.cuda.synchronize()
         lib.check_status()
+    # 5b. multi-head latent attention (DeepSeek-V3 / Kimi-VL language model) under the same switch: the three
+    #     operands have different head widths (query / key 48, value 32 in the tiny configuration)
+    if not cuda:
+        cfg5b = get_config("tiny-deepseek-v3")
+        mla_full = build_model(cfg5b, dtype=dtype, device=dev, seed=11)
+        mla_sp = build_model(cfg5b, dtype=dtype, device=dev, seed=11)
+        wide = cfg5b.num_heads * (2 * (cfg5b.qk_nope_head_dim + cfg5b.qk_rope_head_dim) + cfg5b.v_head_dim)
+        mla_sp.attach_sequence_parallel(UlyssesSP(dist.group.WORLD, comm, max_elems=512 * wide))
+        hb_full = mla_full.forward_hidden(ids, info.positions, info)
+        hb_loc = mla_sp.forward_hidden(ids, info.positions, info)
+        assert (hb_loc[:n_real].float() - hb_full[lo:lo + n_real].float()).abs().max().item() < 1e-4, "MLA SP rows"
+        (hb_full.float() * coef.float()).sum().backward()
+        (hb_loc[:n_real].float() * coef[lo:lo + n_real].float()).sum().backward()
+        pf, ps = dict(mla_full.named_parameters()), dict(mla_sp.named_parameters())
+        for n5 in ("layers.0.kv_b_proj_weight", "layers.1.q_b_proj_weight", "layers.2.kv_a_proj_weight"):
+            g2 = (ps[n5].grad if ps[n5].grad is not None else ps[n5].main_grad).float().clone()
+            dist.all_reduce(g2)
+            g1 = (pf[n5].grad if pf[n5].grad is not None else pf[n5].main_grad).float()
+            assert (g1 - g2).abs().max().item() < 1e-3, f"MLA SP grad {n5}"
     # 6. ring (context-parallel) attention equals causal attention over the whole sequences, values and gradients
     from siirl_b200.ops.attention import attention_packed
     from siirl_b200.parallel.ring_attention import RingContext, ring_attention, split_for_context_parallel
