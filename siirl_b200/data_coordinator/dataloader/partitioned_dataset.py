@@ -141,7 +141,7 @@ class PartitionedRLHFDataset(Dataset):
             from ...models.vision_processor import make_vl_processor
             m = self._full_config.actor_rollout_ref.model
             mcfg = get_config(m.arch_preset or m.path, dict(m.override_config or {}))
-            if mcfg.vision is None and mcfg.vit is None:
+            if mcfg.vision is None and mcfg.vit is None and mcfg.moonvit is None:
                 raise ValueError("the dataset has images but the model has no vision tower")
             self._vl = make_vl_processor(mcfg, m.image_min_pixels, m.image_max_pixels)
         return self._vl

@@ -58,6 +58,21 @@ class ViTConfig:
 
 
 @dataclass
+class MoonViTConfig:
+    """Kimi-VL's native-resolution vision tower: learnable 2-D position table interpolated to each image's grid,
+    rotary positions over (x, y), LayerNorm / GELU blocks, 2 x 2 patch merge into the projector."""
+    patch_size: int = 14
+    init_pos_emb_height: int = 64
+    init_pos_emb_width: int = 64
+    hidden_size: int = 1152
+    num_heads: int = 16
+    intermediate_size: int = 4304
+    depth: int = 27
+    merge: int = 2
+    in_channels: int = 3
+
+
+@dataclass
 class PrismaticConfig:
     """OpenVLA's vision side: a DINOv2 ViT and (fused backbone) a SigLIP ViT over the same image, patch features
     concatenated along the channel axis, then a GELU MLP into the language model width."""
@@ -144,6 +159,7 @@ class DecoderConfig:
     # OpenVLA / OpenVLA-OFT: Prismatic vision backbone; actions are the last ``n_action_bins`` ids below
     # ``action_vocab_size`` (the tokenizer's size: the embedding matrix is padded beyond it)
     prismatic: Optional[PrismaticConfig] = None
+    moonvit: Optional[MoonViTConfig] = None
     action_vocab_size: int = 0
     n_action_bins: int = 256
     image_token_id: int = 151655
@@ -210,6 +226,13 @@ class DecoderConfig:
             out = cls.from_hf_config(dict(cfg["text_config"], model_type="deepseek_v3"))
             out.model_type = "kimi_vl"
             out.image_token_id = int(cfg.get("media_placeholder_token_id", 163605))
+            vc = cfg.get("vision_config", {})
+            mk = vc.get("merge_kernel_size", [2, 2])
+            out.moonvit = MoonViTConfig(
+                patch_size=vc.get("patch_size", 14), init_pos_emb_height=vc.get("init_pos_emb_height", 64),
+                init_pos_emb_width=vc.get("init_pos_emb_width", 64), hidden_size=vc.get("hidden_size", 1152),
+                num_heads=vc.get("num_attention_heads", 16), intermediate_size=vc.get("intermediate_size", 4304),
+                depth=vc.get("num_hidden_layers", 27), merge=int(mk[0] if isinstance(mk, (list, tuple)) else mk))
             return out
         nh = text["num_attention_heads"]
         hd = text.get("head_dim") or text["hidden_size"] // nh
@@ -386,6 +409,17 @@ class DecoderConfig:
                 d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
         if self.mrope_section:
             d["rope_scaling"] = {"type": "mrope", "mrope_section": self.mrope_section}
+        if self.moonvit is not None:
+            mv = self.moonvit
+            text = dict(d, model_type="deepseek_v3")
+            text.pop("architectures", None)
+            return {"architectures": ["KimiVLForConditionalGeneration"], "model_type": "kimi_vl", "text_config": text,
+                    "vision_config": {"model_type": "moonvit", "patch_size": mv.patch_size,
+                                      "init_pos_emb_height": mv.init_pos_emb_height,
+                                      "init_pos_emb_width": mv.init_pos_emb_width, "hidden_size": mv.hidden_size,
+                                      "num_attention_heads": mv.num_heads, "intermediate_size": mv.intermediate_size,
+                                      "num_hidden_layers": mv.depth, "merge_kernel_size": [mv.merge, mv.merge]},
+                    "media_placeholder_token_id": self.image_token_id, "torch_dtype": "bfloat16"}
         if self.prismatic is not None:
             pc = self.prismatic
             towers = [pc.featurizer] + ([pc.fused_featurizer] if pc.fused_featurizer else [])
@@ -489,6 +523,24 @@ PRESETS: Dict[str, DecoderConfig] = {
                                        shared_expert_intermediate_size=2816, n_group=1, topk_group=1,
                                        scoring_func="sigmoid", topk_method="noaux_tc", routed_scaling_factor=2.446,
                                        first_k_dense_replace=1, eos_token_id=163585, pad_token_id=163839),
+    # Kimi-VL-A3B: MoonViT-SO-400M + Moonlight-16B-A3B
+    "kimi-vl-a3b": DecoderConfig(model_type="kimi_vl", vocab_size=163840, hidden_size=2048, intermediate_size=11264,
+                                 num_layers=27, num_heads=16, num_kv_heads=16, head_dim=192, rope_theta=8e5,
+                                 qkv_bias=False, kv_lora_rank=512, q_lora_rank=0, qk_nope_head_dim=128,
+                                 qk_rope_head_dim=64, v_head_dim=128, num_experts=64, num_experts_per_tok=6,
+                                 moe_intermediate_size=1408, shared_expert_intermediate_size=2816, n_group=1,
+                                 topk_group=1, scoring_func="sigmoid", topk_method="noaux_tc",
+                                 routed_scaling_factor=2.446, first_k_dense_replace=1, moonvit=MoonViTConfig(),
+                                 image_token_id=163605, eos_token_id=163585, pad_token_id=163839),
+    "tiny-kimi-vl": DecoderConfig(model_type="kimi_vl", vocab_size=1024, hidden_size=128, intermediate_size=352,
+                                  num_layers=2, num_heads=4, num_kv_heads=4, head_dim=48, qkv_bias=False,
+                                  kv_lora_rank=32, q_lora_rank=0, qk_nope_head_dim=32, qk_rope_head_dim=16,
+                                  v_head_dim=32, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                                  shared_expert_intermediate_size=128, scoring_func="sigmoid",
+                                  topk_method="noaux_tc", routed_scaling_factor=2.0, first_k_dense_replace=1,
+                                  moonvit=MoonViTConfig(init_pos_emb_height=8, init_pos_emb_width=8, hidden_size=64,
+                                                        num_heads=2, intermediate_size=128, depth=2),
+                                  image_token_id=1000),
     "tiny-deepseek-v3": DecoderConfig(model_type="deepseek_v3", vocab_size=1024, hidden_size=128, intermediate_size=352,
                                       num_layers=3, num_heads=4, num_kv_heads=4, head_dim=48, qkv_bias=False,
                                       kv_lora_rank=32, q_lora_rank=48, qk_nope_head_dim=32, qk_rope_head_dim=16,

@@ -288,6 +288,9 @@ class DecoderLM(nn.Module):
         if cfg.vision is not None:
             from .vision import VisionTower
             self.vision = VisionTower(cfg.vision, dtype, device, gen)
+        elif cfg.moonvit is not None:
+            from .moonvit import MoonViT
+            self.vision = MoonViT(cfg.moonvit, cfg.hidden_size, dtype, device, gen)
         elif cfg.prismatic is not None:
             from .embodied.prismatic import PrismaticVision
             self.vision = PrismaticVision(cfg.prismatic, cfg.hidden_size, dtype, device, gen)

@@ -96,7 +96,7 @@ def _decoder_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
 # ---- family-specific names ----------------------------------------------------------------------------------------
 def _llm_names(cfg: DecoderConfig) -> Tuple[str, str]:
     """(prefix replacing ``model.``, name of the vocabulary head) of the language model inside a checkpoint."""
-    if cfg.prismatic is not None:
+    if cfg.prismatic is not None or cfg.moonvit is not None:
         return "language_model.model.", "language_model.lm_head.weight"
     if cfg.vit is not None and cfg.hf_naming == "internvl_chat":
         return "language_model.model.", ("language_model.output.weight" if cfg.llm_type == "internlm2"
@@ -210,6 +210,44 @@ def _prismatic_state(vision) -> Iterator[Tuple[str, torch.Tensor]]:
         yield f"projector.fc{i + 1}.bias", getattr(vision.projector, f"fc{i}_bias").data
 
 
+class _RowPermuted:
+    """A parameter held with permuted rows: ``memory[i] = checkpoint[perm[i]]``."""
+
+    def __init__(self, dst: torch.Tensor, perm: torch.Tensor):
+        self.dst, self.perm = dst, perm
+
+    def load(self, src: torch.Tensor) -> None:
+        self.dst.copy_(src.to(self.dst.dtype)[self.perm.to(src.device)])
+
+    def export(self) -> torch.Tensor:
+        return self.dst[torch.argsort(self.perm).to(self.dst.device)]
+
+
+def _moonvit_state(vision) -> Iterator[Tuple[str, object]]:
+    """Kimi-VL's tower and projector under the checkpoint's names; ``wqkv`` rows leave the in-memory rotary layout
+    (siirl_b200/models/moonvit.py) for the checkpoint's interleaved one."""
+    from .moonvit import qk_row_permutation
+    vc = vision.cfg
+    P = vc.patch_size
+    perm = qk_row_permutation(vc)
+    yield "vision_tower.patch_embed.proj.weight", vision.patch_embed_weight.data[:, :vision.patch_dim].unflatten(
+        1, (vc.in_channels, P, P))
+    yield "vision_tower.patch_embed.proj.bias", vision.patch_embed_bias.data
+    yield "vision_tower.patch_embed.pos_emb.weight", vision.pos_emb.data
+    for i, b in enumerate(vision.blocks):
+        p = f"vision_tower.encoder.blocks.{i}."
+        for ours, theirs in (("norm0", "norm0"), ("norm1", "norm1"), ("wo", "wo"), ("fc0", "mlp.fc0"), ("fc1", "mlp.fc1")):
+            yield p + theirs + ".weight", getattr(b, ours + "_weight").data
+            yield p + theirs + ".bias", getattr(b, ours + "_bias").data
+        yield p + "wqkv.weight", _RowPermuted(b.wqkv_weight.data, perm)
+        yield p + "wqkv.bias", _RowPermuted(b.wqkv_bias.data, perm)
+    yield "vision_tower.encoder.final_layernorm.weight", vision.final_norm_weight.data
+    yield "vision_tower.encoder.final_layernorm.bias", vision.final_norm_bias.data
+    for ours, theirs in (("pre_norm", "pre_norm"), ("linear_1", "linear_1"), ("linear_2", "linear_2")):
+        yield f"multi_modal_projector.{theirs}.weight", getattr(vision, ours + "_weight").data
+        yield f"multi_modal_projector.{theirs}.bias", getattr(vision, ours + "_bias").data
+
+
 def _qwen_visual_state(vision, prefix: str = "model.visual.") -> Iterator[Tuple[str, torch.Tensor]]:
     """Qwen2.5-VL tower under transformers' names (``visual.patch_embed.proj``: a 3-D convolution weight)."""
     vc = vision.cfg
@@ -262,7 +300,9 @@ def _hf_targets(model) -> Iterator[Tuple[str, object]]:
                 name = name.replace(ours, theirs)
         yield name, t
     vision = getattr(model, "vision", None)
-    if vision is not None and cfg.prismatic is not None:
+    if vision is not None and cfg.moonvit is not None:
+        yield from _moonvit_state(vision)
+    elif vision is not None and cfg.prismatic is not None:
         yield from _prismatic_state(vision)
     elif vision is not None and cfg.vit is not None:
         yield from _vit_state(vision, cfg.hf_naming)
@@ -273,7 +313,11 @@ def _hf_targets(model) -> Iterator[Tuple[str, object]]:
 def to_hf_state(model) -> Iterator[Tuple[str, torch.Tensor]]:
     """Every parameter under the names of the family's HF checkpoint (language model, then the vision tower)."""
     for name, t in _hf_targets(model):
-        yield name, (_fuse_wqkv(*t, model.cfg) if isinstance(t, tuple) else t)
+        if isinstance(t, tuple):
+            t = _fuse_wqkv(*t, model.cfg)
+        elif isinstance(t, _RowPermuted):
+            t = t.export()
+        yield name, t
 
 
 def save_hf_model(model, out_dir: str, max_shard_bytes: int = 4 << 30, tokenizer=None, tensors=None) -> None:
@@ -364,7 +408,9 @@ def load_hf_weights(model, path: str, strict: bool = True) -> None:
                 continue
             if name.endswith("embed_tokens.weight") or name.endswith("tok_embeddings.weight"):
                 embed = src
-            if isinstance(dst, tuple):
+            if isinstance(dst, _RowPermuted):
+                dst.load(src)
+            elif isinstance(dst, tuple):
                 for d, part in zip(dst, _split_wqkv(src, cfg)):
                     d.copy_(part.to(d.dtype))
             else:

@@ -137,6 +137,9 @@ class VLProcessor:
 def make_vl_processor(cfg: DecoderConfig, min_pixels: int = 32 * 32, max_pixels: int = 768 * 768):
     """Image processor matching the model's vision tower: native-resolution patches for Qwen2.5-VL, 448-pixel tiles for
     the InternVL family (``max_pixels`` bounds the tile count there)."""
+    if cfg.moonvit is not None:
+        from .moonvit import MoonViTProcessor
+        return MoonViTProcessor(cfg, min_pixels, max_pixels)
     if cfg.vit is not None:
         from .internvl import InternVLProcessor
         s = cfg.vit.image_size

@@ -286,3 +286,100 @@ def test_oft_parallel_decode_matches_scoring():
                                      image_mask=proc.image_mask(torch.tensor([0]), ids.numel()), zero_mask=zero)
             logp = torch.log_softmax(oft_action_logits(model, h[-A:], 1.0), -1)
         assert torch.allclose(logp.gather(1, (tok[i] - lo)[:, None])[:, 0], lp[i], atol=1e-5)
+
+
+def _moonvit_reference(sd, cfg, pixels, grids):
+    """Plain-PyTorch statement of the tower in the checkpoint's own layout: interleaved rotary pairs (even pair: x
+    position, odd pair: y position) applied as complex multiplications, full attention per image."""
+    import torch.nn.functional as F
+    g = lambda n: sd[n].float()  # noqa: E731
+    H, nh = cfg.hidden_size, cfg.num_heads
+    hd = H // nh
+    x = F.linear(pixels, g("vision_tower.patch_embed.proj.weight").reshape(H, -1), g("vision_tower.patch_embed.proj.bias"))
+    pe = g("vision_tower.patch_embed.pos_emb.weight")
+    pos, freqs = [], []
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 4)[: hd // 4].float() / hd))
+    for h, w in grids:
+        if (h, w) == tuple(pe.shape[:2]):
+            pos.append(pe.reshape(h * w, H))
+        else:
+            pos.append(F.interpolate(pe.permute(2, 0, 1)[None], size=(h, w), mode="bicubic")[0].permute(1, 2, 0).reshape(h * w, H))
+        xs = torch.arange(w).repeat(h).float()
+        ys = torch.arange(h).repeat_interleave(w).float()
+        fx = torch.polar(torch.ones(h * w, hd // 4), torch.outer(xs, inv))
+        fy = torch.polar(torch.ones(h * w, hd // 4), torch.outer(ys, inv))
+        freqs.append(torch.stack([fx, fy], -1).reshape(h * w, hd // 2))
+    x = x + torch.cat(pos)
+    fc = torch.cat(freqs)
+
+    def rot(t):                                   # [T, nh, hd]
+        c = torch.view_as_complex(t.float().reshape(t.shape[0], nh, hd // 2, 2))
+        return torch.view_as_real(c * fc[:, None, :]).reshape(t.shape[0], nh, hd)
+    for i in range(cfg.depth):
+        b = f"vision_tower.encoder.blocks.{i}."
+        y = F.layer_norm(x, (H,), g(b + "norm0.weight"), g(b + "norm0.bias"), 1e-5)
+        q, k, v = F.linear(y, g(b + "wqkv.weight"), g(b + "wqkv.bias")).reshape(-1, 3, nh, hd).unbind(1)
+        q, k = rot(q), rot(k)
+        outs, at = [], 0
+        for h, w in grids:
+            n = h * w
+            o = F.scaled_dot_product_attention(q[at:at + n].transpose(0, 1), k[at:at + n].transpose(0, 1),
+                                               v[at:at + n].transpose(0, 1))
+            outs.append(o.transpose(0, 1).reshape(n, H))
+            at += n
+        x = x + F.linear(torch.cat(outs), g(b + "wo.weight"), g(b + "wo.bias"))
+        y = F.layer_norm(x, (H,), g(b + "norm1.weight"), g(b + "norm1.bias"), 1e-5)
+        x = x + F.linear(F.gelu(F.linear(y, g(b + "mlp.fc0.weight"), g(b + "mlp.fc0.bias")), approximate="tanh"),
+                         g(b + "mlp.fc1.weight"), g(b + "mlp.fc1.bias"))
+    x = F.layer_norm(x, (H,), g("vision_tower.encoder.final_layernorm.weight"), g("vision_tower.encoder.final_layernorm.bias"), 1e-5)
+    x = F.layer_norm(x, (H,), g("multi_modal_projector.pre_norm.weight"), g("multi_modal_projector.pre_norm.bias"), 1e-5)
+    merged, at = [], 0
+    for h, w in grids:
+        t = x[at:at + h * w].reshape(h // 2, 2, w // 2, 2, H).permute(0, 2, 1, 3, 4).reshape(h * w // 4, 4 * H)
+        merged.append(t)
+        at += h * w
+    y = F.linear(torch.cat(merged), g("multi_modal_projector.linear_1.weight"), g("multi_modal_projector.linear_1.bias"))
+    return F.linear(F.gelu(y), g("multi_modal_projector.linear_2.weight"), g("multi_modal_projector.linear_2.bias"))
+
+
+def test_kimi_vl_tower_checkpoint_layout_and_language_model(tmp_path):
+    """MoonViT (interpolated position table, (x, y) rotary pairs held permuted in memory, 2 x 2 merge, projector)
+    against the tower's math stated on the exported weights in the checkpoint's interleaved layout; the checkpoint
+    round-trips; image features land on the placeholders of the multi-head-latent-attention language model."""
+    from safetensors.torch import load_file
+    from siirl_b200.models.hf_io import to_hf_state
+    from siirl_b200.models.moonvit import MoonViTProcessor
+    cfg = get_config("tiny-kimi-vl")
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=13)
+    with torch.no_grad():
+        for n, p in model.vision.named_parameters():
+            if n.endswith("bias"):
+                p.copy_(0.2 * torch.randn(p.shape, generator=torch.Generator().manual_seed(len(n))))
+    save_hf_model(model, str(tmp_path))
+    sd = load_file(str(tmp_path / "model.safetensors"))
+    assert {"vision_tower.patch_embed.pos_emb.weight", "vision_tower.encoder.blocks.1.wqkv.bias",
+            "multi_modal_projector.linear_2.weight", "language_model.model.layers.0.self_attn.kv_a_proj_with_mqa.weight",
+            "language_model.model.layers.1.mlp.gate.e_score_correction_bias", "language_model.lm_head.weight"} <= set(sd)
+    grids = [(4, 6), (8, 8), (2, 2)]
+    grid = torch.tensor([[1, h, w] for h, w in grids])
+    pixels = torch.randn(sum(h * w for h, w in grids), 588, generator=torch.Generator().manual_seed(4))
+    with torch.no_grad():
+        got = model.vision(pixels, grid)
+        want = _moonvit_reference(sd, cfg.moonvit, pixels, grids)
+    assert got.shape == (sum(h * w for h, w in grids) // 4, cfg.hidden_size)
+    assert torch.allclose(got, want, atol=3e-5), (got - want).abs().max()
+    cfg2 = DecoderConfig.from_pretrained(str(tmp_path))
+    assert cfg2.moonvit is not None and cfg2.is_mla and cfg2.moonvit.depth == 2 and cfg2.image_token_id == 1000
+    again = build_model(cfg2, dtype=torch.float32, device="cpu", seed=1)
+    load_hf_weights(again, str(tmp_path))
+    for (n1, a), (n2, b) in zip(to_hf_state(model), to_hf_state(again)):
+        assert n1 == n2 and torch.equal(a, b), n1
+    proc = MoonViTProcessor(cfg, 28 * 28, 112 * 112)
+    out = proc([5, cfg.image_token_id, 6], [torch.rand(3, 60, 90)])
+    gh, gw = out["image_grid_thw"][0, 1:].tolist()
+    assert out["input_ids"].count(cfg.image_token_id) == gh * gw // 4 and out["pixel_values"].shape == (gh * gw, 588)
+    ids = torch.tensor(out["input_ids"])
+    with torch.no_grad():
+        lp = _mm_logprobs_ours(model, ids, out["pixel_values"], out["image_grid_thw"])
+        lp2 = _mm_logprobs_ours(model, ids, out["pixel_values"] + 0.5, out["image_grid_thw"])
+    assert torch.isfinite(lp).all() and torch.equal(lp[0], lp2[0]) and not torch.allclose(lp[-1], lp2[-1])
