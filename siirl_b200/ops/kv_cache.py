@@ -76,7 +76,7 @@ def kv_copy_blocks(cache_layer: torch.Tensor, src: torch.Tensor, dst: torch.Tens
 
 # "split": persistent warp-specialised kernel with split K/V (csrc/fmha_decode_split.cu); "simple": one CTA per
 # (sequence, kv head) (csrc/fmha_decode.cu)
-DECODE_KERNEL = "simple"
+DECODE_KERNEL = "split"
 _split_ws: dict = {}
 
 

@@ -122,10 +122,11 @@ def test_split_decode_attention_matches_eager(D, hq, hkv):
         lib.check_status()
         again = kvc.decode_attention(q, cache, seq_lens, table, hq, hkv, D)      # barriers / workspace reuse
         lib.check_status()
-    finally:
         kvc.set_decode_kernel("simple")
-    simple = kvc.decode_attention(q, cache, seq_lens, table, hq, hkv, D)
-    lib.check_status()
+        simple = kvc.decode_attention(q, cache, seq_lens, table, hq, hkv, D)
+        lib.check_status()
+    finally:
+        kvc.set_decode_kernel("split")
     want = kvc.decode_attention(q.cpu().float(), cache.cpu().float(), seq_lens.cpu(), table.cpu().clamp(min=0), hq, hkv, D)
     assert torch.equal(out, again)
     live = [i for i, n in enumerate(lens) if n > 0]
