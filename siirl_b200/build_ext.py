@@ -6,7 +6,7 @@ dependency on torch or Python (it shares ``libcudart.so.12`` with torch, so the 
 context that torch sets on a thread — autograd worker threads included — are the ones it sees): its ``extern "C"`` entry points are called through ``ctypes`` (see
 ``siirl_b200/ops/lib.py``).  nvcc cross-compiles without a GPU, so this runs on a CPU-only box.
 
-Usage: ``python -m siirl_b200.build_ext [--force] [--verbose]``.
+Usage: ``python -m siirl_b200.build_ext [--force] [--verbose] [--debug-bounds]``.
 """
 from __future__ import annotations
 
@@ -21,6 +21,9 @@ SRC_DIR = PKG_DIR / "csrc"
 OBJ_DIR = PKG_DIR / "build"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libsiirl_b200.so"
+# debug-bounds variant (-DSB_DEBUG_BOUNDS: data-dependent indices report their first violation, see csrc/common.cuh)
+DBG_OBJ_DIR = PKG_DIR / "build_dbg"
+DBG_LIB_PATH = LIB_DIR / "libsiirl_b200_dbg.so"
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -36,14 +39,16 @@ def _headers_mtime() -> float:
     return max((h.stat().st_mtime for h in hs), default=0.0)
 
 
-def _obj_for(src: Path) -> Path:
+def _obj_for(src: Path, debug_bounds: bool = False) -> Path:
     rel = src.relative_to(SRC_DIR)
-    return OBJ_DIR / (str(rel).replace(os.sep, "__") + ".o")
+    return (DBG_OBJ_DIR if debug_bounds else OBJ_DIR) / (str(rel).replace(os.sep, "__") + ".o")
 
 
-def _compile(src: Path, verbose: bool) -> tuple[Path, str]:
-    obj = _obj_for(src)
+def _compile(src: Path, verbose: bool, debug_bounds: bool = False) -> tuple[Path, str]:
+    obj = _obj_for(src, debug_bounds)
     cmd = [NVCC, *ARCH_FLAGS, *COMMON_FLAGS, "-I", str(SRC_DIR)]
+    if debug_bounds:
+        cmd += ["-DSB_DEBUG_BOUNDS"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-c", str(src), "-o", str(obj)]
@@ -53,36 +58,39 @@ def _compile(src: Path, verbose: bool) -> tuple[Path, str]:
     return obj, proc.stderr
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> Path:
     """Compile stale objects and link the shared library; returns its path."""
-    OBJ_DIR.mkdir(exist_ok=True)
+    obj_dir, lib_path = (DBG_OBJ_DIR, DBG_LIB_PATH) if debug_bounds else (OBJ_DIR, LIB_PATH)
+    obj_dir.mkdir(exist_ok=True)
     LIB_DIR.mkdir(exist_ok=True)
     hdr_m = _headers_mtime()
     srcs = _sources()
+    if not force and lib_path.exists() and lib_path.stat().st_mtime >= max([hdr_m] + [x.stat().st_mtime for x in srcs]):
+        return lib_path         # a library newer than every source: nothing to do (object files may be absent)
     stale = []
     for s in srcs:
-        o = _obj_for(s)
+        o = _obj_for(s, debug_bounds)
         if force or not o.exists() or o.stat().st_mtime < max(s.stat().st_mtime, hdr_m):
             stale.append(s)
     logs = []
     if stale:
         with cf.ThreadPoolExecutor(max_workers=min(len(stale), os.cpu_count() or 4)) as ex:
-            for obj, log in ex.map(lambda s: _compile(s, verbose), stale):
+            for obj, log in ex.map(lambda s: _compile(s, verbose, debug_bounds), stale):
                 logs.append((obj, log))
-    objs = [_obj_for(s) for s in srcs]
-    need_link = bool(stale) or not LIB_PATH.exists() or any(
-        o.stat().st_mtime > LIB_PATH.stat().st_mtime for o in objs)
+    objs = [_obj_for(s, debug_bounds) for s in srcs]
+    need_link = bool(stale) or not lib_path.exists() or any(
+        o.stat().st_mtime > lib_path.stat().st_mtime for o in objs)
     if need_link:
-        cmd = [NVCC, *ARCH_FLAGS, "-shared", "--cudart", "shared", "-o", str(LIB_PATH), *map(str, objs), "-lpthread"]
+        cmd = [NVCC, *ARCH_FLAGS, "-shared", "--cudart", "shared", "-o", str(lib_path), *map(str, objs), "-lpthread"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
     if verbose:
         for obj, log in logs:
             print(f"== {obj.name}\n{log}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
+    p = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, debug_bounds="--debug-bounds" in sys.argv)
     print(p)

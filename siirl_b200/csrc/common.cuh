@@ -332,6 +332,36 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
 }
 
 // ---------------------------------------------------------------------------------------
+// Debug-bounds build (-DSB_DEBUG_BOUNDS, `python -m siirl_b200.build_ext --debug-bounds`): data-dependent indices
+// (token ids, cache block ids, cache positions) are reported through SB_CHECK_INDEX, which records the FIRST violation
+// of a translation unit (site, index, limit) in a device word that the host reads with sb_bounds_read_<unit>(); the
+// access itself is still guarded by the kernel's own clamp / skip, so nothing faults.  In the normal build the macro
+// expands to nothing.  A unit that uses it places SB_BOUNDS_WORD_DEFINE(<unit>) at file scope.
+// ---------------------------------------------------------------------------------------
+#ifdef SB_DEBUG_BOUNDS
+#define SB_BOUNDS_WORD_DEFINE(unit)                                                              \
+  static __device__ int sb_bounds_word[4];                                                       \
+  extern "C" int sb_bounds_read_##unit(int* out4) {                                              \
+    int zero[4] = {0, 0, 0, 0};                                                                  \
+    cudaError_t e = cudaMemcpyFromSymbol(out4, sb_bounds_word, sizeof(zero));                     \
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(sb_bounds_word, zero, sizeof(zero));             \
+    return (int)e;                                                                               \
+  }
+#define SB_CHECK_INDEX(i, n, site)                                                               \
+  do {                                                                                           \
+    const long long sb_i_ = (long long)(i), sb_n_ = (long long)(n);                              \
+    if ((sb_i_ < 0 || sb_i_ >= sb_n_) && atomicCAS(&sb_bounds_word[0], 0, 1) == 0) {             \
+      sb_bounds_word[1] = (site);                                                                \
+      sb_bounds_word[2] = (int)sb_i_;                                                            \
+      sb_bounds_word[3] = (int)sb_n_;                                                            \
+    }                                                                                            \
+  } while (0)
+#else
+#define SB_BOUNDS_WORD_DEFINE(unit)
+#define SB_CHECK_INDEX(i, n, site) do { } while (0)
+#endif
+
+// ---------------------------------------------------------------------------------------
 // UMMA descriptors (bf16 operands, 128-byte swizzle, tile base 1024-byte aligned)
 // ---------------------------------------------------------------------------------------
 // Shared-memory matrix descriptor.  Fields (16-byte units): start address [0,14),

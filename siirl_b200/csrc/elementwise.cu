@@ -252,6 +252,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
 // ---------------------------------------------------------------------------------------
 // Embedding gather and its gradient (fp32 scatter-add into the main-grad buffer).
 // ---------------------------------------------------------------------------------------
+SB_BOUNDS_WORD_DEFINE(elementwise)
+
 __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, int T, int H, int V) {
   const int nvec = H / 8;
@@ -260,6 +262,7 @@ __global__ void embedding_fwd_kernel(const long long* __restrict__ ids, const __
        idx += (long long)gridDim.x * blockDim.x) {
     const int t = (int)(idx / nvec), v = (int)(idx % nvec);
     long long id = ids[t];
+    SB_CHECK_INDEX(id, V, 1);
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);
     reinterpret_cast<uint4*>(out + (size_t)t * H)[v] = reinterpret_cast<const uint4*>(table + (size_t)id * H)[v];
   }
@@ -273,6 +276,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids, const __
        idx += (long long)gridDim.x * blockDim.x) {
     const int t = (int)(idx / nvec), v = (int)(idx % nvec);
     long long id = ids[t];
+    SB_CHECK_INDEX(id, V, 2);
     if (id < 0 || id >= V) continue;
     float d[8];
     bf16x8_to_float(reinterpret_cast<const uint4*>(dout + (size_t)t * H)[v], d);

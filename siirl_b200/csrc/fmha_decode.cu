@@ -19,6 +19,8 @@ constexpr int kBlk = 64;  // tokens per cache block = kv tile
 // ---------------------------------------------------------------------------------------
 // cache append: copies the k and v parts of packed qkv rows into their cache slots
 // ---------------------------------------------------------------------------------------
+SB_BOUNDS_WORD_DEFINE(kv_cache)
+
 __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride, const int* __restrict__ seq_ids,
                                  const int* __restrict__ positions, const int* __restrict__ block_table,
                                  int max_blocks, __nv_bfloat16* __restrict__ cache, int T, int Hq, int Hkv, int D) {
@@ -35,7 +37,10 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ qkv, int row_
     const int pos = positions[t];
     const int seq = seq_ids[t];
     if (pos < 0 || seq < 0) continue;
+    SB_CHECK_INDEX(pos / kBlk, max_blocks, 3);
+    if (pos / kBlk >= max_blocks) continue;
     const int blk = block_table[(size_t)seq * max_blocks + pos / kBlk];
+    SB_CHECK_INDEX(blk, 0x7fffffff, 4);
     if (blk < 0) continue;
     const uint4 val = *reinterpret_cast<const uint4*>(qkv + (size_t)t * row_stride + (size_t)(Hq + kv * Hkv + head) * D + v * 8);
     __nv_bfloat16* dst = cache + ((((size_t)blk * 2 + kv) * Hkv + head) * kBlk + (pos % kBlk)) * D + v * 8;
@@ -101,7 +106,9 @@ __global__ void rope_kv_append_kernel(__nv_bfloat16* __restrict__ qkv, int row_s
     if (to_cache) {
       const int kv = head >= Hq + Hkv ? 1 : 0;
       const int h = head - Hq - kv * Hkv;
-      const int blk = block_table[(size_t)seq * max_blocks + cp / kBlk];
+      SB_CHECK_INDEX(cp / kBlk, max_blocks, 5);
+      const int blk = cp / kBlk < max_blocks ? block_table[(size_t)seq * max_blocks + cp / kBlk] : -1;
+      SB_CHECK_INDEX(blk, 0x7fffffff, 6);
       if (blk >= 0) {
         __nv_bfloat16* dst = cache + ((((size_t)blk * 2 + kv) * Hkv + h) * kBlk + (cp % kBlk)) * D;
         *reinterpret_cast<uint4*>(dst + i0) = lo;

@@ -78,9 +78,37 @@ def available() -> bool:
     return _LIB_PATH.exists()
 
 
+def _debug_bounds() -> bool:
+    """``SIIRL_DEBUG_BOUNDS=1`` loads the debug-bounds build of the library (built on first use): data-dependent
+    indices report their first violation, read with :func:`bounds_violations`."""
+    return os.environ.get("SIIRL_DEBUG_BOUNDS", "0") not in ("", "0")
+
+
+def bounds_violations() -> list:
+    """``[(unit, site, index, limit)]`` recorded by the debug-bounds build since the last call (empty in the normal
+    build, which carries no records)."""
+    out = []
+    if not _debug_bounds():
+        return out
+    L = get_lib()
+    for unit in ("elementwise", "kv_cache"):
+        try:
+            fn = getattr(L._cdll, f"sb_bounds_read_{unit}")
+        except AttributeError:
+            continue
+        buf = (ctypes.c_int * 4)()
+        check(fn(buf), f"sb_bounds_read_{unit}")
+        if buf[0]:
+            out.append((unit, int(buf[1]), int(buf[2]), int(buf[3])))
+    return out
+
+
 def get_lib() -> "_CountingLib":
-    global _lib
+    global _lib, _LIB_PATH
     if _lib is None:
+        if _debug_bounds():
+            from .. import build_ext
+            _LIB_PATH = build_ext.build(debug_bounds=True)
         if not _LIB_PATH.exists():
             raise NativeLibraryMissing(
                 f"{_LIB_PATH} not found: run `python -m siirl_b200.build_ext` (or __graft_entry__.build())")
