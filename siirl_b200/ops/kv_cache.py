@@ -6,6 +6,7 @@ Cache layout (one tensor for all layers): ``[layers, num_blocks, 2, Hkv, 64, D]`
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from typing import Optional
 
@@ -76,7 +77,7 @@ def kv_copy_blocks(cache_layer: torch.Tensor, src: torch.Tensor, dst: torch.Tens
 
 # "split": persistent warp-specialised kernel with split K/V (csrc/fmha_decode_split.cu); "simple": one CTA per
 # (sequence, kv head) (csrc/fmha_decode.cu)
-DECODE_KERNEL = "split"
+DECODE_KERNEL = os.environ.get("SIIRL_DECODE_KERNEL", "split")      # environment override for A/B runs
 _split_ws: dict = {}
 
 
