@@ -322,16 +322,18 @@ class _ModelWorkerBase:
             if self.world % n:
                 raise ValueError(f"pipeline_model_parallel_size={n} must divide the group size {self.world}")
             ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
-            mine = dp = None
+            mine = dp = fwd = bwd = None
             for b in range(self.world // n):
                 g = dist.new_group(ranks[b * n:(b + 1) * n])
+                gf = dist.new_group(ranks[b * n:(b + 1) * n])      # activations
+                gb = dist.new_group(ranks[b * n:(b + 1) * n])      # activation gradients
                 if b == self.rank // n:
-                    mine = g
+                    mine, fwd, bwd = g, gf, gb
             for s_ in range(n):
                 g = dist.new_group(ranks[s_::n])
                 if s_ == self.rank % n:
                     dp = g
-            self._pp_ctx = PipelineContext(mine, self.model_config.num_layers)
+            self._pp_ctx = PipelineContext(mine, self.model_config.num_layers, fwd, bwd)
             self._pp_dp_group = dp
         model.attach_pipeline_parallel(self._pp_ctx)
         pc = self._pp_ctx
@@ -446,6 +448,12 @@ class _ModelWorkerBase:
             if pc.is_last:
                 lp_l, ent_l = lm_head_logprob_entropy(hidden.index_select(0, pk.sel), model.head_weight, pk.labels,
                                                       temperature, with_entropy)
+            if getattr(self, "_pp_stage_local", False):
+                # pipelined training (1F1B): nothing is broadcast per micro-batch; the last stage holds the values,
+                # the other stages only the handle whose backward receives the activation gradient
+                if pc.is_last:
+                    return pk.scatter(lp_l), (pk.scatter(ent_l) if ent_l is not None else None)
+                return handle, None
             vals = P.broadcast_from_last(pc, [lp_l] + ([ent_l] if with_entropy else []), [(N,)] * (2 if with_entropy
                                          else 1), [torch.float32] * 2, self.device)
             lp = lp_l if pc.is_last else vals[0]
@@ -919,6 +927,8 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
             mini = -(-bs // n_mini)
             n_mini = max(1, -(-bs // mini))
         on_policy = a.ppo_epochs == 1 and n_mini == 1
+        pc = getattr(self.model, "pp", None)
+        pipelined = pc is not None and pc.pp > 1 and pc.pipelined
         self.store.zero_grad()
         for _epoch in range(a.ppo_epochs):
             order = torch.randperm(bs).tolist() if a.shuffle else list(range(bs))
@@ -927,11 +937,14 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 mini_batch = data.select_idxs(mini_idx)
                 mbs = _micro_batches(mini_batch, self.ppo_micro_batch_size, a.use_dynamic_bsz,
                                      a.ppo_max_token_len_per_gpu, self.group)
-                for idx, mb in mbs:
+                def micro_forward(idx, mb):
+                    """Forward pass and loss of one micro-batch -> (tensor to call ``backward`` on, metrics)."""
                     scale = (len(idx) / len(mini_idx)) if a.use_dynamic_bsz else 1.0 / len(mbs)
                     mask = mb["response_mask"].to(self.device).float()
                     adv = mb["advantages"].to(self.device).float()
                     logp, ent = self._forward_logprob(self.model, mb, temperature, need_entropy)
+                    if pipelined and not pc.is_last:
+                        return logp, {}             # the stage's handle: its backward receives dL/dh from the next stage
                     old = logp.detach() if on_policy else mb["old_log_probs"].to(self.device).float()
                     ref = mb["ref_log_prob"].to(self.device).float() if (a.use_kl_loss and "ref_log_prob" in mb) \
                         else None
@@ -974,14 +987,43 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                             drift = core_algos.cpgd_policy_drift(old, logp, mask, a.loss_agg_mode)
                             loss = loss + a.policy_drift_coeff * drift
                             rec["actor/policy_drift"] = drift.detach()
-                    (loss * scale).backward()
+                    return loss * scale, rec
+
+                def record(rec):
                     for k, v in rec.items():
                         metrics.setdefault(k, []).append(v)
+
+                if pipelined:
+                    # 1F1B: warm-up forwards, then one forward and one backward in turn, then the remaining backwards
+                    from ..parallel.pipeline import schedule_1f1b
+                    inflight = {}
+                    self._pp_stage_local = True
+                    try:
+                        for op, i in schedule_1f1b(pc.stage, pc.pp, len(mbs)):
+                            if op == "F":
+                                inflight[i] = micro_forward(*mbs[i])
+                            else:
+                                target, rec = inflight.pop(i)
+                                target.backward()
+                                record(rec)
+                    finally:
+                        self._pp_stage_local = False
+                    pc.drain()
+                else:
+                    for idx, mb in mbs:
+                        target, rec = micro_forward(idx, mb)
+                        target.backward()
+                        record(rec)
                 norm = self._optimizer_step(a.optim, a.grad_clip)
                 metrics.setdefault("actor/grad_norm", []).append(norm.detach().clone())
         out = {k: float(torch.stack([torch.as_tensor(x, dtype=torch.float32, device="cpu") if not
                                      isinstance(x, torch.Tensor) else x.float().cpu() for x in v]).mean())
                for k, v in metrics.items()}
+        if pipelined:
+            # the loss metrics exist on the last stage only: hand them to the other stages of the pipeline
+            box = [out if pc.is_last else None]
+            dist.broadcast_object_list(box, src=pc.last_global, group=pc.group)
+            out = dict(box[0], **{"actor/grad_norm": out.get("actor/grad_norm", box[0].get("actor/grad_norm", 0.0))})
         out["actor/lr"] = self.last_lr
         if self.device.type == "cuda":
             out["perf/max_memory_allocated_gb"] = torch.cuda.max_memory_allocated(self.device) / 2 ** 30

@@ -13,9 +13,16 @@ functions, so an ordinary ``loss.backward()`` on every rank drives the whole pip
 * ``send_to_next``    forward: send ``h`` to the next stage and return a 0-d "handle"; backward: ignore the
   handle's (zero) incoming gradient, receive ``dL/dh`` from the next stage and return it.
 
-A non-last stage adds ``0 * handle`` to the values it reports, which ties its autograd graph to the transfer.  One
-micro-batch crosses the stages at a time (no interleaving of micro-batches): the schedule is the simplest correct
-one, meant for capability parity, not for throughput.
+A non-last stage adds ``0 * handle`` to the values it reports, which ties its autograd graph to the transfer.
+
+Schedules.  Scoring passes run one micro-batch at a time.  Training runs Megatron's non-interleaved 1F1B order
+(``schedule_1f1b``): stage ``s`` of ``P`` first runs ``P - s - 1`` warm-up forwards, then alternates one forward and
+one backward, then drains its backwards, so up to ``P`` micro-batches are in flight and the stages work concurrently.
+For that the sends are asynchronous (``isend``; buffers are kept until ``drain``) and the two directions use two
+process groups of their own: a stage's "send activation of micro-batch k+1" and its neighbour's "send gradient of
+micro-batch j" are then never queued behind one another (on NCCL each group has its own stream; on gloo the sends
+return at once), which is what the combined send-forward / receive-backward calls of Megatron achieve with grouped
+operations.  The interleaved (virtual-stage) schedule is not built.
 """
 from __future__ import annotations
 
@@ -25,9 +32,23 @@ import torch
 import torch.distributed as dist
 
 
+def schedule_1f1b(stage: int, stages: int, micro_batches: int) -> List[Tuple[str, int]]:
+    """Order of forward ("F", i) and backward ("B", i) passes of one stage under non-interleaved 1F1B."""
+    warm = min(stages - stage - 1, micro_batches)
+    order: List[Tuple[str, int]] = [("F", i) for i in range(warm)]
+    for i in range(micro_batches - warm):
+        order += [("F", warm + i), ("B", i)]
+    order += [("B", i) for i in range(micro_batches - warm, micro_batches)]
+    return order
+
+
 class PipelineContext:
-    def __init__(self, group, num_layers: int):
+    def __init__(self, group, num_layers: int, fwd_group=None, bwd_group=None):
         self.group = group
+        # groups of the same ranks that carry activations (forward) and their gradients (backward); None: the
+        # default group carries both (sends are then only safe with one micro-batch in flight)
+        self.fwd_group, self.bwd_group = fwd_group, bwd_group
+        self._pending: list = []
         self.pp = dist.get_world_size(group)
         self.stage = dist.get_rank(group)
         ranks = dist.get_process_group_ranks(group)
@@ -45,6 +66,32 @@ class PipelineContext:
     @property
     def is_last(self) -> bool:
         return self.stage == self.pp - 1
+
+    @property
+    def pipelined(self) -> bool:
+        return self.fwd_group is not None and self.bwd_group is not None
+
+    def send(self, t: torch.Tensor, dst: int, forward: bool) -> None:
+        """Asynchronous when the direction groups exist (the tensor is kept alive until ``drain``), else blocking."""
+        t = t.contiguous()
+        if not self.pipelined:
+            dist.send(t, dst=dst)
+            return
+        self._pending.append((dist.isend(t, dst=dst, group=self.fwd_group if forward else self.bwd_group), t))
+        if len(self._pending) > 4 * self.pp:
+            self.drain(keep=2 * self.pp)
+
+    def recv(self, buf: torch.Tensor, src: int, forward: bool) -> None:
+        if not self.pipelined:
+            dist.recv(buf, src=src)
+        else:
+            dist.recv(buf, src=src, group=self.fwd_group if forward else self.bwd_group)
+
+    def drain(self, keep: int = 0) -> None:
+        """Wait for the oldest outstanding sends (all of them by default)."""
+        while len(self._pending) > keep:
+            work, _ = self._pending.pop(0)
+            work.wait()
 
     def owns_param(self, name: str) -> bool:
         """Stage that trains a parameter: layers by index, embedding on the first stage, final norm / heads on the
@@ -69,12 +116,12 @@ class _RecvFromPrev(torch.autograd.Function):
     def forward(ctx, anchor: torch.Tensor, pc: PipelineContext, shape: Tuple[int, ...], dtype, device):
         ctx.pc = pc
         buf = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(buf, src=pc.prev)
+        pc.recv(buf, pc.prev, forward=True)
         return buf
 
     @staticmethod
     def backward(ctx, grad):
-        dist.send(grad.contiguous(), dst=ctx.pc.prev)
+        ctx.pc.send(grad, ctx.pc.prev, forward=False)
         return None, None, None, None, None
 
 
@@ -82,14 +129,14 @@ class _SendToNext(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h: torch.Tensor, pc: PipelineContext):
         ctx.pc, ctx.meta = pc, (h.shape, h.dtype, h.device)
-        dist.send(h.contiguous(), dst=pc.next)
+        pc.send(h, pc.next, forward=True)
         return h.new_zeros(())
 
     @staticmethod
     def backward(ctx, _zero):
         shape, dtype, device = ctx.meta
         g = torch.empty(shape, dtype=dtype, device=device)
-        dist.recv(g, src=ctx.pc.next)
+        ctx.pc.recv(g, ctx.pc.next, forward=False)
         return g, None
 
 
@@ -98,7 +145,7 @@ def recv_from_prev(pc: PipelineContext, shape, dtype, device, needs_grad: bool) 
         anchor = torch.zeros((), device=device, requires_grad=True)
         return _RecvFromPrev.apply(anchor, pc, tuple(shape), dtype, device)
     buf = torch.empty(tuple(shape), dtype=dtype, device=device)
-    dist.recv(buf, src=pc.prev)
+    pc.recv(buf, pc.prev, forward=True)
     return buf
 
 
@@ -106,7 +153,7 @@ def send_to_next(pc: PipelineContext, h: torch.Tensor) -> Optional[torch.Tensor]
     """Returns the 0-d handle when ``h`` carries gradient history, else ``None``."""
     if h.requires_grad and torch.is_grad_enabled():
         return _SendToNext.apply(h, pc)
-    dist.send(h.contiguous(), dst=pc.next)
+    pc.send(h, pc.next, forward=True)
     return None
 
 

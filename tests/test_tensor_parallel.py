@@ -36,3 +36,13 @@ def test_tensor_parallel_training_matches_the_whole_model():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="2"))
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_TRAIN_OK" in out.stdout
+
+
+def test_pipeline_1f1b_schedule_matches_the_whole_model():
+    """Three stages, five micro-batches under 1F1B with asynchronous sends: per-stage gradients equal the whole model's."""
+    from siirl_b200.execution.scheduler.launch import find_free_port
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr",
+           "127.0.0.1", "--master-port", str(find_free_port()), os.path.join(os.path.dirname(__file__), "pp_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    assert "PP_1F1B_OK" in out.stdout
