@@ -330,6 +330,8 @@ def main() -> int:
             "clocks": sampler.summary() if not final else clocks_final[0], "gpu_launches": launches,
             "impl": "native", "partial": not final,
             "step_split_s": {k: round(v, 4) for k, v in worker.timing_raw.items()},
+            "engine_stats": {k: (round(v, 3) if isinstance(v, float) else v) for w_ in worker.workers.values()
+                             for k, v in getattr(getattr(w_, "engine", None), "stats", {}).items()},
             "e2e": {"value": tokens_all / wall, "unit": "tokens/s", "ms_per_step": wall * 1e3 / done, "steps": done,
                     "h2d_bytes_per_step": h2d // done, "d2h_bytes_per_step": d2h // done,
                     "clock": "host perf_counter around DAGWorker.train_step (pinned host batch -> device, DAG walk, "

@@ -16,6 +16,8 @@ Scheduling model
 """
 from __future__ import annotations
 
+import os
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -28,6 +30,9 @@ from ...ops.lm_head import lm_head_logits
 from ...ops.sampling import sample
 
 BLOCK = kvc.BLOCK
+
+
+_STREAM_KEY = 0x9E3779B97F4A7C15 & 0x7FFFFFFFFFFFFFFF      # Philox key of the CUDA-graph decode path
 
 
 @dataclass
@@ -177,6 +182,8 @@ class RolloutEngine:
         self._graph_launches: Dict[int, int] = {}
         self._out_buf = None
         self.stats = {"prefill_tokens": 0, "decode_steps": 0, "generated_tokens": 0}
+        # SIIRL_ENGINE_TIMING=1: synchronise around every decode round and accumulate decode_s / capture_s in stats
+        self._timing = os.environ.get("SIIRL_ENGINE_TIMING", "0") not in ("", "0") and self.device.type == "cuda"
         self.wake_up()
 
     # ---- memory hand-off with the trainer -------------------------------------------------------
@@ -336,7 +343,9 @@ class RolloutEngine:
         hidden = self.model.forward_cached(self.last_token, st["pos"], self.cache, self.block_table, st["seq_ids"],
                                            seq_lens=st["seq_lens"], rope_positions=st["rope_pos"])
         logits = lm_head_logits(hidden, self.model.head_weight)
-        tok, lp = sample(logits, sp.temperature, sp.top_k, sp.top_p, seed=sp.seed, step_dev=self.step_counter)
+        # the request's seed lives in the device-side step counter (see ``generate``), not in a launch argument, so
+        # that one captured graph serves every seed
+        tok, lp = sample(logits, sp.temperature, sp.top_k, sp.top_p, seed=_STREAM_KEY, step_dev=self.step_counter)
         eos = -1 if (sp.eos_token_id is None or sp.ignore_eos) else int(sp.eos_token_id)
         _lib.check(L.sb_decode_commit(_lib.ptr(tok), _lib.ptr(lp), _lib.ptr(self.finished), _lib.ptr(self.hit_eos),
                                       _lib.ptr(self.ctx_len), _lib.ptr(self.remaining), _lib.ptr(self.gen_index),
@@ -349,7 +358,7 @@ class RolloutEngine:
             for _ in range(k):
                 self._decode_step(sp, tokens_out, logp_out)
             return
-        key = (k, sp.temperature, sp.top_k, sp.top_p, sp.seed, sp.eos_token_id, sp.ignore_eos)
+        key = (k, sp.temperature, sp.top_k, sp.top_p, sp.eos_token_id, sp.ignore_eos)
         g = self._graphs.get(key)
         if g is None:
             # warm-up on a side stream (allocator and lazy initialisation), then capture k steps as one graph
@@ -407,6 +416,9 @@ class RolloutEngine:
         logp_out.zero_()
         self.gen_index.zero_()
         self.hit_eos.zero_()
+        if dev.type == "cuda":
+            # random stream of this call: counter range [seed << 24, ...) of the fixed key (16 M steps per seed)
+            self.step_counter.fill_((int(sp.seed) & 0x7FFFFFFF) << 24)
         self.finished.fill_(True)
         self.ctx_len.zero_()
         self.remaining.zero_()
@@ -562,7 +574,16 @@ class RolloutEngine:
                 self.finished[sl] = fin
             # ---- decode until the next host check ----
             if group_any(bool((~self.finished).any().item()))[0]:
+                if self._timing:
+                    torch.cuda.synchronize(dev)
+                    t_dec = time.perf_counter()
+                    n_graphs = len(self._graphs)
                 self._run_decode_steps(self.sync_interval, sp, tokens_out, logp_out)
+                if self._timing:
+                    torch.cuda.synchronize(dev)
+                    dt = time.perf_counter() - t_dec
+                    key = "capture_s" if len(self._graphs) != n_graphs else "decode_s"
+                    self.stats[key] = self.stats.get(key, 0.0) + dt
                 self.stats["decode_steps"] += self.sync_interval
             # ---- retire finished sequences ----
             fin_cpu = self.finished.cpu().tolist()
