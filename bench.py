@@ -20,6 +20,8 @@ the allocator and the collectives; the last, full-size one captures the decode g
 prints the cumulative JSON line after every finished timed step; the last line printed is the result.
 
 ``--impl reference`` is the arm that would run the unmodified reference; it reports why it cannot run here.
+``--impl library`` (one GPU) runs the same step through vLLM, transformers, flash-attn and ``torch.optim.AdamW``
+(``baseline/library_arm.py``) and prints ``"impl": "library"``.
 """
 from __future__ import annotations
 
@@ -51,7 +53,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "library"],
+                    help="library: the same step through vLLM + transformers + flash-attn + torch AdamW (1 GPU), a bar "
+                         "on this box that is not the reference")
     ap.add_argument("--budget-s", type=float, default=600.0,
                     help="wall-clock budget of the whole run, from process start; --steps/--warmup are upper bounds")
     ap.add_argument("--model", default="qwen2.5-7b")
@@ -190,6 +194,14 @@ def main() -> int:
     args = parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "library":
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "library", "unavailable": "the library arm runs on one GPU"}), flush=True)
+            return 0
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        from baseline.library_arm import run as library_run
+        return library_run(args, _T_PROCESS_START)
     import torch
     import torch.distributed as dist
 
