@@ -113,6 +113,8 @@ class DecoderConfig:
     qk_norm: bool = False           # Qwen3 family
     tie_word_embeddings: bool = False
     mrope_section: Optional[List[int]] = None   # Qwen2-VL multimodal rope (t, h, w halves)
+    # checkpoint's rope_scaling of type linear / llama3 / yarn (None: plain rotary frequencies)
+    rope_scaling: Optional[Dict[str, Any]] = None
     # mixture of experts (0 experts = dense)
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -253,6 +255,8 @@ class DecoderConfig:
             qk_norm=mt.startswith("qwen3"),
             tie_word_embeddings=bool(cfg.get("tie_word_embeddings", False)),
             mrope_section=rope_scaling.get("mrope_section"),
+            rope_scaling=(dict(rope_scaling) if rope_scaling.get("rope_type", rope_scaling.get("type")) in
+                          ("linear", "llama3", "yarn") else None),
             num_experts=text.get("num_experts", text.get("num_local_experts", 0)) or 0,
             num_experts_per_tok=text.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=text.get("moe_intermediate_size", 0) or 0,
@@ -409,6 +413,8 @@ class DecoderConfig:
                 d["shared_expert_intermediate_size"] = self.shared_expert_intermediate_size
         if self.mrope_section:
             d["rope_scaling"] = {"type": "mrope", "mrope_section": self.mrope_section}
+        elif self.rope_scaling:
+            d["rope_scaling"] = dict(self.rope_scaling)
         if self.moonvit is not None:
             mv = self.moonvit
             text = dict(d, model_type="deepseek_v3")

@@ -169,6 +169,10 @@ class DecoderLayer(nn.Module):
         cfg = self.cfg
         q, k, v = self.mla_qkv(x, positions, rope)
         scale = 1.0 / math.sqrt(cfg.qk_nope_head_dim + cfg.qk_rope_head_dim)
+        rs = cfg.rope_scaling or {}
+        if rs.get("rope_type", rs.get("type")) == "yarn" and rs.get("mscale_all_dim"):
+            from ..ops.reference import yarn_mscale
+            scale *= yarn_mscale(float(rs.get("factor", 1.0)), float(rs["mscale_all_dim"])) ** 2
         sp = getattr(self, "sp", None)
         if sp is not None and sp.sp > 1:
             # Ulysses (the switch the reference patches into Kimi-VL's attention,
@@ -303,7 +307,8 @@ class DecoderLM(nn.Module):
         need = max(min_len, 1)
         if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < need:
             n = max(need, min(self.cfg.max_position_embeddings, 8192))
-            self._rope = ops.rope_tables(self.cfg.rope_dim, n, self.cfg.rope_theta, device=device)
+            self._rope = ops.rope_tables(self.cfg.rope_dim, n, self.cfg.rope_theta, device=device,
+                                         scaling=self.cfg.rope_scaling)
         return self._rope
 
     @property

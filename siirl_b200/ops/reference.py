@@ -21,11 +21,62 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optiona
     return y, h
 
 
-def rope_tables(head_dim: int, max_pos: int, theta: float, device=None):
+def yarn_mscale(scale: float, mscale: float = 1.0) -> float:
+    return 1.0 if scale <= 1 else 0.1 * mscale * math.log(scale) + 1.0
+
+
+def scaled_inv_freq(head_dim: int, theta: float, scaling: Optional[dict], device=None):
+    """Inverse rotary frequencies under a checkpoint's ``rope_scaling`` (public formulas: "linear" divides every
+    frequency by ``factor``; "llama3" keeps the high frequencies, divides the low ones and blends between the two
+    wavelength bounds; "yarn" blends interpolated and original frequencies with a linear ramp between the dimensions
+    whose wavelength completes ``beta_fast`` / ``beta_slow`` rotations inside the original context).  Returns
+    ``(inv_freq, attention_factor)``; cos / sin are multiplied by the factor (yarn's temperature correction)."""
     inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64, device=device) / head_dim))
+    if not scaling:
+        return inv, 1.0
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    factor = float(scaling.get("factor", 1.0))
+    if kind == "linear":
+        return inv / factor, 1.0
+    if kind == "llama3":
+        lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        old = float(scaling.get("original_max_position_embeddings", 8192))
+        wavelen = 2 * math.pi / inv
+        smooth = ((old / wavelen - lo) / (hi - lo)).clamp(0, 1)
+        blended = (1 - smooth) * inv / factor + smooth * inv
+        out = torch.where(wavelen > old / lo, inv / factor, torch.where(wavelen < old / hi, inv, blended))
+        return out, 1.0
+    if kind == "yarn":
+        old = float(scaling.get("original_max_position_embeddings", 4096))
+        fast, slow = float(scaling.get("beta_fast", 32)), float(scaling.get("beta_slow", 1))
+
+        def corr_dim(rot):
+            return head_dim * math.log(old / (rot * 2 * math.pi)) / (2 * math.log(theta))
+        low, high = corr_dim(fast), corr_dim(slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, head_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(head_dim // 2, dtype=torch.float64, device=device) - low) / (high - low)).clamp(0, 1)
+        keep = 1 - ramp                                   # 1: original frequency, 0: interpolated
+        out = inv / factor * (1 - keep) + inv * keep
+        ms, ms_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+        if scaling.get("attention_factor") is not None:
+            att = float(scaling["attention_factor"])
+        elif ms and ms_all:
+            att = yarn_mscale(factor, float(ms)) / yarn_mscale(factor, float(ms_all))
+        else:
+            att = yarn_mscale(factor)
+        return out, att
+    return inv, 1.0
+
+
+def rope_tables(head_dim: int, max_pos: int, theta: float, device=None, scaling: Optional[dict] = None):
+    inv, att = scaled_inv_freq(head_dim, theta, scaling, device)
     t = torch.arange(max_pos, dtype=torch.float64, device=device)
     ang = torch.outer(t, inv)
-    return ang.cos().float(), ang.sin().float()
+    return (ang.cos() * att).float(), (ang.sin() * att).float()
 
 
 def _select_pos(positions: torch.Tensor, half: int, mrope_section):

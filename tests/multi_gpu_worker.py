@@ -34,6 +34,7 @@ def main():
     info = SeqInfo([64 + 16 * rank, 100], device=dev)
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     ids = torch.randint(3, cfg.vocab_size, (info.total,), device=dev, generator=g)
+    ids_train = ids
     norms = []
     for step in range(2):
         for model, store in stores:
@@ -95,6 +96,44 @@ def main():
     assert flat == sorted(f"r{r}s{i}" for r in range(world) for i in range(per_rank)), "a sample was lost or duplicated"
     torch.cuda.synchronize()
     lib.check_status()
+
+    # 4. adversarial arrival order: every rank sleeps a different, random time on the host before each flag barrier and
+    #    before each fused optimizer step (up to 150 ms, far above a kernel's duration but below the bounded waits).
+    #    Epoch-tagged flags must never let a late rank pass on a stale flag: after every barrier each rank reads what
+    #    its left neighbour wrote into symmetric memory just before arriving.
+    import random
+    import time
+    rng = random.Random(1000 + rank)
+    box = comm.alloc(16, torch.int64)
+    peers = comm.peers_of(box)
+    left = (rank - 1) % world
+    for it in range(12):
+        time.sleep(rng.random() * 0.15)
+        box.fill_(1000 * it + rank)
+        torch.cuda.synchronize()
+        comm.barrier()
+        seen_left = torch.empty(16, dtype=torch.int64, device=dev)
+        lib.check(lib.get_lib().sb_segment_pull(peers.ptr_array, world, lib.ptr(torch.tensor(
+            [[0, 0, 128, left]], dtype=torch.int64, device=dev)), 1, lib.ptr(seen_left), lib.stream()),
+            "sb_segment_pull")
+        torch.cuda.synchronize()
+        assert int(seen_left[0]) == 1000 * it + left, (it, int(seen_left[0]))
+        comm.barrier()                      # nobody overwrites its box before every reader is done
+    model, store = stores[0]
+    ref_model, ref_store = stores[1]
+    for it in range(4):
+        for m_, st_ in ((model, store), (ref_model, ref_store)):
+            st_.zero_grad()
+            lp, _ = m_.logprobs(ids_train, info.positions, info, torch.roll(ids_train, -1), with_entropy=False)
+            (-lp.mean()).backward()
+        time.sleep(rng.random() * 0.15)
+        n1 = store.step(lr=1e-3, max_grad_norm=1.0)
+        n2 = ref_store.step(lr=1e-3, max_grad_norm=1.0)
+        assert abs(n1.item() - n2.item()) < 1e-2 * max(1.0, n2.item()), (it, n1.item(), n2.item())
+    torch.cuda.synchronize()
+    lib.check_status()
+    err = (store.flat_param.float() - ref_store.flat_param.float()).abs().max().item()
+    assert err < 2e-2, f"skewed arrival: fused vs NCCL parameters differ by {err}"
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK", world)

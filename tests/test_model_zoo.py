@@ -383,3 +383,37 @@ def test_kimi_vl_tower_checkpoint_layout_and_language_model(tmp_path):
         lp = _mm_logprobs_ours(model, ids, out["pixel_values"], out["image_grid_thw"])
         lp2 = _mm_logprobs_ours(model, ids, out["pixel_values"] + 0.5, out["image_grid_thw"])
     assert torch.isfinite(lp).all() and torch.equal(lp[0], lp2[0]) and not torch.allclose(lp[-1], lp2[-1])
+
+
+@pytest.mark.parametrize("preset,scaling", [
+    ("tiny-deepseek-v3", {"rope_type": "yarn", "type": "yarn", "factor": 8.0, "original_max_position_embeddings": 16,
+                          "beta_fast": 32, "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0}),
+    ("tiny", {"rope_type": "llama3", "type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+              "original_max_position_embeddings": 16}),
+    ("tiny", {"rope_type": "linear", "type": "linear", "factor": 4.0}),
+])
+def test_rope_scaling_matches_transformers(preset, scaling, tmp_path):
+    """Checkpoint rope scaling (YaRN with its attention-temperature factor on multi-head latent attention, Llama-3's
+    wavelength-dependent scaling, linear interpolation) against transformers on a sequence longer than the original
+    context of the scaling."""
+    import dataclasses
+    cfg = dataclasses.replace(get_config(preset), rope_scaling=scaling)
+    if preset == "tiny":
+        cfg = dataclasses.replace(cfg, model_type="llama", qkv_bias=False)
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=21)
+    save_hf_model(model, str(tmp_path))
+    try:
+        hf = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path), torch_dtype=torch.float32,
+                                                               attn_implementation="eager")
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"transformers cannot build {cfg.model_type} with {scaling['type']}: {type(e).__name__}: {e}")
+    hf.eval()
+    ids = torch.randint(3, cfg.vocab_size, (61,), generator=torch.Generator().manual_seed(2))
+    with torch.no_grad():
+        want = torch.log_softmax(hf(ids[None]).logits[0].float(), -1)
+        got = _logprobs_ours(model, ids)
+    assert (got - want).abs().max().item() < 3e-4, (got - want).abs().max().item()
+    plain = build_model(dataclasses.replace(cfg, rope_scaling=None), dtype=torch.float32, device="cpu", seed=21)
+    with torch.no_grad():
+        assert (_logprobs_ours(plain, ids) - got).abs().max().item() > 1e-3      # the scaling is not a no-op here
+    assert DecoderConfig.from_pretrained(str(tmp_path)).rope_scaling["factor"] == scaling["factor"]
