@@ -5,9 +5,13 @@
 // 32 KB stage in flight per CTA) and by the tail wave of a grid that is not a multiple of the resident slots.  Here:
 //   * one CTA per SM walks a list of work items (chunk, sequence, kv head); a sequence is cut into chunks of
 //     kChunkTiles cache blocks, so items are of similar size whatever the batch and the context lengths;
-//   * three warps: warp 0 soft-max / output, warp 1 TMA producer, warp 2 MMA issuer.  The producer keeps a ring of
-//     K/V stages full across item boundaries (160 KB in flight per SM at d = 128), S is double-buffered in TMEM so the
-//     scores of tile t+1 are computed while tile t is in the soft-max, and P is double-buffered in shared memory;
+//   * four working warps: warp 0 soft-max, warp 1 TMA producer, warp 2 MMA issuer, warp 4 output (warp 3 only makes
+//     warp 4 exist: rows 0..31 of TMEM belong to the warps whose index is a multiple of four).  The producer keeps a
+//     ring of K/V stages full across item boundaries (128 KB in flight per SM at d = 128) and fetches the NEXT item's
+//     query rows while the current item runs; S is double-buffered in TMEM so the scores of tile t+1 are computed while
+//     tile t is in the soft-max, P is double-buffered in shared memory, and the output accumulator is double-buffered
+//     in TMEM so that an item's normalisation and store overlap the next item's tiles: an item boundary costs no
+//     pipeline drain;
 //   * the running maximum is only raised when it grows by more than 2^8 (the accumulator is rescaled rarely);
 //   * chunks of one sequence leave (normalised partial output, log-sum-exp) in a workspace and a small kernel merges
 //     them; a sequence that fits one chunk is written directly.
@@ -38,17 +42,19 @@ struct SplitParams {
 
 template <int D>
 struct SplitSmem {
-  static constexpr int kStages = (D == 128) ? 5 : 8;
-  static constexpr int kQBytes = 128 * D * 2;
+  static constexpr int kStages = (D == 128) ? 4 : 8;
+  static constexpr int kQBytes = 128 * D * 2;          // one query tile; there are two
   static constexpr int kKBytes = kSBlk * D * 2;        // one K (or V) tile
   static constexpr int kPBytes = 128 * kSBlk * 2;
   static constexpr int kQOff = 0;
-  static constexpr int kPOff = kQOff + kQBytes;
+  static constexpr int kPOff = kQOff + 2 * kQBytes;
   static constexpr int kKVOff = kPOff + 2 * kPBytes;   // stage s: K at kKVOff + s * 2 * kKBytes, V right after
   static constexpr int kBarOff = kKVOff + kStages * 2 * kKBytes;
-  // kv_full[S], kv_empty[S], q_full, q_empty, s_full[2], s_empty[2], p_full[2], p_empty[2], o_full, o_empty
-  static constexpr int kNumBars = 2 * kStages + 12;
-  static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+  // kv_full[S], kv_empty[S], then pairs: q_full, q_empty, s_full, s_empty, p_full, p_empty, o_full, o_empty,
+  // stat_full, stat_empty
+  static constexpr int kNumBars = 2 * kStages + 20;
+  static constexpr int kStatOff = kBarOff + kNumBars * 8 + 16;   // [2][32] reference maxima, [2][32] row sums
+  static constexpr int kTotal = kStatOff + 4 * 32 * 4;
 };
 
 // work item `idx` -> (chunk, sequence, kv head); chunk-major so that the valid items of equal-length sequences form a
@@ -62,13 +68,13 @@ __device__ __forceinline__ void split_item(int idx, int B, int Hkv, int& c, int&
 }
 
 template <int D>
-__global__ void __launch_bounds__(96, 1)
+__global__ void __launch_bounds__(160, 1)
 fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __grid_constant__ CUtensorMap map_q,
                          SplitParams p) {
   using L = SplitSmem<D>;
   constexpr int NS = L::kStages;
   constexpr int kDChunks = D / 64;
-  constexpr uint32_t kTmemCols = 256;   // S: 2 x 64 columns, O: D columns
+  constexpr uint32_t kTmemCols = 512;   // S: 2 x 64 columns, O: 2 x 128 columns
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = smem_raw;
   if (smem_u32(smem) & 1023u) {
@@ -81,14 +87,18 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
   uint64_t* kv_full = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t* kv_empty = kv_full + NS;
   uint64_t* q_full = kv_empty + NS;
-  uint64_t* q_empty = q_full + 1;
-  uint64_t* s_full = q_empty + 1;
+  uint64_t* q_empty = q_full + 2;
+  uint64_t* s_full = q_empty + 2;
   uint64_t* s_empty = s_full + 2;
   uint64_t* p_full = s_empty + 2;
   uint64_t* p_empty = p_full + 2;
   uint64_t* o_full = p_empty + 2;
-  uint64_t* o_empty = o_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_empty + 1);
+  uint64_t* o_empty = o_full + 2;
+  uint64_t* stat_full = o_empty + 2;
+  uint64_t* stat_empty = stat_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_empty + 2);
+  float* s_mref = reinterpret_cast<float*>(smem + L::kStatOff);      // [2][32]
+  float* s_lrun = s_mref + 64;                                       // [2][32]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rep = p.Hq / p.Hkv;
@@ -106,35 +116,64 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
     tmem_relinquish();
   }
   // rows the MMAs read but nobody writes start as zeros (Q rows >= the TMA box, P rows >= 32)
-  for (int i = tid; i < (L::kQBytes + 2 * L::kPBytes) / 16; i += blockDim.x)
+  for (int i = tid; i < (2 * L::kQBytes + 2 * L::kPBytes) / 16; i += blockDim.x)
     reinterpret_cast<uint4*>(smem)[i] = make_uint4(0, 0, 0, 0);
   fence_proxy_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
+  const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;      // output accumulator b at tmem_o + b * 128
+
+  // (chunk, sequence, kv head, first tile, tile count) of the first valid work item at or after `idx`; false at the end
+  auto find_item = [&](int& idx, int& c, int& b, int& g, int& t0, int& n, int& seq_tiles) -> bool {
+    for (; idx < total_items; idx += gridDim.x) {
+      split_item(idx, p.B, p.Hkv, c, b, g);
+      const int ctx = p.seq_lens[b];
+      seq_tiles = (ctx + kSBlk - 1) / kSBlk;
+      t0 = c * kChunkTiles;
+      const int t1 = min(seq_tiles, t0 + kChunkTiles);
+      if (t1 > t0) {
+        n = t1 - t0;
+        return true;
+      }
+    }
+    return false;
+  };
 
   if (warp == 1) {
-    // ------------------------------ K/V producer ------------------------------
+    // ------------------------------ producer: K/V ring and query rows ------------------------------
     if (lane == 0) {
-      uint32_t tile_no = 0;   // tiles loaded so far by this CTA (ring position and phase)
+      uint32_t tile_no = 0, item_no = 0;   // tiles / items issued so far by this CTA (ring position and phases)
       bool ok = true;
-      for (int idx = blockIdx.x; idx < total_items && ok; idx += gridDim.x) {
-        int c, b, g;
-        split_item(idx, p.B, p.Hkv, c, b, g);
-        const int ctx = p.seq_lens[b];
-        const int t0 = c * kChunkTiles;
-        const int t1 = min((ctx + kSBlk - 1) / kSBlk, t0 + kChunkTiles);
+      auto load_q = [&](uint32_t item, int b, int g) -> bool {
+        const int qb = item & 1;
+        if (!mbar_wait(&q_empty[qb], ((item >> 1) & 1) ^ 1, p.status, kStatusTimeoutProducer)) return false;
+        mbar_arrive_expect_tx(&q_full[qb], (uint32_t)(kDChunks * q_box_rows * 128));
+#pragma unroll
+        for (int cc = 0; cc < kDChunks; ++cc)
+          tma_load_2d(sQ + qb * L::kQBytes + cc * 16384, &map_q, &q_full[qb], cc * 64,
+                      b * p.q_rows_per_seq + g * rep);
+        return true;
+      };
+      int idx = blockIdx.x, c, b, g, t0, n, st;
+      bool have = find_item(idx, c, b, g, t0, n, st);
+      if (have) ok = load_q(0, b, g);
+      while (have && ok) {
+        // the item after this one (its query rows are fetched a few tiles into the current item, when the score
+        // MMAs of the item before have long completed and their query buffer is free)
+        int idx2 = idx + gridDim.x, c2, b2, g2, t02, n2, st2;
+        const bool have2 = find_item(idx2, c2, b2, g2, t02, n2, st2);
+        const int q_at = min(n - 1, 3);
         const int* blocks = p.block_table + (size_t)b * p.max_blocks;
-        for (int t = t0; t < t1; ++t, ++tile_no) {
+        for (int t = 0; t < n && ok; ++t, ++tile_no) {
           const int stage = tile_no % NS;
           const uint32_t round = tile_no / NS;
           if (!mbar_wait(&kv_empty[stage], (round & 1) ^ 1, p.status, kStatusTimeoutProducer)) {
             ok = false;
             break;
           }
-          const int blk = blocks[t];
+          const int blk = blocks[t0 + t];
           uint8_t* sk = sKV + stage * 2 * L::kKBytes;
           uint8_t* sv = sk + L::kKBytes;
           mbar_arrive_expect_tx(&kv_full[stage], 2 * L::kKBytes);
@@ -145,32 +184,26 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
             tma_load_2d(sk + cc * 8192, &map_cache, &kv_full[stage], cc * 64, krow);
             tma_load_2d(sv + cc * 8192, &map_cache, &kv_full[stage], cc * 64, vrow);
           }
+          if (t == q_at && have2) ok = load_q(item_no + 1, b2, g2);
         }
+        ++item_no;
+        idx = idx2; c = c2; b = b2; g = g2; t0 = t02; n = n2; st = st2;
+        have = have2;
       }
     }
   } else if (warp == 2) {
-    // ------------------------------ MMA issuer (and Q loads) ------------------------------
+    // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, kSBlk, 0, 0);
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, D, 0, 1);
       uint32_t tile_no = 0, item_no = 0;
       bool ok = true;
-      const uint32_t aq = smem_u32(sQ);
-      for (int idx = blockIdx.x; idx < total_items && ok; idx += gridDim.x) {
-        int c, b, g;
-        split_item(idx, p.B, p.Hkv, c, b, g);
-        const int ctx = p.seq_lens[b];
-        const int t0 = c * kChunkTiles;
-        const int t1 = min((ctx + kSBlk - 1) / kSBlk, t0 + kChunkTiles);
-        if (t1 <= t0) continue;
-        const int n = t1 - t0;
-        // the previous item's score MMAs have read Q: fetch this item's query rows
-        if (!mbar_wait(q_empty, (item_no & 1) ^ 1, p.status, kStatusTimeoutMma)) break;
-        mbar_arrive_expect_tx(q_full, (uint32_t)(kDChunks * q_box_rows * 128));
-#pragma unroll
-        for (int cc = 0; cc < kDChunks; ++cc)
-          tma_load_2d(sQ + cc * 16384, &map_q, q_full, cc * 64, b * p.q_rows_per_seq + g * rep);
-        if (!mbar_wait(q_full, item_no & 1, p.status, kStatusTimeoutMma)) break;
+      int idx = blockIdx.x, c, b, g, t0, n, st;
+      for (; ok && find_item(idx, c, b, g, t0, n, st); idx += gridDim.x) {
+        const int ib = item_no & 1;                   // query buffer and output accumulator of this item
+        const uint32_t aq = smem_u32(sQ + ib * L::kQBytes);
+        const uint32_t tmem_oi = tmem_o + ib * 128;
+        if (!mbar_wait(&q_full[ib], (item_no >> 1) & 1, p.status, kStatusTimeoutMma)) break;
         tc_fence_after();
         const uint32_t first_tile = tile_no;
         for (int t = 0; t <= n && ok; ++t) {
@@ -193,16 +226,16 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
               umma_bf16_ss(tmem_s + sb_ * 64, da, db, idesc_s, kk ? 1u : 0u);
             }
             umma_commit(&s_full[sb_]);
-            if (t == n - 1) umma_commit(q_empty);
+            if (t == n - 1) umma_commit(&q_empty[ib]);
           }
           if (t > 0) {
             // O += P(t-1) V(t-1)
             const uint32_t tn = first_tile + t - 1;
             const int stage = tn % NS;
             const int pb = tn & 1;
-            // (first PV of the item: the soft-max warp has read the previous item's output accumulator)
+            // (first PV of the item: the output warp has read this accumulator's previous item)
             if (!mbar_wait(&p_full[pb], (tn >> 1) & 1, p.status, kStatusTimeoutMma) ||
-                (t == 1 && !mbar_wait(o_empty, (item_no & 1) ^ 1, p.status, kStatusTimeoutMma))) {
+                (t == 1 && !mbar_wait(&o_empty[ib], ((item_no >> 1) & 1) ^ 1, p.status, kStatusTimeoutMma))) {
               ok = false;
               break;
             }
@@ -213,31 +246,26 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
             for (int kk = 0; kk < kSBlk / 16; ++kk) {
               const uint64_t da = umma_smem_desc(ap + kk * 32, 16, 1024);
               const uint64_t db = umma_smem_desc(bv + kk * 2048, 8192, 1024);
-              umma_bf16_ss(tmem_o, da, db, idesc_o, (t > 1 || kk) ? 1u : 0u);
+              umma_bf16_ss(tmem_oi, da, db, idesc_o, (t > 1 || kk) ? 1u : 0u);
             }
             umma_commit(&kv_empty[stage]);
             umma_commit(&p_empty[pb]);
-            if (t == n) umma_commit(o_full);
+            if (t == n) umma_commit(&o_full[ib]);
           }
         }
         tile_no += n;
         ++item_no;
       }
     }
-  } else {
-    // ------------------------------ soft-max and output (warp 0: TMEM lanes 0..31) ------------------------------
+  } else if (warp == 0) {
+    // ------------------------------ soft-max (warp 0: TMEM lanes 0..31) ------------------------------
     uint32_t tile_no = 0, item_no = 0;
     bool ok = true;
     const bool row_valid = lane < rep;
-    for (int idx = blockIdx.x; idx < total_items && ok; idx += gridDim.x) {
-      int c, b, g;
-      split_item(idx, p.B, p.Hkv, c, b, g);
+    int idx = blockIdx.x, c, b, g, t0, n, n_seq_tiles;
+    for (; ok && find_item(idx, c, b, g, t0, n, n_seq_tiles); idx += gridDim.x) {
       const int ctx = p.seq_lens[b];
-      const int t0 = c * kChunkTiles;
-      const int n_seq_tiles = (ctx + kSBlk - 1) / kSBlk;
-      const int t1 = min(n_seq_tiles, t0 + kChunkTiles);
-      if (t1 <= t0) continue;
-      const int n = t1 - t0;
+      const uint32_t tmem_oi = tmem_o + (item_no & 1) * 128;
       float m_ref = -INFINITY, l_run = 0.f;
       if (rep <= 8) {
         // Narrow groups (at most 8 query heads per kv head): the scores are read in the accumulator-fragment layout,
@@ -301,11 +329,11 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
 #pragma unroll 1
             for (int cc = 0; cc < D / 32; ++cc) {
               uint32_t r[32];
-              tmem_ld_32x32(tmem_o + cc * 32, r);
+              tmem_ld_32x32(tmem_oi + cc * 32, r);
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st_32x32(tmem_o + cc * 32, r);
+              tmem_st_32x32(tmem_oi + cc * 32, r);
             }
             tmem_st_wait();
             tc_fence_before();
@@ -387,11 +415,11 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
   #pragma unroll 1
             for (int cc = 0; cc < D / 32; ++cc) {
               uint32_t r[32];
-              tmem_ld_32x32(tmem_o + cc * 32, r);
+              tmem_ld_32x32(tmem_oi + cc * 32, r);
               tmem_ld_wait();
   #pragma unroll
               for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-              tmem_st_32x32(tmem_o + cc * 32, r);
+              tmem_st_32x32(tmem_oi + cc * 32, r);
             }
             tmem_st_wait();
             tc_fence_before();
@@ -426,12 +454,40 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
       }
       if (!ok) break;
       tile_no += n;
-      // item output: all PV MMAs of the item have completed
-      if (!__all_sync(0xffffffffu, mbar_wait(o_full, item_no & 1, p.status, kStatusTimeoutEpilogue))) {
+      // hand the row statistics to the output warp (lane r holds row r's values in both paths) and go on with the
+      // next item: normalisation and store of this item's accumulator overlap its tiles
+      {
+        const int ib = item_no & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(&stat_empty[ib], ((item_no >> 1) & 1) ^ 1, p.status,
+                                               kStatusTimeoutEpilogue))) {
+          ok = false;
+          break;
+        }
+        s_mref[ib * 32 + lane] = m_ref;
+        s_lrun[ib * 32 + lane] = l_run;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&stat_full[ib]);
+      }
+      ++item_no;
+    }
+  } else if (warp == 4) {
+    // ------------------------------ output (warp 4: TMEM lanes 0..31) ------------------------------
+    uint32_t item_no = 0;
+    bool ok = true;
+    const bool row_valid = lane < rep;
+    int idx = blockIdx.x, c, b, g, t0, n, n_seq_tiles;
+    for (; ok && find_item(idx, c, b, g, t0, n, n_seq_tiles); idx += gridDim.x) {
+      const int ib = item_no & 1;
+      const uint32_t par = (item_no >> 1) & 1;
+      const uint32_t tmem_oi = tmem_o + ib * 128;
+      // the item's statistics are in shared memory and all its PV MMAs have completed
+      if (!__all_sync(0xffffffffu, mbar_wait(&stat_full[ib], par, p.status, kStatusTimeoutEpilogue)) ||
+          !__all_sync(0xffffffffu, mbar_wait(&o_full[ib], par, p.status, kStatusTimeoutEpilogue))) {
         ok = false;
         break;
       }
       tc_fence_after();
+      const float m_ref = s_mref[ib * 32 + lane], l_run = s_lrun[ib * 32 + lane];
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       const int head = g * rep + (row_valid ? lane : 0);
       const bool single = n_seq_tiles <= kChunkTiles;
@@ -440,7 +496,7 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
 #pragma unroll 1
       for (int cc = 0; cc < D / 32; ++cc) {
         uint32_t r[32];
-        tmem_ld_32x32(tmem_o + cc * 32, r);
+        tmem_ld_32x32(tmem_oi + cc * 32, r);
         tmem_ld_wait();
         if (row_valid) {
           if (single) {
@@ -467,7 +523,10 @@ fmha_decode_split_kernel(const __grid_constant__ CUtensorMap map_cache, const __
         p.ws_lse[((size_t)b * p.Hq + head) * p.max_chunks + c] = l_run > 0.f ? m_ref + log2f(l_run) : -INFINITY;
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(o_empty);
+      if (lane == 0) {
+        mbar_arrive(&o_empty[ib]);
+        mbar_arrive(&stat_empty[ib]);
+      }
       ++item_no;
     }
   }
@@ -519,7 +578,7 @@ static int launch_decode_split(const CUtensorMap& mc, const CUtensorMap& mq, con
   }
   const int items = p.max_chunks * p.B * p.Hkv;
   const int grid = items < num_sms() ? items : num_sms();
-  kernel<<<grid, 96, L::kTotal, stream>>>(mc, mq, p);
+  kernel<<<grid, 160, L::kTotal, stream>>>(mc, mq, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   fmha_decode_merge_kernel<D><<<dim3(p.B, p.Hq), D, 0, stream>>>(p);
