@@ -40,15 +40,20 @@ def main() -> None:
     model = build_model(cfg, dtype=torch.bfloat16, device=dev, seed=0)
     res = {"model": args.model, "layers": cfg.num_layers, "seqs": args.seqs, "context": args.context,
            "max_model_len": args.max_model_len, "n": args.n, "decode_kernel": args.decode_kernel or "default"}
+    # prompts are prefilled at most 256 k tokens per engine iteration (a whole 256 x 2700 batch would need a 24 GB MLP
+    # intermediate); every sequence decodes `extra` more rounds than the three of a single-batch prefill, so that a
+    # round exists in which all sequences are active (the one that is reported)
+    total_prompt = args.seqs // args.n * args.context
+    batched = max(8192, min(total_prompt, 262144))
+    extra = (total_prompt + batched - 1) // batched - 1
     for graph in ([False] if args.no_graph else [False, True]):
         eng = RolloutEngine(model, max_num_seqs=args.seqs,
-                            max_model_len=args.max_model_len or args.context + 4 * args.steps + 64,
-                            use_cuda_graph=graph, sync_interval=args.steps,
-                            max_num_batched_tokens=max(8192, args.seqs // args.n * args.context))
+                            max_model_len=args.max_model_len or args.context + (4 + extra) * args.steps + 64,
+                            use_cuda_graph=graph, sync_interval=args.steps, max_num_batched_tokens=batched)
         g = torch.Generator().manual_seed(0)
         prompts = [torch.randint(3, cfg.vocab_size, (args.context,), generator=g).tolist()
                    for _ in range(args.seqs // args.n)]
-        sp = SamplingParams(n=args.n, temperature=1.0, max_new_tokens=1 + 3 * args.steps, eos_token_id=None)
+        sp = SamplingParams(n=args.n, temperature=1.0, max_new_tokens=1 + (3 + extra) * args.steps, eos_token_id=None)
         # generate = prefill + first token + 3 rounds of `steps` decode steps; time the last round only
         times = []
         orig = eng._run_decode_steps
@@ -64,7 +69,9 @@ def main() -> None:
         eng._run_decode_steps = timed
         eng.generate(prompts, sp)
         lib.check_status()
-        res["graph_ms_per_step" if graph else "eager_ms_per_step"] = times[-1]
+        # rounds 0 .. extra-1 run while later prompts are still being prefilled; round extra + 2 is the third with every
+        # sequence active and none finished
+        res["graph_ms_per_step" if graph else "eager_ms_per_step"] = times[min(extra + 2, len(times) - 1)]
         eng.sleep()
     print(json.dumps(res))
 
