@@ -29,6 +29,6 @@ def run_smoke(device: torch.device) -> dict:
     lib.check_status()
     assert torch.isfinite(loss).item() and torch.isfinite(norm).item()
     assert len(outs) == 4 and all(len(o.token_ids) == 12 for o in outs)
-    res = {"loss": float(loss), "grad_norm": float(norm), "kernel_launches": lib.launch_count()}
+    res = {"loss": float(loss.detach()), "grad_norm": float(norm.detach()), "kernel_launches": lib.launch_count()}
     print(f"smoke ok: {res}")
     return res
