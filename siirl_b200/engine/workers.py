@@ -370,10 +370,13 @@ class _ModelWorkerBase:
             seq = ((r.prompt_length or 512) + (r.response_length or 512)) if r is not None else 4096
             tokens = max(int(getattr(cfgs, "ppo_max_token_len_per_gpu", 0) or 0),
                          int(getattr(cfgs, "ppo_micro_batch_size_per_gpu", 0) or 1) * seq, seq)
-            rows = tokens // n + 64 * n
+            rows = tokens // n + 128 * n
+            layout = str(getattr(cfgs.megatron, "context_parallel_layout", "zigzag") or "zigzag")
+            if layout not in ("zigzag", "contiguous"):
+                raise ValueError(f"context_parallel_layout={layout!r}: expected 'zigzag' or 'contiguous'")
             self._cp_ctx = RingContext(mine, comm, max_rows=rows,
                                        qkv_width=(mc.num_heads + 2 * mc.num_kv_heads) * mc.head_dim,
-                                       kv_width=2 * mc.num_kv_heads * mc.head_dim)
+                                       kv_width=2 * mc.num_kv_heads * mc.head_dim, zigzag=layout == "zigzag")
         model.attach_context_parallel(self._cp_ctx)
 
     def _attach_expert_parallel(self, model_args) -> None:

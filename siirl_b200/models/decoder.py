@@ -449,18 +449,22 @@ class DecoderLM(nn.Module):
         return r * Tl, (r + 1) * Tl, Tl * n - T
 
     def cp_rows(self, info: SeqInfo):
-        """Context parallelism: every sequence is padded to a multiple of the group size and cut into equal chunks;
-        this rank holds chunk ``rank`` of each.  Returns (index into the unpadded packed stream of each local row,
-        -1 for padding; the same for use as a mask; the ``SeqInfo`` of the chunk lengths)."""
+        """Context parallelism: every sequence is padded to a multiple of the number of chunks and cut into equal
+        chunks; this rank holds chunk ``rank`` of each (contiguous assignment) or chunks ``rank`` and
+        ``2 n - 1 - rank`` of ``2 n`` (zig-zag).  Returns (index into the unpadded packed stream of each local row,
+        -1 for padding; the same for use as a mask; the ``SeqInfo`` of the local lengths)."""
+        from ..parallel.ring_attention import chunk_positions
         cp = self.cp
         n, r = cp.cp, cp.rank
+        zz = bool(getattr(cp, "zigzag", False))
+        parts = 2 * n if zz else n
         dev = self.embed_tokens.device
         idx, lens, start = [], [], 0
         for L in info.seqlens:
-            c = (L + n - 1) // n
-            j = torch.arange(r * c, (r + 1) * c)
+            local = (L + parts - 1) // parts * (parts // n)
+            j = chunk_positions([local], n, r, zz)
             idx.append(torch.where(j < L, j + start, torch.full_like(j, -1)))
-            lens.append(c)
+            lens.append(local)
             start += L
         rows = torch.cat(idx).to(dev) if idx else torch.zeros(0, dtype=torch.int64, device=dev)
         return rows, rows >= 0, SeqInfo(lens, device=dev)

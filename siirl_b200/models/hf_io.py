@@ -262,11 +262,12 @@ def _qwen_visual_state(vision, prefix: str = "model.visual.") -> Iterator[Tuple[
         yield p + "attn.qkv.bias", b.qkv_bias.data
         yield p + "attn.proj.weight", b.proj_weight.data
         yield p + "attn.proj.bias", b.proj_bias.data
+        Ip = b.padded_intermediate                      # rows / columns beyond I are the zero padding of the MLP width
         yield p + "mlp.gate_proj.weight", b.gate_up_weight.data[:I]
         yield p + "mlp.gate_proj.bias", b.gate_up_bias.data[:I]
-        yield p + "mlp.up_proj.weight", b.gate_up_weight.data[I:]
-        yield p + "mlp.up_proj.bias", b.gate_up_bias.data[I:]
-        yield p + "mlp.down_proj.weight", b.down_weight.data
+        yield p + "mlp.up_proj.weight", b.gate_up_weight.data[Ip:Ip + I]
+        yield p + "mlp.up_proj.bias", b.gate_up_bias.data[Ip:Ip + I]
+        yield p + "mlp.down_proj.weight", b.down_weight.data[:, :I]
         yield p + "mlp.down_proj.bias", b.down_bias.data
     yield prefix + "merger.ln_q.weight", vision.merger_norm.data
     yield prefix + "merger.mlp.0.weight", vision.merger_fc1_weight.data

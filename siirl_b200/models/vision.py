@@ -31,10 +31,19 @@ class VisionBlock(nn.Module):
         self.proj_weight = param((H, H), dtype, device, 0.02, gen)
         self.proj_bias = param((H,), dtype, device, 0, gen)
         self.norm2 = param((H,), dtype, device, -1, gen)
-        self.gate_up_weight = param((2 * I, H), dtype, device, 0.02, gen)
-        self.gate_up_bias = param((2 * I,), dtype, device, 0, gen)
-        self.down_weight = param((H, I), dtype, device, 0.02, gen)
+        # The element-wise and GEMM kernels move 16-byte vectors, so the MLP width is rounded up to a multiple of 64
+        # (Qwen2.5-VL: 3420 -> 3456).  The extra gate / up rows and down columns are zero and stay zero under
+        # training: their activations are silu(0) * 0 and the gradient reaching them is a product with those zeros.
+        Ip = self.padded_intermediate = (I + 63) // 64 * 64
+        self.gate_up_weight = param((2 * Ip, H), dtype, device, 0.02, gen)
+        self.gate_up_bias = param((2 * Ip,), dtype, device, 0, gen)
+        self.down_weight = param((H, Ip), dtype, device, 0.02, gen)
         self.down_bias = param((H,), dtype, device, 0, gen)
+        if Ip != I:
+            with torch.no_grad():
+                self.gate_up_weight[I:Ip].zero_()
+                self.gate_up_weight[Ip + I:].zero_()
+                self.down_weight[:, I:].zero_()
 
 
 class VisionTower(nn.Module):

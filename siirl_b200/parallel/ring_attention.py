@@ -10,7 +10,15 @@ previous chunk; partial results are merged with their log-sum-exp.  The backward
 FINAL ``out`` / ``lse`` (as flash attention does), accumulates dQ locally and returns dK/dV of remote chunks to
 their owners through a second pull.
 
-Chunks are assigned contiguously, so rank r does r + 1 blocks of work (no zig-zag balancing).
+Two chunk assignments:
+
+* contiguous (``zigzag=False``): rank r holds chunk r of ``cp`` and does r + 1 blocks of work: the last rank sets the
+  pace with ``cp`` blocks while rank 0 does one.
+* zig-zag (``zigzag=True``, the balanced assignment Megatron-core / Transformer-Engine use): every sequence is cut into
+  ``2 cp`` chunks and rank r holds chunks r ("low") and ``2 cp - 1 - r`` ("high"), stored one after the other.  Its
+  own pair is one causal block over the concatenation; against a rank j < r all local queries see j's low chunk only;
+  against a rank j > r only the high queries see anything, and they see both of j's chunks.  Every remote step is two
+  ``c x c`` unmasked blocks, so all ranks do the same ``2 cp + 1`` half-blocks of work.
 """
 from __future__ import annotations
 
@@ -55,8 +63,10 @@ def _block_bwd(qkv, out, lse, dout, info: SeqInfo, hq, hkv, d, causal, scale) ->
 class RingContext:
     """Symmetric staging of one context-parallel group: two alternating ``qkv`` buffers and the dK/dV return slots."""
 
-    def __init__(self, group, comm=None, max_rows: int = 0, qkv_width: int = 0, kv_width: int = 0):
+    def __init__(self, group, comm=None, max_rows: int = 0, qkv_width: int = 0, kv_width: int = 0,
+                 zigzag: bool = False):
         self.group, self.comm = group, comm
+        self.zigzag = bool(zigzag)
         self.cp = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
         self.stage = None
@@ -76,11 +86,19 @@ class RingContext:
     def pull_cols(self, buf: torch.Tensor, src_rank: int, out: torch.Tensor, src_off_elems: int, dst_off_elems: int,
                   src_pitch: int, dst_pitch: int, rows: int, cols: int) -> None:
         """Copy ``rows x cols`` bf16 elements from ``src_rank``'s instance of ``buf`` into ``out``."""
-        blk = (_PullBlock * 1)(_PullBlock(src_off_elems * 2, dst_off_elems * 2, src_pitch * 2, dst_pitch * 2, rows,
-                                          cols * 2, src_rank, 0))
+        self.pull_blocks(buf, out, [(src_rank, src_off_elems, dst_off_elems, src_pitch, dst_pitch, rows, cols)])
+
+    def pull_blocks(self, buf: torch.Tensor, out: torch.Tensor, blocks) -> None:
+        """``blocks``: (source rank, source offset, destination offset, source pitch, destination pitch, rows,
+        columns), all in bf16 elements; launched 64 blocks at a time."""
         L = _lib.get_lib()
-        _lib.check(L.sb_block_pull(self.comm.peers_of(buf).ptr_array, self.cp, blk, 1, _lib.ptr(out), _lib.stream()),
-                   "sb_block_pull")
+        peers = self.comm.peers_of(buf).ptr_array
+        for at in range(0, len(blocks), 64):
+            part = blocks[at:at + 64]
+            arr = (_PullBlock * len(part))()
+            for i, (r, so, do, sp_, dp_, rows, cols) in enumerate(part):
+                arr[i] = _PullBlock(so * 2, do * 2, sp_ * 2, dp_ * 2, rows, cols * 2, r, 0)
+            _lib.check(L.sb_block_pull(peers, self.cp, arr, len(part), _lib.ptr(out), _lib.stream()), "sb_block_pull")
 
 
 def _merge(out, lse, o_s, lse_s):
@@ -148,6 +166,128 @@ class _RingAttn(torch.autograd.Function):
         return torch.cat([dq, dkv], dim=1).to(qkv.dtype), None, None, None, None, None, None
 
 
+def _halves(info: SeqInfo, device):
+    """Zig-zag layout: a rank's rows of sequence i are its low chunk then its high chunk (``c_i`` rows each).
+    Returns (row indices of the low halves, of the high halves, the ``SeqInfo`` of the ``c_i, c_i, ...`` half
+    blocks, per-sequence (first row, c_i))."""
+    lo, hi, lens, spans, at = [], [], [], [], 0
+    for n in info.seqlens:
+        assert n % 2 == 0, "zig-zag chunks come in pairs"
+        c = n // 2
+        lo.append(torch.arange(at, at + c))
+        hi.append(torch.arange(at + c, at + n))
+        lens += [c, c]
+        spans.append((at, c))
+        at += n
+    cat = lambda xs: (torch.cat(xs) if xs else torch.zeros(0, dtype=torch.int64)).to(device)  # noqa: E731
+    return cat(lo), cat(hi), SeqInfo(lens, device=device), spans
+
+
+def _fetch_zigzag(rc: RingContext, buf, qkv, src: int, lo, hi, spans, W: int, qw: int, kvw: int, side):
+    """Block against rank ``src`` in the zig-zag layout (on a side stream).  ``src`` below this rank: the local
+    queries, with ``src``'s low-chunk K/V under both halves.  ``src`` above: the high queries under both halves, with
+    ``src``'s K/V as they lie."""
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        if src < rc.rank:
+            blk = qkv.clone()
+            blocks = []
+            for at, c in spans:
+                if c:
+                    blocks.append((src, at * W + qw, at * W + qw, W, W, c, kvw))
+                    blocks.append((src, at * W + qw, (at + c) * W + qw, W, W, c, kvw))
+            rc.pull_blocks(buf, blk, blocks)
+        else:
+            dup = torch.empty(qkv.shape[0], dtype=torch.int64, device=qkv.device)
+            dup[lo] = hi
+            dup[hi] = hi
+            blk = qkv.index_select(0, dup)
+            rc.pull_blocks(buf, blk, [(src, qw, qw, W, W, qkv.shape[0], kvw)])
+        ev = torch.cuda.Event()
+        ev.record(side)
+    blk.record_stream(torch.cuda.current_stream())
+    return blk, ev
+
+
+class _RingAttnZigzag(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, rc: RingContext, info: SeqInfo, hq, hkv, d, scale):
+        me, n = rc.rank, rc.cp
+        Tl, W = qkv.shape
+        qw, kvw = hq * d, 2 * hkv * d
+        lo, hi, info_h, spans = _halves(info, qkv.device)
+        buf = rc.publish(qkv)
+        side = torch.cuda.Stream()
+        out, lse = _block_fwd(qkv, info, hq, hkv, d, True, scale)        # own pair of chunks: one causal block
+        order = [(me - s) % n for s in range(1, n)]
+        nxt = _fetch_zigzag(rc, buf, qkv, order[0], lo, hi, spans, W, qw, kvw, side) if order else None
+        for k, j in enumerate(order):
+            blk, ev = nxt
+            torch.cuda.current_stream().wait_event(ev)
+            nxt = (_fetch_zigzag(rc, buf, qkv, order[k + 1], lo, hi, spans, W, qw, kvw, side)
+                   if k + 1 < len(order) else None)
+            o_s, lse_s = _block_fwd(blk, info_h, hq, hkv, d, False, scale)
+            if j < me:
+                out, lse = _merge(out, lse, o_s, lse_s)
+            else:                                                        # both halves hold partials of the high queries
+                o_h, l_h = _merge(out[hi], lse[:, hi], o_s[lo], lse_s[:, lo])
+                o_h, l_h = _merge(o_h, l_h, o_s[hi], lse_s[:, hi])
+                out = out.index_copy(0, hi, o_h)
+                lse = lse.index_copy(1, hi, l_h)
+        ctx.save_for_backward(qkv, out, lse)
+        ctx.meta = (rc, info, hq, hkv, d, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse = ctx.saved_tensors
+        rc, info, hq, hkv, d, scale = ctx.meta
+        me, n = rc.rank, rc.cp
+        Tl, W = qkv.shape
+        qw, kvw = hq * d, 2 * hkv * d
+        lo, hi, info_h, spans = _halves(info, qkv.device)
+        dout = dout.contiguous()
+        buf = rc.publish(qkv)
+        side = torch.cuda.Stream()
+        g = _block_bwd(qkv, out, lse, dout, info, hq, hkv, d, True, scale)
+        dq = g[:, :qw].float()
+        dkv = g[:, qw:].float()
+        gs = rc.gstage.view(n, -1)
+        dup = torch.empty(Tl, dtype=torch.int64, device=qkv.device)
+        dup[lo] = hi
+        dup[hi] = hi
+        out_h = lse_h = dout_h = None
+        order = [(me - s) % n for s in range(1, n)]
+        nxt = _fetch_zigzag(rc, buf, qkv, order[0], lo, hi, spans, W, qw, kvw, side) if order else None
+        for k, j in enumerate(order):
+            blk, ev = nxt
+            torch.cuda.current_stream().wait_event(ev)
+            nxt = (_fetch_zigzag(rc, buf, qkv, order[k + 1], lo, hi, spans, W, qw, kvw, side)
+                   if k + 1 < len(order) else None)
+            if j < me:
+                g = _block_bwd(blk, out, lse, dout, info_h, hq, hkv, d, False, scale)
+                dq += g[:, :qw].float()
+                gk = g[:, qw:].float()
+                ret = torch.zeros(Tl, kvw, dtype=qkv.dtype, device=qkv.device)
+                ret[lo] = (gk[lo] + gk[hi]).to(qkv.dtype)                # both halves attended j's low chunk
+            else:
+                if out_h is None:
+                    out_h = out.index_select(0, dup)
+                    lse_h = lse.index_select(1, dup).contiguous()
+                    dout_h = dout.index_select(0, dup)
+                g = _block_bwd(blk, out_h, lse_h, dout_h, info_h, hq, hkv, d, False, scale)
+                dq.index_add_(0, hi, g[lo, :qw].float() + g[hi, :qw].float())
+                ret = g[:, qw:]
+            gs[k + 1, : Tl * kvw].copy_(ret.reshape(-1))                 # slot s: gradient for the chunks of rank me - s
+        rc.comm.barrier()
+        tmp = torch.empty(Tl, kvw, dtype=qkv.dtype, device=qkv.device)
+        for s in range(1, n):                                            # rank me + s used my chunks at its step s
+            rc.pull_cols(rc.gstage, (me + s) % n, tmp, s * gs.shape[1], 0, kvw, kvw, Tl, kvw)
+            dkv += tmp.float()
+        rc.comm.barrier()                                                # the return slots may be rewritten
+        return torch.cat([dq, dkv], dim=1).to(qkv.dtype), None, None, None, None, None, None
+
+
 def _fetch(rc: RingContext, buf, qkv, src: int, Tl: int, W: int, qw: int, kvw: int, side):
     """Block for chunk ``src``: local queries next to the K/V columns pulled from rank ``src`` (on a side stream)."""
     side.wait_stream(torch.cuda.current_stream())
@@ -162,14 +302,16 @@ def _fetch(rc: RingContext, buf, qkv, src: int, Tl: int, W: int, qw: int, kvw: i
 
 def ring_attention(qkv: torch.Tensor, rc: Optional[RingContext], info: SeqInfo, n_heads: int, n_kv_heads: int,
                    head_dim: int, scale: Optional[float] = None) -> torch.Tensor:
-    """Causal attention of this rank's chunk ``qkv [Tl, (hq + 2 hkv) d]`` against the chunks of ranks ``<= rank``."""
+    """Causal attention of this rank's chunk(s) ``qkv [Tl, (hq + 2 hkv) d]`` against every chunk at lower positions
+    (``rc.zigzag`` selects the chunk assignment; ``info`` holds the local length of every sequence)."""
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     from ..ops.attention import attention_packed
     if rc is None or rc.cp == 1:
         return attention_packed(qkv, info, n_heads, n_kv_heads, head_dim, causal=True, scale=scale)
     if qkv.is_cuda and rc.stage is not None:
         assert head_dim in (64, 128), "ring attention uses the 64/128-wide attention kernels"
-        return _RingAttn.apply(qkv.contiguous(), rc, info, n_heads, n_kv_heads, head_dim, scale)
+        fn = _RingAttnZigzag if rc.zigzag else _RingAttn
+        return fn.apply(qkv.contiguous(), rc, info, n_heads, n_kv_heads, head_dim, scale)
     return _ring_attention_gathered(qkv, rc, info, n_heads, n_kv_heads, head_dim, scale)
 
 
@@ -191,43 +333,54 @@ class _GatherRows(torch.autograd.Function):
         return g[dist.get_rank(ctx.group)], None
 
 
+def chunk_positions(local_lens, cp: int, rank: int, zigzag: bool) -> torch.Tensor:
+    """Position inside its sequence of every local row of rank ``rank`` (``local_lens``: that rank's row count per
+    sequence, the same on every rank)."""
+    pos = []
+    for n in local_lens:
+        if zigzag:
+            c = n // 2
+            pos.append(torch.arange(rank * c, (rank + 1) * c))
+            pos.append(torch.arange((2 * cp - 1 - rank) * c, (2 * cp - rank) * c))
+        else:
+            pos.append(torch.arange(rank * n, (rank + 1) * n))
+    return torch.cat(pos) if pos else torch.zeros(0, dtype=torch.int64)
+
+
 def _ring_attention_gathered(qkv, rc: RingContext, info: SeqInfo, hq, hkv, d, scale):
-    """Library-collective path (CPU / gloo): gather all chunks, attend with an explicit chunk-causal mask."""
+    """Library-collective path (CPU / gloo): gather all chunks, attend under a mask built from the rows' positions."""
     Tl = qkv.shape[0]
     allq = _GatherRows.apply(qkv, rc.group)                              # [cp, Tl, W]
     q = qkv[:, : hq * d].reshape(Tl, hq, d).float()
     out = torch.zeros(Tl, hq, d, dtype=torch.float32, device=qkv.device)
     cu = info.cu_seqlens_cpu
     rep = hq // hkv
+    pos = [chunk_positions(info.seqlens, rc.cp, r, rc.zigzag).to(qkv.device) for r in range(rc.cp)]
     for i in range(len(cu) - 1):
         a, b = cu[i], cu[i + 1]
         if b == a:
             continue
-        ks, vs, masks = [], [], []
-        for r in range(rc.rank + 1):
-            kv = allq[r, a:b, hq * d:].float()
-            ks.append(kv[:, : hkv * d].reshape(b - a, hkv, d))
-            vs.append(kv[:, hkv * d:].reshape(b - a, hkv, d))
-            m = torch.ones(b - a, b - a, dtype=torch.bool, device=qkv.device)
-            masks.append(torch.tril(m) if r == rc.rank else m)
-        k = torch.cat(ks).repeat_interleave(rep, dim=1)
-        v = torch.cat(vs).repeat_interleave(rep, dim=1)
-        mask = torch.cat(masks, dim=1)
+        kv = allq[:, a:b, hq * d:].float().reshape(rc.cp * (b - a), 2, hkv, d)
+        k = kv[:, 0].repeat_interleave(rep, dim=1)
+        v = kv[:, 1].repeat_interleave(rep, dim=1)
+        kpos = torch.cat([p[a:b] for p in pos])
+        mask = pos[rc.rank][a:b, None] >= kpos[None, :]
         sc = torch.einsum("qhd,khd->hqk", q[a:b], k) * scale
         sc = sc.masked_fill(~mask[None], float("-inf"))
         out[a:b] = torch.einsum("hqk,khd->qhd", torch.softmax(sc, dim=-1), v)
     return out.reshape(Tl, hq * d).to(qkv.dtype)
 
 
-def split_for_context_parallel(seqlens, cp: int, rank: int, device=None):
-    """Row indices (into the packed stream), positions and the chunk ``SeqInfo`` of rank ``rank`` when every sequence
-    (length divisible by ``cp``) is cut into ``cp`` contiguous chunks."""
-    idx, pos, lens, start = [], [], [], 0
+def split_for_context_parallel(seqlens, cp: int, rank: int, device=None, zigzag: bool = False):
+    """Row indices (into the packed stream), positions and the local ``SeqInfo`` of rank ``rank`` when every sequence
+    is cut into ``cp`` contiguous chunks (length divisible by ``cp``) or, with ``zigzag``, into ``2 cp`` chunks of
+    which the rank takes chunk ``rank`` and chunk ``2 cp - 1 - rank`` (length divisible by ``2 cp``)."""
+    parts = cp * (2 if zigzag else 1)
+    idx, lens, start = [], [], 0
     for n in seqlens:
-        assert n % cp == 0, "context parallelism needs sequence lengths divisible by the group size"
-        c = n // cp
-        idx.append(torch.arange(start + rank * c, start + (rank + 1) * c))
-        pos.append(torch.arange(rank * c, (rank + 1) * c))
-        lens.append(c)
+        assert n % parts == 0, "context parallelism needs sequence lengths divisible by the number of chunks"
+        lens.append(n // cp)
+        idx.append(chunk_positions([n // cp], cp, rank, zigzag) + start)
         start += n
-    return torch.cat(idx).to(device), torch.cat(pos).to(device), SeqInfo(lens, device=device)
+    pos = chunk_positions(lens, cp, rank, zigzag)
+    return torch.cat(idx).to(device), pos.to(device), SeqInfo(lens, device=device)

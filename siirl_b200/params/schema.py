@@ -43,6 +43,9 @@ class MegatronArguments:
     tensor_model_parallel_size: int = 1
     pipeline_model_parallel_size: int = 1
     context_parallel_size: int = 1
+    # chunk assignment of ring attention: "zigzag" (rank r holds chunks r and 2n-1-r: equal causal work per rank)
+    # or "contiguous" (rank r holds chunk r and does r+1 blocks)
+    context_parallel_layout: str = "zigzag"
     expert_model_parallel_size: int = 1
     expert_tensor_parallel_size: int = 1
     virtual_pipeline_model_parallel_size: Optional[int] = None

@@ -144,9 +144,13 @@ def test_internvl_tiling_and_processor():
 def test_qwen2_5_vl_matches_transformers(tmp_path):
     """Vision tower (window attention, 2-D rope, merger), multimodal rope and language model against transformers'
     Qwen2.5-VL classes through an export in their parameter names."""
+    import dataclasses
     from siirl_b200.models.vision import mrope_positions
     cfg = get_config("tiny-vl")
+    # an MLP width that is no multiple of 8, like the released 7B tower's 3420: the model pads it internally
+    cfg = dataclasses.replace(cfg, vision=dataclasses.replace(cfg.vision, intermediate_size=108))
     model = build_model(cfg, dtype=torch.float32, device="cpu", seed=8)
+    assert model.vision.blocks[0].padded_intermediate == 128
     save_hf_model(model, str(tmp_path))
     import json
     hfc = json.load(open(tmp_path / "config.json"))

@@ -168,30 +168,32 @@ def main():
     from siirl_b200.parallel.ring_attention import RingContext, ring_attention, split_for_context_parallel
     hq6, hkv6, d6 = 4, 2, 64
     W6 = (hq6 + 2 * hkv6) * d6
-    lens6 = [64 * world, 192 * world]
+    lens6 = [128 * world, 192 * world]
     T6 = sum(lens6)
     full6 = (0.5 * torch.randn(T6, W6, generator=g)).to(dev, dtype)
     go6 = torch.randn(T6, hq6 * d6, generator=g).to(dev, dtype)
     ref_in = full6.clone().requires_grad_()
     ref_out = attention_packed(ref_in, SeqInfo(lens6, device=dev), hq6, hkv6, d6, causal=True)
     ref_out.backward(go6)
-    rows, _, info6 = split_for_context_parallel(lens6, world, rank, device=dev)
-    rc = RingContext(dist.group.WORLD, comm, max_rows=rows.numel(), qkv_width=W6, kv_width=2 * hkv6 * d6)
-    loc = full6[rows].clone().requires_grad_()
-    out6 = ring_attention(loc, rc, info6, hq6, hkv6, d6)
-    out6.backward(go6[rows])
     t6 = 0.06 if cuda else 1e-4
-    assert (out6.float() - ref_out[rows].float()).abs().max().item() < t6, "ring attention output"
-    assert (loc.grad.float() - ref_in.grad[rows].float()).abs().max().item() < 4 * t6, "ring attention gradient"
-    if cuda:
-        torch.cuda.synchronize()
-        lib.check_status()
+    for zz in (False, True):
+        rows, _, info6 = split_for_context_parallel(lens6, world, rank, device=dev, zigzag=zz)
+        rc = RingContext(dist.group.WORLD, comm, max_rows=rows.numel(), qkv_width=W6, kv_width=2 * hkv6 * d6,
+                         zigzag=zz)
+        loc = full6[rows].clone().requires_grad_()
+        out6 = ring_attention(loc, rc, info6, hq6, hkv6, d6)
+        out6.backward(go6[rows])
+        assert (out6.float() - ref_out[rows].float()).abs().max().item() < t6, f"ring attention output (zigzag={zz})"
+        assert (loc.grad.float() - ref_in.grad[rows].float()).abs().max().item() < 4 * t6, f"ring attention gradient (zigzag={zz})"
+        if cuda:
+            torch.cuda.synchronize()
+            lib.check_status()
     # 7. a decoder under context parallelism (ring attention inside every layer): the rows this rank computes equal
     #    the single-rank hidden states, and summed parameter gradients match
     m_cp = build_model(cfg5, dtype=dtype, device=dev, seed=9)
     m_ref = build_model(cfg5, dtype=dtype, device=dev, seed=9)
     m_cp.attach_context_parallel(RingContext(dist.group.WORLD, comm, max_rows=256, qkv_width=width,
-                                             kv_width=2 * cfg5.num_kv_heads * cfg5.head_dim))
+                                             kv_width=2 * cfg5.num_kv_heads * cfg5.head_dim, zigzag=True))
     lens7 = [37, 64, 23]
     info7 = SeqInfo(lens7, device=dev)
     ids7 = torch.randint(3, cfg5.vocab_size, (sum(lens7),), generator=g).to(dev)
