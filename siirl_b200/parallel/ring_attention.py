@@ -34,9 +34,35 @@ from ..ops.attention import SeqInfo
 from .ulysses import _PullBlock
 
 
+def _eager_blocks(qkv, info: SeqInfo, hq, hkv, d, causal, scale):
+    """Per sequence: (row range, q, k, v as fp32 ``[n, hq, d]``, scores ``[hq, n, n]`` with the mask applied)."""
+    cu = info.cu_seqlens_cpu
+    rep = hq // hkv
+    for i in range(len(cu) - 1):
+        a, b = cu[i], cu[i + 1]
+        if b == a:
+            continue
+        q, k, v = qkv[a:b].float().split([hq * d, hkv * d, hkv * d], dim=-1)
+        q = q.reshape(b - a, hq, d)
+        k = k.reshape(b - a, hkv, d).repeat_interleave(rep, dim=1)
+        v = v.reshape(b - a, hkv, d).repeat_interleave(rep, dim=1)
+        sc = torch.einsum("qhd,khd->hqk", q, k) * scale
+        if causal:
+            keep = torch.ones(b - a, b - a, dtype=torch.bool, device=qkv.device).tril()
+            sc = sc.masked_fill(~keep[None], float("-inf"))
+        yield a, b, q, k, v, sc
+
+
 def _block_fwd(qkv, info: SeqInfo, hq, hkv, d, causal, scale) -> Tuple[torch.Tensor, torch.Tensor]:
-    L = _lib.get_lib()
     T = qkv.shape[0]
+    if not qkv.is_cuda:                                  # eager statement of the kernel (same outputs: out, lse)
+        out = torch.zeros(T, hq * d, dtype=qkv.dtype)
+        lse = torch.zeros(hq, T, dtype=torch.float32)
+        for a, b, q, k, v, sc in _eager_blocks(qkv, info, hq, hkv, d, causal, scale):
+            lse[:, a:b] = torch.logsumexp(sc, dim=-1)
+            out[a:b] = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v).reshape(b - a, hq * d).to(qkv.dtype)
+        return out, lse
+    L = _lib.get_lib()
     out = torch.empty(T, hq * d, dtype=qkv.dtype, device=qkv.device)
     lse = torch.empty(hq, T, dtype=torch.float32, device=qkv.device)
     ts, tl, t0, n = info.tiles()
@@ -47,8 +73,24 @@ def _block_fwd(qkv, info: SeqInfo, hq, hkv, d, causal, scale) -> Tuple[torch.Ten
 
 
 def _block_bwd(qkv, out, lse, dout, info: SeqInfo, hq, hkv, d, causal, scale) -> torch.Tensor:
-    L = _lib.get_lib()
     T = qkv.shape[0]
+    if not qkv.is_cuda:          # flash-attention backward with the FINAL out / lse: P = exp(S - lse), dS = P (dP - delta)
+        dqkv = torch.zeros_like(qkv)
+        rep = hq // hkv
+        for a, b, q, k, v, sc in _eager_blocks(qkv, info, hq, hkv, d, causal, scale):
+            n = b - a
+            p = torch.exp(sc - lse[:, a:b, None])
+            do = dout[a:b].float().reshape(n, hq, d)
+            delta = (do * out[a:b].float().reshape(n, hq, d)).sum(-1).t()          # [hq, n]
+            dv = torch.einsum("hqk,qhd->khd", p, do)
+            ds = p * (torch.einsum("qhd,khd->hqk", do, v) - delta[:, :, None])
+            dq = torch.einsum("hqk,khd->qhd", ds, k) * scale
+            dk = torch.einsum("hqk,qhd->khd", ds, q) * scale
+            dk = dk.reshape(n, hkv, rep, d).sum(2)
+            dv = dv.reshape(n, hkv, rep, d).sum(2)
+            dqkv[a:b] = torch.cat([dq.reshape(n, -1), dk.reshape(n, -1), dv.reshape(n, -1)], -1).to(qkv.dtype)
+        return dqkv
+    L = _lib.get_lib()
     dqkv = torch.empty_like(qkv)
     delta = torch.empty(hq, T, dtype=torch.float32, device=qkv.device)
     dq_acc = torch.empty(T, hq * d, dtype=torch.float32, device=qkv.device)
@@ -61,27 +103,69 @@ def _block_bwd(qkv, out, lse, dout, info: SeqInfo, hq, hkv, d, causal, scale) ->
 
 
 class RingContext:
-    """Symmetric staging of one context-parallel group: two alternating ``qkv`` buffers and the dK/dV return slots."""
+    """Symmetric staging of one context-parallel group: two alternating ``qkv`` buffers and the dK/dV return slots.
+
+    ``comm``: the group's symmetric-memory communicator (GPUs).  ``emulate=True`` (CPU ranks under ``gloo``) stands in
+    for it with all-gathers: publishing a buffer hands every rank a copy of every rank's instance, and a "pull" reads
+    from that copy, so the block algorithms below run unchanged where there is no peer memory."""
 
     def __init__(self, group, comm=None, max_rows: int = 0, qkv_width: int = 0, kv_width: int = 0,
-                 zigzag: bool = False):
+                 zigzag: bool = False, emulate: bool = False):
         self.group, self.comm = group, comm
         self.zigzag = bool(zigzag)
         self.cp = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
         self.stage = None
+        self.emulate = bool(emulate) and comm is None and self.cp > 1
         if comm is not None and self.cp > 1:
             self.stage = [comm.alloc(max_rows * qkv_width, torch.bfloat16) for _ in range(2)]
             self.gstage = comm.alloc(self.cp * max_rows * kv_width, torch.bfloat16)
             self._turn = 0
             comm.barrier()
+        elif self.emulate:
+            self.stage = [None, None]
+            self._turn = 0
+            self._copies = {}
+            self._slot = (max_rows, kv_width)
+            self.gstage = None
+
+    # ---- publication ----------------------------------------------------------------------------------------------
+    def _gather(self, x: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(self.cp * x.numel(), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous().reshape(-1), group=self.group)
+        return out.view(self.cp, -1)
 
     def publish(self, x: torch.Tensor) -> torch.Tensor:
+        """Make ``x`` readable by the group; returns the handle to pass to ``pull_blocks``."""
+        if self.emulate:
+            buf = x.detach().reshape(-1).clone()
+            self._copies = {id(buf): self._gather(buf)}
+            return buf
         buf = self.stage[self._turn]
         self._turn ^= 1
         buf[: x.numel()].copy_(x.reshape(-1))
         self.comm.barrier()
         return buf
+
+    def return_slots(self, like: torch.Tensor) -> torch.Tensor:
+        """``[cp, slot]`` buffer of the gradient return: slot s is read by the rank ``s`` places below."""
+        if self.emulate:
+            rows, kvw = self._slot
+            self.gstage = torch.zeros(self.cp * max(rows, like.shape[0]) * kvw, dtype=like.dtype, device=like.device)
+        return self.gstage.view(self.cp, -1)
+
+    def returns_written(self) -> None:
+        if self.emulate:
+            self._copies[id(self.gstage)] = self._gather(self.gstage)
+        else:
+            self.comm.barrier()
+
+    def returns_read(self) -> None:
+        """The return slots may be rewritten from here on."""
+        if self.emulate:
+            self._copies.pop(id(self.gstage), None)
+        else:
+            self.comm.barrier()
 
     def pull_cols(self, buf: torch.Tensor, src_rank: int, out: torch.Tensor, src_off_elems: int, dst_off_elems: int,
                   src_pitch: int, dst_pitch: int, rows: int, cols: int) -> None:
@@ -90,7 +174,14 @@ class RingContext:
 
     def pull_blocks(self, buf: torch.Tensor, out: torch.Tensor, blocks) -> None:
         """``blocks``: (source rank, source offset, destination offset, source pitch, destination pitch, rows,
-        columns), all in bf16 elements; launched 64 blocks at a time."""
+        columns), all in elements; launched 64 blocks at a time."""
+        if self.emulate:
+            flat = out.view(-1)
+            for r, so, do, sp_, dp_, rows, cols in blocks:
+                src = self._copies[id(buf)][r]
+                flat.as_strided((rows, cols), (dp_, 1), flat.storage_offset() + do).copy_(
+                    src.as_strided((rows, cols), (sp_, 1), src.storage_offset() + so))
+            return
         L = _lib.get_lib()
         peers = self.comm.peers_of(buf).ptr_array
         for at in range(0, len(blocks), 64):
@@ -99,6 +190,30 @@ class RingContext:
             for i, (r, so, do, sp_, dp_, rows, cols) in enumerate(part):
                 arr[i] = _PullBlock(so * 2, do * 2, sp_ * 2, dp_ * 2, rows, cols * 2, r, 0)
             _lib.check(L.sb_block_pull(peers, self.cp, arr, len(part), _lib.ptr(out), _lib.stream()), "sb_block_pull")
+
+
+class _Side:
+    """The copy stream of the ring: a CUDA side stream on GPUs, the caller's own order on CPU."""
+
+    def __init__(self, device):
+        self.stream = torch.cuda.Stream() if device.type == "cuda" else None
+
+    def run(self, fn):
+        """Run ``fn()`` (returns a tensor) on the side stream; returns (tensor, event or None)."""
+        if self.stream is None:
+            return fn(), None
+        self.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self.stream):
+            blk = fn()
+            ev = torch.cuda.Event()
+            ev.record(self.stream)
+        blk.record_stream(torch.cuda.current_stream())
+        return blk, ev
+
+    @staticmethod
+    def wait(ev) -> None:
+        if ev is not None:
+            _Side.wait(ev)
 
 
 def _merge(out, lse, o_s, lse_s):
@@ -118,14 +233,14 @@ class _RingAttn(torch.autograd.Function):
         Tl, W = qkv.shape
         qw, kvw = hq * d, 2 * hkv * d
         buf = rc.publish(qkv)
-        side = torch.cuda.Stream()
+        side = _Side(qkv.device)
         out, lse = _block_fwd(qkv, info, hq, hkv, d, True, scale)        # own chunk: causal
         nxt = None
         for s in range(1, me + 1):
             if nxt is None:
                 nxt = _fetch(rc, buf, qkv, me - s, Tl, W, qw, kvw, side)
             blk, ev = nxt
-            torch.cuda.current_stream().wait_event(ev)
+            _Side.wait(ev)
             nxt = _fetch(rc, buf, qkv, me - s - 1, Tl, W, qw, kvw, side) if s < me else None
             o_s, lse_s = _block_fwd(blk, info, hq, hkv, d, False, scale)  # earlier chunk: every key is visible
             out, lse = _merge(out, lse, o_s, lse_s)
@@ -142,27 +257,27 @@ class _RingAttn(torch.autograd.Function):
         qw, kvw = hq * d, 2 * hkv * d
         dout = dout.contiguous()
         buf = rc.publish(qkv)
-        side = torch.cuda.Stream()
+        side = _Side(qkv.device)
         g = _block_bwd(qkv, out, lse, dout, info, hq, hkv, d, True, scale)
         dq = g[:, :qw].float()
         dkv = g[:, qw:].float()
-        gs = rc.gstage.view(n, -1)
+        gs = rc.return_slots(qkv)
         nxt = None
         for s in range(1, me + 1):
             if nxt is None:
                 nxt = _fetch(rc, buf, qkv, me - s, Tl, W, qw, kvw, side)
             blk, ev = nxt
-            torch.cuda.current_stream().wait_event(ev)
+            _Side.wait(ev)
             nxt = _fetch(rc, buf, qkv, me - s - 1, Tl, W, qw, kvw, side) if s < me else None
             g = _block_bwd(blk, out, lse, dout, info, hq, hkv, d, False, scale)
             dq += g[:, :qw].float()
             gs[s, : Tl * kvw].copy_(g[:, qw:].reshape(-1))               # slot s: gradient for the chunk of rank me - s
-        rc.comm.barrier()
+        rc.returns_written()
         tmp = torch.empty(Tl, kvw, dtype=qkv.dtype, device=qkv.device)
         for s in range(1, n - me):                                       # rank me + s used my chunk at its step s
             rc.pull_cols(rc.gstage, me + s, tmp, s * gs.shape[1], 0, kvw, kvw, Tl, kvw)
             dkv += tmp.float()
-        rc.comm.barrier()                                                # the return slots may be rewritten
+        rc.returns_read()
         return torch.cat([dq, dkv], dim=1).to(qkv.dtype), None, None, None, None, None, None
 
 
@@ -187,10 +302,9 @@ def _fetch_zigzag(rc: RingContext, buf, qkv, src: int, lo, hi, spans, W: int, qw
     """Block against rank ``src`` in the zig-zag layout (on a side stream).  ``src`` below this rank: the local
     queries, with ``src``'s low-chunk K/V under both halves.  ``src`` above: the high queries under both halves, with
     ``src``'s K/V as they lie."""
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
+    def fill():
         if src < rc.rank:
-            blk = qkv.clone()
+            blk = qkv.detach().clone()
             blocks = []
             for at, c in spans:
                 if c:
@@ -201,12 +315,10 @@ def _fetch_zigzag(rc: RingContext, buf, qkv, src: int, lo, hi, spans, W: int, qw
             dup = torch.empty(qkv.shape[0], dtype=torch.int64, device=qkv.device)
             dup[lo] = hi
             dup[hi] = hi
-            blk = qkv.index_select(0, dup)
+            blk = qkv.detach().index_select(0, dup)
             rc.pull_blocks(buf, blk, [(src, qw, qw, W, W, qkv.shape[0], kvw)])
-        ev = torch.cuda.Event()
-        ev.record(side)
-    blk.record_stream(torch.cuda.current_stream())
-    return blk, ev
+        return blk
+    return side.run(fill)
 
 
 class _RingAttnZigzag(torch.autograd.Function):
@@ -217,13 +329,13 @@ class _RingAttnZigzag(torch.autograd.Function):
         qw, kvw = hq * d, 2 * hkv * d
         lo, hi, info_h, spans = _halves(info, qkv.device)
         buf = rc.publish(qkv)
-        side = torch.cuda.Stream()
+        side = _Side(qkv.device)
         out, lse = _block_fwd(qkv, info, hq, hkv, d, True, scale)        # own pair of chunks: one causal block
         order = [(me - s) % n for s in range(1, n)]
         nxt = _fetch_zigzag(rc, buf, qkv, order[0], lo, hi, spans, W, qw, kvw, side) if order else None
         for k, j in enumerate(order):
             blk, ev = nxt
-            torch.cuda.current_stream().wait_event(ev)
+            _Side.wait(ev)
             nxt = (_fetch_zigzag(rc, buf, qkv, order[k + 1], lo, hi, spans, W, qw, kvw, side)
                    if k + 1 < len(order) else None)
             o_s, lse_s = _block_fwd(blk, info_h, hq, hkv, d, False, scale)
@@ -248,11 +360,11 @@ class _RingAttnZigzag(torch.autograd.Function):
         lo, hi, info_h, spans = _halves(info, qkv.device)
         dout = dout.contiguous()
         buf = rc.publish(qkv)
-        side = torch.cuda.Stream()
+        side = _Side(qkv.device)
         g = _block_bwd(qkv, out, lse, dout, info, hq, hkv, d, True, scale)
         dq = g[:, :qw].float()
         dkv = g[:, qw:].float()
-        gs = rc.gstage.view(n, -1)
+        gs = rc.return_slots(qkv)
         dup = torch.empty(Tl, dtype=torch.int64, device=qkv.device)
         dup[lo] = hi
         dup[hi] = hi
@@ -261,7 +373,7 @@ class _RingAttnZigzag(torch.autograd.Function):
         nxt = _fetch_zigzag(rc, buf, qkv, order[0], lo, hi, spans, W, qw, kvw, side) if order else None
         for k, j in enumerate(order):
             blk, ev = nxt
-            torch.cuda.current_stream().wait_event(ev)
+            _Side.wait(ev)
             nxt = (_fetch_zigzag(rc, buf, qkv, order[k + 1], lo, hi, spans, W, qw, kvw, side)
                    if k + 1 < len(order) else None)
             if j < me:
@@ -279,25 +391,22 @@ class _RingAttnZigzag(torch.autograd.Function):
                 dq.index_add_(0, hi, g[lo, :qw].float() + g[hi, :qw].float())
                 ret = g[:, qw:]
             gs[k + 1, : Tl * kvw].copy_(ret.reshape(-1))                 # slot s: gradient for the chunks of rank me - s
-        rc.comm.barrier()
+        rc.returns_written()
         tmp = torch.empty(Tl, kvw, dtype=qkv.dtype, device=qkv.device)
         for s in range(1, n):                                            # rank me + s used my chunks at its step s
             rc.pull_cols(rc.gstage, (me + s) % n, tmp, s * gs.shape[1], 0, kvw, kvw, Tl, kvw)
             dkv += tmp.float()
-        rc.comm.barrier()                                                # the return slots may be rewritten
+        rc.returns_read()
         return torch.cat([dq, dkv], dim=1).to(qkv.dtype), None, None, None, None, None, None
 
 
 def _fetch(rc: RingContext, buf, qkv, src: int, Tl: int, W: int, qw: int, kvw: int, side):
     """Block for chunk ``src``: local queries next to the K/V columns pulled from rank ``src`` (on a side stream)."""
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        blk = qkv.clone()
+    def fill():
+        blk = qkv.detach().clone()
         rc.pull_cols(buf, src, blk, qw, qw, W, W, Tl, kvw)
-        ev = torch.cuda.Event()
-        ev.record(side)
-    blk.record_stream(torch.cuda.current_stream())
-    return blk, ev
+        return blk
+    return side.run(fill)
 
 
 def ring_attention(qkv: torch.Tensor, rc: Optional[RingContext], info: SeqInfo, n_heads: int, n_kv_heads: int,
@@ -308,8 +417,8 @@ def ring_attention(qkv: torch.Tensor, rc: Optional[RingContext], info: SeqInfo, 
     from ..ops.attention import attention_packed
     if rc is None or rc.cp == 1:
         return attention_packed(qkv, info, n_heads, n_kv_heads, head_dim, causal=True, scale=scale)
-    if qkv.is_cuda and rc.stage is not None:
-        assert head_dim in (64, 128), "ring attention uses the 64/128-wide attention kernels"
+    if rc.stage is not None:
+        assert not qkv.is_cuda or head_dim in (64, 128), "ring attention uses the 64/128-wide attention kernels"
         fn = _RingAttnZigzag if rc.zigzag else _RingAttn
         return fn.apply(qkv.contiguous(), rc, info, n_heads, n_kv_heads, head_dim, scale)
     return _ring_attention_gathered(qkv, rc, info, n_heads, n_kv_heads, head_dim, scale)

@@ -176,15 +176,17 @@ def main():
     ref_out = attention_packed(ref_in, SeqInfo(lens6, device=dev), hq6, hkv6, d6, causal=True)
     ref_out.backward(go6)
     t6 = 0.06 if cuda else 1e-4
-    for zz in (False, True):
+    # on CPU ranks: once through the gathered statement, once through the block algorithms of the GPU path over an
+    # emulated symmetric memory
+    for zz, emu in ((False, False), (True, False)) + (() if cuda else ((False, True), (True, True))):
         rows, _, info6 = split_for_context_parallel(lens6, world, rank, device=dev, zigzag=zz)
         rc = RingContext(dist.group.WORLD, comm, max_rows=rows.numel(), qkv_width=W6, kv_width=2 * hkv6 * d6,
-                         zigzag=zz)
+                         zigzag=zz, emulate=emu)
         loc = full6[rows].clone().requires_grad_()
         out6 = ring_attention(loc, rc, info6, hq6, hkv6, d6)
         out6.backward(go6[rows])
-        assert (out6.float() - ref_out[rows].float()).abs().max().item() < t6, f"ring attention output (zigzag={zz})"
-        assert (loc.grad.float() - ref_in.grad[rows].float()).abs().max().item() < 4 * t6, f"ring attention gradient (zigzag={zz})"
+        assert (out6.float() - ref_out[rows].float()).abs().max().item() < t6, f"ring attention output (zigzag={zz}, emulated={emu})"
+        assert (loc.grad.float() - ref_in.grad[rows].float()).abs().max().item() < 4 * t6, f"ring attention gradient (zigzag={zz}, emulated={emu})"
         if cuda:
             torch.cuda.synchronize()
             lib.check_status()
