@@ -322,18 +322,26 @@ class _ModelWorkerBase:
             if self.world % n:
                 raise ValueError(f"pipeline_model_parallel_size={n} must divide the group size {self.world}")
             ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
-            mine = dp = fwd = bwd = None
+            virtual = int(getattr(cfgs.megatron, "virtual_pipeline_model_parallel_size", None) or 1)
+            if virtual > 1 and self.model_config.num_layers < n * virtual:
+                raise ValueError(f"virtual_pipeline_model_parallel_size={virtual} x pipeline_model_parallel_size={n} "
+                                 f"exceeds the {self.model_config.num_layers} layers of the model")
+            mine = dp = fwd = bwd = wfwd = wbwd = None
             for b in range(self.world // n):
                 g = dist.new_group(ranks[b * n:(b + 1) * n])
                 gf = dist.new_group(ranks[b * n:(b + 1) * n])      # activations
                 gb = dist.new_group(ranks[b * n:(b + 1) * n])      # activation gradients
+                # interleaved schedule: the link that closes the ring (last stage -> first stage) in both directions
+                wf = dist.new_group(ranks[b * n:(b + 1) * n]) if virtual > 1 else None
+                wb = dist.new_group(ranks[b * n:(b + 1) * n]) if virtual > 1 else None
                 if b == self.rank // n:
-                    mine, fwd, bwd = g, gf, gb
+                    mine, fwd, bwd, wfwd, wbwd = g, gf, gb, wf, wb
             for s_ in range(n):
                 g = dist.new_group(ranks[s_::n])
                 if s_ == self.rank % n:
                     dp = g
-            self._pp_ctx = PipelineContext(mine, self.model_config.num_layers, fwd, bwd)
+            self._pp_ctx = PipelineContext(mine, self.model_config.num_layers, fwd, bwd, virtual=virtual,
+                                           wrap_fwd_group=wfwd, wrap_bwd_group=wbwd)
             self._pp_dp_group = dp
         model.attach_pipeline_parallel(self._pp_ctx)
         pc = self._pp_ctx
@@ -445,16 +453,28 @@ class _ModelWorkerBase:
             # pipeline parallel: this rank runs its stage; the last stage scores, every stage receives the values,
             # and a non-last stage ties them to the handle whose backward pulls the activation gradient
             from ..parallel import pipeline as P
-            hidden, handle = model.forward_hidden_pp(pk.input_ids, positions, pk.info)
+            stage_local = getattr(self, "_pp_stage_local", False)
+            if stage_local:
+                # pipelined training: the schedule names the local model chunk of this call
+                chunk = int(getattr(self, "_pp_chunk", 0))
+                hidden, handle = model.forward_hidden_pp(pk.input_ids, positions, pk.info, chunk=chunk)
+                scores_here = pc.chunk_is_last(chunk)
+            else:
+                # one micro-batch at a time: the stage runs its chunks in turn (the ring of stages once per chunk)
+                assert pc.virtual == 1 or not torch.is_grad_enabled(), \
+                    "virtual pipeline stages with gradients run under the interleaved schedule only"
+                for chunk in range(pc.virtual):
+                    hidden, handle = model.forward_hidden_pp(pk.input_ids, positions, pk.info, chunk=chunk)
+                scores_here = pc.is_last
             N = pk.sel.shape[0]
             lp_l = ent_l = None
-            if pc.is_last:
+            if scores_here:
                 lp_l, ent_l = lm_head_logprob_entropy(hidden.index_select(0, pk.sel), model.head_weight, pk.labels,
                                                       temperature, with_entropy)
-            if getattr(self, "_pp_stage_local", False):
-                # pipelined training (1F1B): nothing is broadcast per micro-batch; the last stage holds the values,
-                # the other stages only the handle whose backward receives the activation gradient
-                if pc.is_last:
+            if stage_local:
+                # nothing is broadcast per micro-batch; the last chunk of the model holds the values, every other
+                # chunk only the handle whose backward receives the activation gradient
+                if scores_here:
                     return pk.scatter(lp_l), (pk.scatter(ent_l) if ent_l is not None else None)
                 return handle, None
             vals = P.broadcast_from_last(pc, [lp_l] + ([ent_l] if with_entropy else []), [(N,)] * (2 if with_entropy
@@ -940,14 +960,16 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 mini_batch = data.select_idxs(mini_idx)
                 mbs = _micro_batches(mini_batch, self.ppo_micro_batch_size, a.use_dynamic_bsz,
                                      a.ppo_max_token_len_per_gpu, self.group)
-                def micro_forward(idx, mb):
-                    """Forward pass and loss of one micro-batch -> (tensor to call ``backward`` on, metrics)."""
+                def micro_forward(idx, mb, chunk=0):
+                    """Forward pass and loss of one micro-batch (of one local model chunk under the interleaved
+                    pipeline schedule) -> (tensor to call ``backward`` on, metrics)."""
                     scale = (len(idx) / len(mini_idx)) if a.use_dynamic_bsz else 1.0 / len(mbs)
                     mask = mb["response_mask"].to(self.device).float()
                     adv = mb["advantages"].to(self.device).float()
+                    self._pp_chunk = chunk
                     logp, ent = self._forward_logprob(self.model, mb, temperature, need_entropy)
-                    if pipelined and not pc.is_last:
-                        return logp, {}             # the stage's handle: its backward receives dL/dh from the next stage
+                    if pipelined and not pc.chunk_is_last(chunk):
+                        return logp, {}             # the chunk's handle: its backward receives dL/dh from the next stage
                     old = logp.detach() if on_policy else mb["old_log_probs"].to(self.device).float()
                     ref = mb["ref_log_prob"].to(self.device).float() if (a.use_kl_loss and "ref_log_prob" in mb) \
                         else None
@@ -997,20 +1019,22 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                         metrics.setdefault(k, []).append(v)
 
                 if pipelined:
-                    # 1F1B: warm-up forwards, then one forward and one backward in turn, then the remaining backwards
-                    from ..parallel.pipeline import schedule_1f1b
+                    # 1F1B (interleaved over the stage's model chunks when virtual stages are configured): warm-up
+                    # forwards, then one forward and one backward in turn, then the remaining backwards
+                    from ..parallel.pipeline import schedule_interleaved
                     inflight = {}
                     self._pp_stage_local = True
                     try:
-                        for op, i in schedule_1f1b(pc.stage, pc.pp, len(mbs)):
+                        for op, i, c in schedule_interleaved(pc.stage, pc.pp, len(mbs), pc.virtual):
                             if op == "F":
-                                inflight[i] = micro_forward(*mbs[i])
+                                inflight[i, c] = micro_forward(*mbs[i], chunk=c)
                             else:
-                                target, rec = inflight.pop(i)
+                                target, rec = inflight.pop((i, c))
                                 target.backward()
                                 record(rec)
                     finally:
                         self._pp_stage_local = False
+                        self._pp_chunk = 0
                     pc.drain()
                 else:
                     for idx, mb in mbs:

@@ -55,9 +55,6 @@ def _warn_unsupported_keys(config) -> None:
         if int(mg.tensor_model_parallel_size or 1) > 1 and not getattr(mg, "_native_tp", True):
             _warn_once("actor.megatron.tensor_model_parallel_size", "training tensor parallelism is mapped to the "
                        "native column/row-parallel layers")
-        if mg.virtual_pipeline_model_parallel_size:
-            _warn_once("actor.megatron.virtual_pipeline_model_parallel_size", "interleaved pipeline stages are not "
-                       "implemented: every rank holds one contiguous stage")
 
 
 def validate_config(config, world_size: Optional[int] = None) -> None:

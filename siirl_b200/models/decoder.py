@@ -408,28 +408,31 @@ class DecoderLM(nn.Module):
             return lp, (ent if with_entropy else None)
         return lm_head_logprob_entropy(hidden, self.head_weight, labels, temperature, with_entropy)
 
-    def forward_hidden_pp(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo):
-        """Pipeline-parallel forward of this rank's stage.  Returns ``(hidden, None)`` on the last stage (final-norm
-        hidden states) and ``(None, handle)`` elsewhere, where ``handle`` is a 0-d tensor whose backward receives
-        the gradient of the activations sent downstream (``None`` without gradient history)."""
+    def forward_hidden_pp(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo, chunk: int = 0):
+        """Pipeline-parallel forward of this rank's stage (of its local model chunk ``chunk`` under the interleaved
+        schedule).  Returns ``(hidden, None)`` for the last chunk of the model (final-norm hidden states) and
+        ``(None, handle)`` elsewhere, where ``handle`` is a 0-d tensor whose backward receives the gradient of the
+        activations sent downstream (``None`` without gradient history)."""
         from ..parallel import pipeline as P
         pc = self.pp
         pmax = int(positions.max().item()) + 1 if positions.numel() else 1
         rope = self.rope_tables(input_ids.device, pmax)
         T, H = input_ids.shape[0], self.cfg.hidden_size
-        if pc.is_first:
+        first, last = pc.chunk_is_first(chunk), pc.chunk_is_last(chunk)
+        lo, hi = pc.chunk_layers(chunk)
+        if first:
             h = self.embed(input_ids)
         else:
             h = P.recv_from_prev(pc, (T, H), self.embed_tokens.dtype, input_ids.device, torch.is_grad_enabled())
         delta = None
-        for layer in self.layers[pc.layer_lo:pc.layer_hi]:
+        for layer in self.layers[lo:hi]:
             if self.gradient_checkpointing and torch.is_grad_enabled():
                 if delta is not None:
                     h, delta = h + delta, None
                 h, delta = ckpt.checkpoint(layer, h, None, positions, info, rope, use_reentrant=False)
             else:
                 h, delta = layer(h, delta, positions, info, rope)
-        if pc.is_last:
+        if last:
             if delta is None:       # a stage without layers
                 return ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)[0], None
             return ops.rmsnorm(delta, self.norm, self.cfg.rms_norm_eps, residual=h)[0], None

@@ -213,7 +213,7 @@ class _Side:
     @staticmethod
     def wait(ev) -> None:
         if ev is not None:
-            _Side.wait(ev)
+            torch.cuda.current_stream().wait_event(ev)
 
 
 def _merge(out, lse, o_s, lse_s):

@@ -174,11 +174,14 @@ def test_context_parallel_ring_attention_two_ranks(tmp_path):
         assert r["actor/grad_norm"] > 0 and abs(r["actor/ppo_kl"]) < 1e-3       # on-policy: same log-probs twice
 
 
-def test_pipeline_parallel_two_stages(tmp_path):
+@pytest.mark.parametrize("virtual", [1, 2])
+def test_pipeline_parallel_two_stages(tmp_path, virtual):
     """Two ranks as one two-stage pipeline (layers split, activations and their gradients sent point to point, trained
-    stage weights re-broadcast after the update so the rollout engines keep whole, identical replicas)."""
+    stage weights re-broadcast after the update so the rollout engines keep whole, identical replicas); with
+    ``virtual=2`` every stage holds two model chunks and training runs the interleaved schedule."""
     out = _run(["actor_rollout_ref.actor.megatron.pipeline_model_parallel_size=2",
-                "actor_rollout_ref.model.override_config={tie_word_embeddings: False}",
+                f"actor_rollout_ref.actor.megatron.virtual_pipeline_model_parallel_size={virtual}",
+                "actor_rollout_ref.model.override_config={tie_word_embeddings: False, num_layers: 4}",
                 "actor_rollout_ref.rollout.max_num_seqs=32", f"trainer.default_local_dir={tmp_path / 'c'}",
                 "trainer.total_training_steps=2", "trainer.save_freq=-1"], tmp_path / "log")
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]

@@ -3,6 +3,8 @@ import os
 import subprocess
 import sys
 
+import pytest
+
 
 def test_tensor_parallel_two_cpu_ranks():
     here = os.path.dirname(os.path.abspath(__file__))
@@ -38,11 +40,15 @@ def test_tensor_parallel_training_matches_the_whole_model():
     assert "TP_TRAIN_OK" in out.stdout
 
 
-def test_pipeline_1f1b_schedule_matches_the_whole_model():
-    """Three stages, five micro-batches under 1F1B with asynchronous sends: per-stage gradients equal the whole model's."""
+@pytest.mark.parametrize("virtual,extra", [(1, 0), (2, 0), (2, 2)])
+def test_pipeline_1f1b_schedule_matches_the_whole_model(virtual, extra):
+    """Three stages under 1F1B with asynchronous sends (five micro-batches), and under the interleaved schedule with
+    two model chunks per stage (six micro-batches; eight, i.e. a group that does not fill the pipeline): per-stage
+    gradients equal the whole model's."""
     from siirl_b200.execution.scheduler.launch import find_free_port
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr",
            "127.0.0.1", "--master-port", str(find_free_port()), os.path.join(os.path.dirname(__file__), "pp_worker.py")]
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, OMP_NUM_THREADS="1"))
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=600,
+                         env=dict(os.environ, OMP_NUM_THREADS="1", PP_VIRTUAL=str(virtual), PP_EXTRA=str(extra)))
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "PP_1F1B_OK" in out.stdout
