@@ -220,6 +220,11 @@ class DecoderConfig:
     def from_hf_config(cls, cfg: Dict[str, Any]) -> "DecoderConfig":
         text = cfg.get("text_config") or cfg.get("llm_config") or cfg
         mt = cfg.get("model_type", "qwen2")
+        if mt in ("llama4", "llama4_text"):
+            # same answer as the reference's converter, which lists Llama4ForConditionalGeneration and raises
+            # (siirl/models/mcore/config_converter.py:282-284): chunked attention, rope-free layers and the
+            # interleaved dense / MoE stack of that family are not built
+            raise NotImplementedError("Llama4ForConditionalGeneration is not supported")
         if mt in ("internvl", "internvl_chat"):
             return cls._from_internvl_config(cfg)
         if mt in ("openvla", "prismatic"):

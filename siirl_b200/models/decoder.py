@@ -316,11 +316,12 @@ class DecoderLM(nn.Module):
         return self.lm_head if self.lm_head is not None else self.embed_tokens
 
     def embed(self, input_ids: torch.Tensor, pixel_values=None, image_grid_thw=None, image_mask=None,
-              zero_mask=None) -> torch.Tensor:
+              zero_mask=None, extra_embeds=None) -> torch.Tensor:
         """Token embeddings with vision features written over the image placeholders.  ``image_mask`` names the
         placeholder positions explicitly; the default (ids equal to ``image_token_id``) is only safe when generated
         tokens cannot collide with the placeholder id.  Rows of ``zero_mask`` enter the model as zero vectors (the
-        action placeholders of OpenVLA-OFT's parallel decoding)."""
+        action placeholders of OpenVLA-OFT's parallel decoding).  ``extra_embeds = (rows, values [len(rows), H])``
+        writes given vectors over further rows (OpenVLA-OFT's proprioception pseudo-token)."""
         h = ops.embedding(input_ids, self.embed_tokens)
         if zero_mask is not None:
             h = h * (~zero_mask).to(h.dtype)[:, None]
@@ -329,11 +330,14 @@ class DecoderLM(nn.Module):
             mask = image_mask if image_mask is not None else input_ids == self.cfg.image_token_id
             idx = mask.nonzero(as_tuple=True)[0]
             h = h.index_copy(0, idx, img[: idx.numel()])
+        if extra_embeds is not None:
+            rows, values = extra_embeds
+            h = h.index_copy(0, rows.to(h.device), values.to(h.device, h.dtype))
         return h
 
     # ---- training / scoring path ---------------------------------------------------------------
     def forward_hidden(self, input_ids: torch.Tensor, positions: torch.Tensor, info: SeqInfo, pixel_values=None,
-                       image_grid_thw=None, image_mask=None, zero_mask=None) -> torch.Tensor:
+                       image_grid_thw=None, image_mask=None, zero_mask=None, extra_embeds=None) -> torch.Tensor:
         """Final-norm hidden states ``[T, H]`` of a packed batch.  With sequence parallelism attached
         (``self.sp``), the packed stream is padded to a multiple of the group size and this rank computes rows
         ``[rank * T/sp, (rank + 1) * T/sp)``: the result holds those rows only (see ``sp_slice``)."""
@@ -370,7 +374,7 @@ class DecoderLM(nn.Module):
                 input_ids = torch.cat([input_ids, input_ids.new_zeros(pad)])
                 positions = torch.cat([positions, positions.new_zeros(*positions.shape[:-1], pad)], dim=-1)
                 info = SeqInfo(list(info.seqlens) + [pad], device=input_ids.device)
-        h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask, zero_mask)
+        h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask, zero_mask, extra_embeds)
         if sp_rows is not None:
             from ..parallel.megatron_tp import take_rows_for_sp
             h = take_rows_for_sp(h, tp)

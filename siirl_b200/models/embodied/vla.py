@@ -217,3 +217,57 @@ def oft_parallel_decode(model, proc: "VLAProcessor", prompts: Sequence[Sequence[
         pick = logp.argmax(-1)
     lp = logp.gather(1, pick[:, None])[:, 0]
     return (pick + lo).reshape(len(prompts), A), lp.reshape(len(prompts), A)
+
+
+# ---- OpenVLA-OFT continuous actions --------------------------------------------------------------------------------
+def oft_action_hidden(model, proc: "VLAProcessor", prompts: Sequence[Sequence[int]], images_u8: torch.Tensor,
+                      n_action_tokens: int, proprio: Optional[torch.Tensor] = None, proprio_projector=None
+                      ) -> torch.Tensor:
+    """Final hidden states ``[N, n_action_tokens, H]`` of the zeroed action placeholder rows of one control step
+    (one forward pass; gradients flow when enabled).  With ``proprio [N, proprio_dim]`` and a projector, one
+    pseudo-token carrying the projected robot state is placed directly behind the image patch rows (the reference
+    appends it to the projected patch embeddings, modeling_prismatic.py:449-459)."""
+    from ...ops.attention import SeqInfo
+    dev = images_u8.device
+    A = n_action_tokens
+    pad = model.cfg.pad_token_id or 0
+    with_state = proprio is not None and proprio_projector is not None
+    cut = proc.image_offset + proc.tokens_per_image          # first row behind the patches
+    rows = []
+    for p in prompts:
+        p = list(p)
+        rows.append(p[:cut] + ([pad] if with_state else []) + p[cut:] + [pad] * A)
+    lens = [len(r) for r in rows]
+    ids = torch.tensor([t for r in rows for t in r], dtype=torch.int64, device=dev)
+    info = SeqInfo(lens, device=dev)
+    first = torch.tensor(info.cu_seqlens_cpu[:-1], device=dev)
+    ends = torch.tensor(info.cu_seqlens_cpu[1:], device=dev)
+    act_rows = (ends[:, None] - A + torch.arange(A, device=dev)[None, :]).flatten()
+    zero_mask = torch.zeros(ids.shape[0], dtype=torch.bool, device=dev)
+    zero_mask[act_rows] = True
+    extra = None
+    if with_state:
+        extra = (first + cut, proprio_projector(proprio.reshape(len(prompts), -1)))
+    pv, grid = proc.patchify(images_u8, model.embed_tokens.dtype)
+    if proc.prismatic is None:
+        positions = torch.cat([proc.rope_layout(len(p), A + int(with_state))[0] for p in prompts], 1).to(dev)
+    else:
+        positions = info.positions
+    hidden = model.forward_hidden(ids, positions, info, pixel_values=pv, image_grid_thw=grid,
+                                  image_mask=proc.image_mask(first, ids.shape[0]), zero_mask=zero_mask,
+                                  extra_embeds=extra)
+    return hidden.index_select(0, act_rows).reshape(len(prompts), A, -1)
+
+
+def oft_continuous_actions(model, proc: "VLAProcessor", prompts: Sequence[Sequence[int]], images_u8: torch.Tensor,
+                           action_head, chunk_len: int, proprio: Optional[torch.Tensor] = None, proprio_projector=None,
+                           norm_stats: Optional[dict] = None, norm_type: str = "bounds_q99") -> torch.Tensor:
+    """L1-regression prediction of one control step: ``[N, chunk_len, action_dim]`` actions, un-normalised with the
+    dataset statistics when ``norm_stats`` is given (the reference: ``_regression_or_discrete_prediction`` with an
+    ``action_head``, then ``_unnormalize_actions``; modeling_prismatic.py:1485-1550, 1378-1397)."""
+    from .action_heads import unnormalize_actions
+    with torch.no_grad():
+        h = oft_action_hidden(model, proc, prompts, images_u8, chunk_len * action_head.action_dim, proprio,
+                              proprio_projector)
+        a = action_head.predict_action(h).float()
+    return unnormalize_actions(a, norm_stats, norm_type) if norm_stats is not None else a.cpu()

@@ -155,3 +155,59 @@ def test_embodied_pipeline_two_steps(tmp_path, policy):
     assert any(r["actor/grad_norm"] > 0 for r in m)          # some group mixes successes and failures
     assert m[0]["embodied_sampling/initial_trajectories"] == 16.0
     assert m[0]["response_length/max"] <= 8 * 7
+
+
+@pytest.mark.parametrize("preset", ["tiny-openvla", "tiny-vl"])
+def test_oft_l1_regression_head_and_proprio(preset):
+    """OpenVLA-OFT's continuous path: the proprioception pseudo-token changes the prediction, the head learns a fixed
+    target through an L1 loss (gradients reach head, projector and decoder), and un-normalisation follows the dataset
+    statistics."""
+    from siirl_b200.models.config import get_config
+    from siirl_b200.models.decoder import build_model
+    from siirl_b200.models.embodied.action_heads import (L1RegressionActionHead, ProprioProjector, normalize_proprio,
+                                                        unnormalize_actions)
+    from siirl_b200.models.embodied.vla import VLAProcessor, oft_action_hidden, oft_continuous_actions
+
+    class Tok:
+        def encode(self, s):
+            return [5 + (ord(c) % 50) for c in s][:12]
+
+    cfg = get_config(preset)
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=2)
+    proc = VLAProcessor(cfg, Tok(), image_size=56)
+    N, chunk, adim, pdim = 2, 3, 7, 8
+    head = L1RegressionActionHead(cfg.hidden_size, adim, head_hidden=64, blocks=2, dtype=torch.float32, seed=1)
+    proj = ProprioProjector(pdim, cfg.hidden_size, dtype=torch.float32, seed=2)
+    g = torch.Generator().manual_seed(0)
+    images = torch.randint(0, 255, (N, proc.image_size, proc.image_size, 3), generator=g, dtype=torch.uint8)
+    prompts = [proc.prompt_ids("pick up the block"), proc.prompt_ids("open the drawer")]
+    stats = {"q01": [-2.0] * adim, "q99": [2.0] * adim, "mask": [True] * (adim - 1) + [False]}
+    state = normalize_proprio(torch.randn(N, pdim, generator=g) * 3, {"q01": [-3.0] * pdim, "q99": [3.0] * pdim})
+    assert state.abs().max() <= 1.0
+    a0 = oft_continuous_actions(model, proc, prompts, images, head, chunk)
+    a1 = oft_continuous_actions(model, proc, prompts, images, head, chunk, proprio=state, proprio_projector=proj)
+    assert a0.shape == (N, chunk, adim) and (a0 - a1).abs().max() > 1e-6          # the state token is seen
+    un = oft_continuous_actions(model, proc, prompts, images, head, chunk, norm_stats=stats)
+    assert torch.allclose(un[..., :-1], 0.5 * (a0[..., :-1] + 1) * 4.0 - 2.0, atol=1e-5)
+    assert torch.allclose(un[..., -1], a0[..., -1])                              # masked dimension stays as predicted
+    assert torch.allclose(unnormalize_actions(torch.zeros(adim), stats), torch.zeros(adim), atol=1e-6)
+    # a few L1 steps on a fixed target
+    target = torch.rand(N, chunk, adim, generator=g) * 2 - 1
+    params = list(head.parameters()) + list(proj.parameters()) + [p for p in model.parameters() if p.requires_grad]
+    opt = torch.optim.Adam(params, lr=5e-4)
+    losses = []
+    for _ in range(20):
+        opt.zero_grad()
+        for p in model.parameters():
+            if getattr(p, "main_grad", None) is not None:
+                p.main_grad.zero_()
+        h = oft_action_hidden(model, proc, prompts, images, chunk * adim, state, proj)
+        loss = head.l1_loss(h, target)
+        loss.backward()
+        for p in model.parameters():                      # the decoder's custom ops accumulate into ``main_grad``
+            if p.grad is None and getattr(p, "main_grad", None) is not None:
+                p.grad = p.main_grad.to(p.dtype).clone()
+        losses.append(float(loss.detach()))
+        opt.step()
+    assert proj.fc1_weight.grad is not None and proj.fc1_weight.grad.abs().sum() > 0
+    assert min(losses[-3:]) < 0.7 * losses[0], losses
