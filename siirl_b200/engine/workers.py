@@ -726,8 +726,6 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
             return TPDecoder(self.model, ctx, presharded=True)
         if self.world % tp:
             raise ValueError(f"rollout.tensor_model_parallel_size={tp} does not divide the group size {self.world}")
-        if self.model_config.lora_rank > 0:
-            raise ValueError("tensor-parallel rollout with LoRA adapters is not supported: use tensor_model_parallel_size=1")
         ranks = dist.get_process_group_ranks(self.group) if self.group is not None else list(range(self.world))
         mine = None
         for b in range(self.world // tp):

@@ -84,6 +84,36 @@ class TPDecoder:
         gu_rows = torch.cat([torch.arange(r * I, (r + 1) * I),
                              torch.arange(c.intermediate_size + r * I, c.intermediate_size + (r + 1) * I)]).to(rows.device)
         first = not self.layers
+        if c.lora_rank > 0:
+            # low-rank adapters are folded into the engine's slices: W + (alpha / r) B A, cut the same way (rows of
+            # B for the column-parallel layers, columns of A for the row-parallel ones).  The trainer keeps base
+            # weights and adapters apart; the engine decodes with one GEMM per projection.
+            sc = c.lora_alpha / c.lora_rank
+            o_cols = torch.arange(r * hq * D, (r + 1) * hq * D, device=rows.device)
+            d_cols = torch.arange(r * I, (r + 1) * I, device=rows.device)
+
+            def fold(layer, name, row_idx=None, col_idx=None):
+                W = getattr(layer, f"{name}_weight").detach()
+                A = getattr(layer, f"{name}_lora_A").detach().float()
+                B = getattr(layer, f"{name}_lora_B").detach().float()
+                if row_idx is not None:
+                    W, B = W.index_select(0, row_idx), B.index_select(0, row_idx)
+                if col_idx is not None:
+                    W, A = W.index_select(1, col_idx), A.index_select(1, col_idx)
+                if not getattr(layer, "lora_enabled", True):
+                    return W.contiguous()
+                return (W.float() + sc * (B @ A)).to(W.dtype)
+
+            self.layers = []
+            for layer in self.full.layers:
+                t = _TPLayer()
+                t.qkv_w = fold(layer, "qkv_proj", row_idx=rows)
+                t.qkv_b = layer.qkv_proj_bias.detach().index_select(0, rows) if layer.qkv_proj_bias is not None else None
+                t.gate_up_w = fold(layer, "gate_up_proj", row_idx=gu_rows)
+                t.o_w = fold(layer, "o_proj", col_idx=o_cols)
+                t.down_w = fold(layer, "down_proj", col_idx=d_cols)
+                self.layers.append(t)
+            return
         for li, layer in enumerate(self.full.layers):
             if first:
                 t = _TPLayer()

@@ -147,11 +147,14 @@ def test_ulysses_and_tensor_parallel_rollout_two_ranks(tmp_path):
         assert r["perf/total_num_tokens"] > 8 * 4 * 17
 
 
-def test_lora_adapters_train_against_the_frozen_base(tmp_path):
+@pytest.mark.parametrize("rollout_tp", [1, 2])
+def test_lora_adapters_train_against_the_frozen_base(tmp_path, rollout_tp):
     """LoRA: only the adapters are in the optimizer store; the reference policy is the same model with the
-    adapters switched off, so the KL term starts at zero and becomes positive once the adapters move."""
+    adapters switched off, so the KL term starts at zero and becomes positive once the adapters move.  With
+    ``rollout_tp=2`` two ranks decode as one tensor-parallel engine whose weight slices have the adapters folded in."""
     out = _run(["actor_rollout_ref.model.lora_rank=8", "actor_rollout_ref.model.lora_alpha=16",
-                "actor_rollout_ref.actor.optim.lr=1e-3", "trainer.n_gpus_per_node=1",
+                "actor_rollout_ref.actor.optim.lr=1e-3", f"trainer.n_gpus_per_node={rollout_tp}",
+                f"actor_rollout_ref.rollout.tensor_model_parallel_size={rollout_tp}",
                 f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=3",
                 "trainer.save_freq=-1"], tmp_path / "log")
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]

@@ -76,6 +76,25 @@ def main():
     if cuda:
         torch.cuda.synchronize()
         lib.check_status()
+    # 2b. low-rank adapters are folded into the engine's slices: same greedy tokens as the single-rank engine, which
+    #     applies base weight and adapter separately
+    cfg_l = get_config("tiny-gpu" if cuda else "tiny", {"lora_rank": 8, "lora_alpha": 16.0})
+    model_l = build_model(cfg_l, dtype=dtype, device=dev, seed=6)
+    with torch.no_grad():
+        for n_, p_ in model_l.named_parameters():
+            if "_lora_B" in n_:
+                p_.copy_((0.05 * torch.randn(p_.shape, generator=g)).to(dev, dtype))
+    ref_l = RolloutEngine(model_l, max_num_seqs=8, max_model_len=128, num_blocks=32)
+    want_l = [o.token_ids for o in ref_l.generate(prompts, sp)]
+    ref_l.sleep()
+    model_l.set_lora_enabled(False)
+    base_l = [o.token_ids for o in RolloutEngine(model_l, max_num_seqs=8, max_model_len=128, num_blocks=32).generate(prompts, sp)]
+    model_l.set_lora_enabled(True)
+    assert base_l != want_l, "the adapters must change the greedy tokens for this check to mean anything"
+    tp_l = TPDecoder(model_l, ctx2)
+    got_l = [o.token_ids for o in RolloutEngine(tp_l, max_num_seqs=8, max_model_len=128, num_blocks=32).generate(prompts, sp)]
+    same_l = sum(int(a == b) for x, y in zip(want_l, got_l) for a, b in zip(x, y))
+    assert same_l >= (total if not cuda else int(0.8 * total)), (same_l, total)
     # 3. all-gather -> GEMM: weight rows sharded over the ranks, gathered inside the GEMM launch
     from siirl_b200.parallel.ag_gemm import AgLinear
     N2, K2 = 1536 * world, 640
