@@ -659,13 +659,20 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
             if tp > 1:
                 self.tp_model = self._build_tp_model(tp, r.max_num_batched_tokens)
             if str(r.name).lower() == "hf" or self.model_config.is_mla:
-                # cache-free generation through the training forward: the reference's ``rollout.name=hf``, and the
-                # families whose attention has no paged-cache kernel (multi-head latent attention)
-                from .rollout.recompute_engine import RecomputeEngine
+                # ``rollout.name=hf``: cache-free generation through the training forward (the reference's HF
+                # rollout).  Multi-head latent attention has no paged-cache kernel: it decodes against a cache of
+                # the compressed latents instead.
                 if tp > 1:
-                    raise ValueError("the cache-free rollout runs on whole weights: set "
+                    raise ValueError("this rollout engine runs on whole weights: set "
                                      "rollout.tensor_model_parallel_size=1")
-                self.engine = RecomputeEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024), max_model_len=max_len)
+                if str(r.name).lower() != "hf" and getattr(self, "ep_ctx", None) is None:
+                    from .rollout.latent_engine import LatentCacheEngine
+                    self.engine = LatentCacheEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024),
+                                                    max_model_len=max_len)
+                else:
+                    from .rollout.recompute_engine import RecomputeEngine
+                    self.engine = RecomputeEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024),
+                                                  max_model_len=max_len)
             else:
                 self.engine = self._paged_engine(r, max_len)
             if r.free_cache_engine and self._is_actor and getattr(self, "store", None) is not None \

@@ -134,13 +134,13 @@ class DecoderLayer(nn.Module):
             positions = positions[0]            # three equal rows from a multimodal processor of a 1-D rope family
         return ops.rope(qkv, cfg.num_heads + cfg.num_kv_heads, cfg.head_dim, positions, cos, sin, cfg.mrope_section)
 
-    def mla_qkv(self, x: torch.Tensor, positions: torch.Tensor, rope):
-        """Per-head queries / keys ``[T, nh, nope + rope]`` (rotary part rotated) and values ``[T, nh, v]`` of
-        multi-head latent attention (reference path: HF DeepseekV3Attention as patched by
-        siirl/models/transformers/kimi_vl.py:120-225)."""
+    def mla_latent(self, x: torch.Tensor, positions: torch.Tensor, rope):
+        """Multi-head latent attention before the key / value expansion: per-head queries ``[T, nh, nope + rope]``
+        (rotary part rotated), the normalised latent ``[T, kv_lora_rank]`` and the rotated shared rotary key
+        ``[T, rope]``.  The latent and the rotary key are all a cache has to keep per token."""
         cfg = self.cfg
         T = x.shape[0]
-        nh, dn, dr, dv = cfg.num_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        nh, dn, dr = cfg.num_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim
         if cfg.q_lora_rank > 0:
             qa, _ = ops.rmsnorm(ops.linear(x, self.q_a_proj_weight), self.q_a_layernorm, cfg.rms_norm_eps)
             q = ops.linear(qa, self.q_b_proj_weight)
@@ -150,7 +150,6 @@ class DecoderLayer(nn.Module):
         ckv = ops.linear(x, self.kv_a_proj_weight)
         c, k_pe = ckv[:, : cfg.kv_lora_rank], ckv[:, cfg.kv_lora_rank:]
         cn, _ = ops.rmsnorm(c.contiguous(), self.kv_a_layernorm, cfg.rms_norm_eps)
-        kv = ops.linear(cn, self.kv_b_proj_weight).reshape(T, nh, dn + dv)
         pe = torch.cat([q[:, :, dn:], k_pe.reshape(T, 1, dr)], 1)               # [T, nh + 1, dr]
         if cfg.rope_interleave:
             # checkpoints store rotary pairs interleaved (2i, 2i+1); the rotate-half kernel wants (i, i + dr/2)
@@ -160,19 +159,34 @@ class DecoderLayer(nn.Module):
         cos, sin = rope
         pe = ops.rope(pe.reshape(T, (nh + 1) * dr).contiguous(), nh + 1, dr, positions, cos, sin, None)
         pe = pe.reshape(T, nh + 1, dr)
-        qf = torch.cat([q[:, :, :dn], pe[:, :nh]], -1)
-        kf = torch.cat([kv[:, :, :dn], pe[:, nh:].expand(T, nh, dr)], -1)
+        return torch.cat([q[:, :, :dn], pe[:, :nh]], -1), cn, pe[:, nh]
+
+    def mla_qkv(self, x: torch.Tensor, positions: torch.Tensor, rope):
+        """Per-head queries / keys ``[T, nh, nope + rope]`` (rotary part rotated) and values ``[T, nh, v]`` of
+        multi-head latent attention (reference path: HF DeepseekV3Attention as patched by
+        siirl/models/transformers/kimi_vl.py:120-225)."""
+        cfg = self.cfg
+        T = x.shape[0]
+        nh, dn, dr, dv = cfg.num_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
+        qf, cn, k_pe = self.mla_latent(x, positions, rope)
+        kv = ops.linear(cn, self.kv_b_proj_weight).reshape(T, nh, dn + dv)
+        kf = torch.cat([kv[:, :, :dn], k_pe[:, None, :].expand(T, nh, dr)], -1)
         return qf, kf, kv[:, :, dn:]
 
-    def mla_attention(self, x: torch.Tensor, positions: torch.Tensor, info: SeqInfo, rope, causal=True) -> torch.Tensor:
-        from ..ops.attention import attention_wide_heads
+    def mla_scale(self) -> float:
         cfg = self.cfg
-        q, k, v = self.mla_qkv(x, positions, rope)
         scale = 1.0 / math.sqrt(cfg.qk_nope_head_dim + cfg.qk_rope_head_dim)
         rs = cfg.rope_scaling or {}
         if rs.get("rope_type", rs.get("type")) == "yarn" and rs.get("mscale_all_dim"):
             from ..ops.reference import yarn_mscale
             scale *= yarn_mscale(float(rs.get("factor", 1.0)), float(rs["mscale_all_dim"])) ** 2
+        return scale
+
+    def mla_attention(self, x: torch.Tensor, positions: torch.Tensor, info: SeqInfo, rope, causal=True) -> torch.Tensor:
+        from ..ops.attention import attention_wide_heads
+        cfg = self.cfg
+        q, k, v = self.mla_qkv(x, positions, rope)
+        scale = self.mla_scale()
         sp = getattr(self, "sp", None)
         if sp is not None and sp.sp > 1:
             # Ulysses (the switch the reference patches into Kimi-VL's attention,

@@ -303,3 +303,36 @@ def test_cache_free_engine_equals_the_paged_engine_and_serves_latent_attention()
     mla = build_model(get_config("tiny-deepseek-v3"), dtype=torch.float32, device="cpu", seed=2)
     outs = RecomputeEngine(mla).generate(prompts[:2], SamplingParams(n=1, temperature=1.0, max_new_tokens=5, seed=3))
     assert [len(o.token_ids) for o in outs] == [5, 5] and all(o.finish_reason == "length" for o in outs)
+
+
+@pytest.mark.parametrize("preset", ["tiny-deepseek-v3", "tiny-kimi-vl"])
+def test_latent_cache_engine_equals_the_cache_free_engine(preset):
+    """Multi-head latent attention: decoding against the cache of compressed latents (key / value expansion folded
+    into query and output) gives the tokens and log-probs of recomputing the whole prefix with expanded keys and
+    values; two waves, samples of a prompt sharing its prefill, EOS stops."""
+    from siirl_b200.engine.rollout.latent_engine import LatentCacheEngine
+    from siirl_b200.engine.rollout.recompute_engine import RecomputeEngine
+    cfg = get_config(preset)
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=4)
+    prompts = [[5, 6, 7, 8, 9, 10], [9, 10, 11], [100, 200, 300, 400, 500], [7, 7, 7, 7]]
+    for sp in (SamplingParams(n=2, temperature=0.0, max_new_tokens=9, eos_token_id=2),
+               SamplingParams(n=1, temperature=0.0, max_new_tokens=4, ignore_eos=True)):
+        want = RecomputeEngine(model, max_num_seqs=16).generate(prompts, sp)
+        eng = LatentCacheEngine(model, max_num_seqs=4, max_model_len=32)      # 4 slots: two prompts x two samples per wave
+        got = eng.generate(prompts, sp)
+        assert eng.cache is None                                              # woke up for the call, asleep again
+        assert [(o.prompt_index, o.sample_index, o.token_ids, o.finish_reason) for o in got] == \
+            [(o.prompt_index, o.sample_index, o.token_ids, o.finish_reason) for o in want]
+        assert max(abs(x - y) for o, p in zip(got, want) for x, y in zip(o.logprobs, p.logprobs)) < 1e-4
+    if cfg.moonvit is not None:                     # image features enter through the prompt's placeholder rows
+        v = cfg.moonvit
+        gen = torch.Generator().manual_seed(0)
+        n_img = 4 * 6 // v.merge ** 2
+        mm = [{"pixel_values": torch.randn(24, 3 * v.patch_size ** 2, generator=gen),
+               "image_grid_thw": torch.tensor([[1, 4, 6]])}, None]
+        vp = [[5, 6] + [cfg.image_token_id] * n_img + [8, 9], [9, 10, 11]]
+        sp = SamplingParams(n=2, temperature=0.0, max_new_tokens=6, ignore_eos=True)
+        want = RecomputeEngine(model).generate(vp, sp, mm_inputs=mm)
+        got = LatentCacheEngine(model, max_num_seqs=4, max_model_len=32).generate(vp, sp, mm_inputs=mm)
+        assert [o.token_ids for o in got] == [o.token_ids for o in want]
+    assert eng.stats["decode_steps"] > 0 and eng.cache_bytes() == cfg.num_layers * 4 * 32 * (cfg.kv_lora_rank + cfg.qk_rope_head_dim) * 2
