@@ -360,35 +360,51 @@ class DecoderLM(nn.Module):
         if getattr(self, "pp", None) is not None and self.pp.pp > 1:
             raise RuntimeError("pipeline-parallel models are driven through forward_hidden_pp")
         sp = getattr(self, "sp", None)
+        cp = getattr(self, "cp", None)
+        tp = getattr(self, "tp", None)
+        split = (sp is not None and sp.sp > 1) or (cp is not None and cp.cp > 1) or \
+            (tp is not None and tp.sequence_parallel)
+        h_pre = None
+        if split and (pixel_values is not None or zero_mask is not None or extra_embeds is not None):
+            # rows are about to be divided over a group: image features (and other per-row overrides) are written
+            # over the whole stream first, on every rank, and divided like the token rows (the reference's
+            # vision-language Ulysses patch runs the tower on every rank too,
+            # siirl/models/transformers/qwen2_vl.py ulysses_flash_attn_forward)
+            h_pre = self.embed(input_ids, pixel_values, image_grid_thw, image_mask, zero_mask, extra_embeds)
+
+        def pad_rows(t, n):
+            return torch.cat([t, t.new_zeros(n, *t.shape[1:])]) if t is not None and n else t
+
         if sp is not None and sp.sp > 1:
-            assert pixel_values is None, "sequence parallelism with image inputs is not wired"
             lo, hi, pad = self.sp_slice(input_ids.shape[0])
             if pad:
                 input_ids = torch.cat([input_ids, input_ids.new_zeros(pad)])
                 positions = torch.cat([positions, positions.new_zeros(*positions.shape[:-1], pad)], dim=-1)
                 info = SeqInfo(list(info.seqlens) + [pad], device=input_ids.device)
+                h_pre = pad_rows(h_pre, pad)
             input_ids, positions = input_ids[lo:hi], positions[..., lo:hi].contiguous()
-        cp = getattr(self, "cp", None)
+            h_pre = h_pre[lo:hi] if h_pre is not None else None
         if cp is not None and cp.cp > 1:
-            assert pixel_values is None and positions.dim() == 1, "context parallelism: text-only, 1-D positions"
             rows, _, info = self.cp_rows(info)
             keep = rows >= 0
             safe = rows.clamp(min=0)
             input_ids = torch.where(keep, input_ids[safe], torch.zeros_like(safe))
-            positions = torch.where(keep, positions[safe], torch.zeros_like(positions[safe]))
-        tp = getattr(self, "tp", None)
+            positions = torch.where(keep, positions[..., safe], torch.zeros_like(positions[..., safe])).contiguous()
+            if h_pre is not None:
+                h_pre = h_pre.index_select(0, safe) * keep.to(h_pre.dtype)[:, None]
         sp_rows = None
         if tp is not None and tp.sequence_parallel:
             # Megatron sequence parallelism: between the tensor-parallel blocks every rank keeps 1 / tp of the token
             # rows.  The packed stream is padded (one dummy sequence) to a multiple of the group size.
-            assert pixel_values is None, "sequence-parallel training with image inputs is not wired"
             sp_rows = input_ids.shape[0]
             pad = (-sp_rows) % tp.size
             if pad:
                 input_ids = torch.cat([input_ids, input_ids.new_zeros(pad)])
                 positions = torch.cat([positions, positions.new_zeros(*positions.shape[:-1], pad)], dim=-1)
                 info = SeqInfo(list(info.seqlens) + [pad], device=input_ids.device)
-        h = self.embed(input_ids, pixel_values, image_grid_thw, image_mask, zero_mask, extra_embeds)
+                h_pre = pad_rows(h_pre, pad)
+        h = h_pre if h_pre is not None else self.embed(input_ids, pixel_values, image_grid_thw, image_mask, zero_mask,
+                                                       extra_embeds)
         if sp_rows is not None:
             from ..parallel.megatron_tp import take_rows_for_sp
             h = take_rows_for_sp(h, tp)

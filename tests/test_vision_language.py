@@ -61,7 +61,10 @@ def test_vl_rollout_and_training_logprobs_agree():
     assert (out["old_log_probs"] - out["rollout_log_probs"])[m].abs().max().item() < 1e-4
 
 
-def test_vl_grpo_pipeline(tmp_path):
+@pytest.mark.parametrize("ulysses", [1, 2])
+def test_vl_grpo_pipeline(tmp_path, ulysses):
+    """GRPO on the vision-language decoder; with ``ulysses=2`` two ranks share every packed stream (image features
+    are written over the whole stream on both ranks before the rows are divided)."""
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, OMP_NUM_THREADS="2", SIIRL_LOG_DIR=str(tmp_path / "log"))
     env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
@@ -70,7 +73,8 @@ def test_vl_grpo_pipeline(tmp_path):
             "data.max_response_length=16", "data.train_batch_size=4", "actor_rollout_ref.model.arch_preset=tiny-vl",
             "actor_rollout_ref.rollout.n=4", "actor_rollout_ref.rollout.max_num_seqs=16",
             "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8",
-            "actor_rollout_ref.actor.use_kl_loss=True", "trainer.n_gpus_per_node=1", "trainer.device=cpu",
+            "actor_rollout_ref.actor.use_kl_loss=True", f"trainer.n_gpus_per_node={ulysses}", "trainer.device=cpu",
+            f"actor_rollout_ref.actor.ulysses_sequence_parallel_size={ulysses}",
             "trainer.val_before_train=False", "trainer.logger=['jsonl']", "trainer.total_training_steps=2",
             "trainer.save_freq=-1"]
     out = subprocess.run([sys.executable, "-m", "siirl_b200.main_dag", *args], env=env, cwd=root, capture_output=True,
@@ -79,6 +83,7 @@ def test_vl_grpo_pipeline(tmp_path):
     with open(tmp_path / "log" / "metrics.jsonl") as f:
         m = [json.loads(line) for line in f]
     assert [r["step"] for r in m] == [1, 2] and any(r["actor/grad_norm"] > 0 for r in m)
+    assert abs(m[0]["actor/ppo_kl"]) < 1e-3          # training forward = scoring forward on the first, on-policy step
 
 
 def test_video_inputs_sampling_patching_and_forward():

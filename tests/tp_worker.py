@@ -238,6 +238,49 @@ def main():
     if cuda:
         torch.cuda.synchronize()
         lib.check_status()
+    # 7b. a vision-language decoder under sequence and under context parallelism: image features are written over the
+    #     whole stream before the rows are divided; local rows and summed gradients (tower included) equal one rank's
+    if not cuda:
+        from siirl_b200.models.vision import mrope_positions
+        cfgv = get_config("tiny-vl")
+        grid = torch.tensor([[1, 8, 12]])
+        n_img = 8 * 12 // cfgv.vision.spatial_merge_size ** 2
+        seq_a = torch.cat([torch.randint(3, 900, (5,), generator=g), torch.full((n_img,), cfgv.image_token_id),
+                           torch.randint(3, 900, (11,), generator=g)])
+        seq_b = torch.randint(3, 900, (21,), generator=g)
+        idsv = torch.cat([seq_a, seq_b]).to(dev)
+        lensv = [seq_a.numel(), seq_b.numel()]
+        infov = SeqInfo(lensv, device=dev)
+        posv = torch.cat([mrope_positions(seq_a, cfgv.image_token_id, grid, cfgv.vision.spatial_merge_size),
+                          torch.arange(seq_b.numel()).expand(3, -1)], 1).to(dev)
+        coefv = torch.randn(sum(lensv), cfgv.hidden_size, generator=g).to(dev, dtype)
+        for mode in ("ulysses", "ring"):
+            mv_ref = build_model(cfgv, dtype=dtype, device=dev, seed=11)
+            mv = build_model(cfgv, dtype=dtype, device=dev, seed=11)
+            pix = torch.randn(8 * 12, mv.vision.patch_dim, generator=g).to(dev, dtype)
+            wv = (cfgv.num_heads + 2 * cfgv.num_kv_heads) * cfgv.head_dim
+            if mode == "ulysses":
+                mv.attach_sequence_parallel(UlyssesSP(dist.group.WORLD, comm, max_elems=512 * wv))
+            else:
+                mv.attach_context_parallel(RingContext(dist.group.WORLD, comm, max_rows=256, qkv_width=wv,
+                                                       kv_width=2 * cfgv.num_kv_heads * cfgv.head_dim, zigzag=True))
+            hv_ref = mv_ref.forward_hidden(idsv, posv, infov, pixel_values=pix, image_grid_thw=grid)
+            (hv_ref.float() * coefv.float()).sum().backward()
+            hv = mv.forward_hidden(idsv, posv, infov, pixel_values=pix, image_grid_thw=grid)
+            loc = mv.local_row_index(infov, sum(lensv))
+            keep = loc >= 0
+            assert (hv[keep].float() - hv_ref[loc[keep]].float()).abs().max().item() < 1e-4, f"VL hidden rows ({mode})"
+            (hv[keep].float() * coefv[loc[keep]].float()).sum().backward()
+            seen_tower = False
+            for (n1, p1), (_, p2) in zip(mv_ref.named_parameters(), mv.named_parameters()):
+                g1 = p1.grad if p1.grad is not None else getattr(p1, "main_grad", None)
+                if g1 is None:
+                    continue
+                g2 = (p2.grad if p2.grad is not None else p2.main_grad).float().clone()
+                dist.all_reduce(g2)
+                assert (g1.float() - g2).abs().max().item() < 1e-3, f"VL grad {n1} ({mode})"
+                seen_tower = seen_tower or n1.startswith("vision.")
+            assert seen_tower
     # 8. pipeline parallelism: stages exchange activations / gradients point to point; every stage's parameter
     #    gradients equal the single-rank ones, and weight sync after an update restores identical replicas
     from siirl_b200.parallel.pipeline import PipelineContext, sync_stage_weights
