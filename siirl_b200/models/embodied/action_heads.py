@@ -1,5 +1,5 @@
-"""Continuous-action modules of OpenVLA-OFT: L1-regression action head, proprioception projector, and the
-(un)normalisation of actions / proprioceptive state with dataset statistics.
+"""Continuous-action modules of OpenVLA-OFT: L1-regression action head, diffusion action head, proprioception projector,
+and the (un)normalisation of actions / proprioceptive state with dataset statistics.
 
 The reference's OpenVLA-OFT model takes these as outside modules (``action_head`` / ``proprio_projector`` arguments of
 siirl/models/embodied/openvla_oft/modeling_prismatic.py:1485-1550 ``_regression_or_discrete_prediction``, :449-459
@@ -12,6 +12,9 @@ the package's GEMM (``ops.linear``) that read the decoder's final hidden states 
   trained with an L1 loss.
 * ``ProprioProjector``: ``Linear -> GELU -> Linear`` from the robot state to one pseudo-token of the language model's
   width, placed directly behind the image patch rows.
+* ``DiffusionActionHead`` + ``DDIMSchedule``: the action rows carry the projected noisy action chunk, a timestep
+  pseudo-token sits behind the patches, a residual MLP predicts the noise; sampling is deterministic DDIM
+  (modeling_prismatic.py:1399-1483 ``_run_diffusion_prediction``).
 """
 from __future__ import annotations
 
@@ -105,6 +108,83 @@ class ProprioProjector(nn.Module):
             x = F.pad(x, (0, self.in_dim - x.shape[-1]))
         x = F.gelu(ops.linear(x, self.fc1_weight, self.fc1_bias).float()).to(x.dtype)
         return ops.linear(x, self.fc2_weight, self.fc2_bias)
+
+
+# ---- diffusion head ------------------------------------------------------------------------------------------------
+class DDIMSchedule:
+    """Discrete-time diffusion with the squared-cosine noise schedule and deterministic (eta = 0) DDIM sampling of an
+    epsilon-predicting model: ``x_t = sqrt(abar_t) x_0 + sqrt(1 - abar_t) eps``."""
+
+    def __init__(self, num_train_steps: int = 100):
+        import math
+        self.num_train_steps = num_train_steps
+        f = lambda u: math.cos((u + 0.008) / 1.008 * math.pi / 2) ** 2        # noqa: E731
+        betas = [min(1.0 - f((i + 1) / num_train_steps) / f(i / num_train_steps), 0.999) for i in range(num_train_steps)]
+        self.alphas_cumprod = torch.cumprod(1.0 - torch.tensor(betas, dtype=torch.float64), 0).float()
+
+    def add_noise(self, x0: torch.Tensor, noise: torch.Tensor, t: torch.Tensor) -> torch.Tensor:
+        ab = self.alphas_cumprod[t].reshape(-1, *([1] * (x0.dim() - 1)))
+        return ab.sqrt() * x0 + (1.0 - ab).sqrt() * noise
+
+    def inference_steps(self, n: int):
+        """``(t, previous t)`` pairs from the noisiest step down; the previous step of the last one is -1 (clean)."""
+        n = max(1, min(n, self.num_train_steps))
+        ts = [int(round(i * (self.num_train_steps - 1) / max(n - 1, 1))) for i in range(n)][::-1] if n > 1 \
+            else [self.num_train_steps - 1]
+        return list(zip(ts, ts[1:] + [-1]))
+
+    def step(self, eps: torch.Tensor, t: int, t_prev: int, x: torch.Tensor) -> torch.Tensor:
+        ab = self.alphas_cumprod[t]
+        ab_prev = self.alphas_cumprod[t_prev] if t_prev >= 0 else torch.tensor(1.0)
+        x0 = ((x - (1.0 - ab).sqrt() * eps) / ab.sqrt()).clamp(-1.0, 1.0)        # actions live in [-1, 1]
+        eps = (x - ab.sqrt() * x0) / (1.0 - ab).sqrt()
+        return ab_prev.sqrt() * x0 + (1.0 - ab_prev).sqrt() * eps
+
+
+class DiffusionActionHead(nn.Module):
+    """OpenVLA-OFT's diffusion head: the decoder sees the noisy action chunk (every scalar projected to one row of the
+    language model's width) plus a timestep pseudo-token, and a residual MLP predicts the noise from the hidden
+    states of the action rows; sampling runs ``num_inference_steps`` DDIM steps, one decoder forward each."""
+
+    def __init__(self, hidden_size: int, action_dim: int = 7, head_hidden: Optional[int] = None, blocks: int = 2,
+                 num_train_steps: int = 100, num_inference_steps: int = 50, dtype=torch.bfloat16, device="cpu",
+                 seed: int = 0):
+        super().__init__()
+        gen = torch.Generator().manual_seed(seed)
+        self.action_dim, self.hidden_size = action_dim, hidden_size
+        self.num_inference_steps = num_inference_steps
+        self.schedule = DDIMSchedule(num_train_steps)
+        self.mlp = _ResidualMLP(hidden_size * action_dim, head_hidden or hidden_size, action_dim, blocks, dtype, device,
+                                gen)
+        # noisy scalar -> row of the model's width: Linear(1, H) is an outer product, kept as a vector pair
+        self.act_in_weight = nn.Parameter((torch.randn(hidden_size, generator=gen) * 0.5).to(device=device, dtype=dtype))
+        self.act_in_bias = nn.Parameter(torch.zeros(hidden_size, dtype=dtype, device=device))
+        self.act_out_weight, self.act_out_bias = _linear_param(hidden_size, hidden_size, dtype, device, gen)
+        self.time_weight, self.time_bias = _linear_param(hidden_size, hidden_size, dtype, device, gen)
+
+    def project_noisy_actions(self, x: torch.Tensor) -> torch.Tensor:
+        """``[N, chunk, action_dim]`` noisy actions -> ``[N, chunk * action_dim, H]`` input rows."""
+        w = self.act_in_weight
+        v = x.reshape(x.shape[0], -1, 1).to(w.device, torch.float32)
+        h = F.gelu(v * w.float() + self.act_in_bias.float()).to(w.dtype)
+        return ops.linear(h.reshape(-1, self.hidden_size), self.act_out_weight, self.act_out_bias).reshape(
+            x.shape[0], -1, self.hidden_size)
+
+    def time_embedding(self, t: torch.Tensor) -> torch.Tensor:
+        """Sinusoidal features of the timestep -> ``[N, H]`` pseudo-token."""
+        import math
+        half = self.hidden_size // 2
+        freq = torch.exp(-math.log(10000.0) * torch.arange(half, dtype=torch.float32) / max(half - 1, 1))
+        ang = t.float().reshape(-1, 1) * freq[None, :]
+        emb = torch.cat([ang.sin(), ang.cos()], -1)
+        if emb.shape[-1] < self.hidden_size:
+            emb = F.pad(emb, (0, self.hidden_size - emb.shape[-1]))
+        emb = emb.to(self.time_weight.device, self.time_weight.dtype)
+        return ops.linear(emb, self.time_weight, self.time_bias)
+
+    def predict_noise(self, action_hidden: torch.Tensor) -> torch.Tensor:
+        N, rows, H = action_hidden.shape
+        return self.mlp(action_hidden.reshape(N, rows // self.action_dim, self.action_dim * H))
 
 
 # ---- dataset statistics -------------------------------------------------------------------------------------------

@@ -221,42 +221,60 @@ def oft_parallel_decode(model, proc: "VLAProcessor", prompts: Sequence[Sequence[
 
 # ---- OpenVLA-OFT continuous actions --------------------------------------------------------------------------------
 def oft_action_hidden(model, proc: "VLAProcessor", prompts: Sequence[Sequence[int]], images_u8: torch.Tensor,
-                      n_action_tokens: int, proprio: Optional[torch.Tensor] = None, proprio_projector=None
-                      ) -> torch.Tensor:
-    """Final hidden states ``[N, n_action_tokens, H]`` of the zeroed action placeholder rows of one control step
-    (one forward pass; gradients flow when enabled).  With ``proprio [N, proprio_dim]`` and a projector, one
-    pseudo-token carrying the projected robot state is placed directly behind the image patch rows (the reference
-    appends it to the projected patch embeddings, modeling_prismatic.py:449-459)."""
+                      n_action_tokens: int, proprio: Optional[torch.Tensor] = None, proprio_projector=None,
+                      pseudo_tokens: Optional[Sequence[torch.Tensor]] = None,
+                      action_embeds: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Final hidden states ``[N, n_action_tokens, H]`` of the action placeholder rows of one control step (one forward
+    pass; gradients flow when enabled).  The action rows enter as zero vectors, or as ``action_embeds [N, A, H]`` (the
+    projected noisy actions of the diffusion head).  Pseudo-tokens are placed directly behind the image patch rows,
+    in this order: the projected robot state (``proprio [N, proprio_dim]`` with a projector), then every
+    ``pseudo_tokens[i] [N, H]`` (the diffusion timestep embedding); the reference appends them to the projected patch
+    embeddings (modeling_prismatic.py:449-459, 1425-1434)."""
     from ...ops.attention import SeqInfo
     dev = images_u8.device
     A = n_action_tokens
+    N = len(prompts)
     pad = model.cfg.pad_token_id or 0
-    with_state = proprio is not None and proprio_projector is not None
+    extras = []
+    if proprio is not None and proprio_projector is not None:
+        extras.append(proprio_projector(proprio.reshape(N, -1)))
+    extras += list(pseudo_tokens or [])
+    E = len(extras)
     cut = proc.image_offset + proc.tokens_per_image          # first row behind the patches
     rows = []
     for p in prompts:
         p = list(p)
-        rows.append(p[:cut] + ([pad] if with_state else []) + p[cut:] + [pad] * A)
+        rows.append(p[:cut] + [pad] * E + p[cut:] + [pad] * A)
     lens = [len(r) for r in rows]
     ids = torch.tensor([t for r in rows for t in r], dtype=torch.int64, device=dev)
     info = SeqInfo(lens, device=dev)
     first = torch.tensor(info.cu_seqlens_cpu[:-1], device=dev)
     ends = torch.tensor(info.cu_seqlens_cpu[1:], device=dev)
     act_rows = (ends[:, None] - A + torch.arange(A, device=dev)[None, :]).flatten()
-    zero_mask = torch.zeros(ids.shape[0], dtype=torch.bool, device=dev)
-    zero_mask[act_rows] = True
+    zero_mask = None
+    over_rows, over_vals = [], []
+    if action_embeds is None:
+        zero_mask = torch.zeros(ids.shape[0], dtype=torch.bool, device=dev)
+        zero_mask[act_rows] = True
+    else:
+        over_rows.append(act_rows)
+        over_vals.append(action_embeds.reshape(N * A, -1))
+    for i, e in enumerate(extras):
+        over_rows.append(first + cut + i)
+        over_vals.append(e)
     extra = None
-    if with_state:
-        extra = (first + cut, proprio_projector(proprio.reshape(len(prompts), -1)))
+    if over_rows:
+        dt = model.embed_tokens.dtype
+        extra = (torch.cat(over_rows), torch.cat([v.to(dev, dt) for v in over_vals]))
     pv, grid = proc.patchify(images_u8, model.embed_tokens.dtype)
     if proc.prismatic is None:
-        positions = torch.cat([proc.rope_layout(len(p), A + int(with_state))[0] for p in prompts], 1).to(dev)
+        positions = torch.cat([proc.rope_layout(len(p), A + E)[0] for p in prompts], 1).to(dev)
     else:
         positions = info.positions
     hidden = model.forward_hidden(ids, positions, info, pixel_values=pv, image_grid_thw=grid,
                                   image_mask=proc.image_mask(first, ids.shape[0]), zero_mask=zero_mask,
                                   extra_embeds=extra)
-    return hidden.index_select(0, act_rows).reshape(len(prompts), A, -1)
+    return hidden.index_select(0, act_rows).reshape(N, A, -1)
 
 
 def oft_continuous_actions(model, proc: "VLAProcessor", prompts: Sequence[Sequence[int]], images_u8: torch.Tensor,
@@ -271,3 +289,23 @@ def oft_continuous_actions(model, proc: "VLAProcessor", prompts: Sequence[Sequen
                               proprio_projector)
         a = action_head.predict_action(h).float()
     return unnormalize_actions(a, norm_stats, norm_type) if norm_stats is not None else a.cpu()
+
+
+def oft_diffusion_actions(model, proc: "VLAProcessor", prompts: Sequence[Sequence[int]], images_u8: torch.Tensor,
+                          head, chunk_len: int, proprio: Optional[torch.Tensor] = None, proprio_projector=None,
+                          norm_stats: Optional[dict] = None, norm_type: str = "bounds_q99",
+                          generator: Optional[torch.Generator] = None) -> torch.Tensor:
+    """Diffusion prediction of one control step: start from Gaussian noise ``[N, chunk_len, action_dim]`` and run the
+    head's reverse steps; every step is one decoder forward whose action rows carry the projected noisy actions and
+    whose timestep embedding sits behind the patches (the reference: ``_run_diffusion_prediction``,
+    modeling_prismatic.py:1399-1483)."""
+    from .action_heads import unnormalize_actions
+    N, adim = len(prompts), head.action_dim
+    x = torch.randn(N, chunk_len, adim, generator=generator)
+    with torch.no_grad():
+        for t, t_prev in head.schedule.inference_steps(head.num_inference_steps):
+            h = oft_action_hidden(model, proc, prompts, images_u8, chunk_len * adim, proprio, proprio_projector,
+                                  pseudo_tokens=[head.time_embedding(torch.full((N,), t))],
+                                  action_embeds=head.project_noisy_actions(x))
+            x = head.schedule.step(head.predict_noise(h).float().cpu(), t, t_prev, x)
+    return unnormalize_actions(x, norm_stats, norm_type) if norm_stats is not None else x

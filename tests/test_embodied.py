@@ -211,3 +211,52 @@ def test_oft_l1_regression_head_and_proprio(preset):
         opt.step()
     assert proj.fc1_weight.grad is not None and proj.fc1_weight.grad.abs().sum() > 0
     assert min(losses[-3:]) < 0.7 * losses[0], losses
+
+
+def test_oft_diffusion_head_trains_and_samples():
+    """OpenVLA-OFT's diffusion head: the noise-prediction loss falls on a fixed target, sampling walks the DDIM steps
+    (one decoder forward each) and is reproducible from the generator."""
+    from siirl_b200.models.config import get_config
+    from siirl_b200.models.decoder import build_model
+    from siirl_b200.models.embodied.action_heads import DDIMSchedule, DiffusionActionHead
+    from siirl_b200.models.embodied.vla import VLAProcessor, oft_action_hidden, oft_diffusion_actions
+
+    class Tok:
+        def encode(self, s):
+            return [5 + (ord(c) % 50) for c in s][:12]
+
+    sch = DDIMSchedule(100)
+    assert sch.alphas_cumprod[0] > 0.99 and sch.alphas_cumprod[-1] < 1e-3 and (sch.alphas_cumprod.diff() < 0).all()
+    steps = sch.inference_steps(10)
+    assert steps[0][0] == 99 and steps[-1] == (0, -1) and len(steps) == 10
+    x0 = torch.rand(4, 3, 7) * 2 - 1
+    eps = torch.randn(4, 3, 7)
+    xt = sch.add_noise(x0, eps, torch.tensor([50, 50, 50, 50]))
+    assert torch.allclose(sch.step(eps, 50, -1, xt), x0, atol=1e-4)        # the true noise recovers the clean sample
+    cfg = get_config("tiny-openvla")
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=2)
+    proc = VLAProcessor(cfg, Tok(), image_size=56)
+    N, chunk, adim = 2, 2, 7
+    head = DiffusionActionHead(cfg.hidden_size, adim, head_hidden=64, num_inference_steps=4, dtype=torch.float32, seed=1)
+    g = torch.Generator().manual_seed(0)
+    images = torch.randint(0, 255, (N, proc.image_size, proc.image_size, 3), generator=g, dtype=torch.uint8)
+    prompts = [proc.prompt_ids("pick up the block"), proc.prompt_ids("open the drawer")]
+    a = oft_diffusion_actions(model, proc, prompts, images, head, chunk, generator=torch.Generator().manual_seed(5))
+    b = oft_diffusion_actions(model, proc, prompts, images, head, chunk, generator=torch.Generator().manual_seed(5))
+    assert a.shape == (N, chunk, adim) and torch.equal(a, b) and a.abs().max() <= 1.0 + 1e-5
+    target = torch.rand(N, chunk, adim, generator=g) * 2 - 1
+    opt = torch.optim.Adam(head.parameters(), lr=2e-3)
+    losses = []
+    for it in range(30):
+        opt.zero_grad()
+        t = torch.randint(0, 100, (N,), generator=g)
+        noise = torch.randn(N, chunk, adim, generator=g)
+        noisy = head.schedule.add_noise(target, noise, t)
+        h = oft_action_hidden(model, proc, prompts, images, chunk * adim, pseudo_tokens=[head.time_embedding(t)],
+                              action_embeds=head.project_noisy_actions(noisy))
+        loss = ((head.predict_noise(h) - noise) ** 2).mean()
+        loss.backward()
+        losses.append(float(loss.detach()))
+        opt.step()
+    assert head.act_in_weight.grad is not None and head.time_weight.grad.abs().sum() > 0
+    assert sum(losses[-5:]) / 5 < 0.85 * sum(losses[:5]) / 5, losses
