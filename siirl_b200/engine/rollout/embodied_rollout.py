@@ -33,8 +33,9 @@ class EmbodiedRollout:
         self.model_config = model_config
         self.actions = ActionTokenizer(model_config.action_vocab_size or model_config.vocab_size,
                                        n_bins=model_config.n_action_bins)
+        self.num_images = max(1, int(getattr(embodied_cfg, "num_images_in_input", 1) or 1))
         self.proc = VLAProcessor(model_config, tokenizer, image_size=getattr(embodied_cfg, "policy_image_size", 224),
-                                 center_crop=embodied_cfg.center_crop)
+                                 center_crop=embodied_cfg.center_crop, num_images=self.num_images)
         self.chunk = embodied_cfg.action_chunks_len
         self.atl = embodied_cfg.action_token_len
         self.seed = seed
@@ -52,6 +53,16 @@ class EmbodiedRollout:
                                         num_steps_wait=e.num_steps_wait, model_family=e.model_family,
                                         device=str(self.device), **dict(getattr(e, "env_kwargs", None) or {}))
         return self.env
+
+    def _frames(self, ob) -> torch.Tensor:
+        """Camera frames of one environment: ``[H, W, 3]``, or ``[num_images, H, W, 3]`` (third-person view first,
+        then the wrist camera) when the policy takes several images."""
+        if self.num_images == 1:
+            return torch.as_tensor(ob["image"])
+        views = [ob["image"]] + [ob.get(k) for k in ("wrist_image", "wrist_image_2")[: self.num_images - 1]]
+        if len(views) != self.num_images or any(v is None for v in views):
+            raise ValueError(f"num_images_in_input={self.num_images}: the environment returned {len(views)} camera views")
+        return torch.stack([torch.as_tensor(v) for v in views])
 
     def _full_model(self):
         m = self.engine.model
@@ -83,7 +94,7 @@ class EmbodiedRollout:
         dev = self.device
         out_resp = torch.zeros(B, L, A, dtype=torch.int64, device=dev)
         out_logp = torch.zeros(B, L, A, dtype=torch.float32, device=dev)
-        out_img = torch.zeros(B, L, S, S, 3, dtype=torch.uint8, device=dev)
+        out_img = torch.zeros(B, L, self.num_images * S, S, 3, dtype=torch.uint8, device=dev)   # cameras stacked by height
         finish = torch.zeros(B, dtype=torch.int64)
         complete = torch.zeros(B, dtype=torch.bool)
         prompt_ids: List[Optional[List[int]]] = [None] * B
@@ -101,7 +112,7 @@ class EmbodiedRollout:
                 act_rows = [k for k in range(len(rows)) if live[k]]
                 if not act_rows:
                     break
-                frames = torch.stack([torch.as_tensor(obs[k]["image"]) for k in act_rows]).to(dev)
+                frames = torch.stack([self._frames(obs[k]) for k in act_rows]).to(dev)
                 imgs = self.proc.resize(frames.contiguous())
                 p_list = [prompt_ids[rows[k]] for k in act_rows]
                 step_seed = (self.seed + 7919 * int(meta.get("global_steps", 0)) + 31 * l + g0) & 0x7FFFFFFF
@@ -149,7 +160,7 @@ class EmbodiedRollout:
         out["attention_mask"] = mask
         if self.video_embedder is not None:
             calls = (finish + self.chunk - 1) // self.chunk
-            out["vjepa_embedding"] = self.video_embedder(out_img, calls).to(dev)
+            out["vjepa_embedding"] = self.video_embedder(out_img[:, :, :S], calls).to(dev)     # third-person camera
         out.non_tensors["task_file_name"] = [f"task_{t}" for t in task_ids]
         out.meta["timing_generate_s"] = time.time() - t0
         out.meta["total_output_tokens"] = int(mask.sum())

@@ -758,7 +758,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
             from ..data_coordinator.dataloader.tokenizer import SyntheticTokenizer
             tok = SyntheticTokenizer(self.model_config.vocab_size)
         self.vla_processor = VLAProcessor(self.model_config, tok, image_size=emb.policy_image_size,
-                                          center_crop=emb.center_crop)
+                                          center_crop=emb.center_crop, num_images=emb.num_images_in_input)
         if self._is_rollout:
             from .rollout.embodied_rollout import EmbodiedRollout
             embedder = None

@@ -54,16 +54,23 @@ class LIBEROAdapter(BaseVLAEnvironment):
         self.env = SubprocVectorEnv(self._make_fns(task_ids))
         obs = self.env.reset()
         self.steps[:] = 0
-        return [{"image": o["agentview_image"][::-1, ::-1], "state": o.get("robot0_eef_pos"),
+        return [{"image": o["agentview_image"][::-1, ::-1], "wrist_image": self._wrist(o), "state": o.get("robot0_eef_pos"),
                  "task_description": self.benchmark.get_task(t).language, "step": 0, "done": False, "success": False}
                 for o, t in zip(obs, task_ids)]
 
     async def step(self, action) -> List[Dict[str, Any]]:
         obs, rew, done, info = self.env.step(np.asarray(action))
         self.steps += 1
-        return [{"image": o["agentview_image"][::-1, ::-1], "reward": float(r), "done": bool(d) or self.steps[i] >=
+        return [{"image": o["agentview_image"][::-1, ::-1], "wrist_image": self._wrist(o), "reward": float(r),
+                 "done": bool(d) or self.steps[i] >=
                  self.max_steps, "success": bool(d), "step": int(self.steps[i])}
                 for i, (o, r, d) in enumerate(zip(obs, rew, done))]
+
+    @staticmethod
+    def _wrist(o):
+        """Wrist-camera frame (rotated like the third-person view), ``None`` when the suite renders none."""
+        w = o.get("robot0_eye_in_hand_image")
+        return w[::-1, ::-1] if w is not None else None
 
     def close(self) -> None:
         if self.env is not None:

@@ -40,9 +40,24 @@ class SyntheticReachEnv(BaseVLAEnvironment):
         st = torch.from_numpy(self.state).to(self.device)
         return raster_synth_env(st, self.image_size, self.image_size)
 
+    def _wrist_view(self, img: torch.Tensor) -> torch.Tensor:
+        """A second camera: the quarter of the scene around the gripper, magnified to the full frame (what a wrist
+        camera sees: the surroundings of the end effector)."""
+        S = self.image_size
+        half = S // 4
+        cx = np.clip((self.state[:, 0] * S).astype(np.int64), half, S - half)
+        cy = np.clip((self.state[:, 1] * S).astype(np.int64), half, S - half)
+        dev = img.device
+        zoom = torch.arange(S, device=dev) // 2                                  # every source pixel twice
+        rows = torch.from_numpy(cy - half).to(dev)[:, None] + zoom[None, :]      # [N, S]
+        cols = torch.from_numpy(cx - half).to(dev)[:, None] + zoom[None, :]
+        n = torch.arange(self.num_envs, device=dev)[:, None, None]
+        return img[n, rows[:, :, None], cols[:, None, :]]
+
     def _obs(self) -> List[Dict[str, Any]]:
         img = self._render()
-        return [{"image": img[i], "state": self.state[i, :5].copy(), "task_description": self.task_description(
+        wrist = self._wrist_view(img)
+        return [{"image": img[i], "wrist_image": wrist[i], "state": self.state[i, :5].copy(), "task_description": self.task_description(
             int(self.task_ids[i])), "step": int(self.steps[i]), "done": bool(self.done[i]),
             "success": bool(self.success[i])} for i in range(self.num_envs)]
 

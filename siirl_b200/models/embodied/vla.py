@@ -49,14 +49,20 @@ class ActionTokenizer:
 class VLAProcessor:
     """Builds model inputs for one control step of a batch of environments.
 
-    Prompt layout per step: ``[image placeholders x tokens_per_image] [task text tokens]`` followed, in training,
-    by the ``action_chunks_len * action_token_len`` action tokens.  Rope positions follow the multimodal
+    Prompt layout per step: ``[image placeholders x tokens_per_image x num_images] [task text tokens]`` followed, in
+    training, by the ``action_chunks_len * action_token_len`` action tokens.  Rope positions follow the multimodal
     convention of the VL decoder: an image of a ``g x g`` merged grid advances the position by ``g`` and the text
-    continues from there, so ``rope_delta = tokens_per_image - g`` per image."""
+    continues from there, so ``rope_delta = tokens_per_image - g`` per image.
+
+    ``num_images > 1`` (third-person + wrist camera; the reference's ``num_images_in_input``,
+    siirl/engine/rollout/embodied_rollout.py:652-666): the policy images of one step are kept stacked along the
+    height, ``[N, num_images * S, S, 3]``, so buffers and batches keep one image tensor per step; every image gets
+    its own placeholders, in camera order."""
 
     def __init__(self, model_config, tokenizer, image_size: int = 224, center_crop: bool = True,
-                 max_text_len: int = 48):
+                 max_text_len: int = 48, num_images: int = 1):
         self.cfg, self.tok = model_config, tokenizer
+        self.num_images = max(1, int(num_images))
         self.center_crop = center_crop
         self.max_text_len = max_text_len
         self.image_token_id = model_config.image_token_id
@@ -69,6 +75,7 @@ class VLAProcessor:
             self.patch, self.merge, self.tpatch = pc.featurizer.patch_size, 1, 1
             self.grid = self.image_size // self.patch
             self.tokens_per_image = pc.tokens_per_image
+            self.image_tokens = self.tokens_per_image * self.num_images
             self.image_offset = 1
             return
         v = model_config.vision
@@ -78,19 +85,29 @@ class VLAProcessor:
         self.image_size = max(unit, image_size // unit * unit)
         self.grid = self.image_size // self.patch
         self.tokens_per_image = (self.grid // self.merge) ** 2
+        self.image_tokens = self.tokens_per_image * self.num_images
 
     # ---- images --------------------------------------------------------------------------------------
     def resize(self, images: torch.Tensor) -> torch.Tensor:
         """``[N, H, W, 3] uint8`` camera frames -> ``[N, S, S, 3] uint8`` policy input (centre crop of 90 % area when
-        enabled, then bilinear resize; reference: embodied_rollout.py:65-133)."""
-        N, H, W, _ = images.shape
+        enabled, then bilinear resize; reference: embodied_rollout.py:65-133).  ``[N, num_images, H, W, 3]`` gives the
+        cameras stacked along the height, ``[N, num_images * S, S, 3]``."""
+        stacked = images.dim() == 5
+        if stacked:
+            N, k = images.shape[:2]
+            images = images.reshape(N * k, *images.shape[2:])
+        H, W = images.shape[1:3]
         crop = center_crop_box(H, W, 0.9) if self.center_crop else None
-        return resize_bilinear(images, (self.image_size, self.image_size), crop)
+        out = resize_bilinear(images, (self.image_size, self.image_size), crop)
+        return out.reshape(N, k * self.image_size, self.image_size, 3) if stacked else out
 
     def patchify(self, images_u8: torch.Tensor, dtype=torch.bfloat16) -> Tuple[torch.Tensor, torch.Tensor]:
         """Resized frames ``[N, S, S, 3] uint8`` -> flattened patches ``[N * grid^2, C*T*P*P]`` in the vision tower's
         order (per image ``(h/m, w/m, m, m)`` patch order, each patch ``C x T x P x P``) and ``grid_thw [N, 3]``."""
-        N, S = images_u8.shape[0], self.image_size
+        S = self.image_size
+        if self.num_images > 1:                 # cameras stacked along the height -> one image each, camera-minor order
+            images_u8 = images_u8.reshape(images_u8.shape[0] * self.num_images, S, S, 3)
+        N = images_u8.shape[0]
         if self.prismatic is not None:
             from .prismatic import normalize_for_towers
             x = normalize_for_towers(images_u8, self.prismatic.fused_featurizer is not None)
@@ -118,7 +135,7 @@ class VLAProcessor:
         return list(ids)[: self.max_text_len]
 
     def prompt_ids(self, task_description: str) -> List[int]:
-        img = [self.image_token_id] * self.tokens_per_image
+        img = [self.image_token_id] * self.image_tokens
         if self.prismatic is not None:
             bos = self.cfg.bos_token_id if self.cfg.bos_token_id is not None else 1
             return [bos] + img + self.text_tokens(task_description)
@@ -128,7 +145,7 @@ class VLAProcessor:
         """Placeholder positions of a packed batch whose sequences start at ``first_rows``."""
         dev = first_rows.device
         mask = torch.zeros(total_rows, dtype=torch.bool, device=dev)
-        at = first_rows[:, None] + self.image_offset + torch.arange(self.tokens_per_image, device=dev)[None, :]
+        at = first_rows[:, None] + self.image_offset + torch.arange(self.image_tokens, device=dev)[None, :]
         mask[at.flatten()] = True
         return mask
 
@@ -140,19 +157,21 @@ class VLAProcessor:
         gm = self.grid // self.merge
         hh = torch.arange(gm).repeat_interleave(gm)
         ww = torch.arange(gm).repeat(gm)
-        img = torch.stack([torch.zeros(gm * gm, dtype=torch.int64), hh, ww])
-        n_text = prompt_len - self.tokens_per_image + extra
-        txt = (torch.arange(n_text) + gm).expand(3, n_text)
-        return torch.cat([img, txt], 1), self.tokens_per_image - gm
+        one = torch.stack([torch.zeros(gm * gm, dtype=torch.int64), hh, ww])
+        img = torch.cat([one + j * gm for j in range(self.num_images)], 1)     # every image advances the position by gm
+        n_text = prompt_len - self.image_tokens + extra
+        txt = (torch.arange(n_text) + gm * self.num_images).expand(3, n_text)
+        return torch.cat([img, txt], 1), self.image_tokens - gm * self.num_images
 
     def mm_inputs(self, images_u8: torch.Tensor, prompt_lens: Sequence[int], dtype=torch.bfloat16) -> List[Dict]:
         """Per-prompt multimodal inputs for ``RolloutEngine.generate``."""
         pv, grid = self.patchify(images_u8, dtype)
-        per = 1 if self.prismatic is not None else self.grid * self.grid
+        k = self.num_images
+        per = (1 if self.prismatic is not None else self.grid * self.grid) * k
         out = []
         for i, n in enumerate(prompt_lens):
             pos, delta = self.rope_layout(n)
-            out.append({"pixel_values": pv[i * per:(i + 1) * per], "image_grid_thw": grid[i:i + 1],
+            out.append({"pixel_values": pv[i * per:(i + 1) * per], "image_grid_thw": grid[i * k:(i + 1) * k],
                         "rope_positions": pos, "rope_delta": delta})
         return out
 
@@ -240,7 +259,7 @@ def oft_action_hidden(model, proc: "VLAProcessor", prompts: Sequence[Sequence[in
         extras.append(proprio_projector(proprio.reshape(N, -1)))
     extras += list(pseudo_tokens or [])
     E = len(extras)
-    cut = proc.image_offset + proc.tokens_per_image          # first row behind the patches
+    cut = proc.image_offset + proc.image_tokens              # first row behind the patches
     rows = []
     for p in prompts:
         p = list(p)

@@ -124,16 +124,18 @@ def test_flatten_and_scatter_trajectories():
     assert torch.equal(back[run_tok], data["advantages"][run_tok]) and float(back[~run_tok].abs().sum()) == 0
 
 
-@pytest.mark.parametrize("policy", ["native-vla", "openvla-oft"])
-def test_embodied_pipeline_two_steps(tmp_path, policy):
+@pytest.mark.parametrize("policy,cameras", [("native-vla", 1), ("openvla-oft", 1), ("native-vla", 2), ("openvla-oft", 2)])
+def test_embodied_pipeline_two_steps(tmp_path, policy, cameras):
     """``native-vla``: the framework's VL decoder decoding action tokens one by one; ``openvla-oft``: the Prismatic
-    backbone (DINOv2 + SigLIP towers) with one-pass chunk decoding and scoring over the action bins."""
+    backbone (DINOv2 + SigLIP towers) with one-pass chunk decoding and scoring over the action bins.  ``cameras=2``:
+    third-person and wrist view per step (``num_images_in_input``)."""
     preset = "tiny-vl" if policy == "native-vla" else "tiny-openvla"
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, OMP_NUM_THREADS="2", SIIRL_LOG_DIR=str(tmp_path / "log"))
     env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
     args = ["algorithm.adv_estimator=grpo", "algorithm.workflow_type=embodied", "data.synthetic=embodied",
             "data.synthetic_size=32", "data.max_prompt_length=32", "data.max_response_length=32",
+            f"actor_rollout_ref.embodied.num_images_in_input={cameras}",
             "data.train_batch_size=4", f"actor_rollout_ref.model.arch_preset={preset}", "actor_rollout_ref.rollout.n=4",
             f"actor_rollout_ref.embodied.embodied_type={policy}",
             "actor_rollout_ref.rollout.max_num_seqs=16", "actor_rollout_ref.actor.ppo_mini_batch_size=4",
@@ -155,6 +157,7 @@ def test_embodied_pipeline_two_steps(tmp_path, policy):
     assert any(r["actor/grad_norm"] > 0 for r in m)          # some group mixes successes and failures
     assert m[0]["embodied_sampling/initial_trajectories"] == 16.0
     assert m[0]["response_length/max"] <= 8 * 7
+    assert abs(m[0]["actor/ppo_kl"]) < 1e-3                  # scoring sees the same images in the same layout as rollout
 
 
 @pytest.mark.parametrize("preset", ["tiny-openvla", "tiny-vl"])
