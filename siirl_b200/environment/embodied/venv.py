@@ -29,6 +29,11 @@ class DummyVectorEnv:
     def seed(self, seed: Optional[int] = None):
         return [e.seed(seed + i) if hasattr(e, "seed") and seed is not None else None for i, e in enumerate(self.envs)]
 
+    def call(self, method: str, args: Sequence[Any], ids: Optional[List[int]] = None):
+        """``env.method(args[k])`` on every listed environment (e.g. ``set_init_state``); returns the results."""
+        ids = list(range(self.env_num)) if ids is None else ids
+        return [getattr(self.envs[i], method)(args[k]) for k, i in enumerate(ids)]
+
     def close(self):
         for e in self.envs:
             if hasattr(e, "close"):
@@ -53,6 +58,8 @@ def _worker(conn, fn):
                 conn.send(env.step(data))
             elif cmd == "seed":
                 conn.send(env.seed(data) if hasattr(env, "seed") else None)
+            elif cmd == "call":
+                conn.send(getattr(env, data[0])(data[1]))
             elif cmd == "close":
                 if hasattr(env, "close"):
                     env.close()
@@ -92,6 +99,12 @@ class SubprocVectorEnv:
             self.parents[i].send(("step", actions[k]))
         outs = [self.parents[i].recv() for i in ids]
         return tuple(_stack(x) for x in zip(*outs))
+
+    def call(self, method: str, args: Sequence[Any], ids: Optional[List[int]] = None):
+        ids = list(range(self.env_num)) if ids is None else ids
+        for k, i in enumerate(ids):
+            self.parents[i].send(("call", (method, args[k])))
+        return [self.parents[i].recv() for i in ids]
 
     def close(self):
         for c in self.parents:
