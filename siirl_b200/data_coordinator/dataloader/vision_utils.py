@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import math
 import os
-from typing import Any, List, Optional, Sequence, Union
+from typing import Any, List, Optional
 
 import numpy as np
 import torch

@@ -26,7 +26,7 @@ tensor-parallel width equals the trainer's, so the train -> rollout hand-off mov
 """
 from __future__ import annotations
 
-from typing import Iterator, List, Optional, Tuple
+from typing import Iterator, List, Tuple
 
 import torch
 import torch.distributed as dist
