@@ -31,12 +31,14 @@ from .native_engine import RolloutOutput, SamplingParams
 
 
 class LatentCacheEngine:
-    def __init__(self, model, max_num_seqs: int = 64, max_model_len: int = 8192, **_unused):
+    def __init__(self, model, max_num_seqs: int = 64, max_model_len: int = 8192, max_num_batched_tokens: int = 16384,
+                 **_unused):
         cfg = model.cfg
         assert cfg.is_mla, "the latent-cache engine serves multi-head latent attention models"
         self.model = model
         self.max_num_seqs = int(max_num_seqs)
         self.max_model_len = int(max_model_len)
+        self.max_num_batched_tokens = max(1, int(max_num_batched_tokens or 16384))   # prompt tokens per prefill pass
         self.device = model.embed_tokens.device
         self.width = cfg.kv_lora_rank + cfg.qk_rope_head_dim
         self.cache: Optional[torch.Tensor] = None
@@ -158,7 +160,16 @@ class LatentCacheEngine:
             wave = [list(p)[: self.max_model_len - 1] for p in prompts[w0:w0 + per_wave]]
             P = len(wave)
             first_slots = [i * n for i in range(P)]
-            hidden = self._prefill(wave, first_slots, mm_inputs[w0:w0 + per_wave] if mm_inputs is not None else None)
+            mms = mm_inputs[w0:w0 + per_wave] if mm_inputs is not None else None
+            parts, g0 = [], 0
+            while g0 < P:                                          # prompts of one prefill pass: bounded token count
+                g1, toks = g0, 0
+                while g1 < P and (g1 == g0 or toks + len(wave[g1]) <= self.max_num_batched_tokens):
+                    toks += len(wave[g1])
+                    g1 += 1
+                parts.append(self._prefill(wave[g0:g1], first_slots[g0:g1], mms[g0:g1] if mms is not None else None))
+                g0 = g1
+            hidden = torch.cat(parts)
             plen = [len(p) for p in wave]
             if n > 1:                                              # the samples of a prompt share its latent rows
                 src = torch.tensor(first_slots, device=dev)

@@ -668,7 +668,8 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 if str(r.name).lower() != "hf" and getattr(self, "ep_ctx", None) is None:
                     from .rollout.latent_engine import LatentCacheEngine
                     self.engine = LatentCacheEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024),
-                                                    max_model_len=max_len)
+                                                    max_model_len=max_len,
+                                                    max_num_batched_tokens=r.max_num_batched_tokens)
                 else:
                     from .rollout.recompute_engine import RecomputeEngine
                     self.engine = RecomputeEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024),

@@ -318,7 +318,8 @@ def test_latent_cache_engine_equals_the_cache_free_engine(preset):
     for sp in (SamplingParams(n=2, temperature=0.0, max_new_tokens=9, eos_token_id=2),
                SamplingParams(n=1, temperature=0.0, max_new_tokens=4, ignore_eos=True)):
         want = RecomputeEngine(model, max_num_seqs=16).generate(prompts, sp)
-        eng = LatentCacheEngine(model, max_num_seqs=4, max_model_len=32)      # 4 slots: two prompts x two samples per wave
+        # 4 slots: two prompts x two samples per wave; 8 prompt tokens per prefill pass: one prompt at a time
+        eng = LatentCacheEngine(model, max_num_seqs=4, max_model_len=32, max_num_batched_tokens=8)
         got = eng.generate(prompts, sp)
         assert eng.cache is None                                              # woke up for the call, asleep again
         assert [(o.prompt_index, o.sample_index, o.token_ids, o.finish_reason) for o in got] == \
