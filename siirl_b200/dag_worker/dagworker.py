@@ -615,7 +615,35 @@ class DAGWorker:
                 if kind == "sleep":
                     time.sleep(float(f.get("seconds", 5.0)))
 
+    def _start_metric_worker(self) -> None:
+        """``trainer.async_metrics``: a collector thread on rank 0 merges the ranks' step metrics out of band."""
+        self._metric_client = self._metric_worker = None
+        if not getattr(self.config.trainer, "async_metrics", False) or self.world_size <= 1:
+            return
+        from ..execution.metric_worker.metric_worker import MetricClient, MetricWorker, default_store
+        store = default_store()
+        if store is None:
+            return
+        self._metric_client = MetricClient(store, self._rank)
+        if self._rank == 0:
+            def sink(merged, step):
+                merged = dict(merged)
+                self._async_history.append(merged)
+                if self.tracker is not None:
+                    self.tracker.log(merged, step=step)
+            self._async_history = []
+            self._metric_worker = MetricWorker(store, self.world_size, sink)
+
     def _run_training_loop(self) -> None:
+        self._start_metric_worker()
+        try:
+            self._training_loop_body()
+        finally:
+            if getattr(self, "_metric_worker", None) is not None:
+                self._metric_worker.close()          # deliver what is outstanding to the loggers
+                self._metric_worker = None
+
+    def _training_loop_body(self) -> None:
         t = self.config.trainer
         if t.val_before_train and self.validator.enabled and self.global_steps == 0:
             val = self.validator.validate()
@@ -647,7 +675,13 @@ class DAGWorker:
                     with _Timer("save_checkpoint", self.timing_raw, False):
                         self.checkpoint_manager.save_checkpoint(self.global_steps)
                 self.history.append(metrics)
-                if self._rank == 0 and self.tracker is not None:
+                if getattr(self, "_metric_client", None) is not None:
+                    # the step's own metrics reach the loggers through the collector thread; what was added after
+                    # the step (validation) is logged here
+                    late = {k: v for k, v in metrics.items() if k not in self._posted_keys}
+                    if self._rank == 0 and self.tracker is not None and late:
+                        self.tracker.log(late, step=self.global_steps)
+                elif self._rank == 0 and self.tracker is not None:
                     self.tracker.log(metrics, step=self.global_steps)
 
     def train_step(self, epoch: int = 0, batch_idx: int = 0) -> Optional[Dict[str, float]]:
@@ -745,7 +779,16 @@ class DAGWorker:
             if getattr(self, "_perf_dir", None) is None:
                 self._perf_dir = os.path.join("performance_logs", model, time.strftime("%Y-%m-%d-%H-%M-%S"))
             write_rank_performance_csv(numeric, self.global_steps + 1, self._rank, self.world_size, self._perf_dir)
-        metrics = reduce_metrics_across_ranks(numeric)
+        if getattr(self, "_metric_client", None) is not None:
+            # out-of-band: post and carry on; this rank keeps its own numbers, rank 0's collector merges all ranks'
+            step = self.global_steps + 1
+            self._metric_client.submit_metric(numeric, step)
+            if self._metric_worker is not None:
+                self._metric_worker.expect(step, {"training/global_step": step, "training/epoch": epoch})
+            metrics = dict(numeric)
+            self._posted_keys = set(metrics) | {"training/global_step", "training/epoch"}
+        else:
+            metrics = reduce_metrics_across_ranks(numeric)
         metrics["training/global_step"] = self.global_steps + 1
         metrics["training/epoch"] = epoch
         if self._rank == 0 and self.config.trainer.logger and "console" in list(self.config.trainer.logger):

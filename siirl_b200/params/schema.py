@@ -540,6 +540,9 @@ class TrainingArguments:
     project_name: str = "siirl_examples"
     experiment_name: str = "gsm8k"
     logger: List[str] = field(default_factory=lambda: ["console"])
+    # True: ranks post their step metrics to a collector thread on rank 0 (execution/metric_worker) instead of
+    # reducing them with collectives inside the step; the loggers then receive a step's metrics a little later
+    async_metrics: bool = False
     log_val_generations: int = 0
     nnodes: int = 1
     n_gpus_per_node: int = 8

@@ -74,12 +74,16 @@ def compute_throughput_metrics(batch, timing_raw: Dict[str, float], n_gpus: int)
 
 
 def reduce_kind(key: str) -> str:
-    k = key.lower()
-    if "max" in k:
+    """How a metric is merged over ranks, from the words of its name (split at ``/ _ @ . -``): ``max``, ``min``,
+    ``sum`` / ``total``, else the mean.  Whole words only: ``timing_s/step`` is a mean although "timing" contains
+    "min"."""
+    import re
+    words = set(re.split(r"[/_@.\-]+", key.lower()))
+    if "max" in words:
         return "max"
-    if "min" in k:
+    if "min" in words:
         return "min"
-    if "sum" in k or "total" in k:
+    if "sum" in words or "total" in words:
         return "sum"
     return "mean"
 
