@@ -22,3 +22,17 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def _fixed_random_streams():
+    """Every test starts from the same process-wide random streams, whatever ran before it: inputs drawn without an
+    explicit generator do not depend on the order or the selection of tests."""
+    import random
+
+    import numpy as np
+    import torch
+    random.seed(1234)
+    np.random.seed(1234)
+    torch.manual_seed(1234)
+    yield
