@@ -200,24 +200,49 @@ def stop_heartbeat() -> None:
 
 
 def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = None, poll_s: float = 0.5,
-                 heartbeat_timeout_s: float = 0.0, module: str = "siirl_b200.main_dag") -> int:
-    """Spawn ``nproc`` ranks of ``python -m <module> <argv>`` on this node and babysit them.  Returns the exit code
-    (0 when every rank exited 0; otherwise the first non-zero code after the remaining ranks were terminated)."""
+                 heartbeat_timeout_s: float = 0.0, module: str = "siirl_b200.main_dag", nnodes: int = 1,
+                 node_rank: int = 0, master_addr: str = "127.0.0.1", master_port: int = 0) -> int:
+    """Spawn this node's ``nproc`` ranks of ``python -m <module> <argv>`` and babysit them.  Returns the exit code
+    (0 when every rank exited 0; otherwise the first non-zero code after the remaining ranks were terminated).
+
+    One node (default): the launcher picks a free loopback port.  Several nodes: the same command runs on every
+    node with its ``node_rank``; node 0's launcher hosts the rendezvous store on ``master_port`` (reachable at
+    ``master_addr``), the other launchers and all ranks join it as clients.  Global rank = ``node_rank * nproc +
+    local rank``.  A launcher that stops its ranks (a failed or silent rank) raises an abort flag in the store; the
+    other nodes' launchers see it (or lose the store with node 0) and stop theirs, so a multi-node job ends as a
+    whole instead of waiting in a collective."""
+    import datetime
+
+    import torch.distributed as dist
     # The launcher hosts the rendezvous store itself (the ranks join as clients, the way torchrun's agent does it):
     # the port is bound here, by the process that chose it, so no other job can take it before rank 0 starts.
-    rdzv_store, port = host_store()
+    world = nproc * max(1, nnodes)
+    if nnodes <= 1:
+        rdzv_store, port = host_store()
+        master_addr = "127.0.0.1"
+    elif node_rank == 0:
+        port = int(master_port)
+        rdzv_store = dist.TCPStore(master_addr, port, is_master=True, wait_for_workers=False,
+                                   timeout=datetime.timedelta(seconds=300))
+    else:
+        port = int(master_port)
+        rdzv_store = dist.TCPStore(master_addr, port, is_master=False, wait_for_workers=False,
+                                   timeout=datetime.timedelta(seconds=300))
+    abort_key = f"siirl_launcher/abort/{(env or {}).get('SIIRL_RESTART_COUNT', '0')}"
     procs: List[subprocess.Popen] = []
     base = dict(os.environ)
     base.update(env or {})
-    base.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "WORLD_SIZE": str(nproc),
-                 "LOCAL_WORLD_SIZE": str(nproc), "SIIRL_LAUNCHED": "1", "TORCHELASTIC_USE_AGENT_STORE": "True"})
+    base.update({"MASTER_ADDR": master_addr, "MASTER_PORT": str(port), "WORLD_SIZE": str(world),
+                 "LOCAL_WORLD_SIZE": str(nproc), "GROUP_RANK": str(node_rank), "SIIRL_LAUNCHED": "1",
+                 "TORCHELASTIC_USE_AGENT_STORE": "True"})
     store = None
     if heartbeat_timeout_s > 0:
         store, hb_port = host_store(timeout_s=5.0)
         base["SIIRL_HEARTBEAT_PORT"] = str(hb_port)
-    for r in range(nproc):
+    ranks = [node_rank * nproc + r for r in range(nproc)]
+    for local, r in enumerate(ranks):
         e = dict(base)
-        e.update({"RANK": str(r), "LOCAL_RANK": str(r)})
+        e.update({"RANK": str(r), "LOCAL_RANK": str(local)})
         procs.append(subprocess.Popen([sys.executable, "-m", module, *argv], env=e))
     code = 0
     try:
@@ -230,14 +255,30 @@ def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = No
             if all(s == 0 for s in states):
                 break
             if store is not None:
-                stale = stale_ranks(store, [r for r, s in enumerate(states) if s is None], heartbeat_timeout_s)
+                stale = stale_ranks(store, [ranks[i] for i, s in enumerate(states) if s is None], heartbeat_timeout_s)
                 if stale:
                     print(f"[siirl_b200] no heartbeat from rank(s) {stale} for {heartbeat_timeout_s:.0f} s: stopping "
                           f"the job", file=sys.stderr)
                     code = HEARTBEAT_EXIT_CODE
                     break
+            if nnodes > 1:
+                try:
+                    if rdzv_store.check([abort_key]):
+                        print(f"[siirl_b200] node {node_rank}: another node stopped the job", file=sys.stderr)
+                        code = int(rdzv_store.get(abort_key).decode() or 1)
+                        break
+                except Exception as e:  # noqa: BLE001  (node 0 and its store are gone)
+                    print(f"[siirl_b200] node {node_rank}: lost the rendezvous store ({type(e).__name__}): stopping "
+                          f"the local ranks", file=sys.stderr)
+                    code = 1
+                    break
             time.sleep(poll_s)
     finally:
+        if code != 0 and nnodes > 1:
+            try:
+                rdzv_store.set(abort_key, str(code))
+            except Exception:  # noqa: BLE001
+                pass
         for p in procs:
             if p.poll() is None:
                 p.terminate()
@@ -247,5 +288,23 @@ def launch_local(argv: List[str], nproc: int, env: Optional[Dict[str, str]] = No
                 p.wait(timeout=max(0.1, deadline - time.time()))
             except subprocess.TimeoutExpired:
                 p.kill()
+        if code != 0 and nnodes > 1 and node_rank == 0:
+            time.sleep(2 * poll_s + 0.5)          # the other launchers poll the flag from this process's store
         _ = (store, rdzv_store)
     return code
+
+
+def node_placement(nnodes: int) -> tuple:
+    """``(node_rank, master_addr, master_port)`` of this node from the environment of the usual cluster launchers
+    (``NODE_RANK`` / ``GROUP_RANK`` / ``SLURM_NODEID`` / ``OMPI_COMM_WORLD_RANK``; ``MASTER_ADDR``, ``MASTER_PORT``)."""
+    if nnodes <= 1:
+        return 0, "127.0.0.1", 0
+    rank = next((os.environ[k] for k in ("NODE_RANK", "GROUP_RANK", "SLURM_NODEID", "OMPI_COMM_WORLD_RANK")
+                 if os.environ.get(k, "") != ""), None)
+    addr, port = os.environ.get("MASTER_ADDR"), os.environ.get("MASTER_PORT")
+    if rank is None or not addr or not port:
+        raise RuntimeError(f"trainer.nnodes={nnodes}: start the same command on every node with NODE_RANK (0 .. "
+                           f"{nnodes - 1}), MASTER_ADDR (node 0) and MASTER_PORT set")
+    if not 0 <= int(rank) < nnodes:
+        raise RuntimeError(f"NODE_RANK={rank} is outside 0 .. {nnodes - 1}")
+    return int(rank), addr, int(port)

@@ -99,10 +99,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     argv = list(sys.argv[1:] if argv is None else argv)
     config = parse_config(argv)
     already_rank = "RANK" in os.environ and "WORLD_SIZE" in os.environ
-    nproc = config.trainer.n_gpus_per_node * config.trainer.nnodes
-    if already_rank or nproc <= 1:
+    nnodes = max(1, int(config.trainer.nnodes))
+    nproc = config.trainer.n_gpus_per_node
+    if already_rank or nproc * nnodes <= 1:
         run_rank(config)
         return 0
+    from .execution.scheduler.launch import node_placement
+    node_rank, master_addr, master_port = node_placement(nnodes)
     restarts = 0
     while True:
         run_argv = list(argv)
@@ -114,7 +117,8 @@ def main(argv: Optional[List[str]] = None) -> int:
             if config.trainer.resume_mode == "disable" or find_latest_complete_ckpt_path(root, log=lambda *_: None):
                 run_argv.append("trainer.resume_mode=auto")
         code = launch_local(run_argv, nproc, env={"SIIRL_RESTART_COUNT": str(restarts)},
-                            heartbeat_timeout_s=config.fault.heartbeat_timeout_s)
+                            heartbeat_timeout_s=config.fault.heartbeat_timeout_s, nnodes=nnodes, node_rank=node_rank,
+                            master_addr=master_addr, master_port=master_port)
         if code == 0 or not config.fault.auto_restart or restarts >= config.fault.max_restarts:
             return code
         restarts += 1

@@ -366,3 +366,43 @@ def test_async_metric_worker_two_ranks(tmp_path):
         assert 0.6 < ra["perf/total_num_tokens"] / rb["perf/total_num_tokens"] < 1.6
         assert 0.0 <= ra["critic/score/mean"] <= 1.0 and ra["actor/grad_norm"] > 0
         assert set(rb) - set(ra) == set()
+
+
+def _spawn_node(args, log_dir, node_rank, port):
+    env = dict(os.environ, OMP_NUM_THREADS="2", SIIRL_LOG_DIR=str(log_dir), NODE_RANK=str(node_rank),
+               MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    return subprocess.Popen([sys.executable, "-m", "siirl_b200.main_dag", *ARGS, *args], env=env, cwd=root,
+                            stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+
+
+def test_two_node_launch_on_one_host(tmp_path):
+    """``trainer.nnodes=2``: the same command on two "nodes" (here: two launchers on one host) with NODE_RANK /
+    MASTER_ADDR / MASTER_PORT; node 0 hosts the rendezvous, each launcher spawns its own ranks."""
+    from siirl_b200.execution.scheduler.launch import find_free_port
+    port = find_free_port()
+    args = ["trainer.nnodes=2", "trainer.n_gpus_per_node=1", f"trainer.default_local_dir={tmp_path / 'c'}",
+            "trainer.total_training_steps=2", "trainer.save_freq=-1"]
+    nodes = [_spawn_node(args, tmp_path / "log", r, port) for r in (0, 1)]
+    outs = [p.communicate(timeout=600) for p in nodes]
+    assert [p.returncode for p in nodes] == [0, 0], outs[0][1][-3000:] + outs[1][1][-3000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2] and all(r["actor/grad_norm"] > 0 for r in m)
+
+
+def test_two_node_job_stops_as_a_whole_when_one_node_fails(tmp_path):
+    """A rank of node 1 raises at step 1: node 1's launcher flags the abort in the rendezvous store, node 0's launcher
+    sees it and stops its ranks; both commands return non-zero instead of waiting in a collective."""
+    from siirl_b200.execution.scheduler.launch import find_free_port
+    port = find_free_port()
+    args = ["trainer.nnodes=2", "trainer.n_gpus_per_node=1", f"trainer.default_local_dir={tmp_path / 'c'}",
+            "trainer.total_training_steps=3", "trainer.save_freq=-1",
+            "fault.inject=[{rank: 1, step: 1, node: function_reward, kind: exit, code: 23}]"]
+    nodes = [_spawn_node(args, tmp_path / "log", r, port) for r in (0, 1)]
+    outs = [p.communicate(timeout=300) for p in nodes]
+    assert nodes[1].returncode == 23, outs[1][1][-3000:]
+    assert nodes[0].returncode != 0, outs[0][1][-3000:]
+    assert "another node stopped the job" in outs[0][1] or nodes[0].returncode == 23
