@@ -33,6 +33,13 @@ class CheckpointManager:
         self.hdfs_root = worker.config.trainer.default_hdfs_dir or None
         self._pending = None        # (global_step, [PendingSave, ...]) of a save whose tracker is not written yet
 
+    @staticmethod
+    def _save_contents(ck):
+        """``checkpoint.save_contents`` (the reference's key) when the user set it, else ``checkpoint.contents``."""
+        default = ["model", "optimizer", "extra"]
+        sc = list(getattr(ck, "save_contents", None) or default)
+        return sc if sorted(sc) != sorted(default) else list(ck.contents)
+
     def _roles(self):
         out = []
         seen = set()
@@ -42,10 +49,10 @@ class CheckpointManager:
             seen.add(id(wk))
             if key.startswith("actor_rollout_ref_") and getattr(wk, "store", None) is not None:
                 out.append((f"actor_agent_{key.rsplit('_', 1)[-1]}", wk,
-                            self.w.config.actor_rollout_ref.actor.checkpoint.contents,
+                            self._save_contents(self.w.config.actor_rollout_ref.actor.checkpoint),
                             self.w.config.trainer.max_actor_ckpt_to_keep))
             elif key.startswith("critic_"):
-                out.append((f"critic_agent_{key.rsplit('_', 1)[-1]}", wk, self.w.config.critic.checkpoint.contents,
+                out.append((f"critic_agent_{key.rsplit('_', 1)[-1]}", wk, self._save_contents(self.w.config.critic.checkpoint),
                             self.w.config.trainer.max_critic_ckpt_to_keep))
         return out
 

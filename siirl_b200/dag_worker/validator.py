@@ -73,6 +73,7 @@ class Validator:
                 rl = int(out["response_mask"][i].sum())
                 outputs.append(w.tokenizer.decode(out["responses"][i, :rl].tolist()))
                 scores.append(float(seq[i]))
+        self._dump_rank_generations(sources, inputs, outputs, scores)
         if w._dist and w.world_size > 1:
             gathered = [None] * w.world_size
             dist.all_gather_object(gathered, (sources, inputs, scores, outputs))
@@ -95,3 +96,21 @@ class Validator:
             ValidationGenerationsLogger(t.validation_data_dir).log(
                 list(zip(inputs, outputs, scores))[: t.log_val_generations], w.global_steps)
         return metrics
+
+    def _dump_rank_generations(self, sources, inputs, outputs, scores) -> None:
+        """``trainer.rollout_data_dir``: every rank writes the validation generations it produced to
+        ``step_<N>_rank_<r>.json`` (reference: siirl/dag_worker/dag_utils.py:637-683)."""
+        import json
+        import os
+        w = self.w
+        out_dir = getattr(w.config.trainer, "rollout_data_dir", None)
+        if not out_dir:
+            return
+        try:
+            os.makedirs(out_dir, exist_ok=True)
+            rows = [{"rank": w._rank, "global_step": w.global_steps, "data_source": s, "input": i, "output": o,
+                     "score": float(c)} for s, i, o, c in zip(sources, inputs, outputs, scores)]
+            with open(os.path.join(out_dir, f"step_{w.global_steps}_rank_{w._rank}.json"), "w", encoding="utf-8") as f:
+                json.dump(rows, f, ensure_ascii=False, indent=4)
+        except OSError as e:
+            print(f"[siirl_b200] rank {w._rank}: could not write validation generations to {out_dir}: {e}")

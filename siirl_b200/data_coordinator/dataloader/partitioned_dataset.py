@@ -159,9 +159,12 @@ class PartitionedRLHFDataset(Dataset):
             if has_vid:
                 from .vision_utils import process_video
                 m = self._full_config.actor_rollout_ref.model
+                # videos have pixel limits and a frame budget of their own (the reference's processor keys,
+                # siirl/data_coordinator/dataloader/partitioned_dataset.py:136-139, 355-358)
                 frames = [v if isinstance(v, torch.Tensor) and v.dim() == 4 else
-                          process_video(v if isinstance(v, dict) else {"video": v}, max_pixels=m.image_max_pixels,
-                                        min_pixels=m.image_min_pixels) for v in videos]
+                          process_video(v if isinstance(v, dict) else {"video": v}, fps=m.video_fps,
+                                        fps_max_frames=m.video_maxlen, max_pixels=m.video_max_pixels,
+                                        min_pixels=m.video_min_pixels) for v in videos]
             out = self._vl_processor()(ids, list(images) if has_img else [], frames)
             ids = out["input_ids"]
             mm_inputs = {"pixel_values": out["pixel_values"], "image_grid_thw": out["image_grid_thw"]}

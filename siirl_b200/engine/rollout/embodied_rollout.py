@@ -28,7 +28,7 @@ from .native_engine import RolloutEngine, SamplingParams
 
 class EmbodiedRollout:
     def __init__(self, engine: RolloutEngine, model_config, tokenizer, embodied_cfg, device, seed: int = 0,
-                 video_embedder=None):
+                 video_embedder=None, model_path: Optional[str] = None):
         self.engine, self.cfg, self.device = engine, embodied_cfg, torch.device(device)
         self.model_config = model_config
         self.actions = ActionTokenizer(model_config.action_vocab_size or model_config.vocab_size,
@@ -43,6 +43,10 @@ class EmbodiedRollout:
         self.parallel = uses_parallel_decode(embodied_cfg, model_config)
         self.env = None
         self.video_embedder = video_embedder
+        # fine-tuned checkpoints carry the action statistics of their dataset: decoded bin centres in [-1, 1] become
+        # robot units before they reach the environment (``embodied.unnorm_key`` names the dataset)
+        from ...models.embodied.action_heads import load_action_norm_stats
+        self.norm_stats = load_action_norm_stats(model_path, getattr(embodied_cfg, "unnorm_key", "") or "")
 
     def _make_env(self, n: int):
         e = self.cfg.env
@@ -130,7 +134,11 @@ class EmbodiedRollout:
                 gen_tokens += tok.numel()
                 gi = torch.tensor([rows[k] for k in act_rows], device=dev)
                 out_resp[gi, l], out_logp[gi, l], out_img[gi, l] = tok, lp, imgs
-                acts = self.actions.decode(tok).reshape(len(act_rows), self.chunk, self.atl).cpu().numpy()
+                acts = self.actions.decode(tok).reshape(len(act_rows), self.chunk, self.atl).cpu()
+                if self.norm_stats is not None:
+                    from ...models.embodied.action_heads import unnormalize_actions
+                    acts = unnormalize_actions(acts, self.norm_stats)
+                acts = acts.numpy()
                 full = torch.zeros(len(rows), self.chunk, self.atl).numpy()
                 full[act_rows] = acts
                 obs = self._run(env.step(full))

@@ -511,7 +511,12 @@ class _ModelWorkerBase:
         return pk.scatter(lp), (pk.scatter(ent) if ent is not None else None)
 
     def _optimizer_step(self, optim_cfg, grad_clip: float) -> torch.Tensor:
-        lr = lr_at_step(optim_cfg, self.opt_step, max(self.total_training_steps, optim_cfg.total_training_steps))
+        megatron = str(getattr(getattr(self.config, "actor", self.config), "strategy", "")) == "megatron"
+        lr = lr_at_step(optim_cfg, self.opt_step, max(self.total_training_steps, optim_cfg.total_training_steps),
+                        megatron=megatron)
+        if megatron:
+            grad_clip = float(optim_cfg.clip_grad)             # the Megatron optimizer's own key (reference:
+            #                                                    siirl/utils/megatron/optimizer.py, ``clip_grad``)
         if getattr(self, "_tp_train", None) is not None:
             from ..parallel.megatron_tp import allreduce_sequence_parallel_grads
             self.store.collect_grads()
@@ -563,7 +568,9 @@ class _ModelWorkerBase:
                 fs.copy(hdfs_path, local_path)
             if self.world > 1:
                 dist.barrier(group=self.group)
-        extra = ShardedCheckpointManager(self.model, self.store, self.model_config, group=group).load(local_path)
+        ck = getattr(getattr(self.config, "actor", self.config), "checkpoint", None)
+        extra = ShardedCheckpointManager(self.model, self.store, self.model_config, group=group).load(
+            local_path, contents=list(ck.load_contents) if ck is not None and ck.load_contents is not None else None)
         if extra:
             self.opt_step = int(extra.get("opt_step", self.opt_step))
         if del_local_after_load:
@@ -770,7 +777,7 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                                          checkpoint=emb.video_embedding_model_path or None)
             self.embodied_rollout = EmbodiedRollout(self.engine, self.model_config, tok, emb, self.device,
                                                     seed=self.config.rollout.seed + 104729 * self.rank,
-                                                    video_embedder=embedder)
+                                                    video_embedder=embedder, model_path=self.config.model.path)
 
     # ---- rollout -------------------------------------------------------------------------------------
     @torch.no_grad()

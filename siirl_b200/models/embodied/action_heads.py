@@ -213,3 +213,32 @@ def normalize_proprio(proprio: torch.Tensor, stats: Dict[str, Sequence[float]], 
     lo, hi, mask = _bounds(stats, kind)
     p = proprio.float().cpu()
     return torch.where(mask, (2.0 * (p - lo) / (hi - lo + 1e-8) - 1.0).clamp(-1.0, 1.0), p)
+
+
+def load_action_norm_stats(model_path: Optional[str], unnorm_key: str) -> Optional[Dict[str, Sequence[float]]]:
+    """Action statistics of one dataset from a fine-tuned checkpoint: ``dataset_statistics.json`` beside the weights,
+    else ``norm_stats`` inside ``config.json`` (where OpenVLA keeps them).  ``unnorm_key`` falls back to
+    ``<key>_no_noops`` as the reference does (siirl/engine/rollout/embodied_rollout.py:197-200,
+    siirl/engine/fsdp_workers.py:456-470).  ``None`` when the checkpoint carries no statistics (base checkpoints,
+    random-init models): actions then stay in ``[-1, 1]``."""
+    import json
+    import os
+    if not model_path or not os.path.isdir(str(model_path)):
+        return None
+    stats = None
+    f = os.path.join(str(model_path), "dataset_statistics.json")
+    if os.path.isfile(f):
+        with open(f) as fh:
+            stats = json.load(fh)
+    else:
+        c = os.path.join(str(model_path), "config.json")
+        if os.path.isfile(c):
+            with open(c) as fh:
+                stats = json.load(fh).get("norm_stats")
+    if not stats:
+        return None
+    key = unnorm_key if unnorm_key in stats else f"{unnorm_key}_no_noops"
+    if key not in stats:
+        raise KeyError(f"action un-normalisation key {unnorm_key!r} not found in the checkpoint's statistics "
+                       f"(have: {sorted(stats)})")
+    return stats[key].get("action", stats[key])

@@ -301,11 +301,38 @@ class FlatParamStore:
             yield n, self.flat_param[o:o + k].view(shp)
 
 
-def lr_at_step(optim_cfg, step: int, total_steps: int) -> float:
-    """Learning-rate schedule of the reference's optimizer config (constant / cosine / wsd with linear warm-up;
-    siirl/utils/model_utils/torch_functional.py:518-702)."""
+def lr_at_step(optim_cfg, step: int, total_steps: int, megatron: bool = False) -> float:
+    """Learning-rate schedule of the reference's optimizer config.
+
+    FSDP-style keys (siirl/utils/model_utils/torch_functional.py:518-702): linear warm-up from 0 over
+    ``lr_warmup_steps`` (or ``lr_warmup_steps_ratio``), then ``warmup_style`` constant / cosine / wsd down to
+    ``min_lr_ratio * lr``.
+
+    ``megatron=True`` reads the keys the reference hands to Megatron-core's parameter scheduler
+    (siirl/utils/megatron/optimizer.py:40-75): warm-up from ``lr_warmup_init``, then ``lr_decay_style`` constant /
+    linear / cosine / inverse-square-root over ``lr_decay_steps`` (default: the whole run) down to ``min_lr``."""
     base = optim_cfg.lr
     warm = optim_cfg.lr_warmup_steps
+    if megatron:
+        decay_steps = int(optim_cfg.lr_decay_steps or total_steps or 0)
+        if warm is None or warm <= 0:
+            warm = int((optim_cfg.lr_warmup_steps_ratio or 0.0) * max(decay_steps, 0))
+        init, floor = float(optim_cfg.lr_warmup_init or 0.0), float(optim_cfg.min_lr or 0.0)
+        if warm > 0 and step < warm:
+            return init + (base - init) * (step + 1) / warm
+        style = optim_cfg.lr_decay_style or "constant"
+        if style == "constant" or decay_steps <= warm:
+            return base
+        if step >= decay_steps:
+            return floor
+        prog = (step - warm) / max(1, decay_steps - warm)
+        if style == "linear":
+            return floor + (base - floor) * (1.0 - prog)
+        if style == "cosine":
+            return floor + (base - floor) * 0.5 * (1.0 + math.cos(math.pi * prog))
+        if style == "inverse-square-root":
+            return max(floor, base * math.sqrt(max(warm, 1)) / math.sqrt(max(step, 1)))
+        raise ValueError(f"unknown lr_decay_style {style!r}")
     if warm is None or warm < 0:
         warm = int(optim_cfg.lr_warmup_steps_ratio * max(total_steps, 0))
     if warm > 0 and step < warm:

@@ -273,11 +273,16 @@ class ShardedCheckpointManager:
             st.release_full()
         return PendingSave(write, async_save)
 
-    def load(self, directory: str) -> Optional[Dict[str, Any]]:
+    def load(self, directory: str, contents: Optional[List[str]] = None) -> Optional[Dict[str, Any]]:
+        """``contents`` (the reference's ``checkpoint.load_contents``): which parts of the checkpoint to take.
+        Without ``"optimizer"`` the weights are loaded and the optimizer starts fresh from them; without ``"extra"``
+        neither the random streams nor the scheduler / dataloader fields are restored (the step counter still is);
+        without ``"model"`` nothing of the training state is read."""
+        take = set(contents) if contents is not None else {"model", "optimizer", "extra"}
         with open(os.path.join(directory, "manifest.json")) as f:
             manifest = json.load(f)
         saved_world = manifest["world_size"]
-        st = self.store
+        st = self.store if "model" in take else None
         mpath, opath, epath = self._names(directory)
         ex = getattr(st, "expert", None)
         if ex is not None:
@@ -295,7 +300,10 @@ class ShardedCheckpointManager:
                 st.flat_param[st.lo:st.hi].copy_(m["flat"].to(st.device))
                 if self.world > 1:
                     st._all_gather_params()
-                if os.path.exists(opath) and st.master is not None:
+                if "optimizer" not in take:
+                    if st.master is not None:
+                        st.sync_master_from_params()
+                elif os.path.exists(opath) and st.master is not None:
                     st.load_shard_state_dict(torch.load(opath, map_location="cpu", weights_only=False))
                 elif st.master is not None:
                     if "optimizer" in manifest.get("contents", []) and manifest.get("has_optimizer_state", True):
@@ -306,7 +314,9 @@ class ShardedCheckpointManager:
                     st.sync_master_from_params()
             else:
                 self._load_resharded(directory, saved_world, manifest)
-        elif os.path.exists(os.path.join(directory, f"model_world_size_{saved_world}_rank_0.pt")):
+                if "optimizer" not in take and st.master is not None:
+                    st.sync_master_from_params()
+        elif "model" in take and os.path.exists(os.path.join(directory, f"model_world_size_{saved_world}_rank_0.pt")):
             m = torch.load(os.path.join(directory, f"model_world_size_{saved_world}_rank_0.pt"), map_location="cpu",
                            weights_only=False)
             if "state_dict" in m:
@@ -316,12 +326,12 @@ class ShardedCheckpointManager:
             epath = os.path.join(directory, f"extra_state_world_size_{saved_world}_rank_0.pt")
         if os.path.exists(epath):
             e = torch.load(epath, map_location="cpu", weights_only=False)
-            if saved_world == self.world:
+            if saved_world == self.world and "extra" in take:
                 try:
                     load_rng_state(e["rng"])
                 except Exception:  # noqa: BLE001  (a CUDA state cannot be restored on a CPU-only machine)
                     pass
-            extra = dict(e.get("extra", {}))
+            extra = dict(e.get("extra", {})) if "extra" in take else {}
             extra["global_step"] = e.get("global_step", 0)
         return extra
 

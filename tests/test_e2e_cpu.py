@@ -406,3 +406,17 @@ def test_two_node_job_stops_as_a_whole_when_one_node_fails(tmp_path):
     assert nodes[1].returncode == 23, outs[1][1][-3000:]
     assert nodes[0].returncode != 0, outs[0][1][-3000:]
     assert "another node stopped the job" in outs[0][1] or nodes[0].returncode == 23
+
+
+def test_validation_generations_are_dumped_per_rank(tmp_path):
+    """``trainer.rollout_data_dir``: each rank writes ``step_<N>_rank_<r>.json`` with the generations it validated."""
+    out = _run(["trainer.test_freq=1", f"trainer.rollout_data_dir={tmp_path / 'dump'}",
+                f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=1", "trainer.save_freq=-1"],
+               tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert "val-core/all/reward/mean" in m[-1]
+    files = sorted(os.listdir(tmp_path / "dump"))
+    assert files == ["step_1_rank_0.json", "step_1_rank_1.json"], files
+    rows = json.load(open(tmp_path / "dump" / files[1]))
+    assert rows and rows[0]["rank"] == 1 and {"data_source", "input", "output", "score", "global_step"} <= set(rows[0])

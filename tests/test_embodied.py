@@ -263,3 +263,24 @@ def test_oft_diffusion_head_trains_and_samples():
         opt.step()
     assert head.act_in_weight.grad is not None and head.time_weight.grad.abs().sum() > 0
     assert sum(losses[-5:]) / 5 < 0.85 * sum(losses[:5]) / 5, losses
+
+
+def test_action_statistics_of_a_checkpoint(tmp_path):
+    """``dataset_statistics.json`` (or ``norm_stats`` in config.json) + ``embodied.unnorm_key``, with the
+    ``_no_noops`` fallback; no statistics -> ``None``."""
+    import json as _json
+
+    from siirl_b200.models.embodied.action_heads import load_action_norm_stats, unnormalize_actions
+    assert load_action_norm_stats(None, "libero_goal") is None and load_action_norm_stats(str(tmp_path), "x") is None
+    st = {"libero_goal_no_noops": {"action": {"q01": [-0.5] * 7, "q99": [0.5] * 7, "mask": [True] * 6 + [False]}}}
+    (tmp_path / "dataset_statistics.json").write_text(_json.dumps(st))
+    got = load_action_norm_stats(str(tmp_path), "libero_goal")
+    assert got["q99"][0] == 0.5
+    a = unnormalize_actions(torch.tensor([[1.0] * 7, [-1.0] * 7]), got)
+    assert torch.allclose(a[0, :6], torch.full((6,), 0.5), atol=1e-6) and a[0, 6] == 1.0 and a[1, 6] == -1.0
+    with pytest.raises(KeyError):
+        load_action_norm_stats(str(tmp_path), "bridge_orig")
+    other = tmp_path / "b"
+    other.mkdir()
+    (other / "config.json").write_text(_json.dumps({"norm_stats": {"bridge_orig": {"action": {"q01": [0.0], "q99": [1.0]}}}}))
+    assert load_action_norm_stats(str(other), "bridge_orig")["q99"] == [1.0]

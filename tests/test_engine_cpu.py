@@ -119,6 +119,18 @@ def test_lr_schedules():
     assert lr_at_step(cfg, 10, 10) == pytest.approx(0.0, abs=1e-6)
     cfg.warmup_style = "constant"
     assert lr_at_step(cfg, 7, 10) == 1.0
+    # the keys of the Megatron parameter scheduler
+    mg = parse_config(["actor_rollout_ref.actor.optim.lr=1.0", "actor_rollout_ref.actor.optim.lr_warmup_steps=4",
+                       "actor_rollout_ref.actor.optim.lr_warmup_init=0.2", "actor_rollout_ref.actor.optim.min_lr=0.1",
+                       "actor_rollout_ref.actor.optim.lr_decay_style=cosine",
+                       "actor_rollout_ref.actor.optim.lr_decay_steps=14"]).actor_rollout_ref.actor.optim
+    assert lr_at_step(mg, 0, 100, megatron=True) == pytest.approx(0.4) and lr_at_step(mg, 3, 100, megatron=True) == 1.0
+    assert lr_at_step(mg, 9, 100, megatron=True) == pytest.approx(0.1 + 0.9 * 0.5)      # half way down the cosine
+    assert lr_at_step(mg, 14, 100, megatron=True) == 0.1 and lr_at_step(mg, 50, 100, megatron=True) == 0.1
+    mg.lr_decay_style = "linear"
+    assert lr_at_step(mg, 9, 100, megatron=True) == pytest.approx(0.55)
+    mg.lr_decay_style = "constant"
+    assert lr_at_step(mg, 9, 100, megatron=True) == 1.0
 
 
 def test_hf_roundtrip_and_sharded_checkpoint(tmp_path, tiny):
@@ -141,6 +153,17 @@ def test_hf_roundtrip_and_sharded_checkpoint(tmp_path, tiny):
     assert extra["global_step"] == 4 and extra["opt_step"] == 1
     assert torch.equal(s3.flat_param, s4.flat_param) and torch.equal(s3.exp_avg_sq, s4.exp_avg_sq)
     assert s4.step_count == 1
+    # load_contents without the optimizer: weights are taken, Adam state starts fresh from them
+    m5 = build_model(get_config("tiny"), dtype=torch.float32, seed=7)
+    s5 = FlatParamStore(m5)
+    extra = ShardedCheckpointManager(m5, s5, m5.cfg).load(str(tmp_path / "ck"), contents=["model"])
+    assert torch.equal(s3.flat_param, s5.flat_param) and s5.step_count == 0 and float(s5.exp_avg_sq.abs().sum()) == 0.0
+    assert torch.equal(s5.master, s5.flat_param[s5.lo:s5.hi].float()) and extra == {"global_step": 4}
+    from siirl_b200.dag_worker.checkpoint_manager import CheckpointManager
+    ck = parse_config(["actor_rollout_ref.actor.checkpoint.save_contents=[model,hf_model]"]).actor_rollout_ref.actor.checkpoint
+    assert CheckpointManager._save_contents(ck) == ["model", "hf_model"]
+    ck = parse_config(["actor_rollout_ref.actor.checkpoint.contents=[model]"]).actor_rollout_ref.actor.checkpoint
+    assert CheckpointManager._save_contents(ck) == ["model"]
 
 
 def test_reward_managers_place_score_at_last_valid_token():
