@@ -41,7 +41,29 @@ def resolve_model_config(model_args, value_head: bool = False) -> DecoderConfig:
         cfg.tie_word_embeddings = False
     if int(getattr(model_args, "lora_rank", 0) or 0) > 0:
         cfg.lora_rank, cfg.lora_alpha = int(model_args.lora_rank), float(model_args.lora_alpha)
+        cfg.lora_targets = lora_targets(getattr(model_args, "target_modules", "all-linear"))
     return cfg
+
+
+def lora_targets(target_modules) -> Optional[tuple]:
+    """peft-style ``target_modules`` ("all-linear" or names such as ``q_proj``, ``up_proj``; the reference passes them
+    to peft, siirl/engine/fsdp_workers.py:516,890) -> the fused projections that get an adapter.  q / k / v share one
+    fused projection here, as do gate / up: naming any member adapts the fused matrix.  ``None``: all four."""
+    if target_modules is None or target_modules == "all-linear":
+        return None
+    names = [target_modules] if isinstance(target_modules, str) else list(target_modules)
+    names = [n.strip(" []'\"") for s_ in names for n in str(s_).split(",")]     # also a list that arrived as text
+    names = [n for n in names if n]
+    if names == ["all-linear"]:
+        return None
+    fused = {"q_proj": "qkv_proj", "k_proj": "qkv_proj", "v_proj": "qkv_proj", "qkv_proj": "qkv_proj",
+             "o_proj": "o_proj", "gate_proj": "gate_up_proj", "up_proj": "gate_up_proj",
+             "gate_up_proj": "gate_up_proj", "down_proj": "down_proj"}
+    unknown = [n for n in names if n not in fused]
+    if unknown:
+        raise ValueError(f"model.target_modules: unknown projection(s) {unknown} (known: {sorted(fused)} or 'all-linear')")
+    out = tuple(k for k in ("qkv_proj", "o_proj", "gate_up_proj", "down_proj") if k in {fused[n] for n in names})
+    return out or None
 
 
 def _micro_batches(batch: Batch, micro_bs: Optional[int], use_dynamic: bool, max_tokens: int, group=None):

@@ -125,6 +125,8 @@ class DecoderConfig:
     # LoRA adapters on the four projections of every layer (0: none); runtime option, not part of the HF config
     lora_rank: int = 0
     lora_alpha: float = 16.0
+    # fused projections that carry an adapter: subset of ("qkv_proj", "o_proj", "gate_up_proj", "down_proj")
+    lora_targets: Optional[tuple] = None
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
     # shared expert (Qwen2-MoE, DeepSeek-style): a dense SwiGLU MLP every token passes through, added to the routed

@@ -115,12 +115,14 @@ class DecoderLayer(nn.Module):
             for name, (n_out, n_in) in {"qkv_proj": (cfg.qkv_width, H), "o_proj": (H, cfg.q_width),
                                         "gate_up_proj": (2 * cfg.intermediate_size, H),
                                         "down_proj": (H, cfg.intermediate_size)}.items():
+                if cfg.lora_targets is not None and name not in cfg.lora_targets:
+                    continue
                 setattr(self, f"{name}_lora_A", _param((r, n_in), dtype, device, 1.0 / r, gen))
                 setattr(self, f"{name}_lora_B", _param((n_out, r), dtype, device, 0, gen))
 
     def _linear(self, x: torch.Tensor, name: str, bias=None) -> torch.Tensor:
         y = ops.linear(x, getattr(self, f"{name}_weight"), bias)
-        if self.cfg.lora_rank > 0 and self.lora_enabled:
+        if self.cfg.lora_rank > 0 and self.lora_enabled and hasattr(self, f"{name}_lora_A"):
             a = ops.linear(x, getattr(self, f"{name}_lora_A"))
             y = y + ops.linear(a, getattr(self, f"{name}_lora_B")) * (self.cfg.lora_alpha / self.cfg.lora_rank)
         return y

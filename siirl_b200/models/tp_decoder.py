@@ -94,14 +94,15 @@ class TPDecoder:
 
             def fold(layer, name, row_idx=None, col_idx=None):
                 W = getattr(layer, f"{name}_weight").detach()
+                if not hasattr(layer, f"{name}_lora_A") or not getattr(layer, "lora_enabled", True):
+                    W = W.index_select(0, row_idx) if row_idx is not None else W
+                    return (W.index_select(1, col_idx) if col_idx is not None else W).contiguous()
                 A = getattr(layer, f"{name}_lora_A").detach().float()
                 B = getattr(layer, f"{name}_lora_B").detach().float()
                 if row_idx is not None:
                     W, B = W.index_select(0, row_idx), B.index_select(0, row_idx)
                 if col_idx is not None:
                     W, A = W.index_select(1, col_idx), A.index_select(1, col_idx)
-                if not getattr(layer, "lora_enabled", True):
-                    return W.contiguous()
                 return (W.float() + sc * (B @ A)).to(W.dtype)
 
             self.layers = []

@@ -123,7 +123,7 @@ class ModelArguments(ProcessorArguments):
     rm_tokenizer: Optional[str] = None
     lora_rank: int = 0
     lora_alpha: float = 16
-    target_modules: str = "all-linear"
+    target_modules: Any = "all-linear"      # "all-linear" or a list of projection names (q_proj, up_proj, ...)
     use_shm: bool = False
     enable_activation_offload: bool = False
     model_type: str = "llm"

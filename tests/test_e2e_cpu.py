@@ -149,6 +149,20 @@ def test_ulysses_and_tensor_parallel_rollout_two_ranks(tmp_path):
 
 @pytest.mark.parametrize("rollout_tp", [1, 2])
 def test_lora_adapters_train_against_the_frozen_base(tmp_path, rollout_tp):
+    _lora_run(tmp_path, rollout_tp, [])
+
+
+def test_lora_target_modules_select_the_adapted_projections(tmp_path):
+    """peft-style ``target_modules``: adapters on the attention projections only."""
+    _lora_run(tmp_path, 1, ["actor_rollout_ref.model.target_modules=[q_proj,v_proj,o_proj]"])
+    from siirl_b200.engine.workers import lora_targets
+    assert lora_targets("all-linear") is None and lora_targets(["q_proj", "v_proj", "o_proj"]) == ("qkv_proj", "o_proj")
+    assert lora_targets("up_proj") == ("gate_up_proj",)
+    with pytest.raises(ValueError):
+        lora_targets(["lm_head"])
+
+
+def _lora_run(tmp_path, rollout_tp, more):
     """LoRA: only the adapters are in the optimizer store; the reference policy is the same model with the
     adapters switched off, so the KL term starts at zero and becomes positive once the adapters move.  With
     ``rollout_tp=2`` two ranks decode as one tensor-parallel engine whose weight slices have the adapters folded in."""
@@ -156,7 +170,7 @@ def test_lora_adapters_train_against_the_frozen_base(tmp_path, rollout_tp):
                 "actor_rollout_ref.actor.optim.lr=1e-3", f"trainer.n_gpus_per_node={rollout_tp}",
                 f"actor_rollout_ref.rollout.tensor_model_parallel_size={rollout_tp}",
                 f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=3",
-                "trainer.save_freq=-1"], tmp_path / "log")
+                "trainer.save_freq=-1", *more], tmp_path / "log")
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     m = _metrics(tmp_path / "log")
     assert [r["step"] for r in m] == [1, 2, 3]
