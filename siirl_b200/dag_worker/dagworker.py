@@ -106,7 +106,8 @@ class DAGWorker:
             tok_path = self.config.data.tokenizer or self.config.actor_rollout_ref.model.path
             vocab = self._vocab_size_hint()
             self.tokenizer = load_tokenizer(tok_path if not self.config.actor_rollout_ref.model.arch_preset else None,
-                                            vocab_size=vocab)
+                                            vocab_size=vocab, model_args=self.config.actor_rollout_ref.model)
+        self._import_external_libs()
         self._setup_dataloader()
         self._setup_reward_managers()
         self._bind_default_executables()
@@ -614,6 +615,19 @@ class DAGWorker:
                     os._exit(int(f.get("code", 17)))
                 if kind == "sleep":
                     time.sleep(float(f.get("seconds", 5.0)))
+
+    def _import_external_libs(self) -> None:
+        """``model.external_lib``: modules to import before models and rewards are built, so that user code can
+        register architecture presets, reward scorers or pipelines (reference: ``import_external_libs``,
+        siirl/utils/extras/import_utils.py, called from the workers' ``init_model``)."""
+        import importlib
+        libs = self.config.actor_rollout_ref.model.external_lib
+        if not libs:
+            return
+        for name in ([libs] if isinstance(libs, str) else list(libs)):
+            for mod in str(name).split(","):
+                if mod.strip():
+                    importlib.import_module(mod.strip())
 
     def _start_metric_worker(self) -> None:
         """``trainer.async_metrics``: a collector thread on rank 0 merges the ranks' step metrics out of band."""

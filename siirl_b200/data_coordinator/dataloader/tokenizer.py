@@ -53,14 +53,34 @@ class SyntheticTokenizer:
         return self.vocab_size
 
 
-def load_tokenizer(path: Optional[str], vocab_size: int = 1024, trust_remote_code: bool = False):
-    """HF tokenizer from ``path`` when it is a directory with tokenizer files, else the synthetic tokenizer."""
+def load_tokenizer(path: Optional[str], vocab_size: int = 1024, trust_remote_code: bool = False, model_args=None):
+    """HF tokenizer from ``path`` when it is a directory with tokenizer files, else the synthetic tokenizer.
+    ``model_args`` (the ``actor_rollout_ref.model`` group) supplies the loader options of the reference
+    (siirl/models/loader.py): ``use_fast_tokenizer``, ``split_special_tokens``, ``new_special_tokens`` (comma
+    separated; they must fit the model's vocabulary unless ``resize_vocab`` is set, which this framework does not
+    do: the embedding matrix belongs to the checkpoint)."""
     if path:
         p = os.path.expanduser(path)
         if os.path.isdir(p) and any(os.path.exists(os.path.join(p, f)) for f in
                                     ("tokenizer.json", "tokenizer_config.json", "tokenizer.model", "vocab.json")):
             from transformers import AutoTokenizer
-            tok = AutoTokenizer.from_pretrained(p, trust_remote_code=trust_remote_code)
+            kw = {}
+            if model_args is not None:
+                kw["use_fast"] = bool(getattr(model_args, "use_fast_tokenizer", True))
+                if getattr(model_args, "split_special_tokens", False):
+                    kw["split_special_tokens"] = True
+                trust_remote_code = trust_remote_code or bool(getattr(model_args, "trust_remote_code", False))
+            tok = AutoTokenizer.from_pretrained(p, trust_remote_code=trust_remote_code, **kw)
+            new = getattr(model_args, "new_special_tokens", None) if model_args is not None else None
+            if new:
+                names = [t.strip() for t in (new.split(",") if isinstance(new, str) else list(new)) if str(t).strip()]
+                added = tok.add_special_tokens({"additional_special_tokens": names}, replace_additional_special_tokens=False)
+                if added and len(tok) > vocab_size and not getattr(model_args, "resize_vocab", False):
+                    raise ValueError(f"model.new_special_tokens adds {added} token(s) beyond the model's vocabulary of "
+                                     f"{vocab_size}: the embedding matrix is not resized")
+                if added and len(tok) > vocab_size:
+                    raise NotImplementedError("model.resize_vocab: growing the embedding matrix is not supported; "
+                                              "use tokens inside the checkpoint's vocabulary")
             if tok.pad_token_id is None:
                 tok.pad_token = tok.eos_token
             return tok

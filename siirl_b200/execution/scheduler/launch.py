@@ -59,6 +59,9 @@ def _warn_unsupported_keys(config) -> None:
 
 def validate_config(config, world_size: Optional[int] = None) -> None:
     t = config.trainer
+    if int(getattr(config.actor_rollout_ref.actor.megatron, "expert_tensor_parallel_size", 1) or 1) > 1:
+        raise ValueError("megatron.expert_tensor_parallel_size > 1 is not supported: experts are whole on one rank "
+                         "(expert_model_parallel_size spreads them over the group)")
     world = world_size or t.nnodes * t.n_gpus_per_node
     a, r, rf, c = (config.actor_rollout_ref.actor, config.actor_rollout_ref.rollout, config.actor_rollout_ref.ref,
                    config.critic)

@@ -162,3 +162,31 @@ def test_memory_helpers_on_cpu():
     assert set(rep) == {"allocated_gib", "reserved_gib", "max_allocated_gib", "free_gib", "total_gib"}
     assert release_memory() >= 0.0
     reset_peak_stats()
+
+
+def test_external_lib_is_imported_before_models_are_built(tmp_path, monkeypatch):
+    """``model.external_lib`` names modules to import (they register presets / scorers as a side effect)."""
+    import sys
+    import types
+
+    from siirl_b200.dag_worker.dagworker import DAGWorker
+    (tmp_path / "my_ext_lib.py").write_text("LOADED = True\n")
+    monkeypatch.syspath_prepend(str(tmp_path))
+    w = types.SimpleNamespace(config=types.SimpleNamespace(actor_rollout_ref=types.SimpleNamespace(
+        model=types.SimpleNamespace(external_lib="my_ext_lib"))))
+    DAGWorker._import_external_libs(w)
+    assert sys.modules["my_ext_lib"].LOADED
+    w.config.actor_rollout_ref.model.external_lib = "no_such_module_xyz"
+    import pytest
+    with pytest.raises(ModuleNotFoundError):
+        DAGWorker._import_external_libs(w)
+
+
+def test_expert_tensor_parallel_is_refused():
+    import pytest
+
+    from siirl_b200.execution.scheduler.launch import validate_config
+    from siirl_b200.params import parse_config
+    cfg = parse_config(["actor_rollout_ref.actor.megatron.expert_tensor_parallel_size=2", "trainer.n_gpus_per_node=1"])
+    with pytest.raises(ValueError, match="expert_tensor_parallel_size"):
+        validate_config(cfg, 1)
