@@ -4,11 +4,17 @@ Contract of the reference node (siirl/data_coordinator/dataloader/data_loader_no
 data-parallel width is ``group_world_size / rollout_tp``; each data-parallel rank draws
 ``train_batch_size // ddp_world`` prompts per step from its own partition with a seeded shuffle; TP peers of one
 data-parallel rank see identical batches; ``auto_repeat`` wraps small datasets; ``state_dict`` /
-``load_state_dict`` make resume continue with the next unseen batch."""
+``load_state_dict`` make resume continue with the next unseen batch.
+
+``data.num_loader_workers > 0`` (the reference hands that number to ``torch.utils.data.DataLoader``): the next
+training batch is tokenised / image-processed by a pool of threads while the current step runs on the GPU, one batch
+ahead.  The checkpointed position only moves when a batch is handed out, so a prefetched batch that was never used is
+drawn again after a resume."""
 from __future__ import annotations
 
 import random
-from typing import Any, Dict, Optional
+from concurrent.futures import Future, ThreadPoolExecutor
+from typing import Any, Dict, List, Optional, Tuple
 
 from ..protocol import Batch
 from .partitioned_dataset import PartitionedRLHFDataset, collate_fn
@@ -47,6 +53,9 @@ class DataLoaderNode:
         self.num_val_batches = 0 if self.val_dataset is None else max(
             1, (len(self.val_dataset) + self.val_batch_size - 1) // self.val_batch_size)
         self._val_cursor = 0
+        workers = int(getattr(data, "num_loader_workers", 0) or 0)
+        self._pool = ThreadPoolExecutor(max_workers=workers, thread_name_prefix="loader") if workers > 0 else None
+        self._ahead: Optional[Tuple[Future, int, int]] = None      # (batch being built, epoch and cursor after it)
 
     @property
     def val_batch_size(self) -> int:
@@ -60,17 +69,44 @@ class DataLoaderNode:
             random.Random(self.seed * 1000003 + epoch).shuffle(idx)
         return idx
 
-    def _next_indices(self):
-        out = []
+    def _plan(self, epoch: int, cursor: int) -> Tuple[List[int], int, int]:
+        """Indices of the batch that starts at ``(epoch, cursor)`` and the position after it."""
+        out: List[int] = []
+        order = self._order if epoch == self.epoch else self._make_order(epoch)
         while len(out) < self.batch_size:
-            if self.cursor >= len(self._order):
-                self.epoch += 1
-                self.cursor = 0
-                self._order = self._make_order(self.epoch)
-            take = min(self.batch_size - len(out), len(self._order) - self.cursor)
-            out.extend(self._order[self.cursor:self.cursor + take])
-            self.cursor += take
+            if cursor >= len(order):
+                epoch, cursor = epoch + 1, 0
+                order = self._make_order(epoch)
+            take = min(self.batch_size - len(out), len(order) - cursor)
+            out.extend(order[cursor:cursor + take])
+            cursor += take
+        return out, epoch, cursor
+
+    def _advance(self, epoch: int, cursor: int) -> None:
+        if epoch != self.epoch:
+            self._order = self._make_order(epoch)
+        self.epoch, self.cursor = epoch, cursor
+
+    def _next_indices(self):
+        out, epoch, cursor = self._plan(self.epoch, self.cursor)
+        self._advance(epoch, cursor)
         return out
+
+    def _build(self, indices: List[int]) -> Batch:
+        items = list(self._pool.map(self.train_dataset.__getitem__, indices)) if self._pool is not None else \
+            [self.train_dataset[i] for i in indices]
+        return collate_fn(items)
+
+    def _prefetch(self) -> None:
+        indices, epoch, cursor = self._plan(self.epoch, self.cursor)
+        workers = self._pool._max_workers
+
+        def build() -> Batch:
+            # the task itself holds one thread of the pool; the items go to the others
+            if workers >= 2:
+                return collate_fn(list(self._pool.map(self.train_dataset.__getitem__, indices)))
+            return collate_fn([self.train_dataset[i] for i in indices])
+        self._ahead = (self._pool.submit(build), epoch, cursor)
 
     def run(self, epoch: Optional[int] = None, is_validation_step: bool = False, **_) -> Batch:
         """Next training batch (or the next validation batch)."""
@@ -82,7 +118,16 @@ class DataLoaderNode:
             e = min(s + self.val_batch_size, n)
             self._val_cursor = 0 if e >= n else e
             return collate_fn([self.val_dataset[i] for i in range(s, e)])
-        return collate_fn([self.train_dataset[i] for i in self._next_indices()])
+        if self._pool is None:
+            return collate_fn([self.train_dataset[i] for i in self._next_indices()])
+        if self._ahead is None:                       # first batch (or first after a resume): build it now, in parallel
+            batch = self._build(self._next_indices())
+        else:
+            fut, epoch, cursor = self._ahead
+            batch = fut.result()
+            self._advance(epoch, cursor)
+        self._prefetch()
+        return batch
 
     def state_dict(self) -> Dict[str, Any]:
         return {"epoch": self.epoch, "cursor": self.cursor, "seed": self.seed, "batch_size": self.batch_size}
@@ -92,3 +137,4 @@ class DataLoaderNode:
         self.epoch = int(state["epoch"])
         self.cursor = int(state["cursor"])
         self._order = self._make_order(self.epoch)
+        self._ahead = None                            # whatever was being prefetched belonged to the old position

@@ -190,3 +190,29 @@ def test_expert_tensor_parallel_is_refused():
     cfg = parse_config(["actor_rollout_ref.actor.megatron.expert_tensor_parallel_size=2", "trainer.n_gpus_per_node=1"])
     with pytest.raises(ValueError, match="expert_tensor_parallel_size"):
         validate_config(cfg, 1)
+
+
+def test_dataloader_prefetch_keeps_order_and_resume_position():
+    """One batch is prepared ahead by the loader threads; the sequence of batches and the checkpointed position are
+    those of the synchronous loader (a prefetched, unused batch is drawn again after a resume)."""
+    import torch
+
+    from siirl_b200.data_coordinator.dataloader import DataLoaderNode, load_tokenizer
+    from siirl_b200.params import parse_config
+    args = ["data.synthetic=arith", "data.synthetic_size=40", "data.train_batch_size=6", "data.max_prompt_length=16",
+            "actor_rollout_ref.model.arch_preset=tiny", "trainer.n_gpus_per_node=1"]
+    tok = load_tokenizer(None, 1024)
+    sync = DataLoaderNode(parse_config(args + ["data.num_loader_workers=0"]), tok, None, 1, 0, 1)
+    pre = DataLoaderNode(parse_config(args + ["data.num_loader_workers=3"]), tok, None, 1, 0, 1)
+    assert sync._pool is None and pre._pool is not None
+    want = [sync.run()["input_ids"] for _ in range(9)]            # crosses an epoch boundary (40 / 6)
+    got = []
+    for k in range(4):
+        got.append(pre.run()["input_ids"])
+    state = pre.state_dict()
+    assert state == {"epoch": 0, "cursor": 24, "seed": pre.seed, "batch_size": 6} and pre._ahead is not None
+    resumed = DataLoaderNode(parse_config(args + ["data.num_loader_workers=3"]), tok, None, 1, 0, 1)
+    resumed.load_state_dict(state)
+    for k in range(5):
+        got.append(resumed.run()["input_ids"])
+    assert all(torch.equal(a, b) for a, b in zip(want, got))
