@@ -398,7 +398,7 @@ class DAGWorker:
         (reference: dagworker generate -> AgentLoopManager, siirl/execution/rollout_flow/multiturn/agent_loop)."""
         import time as _time
         if getattr(self, "_agent_loops", None) is None:
-            from ..engine.rollout.async_server import AsyncRolloutServer
+            from ..engine.rollout.async_server import make_async_server
             from ..execution.rollout_flow.multiturn.agent_loop.agent_loop import AgentLoopManager
             from ..execution.rollout_flow.multiturn.tools.tool_registry import initialize_tools_from_config
             mt = self.config.actor_rollout_ref.rollout.multi_turn
@@ -407,7 +407,7 @@ class DAGWorker:
             if mt.interaction_config_path:
                 from ..execution.rollout_flow.multiturn.interactions.base import initialize_interactions_from_config
                 interactions = initialize_interactions_from_config(mt.interaction_config_path)
-            server = AsyncRolloutServer(worker.engine, self.tokenizer)
+            server = make_async_server(worker.engine, self.tokenizer, self.config.actor_rollout_ref.rollout.agent)
             self._agent_loops = AgentLoopManager(self.config, [server], self.tokenizer, tools, interactions)
         t0 = _time.time()
         worker._full_weights(True)

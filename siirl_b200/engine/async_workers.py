@@ -7,14 +7,15 @@ from __future__ import annotations
 import asyncio
 from typing import Any, Dict, List
 
-from .rollout.async_server import AsyncRolloutServer
+from .rollout.async_server import make_async_server
 from .workers import ActorRolloutRefWorker
 
 
 class AsyncActorRolloutRefWorker(ActorRolloutRefWorker):
     def init_model(self) -> None:
         super().init_model()
-        self.server = AsyncRolloutServer(self.engine, self.tokenizer) if self.engine is not None else None
+        self.server = make_async_server(self.engine, self.tokenizer, getattr(self.config.rollout, "agent", None)) \
+            if self.engine is not None else None
 
     async def generate(self, request_id: str, prompt_ids: List[int], sampling_params: Dict[str, Any]) -> Dict[str, Any]:
         return await self.server.generate(request_id, prompt_ids, sampling_params)

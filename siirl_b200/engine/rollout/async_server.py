@@ -105,3 +105,33 @@ class AsyncRolloutServer:
                 "choices": [choice],
                 "usage": {"prompt_tokens": len(ids), "completion_tokens": len(out["token_ids"]),
                           "total_tokens": len(ids) + len(out["token_ids"])}}
+
+
+def make_async_server(engine, tokenizer, agent_cfg=None):
+    """The server agent loops talk to: :class:`AsyncRolloutServer`, or the class named by
+    ``rollout.agent.custom_async_server`` (``path``: a module name or a ``.py`` file, ``name``: the class; the
+    reference loads a custom rollout back end the same way, agent_loop.py:323-328).  A custom class is constructed as
+    ``cls(engine, tokenizer)`` and has to offer ``generate`` / ``wake_up`` / ``sleep`` like the default one."""
+    custom = getattr(agent_cfg, "custom_async_server", None) if agent_cfg is not None else None
+    path, name = (getattr(custom, "path", None), getattr(custom, "name", None)) if custom is not None else (None, None)
+    if not path or not name:
+        return AsyncRolloutServer(engine, tokenizer)
+    import importlib
+    import importlib.util
+    import os
+    if str(path).endswith(".py") or os.path.sep in str(path):
+        spec = importlib.util.spec_from_file_location("siirl_custom_async_server", os.path.expanduser(str(path)))
+        if spec is None or spec.loader is None:
+            raise ImportError(f"rollout.agent.custom_async_server.path={path!r} is not a loadable Python file")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+    else:
+        mod = importlib.import_module(str(path))
+    cls = getattr(mod, name, None)
+    if cls is None:
+        raise AttributeError(f"{path}: no class {name!r} (rollout.agent.custom_async_server.name)")
+    server = cls(engine, tokenizer)
+    for need in ("generate", "wake_up", "sleep"):
+        if not callable(getattr(server, need, None)):
+            raise TypeError(f"custom async server {name} lacks the method {need}()")
+    return server

@@ -216,3 +216,26 @@ def test_dataloader_prefetch_keeps_order_and_resume_position():
     for k in range(5):
         got.append(resumed.run()["input_ids"])
     assert all(torch.equal(a, b) for a, b in zip(want, got))
+
+
+def test_custom_async_server_is_loaded_from_a_file(tmp_path):
+    import types
+
+    import pytest
+
+    from siirl_b200.engine.rollout.async_server import AsyncRolloutServer, make_async_server
+    assert isinstance(make_async_server("engine", None, None), AsyncRolloutServer)
+    f = tmp_path / "my_server.py"
+    f.write_text("class Mine:\n    def __init__(self, engine, tokenizer):\n        self.engine = engine\n"
+                 "    async def generate(self, *a, **k):\n        return {}\n"
+                 "    async def wake_up(self):\n        pass\n    async def sleep(self):\n        pass\n"
+                 "class Broken:\n    def __init__(self, engine, tokenizer):\n        pass\n")
+    agent = types.SimpleNamespace(custom_async_server=types.SimpleNamespace(path=str(f), name="Mine"))
+    s = make_async_server("the-engine", None, agent)
+    assert type(s).__name__ == "Mine" and s.engine == "the-engine"
+    agent.custom_async_server.name = "Broken"
+    with pytest.raises(TypeError, match="generate"):
+        make_async_server("e", None, agent)
+    agent.custom_async_server.name = "Missing"
+    with pytest.raises(AttributeError):
+        make_async_server("e", None, agent)
