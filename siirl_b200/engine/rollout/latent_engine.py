@@ -32,13 +32,21 @@ from .native_engine import RolloutOutput, SamplingParams
 
 class LatentCacheEngine:
     def __init__(self, model, max_num_seqs: int = 64, max_model_len: int = 8192, max_num_batched_tokens: int = 16384,
-                 **_unused):
+                 lockstep_group=None, **_unused):
+        """``lockstep_group``: ranks whose forward passes contain collectives over DIFFERENT requests (expert
+        parallelism: every mixture-of-experts layer exchanges tokens with the group).  Those ranks must run the same
+        number of forward passes, so generation proceeds in rounds: a rank that has a prefill pass or a decoding
+        step left runs it, a rank that has finished runs a one-token pass, until no rank has work."""
         cfg = model.cfg
         assert cfg.is_mla, "the latent-cache engine serves multi-head latent attention models"
         self.model = model
         self.max_num_seqs = int(max_num_seqs)
         self.max_model_len = int(max_model_len)
         self.max_num_batched_tokens = max(1, int(max_num_batched_tokens or 16384))   # prompt tokens per prefill pass
+        self.lockstep_group = lockstep_group
+        bound = int(getattr(model.layers[-1], "ep_pad_tokens", 0) or 0) if len(model.layers) else 0
+        if lockstep_group is not None and bound:
+            self.max_num_batched_tokens = min(self.max_num_batched_tokens, bound)    # the exchange buffers' row bound
         self.device = model.embed_tokens.device
         self.width = cfg.kv_lora_rank + cfg.qk_rope_head_dim
         self.cache: Optional[torch.Tensor] = None
@@ -151,9 +159,41 @@ class LatentCacheEngine:
         asleep = self.cache is None
         if asleep:
             self.wake_up()
+        out: List[RolloutOutput] = []
+        self._drive(self._work(prompts, sp, mm_inputs, out))
+        if asleep:
+            self.sleep()
+        out.sort(key=lambda o: (o.prompt_index, o.sample_index))
+        return out
+
+    def _drive(self, work) -> None:
+        """Run the forward passes ``work`` asks for (it yields callables and receives their results).  With a
+        lock-step group every rank runs one pass per round, an idle one-token pass once its own work is done."""
+        result, finished = None, False
+        while True:
+            job = None
+            if not finished:
+                try:
+                    job = work.send(result)
+                except StopIteration:
+                    finished = True
+            if self.lockstep_group is not None:
+                import torch.distributed as dist
+                flag = torch.tensor([0.0 if finished else 1.0], device=self.device)
+                dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.lockstep_group)
+                if float(flag.item()) == 0.0:
+                    return
+            elif finished:
+                return
+            if job is not None:
+                result = job()
+            else:
+                pad = self.model.cfg.pad_token_id or 0
+                self._prefill([[pad]], [0], None)
+
+    def _work(self, prompts, sp: SamplingParams, mm_inputs, out: List[RolloutOutput]):
         dev = self.device
         gen = torch.Generator(device="cpu").manual_seed(sp.seed) if dev.type == "cpu" else None
-        out: List[RolloutOutput] = []
         n = max(1, sp.n)
         per_wave = max(1, self.max_num_seqs // n)                 # prompts per wave: all samples of a prompt together
         for w0 in range(0, len(prompts), per_wave):
@@ -167,7 +207,9 @@ class LatentCacheEngine:
                 while g1 < P and (g1 == g0 or toks + len(wave[g1]) <= self.max_num_batched_tokens):
                     toks += len(wave[g1])
                     g1 += 1
-                parts.append(self._prefill(wave[g0:g1], first_slots[g0:g1], mms[g0:g1] if mms is not None else None))
+                a, b = g0, g1
+                parts.append((yield lambda: self._prefill(wave[a:b], first_slots[a:b],
+                                                          mms[a:b] if mms is not None else None)))
                 g0 = g1
             hidden = torch.cat(parts)
             plen = [len(p) for p in wave]
@@ -204,12 +246,9 @@ class LatentCacheEngine:
                 for b in live:
                     lens[b] += 1
                 kidx = torch.tensor(keep, device=dev)
-                hidden = self._decode(tok.to(dev).index_select(0, kidx), torch.tensor(live, device=dev),
-                                      torch.tensor([lens[b] for b in live], device=dev))
+                step_tok, step_slots = tok.to(dev).index_select(0, kidx), torch.tensor(live, device=dev)
+                step_lens = torch.tensor([lens[b] for b in live], device=dev)
+                hidden = yield lambda: self._decode(step_tok, step_slots, step_lens)
                 self.stats["decode_steps"] = self.stats.get("decode_steps", 0) + 1
             for b in range(B):
                 out.append(RolloutOutput(w0 + b // n, b % n, new[b], lps[b], done[b] or "length"))
-        if asleep:
-            self.sleep()
-        out.sort(key=lambda o: (o.prompt_index, o.sample_index))
-        return out

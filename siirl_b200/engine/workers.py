@@ -694,11 +694,13 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                 if tp > 1:
                     raise ValueError("this rollout engine runs on whole weights: set "
                                      "rollout.tensor_model_parallel_size=1")
-                if str(r.name).lower() != "hf" and getattr(self, "ep_ctx", None) is None:
+                if str(r.name).lower() != "hf":
                     from .rollout.latent_engine import LatentCacheEngine
+                    ep = getattr(self, "ep_ctx", None) is not None and self.world > 1
                     self.engine = LatentCacheEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024),
                                                     max_model_len=max_len,
-                                                    max_num_batched_tokens=r.max_num_batched_tokens)
+                                                    max_num_batched_tokens=r.max_num_batched_tokens,
+                                                    lockstep_group=self.group if ep else None)
                 else:
                     from .rollout.recompute_engine import RecomputeEngine
                     self.engine = RecomputeEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024),

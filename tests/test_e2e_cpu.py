@@ -116,10 +116,13 @@ def test_injected_rank_failure_stops_the_job(tmp_path):
     assert not (tmp_path / "c" / "latest_checkpointed_iteration.txt").exists()
 
 
-def test_moe_expert_parallel_two_ranks(tmp_path):
+@pytest.mark.parametrize("preset", ["tiny-moe", "tiny-deepseek-v3"])
+def test_moe_expert_parallel_two_ranks(tmp_path, preset):
     """Qwen3-MoE-style tiny model, experts split over two gloo ranks: dispatch / combine across ranks in training,
-    scoring and the lock-step rollout; the dense part in the sharded-state store, the experts in a rank-local one."""
-    out = _run(["actor_rollout_ref.model.arch_preset=tiny-moe", "actor_rollout_ref.model.ep_max_tokens=512",
+    scoring and the lock-step rollout; the dense part in the sharded-state store, the experts in a rank-local one.
+    ``tiny-deepseek-v3``: the same with multi-head latent attention, whose rollout is the latent-cache engine running
+    in lock-step rounds (responses stop at EOS at different lengths on the two ranks)."""
+    out = _run([f"actor_rollout_ref.model.arch_preset={preset}", "actor_rollout_ref.model.ep_max_tokens=512",
                 "actor_rollout_ref.actor.megatron.expert_model_parallel_size=2", "data.max_response_length=16",
                 "actor_rollout_ref.rollout.n=2", "actor_rollout_ref.rollout.max_num_seqs=16",
                 "actor_rollout_ref.actor.use_kl_loss=False", f"trainer.default_local_dir={tmp_path / 'c'}",
