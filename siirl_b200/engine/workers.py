@@ -703,6 +703,10 @@ class ActorRolloutRefWorker(_ModelWorkerBase):
                                                     lockstep_group=self.group if ep else None)
                 else:
                     from .rollout.recompute_engine import RecomputeEngine
+                    if getattr(self, "ep_ctx", None) is not None and self.world > 1:
+                        raise ValueError("rollout.name=hf cannot run under expert parallelism: its ranks would run "
+                                         "different numbers of forward passes around the experts' exchanges; use "
+                                         "the default engine")
                     self.engine = RecomputeEngine(self.model, max_num_seqs=min(r.max_num_seqs, 1024),
                                                   max_model_len=max_len)
             else:
