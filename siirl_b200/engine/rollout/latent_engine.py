@@ -71,8 +71,8 @@ class LatentCacheEngine:
 
     # ---- model pieces --------------------------------------------------------------------------------------------------
     def _rope(self, positions: torch.Tensor):
-        pmax = int(positions.max().item()) + 1 if positions.numel() else 1
-        return self.model.rope_tables(self.device, pmax)
+        # tables for the engine's whole context length: no device read-back of the largest position per pass
+        return self.model.rope_tables(self.device, self.max_model_len)
 
     def _absorbed(self, layer):
         """``kv_b_proj`` as ``W_uk [nh, nope, R]`` and ``W_uv [nh, v, R]`` (views of the parameter)."""
@@ -119,14 +119,17 @@ class LatentCacheEngine:
         return out.index_select(0, last)
 
     @torch.no_grad()
-    def _decode(self, tokens: torch.Tensor, slots: torch.Tensor, lens: torch.Tensor) -> torch.Tensor:
-        """One token per running sequence: ``tokens [B]`` sit at cache positions ``lens - 1``.  Returns hidden ``[B, H]``."""
+    def _decode(self, tokens: torch.Tensor, slots: torch.Tensor, lens: torch.Tensor, lmax: Optional[int] = None,
+                dense_slots: bool = False) -> torch.Tensor:
+        """One token per running sequence: ``tokens [B]`` sit at cache positions ``lens - 1``.  Returns hidden
+        ``[B, H]``.  ``lmax``: the largest entry of ``lens`` when the caller knows it on the host; ``dense_slots``:
+        ``slots`` is ``0 .. B-1`` (every sequence of the wave still runs), so the cache is read in place."""
         m, cfg = self.model, self.model.cfg
         B = tokens.shape[0]
         nh, dn, dr, dv, R = cfg.num_heads, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         positions = lens - 1
         rope = self._rope(positions)
-        Lmax = int(lens.max().item())
+        Lmax = int(lmax) if lmax is not None else int(lens.max().item())
         dead = torch.arange(Lmax, device=self.device)[None, :] >= lens[:, None]          # [B, Lmax]
         h = m.embed(tokens)
         delta = None
@@ -135,7 +138,8 @@ class LatentCacheEngine:
                                residual=h if delta is not None else None)
             q, cn, k_pe = layer.mla_latent(x, positions, rope)
             self.cache[li, slots, positions] = torch.cat([cn, k_pe], -1)
-            lat = self.cache[li, :, :Lmax].index_select(0, slots)                       # [B, Lmax, R + dr]
+            lat = self.cache[li, :B, :Lmax] if dense_slots else \
+                self.cache[li, :, :Lmax].index_select(0, slots)                           # [B, Lmax, R + dr]
             w_uk, w_uv = self._absorbed(layer)
             q_abs = torch.einsum("bhd,hdr->bhr", q[:, :, :dn], w_uk)                     # [B, nh, R]
             qq = torch.cat([q_abs, q[:, :, dn:]], -1)                                    # one 576-wide query per head
@@ -247,8 +251,9 @@ class LatentCacheEngine:
                     lens[b] += 1
                 kidx = torch.tensor(keep, device=dev)
                 step_tok, step_slots = tok.to(dev).index_select(0, kidx), torch.tensor(live, device=dev)
-                step_lens = torch.tensor([lens[b] for b in live], device=dev)
-                hidden = yield lambda: self._decode(step_tok, step_slots, step_lens)
+                host_lens = [lens[b] for b in live]
+                step_lens, step_max, dense = torch.tensor(host_lens, device=dev), max(host_lens), len(live) == B
+                hidden = yield lambda: self._decode(step_tok, step_slots, step_lens, step_max, dense)
                 self.stats["decode_steps"] = self.stats.get("decode_steps", 0) + 1
             for b in range(B):
                 out.append(RolloutOutput(w0 + b // n, b % n, new[b], lps[b], done[b] or "length"))
