@@ -107,3 +107,94 @@ def test_validate_config_rules():
     with pytest.raises(ValueError):
         validate_config(parse_config(["data.train_batch_size=16", "trainer.n_gpus_per_node=4",
                                       "actor_rollout_ref.rollout.tensor_model_parallel_size=3"]))
+
+
+def _simulate_pipeline(P, M, V):
+    """Run every stage's order against blocking receives and asynchronous, order-matched sends (the transport of
+    ``parallel/pipeline.py``): returns the number of executed passes; raises on a deadlock or when the k-th receive
+    on a link would not get the k-th message sent on it."""
+    from siirl_b200.parallel.pipeline import schedule_interleaved
+    orders = [schedule_interleaved(s, P, M, V) for s in range(P)]
+    at = [0] * P
+    sent = {}                                   # (kind, src, dst) -> list of message tags in sending order
+    taken = {}                                  # (kind, src, dst) -> number of messages received so far
+    total = sum(len(o) for o in orders)
+    done = 0
+    last_chunk = V - 1
+    while done < total:
+        progressed = False
+        for s in range(P):
+            while at[s] < len(orders[s]):
+                op, i, c = orders[s][at[s]]
+                if op == "F":
+                    first = s == 0 and c == 0
+                    if not first:
+                        src = (s - 1) % P
+                        link = ("F", src, s)
+                        k = taken.get(link, 0)
+                        if k >= len(sent.get(link, [])):
+                            break                                           # would block in recv
+                        want = (i, c if s > 0 else c - 1)
+                        assert sent[link][k] == want, f"stage {s}: forward recv {k} gets {sent[link][k]}, needs {want}"
+                        taken[link] = k + 1
+                    if not (s == P - 1 and c == last_chunk):
+                        sent.setdefault(("F", s, (s + 1) % P), []).append((i, c))
+                else:
+                    last = s == P - 1 and c == last_chunk
+                    if not last:
+                        src = (s + 1) % P
+                        link = ("B", src, s)
+                        k = taken.get(link, 0)
+                        if k >= len(sent.get(link, [])):
+                            break
+                        want = (i, c if s < P - 1 else c + 1)
+                        assert sent[link][k] == want, f"stage {s}: backward recv {k} gets {sent[link][k]}, needs {want}"
+                        taken[link] = k + 1
+                    if not (s == 0 and c == 0):
+                        sent.setdefault(("B", s, (s - 1) % P), []).append((i, c))
+                at[s] += 1
+                done += 1
+                progressed = True
+        assert progressed, f"deadlock at P={P} M={M} V={V}: positions {at}"
+    return done
+
+
+def test_pipeline_schedules_are_deadlock_free_and_order_matched():
+    """Every stage walks its own list; messages carry no tag, so the k-th receive on a link must be served by the
+    k-th send on it, and blocking receives must never wait on each other in a cycle."""
+    from siirl_b200.parallel.pipeline import schedule_interleaved
+    for P in (2, 3, 4, 5):
+        for V in (1, 2, 3):
+            for M in (1, P - 1, P, P + 1, 2 * P, 3 * P + 2):
+                if M < 1:
+                    continue
+                assert _simulate_pipeline(P, M, V) == 2 * P * M * V
+                for s in range(P):
+                    order = schedule_interleaved(s, P, M, V)
+                    seen = set()
+                    for op, i, c in order:                                   # a backward follows its own forward
+                        if op == "F":
+                            seen.add((i, c))
+                        else:
+                            assert (i, c) in seen
+
+
+def test_context_parallel_chunk_assignments_cover_and_balance():
+    """Both chunk assignments give every position to exactly one rank; under the zig-zag assignment every rank has
+    the same number of (query, visible key) pairs, under the contiguous one the last rank has the most."""
+    import torch
+
+    from siirl_b200.parallel.ring_attention import chunk_positions, split_for_context_parallel
+    for cp in (2, 3, 4):
+        L = 12 * cp
+        for zz in (False, True):
+            pos = [chunk_positions([L // cp], cp, r, zz) for r in range(cp)]
+            assert sorted(torch.cat(pos).tolist()) == list(range(L))
+            work = [int(sum(p + 1 for p in ps.tolist())) for ps in pos]       # keys visible to each causal query
+            if zz:
+                assert max(work) - min(work) == 0, work
+            else:
+                assert work == sorted(work) and work[-1] > work[0]
+            rows, p2, info = split_for_context_parallel([L, 2 * L], cp, 1, zigzag=zz)
+            assert info.seqlens == [L // cp, 2 * L // cp] and rows.numel() == 3 * L // cp
+            assert torch.equal(p2[: L // cp], pos[1])
