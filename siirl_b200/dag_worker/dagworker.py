@@ -652,6 +652,14 @@ class DAGWorker:
         self._start_metric_worker()
         try:
             self._training_loop_body()
+        except BaseException:
+            if getattr(self, "_metric_worker", None) is not None:
+                try:                                 # the loop failed: do not wait long for ranks that may be gone
+                    self._metric_worker.close(timeout_s=5.0)
+                except Exception:  # noqa: BLE001
+                    pass
+                self._metric_worker = None
+            raise
         finally:
             if getattr(self, "_metric_worker", None) is not None:
                 self._metric_worker.close()          # deliver what is outstanding to the loggers
