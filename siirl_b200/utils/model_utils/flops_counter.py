@@ -28,23 +28,42 @@ class FlopsCounter:
     def __init__(self, cfg: DecoderConfig):
         self.cfg = cfg
 
+    def _attention_params(self) -> int:
+        c = self.cfg
+        if c.is_mla:
+            nh, dn, dr, dv, R = c.num_heads, c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim, c.kv_lora_rank
+            q = c.hidden_size * c.q_lora_rank + c.q_lora_rank * nh * (dn + dr) if c.q_lora_rank > 0 else \
+                c.hidden_size * nh * (dn + dr)
+            return q + c.hidden_size * (R + dr) + R * nh * (dn + dv) + nh * dv * c.hidden_size
+        return c.hidden_size * c.qkv_width + c.q_width * c.hidden_size
+
+    def _mlp_params(self, layer: int) -> int:
+        """GEMM parameters one token touches in layer ``layer``'s MLP: a mixture-of-experts layer counts the router,
+        the active routed experts and the shared experts; the first ``first_k_dense_replace`` layers of the
+        DeepSeek-V3 family are dense."""
+        c = self.cfg
+        dense_first = int(getattr(c, "first_k_dense_replace", 0) or 0)
+        if c.is_moe and layer >= dense_first:
+            mlp = c.num_experts_per_tok * 3 * c.hidden_size * c.moe_intermediate_size + c.num_experts * c.hidden_size
+            return mlp + 3 * c.hidden_size * int(getattr(c, "shared_expert_intermediate_size", 0) or 0)
+        return 3 * c.hidden_size * c.intermediate_size
+
     def dense_params_per_token(self) -> int:
         """Parameters touched by one token in the GEMMs (MoE counts the active experts only)."""
         c = self.cfg
-        attn = c.hidden_size * c.qkv_width + c.q_width * c.hidden_size
-        if c.is_moe:
-            mlp = c.num_experts_per_tok * 3 * c.hidden_size * c.moe_intermediate_size + c.num_experts * c.hidden_size
-        else:
-            mlp = 3 * c.hidden_size * c.intermediate_size
         head = c.hidden_size * (1 if c.value_head else c.vocab_size)
-        return c.num_layers * (attn + mlp) + head
+        return c.num_layers * self._attention_params() + sum(self._mlp_params(i) for i in range(c.num_layers)) + head
 
     def forward_flops(self, batch_seqlens: Sequence[int]) -> float:
         c = self.cfg
         tokens = float(sum(batch_seqlens))
         dense = 2.0 * self.dense_params_per_token() * tokens
-        attn = 2.0 * 2.0 * c.num_layers * c.num_heads * c.head_dim * sum(0.5 * s * s for s in batch_seqlens)
-        return dense + attn
+        pairs = sum(0.5 * s * s for s in batch_seqlens)              # causal (query, key) pairs
+        if c.is_mla:
+            per_pair = c.num_heads * (c.qk_nope_head_dim + c.qk_rope_head_dim + c.v_head_dim)   # scores + values
+        else:
+            per_pair = 2.0 * c.num_heads * c.head_dim
+        return dense + 2.0 * c.num_layers * per_pair * pairs
 
     def estimate_flops(self, batch_seqlens: Sequence[int], delta_time: float,
                        forward_only: bool = False) -> Tuple[float, float]:

@@ -239,3 +239,20 @@ def test_custom_async_server_is_loaded_from_a_file(tmp_path):
     agent.custom_async_server.name = "Missing"
     with pytest.raises(AttributeError):
         make_async_server("e", None, agent)
+
+
+def test_flops_counter_counts_active_parameters_per_family():
+    """GEMM parameters one token touches: dense 7B, a routed mixture of experts, and the DeepSeek-V3 family (latent
+    attention projections, shared experts, dense first layers) land on the models' published active sizes."""
+    from siirl_b200.models.config import get_config
+    from siirl_b200.utils.model_utils.flops_counter import FlopsCounter
+    active = {n: FlopsCounter(get_config(n)).dense_params_per_token() / 1e9
+              for n in ("qwen2.5-7b", "qwen3-30b-a3b", "moonlight-16b-a3b", "deepseek-v3")}
+    assert 6.9 < active["qwen2.5-7b"] < 7.2              # 7.6 B with the input embedding, which is no GEMM
+    assert 2.9 < active["qwen3-30b-a3b"] < 3.4           # "A3B"
+    assert 2.2 < active["moonlight-16b-a3b"] < 3.0
+    assert 35.0 < active["deepseek-v3"] < 38.5           # 37 B active
+    f = FlopsCounter(get_config("moonlight-16b-a3b"))
+    assert f.forward_flops([2048]) > 2 * f.dense_params_per_token() * 2048          # attention adds to the GEMMs
+    achieved, _ = f.estimate_flops([1024, 1024], 1.0)
+    assert achieved == 3 * f.forward_flops([1024, 1024]) / 1e12
