@@ -75,6 +75,8 @@ def init_distributed(config: SiiRLArguments) -> int:
 def run_rank(config: SiiRLArguments):
     from .dag_worker.dagworker import DAGWorker
     from .execution.scheduler.launch import start_heartbeat
+    from .utils.logger.logging_utils import set_basic_config
+    set_basic_config()
     start_heartbeat(config.fault.heartbeat_interval_s)
     world = init_distributed(config)
     validate_config(config, world)

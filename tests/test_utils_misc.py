@@ -256,3 +256,26 @@ def test_flops_counter_counts_active_parameters_per_family():
     assert f.forward_flops([2048]) > 2 * f.dense_params_per_token() * 2048          # attention adds to the GEMMs
     achieved, _ = f.estimate_flops([1024, 1024], 1.0)
     assert achieved == 3 * f.forward_flops([1024, 1024]) / 1e12
+
+
+def test_logging_setup_writes_rank_tagged_records(tmp_path, monkeypatch, capsys):
+    import logging
+
+    from siirl_b200.utils.logger import logging_utils as LU
+    monkeypatch.setenv("SIIRL_LOG_DIR", str(tmp_path))
+    monkeypatch.setenv("SIIRL_LOG_LEVEL", "debug")
+    monkeypatch.setenv("RANK", "3")
+    root = LU.set_basic_config(force=True)
+    assert root.level == logging.DEBUG and LU.set_basic_config() is root           # second call changes nothing
+    logging.getLogger("siirl_b200.engine.something").debug("hello %d", 7)
+    LU.log_with_rank("only zero", 1, log_only_rank_0=True)
+    LU.log_with_rank("everyone", 1)
+    LU.DecoratorLoggerBase("[actor]", rank=0).log("via print")
+    for h in root.handlers:
+        h.flush()
+    text = (tmp_path / "siirl_rank3.log").read_text()
+    assert "rank 3" in text and "hello 7" in text and "[Rank 1] everyone" in text and "only zero" not in text
+    assert "via print" in capsys.readouterr().out
+    monkeypatch.delenv("SIIRL_LOG_DIR")
+    monkeypatch.setenv("SIIRL_LOG_LEVEL", "nonsense")
+    assert LU.set_basic_config(force=True).level == logging.INFO
