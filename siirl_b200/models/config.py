@@ -217,6 +217,32 @@ class DecoderConfig:
     def to_dict(self) -> Dict[str, Any]:
         return asdict(self)
 
+    @classmethod
+    def from_dict(cls, d: Dict[str, Any]) -> "DecoderConfig":
+        """Inverse of ``to_dict`` (checkpoint manifests keep the model configuration in that form); unknown keys of
+        a newer version are dropped."""
+        import dataclasses
+
+        def build(kind, val):
+            if val is None or not isinstance(val, dict):
+                return val
+            names = {f.name for f in dataclasses.fields(kind)}
+            return kind(**{k: v for k, v in val.items() if k in names})
+        d = dict(d)
+        for key, kind in (("vision", VisionConfig), ("vit", ViTConfig), ("moonvit", MoonViTConfig)):
+            d[key] = build(kind, d.get(key))
+        pr = d.get("prismatic")
+        if isinstance(pr, dict):
+            pr = dict(pr)
+            pr["featurizer"] = build(ViTConfig, pr.get("featurizer"))
+            pr["fused_featurizer"] = build(ViTConfig, pr.get("fused_featurizer"))
+            d["prismatic"] = build(PrismaticConfig, pr)
+        for key in ("lora_targets", "mrope_section"):
+            if isinstance(d.get(key), list) and key == "lora_targets":
+                d[key] = tuple(d[key])
+        names = {f.name for f in dataclasses.fields(cls)}
+        return cls(**{k: v for k, v in d.items() if k in names})
+
     # ---- HF interchange -----------------------------------------------------------------------
     @classmethod
     def from_hf_config(cls, cfg: Dict[str, Any]) -> "DecoderConfig":

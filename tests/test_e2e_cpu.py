@@ -434,3 +434,33 @@ def test_validation_generations_are_dumped_per_rank(tmp_path):
     assert files == ["step_1_rank_0.json", "step_1_rank_1.json"], files
     rows = json.load(open(tmp_path / "dump" / files[1]))
     assert rows and rows[0]["rank"] == 1 and {"data_source", "input", "output", "score", "global_step"} <= set(rows[0])
+
+
+def test_offline_export_of_a_two_rank_checkpoint(tmp_path):
+    """A checkpoint written by two ranks (one parameter slice each) is reassembled in one process and written as a
+    Hugging Face directory that loads back into the same weights."""
+    import torch
+
+    from siirl_b200.models.config import DecoderConfig, get_config
+    from siirl_b200.models.decoder import build_model
+    from siirl_b200.models.hf_io import load_hf_weights
+    from siirl_b200.utils.checkpoint.export_hf import main as export_main
+    out = _run([f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=1", "trainer.save_freq=1"],
+               tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    role = tmp_path / "c" / "global_step_1" / "actor_agent_0"
+    assert (role / "model_world_size_2_rank_1.pt").exists()
+    assert export_main(["--checkpoint", str(role), "--out", str(tmp_path / "hf"), "--dtype", "float32"]) == 0
+    cfg = DecoderConfig.from_hf_config(json.load(open(tmp_path / "hf" / "config.json")))
+    assert cfg.hidden_size == get_config("tiny").hidden_size
+    m = build_model(cfg, dtype=torch.float32, device="cpu", seed=123)
+    load_hf_weights(m, str(tmp_path / "hf"))
+    flat = torch.cat([torch.load(role / f"model_world_size_2_rank_{r}.pt", weights_only=False)["flat"].float()
+                      for r in range(2)])
+    manifest = json.load(open(role / "manifest.json"))
+    for name, p in m.named_parameters():
+        o, k, shape = manifest["offsets"][name]
+        assert torch.allclose(p.detach().float().reshape(-1), flat[o:o + k], atol=1e-6), name
+    os.remove(role / "model_world_size_2_rank_1.pt")
+    with pytest.raises(FileNotFoundError):
+        export_main(["--checkpoint", str(role), "--out", str(tmp_path / "hf2")])
