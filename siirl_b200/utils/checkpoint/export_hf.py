@@ -6,9 +6,9 @@ A training checkpoint holds one slice of the flat bf16 parameter buffer per rank
 (``model_world_size_<W>_rank_<r>.pt``) plus a manifest with the parameter offsets and the model configuration.  This
 reads all slices in one process, rebuilds the model and writes ``config.json`` + safetensors under the family's
 checkpoint names (``models/hf_io.py``), the same files ``checkpoint.contents=[..., hf_model]`` writes during
-training.  ``--tokenizer`` copies a tokenizer directory beside the weights.  Expert-parallel and tensor-parallel
-checkpoints keep per-rank expert / slice files that only the layout that wrote them can read: export those from the
-training job with ``hf_model`` in ``checkpoint.contents``.
+training.  ``--tokenizer`` copies a tokenizer directory beside the weights.  Expert-parallel, parameter-sharded
+(``sharding=zero3``) and tensor-parallel checkpoints keep per-rank files that only the layout that wrote them can
+read: export those from the training job with ``hf_model`` in ``checkpoint.contents``.
 """
 from __future__ import annotations
 
@@ -30,8 +30,9 @@ def export(checkpoint: str, out: str, tokenizer: Optional[str] = None, dtype: st
     with open(os.path.join(checkpoint, "manifest.json")) as f:
         manifest = json.load(f)
     if manifest.get("expert_parallel"):
-        raise ValueError("expert-parallel checkpoint: the experts live in per-rank files of the layout that wrote "
-                         "them; export from the training job with hf_model in checkpoint.contents")
+        raise ValueError("expert-parallel or parameter-sharded (sharding=zero3) checkpoint: part of the weights lives "
+                         "in per-rank files of the layout that wrote them; export from the training job with "
+                         "hf_model in checkpoint.contents")
     if os.path.isdir(os.path.join(checkpoint, "tp_rank_0")):
         raise ValueError("tensor-parallel training checkpoint (tp_rank_* directories): export from the training job")
     if manifest.get("model_config") is None or manifest.get("offsets") is None:
