@@ -774,7 +774,9 @@ class DAGWorker:
                     self._dapo_gen_batches += 1
                     return None
                 nxt = self.taskgraph.get_dependents(node.node_id)
-                enforce = node.node_role == NodeRole.DYNAMIC_SAMPLING
+                enforce = node.node_role == NodeRole.DYNAMIC_SAMPLING or (
+                    node.node_role == NodeRole.ROLLOUT and self._dist and self.world_size > 1
+                    and bool(getattr(self.config.data, "rebalance_after_rollout", False)))
                 for child in nxt:
                     cdp = self._get_node_dp_info(child)[0]
                     self.put_data_to_buffers(child.node_id, cur, dp_size, cdp, enforce_buffer=enforce, tp_rank=tp_rank)

@@ -33,6 +33,36 @@ def _small_at_both_ends(idxs: List[int], tokens: List[int]) -> List[int]:
     return s[::2] + s[1::2][::-1]
 
 
+def balanced_plan(tokens: List[int], group_keys: List[Any], parts: int) -> List[List[int]]:
+    """Length-balanced split of ``len(tokens)`` samples into ``parts`` equal-sized partitions (indices into the
+    lists).  Samples that belong together -- entries with the same non-``None`` ``group_keys`` value: the
+    responses to one prompt -- stay on one partition whenever all groups have the same size and that size divides
+    the partition size, because group-relative advantages (GRPO, RLOO) are computed per rank on the rows it holds;
+    otherwise single samples are balanced."""
+    work = calculate_workload(tokens).tolist()
+    n = len(tokens)
+    by_key: Dict[Any, List[int]] = {}
+    groups: List[List[int]] = []
+    for i, k in enumerate(group_keys):
+        if k is None:
+            groups.append([i])
+        elif k in by_key:
+            by_key[k].append(i)
+        else:
+            by_key[k] = [i]
+            groups.append(by_key[k])
+    size = len(groups[0]) if groups else 1
+    whole = (size > 1 and all(k is not None for k in group_keys) and all(len(g) == size for g in groups)
+             and n % parts == 0 and (n // parts) % size == 0)
+    if not whole:
+        plan = get_seqlen_balanced_partitions(work, parts, equal_size=True)
+        return [_small_at_both_ends(p, tokens) for p in plan]
+    gwork = [sum(work[i] for i in g) for g in groups]
+    gtok = [sum(tokens[i] for i in g) for g in groups]
+    gplan = get_seqlen_balanced_partitions(gwork, parts, equal_size=True)
+    return [[i for gi in _small_at_both_ends(part, gtok) for i in groups[gi]] for part in gplan]
+
+
 class DataCoordinator:
     def __init__(self, nnodes: int = 1, ppo_mini_batch_size: int = 0, world_size: int = 1,
                  group: Optional[dist.ProcessGroup] = None, comm=None):
@@ -99,9 +129,7 @@ class DataCoordinator:
     @staticmethod
     def _apply_length_balancing(infos: Sequence[SampleInfo], partitions: int) -> List[List[int]]:
         tokens = [max(int(i.sum_tokens), 1) for i in infos]
-        work = calculate_workload(tokens).tolist()
-        plan = get_seqlen_balanced_partitions(work, partitions, equal_size=True)
-        return [_small_at_both_ends(p, tokens) for p in plan]
+        return balanced_plan(tokens, [i.uid for i in infos], partitions)
 
     def get_all_by_filter(self, filter_plugin: Callable[[SampleInfo], bool]) -> List[Any]:
         with self._lock:
@@ -150,19 +178,20 @@ class DataCoordinator:
         world = dist.get_world_size(self.group)
         me = dist.get_rank(self.group)
         mine = [(info, seq) for info, _, seq in self._queue if filter_plugin is None or filter_plugin(info)]
-        meta_local = [(seq, int(info.sum_tokens)) for info, seq in mine]
+        meta_local = [(seq, int(info.sum_tokens), info.uid) for info, seq in mine]
         gathered: List[Any] = [None] * world
         dist.all_gather_object(gathered, (meta_local, dp_rank), group=self.group)
-        flat = [(seq, r, tok) for r, (metas, _) in enumerate(gathered) for (seq, tok) in metas]
+        flat = [(seq, r, tok, uid) for r, (metas, _) in enumerate(gathered) for (seq, tok, uid) in metas]
         need = batch_size * dp_size
         if len(flat) < need:
             return []
         flat.sort(key=lambda x: (x[0], x[1]))
         chosen = flat[:need]
-        tokens = [max(t, 1) for _, _, t in chosen]
+        tokens = [max(t, 1) for _, _, t, _ in chosen]
         if balance and dp_size > 1:
-            plan = get_seqlen_balanced_partitions(calculate_workload(tokens).tolist(), dp_size, equal_size=True)
-            plan = [_small_at_both_ends(p, tokens) for p in plan]
+            # a prompt's responses come from one producer: (producer, uid) names the group
+            keys = [(src, uid) if uid is not None else None for _, src, _, uid in chosen]
+            plan = balanced_plan(tokens, keys, dp_size)
         else:
             plan = [list(range(i * batch_size, (i + 1) * batch_size)) for i in range(dp_size)]
         dp_of_rank = [g[1] for g in gathered]
@@ -171,7 +200,7 @@ class DataCoordinator:
         send: List[List[Tuple[int, Sample]]] = [[] for _ in range(world)]
         for dst in range(world):
             for pos, ci in enumerate(plan[dp_of_rank[dst]]):
-                seq, src, _ = chosen[ci]
+                seq, src = chosen[ci][0], chosen[ci][1]
                 if src == me:
                     send[dst].append((pos, local_by_seq[seq]))
         recv = self._exchange(send)
@@ -179,7 +208,7 @@ class DataCoordinator:
         for part in recv:
             for pos, s in part:
                 got[pos] = s
-        taken = {seq for seq, src, _ in chosen if src == me}
+        taken = {c[0] for c in chosen if c[1] == me}
         with self._lock:
             self._queue = deque(e for e in self._queue if e[2] not in taken)
         assert all(s is not None for s in got), "redistribution lost a sample"

@@ -522,6 +522,10 @@ class DataArguments:
     multi_agent: bool = False
     auto_repeat: bool = False
     num_loader_workers: int = 8
+    # native addition: after the rollout node the samples go through the data coordinator, which hands every
+    # data-parallel rank the same number of whole prompt groups with balanced token counts (ranks that drew long
+    # responses otherwise hold up the scoring and training passes of the others)
+    rebalance_after_rollout: bool = False
     force_on_the_fly: bool = False
     processor: ProcessorArguments = _dc(ProcessorArguments)
     # native addition: generate a synthetic dataset instead of reading parquet

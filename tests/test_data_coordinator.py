@@ -123,3 +123,30 @@ def test_batch_container_ops():
     assert c.batch_size == 6 and c.chunk(4)[0].batch_size == 2 and len(c.split(4)) == 2
     with pytest.raises(ValueError):
         Batch({"a": torch.zeros(2)}, {"n": [1, 2, 3]})
+
+
+def test_balanced_plan_keeps_the_responses_of_a_prompt_together():
+    """Group-relative advantages are computed per rank: redistribution moves whole groups when it can."""
+    from siirl_b200.data_coordinator.data_buffer import balanced_plan
+    import random
+    rnd = random.Random(0)
+    n_groups, size, parts = 12, 4, 3
+    keys = [("p", g) for g in range(n_groups) for _ in range(size)]
+    order = list(range(len(keys)))
+    rnd.shuffle(order)                                            # producers interleave in the global FIFO order
+    keys = [keys[i] for i in order]
+    tokens = [rnd.randint(10, 400) for _ in keys]
+    plan = balanced_plan(tokens, keys, parts)
+    assert sorted(i for p in plan for i in p) == list(range(len(keys))) and {len(p) for p in plan} == {16}
+    for p in plan:
+        per_key = {}
+        for i in p:
+            per_key[keys[i]] = per_key.get(keys[i], 0) + 1
+        assert set(per_key.values()) == {size}                    # every group is whole on its partition
+    loads = [sum(tokens[i] for i in p) for p in plan]
+    assert max(loads) - min(loads) < 0.25 * max(loads)
+    # ragged groups (or no uid): falls back to balancing single samples
+    ragged = balanced_plan(tokens[:-2], keys[:-2], 2)
+    assert sorted(i for p in ragged for i in p) == list(range(len(keys) - 2))
+    nokeys = balanced_plan(tokens, [None] * len(tokens), parts)
+    assert {len(p) for p in nokeys} == {16}

@@ -464,3 +464,16 @@ def test_offline_export_of_a_two_rank_checkpoint(tmp_path):
     os.remove(role / "model_world_size_2_rank_1.pt")
     with pytest.raises(FileNotFoundError):
         export_main(["--checkpoint", str(role), "--out", str(tmp_path / "hf2")])
+
+
+def test_rebalance_after_rollout_two_ranks(tmp_path):
+    """``data.rebalance_after_rollout``: after generation the ranks exchange whole prompt groups so that their token
+    counts match; group-relative advantages still see complete groups (mean advantage ~ 0, finite gradients)."""
+    out = _run(["data.rebalance_after_rollout=True", f"trainer.default_local_dir={tmp_path / 'c'}",
+                "trainer.total_training_steps=2", "trainer.save_freq=-1"], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    for r in m:
+        assert abs(r["critic/advantages/mean"]) < 0.2 and r["actor/grad_norm"] > 0
+        assert abs(r["actor/ppo_kl"]) < 1e-3
