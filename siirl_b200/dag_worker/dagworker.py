@@ -735,7 +735,10 @@ class DAGWorker:
             with _Timer("data_loading", self.timing_raw, False):
                 batch = self.dataloader.run(epoch=epoch)
                 self.last_h2d_bytes = 0
-                batch = preprocess_dataloader(batch, n)
+                # group ids unique over ranks and over the generation batches of this run: (draw, rank, prompt)
+                self._uid_draw = getattr(self, "_uid_draw", -1) + 1
+                batch = preprocess_dataloader(batch, n, uid_offset=(self._uid_draw * max(self.world_size, 1)
+                                                                    + self._rank) * batch.batch_size)
                 if self.device.type == "cuda":
                     batch = batch.pin_memory()
                     self.last_h2d_bytes = batch.nbytes()

@@ -39,11 +39,13 @@ class Sample:
         return sum(t.numel() * t.element_size() for t in self.tensors.values())
 
 
-def preprocess_dataloader(batch: Batch, n: int) -> Batch:
-    """Repeat each prompt ``n`` times (interleaved) and attach ``uid`` = index of the prompt inside this
-    rank-local batch, so that a prompt group never spans ranks at advantage time."""
+def preprocess_dataloader(batch: Batch, n: int, uid_offset: int = 0) -> Batch:
+    """Repeat each prompt ``n`` times (interleaved) and attach the integer group id ``uid`` = ``uid_offset`` + index
+    of the prompt inside this rank-local batch.  Callers that let samples travel between ranks (or accumulate
+    several generation batches) pass offsets that do not overlap, so that two prompts never share an id when a rank
+    computes group-relative advantages over the rows it holds."""
     bs = batch.batch_size
-    uid = torch.arange(bs, dtype=torch.int64)
+    uid = torch.arange(bs, dtype=torch.int64) + int(uid_offset)
     dev = next(iter(batch.tensors.values())).device if batch.tensors else torch.device("cpu")
     batch["uid"] = uid.to(dev)
     return batch.repeat(n, interleave=True) if n > 1 else batch

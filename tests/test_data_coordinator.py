@@ -150,3 +150,17 @@ def test_balanced_plan_keeps_the_responses_of_a_prompt_together():
     assert sorted(i for p in ragged for i in p) == list(range(len(keys) - 2))
     nokeys = balanced_plan(tokens, [None] * len(tokens), parts)
     assert {len(p) for p in nokeys} == {16}
+
+
+def test_group_ids_do_not_collide_across_ranks_and_draws():
+    from siirl_b200.data_coordinator.sample import preprocess_dataloader
+    ids = set()
+    for draw in range(2):
+        for rank in range(3):
+            b = Batch({"input_ids": torch.zeros(4, 5, dtype=torch.long)})
+            out = preprocess_dataloader(b, 2, uid_offset=(draw * 3 + rank) * 4)
+            u = out["uid"].tolist()
+            assert u[0] == u[1] and u[2] == u[3] and len(set(u)) == 4
+            assert not (ids & set(u))
+            ids |= set(u)
+    assert len(ids) == 24
