@@ -284,3 +284,46 @@ def test_action_statistics_of_a_checkpoint(tmp_path):
     other.mkdir()
     (other / "config.json").write_text(_json.dumps({"norm_stats": {"bridge_orig": {"action": {"q01": [0.0], "q99": [1.0]}}}}))
     assert load_action_norm_stats(str(other), "bridge_orig")["q99"] == [1.0]
+
+
+@pytest.mark.parametrize("preset", ["tiny-vl", "tiny-openvla"])
+def test_processor_with_two_cameras(preset):
+    """Two views per step: stacked along the height in storage, one placeholder run and one rope block per view; the
+    second view changes the hidden states of the text that follows."""
+    from siirl_b200.models.config import get_config
+    from siirl_b200.models.decoder import build_model
+    from siirl_b200.models.embodied.vla import VLAProcessor
+    from siirl_b200.ops.attention import SeqInfo
+
+    class Tok:
+        def encode(self, s):
+            return [5 + (ord(c) % 50) for c in s][:12]
+
+    cfg = get_config(preset)
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=2)
+    one, two = VLAProcessor(cfg, Tok(), image_size=56), VLAProcessor(cfg, Tok(), image_size=56, num_images=2)
+    assert two.image_tokens == 2 * one.tokens_per_image
+    p = two.prompt_ids("pick up the block")
+    assert len(p) == len(one.prompt_ids("pick up the block")) + one.tokens_per_image
+    g = torch.Generator().manual_seed(0)
+    frames = torch.randint(0, 255, (1, 2, 64, 64, 3), generator=g, dtype=torch.uint8)
+    imgs = two.resize(frames)
+    S = two.image_size
+    assert imgs.shape == (1, 2 * S, S, 3) and torch.equal(imgs[:, :S], one.resize(frames[:, 0]))
+
+    def hidden(images):
+        pv, grid = two.patchify(images, torch.float32)
+        info = SeqInfo([len(p)])
+        pos = two.rope_layout(len(p))[0] if two.prismatic is None else info.positions
+        first = torch.tensor([0])
+        return model.forward_hidden(torch.tensor(p), pos, info, pixel_values=pv, image_grid_thw=grid,
+                                    image_mask=two.image_mask(first, len(p)))
+    assert two.patchify(imgs, torch.float32)[1].shape[0] == 2
+    with torch.no_grad():
+        a = hidden(imgs)
+        other = imgs.clone()
+        other[:, S:] = 255 - other[:, S:]                                  # change the wrist view only
+        b = hidden(other)
+    assert a.shape[0] == len(p) and (a[-1] - b[-1]).abs().max() > 1e-6
+    mm = two.mm_inputs(imgs, [len(p)], torch.float32)[0]
+    assert mm["image_grid_thw"].shape[0] == 2 and mm["rope_positions"].shape[1] == len(p)
