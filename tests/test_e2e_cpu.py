@@ -338,9 +338,13 @@ def test_grpo_with_hybrid_sharding(tmp_path):
     base = ["trainer.n_gpus_per_node=4", "data.max_response_length=16",
             "actor_rollout_ref.model.enable_gradient_checkpointing=True",
             "actor_rollout_ref.actor.fsdp_config.fsdp_size=2"]
-    out = _run([*base, "trainer.total_training_steps=1"], tmp_path / "zero2")
+    # the first job also decodes with tensor-parallel engines of two ranks each: rollout data-parallel width 2,
+    # training width 4, so the samples are redistributed (whole prompt groups, ids unique over the producers)
+    out = _run([*base, "trainer.total_training_steps=1", "actor_rollout_ref.rollout.tensor_model_parallel_size=2",
+                "data.train_batch_size=16", "actor_rollout_ref.actor.ppo_mini_batch_size=16"], tmp_path / "zero2")
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
-    assert _metrics(tmp_path / "zero2")[0]["actor/grad_norm"] > 0
+    m0 = _metrics(tmp_path / "zero2")[0]
+    assert m0["actor/grad_norm"] > 0 and abs(m0["actor/ppo_kl"]) < 1e-3 and abs(m0["critic/advantages/mean"]) < 0.2
     z3 = [*base, "actor_rollout_ref.actor.fsdp_config.sharding=zero3", f"trainer.default_local_dir={tmp_path / 'c'}"]
     out = _run([*z3, "trainer.total_training_steps=2", "trainer.save_freq=2"], tmp_path / "zero3")
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
