@@ -6,11 +6,17 @@ import sys
 import pytest
 
 
+def _port() -> str:
+    """A port that is free now: other jobs may share the machine, fixed port numbers collide."""
+    from siirl_b200.execution.scheduler.launch import find_free_port
+    return str(find_free_port())
+
+
 def test_tensor_parallel_two_cpu_ranks():
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ, TP_DEVICE="cpu", OMP_NUM_THREADS="2")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29541", os.path.join(here, "tp_worker.py")]
+           "127.0.0.1", "--master-port", _port(), os.path.join(here, "tp_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_OK" in out.stdout
@@ -20,7 +26,7 @@ def test_expert_parallel_two_cpu_ranks():
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ, EP_DEVICE="cpu", OMP_NUM_THREADS="2")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29545", os.path.join(here, "ep_worker.py")]
+           "127.0.0.1", "--master-port", _port(), os.path.join(here, "ep_worker.py")]
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "EP_OK" in out.stdout
