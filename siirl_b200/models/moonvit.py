@@ -81,6 +81,9 @@ class MoonViT(nn.Module):
         self.patch_dim = cfg.in_channels * cfg.patch_size * cfg.patch_size
         self.patch_dim_padded = (self.patch_dim + 7) // 8 * 8
         self.patch_embed_weight = _param((H, self.patch_dim_padded), dtype, device, 0.02, gen)
+        if self.patch_dim_padded != self.patch_dim:
+            with torch.no_grad():       # columns that only ever meet the zero padding of the input rows
+                self.patch_embed_weight[:, self.patch_dim:].zero_()
         self.patch_embed_bias = _param((H,), dtype, device, 0, gen)
         self.pos_emb = _param((cfg.init_pos_emb_height, cfg.init_pos_emb_width, H), dtype, device, 0.02, gen)
         self.blocks = nn.ModuleList([MoonViTBlock(cfg, dtype, device, gen, _param) for _ in range(cfg.depth)])

@@ -55,6 +55,9 @@ class VisionTower(nn.Module):
         self.patch_dim_padded = (self.patch_dim + 7) // 8 * 8
         H = cfg.hidden_size
         self.patch_embed_weight = _param((H, self.patch_dim_padded), dtype, device, 0.02, gen)
+        if self.patch_dim_padded != self.patch_dim:
+            with torch.no_grad():       # columns that only ever meet the zero padding of the input rows
+                self.patch_embed_weight[:, self.patch_dim:].zero_()
         self.blocks = nn.ModuleList([VisionBlock(cfg, dtype, device, gen, _param) for _ in range(cfg.depth)])
         m = cfg.spatial_merge_size ** 2
         self.merger_norm = _param((H,), dtype, device, -1, gen)

@@ -52,6 +52,9 @@ class ViTEncoder(nn.Module):
         self.patch_dim = cfg.in_channels * cfg.patch_size * cfg.patch_size
         self.patch_dim_padded = (self.patch_dim + 7) // 8 * 8
         self.patch_embed_weight = _param((H, self.patch_dim_padded), dtype, device, 0.02, gen)
+        if self.patch_dim_padded != self.patch_dim:
+            with torch.no_grad():       # columns that only ever meet the zero padding of the input rows
+                self.patch_embed_weight[:, self.patch_dim:].zero_()
         self.patch_embed_bias = _param((H,), dtype, device, 0, gen)
         n_prefix = cfg.num_prefix_tokens
         self.prefix_tokens = _param((max(n_prefix, 1), H), dtype, device, 0.02, gen) if n_prefix else None
