@@ -463,3 +463,26 @@ def test_optional_step_features_two_ranks(tmp_path):
     os.remove(role / "model_world_size_2_rank_1.pt")
     with pytest.raises(FileNotFoundError):
         export_main(["--checkpoint", str(role), "--out", str(tmp_path / "hf2")])
+
+
+def test_offline_export_of_a_parameter_sharded_checkpoint(tmp_path):
+    """``sharding=zero3`` on two ranks: every layer's flat unit is split over the ranks.  The offline exporter puts
+    the pieces back together; its output equals the Hugging Face directory the training job wrote itself."""
+    import torch
+    from safetensors.torch import load_file
+
+    from siirl_b200.utils.checkpoint.export_hf import main as export_main
+    out = _run(["actor_rollout_ref.actor.fsdp_config.sharding=zero3", "data.max_response_length=16",
+                "actor_rollout_ref.model.enable_gradient_checkpointing=True",
+                "actor_rollout_ref.actor.checkpoint.contents=[model,optimizer,extra,hf_model]",
+                f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=1", "trainer.save_freq=1"],
+               tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    role = tmp_path / "c" / "global_step_1" / "actor_agent_0"
+    assert (role / "experts_world_size_2_rank_1.pt").exists()
+    assert export_main(["--checkpoint", str(role), "--out", str(tmp_path / "hf"), "--dtype", "float32"]) == 0
+    want = load_file(str(role / "huggingface" / "model.safetensors"))
+    got = load_file(str(tmp_path / "hf" / "model.safetensors"))
+    assert set(want) == set(got)
+    for k in want:
+        assert torch.equal(want[k], got[k]), k
