@@ -1,0 +1,87 @@
+"""The parquet data path users run: row-group slices per data-parallel rank, chat-format prompts, ground truth under
+``reward_model``, over-long prompts, and a GRPO step on a GSM8K-shaped file scored by the gsm8k rule."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pa = pytest.importorskip("pyarrow")
+import pyarrow.parquet as pq  # noqa: E402
+
+from siirl_b200.data_coordinator.dataloader import DataLoaderNode, load_tokenizer  # noqa: E402
+from siirl_b200.data_coordinator.dataloader.partitioned_dataset import PartitionedRLHFDataset  # noqa: E402
+from siirl_b200.params import parse_config  # noqa: E402
+
+
+def _write(path, n, start=0, long_every=0, row_group_size=7):
+    rows = []
+    for i in range(start, start + n):
+        q = f"What is {i} plus {i + 1}?" + (" please explain in great detail" * 20 if long_every and i % long_every == 0 else "")
+        rows.append({"data_source": "openai/gsm8k", "prompt": [{"role": "user", "content": q}], "ability": "math",
+                     "reward_model": {"style": "rule", "ground_truth": str(2 * i + 1)},
+                     "extra_info": {"index": i, "split": "train"}})
+    pq.write_table(pa.Table.from_pylist(rows), str(path), row_group_size=row_group_size)
+    return rows
+
+
+def test_row_group_slices_cover_the_files_once(tmp_path):
+    _write(tmp_path / "a.parquet", 23)
+    _write(tmp_path / "b.parquet", 18, start=23)
+    args = [f"data.train_files=[{tmp_path / 'a.parquet'},{tmp_path / 'b.parquet'}]", f"data.val_files={tmp_path / 'b.parquet'}",
+            "data.max_prompt_length=64", "actor_rollout_ref.model.arch_preset=tiny", "trainer.n_gpus_per_node=1"]
+    cfg = parse_config(args)
+    tok = load_tokenizer(None, 1024)
+    seen = []
+    for rank in range(3):
+        ds = PartitionedRLHFDataset(cfg, tok, None, rank, 3, is_eval=False)
+        assert len(ds) == 41 // 3                                       # training drops the remainder
+        seen += [r["extra_info"]["index"] for r in ds.rows]
+        item = ds[0]
+        assert item["input_ids"].shape == (64,) and int(item["attention_mask"].sum()) == len(item["raw_prompt_ids"])
+        assert item["data_source"] == "openai/gsm8k" and item["reward_model"]["ground_truth"] == str(2 * ds.rows[0]["extra_info"]["index"] + 1)
+    assert seen == list(range(39))                                      # contiguous slices across the file boundary
+    val = [PartitionedRLHFDataset(cfg, tok, None, r, 4, is_eval=True, drop_last=False) for r in range(4)]
+    assert [len(v) for v in val] == [5, 5, 5, 5]                        # 18 rows: the last rank is padded
+    assert sum(r["padded_duplicate"] for v in val for r in v.rows) == 2
+    real = [r["extra_info"]["index"] for v in val for r in v.rows if not r["padded_duplicate"]]
+    assert real == list(range(23, 41))
+
+
+def test_overlong_prompts_are_filtered_or_truncated(tmp_path):
+    _write(tmp_path / "a.parquet", 12, long_every=4)
+    base = [f"data.train_files={tmp_path / 'a.parquet'}", "data.max_prompt_length=48",
+            "actor_rollout_ref.model.arch_preset=tiny", "trainer.n_gpus_per_node=1"]
+    tok = load_tokenizer(None, 1024)
+    kept = PartitionedRLHFDataset(parse_config(base + ["data.filter_overlong_prompts=True"]), tok, None, 0, 1)
+    assert len(kept) == 9 and all(r["extra_info"]["index"] % 4 for r in kept.rows)
+    ds = PartitionedRLHFDataset(parse_config(base + ["data.truncation=left"]), tok, None, 0, 1)
+    assert len(ds) == 12 and int(ds[0]["attention_mask"].sum()) == 48
+    with pytest.raises(Exception):
+        PartitionedRLHFDataset(parse_config(base + ["data.truncation=error"]), tok, None, 0, 1)[0]
+
+
+def test_grpo_step_on_a_gsm8k_shaped_parquet_file(tmp_path):
+    _write(tmp_path / "train.parquet", 32)
+    _write(tmp_path / "test.parquet", 8, start=100)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, OMP_NUM_THREADS="2", SIIRL_LOG_DIR=str(tmp_path / "log"))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    args = ["algorithm.adv_estimator=grpo", f"data.train_files={tmp_path / 'train.parquet'}",
+            f"data.val_files={tmp_path / 'test.parquet'}", "data.max_prompt_length=64", "data.max_response_length=16",
+            "data.train_batch_size=4", "actor_rollout_ref.model.arch_preset=tiny", "actor_rollout_ref.rollout.n=4",
+            "actor_rollout_ref.rollout.max_num_seqs=16", "actor_rollout_ref.actor.ppo_mini_batch_size=4",
+            "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8", "trainer.n_gpus_per_node=1", "trainer.device=cpu",
+            "trainer.val_before_train=True", "trainer.test_freq=1", "trainer.logger=['jsonl']",
+            "trainer.total_training_steps=2", "trainer.save_freq=-1"]
+    out = subprocess.run([sys.executable, "-m", "siirl_b200.main_dag", *args], env=env, cwd=root, capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    with open(tmp_path / "log" / "metrics.jsonl") as f:
+        m = [json.loads(line) for line in f]
+    assert any("val-core/openai/gsm8k/reward/mean@1" in r or "val-core/all/reward/mean" in r for r in m)
+    steps = [r for r in m if "actor/pg_loss" in r]
+    assert [r["step"] for r in steps] == [1, 2]
+    assert all(r["critic/score/mean"] == 0.0 for r in steps)       # a random model never writes "#### <answer>"
