@@ -74,7 +74,7 @@ def load_tokenizer(path: Optional[str], vocab_size: int = 1024, trust_remote_cod
             new = getattr(model_args, "new_special_tokens", None) if model_args is not None else None
             if new:
                 names = [t.strip() for t in (new.split(",") if isinstance(new, str) else list(new)) if str(t).strip()]
-                added = tok.add_special_tokens({"additional_special_tokens": names}, replace_additional_special_tokens=False)
+                added = tok.add_tokens(names, special_tokens=True)
                 if added and len(tok) > vocab_size and not getattr(model_args, "resize_vocab", False):
                     raise ValueError(f"model.new_special_tokens adds {added} token(s) beyond the model's vocabulary of "
                                      f"{vocab_size}: the embedding matrix is not resized")

@@ -85,3 +85,45 @@ def test_grpo_step_on_a_gsm8k_shaped_parquet_file(tmp_path):
     steps = [r for r in m if "actor/pg_loss" in r]
     assert [r["step"] for r in steps] == [1, 2]
     assert all(r["critic/score/mean"] == 0.0 for r in steps)       # a random model never writes "#### <answer>"
+
+
+def _make_hf_tokenizer(path):
+    """A small word-level tokenizer saved in the Hugging Face layout (tokenizer.json + tokenizer_config.json with a
+    chat template), built offline."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    words = ["<pad>", "<eos>", "<unk>", "<|user|>", "<|assistant|>", "what", "is", "plus", "?", "####"] + \
+        [str(i) for i in range(200)]
+    tk = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tk.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tk, pad_token="<pad>", eos_token="<eos>", unk_token="<unk>")
+    fast.chat_template = ("{% for m in messages %}{{ '<|' + m['role'] + '|> ' + m['content'] + ' ' }}{% endfor %}"
+                          "{% if add_generation_prompt %}{{ '<|assistant|> ' }}{% endif %}")
+    fast.save_pretrained(str(path))
+    return len(words)
+
+
+def test_hugging_face_tokenizer_directory(tmp_path):
+    """``data.tokenizer`` / ``model.path`` with tokenizer files: chat template applied, loader options honoured, new
+    special tokens must fit the model's vocabulary."""
+    import types
+    vocab = _make_hf_tokenizer(tmp_path / "tok")
+    tok = load_tokenizer(str(tmp_path / "tok"), vocab_size=vocab)
+    assert tok.pad_token_id == 0 and tok.eos_token_id == 1
+    rows = [{"data_source": "openai/gsm8k", "prompt": [{"role": "user", "content": f"what is {i} plus {i + 1} ?"}],
+             "reward_model": {"ground_truth": str(2 * i + 1)}} for i in range(6)]
+    pq.write_table(pa.Table.from_pylist(rows), str(tmp_path / "t.parquet"))
+    cfg = parse_config([f"data.train_files={tmp_path / 't.parquet'}", "data.max_prompt_length=16",
+                        "actor_rollout_ref.model.arch_preset=tiny", "trainer.n_gpus_per_node=1"])
+    ds = PartitionedRLHFDataset(cfg, tok, None, 0, 1)
+    ids = ds[2]["raw_prompt_ids"]
+    assert tok.decode(ids) == "<|user|> what is 2 plus 3 ? <|assistant|>"
+    assert ds[2]["input_ids"][-len(ids):].tolist() == ids and int(ds[2]["input_ids"][0]) == tok.pad_token_id   # left pad
+    args = types.SimpleNamespace(use_fast_tokenizer=True, split_special_tokens=False, trust_remote_code=False,
+                                 new_special_tokens="<tool>,<obs>", resize_vocab=False)
+    with pytest.raises(ValueError, match="beyond the model's vocabulary"):
+        load_tokenizer(str(tmp_path / "tok"), vocab_size=vocab, model_args=args)
+    roomy = load_tokenizer(str(tmp_path / "tok"), vocab_size=vocab + 8, model_args=args)
+    assert roomy.convert_tokens_to_ids("<tool>") == vocab and len(roomy) == vocab + 2
+    # a directory without tokenizer files falls back to the synthetic tokenizer
+    assert type(load_tokenizer(str(tmp_path), vocab_size=64)).__name__ == "SyntheticTokenizer"
