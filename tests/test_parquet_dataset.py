@@ -127,3 +127,48 @@ def test_hugging_face_tokenizer_directory(tmp_path):
     assert roomy.convert_tokens_to_ids("<tool>") == vocab and len(roomy) == vocab + 2
     # a directory without tokenizer files falls back to the synthetic tokenizer
     assert type(load_tokenizer(str(tmp_path), vocab_size=64)).__name__ == "SyntheticTokenizer"
+
+
+def test_training_from_a_checkpoint_directory(tmp_path):
+    """The launch line of a real run: ``model.path`` names a directory with ``config.json``, safetensors weights and
+    tokenizer files; data comes from parquet files.  The policy starts from the stored weights (the reference model
+    too, so the KL term starts at zero) and the exported checkpoint keeps the Hugging Face layout."""
+    from siirl_b200.models.config import get_config
+    from siirl_b200.models.decoder import build_model
+    from siirl_b200.models.hf_io import save_hf_model
+    vocab = _make_hf_tokenizer(tmp_path / "model")
+    cfg = get_config("tiny", {"vocab_size": 256, "eos_token_id": 1, "pad_token_id": 0})
+    assert vocab <= cfg.vocab_size
+    model = build_model(cfg, dtype=torch.float32, device="cpu", seed=11)
+    save_hf_model(model, str(tmp_path / "model"))
+    rows = [{"data_source": "openai/gsm8k", "prompt": [{"role": "user", "content": f"what is {i} plus {i + 1} ?"}],
+             "reward_model": {"ground_truth": str(2 * i + 1)}} for i in range(16)]
+    pq.write_table(pa.Table.from_pylist(rows), str(tmp_path / "train.parquet"))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, OMP_NUM_THREADS="2", SIIRL_LOG_DIR=str(tmp_path / "log"))
+    env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
+    args = ["algorithm.adv_estimator=grpo", f"data.train_files={tmp_path / 'train.parquet'}",
+            f"data.val_files={tmp_path / 'train.parquet'}", "data.max_prompt_length=32", "data.max_response_length=12",
+            "data.train_batch_size=4", f"actor_rollout_ref.model.path={tmp_path / 'model'}",
+            "actor_rollout_ref.rollout.n=4", "actor_rollout_ref.rollout.max_num_seqs=16",
+            "actor_rollout_ref.actor.ppo_mini_batch_size=4", "actor_rollout_ref.actor.ppo_micro_batch_size_per_gpu=8",
+            "actor_rollout_ref.actor.use_kl_loss=True", "actor_rollout_ref.actor.optim.lr=1e-4",
+            "actor_rollout_ref.actor.checkpoint.contents=[model,optimizer,extra,hf_model]",
+            "trainer.n_gpus_per_node=1", "trainer.device=cpu", "trainer.val_before_train=False",
+            "trainer.logger=['jsonl']", "trainer.total_training_steps=2", "trainer.save_freq=2",
+            f"trainer.default_local_dir={tmp_path / 'ckpt'}"]
+    out = subprocess.run([sys.executable, "-m", "siirl_b200.main_dag", *args], env=env, cwd=root, capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    with open(tmp_path / "log" / "metrics.jsonl") as f:
+        m = [json.loads(line) for line in f]
+    assert [r["step"] for r in m] == [1, 2]
+    assert m[0]["actor/kl_loss"] == 0.0                    # policy and reference both loaded the stored weights
+    hf = tmp_path / "ckpt" / "global_step_2" / "actor_agent_0" / "huggingface"
+    assert (hf / "model.safetensors").exists() and (hf / "config.json").exists() and (hf / "tokenizer.json").exists()
+    from safetensors.torch import load_file
+    new = load_file(str(hf / "model.safetensors"))
+    old = load_file(str(tmp_path / "model" / "model.safetensors"))
+    assert set(new) == set(old)
+    moved = max((new[k].float() - old[k].float()).abs().max().item() for k in old)
+    assert 0.0 < moved < 0.1                               # trained from the stored weights, not from a fresh init
