@@ -486,3 +486,17 @@ def test_offline_export_of_a_parameter_sharded_checkpoint(tmp_path):
     assert set(want) == set(got)
     for k in want:
         assert torch.equal(want[k], got[k]), k
+
+
+def test_grpo_with_a_reward_model_worker(tmp_path):
+    """``reward_model.enable``: a model with a scalar head scores the responses inside the reward node (its score is
+    added to the rule-based one); the worker lives on the same ranks as the policy."""
+    out = _run(["reward_model.enable=True", "reward_model.model.arch_preset=tiny", "reward_model.model.random_init=True",
+                "reward_model.micro_batch_size_per_gpu=8", "trainer.n_gpus_per_node=1",
+                f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=1", "trainer.save_freq=-1"],
+               tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")[0]
+    assert m["actor/grad_norm"] > 0
+    # the rule scores are 0 / 1; a random scalar head adds real-valued scores, so the mean is no multiple of 1/32
+    assert abs(m["critic/score/mean"] * 32 - round(m["critic/score/mean"] * 32)) > 1e-6
