@@ -279,3 +279,47 @@ def test_logging_setup_writes_rank_tagged_records(tmp_path, monkeypatch, capsys)
     monkeypatch.delenv("SIIRL_LOG_DIR")
     monkeypatch.setenv("SIIRL_LOG_LEVEL", "nonsense")
     assert LU.set_basic_config(force=True).level == logging.INFO
+
+
+def test_tracking_backends(tmp_path, monkeypatch, capsys):
+    """Console, jsonl and TensorBoard sinks write every scalar; an unknown sink or a sink whose package is missing
+    fails at construction, not in the middle of a run; MLflow gets flattened parameters through a stand-in module."""
+    import json
+    import sys
+    import types
+
+    import pytest
+
+    from siirl_b200.utils.logger.tracking import Tracking, _flatten_params
+    monkeypatch.setenv("SIIRL_LOG_DIR", str(tmp_path))
+    monkeypatch.setenv("TENSORBOARD_DIR", str(tmp_path / "tb"))
+    t = Tracking("proj", "exp", ["console", "jsonl", "tensorboard"], config={"a": {"b": 1}})
+    t.log({"actor/pg_loss": 0.5, "training/global_step": 1, "note": "text is skipped by scalar sinks"}, step=1)
+    t.log({"actor/pg_loss": 0.25}, step=2)
+    t.finish()
+    assert "step:2" in capsys.readouterr().out
+    rows = [json.loads(line) for line in open(tmp_path / "metrics.jsonl")]
+    assert [r["step"] for r in rows] == [1, 2] and rows[1]["actor/pg_loss"] == 0.25
+    assert any(f.startswith("events.out.tfevents") for f in os.listdir(tmp_path / "tb"))
+    with pytest.raises((ValueError, AssertionError, KeyError)):
+        Tracking("proj", "exp", ["no_such_sink"])
+    monkeypatch.setitem(sys.modules, "wandb", None)                        # importing it now raises ImportError
+    with pytest.raises(ImportError):
+        Tracking("proj", "exp", ["wandb"])
+    assert _flatten_params({"a": {"b": 1, "c": [2, {"d": 3}]}}) == {"a/b": 1, "a/c/0": 2, "a/c/1/d": 3}
+    calls = []
+    fake = types.ModuleType("mlflow")
+    fake.set_tracking_uri = lambda uri: calls.append(("uri", uri))
+    fake.set_experiment = lambda name: (calls.append(("experiment", name)), types.SimpleNamespace(experiment_id="7"))[1]
+    fake.start_run = lambda experiment_id=None, run_name=None: calls.append(("run", experiment_id, run_name))
+    fake.log_params = lambda p: calls.append(("params", dict(p)))
+    fake.log_metrics = lambda metrics, step=None: calls.append(("metrics", dict(metrics), step))
+    fake.end_run = lambda: calls.append(("end",))
+    monkeypatch.setitem(sys.modules, "mlflow", fake)
+    m = Tracking("proj", "exp", ["mlflow"], config={"trainer": {"seed": 1}})
+    m.log({"x/y@4": 1.5, "skip": "s"}, step=3)
+    m.finish()
+    kinds = [c[0] for c in calls]
+    assert "params" in kinds and ("metrics" in kinds) and kinds[-1] == "end"
+    logged = next(c for c in calls if c[0] == "metrics")
+    assert logged[2] == 3 and logged[1] == {"x/y_at_4": 1.5} and ("run", "7", "exp") in calls
