@@ -66,6 +66,11 @@ def test_grpo_two_ranks_three_steps_and_resume(tmp_path):
                 "trainer.total_training_steps=4", "trainer.resume_mode=auto"], tmp_path / "log2")
     assert out.returncode == 0, out.stderr[-4000:]
     assert [r["step"] for r in _metrics(tmp_path / "log2")] == [4]
+    # an explicit step directory instead of the tracker's latest one
+    out = _run([f"trainer.default_local_dir={tmp_path / 'other'}", "trainer.total_training_steps=3",
+                "trainer.resume_mode=resume_path", f"trainer.resume_from_path={ck / 'global_step_2'}"], tmp_path / "log3")
+    assert out.returncode == 0, out.stderr[-4000:]
+    assert [r["step"] for r in _metrics(tmp_path / "log3")] == [3]
 
 
 def test_grpo_with_sharded_parameters(tmp_path):
