@@ -505,3 +505,31 @@ def test_grpo_with_a_reward_model_worker(tmp_path):
     assert m["actor/grad_norm"] > 0
     # the rule scores are 0 / 1; a random scalar head adds real-valued scores, so the mean is no multiple of 1/32
     assert abs(m["critic/score/mean"] * 32 - round(m["critic/score/mean"] * 32)) > 1e-6
+
+
+def test_custom_pipeline_with_dynamic_batches_and_several_epochs(tmp_path):
+    """A user pipeline function (GRPO without the reference node), token-budget micro-batches, two passes over two
+    mini-batches per step (so the second pass is off-policy against the stored old log-probs), Adam moments parked in
+    host memory between steps."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env_path = os.path.join(root, "examples", "custom_pipeline_example")
+    old = os.environ.get("PYTHONPATH", "")
+    os.environ["PYTHONPATH"] = env_path + os.pathsep + old
+    try:
+        out = _run(["dag.custom_pipeline_fn=custom_grpo:grpo_without_reference",
+                    "actor_rollout_ref.actor.use_kl_loss=False",
+                    "actor_rollout_ref.actor.use_dynamic_bsz=True", "actor_rollout_ref.actor.ppo_max_token_len_per_gpu=160",
+                    "actor_rollout_ref.rollout.log_prob_use_dynamic_bsz=True",
+                    "actor_rollout_ref.rollout.log_prob_max_token_len_per_gpu=160",
+                    "actor_rollout_ref.actor.ppo_epochs=2", "actor_rollout_ref.actor.ppo_mini_batch_size=4",
+                    "actor_rollout_ref.actor.shuffle=True", "actor_rollout_ref.actor.fsdp_config.optimizer_offload=True",
+                    f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=2",
+                    "trainer.save_freq=-1"], tmp_path / "log")
+    finally:
+        os.environ["PYTHONPATH"] = old
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert [r["step"] for r in m] == [1, 2]
+    for r in m:
+        assert r["actor/grad_norm"] > 0 and "timing_s/reference_log_prob" not in r
+        assert 0.0 < abs(r["actor/ppo_kl"]) < 0.05          # the policy moved between the passes, a little
