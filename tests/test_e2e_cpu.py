@@ -533,3 +533,24 @@ def test_custom_pipeline_with_dynamic_batches_and_several_epochs(tmp_path):
     for r in m:
         assert r["actor/grad_norm"] > 0 and "timing_s/reference_log_prob" not in r
         assert 0.0 < abs(r["actor/ppo_kl"]) < 0.05          # the policy moved between the passes, a little
+
+
+@pytest.mark.parametrize("manager", ["naive", "batch"])
+def test_user_reward_function_from_a_file(tmp_path, manager):
+    """``custom_reward_function.path / name``: per-sample signature with the ``naive`` manager, one call per batch with
+    the ``batch`` manager; the scores the file returns are the ones that reach the metrics."""
+    f = tmp_path / "my_reward.py"
+    f.write_text(
+        "def per_sample(data_source, solution_str, ground_truth, extra_info=None):\n"
+        "    return 0.25\n\n"
+        "def per_batch(data_sources, solution_strs, ground_truths, extra_infos=None):\n"
+        "    assert len(data_sources) == len(solution_strs) == len(ground_truths) > 1\n"
+        "    return [0.75] * len(solution_strs)\n")
+    name, want = ("per_sample", 0.25) if manager == "naive" else ("per_batch", 0.75)
+    out = _run([f"custom_reward_function.path={f}", f"custom_reward_function.name={name}",
+                f"reward_model.reward_manager={manager}", "trainer.n_gpus_per_node=1",
+                f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=1", "trainer.save_freq=-1"],
+               tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")[0]
+    assert m["critic/score/mean"] == pytest.approx(want) and m["critic/score/max"] == pytest.approx(want)
