@@ -78,14 +78,26 @@ def test_grpo_with_sharded_parameters(tmp_path):
     for scoring and training and regathered whole for the rollout engine; save and resume included."""
     ck = tmp_path / "c"
     extra = ["actor_rollout_ref.actor.fsdp_config.sharding=zero3",
-             "actor_rollout_ref.model.enable_gradient_checkpointing=True", "data.max_response_length=16"]
+             "actor_rollout_ref.model.enable_gradient_checkpointing=True", "data.max_response_length=16",
+             "actor_rollout_ref.actor.checkpoint.contents=[model,optimizer,extra,hf_model]"]
     out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=2", "trainer.save_freq=2", *extra],
                tmp_path / "log1")
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     m = _metrics(tmp_path / "log1")
     assert [r["step"] for r in m] == [1, 2]
     assert all(r["actor/grad_norm"] > 0 for r in m)
-    assert (ck / "global_step_2" / "actor_agent_0" / "experts_world_size_2_rank_1.pt").exists()
+    role = ck / "global_step_2" / "actor_agent_0"
+    assert (role / "experts_world_size_2_rank_1.pt").exists()
+    # every layer's flat unit is split over the ranks: the offline exporter puts the pieces back together, and its
+    # output equals the Hugging Face directory the training job wrote itself
+    import torch
+    from safetensors.torch import load_file
+
+    from siirl_b200.utils.checkpoint.export_hf import main as export_main
+    assert export_main(["--checkpoint", str(role), "--out", str(tmp_path / "hf"), "--dtype", "float32"]) == 0
+    want = load_file(str(role / "huggingface" / "model.safetensors"))
+    got = load_file(str(tmp_path / "hf" / "model.safetensors"))
+    assert set(want) == set(got) and all(torch.equal(want[k], got[k]) for k in want)
     out = _run([f"trainer.default_local_dir={ck}", "trainer.total_training_steps=3", "trainer.resume_mode=auto",
                 *extra], tmp_path / "log2")
     assert out.returncode == 0, out.stderr[-4000:]
@@ -469,28 +481,6 @@ def test_optional_step_features_two_ranks(tmp_path):
     with pytest.raises(FileNotFoundError):
         export_main(["--checkpoint", str(role), "--out", str(tmp_path / "hf2")])
 
-
-def test_offline_export_of_a_parameter_sharded_checkpoint(tmp_path):
-    """``sharding=zero3`` on two ranks: every layer's flat unit is split over the ranks.  The offline exporter puts
-    the pieces back together; its output equals the Hugging Face directory the training job wrote itself."""
-    import torch
-    from safetensors.torch import load_file
-
-    from siirl_b200.utils.checkpoint.export_hf import main as export_main
-    out = _run(["actor_rollout_ref.actor.fsdp_config.sharding=zero3", "data.max_response_length=16",
-                "actor_rollout_ref.model.enable_gradient_checkpointing=True",
-                "actor_rollout_ref.actor.checkpoint.contents=[model,optimizer,extra,hf_model]",
-                f"trainer.default_local_dir={tmp_path / 'c'}", "trainer.total_training_steps=1", "trainer.save_freq=1"],
-               tmp_path / "log")
-    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
-    role = tmp_path / "c" / "global_step_1" / "actor_agent_0"
-    assert (role / "experts_world_size_2_rank_1.pt").exists()
-    assert export_main(["--checkpoint", str(role), "--out", str(tmp_path / "hf"), "--dtype", "float32"]) == 0
-    want = load_file(str(role / "huggingface" / "model.safetensors"))
-    got = load_file(str(tmp_path / "hf" / "model.safetensors"))
-    assert set(want) == set(got)
-    for k in want:
-        assert torch.equal(want[k], got[k]), k
 
 
 def test_grpo_with_a_reward_model_worker(tmp_path):
