@@ -544,3 +544,14 @@ def test_user_reward_function_from_a_file(tmp_path, manager):
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
     m = _metrics(tmp_path / "log")[0]
     assert m["critic/score/mean"] == pytest.approx(want) and m["critic/score/max"] == pytest.approx(want)
+
+
+def test_validation_only_run(tmp_path):
+    """``trainer.val_only`` with ``val_before_train``: the job validates once, logs the validation metrics at step 0
+    and stops without a training step."""
+    out = _run(["trainer.val_before_train=True", "trainer.val_only=True", "trainer.test_freq=1",
+                "trainer.n_gpus_per_node=1", f"trainer.default_local_dir={tmp_path / 'c'}",
+                "trainer.total_training_steps=3", "trainer.save_freq=-1"], tmp_path / "log")
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-4000:]
+    m = _metrics(tmp_path / "log")
+    assert len(m) == 1 and m[0]["step"] == 0 and "val-core/all/reward/mean" in m[0] and "actor/pg_loss" not in m[0]
